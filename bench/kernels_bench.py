@@ -1,0 +1,136 @@
+"""Single-GPU kernel microbenchmarks: tcgen05 GEMM vs torch.matmul (cuBLAS), decode attention vs the HBM roofline.
+
+Timing: CUDA events on the launching stream, >= 3 warm-up iterations, an L2 flush (write of a
+256 MB buffer) between timed iterations.  Peaks come from MEASURED_PEAKS.json at the repository
+root when present, else the fallback figures (6.65 TB/s, 1.59 PFLOP/s).
+
+    python bench/kernels_bench.py [--quick] [--json out.json]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from blitz_scale_b200 import ops  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+_flush = None
+
+
+def timeit(fn, iters=10, warmup=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        _flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2] * 1e-3
+
+
+def bench_gemm(shapes, out):
+    hbm, flops_peak, src = peaks()
+    for (M, N, K, epi) in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        bcols = 2 * N if epi == "silu_mul" else N
+        b = torch.randn(K, bcols, device="cuda", dtype=torch.bfloat16) * K ** -0.5
+        r = torch.randn(M, N, device="cuda", dtype=torch.bfloat16) if epi == "add" else None
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t = timeit(lambda: ops.gemm(a, b, out=c, residual=r, epilogue=epi))
+        ops.check_status()
+        cref = torch.empty(M, bcols, device="cuda", dtype=torch.bfloat16)
+        t_ref = timeit(lambda: torch.matmul(a, b, out=cref))
+        fl = 2.0 * M * bcols * K
+        by = 2.0 * (M * K + K * bcols + M * N)
+        roof = max(fl / flops_peak, by / hbm)
+        row = dict(kind="gemm", M=M, N=N, K=K, epilogue=epi, us=t * 1e6, cublas_us=t_ref * 1e6,
+                   tflops=fl / t / 1e12, gbs=by / t / 1e9, roofline_frac=roof / t, vs_cublas=t_ref / t, peaks=src)
+        out.append(row)
+        print(json.dumps(row), flush=True)
+
+
+def bench_decode_attn(cases, out):
+    hbm, _, src = peaks()
+    for (B, ctx, qh, kvh, hd, page, splits) in cases:
+        npg = (ctx + page - 1) // page
+        total = B * npg
+        kv = torch.randn(total, 2, page, kvh, hd, device="cuda", dtype=torch.bfloat16)
+        idx = torch.randperm(total, device="cuda").to(torch.int32)
+        indptr = (torch.arange(B + 1, device="cuda") * npg).to(torch.int32)
+        last = torch.full((B,), ctx - (npg - 1) * page, device="cuda", dtype=torch.int32)
+        q = torch.randn(B, qh * hd, device="cuda", dtype=torch.bfloat16)
+        o = torch.empty(B, qh * hd, device="cuda", dtype=torch.bfloat16)
+        ws = torch.empty(max(1, ops.attn_decode_workspace_bytes(B, qh, hd, splits)), dtype=torch.uint8, device="cuda")
+        t = timeit(lambda: ops.attn_decode(q, kv, idx, indptr, last, q_heads=qh, kv_heads=kvh, head_dim=hd,
+                                           page_size=page, num_splits=splits, workspace=ws, out=o))
+        ops.check_status()
+        by = 2.0 * B * ctx * 2 * kvh * hd
+        row = dict(kind="attn_decode", B=B, ctx=ctx, q_heads=qh, kv_heads=kvh, page=page, splits=splits, us=t * 1e6,
+                   gbs=by / t / 1e9, hbm_frac=by / t / hbm, peaks=src)
+        out.append(row)
+        print(json.dumps(row), flush=True)
+
+
+def bench_prefill_attn(cases, out):
+    _, flops_peak, src = peaks()
+    for (B, n, qh, kvh) in cases:
+        hd = 128
+        qkv = torch.randn(B * n, (qh + 2 * kvh) * hd, device="cuda", dtype=torch.bfloat16)
+        indptr = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
+        o = torch.empty(B * n, qh * hd, device="cuda", dtype=torch.bfloat16)
+        t = timeit(lambda: ops.attn_prefill(qkv, indptr, [n] * B, q_heads=qh, kv_heads=kvh, head_dim=hd, out=o))
+        ops.check_status()
+        fl = 4.0 * B * qh * hd * n * n / 2
+        row = dict(kind="attn_prefill", B=B, n=n, q_heads=qh, kv_heads=kvh, us=t * 1e6, tflops=fl / t / 1e12,
+                   frac_of_gemm_peak=fl / t / flops_peak, peaks=src)
+        out.append(row)
+        print(json.dumps(row), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--json", default="")
+    args = ap.parse_args()
+    out = []
+    # Llama-3-8B layer GEMMs at decode (M = batch) and prefill (M = tokens) sizes
+    ms = [16, 256] if args.quick else [16, 64, 256, 1024, 4096, 8192]
+    shapes = []
+    for M in ms:
+        shapes += [(M, 6144, 4096, "store"), (M, 4096, 4096, "add"), (M, 14336, 4096, "silu_mul"),
+                   (M, 4096, 14336, "add")]
+    shapes += [(256, 128256, 4096, "store"), (8192, 8192, 8192, "store")]
+    bench_gemm(shapes, out)
+    cases = [(64, 1024, 32, 8, 128, 64, 1), (256, 1024, 32, 8, 128, 64, 1), (256, 1024, 32, 8, 128, 16, 1),
+             (8, 8192, 32, 8, 128, 64, 8), (1, 16384, 32, 8, 128, 64, 32)]
+    bench_decode_attn(cases[:2] if args.quick else cases, out)
+    bench_prefill_attn([(4, 2048, 32, 8)] if args.quick else [(8, 512, 32, 8), (4, 2048, 32, 8), (1, 8192, 32, 8)], out)
+    if args.json:
+        os.makedirs(os.path.dirname(os.path.abspath(args.json)), exist_ok=True)
+        json.dump(out, open(args.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

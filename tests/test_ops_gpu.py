@@ -1,0 +1,243 @@
+"""GPU numerics of every hand-written kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DT = torch.bfloat16
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from blitz_scale_b200 import ops as o
+    o.lib()  # must load the in-tree kernel library; no fallback
+    return o
+
+
+@pytest.fixture(autouse=True)
+def _status(ops):
+    yield
+    ops.check_status()
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (16, 512, 128), (200, 384, 320),
+                                   (256, 4096, 4096), (1000, 1024, 2048)])
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+def test_gemm_store(ops, M, N, K, layout):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=DT)
+    b = torch.randn(K, N, device="cuda", dtype=DT) * K ** -0.5
+    ref = a.float() @ b.float()
+    bb = b if layout == "kn" else b.t().contiguous()
+    for bn in (0, 64, 128, 256):
+        out = ops.gemm(a, bb, b_layout=layout, bn=bn)
+        torch.cuda.synchronize()
+        assert rel_err(out, ref) < 1e-2, (bn, rel_err(out, ref))
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 256, 128), (300, 1408, 512)])
+def test_gemm_add_and_silu(ops, M, N, K):
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device="cuda", dtype=DT)
+    b = torch.randn(K, N, device="cuda", dtype=DT) * K ** -0.5
+    r = torch.randn(M, N, device="cuda", dtype=DT)
+    ref = a.float() @ b.float() + r.float()
+    out = ops.gemm(a, b, residual=r, epilogue="add")
+    assert rel_err(out, ref) < 1e-2
+    # in-place residual update
+    r2 = r.clone()
+    ops.gemm(a, b, out=r2, residual=r2, epilogue="add")
+    assert rel_err(r2, ref) < 1e-2
+    gu = torch.randn(K, 2 * N, device="cuda", dtype=DT) * K ** -0.5
+    acc = a.float() @ gu.float()
+    ref2 = torch.nn.functional.silu(acc[:, :N]) * acc[:, N:]
+    for bn in (0, 128, 256):
+        out2 = ops.gemm(a, gu, epilogue="silu_mul", bn=bn)
+        assert rel_err(out2, ref2) < 1e-2, bn
+    out3 = ops.gemm(a, gu.t().contiguous(), epilogue="silu_mul", b_layout="nk")
+    assert rel_err(out3, ref2) < 1e-2
+
+
+def test_gemm_fp16(ops):
+    torch.manual_seed(2)
+    a = torch.randn(96, 256, device="cuda", dtype=torch.float16)
+    b = torch.randn(256, 320, device="cuda", dtype=torch.float16) / 16
+    assert rel_err(ops.gemm(a, b), a.float() @ b.float()) < 5e-3
+
+
+# ------------------------------------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("T,H", [(7, 256), (33, 4096), (5, 8192)])
+def test_norms(ops, T, H):
+    torch.manual_seed(3)
+    x = torch.randn(T, H, device="cuda", dtype=DT)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(DT)
+    ref = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    assert rel_err(ops.rms_norm(x, w, 1e-5), ref) < 1e-2
+    res = torch.randn(T, H, device="cuda", dtype=DT)
+    s = (res.float() + x.float()).to(DT)
+    ref2 = s.float() * torch.rsqrt(s.float().pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    res2 = res.clone()
+    out = ops.add_rms_norm(x, res2, w, 1e-5)
+    assert rel_err(res2, s) < 1e-3 and rel_err(out, ref2) < 1e-2
+
+
+def test_silu_add_embed_gather(ops):
+    torch.manual_seed(4)
+    x = torch.randn(9, 2 * 688, device="cuda", dtype=DT)
+    ref = torch.nn.functional.silu(x[:, :688].float()) * x[:, 688:].float()
+    assert rel_err(ops.silu_mul(x), ref) < 1e-2
+    a = torch.randn(9, 512, device="cuda", dtype=DT)
+    b = torch.randn(9, 512, device="cuda", dtype=DT)
+    ref = a.float() + b.float()
+    assert rel_err(ops.add_residual(a, b), ref) < 1e-2
+    table = torch.randn(1000, 256, device="cuda", dtype=DT)
+    ids = torch.randint(0, 1000, (37,), device="cuda", dtype=torch.int32)
+    assert torch.equal(ops.embedding(ids, table), table[ids.long()])
+    # vocab shard [500, 1000): rows owned elsewhere are zero
+    shard = table[500:]
+    out = ops.embedding(ids, shard, vocab_start=500)
+    exp = torch.where((ids >= 500)[:, None], table[ids.long()], torch.zeros_like(table[ids.long()]))
+    assert torch.equal(out, exp)
+    indptr = torch.tensor([0, 3, 10, 37], device="cuda", dtype=torch.int32)
+    xs = torch.randn(37, 256, device="cuda", dtype=DT)
+    assert torch.equal(ops.gather_last(xs, indptr), xs[[2, 9, 36]])
+
+
+def test_argmax_and_sampling(ops):
+    torch.manual_seed(5)
+    lg = torch.randn(6, 128256, device="cuda", dtype=DT)
+    lg[2, 77] = lg[2, 90001] = 50.0  # tie -> smallest index
+    out = ops.argmax(lg)
+    assert torch.equal(out.long(), lg.float().argmax(-1)) or int(out[2]) == 77
+    assert int(out[2]) == 77
+    vals = torch.empty(6, device="cuda")
+    out2 = ops.argmax(lg, out_val=vals, idx_offset=1000)
+    assert torch.equal(out2, out + 1000) and torch.allclose(vals, lg.float().max(-1).values)
+    # sampling: top_k = 1 is greedy; draws stay inside the top-k set; frequencies follow the softmax
+    B, V = 4, 4096
+    lg = torch.randn(B, V, device="cuda", dtype=DT) * 2
+    temp = torch.ones(B, device="cuda")
+    topp = torch.ones(B, device="cuda")
+    seeds = torch.arange(B, device="cuda", dtype=torch.int64) + 11
+    k1 = torch.ones(B, device="cuda", dtype=torch.int32)
+    assert torch.equal(ops.sample(lg, temp, k1, topp, seeds, 0).long(), lg.float().argmax(-1))
+    k8 = torch.full((B,), 8, device="cuda", dtype=torch.int32)
+    top8 = lg.float().topk(8, -1).indices
+    counts = torch.zeros(B, V)
+    for step in range(300):
+        s = ops.sample(lg, temp, k8, topp, seeds, step).long()
+        assert all(int(s[i]) in top8[i].tolist() for i in range(B))
+        counts[torch.arange(B), s.cpu()] += 1
+    p = torch.softmax(lg.float().cpu().gather(1, top8.cpu()), -1)
+    f = counts.gather(1, top8.cpu()) / 300
+    assert float((p - f).abs().max()) < 0.12
+    # top_p small keeps only the head of the distribution
+    sharp = torch.zeros(1, V, device="cuda", dtype=DT)
+    sharp[0, 5] = 10.0
+    tp = torch.full((1,), 0.5, device="cuda")
+    k0 = torch.zeros(1, device="cuda", dtype=torch.int32)
+    for step in range(20):
+        assert int(ops.sample(sharp, temp[:1], k0, tp, seeds[:1], step)) == 5
+
+
+def _rope_ref(x, pos, theta):
+    from blitz_scale_b200.models.oracle import rope_ref
+    return rope_ref(x, pos, theta)
+
+
+@pytest.mark.parametrize("hd,page", [(128, 16), (64, 64)])
+def test_rope_kv_store(ops, hd, page):
+    torch.manual_seed(6)
+    T, qh, kvh, pages = 50, 4, 2, 12
+    qkv = torch.randn(T, (qh + 2 * kvh) * hd, device="cuda", dtype=DT)
+    pos = torch.randint(0, 3000, (T,), device="cuda", dtype=torch.int32)
+    perm = torch.randperm(pages * page)[:T]
+    slot = perm.to(device="cuda", dtype=torch.int32)
+    slot[3] = -1
+    kv = torch.zeros(pages, 2, page, kvh, hd, device="cuda", dtype=DT)
+    orig = qkv.clone()
+    ops.rope_kv_store(qkv, pos, slot, kv, q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=page, rope_theta=5e5)
+    q_ref = _rope_ref(orig[:, :qh * hd].view(T, qh, hd), pos, 5e5)
+    k_ref = _rope_ref(orig[:, qh * hd:(qh + kvh) * hd].view(T, kvh, hd), pos, 5e5)
+    v_ref = orig[:, (qh + kvh) * hd:].view(T, kvh, hd)
+    assert rel_err(qkv[:, :qh * hd].view(T, qh, hd), q_ref) < 1e-2
+    assert rel_err(qkv[:, qh * hd:(qh + kvh) * hd].view(T, kvh, hd), k_ref) < 1e-2
+    flat = kv.view(pages, 2, page, kvh, hd)
+    for t in range(T):
+        s = int(slot[t])
+        if s < 0:
+            continue
+        assert rel_err(flat[s // page, 0, s % page], k_ref[t]) < 1e-2
+        assert torch.equal(flat[s // page, 1, s % page], v_ref[t])
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def _paged_setup(B, lens, page, kvh, hd, seed):
+    g = torch.Generator().manual_seed(seed)
+    npages = [(n + page - 1) // page for n in lens]
+    total = sum(npages) + 3
+    perm = torch.randperm(total, generator=g)
+    kv = torch.zeros(total, 2, page, kvh, hd, dtype=DT)
+    ks, vs, idx, indptr, last = [], [], [], [0], []
+    cur = 0
+    for b, n in enumerate(lens):
+        k = torch.randn(n, kvh, hd, generator=g).to(DT)
+        v = torch.randn(n, kvh, hd, generator=g).to(DT)
+        pg = perm[cur:cur + npages[b]].tolist()
+        cur += npages[b]
+        for i, p in enumerate(pg):
+            seg = slice(i * page, min(n, (i + 1) * page))
+            kv[p, 0, :seg.stop - seg.start] = k[seg]
+            kv[p, 1, :seg.stop - seg.start] = v[seg]
+        ks.append(k); vs.append(v); idx += pg; indptr.append(len(idx)); last.append(n - (npages[b] - 1) * page if n else 0)
+    ti = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    return kv.cuda(), ks, vs, ti(idx), ti(indptr), ti(last)
+
+
+@pytest.mark.parametrize("hd,qh,kvh,page", [(128, 32, 8, 16), (128, 8, 8, 64), (64, 4, 2, 64), (128, 16, 2, 64)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_attn_decode(ops, hd, qh, kvh, page, splits):
+    lens = [1, 17, 64, 200, 1031, 5]
+    B = len(lens)
+    kv, ks, vs, idx, indptr, last = _paged_setup(B, lens, page, kvh, hd, 7)
+    torch.manual_seed(8)
+    q = torch.randn(B, qh * hd, device="cuda", dtype=DT)
+    out = ops.attn_decode(q, kv, idx, indptr, last, q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=page,
+                          num_splits=splits)
+    g = qh // kvh
+    for b in range(B):
+        k = ks[b].cuda().float().repeat_interleave(g, 1)
+        v = vs[b].cuda().float().repeat_interleave(g, 1)
+        s = torch.einsum("hd,shd->hs", q[b].view(qh, hd).float(), k) * hd ** -0.5
+        ref = torch.einsum("hs,shd->hd", s.softmax(-1), v).reshape(-1)
+        assert rel_err(out[b], ref) < 1e-2, (b, rel_err(out[b], ref))
+
+
+@pytest.mark.parametrize("qh,kvh,lens", [(4, 2, [128]), (4, 2, [5, 130, 257]), (8, 8, [300, 64, 1]), (32, 8, [700, 33])])
+def test_attn_prefill(ops, qh, kvh, lens):
+    hd = 128
+    torch.manual_seed(9)
+    T = sum(lens)
+    qkv = torch.randn(T, (qh + 2 * kvh) * hd, device="cuda", dtype=DT)
+    import itertools
+    indptr = torch.tensor([0] + list(itertools.accumulate(lens)), dtype=torch.int32, device="cuda")
+    out = ops.attn_prefill(qkv, indptr, lens, q_heads=qh, kv_heads=kvh, head_dim=hd)
+    g = qh // kvh
+    o = 0
+    for n in lens:
+        q = qkv[o:o + n, :qh * hd].view(n, qh, hd).float()
+        k = qkv[o:o + n, qh * hd:(qh + kvh) * hd].view(n, kvh, hd).float().repeat_interleave(g, 1)
+        v = qkv[o:o + n, (qh + kvh) * hd:].view(n, kvh, hd).float().repeat_interleave(g, 1)
+        s = torch.einsum("thd,shd->hts", q, k) * hd ** -0.5
+        s = s.masked_fill(torch.ones(n, n, device="cuda").triu(1).bool()[None], float("-inf"))
+        ref = torch.einsum("hts,shd->thd", s.softmax(-1), v).reshape(n, qh * hd)
+        assert rel_err(out[o:o + n], ref) < 1e-2, (n, rel_err(out[o:o + n], ref))
+        o += n
