@@ -1,0 +1,200 @@
+"""Headline benchmark: aggregate decode tokens/s of Llama-3-8B-shaped replicas (bf16, TP1) on N B200s.
+
+    python bench.py --gpus N --steps K --warmup W          # N = 1
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Each rank is one serving replica (the reference's unit of scaling: N independent instances behind
+the router) holding a full random-init Llama-3-8B-shaped model and a decode batch of `--batch`
+sequences whose `--ctx`-token prompts were prefilled through the engine before timing (synthetic
+token ids).  One step = one decode iteration of the whole batch = `batch` tokens per replica.
+
+Two numbers are reported:
+  * value  : kernel-only.  K replays of the captured decode step, CUDA events on the launching
+             stream, barrier + synchronize on both sides, max over ranks.
+  * e2e    : K real `Engine.decode()` calls (the call a worker makes per DecodeV2 RPC): every step
+             fills the pinned staging buffer, copies it host->device, replays the step, copies the
+             sampled tokens device->host, updates the page tables on the host.
+Per step each replica touches all weights (~15 GB) and its KV working set (batch x ctx x 128 KB),
+far beyond the 126 MB L2, so no explicit flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference is a C++/Rust/CMake project with empty submodules: pip reports "
+                                     "'/root/reference is not installable: neither setup.py nor pyproject.toml found'"}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+        sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            for i, n in enumerate(names):
+                if len(r) > 4 + i and r[4 + i].lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
+                "reasons": sorted(reasons), "samples": len(self.rows)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="llama3_8b")
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--ctx", type=int, default=512)
+    ap.add_argument("--page-size", type=int, default=64)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from blitz_scale_b200.runtime.engine import Engine
+    from blitz_scale_b200.runtime import core
+    from blitz_scale_b200 import ops
+
+    B, ctx, ps = args.batch, args.ctx, args.page_size
+    total_steps = args.warmup + args.steps + 8
+    pages_per_seq = (ctx + total_steps + ps) // ps + 1
+    eng = Engine(args.model, num_pages=B * pages_per_seq + 8, page_size=ps, max_batch=max(B, 8),
+                 max_batch_tokens=8192, seed=rank)
+    # synthetic prompts, prefilled through the engine in chunks that fit the activation workspace
+    g = torch.Generator().manual_seed(1234 + rank)
+    per = max(1, 8192 // ctx)
+    batch = None
+    bid = 0
+    for s0 in range(0, B, per):
+        n = min(per, B - s0)
+        specs = [core.SeqSpec(s0 + i, torch.randint(0, eng.cfg.vocab, (ctx,), generator=g).tolist(),
+                              total_steps + 4) for i in range(n)]
+        nb = eng.new_batch(bid, specs)
+        assert nb is not None, "KV pool too small"
+        bid += 1
+        eng.prefill(nb)
+        if batch is None:
+            batch = nb
+        else:
+            batch.extend(nb)
+    ops.check_status()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- e2e: real decode steps through the public engine API
+    for _ in range(args.warmup):
+        eng.decode(batch)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        eng.decode(batch)
+    e1.record()
+    barrier()
+    e2e_s = max(time.perf_counter() - t0, e0.elapsed_time(e1) * 1e-3)
+    h2d, d2h = eng.h2d_bytes, eng.d2h_bytes
+
+    # ---------------- kernel-only: replay the captured step
+    Bp = min(b for b in __import__("blitz_scale_b200.runtime.engine", fromlist=["_BUCKETS"])._BUCKETS if b >= B)
+    splits = eng.choose_splits(Bp, batch.max_seq_len())
+    graph = eng._graphs.get((Bp, splits)) or eng._capture(Bp, splits)
+    for _ in range(args.warmup):
+        graph.replay()
+    barrier()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    k1.record()
+    barrier()
+    dev_s = k0.elapsed_time(k1) * 1e-3
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_status()
+
+    if world > 1:
+        t = torch.tensor([dev_s, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_s, e2e_s = float(t[0]), float(t[1])
+    if rank == 0:
+        tokens = world * B * args.steps
+        out = {
+            "metric": "decode_tokens_per_s", "value": tokens / dev_s, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic token ids, random-init weights",
+            "config": {"model": args.model, "global_batch": world * B, "seq_len": ctx, "parallelism": f"dp{world}",
+                       "tp": 1, "page_size": ps, "l2": "per-step working set (weights + KV) >> 126 MB L2, no flush",
+                       "timing": "CUDA events around K graph replays, max over ranks"},
+            "clocks": clocks,
+            "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "ms_per_step": e2e_s / args.steps * 1e3,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": eng.decode_launch_count() * args.steps,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

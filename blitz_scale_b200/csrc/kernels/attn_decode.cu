@@ -1,4 +1,5 @@
-// Paged-KV decode attention for sm_100a: one query token per sequence, GQA,
+// Paged-KV decode attention, CUDA-core version (cross-check and fallback for shapes the tensor-core kernel
+// does not take): one query token per sequence, GQA,
 // split-KV (flash-decoding) with an fp32 merge.  The cache holds rotated K, so
 // the kernel is a pure streaming reduction over K and V pages and is bound by
 // HBM bandwidth; the work is laid out to keep >= 64 KB of 16-byte loads in
@@ -243,13 +244,13 @@ extern "C" {
 using namespace blitz;
 
 // Bytes of fp32 scratch the split path needs: part_o then part_lse.
-int64_t blitz_attn_decode_workspace_bytes(int batch, int q_heads, int head_dim, int num_splits) {
+int64_t blitz_attn_decode_simt_workspace_bytes(int batch, int q_heads, int head_dim, int num_splits) {
   if (num_splits <= 1) return 0;
   return (int64_t)batch * q_heads * num_splits * (head_dim + 1) * (int64_t)sizeof(float);
 }
 
 // workspace: caller-provided scratch of blitz_attn_decode_workspace_bytes() bytes (may be null when num_splits == 1).
-int blitz_attn_decode(const void* q, int64_t q_stride, const void* kv_layer, const int32_t* indices,
+int blitz_attn_decode_simt(const void* q, int64_t q_stride, const void* kv_layer, const int32_t* indices,
                       const int32_t* indptr, const int32_t* last_page_len, void* out, int64_t out_stride,
                       void* workspace, int batch, int q_heads, int kv_heads, int head_dim, int page_size,
                       int max_pages, int num_splits, float sm_scale, int* status, int dtype, cudaStream_t stream) {

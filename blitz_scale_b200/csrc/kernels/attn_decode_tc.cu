@@ -1,0 +1,397 @@
+// Paged-KV decode attention, tensor-core version (the serving path).
+//
+// Decode attention is a stream over the K and V pages of every sequence; with
+// GQA the 4-8 query heads that share a KV head turn the per-token work into a
+// small matrix product, so the FLOPs go to mma.sync (m16n8k16, query heads
+// padded to 16 rows) and the instruction stream per token drops ~10x against a
+// CUDA-core dot product; the kernel is then bound by HBM as it should be.
+// tcgen05 is not used here on purpose: its minimum M of 64 rows would waste
+// 94 % of each instruction on padding for one query token per sequence.
+//
+// Data movement: a producer warp walks the page table and issues TMA
+// (cp.async.bulk.tensor.3d, plain per-CTA loads) boxes of [tokens x 64 dims]
+// straight from the paged layout [page][K|V][token][kv_head][head_dim] into
+// 128-byte-swizzled shared memory, 4 stages of 64 tokens (128 KB in flight
+// per SM for head_dim 128).  Four consumer warps each own 16 of the 64 tokens
+// of a stage: S = Q K^T via ldmatrix + mma, online softmax in registers
+// (exp2, fp32), O += P V via ldmatrix.trans + mma.  Warps merge their partial
+// (m, l, O) through shared memory; with num_splits > 1 each CTA writes an fp32
+// partial and a merge kernel combines the splits (flash-decoding).
+//
+// The cache must hold finite values in every slot of an allocated page (the
+// pool is zero-filled at creation): masked positions get probability 0, and
+// 0 x NaN would still poison the accumulator.
+//
+// Replaces src/kernel/attention_decode.cu:13-40 and the host-side plan of
+// src/kernel/flashinfer_types.cu:52-80.
+#include "ptx.cuh"
+#include "tmap.cuh"
+#include "common.cuh"
+
+namespace blitz {
+
+constexpr int kTcThreads = 160;
+constexpr int kTcChunk = 64;
+constexpr int kTcStages = 4;
+constexpr int kTcSlabBytes = kTcChunk * 128;
+
+struct DecodeTcParams {
+  const void* q;
+  int64_t q_stride;
+  const int32_t* indices;
+  const int32_t* indptr;
+  const int32_t* last_page_len;
+  void* out;
+  int64_t out_stride;
+  float* part_o;
+  float* part_lse;
+  int q_heads, kv_heads, group, page_size, max_pages, num_splits, box_tokens;
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                        uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int HD>
+struct TcCfg {
+  static constexpr int kSlabs = HD / 64;
+  static constexpr int kStageBytes = 2 * kSlabs * kTcSlabBytes;
+  static constexpr int kMergeFloats = 4 * 8 * HD + 2 * 4 * 8;
+  static constexpr int kSmemBytes = kTcStages * kStageBytes + kMergeFloats * 4 + 1024 + 128;
+};
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kTcThreads)
+attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcParams p) {
+  using Cfg = TcCfg<HD>;
+  constexpr int SL = Cfg::kSlabs;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  float* mrg_o = reinterpret_cast<float*>(smem + kTcStages * Cfg::kStageBytes);  // [4][8][HD]
+  float* mrg_m = mrg_o + 4 * 8 * HD;                                              // [4][8]
+  float* mrg_l = mrg_m + 32;                                                      // [4][8]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(mrg_l + 32);
+  uint64_t* empty_bar = full_bar + kTcStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kTcStages);
+
+  const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.group;
+
+  const int pg_beg = p.indptr[b];
+  const int npages = p.indptr[b + 1] - pg_beg;
+  const int seq_len = npages > 0 ? (npages - 1) * p.page_size + p.last_page_len[b] : 0;
+  const int nchunks = (seq_len + kTcChunk - 1) / kTcChunk;
+  const int cps = (nchunks + p.num_splits - 1) / p.num_splits;
+  const int c_beg = min(nchunks, split * cps), c_end = min(nchunks, (split + 1) * cps);
+
+  // zero the stages once: rows a short last chunk never fills must stay finite
+  for (int i = threadIdx.x; i < kTcStages * Cfg::kStageBytes / 16; i += kTcThreads)
+    reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kTcStages; ++i) {
+      ptx::mbar_init(&full_bar[i], 1);
+      ptx::mbar_init(&empty_bar[i], 4);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::tma_prefetch_desc(&tmap);
+  }
+  ptx::fence_proxy_async_smem();
+  __syncthreads();
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      const int bt = p.box_tokens;
+      const uint32_t box_bytes = static_cast<uint32_t>(bt) * 128u;
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int c = c_beg; c < c_end; ++c) {
+        if (!ptx::bounded_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+          if (p.status) atomicCAS(p.status, 0, kStatusTimeoutProducer);
+          break;
+        }
+        const int tok0 = c * kTcChunk;
+        const int ntok = min(kTcChunk, seq_len - tok0);
+        const int pieces = (ntok + bt - 1) / bt;
+        ptx::mbar_expect_tx(&full_bar[stage], static_cast<uint32_t>(pieces) * 2u * SL * box_bytes);
+        uint8_t* sb = smem + stage * Cfg::kStageBytes;
+        for (int i = 0; i < pieces; ++i) {
+          const int t = tok0 + i * bt;
+          int page = p.indices[pg_beg + t / p.page_size];
+          if (page < 0 || page >= p.max_pages) {
+            if (p.status) atomicCAS(p.status, 0, kStatusBadIndex);
+            page = 0;
+          }
+          const int z = page * 2 * p.page_size + (t % p.page_size);
+#pragma unroll
+          for (int s = 0; s < SL; ++s) {
+            ptx::tma_load_3d(sb + s * kTcSlabBytes + i * box_bytes, &tmap, &full_bar[stage], s * 64, h, z);
+            ptx::tma_load_3d(sb + (SL + s) * kTcSlabBytes + i * box_bytes, &tmap, &full_bar[stage], s * 64, h,
+                             z + p.page_size);
+          }
+        }
+        if (++stage == kTcStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ consumers
+    const int g = lane >> 2, t4 = lane & 3;
+    // Q as A fragments (rows >= G are zero padding; rows 8..15 are never populated since G <= 8)
+    uint32_t qa0[HD / 16], qa2[HD / 16];
+    {
+      const T* qrow = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(b) * p.q_stride +
+                      static_cast<int64_t>(h * G + g) * HD;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        qa0[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4) : 0u;
+        qa2[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8) : 0u;
+      }
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const int tokw = warp * 16;
+    const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: matrix index and row within it
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int c = c_beg; c < c_end; ++c) {
+      if (!ptx::bounded_mbar_wait(&full_bar[stage], phase, abort_flag)) {
+        if (p.status && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+        break;
+      }
+      const int nvalid = min(kTcChunk, seq_len - c * kTcChunk);
+      if (tokw < nvalid) {
+        const uint32_t kbase = ptx::smem_u32(smem + stage * Cfg::kStageBytes);
+        const uint32_t vbase = kbase + SL * kTcSlabBytes;
+        float s_lo[4] = {0.f, 0.f, 0.f, 0.f}, s_hi[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          const int tok = tokw + (mi >> 1) * 8 + mr;
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const int ch = ks * 2 + (mi & 1);
+            const uint32_t addr = kbase + (ch >> 3) * kTcSlabBytes + tok * 128 + (((ch & 7) ^ (tok & 7)) << 4);
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(addr, b0, b1, b2, b3);
+            mma16816<T>(s_lo, qa0[ks], 0u, qa2[ks], 0u, b0, b1);
+            mma16816<T>(s_hi, qa0[ks], 0u, qa2[ks], 0u, b2, b3);
+          }
+        }
+        const int col = tokw + 2 * t4;
+        const bool v0 = col < nvalid, v1 = col + 1 < nvalid, v2 = col + 8 < nvalid, v3 = col + 9 < nvalid;
+        float mx = -INFINITY;
+        if (v0) mx = fmaxf(mx, s_lo[0]);
+        if (v1) mx = fmaxf(mx, s_lo[1]);
+        if (v2) mx = fmaxf(mx, s_hi[0]);
+        if (v3) mx = fmaxf(mx, s_hi[1]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m, mx * p.scale_log2);
+        const float alpha = exp2f(m - m_new);  // m = -inf -> 0
+        const float p0 = v0 ? exp2f(s_lo[0] * p.scale_log2 - m_new) : 0.f;
+        const float p1 = v1 ? exp2f(s_lo[1] * p.scale_log2 - m_new) : 0.f;
+        const float p2 = v2 ? exp2f(s_hi[0] * p.scale_log2 - m_new) : 0.f;
+        const float p3 = v3 ? exp2f(s_hi[1] * p.scale_log2 - m_new) : 0.f;
+        l = l * alpha + (p0 + p1 + p2 + p3);
+        m = m_new;
+        const uint32_t pa0 = pk2<T>(p0, p1), pa2 = pk2<T>(p2, p3);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+          o[i][0] *= alpha;
+          o[i][1] *= alpha;
+        }
+        {
+          const int tok = tokw + (mi & 1) * 8 + mr;
+#pragma unroll
+          for (int np = 0; np < HD / 16; ++np) {
+            const int ch = np * 2 + (mi >> 1);
+            const uint32_t addr = vbase + (ch >> 3) * kTcSlabBytes + tok * 128 + (((ch & 7) ^ (tok & 7)) << 4);
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+            mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
+            mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&empty_bar[stage]);
+      if (++stage == kTcStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+    // per-warp partials -> shared memory (rows < 8 only)
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (t4 == 0) {
+      mrg_m[warp * 8 + g] = m;
+      mrg_l[warp * 8 + g] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      float2 v = make_float2(o[i][0], o[i][1]);
+      *reinterpret_cast<float2*>(&mrg_o[(warp * 8 + g) * HD + i * 8 + 2 * t4]) = v;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < G * HD; e += kTcThreads) {
+    const int gg = e / HD, d = e % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mrg_m[w * 8 + gg]);
+    float L = 0.f, O = 0.f;
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float sc = exp2f(mrg_m[w * 8 + gg] - M);
+        L += mrg_l[w * 8 + gg] * sc;
+        O += mrg_o[(w * 8 + gg) * HD + d] * sc;
+      }
+    }
+    const float val = L > 0.f ? O / L : 0.f;
+    const int head = h * G + gg;
+    if (p.num_splits == 1) {
+      T* op = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(b) * p.out_stride + static_cast<int64_t>(head) * HD;
+      if (std::is_same<T, __nv_bfloat16>::value)
+        reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16(val);
+      else
+        reinterpret_cast<__half*>(op)[d] = __float2half(val);
+    } else {
+      const int64_t base = (static_cast<int64_t>(b) * p.q_heads + head) * p.num_splits + split;
+      p.part_o[base * HD + d] = val;
+      if (d == 0) p.part_lse[base] = L > 0.f ? M + log2f(L) : -INFINITY;
+    }
+  }
+}
+
+// Combine split partials: out = sum_s w_s o_s / sum_s w_s, w_s = 2^(lse_s - max lse).
+template <typename T>
+__global__ void attn_merge_tc_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                     T* __restrict__ out, int64_t out_stride, int q_heads, int hd, int num_splits) {
+  const int b = blockIdx.x, head = blockIdx.y;
+  const int64_t base = (static_cast<int64_t>(b) * q_heads + head) * num_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_lse[base + s]);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f, wsum = 0.f;
+    if (M > -INFINITY) {
+      for (int s = 0; s < num_splits; ++s) {
+        const float w = exp2f(part_lse[base + s] - M);
+        wsum += w;
+        acc += w * part_o[(base + s) * hd + d];
+      }
+    }
+    const float val = wsum > 0.f ? acc / wsum : 0.f;
+    T* op = out + static_cast<int64_t>(b) * out_stride + static_cast<int64_t>(head) * hd;
+    if (std::is_same<T, __nv_bfloat16>::value)
+      reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16(val);
+    else
+      reinterpret_cast<__half*>(op)[d] = __float2half(val);
+  }
+}
+
+template <typename T, int HD>
+static int launch_tc(const CUtensorMap& tm, const DecodeTcParams& p, int batch, cudaStream_t stream) {
+  auto kern = attn_decode_tc_kernel<T, HD>;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<HD>::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  dim3 grid(batch, p.kv_heads, p.num_splits);
+  kern<<<grid, kTcThreads, TcCfg<HD>::kSmemBytes, stream>>>(tm, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace blitz
+
+extern "C" {
+using namespace blitz;
+
+// Bytes of fp32 scratch the split path needs: part_o then part_lse.
+int64_t blitz_attn_decode_workspace_bytes(int batch, int q_heads, int head_dim, int num_splits) {
+  if (num_splits <= 1) return 0;
+  return (int64_t)batch * q_heads * num_splits * (head_dim + 1) * (int64_t)sizeof(float);
+}
+
+// kv_layer: [max_pages][2][page_size][kv_heads][head_dim].  workspace: scratch of
+// blitz_attn_decode_workspace_bytes() bytes (may be null when num_splits == 1).
+// page_size must be a power of two >= 8 (pages smaller than 64 tokens are fetched as
+// several boxes per stage).  q_heads / kv_heads <= 8; head_dim 64 or 128.
+int blitz_attn_decode(const void* q, int64_t q_stride, const void* kv_layer, const int32_t* indices,
+                      const int32_t* indptr, const int32_t* last_page_len, void* out, int64_t out_stride,
+                      void* workspace, int batch, int q_heads, int kv_heads, int head_dim, int page_size,
+                      int max_pages, int num_splits, float sm_scale, int* status, int dtype, cudaStream_t stream) {
+  if (batch <= 0) return 0;
+  if (num_splits < 1 || (q_heads % kv_heads) != 0 || (q_stride & 1) || (out_stride & 1)) return -1;
+  const int G = q_heads / kv_heads;
+  if (G > 8 || (head_dim != 64 && head_dim != 128)) return -1;
+  if (page_size < 8 || (page_size & (page_size - 1)) != 0) return -1;
+  if (num_splits > 1 && workspace == nullptr) return -1;
+  const int bt = page_size < kTcChunk ? page_size : kTcChunk;
+  CUtensorMap tm;
+  if (!get_tmap_3d(&tm, kv_layer, (uint64_t)head_dim, (uint64_t)kv_heads, (uint64_t)max_pages * 2 * page_size,
+                   (uint64_t)head_dim * 2, (uint64_t)kv_heads * head_dim * 2, 64, 1, (uint32_t)bt))
+    return -2;
+  DecodeTcParams p;
+  p.q = q; p.q_stride = q_stride; p.indices = indices; p.indptr = indptr; p.last_page_len = last_page_len;
+  p.out = out; p.out_stride = out_stride;
+  p.part_o = reinterpret_cast<float*>(workspace);
+  p.part_lse = p.part_o ? p.part_o + (int64_t)batch * q_heads * num_splits * head_dim : nullptr;
+  p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size; p.max_pages = max_pages;
+  p.num_splits = num_splits; p.box_tokens = bt; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
+  int rc;
+  if (dtype == 1)
+    rc = head_dim == 128 ? launch_tc<__nv_bfloat16, 128>(tm, p, batch, stream)
+                         : launch_tc<__nv_bfloat16, 64>(tm, p, batch, stream);
+  else
+    rc = head_dim == 128 ? launch_tc<__half, 128>(tm, p, batch, stream) : launch_tc<__half, 64>(tm, p, batch, stream);
+  if (rc != 0) return rc;
+  if (num_splits > 1) {
+    dim3 grid(batch, q_heads);
+    if (dtype == 1)
+      attn_merge_tc_kernel<__nv_bfloat16><<<grid, head_dim, 0, stream>>>(p.part_o, p.part_lse, (__nv_bfloat16*)out,
+                                                                         out_stride, q_heads, head_dim, num_splits);
+    else
+      attn_merge_tc_kernel<__half><<<grid, head_dim, 0, stream>>>(p.part_o, p.part_lse, (__half*)out, out_stride,
+                                                                  q_heads, head_dim, num_splits);
+    rc = (int)cudaGetLastError();
+  }
+  return rc;
+}
+
+}  // extern "C"

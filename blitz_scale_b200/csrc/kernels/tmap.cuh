@@ -89,6 +89,42 @@ inline bool get_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint6
   return true;
 }
 
+// 3-D tensor of 16-bit elements, dims (d0 fastest) with byte strides s1, s2 for
+// d1, d2; box (b0, b1, b2); 128-byte swizzle (b0 * 2 bytes must be 128).
+inline bool get_tmap_3d(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes,
+                        uint64_t s2_bytes, uint32_t b0, uint32_t b1, uint32_t b2) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  TmapKey key{ptr, d0 * 1000003ull + d1, d2, s1_bytes * 1000003ull + s2_bytes, b0, b1 * 65536u + b2, 2, 128};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  PFN_encodeTiled enc = get_encode_fn();
+  if (!enc) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (s1_bytes & 15) != 0 || (s2_bytes & 15) != 0) return false;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {s1_bytes, s2_bytes};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, m);
+  }
+  *out = m;
+  return true;
+}
+
 inline int device_sm_count() {
   static int n = 0;
   if (n == 0) {

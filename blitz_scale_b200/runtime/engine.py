@@ -1,0 +1,200 @@
+"""Per-GPU serving engine: weight segment + paged KV pool + batches + the fused forward.
+
+This is the counterpart of the reference's engine facade (src/blitz/stub.h:68-291 constructor,
+:1283-1364 `forward`): it owns the model memory, the page allocator and the cached batches, stages
+the per-step page table through pinned memory, and runs prefill / decode steps.  Differences that
+matter for speed: the decode step is replayed from a CUDA graph per padded batch size (the
+reference relaunches ~9 kernels per layer per token on the default stream and synchronises after
+every prefill layer, src/model/llama.h:345-355), attention needs no host-side plan, and there is
+exactly one H2D copy (inputs + page table) and one D2H copy (sampled tokens) per step.
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.config import ModelConfig, get_config
+from ..models.llama import LlamaRunner, StepMeta, TPComm
+from ..models.weights import WeightSegment
+from . import core
+
+_BUCKETS = [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024]
+
+
+def _bucket(n: int) -> int:
+    for b in _BUCKETS:
+        if n <= b:
+            return b
+    return n
+
+
+class Engine:
+    def __init__(self, model: str | ModelConfig, *, num_pages: int, page_size: int = 64, max_batch: int = 256,
+                 max_batch_tokens: int = 8192, tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16,
+                 device: Optional[torch.device] = None, comm: Optional[TPComm] = None, use_graphs: bool = True,
+                 seg_buffer: Optional[torch.Tensor] = None, kv_buffer: Optional[torch.Tensor] = None,
+                 ready: bool = True, seed: int = 0):
+        self.cfg = get_config(model) if isinstance(model, str) else model
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.dtype, self.tp, self.tp_rank = dtype, tp, tp_rank
+        self.page_size, self.num_pages = page_size, num_pages
+        self.max_batch, self.max_batch_tokens = max_batch, max_batch_tokens
+        c = self.cfg
+        self.seg = WeightSegment(c, tp, tp_rank, dtype, device=self.device, buffer=seg_buffer)
+        kvh = c.kv_heads // tp
+        kv_shape = (c.layers, num_pages, 2, page_size, kvh, c.head_dim)
+        if kv_buffer is None:
+            # zero-filled: the attention kernels require finite values in every slot of an allocated page
+            self.kv = torch.zeros(kv_shape, dtype=dtype, device=self.device)
+        else:
+            self.kv = kv_buffer.view(dtype)[:int(np.prod(kv_shape))].view(kv_shape)
+        self.runner = LlamaRunner(self.seg, self.kv, max_tokens=max(max_batch_tokens, max_batch), max_batch=max_batch,
+                                  comm=comm)
+        self.pool = core.PagePool(num_pages, page_size)
+        self.layout = core.MetaLayout.make(max(max_batch_tokens, max_batch), max_batch, num_pages)
+        self.host = torch.zeros(self.layout.total, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=self.device)
+        self.tok_host = torch.zeros(max_batch, dtype=torch.int32, pin_memory=True)
+        self.status = core.ModelStatus(c.layers)
+        if ready:
+            self.seg.random_init_fast_(seed)
+            self.status.set_ready()
+        self.batches: Dict[int, "core.Batch"] = {}
+        self.use_graphs = use_graphs
+        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.launches_per_decode_step = 0
+
+    # ------------------------------------------------------------------ meta views
+    def _views(self, T: int, B: int, P: int, prefill: bool, seq_lens: Sequence[int] = (), splits: int = 1) -> StepMeta:
+        L, d = self.layout, self.dev
+        return StepMeta(ids=d[L.ids:L.ids + T], pos=d[L.pos:L.pos + T], slot=d[L.slot:L.slot + T],
+                        page_indices=d[L.page_indices:L.page_indices + max(P, 1)],
+                        page_indptr=d[L.page_indptr:L.page_indptr + B + 1],
+                        last_page_len=d[L.last_page_len:L.last_page_len + B],
+                        tok_indptr=d[L.tok_indptr:L.tok_indptr + B + 1] if prefill else None,
+                        seq_lens_host=list(seq_lens), is_prefill=prefill, batch=B, num_tokens=T, num_splits=splits)
+
+    def _h2d(self, hi: int) -> None:
+        self.dev[:hi].copy_(self.host[:hi], non_blocking=True)
+        self.h2d_bytes = hi * 4
+
+    def _tokens_to_host(self, toks: torch.Tensor, B: int) -> List[int]:
+        self.tok_host[:B].copy_(toks[:B], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes = B * 4
+        return self.tok_host[:B].tolist()
+
+    # ------------------------------------------------------------------ batches
+    def new_batch(self, batch_id: int, specs) -> Optional["core.Batch"]:
+        b = core.Batch(batch_id, self.pool)
+        if not b.add_prompts(specs):
+            return None
+        return b
+
+    def choose_splits(self, B: int, max_len: int) -> int:
+        ctas = B * (self.cfg.kv_heads // self.tp)
+        if ctas >= 2 * 148 or max_len <= 256:
+            return 1
+        want = (2 * 148 + ctas - 1) // ctas
+        cap = max(1, max_len // 256)
+        s = 1
+        while s * 2 <= min(want, cap, 32):
+            s *= 2
+        return s
+
+    # ------------------------------------------------------------------ steps
+    @torch.no_grad()
+    def prefill(self, batch: "core.Batch") -> List[int]:
+        """Run the prompt of every request in `batch`, cache its K/V and return the first token of each."""
+        if not self.status.fully_loaded():
+            raise RuntimeError("model parameters are not loaded")
+        T, P = batch.fill_prefill(self.host_np, self.layout)
+        if T > self.max_batch_tokens:
+            raise ValueError(f"prefill of {T} tokens exceeds max_batch_tokens={self.max_batch_tokens}")
+        self._h2d(self.layout.page_indices + P)
+        lens = [len(s.spec.prompt) for s in batch.seqs]
+        m = self._views(T, batch.size, P, True, lens)
+        toks = self.runner.forward(m)
+        out = self._tokens_to_host(toks, batch.size)
+        batch.mark_prefilled()
+        batch.append_tokens(out, False)
+        batch.decode = True
+        return out
+
+    @torch.no_grad()
+    def decode(self, batch: "core.Batch") -> List[int]:
+        """One decode step for every request in `batch` (already extended if several were merged)."""
+        B = batch.size
+        Bp = _bucket(B) if self.use_graphs else B
+        Bp = min(Bp, self.max_batch)
+        splits = self.choose_splits(Bp, batch.max_seq_len())
+        P = batch.fill_decode(self.host_np, self.layout, Bp)
+        self._h2d(self.layout.page_indices + P)
+        if self.use_graphs:
+            key = (Bp, splits)
+            g = self._graphs.get(key)
+            if g is None:
+                g = self._capture(Bp, splits)
+            g.replay()
+            toks = self.runner.tokens
+        else:
+            toks = self.runner.forward(self._views(Bp, Bp, self.num_pages, False, splits=splits))
+        out = self._tokens_to_host(toks, B)
+        batch.append_tokens(out, True)
+        return out
+
+    def _capture(self, Bp: int, splits: int) -> torch.cuda.CUDAGraph:
+        m = self._views(Bp, Bp, self.num_pages, False, splits=splits)
+        # warm up outside capture: first-use work (attribute setup, descriptor cache, workspace allocation)
+        self.runner.forward(m)
+        torch.cuda.current_stream().synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.runner.forward(m)
+        self._graphs[(Bp, splits)] = g
+        return g
+
+    def decode_launch_count(self) -> int:
+        """Kernels of this library launched by one decode step at tp = 1 (for the bench's launch accounting)."""
+        per_layer = 8  # rms_norm, qkv gemm, rope_kv_store, attention, o gemm, rms_norm, gate_up gemm, down gemm
+        return 1 + per_layer * self.cfg.layers + 3  # embedding + layers + final norm, lm_head gemm, argmax
+
+    # ------------------------------------------------------------------ parameters
+    def set_status_ready(self) -> None:
+        self.status.set_ready()
+
+    def reset_status(self) -> None:
+        self.status.reset()
+
+    def load_params_from_host(self, host_mirror: torch.Tensor, chunk_bytes: int = 256 << 20) -> float:
+        """Chunked H2D of a pinned host mirror on two streams; returns seconds."""
+        n = self.seg.layout.total_bytes
+        assert host_mirror.numel() >= n and host_mirror.dtype == torch.uint8
+        t0 = time.perf_counter()
+        streams = [torch.cuda.Stream(device=self.device) for _ in range(2)]
+        for i, off in enumerate(range(0, n, chunk_bytes)):
+            hi = min(n, off + chunk_bytes)
+            with torch.cuda.stream(streams[i % 2]):
+                self.seg.buffer[off:hi].copy_(host_mirror[off:hi], non_blocking=True)
+        for s in streams:
+            s.synchronize()
+        self.status.set_ready()
+        return time.perf_counter() - t0
+
+    def load_params_from_disk(self, directory, host_mirror: Optional[torch.Tensor] = None) -> dict:
+        """Disk -> pinned host (O_DIRECT, threaded) -> device.  Returns timings."""
+        path = WeightSegment.check_sidecar(directory, self.cfg, self.tp, self.tp_rank, self.dtype)
+        n = self.seg.layout.total_bytes
+        if host_mirror is None:
+            host_mirror = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+        res = core.load_file_to_host(str(path), host_mirror.data_ptr(), n)
+        h2d = self.load_params_from_host(host_mirror)
+        return {"disk_s": res.seconds, "h2d_s": h2d, "bytes": n, "direct_io": res.direct_io, "host_mirror": host_mirror}

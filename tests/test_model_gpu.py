@@ -36,29 +36,28 @@ def test_prefill_decode_matches_oracle(page):
     oracle = LlamaOracle(seg, compute_dtype=torch.float32)
     ref_tokens, ref_logits = oracle.generate(prompts, new, return_logits=True)
 
+    def check(step, lg, toks):
+        for b in range(3):
+            r = ref_logits[b][step]
+            err = float((lg[b] - r).norm() / r.norm())
+            assert err < 3e-2, (b, step, err)
+            # greedy tokens agree unless the oracle's own top-2 gap is within the bf16 noise
+            if toks[b] != ref_tokens[b][step]:
+                gap = float(r.max() - r[toks[b]])
+                assert gap < 0.05 * float(r.abs().max()), (b, step, gap)
+
     m = mb.prefill(prompts, tables)
     toks = runner.forward(m).tolist()
     ops.check_status()
-    got = [[t] for t in toks]
-    lg = runner.logits[:3].float().cpu()
-    for b in range(3):
-        r = ref_logits[b][0]
-        assert float((lg[b] - r).norm() / r.norm()) < 2e-2
+    check(0, runner.logits[:3].float().cpu(), toks)
     seq = list(lens)
     for step in range(1, new):
-        m = mb.decode([g_[-1] for g_ in got], seq, tables, num_splits=1 + step % 2)
+        # teacher forcing: feed the oracle's previous token so both sides see the same history
+        m = mb.decode([ref_tokens[b][step - 1] for b in range(3)], seq, tables, num_splits=1 + step % 2)
         toks = runner.forward(m).tolist()
         ops.check_status()
-        lg = runner.logits[:3].float().cpu()
-        for b in range(3):
-            # feed the oracle's token when they diverge on a near-tie so the comparison stays aligned
-            r = ref_logits[b][step]
-            if got[b][-1] == ref_tokens[b][step - 1]:
-                assert float((lg[b] - r).norm() / r.norm()) < 3e-2, (b, step)
-            got[b].append(toks[b])
-            seq[b] += 1
-    agree = sum(int(a == b) for x, y in zip(got, ref_tokens) for a, b in zip(x, y))
-    assert agree >= 0.8 * new * 3, (got, ref_tokens)
+        check(step, runner.logits[:3].float().cpu(), toks)
+        seq = [n + 1 for n in seq]
 
 
 def test_layer_by_layer_equals_full_forward():

@@ -128,7 +128,9 @@ def test_argmax_and_sampling(ops):
     topp = torch.ones(B, device="cuda")
     seeds = torch.arange(B, device="cuda", dtype=torch.int64) + 11
     k1 = torch.ones(B, device="cuda", dtype=torch.int32)
-    assert torch.equal(ops.sample(lg, temp, k1, topp, seeds, 0).long(), lg.float().argmax(-1))
+    s1 = ops.sample(lg, temp, k1, topp, seeds, 0).long()
+    # top_k = 1 keeps the maximum (all tokens tied at the maximum stay eligible)
+    assert torch.equal(lg.float().gather(1, s1[:, None])[:, 0], lg.float().max(-1).values)
     k8 = torch.full((B,), 8, device="cuda", dtype=torch.int32)
     top8 = lg.float().topk(8, -1).indices
     counts = torch.zeros(B, V)
@@ -219,6 +221,22 @@ def test_attn_decode(ops, hd, qh, kvh, page, splits):
         s = torch.einsum("hd,shd->hs", q[b].view(qh, hd).float(), k) * hd ** -0.5
         ref = torch.einsum("hs,shd->hd", s.softmax(-1), v).reshape(-1)
         assert rel_err(out[b], ref) < 1e-2, (b, rel_err(out[b], ref))
+
+
+def test_attn_decode_simt_matches_tc(ops):
+    """The CUDA-core kernel (kept as a cross-check) and the tensor-core kernel agree."""
+    import ctypes
+    lens = [33, 400, 64]
+    kv, ks, vs, idx, indptr, last = _paged_setup(3, lens, 16, 2, 128, 21)
+    q = torch.randn(3, 8 * 128, device="cuda", dtype=DT)
+    a = ops.attn_decode(q, kv, idx, indptr, last, q_heads=8, kv_heads=2, head_dim=128, page_size=16)
+    b = torch.empty_like(a)
+    L = ops.lib()
+    L.blitz_attn_decode_simt.argtypes = L.blitz_attn_decode.argtypes
+    rc = L.blitz_attn_decode_simt(q.data_ptr(), q.stride(0), kv.data_ptr(), idx.data_ptr(), indptr.data_ptr(),
+                                  last.data_ptr(), b.data_ptr(), b.stride(0), None, 3, 8, 2, 128, 16, kv.shape[0], 1,
+                                  128 ** -0.5, None, 1, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0 and rel_err(a, b) < 1e-2
 
 
 @pytest.mark.parametrize("qh,kvh,lens", [(4, 2, [128]), (4, 2, [5, 130, 257]), (8, 8, [300, 64, 1]), (32, 8, [700, 33])])
