@@ -1,0 +1,50 @@
+"""Small single-kernel cases for ncu captures (inputs larger than L2, a few hundred MB on the device).
+
+    python bench/ncu_case.py gemm M N K [epilogue]       # 3 launches of the tcgen05 GEMM
+    python bench/ncu_case.py attn_decode B CTX            # 3 launches of the paged decode attention
+    python bench/ncu_case.py attn_prefill B N             # 3 launches of the ragged prefill attention
+"""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from blitz_scale_b200 import ops  # noqa: E402
+
+
+def main():
+    kind = sys.argv[1]
+    if kind == "gemm":
+        M, N, K = map(int, sys.argv[2:5])
+        epi = sys.argv[5] if len(sys.argv) > 5 else "store"
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(K, 2 * N if epi == "silu_mul" else N, device="cuda", dtype=torch.bfloat16)
+        r = torch.randn(M, N, device="cuda", dtype=torch.bfloat16) if epi == "add" else None
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            ops.gemm(a, b, out=c, residual=r, epilogue=epi)
+    elif kind == "attn_decode":
+        B, ctx = map(int, sys.argv[2:4])
+        qh, kvh, hd, page = 32, 8, 128, 64
+        npg = (ctx + page - 1) // page
+        kv = torch.randn(B * npg, 2, page, kvh, hd, device="cuda", dtype=torch.bfloat16)
+        idx = torch.randperm(B * npg, device="cuda").to(torch.int32)
+        indptr = (torch.arange(B + 1, device="cuda") * npg).to(torch.int32)
+        last = torch.full((B,), ctx - (npg - 1) * page, device="cuda", dtype=torch.int32)
+        q = torch.randn(B, qh * hd, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            ops.attn_decode(q, kv, idx, indptr, last, q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=page)
+    elif kind == "attn_prefill":
+        B, n = map(int, sys.argv[2:4])
+        qkv = torch.randn(B * n, (32 + 16) * 128, device="cuda", dtype=torch.bfloat16)
+        indptr = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
+        for _ in range(3):
+            ops.attn_prefill(qkv, indptr, [n] * B, q_heads=32, kv_heads=8, head_dim=128)
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok")
+
+
+if __name__ == "__main__":
+    main()

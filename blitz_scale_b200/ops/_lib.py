@@ -68,8 +68,9 @@ def _declare(L: ctypes.CDLL) -> None:
                               c_p, c_i, c_p])
     sig("blitz_attn_prefill", [c_p, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_f, c_p, c_i, c_p])
     # comm kernels
-    sig("blitz_param_multicast", [c_p, c_p, c_i, c_p, c_i64, c_p, c_i, ctypes.c_uint32, c_i, c_p, c_p])
-    sig("blitz_kv_push", [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i64, c_i64, c_i64, c_p, ctypes.c_uint32, c_p, c_p])
-    sig("blitz_act_send", [c_p, c_p, c_i64, c_p, ctypes.c_uint32, c_p])
+    pp = ctypes.POINTER(c_p)
+    pi64 = ctypes.POINTER(c_i64)
+    sig("blitz_peer_copy_units", [c_p, pp, pp, c_i, c_p, pi64, pi64, c_i, c_i, c_i, c_i, c_p, c_i, c_p])
+    sig("blitz_kv_push", [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i64, c_i64, c_i64, c_i, c_i, c_p, c_p, c_i, c_p, c_p])
     sig("blitz_flag_wait", [c_p, ctypes.c_uint32, c_u64, c_p, c_p])
-    sig("blitz_flag_set", [c_p, ctypes.c_uint32, c_p])
+    sig("blitz_flag_set", [c_p, ctypes.c_uint32, c_i, c_p])

@@ -1,0 +1,140 @@
+"""Multi-rank GPU checks of the peer-memory kernels; launched by test_multi_gpu.py through torch.distributed.run.
+
+Every rank validates its own view and exits non-zero on a mismatch.  All device-side waits are bounded.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    case = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    from blitz_scale_b200 import ops
+    from blitz_scale_b200.parallel import symm
+    dev = torch.device("cuda", torch.cuda.current_device())
+    wbytes = 96 << 20
+    layers, pages, page_bytes = 4, 64, 2 * 16 * 2 * 128 * 2
+    fab = symm.PeerFabric(symm.FabricSizes(weight_bytes=wbytes, kv_bytes=layers * pages * page_bytes,
+                                           mailbox_slots=4, mailbox_slot_bytes=1 << 20))
+    use_mm = case.endswith("_multimem")
+    if use_mm and not fab.weights.mc_ptr:
+        if rank == 0:
+            print("SKIP: no multicast support")
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0
+
+    if case.startswith("multicast"):
+        units_off = [0, 8 << 20, 40 << 20, 72 << 20, 95 << 20]
+        units_len = [8 << 20, 32 << 20, 32 << 20, 23 << 20, (1 << 20) - 256]
+        g = torch.Generator(device="cuda").manual_seed(7)
+        ref = torch.randint(0, 255, (wbytes,), dtype=torch.uint8, device="cuda", generator=g)  # same on all ranks
+        fab.weights.local.zero_()
+        if rank == 0:
+            fab.weights.local.copy_(ref)
+        torch.cuda.synchronize()
+        dist.barrier()
+        dsts = list(range(1, world))
+        if rank == 0:
+            fab.copy_units(fab.weights, dsts, units_off, units_len, symm.PARAM_FLAG0, use_multimem=use_mm)
+        else:
+            for u in range(len(units_off)):
+                fab.wait_flag(symm.PARAM_FLAG0 + u, 1, budget_ms=5000)
+        torch.cuda.synchronize()
+        ops.check_status()
+        dist.barrier()
+        if rank != 0:
+            for off, n in zip(units_off, units_len):
+                assert torch.equal(fab.weights.local[off:off + n], ref[off:off + n]), (rank, off)
+            assert fab.read_flags(symm.PARAM_FLAG0, len(units_off)) == [1] * len(units_off)
+            # bytes outside the units stay untouched
+            assert int(fab.weights.local[units_off[-1] + units_len[-1]:].sum()) == 0
+        # two-source striping: ranks 0 and 1 each send half of every unit to the last rank
+        if world >= 3 and not use_mm:
+            dist.barrier()
+            last = world - 1
+            if rank == last:
+                fab.weights.local.zero_()
+                fab.reset_param_flags()
+            torch.cuda.synchronize()
+            dist.barrier()
+            if rank in (0, 1):
+                fab.copy_units(fab.weights, [last], units_off, units_len, symm.PARAM_FLAG0, stripe=rank, n_stripes=2)
+            torch.cuda.synchronize()
+            dist.barrier()
+            if rank == last:
+                assert fab.read_flags(symm.PARAM_FLAG0, len(units_off)) == [2] * len(units_off)
+                for off, n in zip(units_off, units_len):
+                    assert torch.equal(fab.weights.local[off:off + n], ref[off:off + n])
+    elif case == "kv_push":
+        kv = fab.kv.local.view(layers, pages, page_bytes)
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        if rank == 0:
+            kv.copy_(torch.randint(0, 255, kv.shape, dtype=torch.uint8, device="cuda", generator=g))
+        torch.cuda.synchronize()
+        dist.barrier()
+        src_pages = torch.tensor([3, 9, 27, 28, 41], dtype=torch.int32, device="cuda")
+        dst_pages = torch.tensor([50, 2, 7, 33, 12], dtype=torch.int32, device="cuda")
+        stride = pages * page_bytes
+        if rank == 0:
+            # first two layers, then the rest (the partial-migration variants)
+            fab.kv_push(1, src_pages, dst_pages, 0, 2, page_bytes, stride, stride, pages, pages, flag_slot=0)
+            fab.kv_push(1, src_pages, dst_pages, 2, layers, page_bytes, stride, stride, pages, pages, flag_slot=0)
+        elif rank == 1:
+            for l in range(layers):
+                fab.wait_flag(symm.KV_FLAG0 + l, 1, budget_ms=5000)
+        torch.cuda.synchronize()
+        ops.check_status()
+        dist.barrier()
+        src_all = fab.kv.peer_tensor(0).view(layers, pages, page_bytes) if rank == 1 else None
+        if rank == 1:
+            mine = kv
+            for s, d in zip(src_pages.tolist(), dst_pages.tolist()):
+                assert torch.equal(mine[:, d], src_all[:, s].clone()), (s, d)
+            untouched = [p for p in range(pages) if p not in dst_pages.tolist()]
+            assert int(mine[:, untouched].sum()) == 0
+    elif case == "mailbox_and_timeout":
+        slot_bytes = 1 << 20
+        if rank == 0:
+            fab.mailbox.local[:slot_bytes].copy_(torch.arange(slot_bytes, device="cuda").to(torch.uint8))
+            torch.cuda.synchronize()
+            fab.copy_units(fab.mailbox, [1], [2 * slot_bytes], [slot_bytes], symm.MAILBOX_FLAG0 + 2)
+        # the copy above sends slot 2 of rank 0 (zeros) -- send slot 0 into slot 0 as the real check
+        dist.barrier()
+        if rank == 0:
+            fab.copy_units(fab.mailbox, [1], [0], [slot_bytes], symm.MAILBOX_FLAG0 + 0)
+        if rank == 1:
+            fab.wait_flag(symm.MAILBOX_FLAG0 + 0, 1, budget_ms=5000)
+            torch.cuda.synchronize()
+            ops.check_status()
+            assert torch.equal(fab.mailbox.local[:slot_bytes], torch.arange(slot_bytes, device="cuda").to(torch.uint8))
+            # a flag nobody sets: the wait gives up after its budget and reports status 4; the context survives
+            fab.wait_flag(symm.MAILBOX_FLAG0 + 3, 1, budget_ms=20)
+            torch.cuda.synchronize()
+            try:
+                ops.check_status()
+                raise SystemExit("expected a timeout status")
+            except RuntimeError as e:
+                assert "flag wait timed out" in str(e)
+            assert float(torch.ones(8, device="cuda").sum()) == 8.0
+        torch.cuda.synchronize()
+        dist.barrier()
+    else:
+        raise SystemExit(f"unknown case {case}")
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        print(f"{case}: OK on {world} ranks")
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,31 @@
+"""Multi-GPU checks (peer-memory kernels) run as child processes, one rank per GPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _run(case, nproc, extra_env=None):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", **(extra_env or {}))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(HERE, "mgpu_worker.py"), case]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+@pytest.mark.parametrize("case", ["multicast", "multicast_multimem", "kv_push", "mailbox_and_timeout"])
+def test_peer_kernels(case):
+    n = min(_ngpu(), 4) if case.startswith("multicast") else 2
+    out = _run(case, n)
+    assert "OK" in out or "SKIP" in out
