@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
 ]
-CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-Wno-sign-compare", "-pthread"]
+CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-Wno-sign-compare", "-pthread", "-fvisibility=hidden"]
 
 
 def _nvcc() -> str:
@@ -108,7 +108,10 @@ def build_host(force: bool = False):
         for f in [ex.submit(_run, j) for j in jobs]:
             f.result()
     if force or jobs or not out.exists():
-        _run([cxx, "-shared", "-o", str(out), *map(str, objs), "-pthread"])
+        # static libstdc++ with local symbol binding: the module must not resolve C++ runtime symbols against
+        # whichever libstdc++ another extension (torch) loaded first
+        _run([cxx, "-shared", "-o", str(out), *map(str, objs), "-pthread", "-static-libstdc++", "-static-libgcc",
+              "-Wl,-Bsymbolic", "-Wl,--exclude-libs,ALL"])
     return out
 
 

@@ -49,8 +49,19 @@ struct GemmCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  // Shared memory is carved at run time: A stages are only as tall as the rows TMA actually fetches
+  // (small-M decode GEMMs then keep 2-3x more weight bytes in flight); all A stages come first so that
+  // the 128-row UMMA view of a short A stage still lies inside the allocation (the extra rows are
+  // garbage and their output rows are never stored).
+  static constexpr int kMaxStages = 24;
+  static constexpr int kBarrierBytes = (2 * kMaxStages + 4) * 8 + 16;
+  static constexpr int kSmemBytes = 227 * 1024;
+  static constexpr int kUsableBytes = kSmemBytes - 1024 /*align slack*/ - kBarrierBytes;
+  __host__ __device__ static int a_stage_bytes(int a_rows) { return ((a_rows * kBK * 2) + 1023) & ~1023; }
+  __host__ __device__ static int num_stages(int a_rows) {
+    int s = (kUsableBytes - kABytes) / (a_stage_bytes(a_rows) + kBBytes);
+    return s > kMaxStages ? kMaxStages : s;
+  }
   static constexpr int kTmemCols = 2 * BN;
 };
 
@@ -84,7 +95,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
   using Cfg = GemmCfg<BN>;
-  constexpr int S = Cfg::kStages;
+  const int S = Cfg::num_stages(p.a_box_rows);
+  const int a_stage = Cfg::a_stage_bytes(p.a_box_rows);
   constexpr int kOutCols = (EPI == kEpiSiluMul) ? BN / 2 : BN;  // output columns per tile
   constexpr uint32_t kFmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t kIdesc = ptx::make_idesc_f16(kFmt, 0u, B_KMAJOR ? 0u : 1u, kBM, BN);
@@ -93,13 +105,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
   uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + S * Cfg::kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint8_t* smem_b = smem + S * a_stage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kUsableBytes);
   uint64_t* full_bar = bars;             // [S]
-  uint64_t* empty_bar = bars + S;        // [S]
-  uint64_t* tfull_bar = bars + 2 * S;    // [2]
-  uint64_t* tempty_bar = bars + 2 * S + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  uint64_t* empty_bar = bars + Cfg::kMaxStages;        // [S]
+  uint64_t* tfull_bar = bars + 2 * Cfg::kMaxStages;    // [2]
+  uint64_t* tempty_bar = bars + 2 * Cfg::kMaxStages + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kMaxStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -147,7 +159,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             break;
           }
           ptx::mbar_expect_tx(&full_bar[stage], tx_bytes);
-          ptx::tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], kb * kBK, m0);
+          ptx::tma_load_2d(smem_a + stage * a_stage, &tmap_a, &full_bar[stage], kb * kBK, m0);
           uint8_t* sb = smem_b + stage * Cfg::kBBytes;
           if (B_KMAJOR) {
             // B is [N,K]: one box of BN rows x 64 K-elements per half (silu: gate rows then up rows).
@@ -201,7 +213,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t a_base = ptx::smem_u32(smem_a + stage * Cfg::kABytes);
+          const uint32_t a_base = ptx::smem_u32(smem_a + stage * a_stage);
           const uint32_t b_base = ptx::smem_u32(smem_b + stage * Cfg::kBBytes);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
@@ -346,18 +358,19 @@ static cudaError_t dispatch_epi(int epi, int bn, const CUtensorMap& ta, const CU
   }
 }
 
-// Tile width: the widest N tile that still yields at least one tile per SM.
+// Tile width.  Measured on B200 at decode sizes: 128-wide tiles win once they give at least ~0.45 tiles per
+// SM; below that 64-wide tiles (more CTAs streaming weights) are better; 256-wide only when it still
+// fills the machine (large M) or for the gate||up GEMM, where a 256-wide tile yields 128 outputs.
 static int choose_bn(int M, int N, int epi, int sms) {
   const int tiles_m = (M + kBM - 1) / kBM;
-  const int cands[3] = {256, 128, 64};
-  for (int i = 0; i < 3; ++i) {
-    int bn = cands[i];
-    if (epi == kEpiSiluMul && bn == 64) break;
-    int out_cols = epi == kEpiSiluMul ? bn / 2 : bn;
-    int tiles = tiles_m * ((N + out_cols - 1) / out_cols);
-    if (tiles >= sms) return bn;
-  }
-  return epi == kEpiSiluMul ? 128 : 64;
+  auto tiles = [&](int bn) {
+    const int out_cols = epi == kEpiSiluMul ? bn / 2 : bn;
+    return tiles_m * ((N + out_cols - 1) / out_cols);
+  };
+  if (tiles(256) >= sms) return 256;
+  if (epi == kEpiSiluMul) return 128;
+  if (tiles(128) * 100 >= sms * 45) return 128;
+  return 64;
 }
 
 }  // namespace blitz

@@ -1,0 +1,916 @@
+// Sans-IO orchestrator core: request queue -> prefill replicas -> KV migration -> decode replicas, plus
+// the autoscaler (planner, executors for the multicast-based system and for the ServerlessLLM-style
+// baseline), live scaling (ZigZag) pairing and the relay queue.
+//
+// The core never performs IO and never reads a clock: the shell (asyncio + gRPC, or the virtual-time
+// simulator) calls `step(now)` to obtain `Action`s, carries them out, and reports completions with the
+// `on_*` methods.  The behaviour condenses the per-replica event loops, migration watchers and
+// executors of the reference router (router_v2/src/replica/disaggregation.rs:741-2543,
+// cybernetics/{planner,exec_blitz,exec_serverless,mod}.rs, relay_queue.rs:10-54) into one
+// deterministic state machine; busy-wait loops become explicit "nothing to do" returns.
+#pragma once
+#include <algorithm>
+#include <deque>
+#include <map>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "queue.h"
+#include "replica.h"
+
+namespace blitz {
+
+enum class ActionType : int {
+  Prefill = 0, ZagPrefill, PrefillPP, Decode, Migrate, MigratePartial, Relay,
+  NvlBroadcast, TanzBroadcast, RdmaBroadcast, LoadParams, ResetStatus, SetStatusReady, ClearCache,
+  Deliver, Fail,
+};
+
+struct Action {
+  ActionType type = ActionType::Deliver;
+  uint64_t op_id = 0;              // completion handle (0: fire and forget)
+  int replica = -1;                // replica that executes
+  int peer = -1;                   // migrate: destination replica; relay / PrefillPP: partner replica
+  uint64_t batch_id = 0;
+  std::vector<uint64_t> batch_ids; // decode: resident batches to run (first id survives the merge)
+  std::vector<uint64_t> request_ids;
+  uint32_t max_tokens = 0;
+  std::vector<int> src_ranks, dst_ranks;
+  int load_case = 1;               // 0 host memory, 1 disk
+  int partial = 0;                 // 1 first half, 2 second half
+  int num_layer = 0;               // dividing layer of a partial migration / start layer of PrefillPP
+  uint32_t zag_seq = 0;
+  bool live = false;               // broadcast feeds a NewPrefill (per-layer readiness matters)
+  bool mock = false;
+  // Deliver / Fail
+  uint64_t request_id = 0;
+  int32_t token = -1;
+  bool final = false;
+};
+
+struct ControllerConfig {
+  int num_ranks = 2, tp = 1;
+  std::vector<int> machines;               // machine id per rank (default all 0)
+  std::vector<std::string> init_states;    // per rank: Prefill | Decode | Normal | Inactive
+  uint32_t block_size = 64;
+  uint32_t max_prefill_tokens = 8192, max_total_tokens = 16000;
+  uint32_t max_blocks_per_replica = 30000;
+  uint32_t zigzag_req_limit = 4, zigzag_req_floor = 2;
+  double zigzag_decay_ms = 200;
+  double planner_interval_ms = 10;
+  uint32_t model_layers = 32;
+  std::string model_name = "llama3_8b";
+  PlannerConfig planner;
+  std::string features = "impl_blitz,impl_fast_pro,impl_live_pro";
+  bool autoscale = true;
+  double mock_load_ms = 0;
+};
+
+class Controller {
+ public:
+  explicit Controller(const ControllerConfig& cfg)
+      : cfg_(cfg), features_(FeatureSet::parse(cfg.features)), queue_(cfg.block_size),
+        steer_(cfg.machines.empty() ? std::vector<int>(cfg.num_ranks, 0) : cfg.machines, cfg.tp) {
+    if (cfg.num_ranks % cfg.tp) throw std::invalid_argument("num_ranks not divisible by tp");
+    const int R = cfg.num_ranks / cfg.tp;
+    reps_.resize(R);
+    for (int r = 0; r < R; ++r) {
+      std::string s = cfg.init_states.empty() ? (r == 0 ? "Prefill" : (r == 1 ? "Decode" : "Inactive"))
+                                              : cfg.init_states[r * cfg.tp];
+      auto st = rstate_from_name(s);
+      if (!st) throw std::invalid_argument("bad init state " + s);
+      reps_[r].m.state = *st;
+      reps_[r].colocated = (s == "Normal");
+      reps_[r].m.model_loaded = (*st != RState::Inactive);
+      reps_[r].m.dst_busy = (*st != RState::Decode);
+      if (reps_[r].m.model_loaded) steer_.record_model_loaded(r);
+      log_transition(r, RState::Inactive, *st, true);
+    }
+    cfg_.planner.block_size = cfg.block_size;
+    cfg_.planner.max_blocks_per_replica = cfg.max_blocks_per_replica;
+  }
+
+  // ------------------------------------------------------------------------------------ inputs
+  void submit(const RequestEntry& e) {
+    requests_[e.id] = e;
+    queue_.append(e);
+    counters_["blitz_request_count"] += 1;
+  }
+  void client_gone(uint64_t id) {
+    queue_.mark_client_gone(id);
+    auto it = requests_.find(id);
+    if (it != requests_.end()) it->second.client_alive = false;
+  }
+
+  struct TokenOut { uint64_t request_id; int32_t token; bool finished; };
+
+  void on_prefill_done(uint64_t op_id, const std::vector<TokenOut>& toks, double now) {
+    Op op = take_op(op_id);
+    Rep& rep = reps_[op.replica];
+    rep.busy = false;
+    ResidentBatch rb = std::move(op.batch);
+    stats_prefill_tokens_ += rb.prompt_tokens;
+    deliver_tokens(rb, toks, now, true);
+    if (op.kind == ActionType::ZagPrefill) {
+      erase_inflight_zag(rep, rb.id);
+      maybe_finish_refractory(op.replica, now);
+    }
+    if (op.kind == ActionType::PrefillPP) {
+      // second half of a relayed batch: its KV for layers [k, L) lives here, first half on the new instance
+      auto it = relayed_.find(rb.id);
+      if (it != relayed_.end()) {
+        it->second.batch = rb;
+        it->second.pp_done = true;
+        if (rb.request_ids.empty()) {  // everything finished at the first token: nothing to migrate
+          release_blocks(op.replica, it->second.blocks);
+          release_blocks(it->second.new_replica, it->second.blocks);
+          finish_relayed_target(it->second);
+          relayed_.erase(it);
+        }
+      }
+      reps_[op.replica].relay_wait = false;
+      return;
+    }
+    if (rb.request_ids.empty()) {
+      release_blocks(op.replica, rb.blocks);
+      out_.push_back(make_simple(ActionType::ClearCache, op.replica, rb.id));
+      return;
+    }
+    shrink_blocks(op.replica, rb);
+    if (rep.colocated || num_in_state(RState::Decode) + num_in_state(RState::AusDecode) +
+                                 num_in_state(RState::MutatingToDecode) + num_in_state(RState::LoadingDecode) == 0) {
+      rep.decode_batches.push_back(std::move(rb));  // no decode side: decode where the KV already is
+    } else {
+      rep.pending_migration.push_back(std::move(rb));
+    }
+  }
+
+  void on_decode_done(uint64_t op_id, const std::vector<TokenOut>& toks, double now) {
+    Op op = take_op(op_id);
+    Rep& rep = reps_[op.replica];
+    rep.busy = false;
+    // the worker merged all resident batches into the first one
+    ResidentBatch merged = std::move(rep.decode_batches.front());
+    for (size_t i = 1; i < rep.decode_batches.size(); ++i) {
+      if (!rep.decode_batches[i].in_step) break;
+      merge_into(merged, rep.decode_batches[i]);
+    }
+    size_t consumed = 0;
+    while (consumed < rep.decode_batches.size() && rep.decode_batches[consumed].in_step) ++consumed;
+    rep.decode_batches.erase(rep.decode_batches.begin(), rep.decode_batches.begin() + consumed);
+    merged.in_step = false;
+    stats_decode_tokens_ += toks.size();
+    deliver_tokens(merged, toks, now, false);
+    if (merged.request_ids.empty()) {
+      release_blocks(op.replica, merged.blocks);
+      out_.push_back(make_simple(ActionType::ClearCache, op.replica, merged.id));
+    } else {
+      shrink_blocks(op.replica, merged);
+      rep.decode_batches.insert(rep.decode_batches.begin(), std::move(merged));
+    }
+  }
+
+  void on_migrate_done(uint64_t op_id, double now) {
+    (void)now;
+    Op op = take_op(op_id);
+    Rep& src = reps_[op.replica];
+    Rep& dst = reps_[op.peer];
+    counters_[op.kind == ActionType::Migrate ? "blitz_kv_cache_times" : "blitz_partial_kv_cache_times"] += 1;
+    if (op.kind == ActionType::Migrate) {
+      src.migrating = false;
+      release_blocks(op.replica, op.batch.blocks);
+      unlock_target(op.peer);
+      dst.decode_batches.push_back(std::move(op.batch));
+      return;
+    }
+    auto it = relayed_.find(op.batch.id);
+    if (it == relayed_.end()) return;
+    Relayed& r = it->second;
+    release_blocks(op.replica, r.blocks);
+    if (op.partial == 1) { r.fst_done = true; reps_[r.new_replica].m.flying_partial -= 1; }
+    if (op.partial == 2) r.snd_done = true;
+    if (r.fst_done && r.snd_done) {
+      unlock_target(op.peer);
+      dst.decode_batches.push_back(r.batch);
+      relayed_.erase(it);
+    }
+  }
+
+  // A parameter transfer / load finished on `replica` (its op may cover several destinations).
+  void on_params_done(uint64_t op_id, double now) {
+    Op op = take_op(op_id);
+    for (int s : op.sources) {
+      steer_.set_nvlink_busy(s, false);
+      reps_[s].m.marker.reset();
+    }
+    for (int d : op.targets) {
+      Rep& rep = reps_[d];
+      rep.m.model_loaded = true;
+      steer_.record_model_loaded(d);
+      steer_.touch_host_cache(steer_.machine_of(d * cfg_.tp), now);
+      switch (rep.m.state) {
+        case RState::LoadingPrefill: set_state(d, RState::Prefill); break;
+        case RState::LoadingDecode: set_state(d, RState::AusDecode); set_state(d, RState::Decode); break;
+        case RState::NewPrefill:
+          set_state(d, RState::RefractoryPrefill);
+          maybe_finish_refractory(d, now);
+          break;
+        default: break;
+      }
+    }
+  }
+
+  // Relay RPC answered: the new instance handed over `batch_id` at transformer layer `next_layer`
+  // (has_batch = false: nothing was left to hand over).
+  void on_relay_done(uint64_t op_id, bool has_batch, uint64_t batch_id, int next_layer, double now) {
+    Op op = take_op(op_id);
+    const int neu = op.replica, old = op.peer;
+    Rep& nrep = reps_[neu];
+    if (!has_batch) {
+      reps_[old].busy = false;
+      reps_[old].relay_wait = false;
+      maybe_finish_refractory(neu, now);
+      return;
+    }
+    ResidentBatch rb;
+    bool found = false;
+    for (auto it = nrep.inflight_zag.begin(); it != nrep.inflight_zag.end(); ++it) {
+      if (it->id == batch_id) { rb = *it; nrep.inflight_zag.erase(it); found = true; break; }
+    }
+    if (!found) { reps_[old].busy = false; reps_[old].relay_wait = false; return; }
+    // the pending ZagPrefill op of this batch is answered by the hand-over, not by tokens
+    for (auto it = ops_.begin(); it != ops_.end(); ++it)
+      if (it->second.kind == ActionType::ZagPrefill && it->second.batch.id == batch_id) { ops_.erase(it); break; }
+    nrep.busy = !nrep.inflight_zag.empty();
+    Relayed r;
+    r.batch = rb; r.new_replica = neu; r.old_replica = old; r.next_layer = std::max(0, next_layer); r.blocks = rb.blocks;
+    r.target = pick_decode_target(rb.blocks);
+    // both replicas hold KV pages of this batch until their half has migrated
+    reps_[old].m.used_blocks += rb.blocks;
+    if (r.target >= 0) acquire_target(r.target, rb.blocks);
+    Action a = make_simple(ActionType::PrefillPP, old, rb.id);
+    a.op_id = new_op(ActionType::PrefillPP, old, neu, rb);
+    a.peer = neu; a.num_layer = r.next_layer; a.request_ids = rb.request_ids; a.max_tokens = rb.max_tokens;
+    a.dst_ranks = steer_.ranks_of_replica(neu);
+    out_.push_back(a);
+    r.fst_done = (r.next_layer == 0);  // nothing on the new instance if it had not run a layer yet
+    relayed_[rb.id] = r;
+    maybe_finish_refractory(neu, now);
+  }
+
+  // An RPC of `op_id` failed: the replica is lost (fail-stop workers, src/util/cuda_utils.h:15-22).
+  void on_failure(uint64_t op_id, double now) {
+    if (!ops_.count(op_id)) return;
+    Op op = take_op(op_id);
+    counters_["blitz_request_failure"] += 1;
+    lose_replica(op.replica, now, &op);
+  }
+
+  // ------------------------------------------------------------------------------------ step
+  std::vector<Action> step(double now) {
+    if (cfg_.autoscale && !features_.has("manually_scale") && now - last_plan_ >= cfg_.planner_interval_ms * 1e-3) {
+      last_plan_ = now;
+      run_planner(now);
+    }
+    expire_parked(now);
+    for (int r = 0; r < num_replicas(); ++r) drive_replica(r, now);
+    for (int r = 0; r < num_replicas(); ++r) drive_migration(r, now);
+    drive_relayed(now);
+    std::vector<Action> o;
+    o.swap(out_);
+    return o;
+  }
+
+  // Manual scaling (HTTP /modify_cluster_state under `manually_scale`, router_v2/src/server.rs:388-483).
+  bool manual_scale(int replica, const std::string& target, double now) {
+    auto st = rstate_from_name(target);
+    if (!st || replica < 0 || replica >= num_replicas()) return false;
+    if (*st == RState::Prefill || *st == RState::Decode) {
+      if (reps_[replica].m.state != RState::Inactive && reps_[replica].m.state != RState::ShuttingNull) return false;
+      scale_up_one(replica, *st == RState::Prefill, now);
+      return true;
+    }
+    if (*st == RState::Inactive) { begin_shutdown(replica, now); return true; }
+    return false;
+  }
+
+  // ------------------------------------------------------------------------------------ views
+  int num_replicas() const { return static_cast<int>(reps_.size()); }
+  const ReplicaMetric& metric(int r) const { return reps_[r].m; }
+  std::string state_name(int r) const { return rstate_name(reps_[r].m.state); }
+  size_t queue_size() const { return queue_.size(); }
+  uint64_t waiting_prefill_tokens() const { return queue_.waiting_prefill_tokens(); }
+  const std::map<std::string, double>& counters() const { return counters_; }
+  const FeatureSet& features() const { return features_; }
+  const RequestEntry* request(uint64_t id) const {
+    auto it = requests_.find(id);
+    return it == requests_.end() ? nullptr : &it->second;
+  }
+  std::vector<std::string> drain_log() { std::vector<std::string> l; l.swap(log_); return l; }
+  std::string system_metrics_line() const {
+    std::ostringstream s;
+    s << "System Metrics: prefill_tokens: " << stats_prefill_tokens_ << ", decode_tokens: " << stats_decode_tokens_;
+    return s.str();
+  }
+  size_t inflight_ops() const { return ops_.size(); }
+  bool idle() const {
+    if (!queue_.empty() || !ops_.empty() || !relayed_.empty()) return false;
+    for (auto& r : reps_)
+      if (!r.decode_batches.empty() || !r.pending_migration.empty() || !r.inflight_zag.empty()) return false;
+    return true;
+  }
+  uint64_t total_used_blocks() const {
+    uint64_t t = 0;
+    for (auto& r : reps_) t += r.m.used_blocks;
+    return t;
+  }
+  ScaleTarget last_target() const { return last_target_; }
+
+ private:
+  struct ResidentBatch {
+    uint64_t id = 0;
+    std::vector<uint64_t> request_ids;
+    uint32_t max_tokens = 0, prompt_tokens = 0, blocks = 0;
+    bool in_step = false;
+  };
+  struct Rep {
+    ReplicaMetric m;
+    bool colocated = false;
+    bool busy = false;        // an inference RPC is in flight
+    bool migrating = false;   // this source has a migration in flight
+    bool relay_wait = false;  // OldPrefill parked in the relay queue
+    std::deque<ResidentBatch> pending_migration;
+    std::vector<ResidentBatch> decode_batches;
+    std::vector<ResidentBatch> inflight_zag;
+    uint32_t zag_seq = 0;
+    double zag_started = 0;
+    int partner = -1;         // OldPrefill <-> NewPrefill pairing
+    int incoming = 0;         // migrations in flight towards this replica
+  };
+  struct Op {
+    ActionType kind;
+    int replica = -1, peer = -1, partial = 0;
+    ResidentBatch batch;
+    std::vector<int> sources, targets;
+  };
+  struct Relayed {
+    ResidentBatch batch;
+    int new_replica = -1, old_replica = -1, target = -1, next_layer = 0;
+    uint32_t blocks = 0;
+    bool pp_done = false, fst_started = false, snd_started = false, fst_done = false, snd_done = false;
+  };
+
+  // ---------------- helpers
+  uint64_t new_op(ActionType k, int replica, int peer, const ResidentBatch& b) {
+    Op op;
+    op.kind = k; op.replica = replica; op.peer = peer; op.batch = b;
+    ops_[++next_op_] = op;
+    return next_op_;
+  }
+  Op take_op(uint64_t id) {
+    auto it = ops_.find(id);
+    if (it == ops_.end()) throw std::invalid_argument("unknown op id");
+    Op op = std::move(it->second);
+    ops_.erase(it);
+    return op;
+  }
+  Action make_simple(ActionType t, int replica, uint64_t batch_id) {
+    Action a;
+    a.type = t; a.replica = replica; a.batch_id = batch_id;
+    return a;
+  }
+  void log_transition(int r, RState a, RState b, bool boot = false) {
+    std::ostringstream s;
+    s << "Replica<" << r << "> " << (boot ? "boot" : rstate_name(a)) << " => " << rstate_name(b);
+    log_.push_back(s.str());
+  }
+  void set_state(int r, RState s) {
+    RState old = reps_[r].m.state;
+    if (old == s) return;
+    if (!transition_allowed(old, s))
+      throw std::logic_error(std::string("illegal transition ") + rstate_name(old) + " => " + rstate_name(s));
+    reps_[r].m.state = s;
+    // dst_mutex invariant: a replica holds its own mutex whenever it is not a decode target
+    if (s == RState::Decode) reps_[r].m.dst_busy = false;
+    else if (old == RState::Decode) reps_[r].m.dst_busy = true;
+    log_transition(r, old, s);
+  }
+  int num_in_state(RState s) const {
+    int n = 0;
+    for (auto& r : reps_) n += r.m.state == s;
+    return n;
+  }
+  void release_blocks(int r, uint32_t blocks) {
+    reps_[r].m.used_blocks = reps_[r].m.used_blocks >= blocks ? reps_[r].m.used_blocks - blocks : 0;
+  }
+  uint32_t blocks_of(const ResidentBatch& b) const {
+    uint64_t t = 0;
+    for (uint64_t id : b.request_ids) {
+      const RequestEntry& e = requests_.at(id);
+      t += (e.input_len + e.max_new_tokens + cfg_.block_size - 1) / cfg_.block_size;
+    }
+    return static_cast<uint32_t>(t);
+  }
+  // FilterBatch accounting: finished requests give their blocks back (router_v2/src/replica/mod.rs:251-269)
+  void shrink_blocks(int r, ResidentBatch& b) {
+    const uint32_t nb = blocks_of(b);
+    if (nb < b.blocks) release_blocks(r, b.blocks - nb);
+    b.blocks = nb;
+    b.max_tokens = nb * cfg_.block_size;
+  }
+  void merge_into(ResidentBatch& a, const ResidentBatch& b) {
+    a.request_ids.insert(a.request_ids.end(), b.request_ids.begin(), b.request_ids.end());
+    a.blocks += b.blocks;
+    a.max_tokens += b.max_tokens;
+  }
+  void deliver_tokens(ResidentBatch& b, const std::vector<TokenOut>& toks, double now, bool prefill) {
+    for (const TokenOut& t : toks) {
+      auto it = requests_.find(t.request_id);
+      if (it == requests_.end()) continue;
+      RequestEntry& e = it->second;
+      if (prefill) {
+        e.t_first_token = now;  // "PrefillDone" precedes the first token (router_v2/src/infer.rs:330-333)
+      } else {
+        if (e.generated == 1) e.t_first_decode_token = now;
+        if (e.generated >= 1 && e.t_last_token >= 0 && e.generated >= 2) e.tbt.push_back(now - e.t_last_token);
+      }
+      e.generated += 1;
+      e.t_last_token = now;
+      const bool fin = t.finished || e.generated >= e.max_new_tokens || !e.client_alive;
+      Action a;
+      a.type = ActionType::Deliver; a.request_id = t.request_id; a.token = t.token; a.final = fin;
+      out_.push_back(a);
+      if (fin) {
+        b.request_ids.erase(std::remove(b.request_ids.begin(), b.request_ids.end(), t.request_id), b.request_ids.end());
+        counters_["blitz_request_success"] += 1;
+        finished_[t.request_id] = e;
+        requests_.erase(it);
+      }
+    }
+  }
+  void erase_inflight_zag(Rep& rep, uint64_t batch_id) {
+    for (auto it = rep.inflight_zag.begin(); it != rep.inflight_zag.end(); ++it)
+      if (it->id == batch_id) { rep.inflight_zag.erase(it); break; }
+    rep.busy = !rep.inflight_zag.empty();
+  }
+  int pick_decode_target(uint32_t need_blocks) const {
+    int best = -1;
+    uint32_t best_used = UINT32_MAX;
+    for (int d = 0; d < num_replicas(); ++d) {
+      const Rep& r = reps_[d];
+      if (r.m.state != RState::Decode || r.m.dst_busy) continue;
+      if (r.m.used_blocks + need_blocks > cfg_.max_blocks_per_replica) continue;
+      if (!features_.has("decode_load_balance")) return d;  // first fit, like the reference's try_lock scan
+      if (r.m.used_blocks < best_used) { best = d; best_used = r.m.used_blocks; }
+    }
+    return best;
+  }
+  void acquire_target(int d, uint32_t blocks) {
+    reps_[d].incoming += 1;
+    reps_[d].m.dst_busy = true;
+    reps_[d].m.used_blocks += blocks;
+  }
+  void unlock_target(int d) {
+    reps_[d].incoming = std::max(0, reps_[d].incoming - 1);
+    reps_[d].m.dst_busy = reps_[d].m.state != RState::Decode || reps_[d].incoming > 0;
+  }
+  void finish_relayed_target(Relayed& r) {
+    if (r.target >= 0) {
+      release_blocks(r.target, r.blocks);
+      unlock_target(r.target);
+    }
+  }
+
+  // ---------------- per-replica driving
+  void drive_replica(int r, double now) {
+    Rep& rep = reps_[r];
+    rep.m.loop_cnt += 1;
+    switch (rep.m.state) {
+      case RState::Prefill:
+      case RState::ShuttingPrefill:
+      case RState::MutatingToDecode:
+        if (rep.colocated && try_decode(r)) return;
+        if (rep.m.state == RState::Prefill) try_prefill(r, now);
+        if (rep.m.state == RState::ShuttingPrefill && !rep.busy && rep.pending_migration.empty() && !rep.migrating)
+          park(r, now);
+        if (rep.m.state == RState::MutatingToDecode && !rep.busy && !rep.migrating) {
+          // flush the batches awaiting migration into itself, then serve as a decode replica
+          while (!rep.pending_migration.empty()) {
+            rep.decode_batches.push_back(rep.pending_migration.front());
+            rep.pending_migration.pop_front();
+          }
+          set_state(r, RState::Decode);
+        }
+        break;
+      case RState::OldPrefill:
+        if (!rep.busy) {
+          if (!try_relay(r, now)) try_prefill(r, now);
+        }
+        break;
+      case RState::NewPrefill:
+        try_zag_prefill(r, now);
+        break;
+      case RState::RefractoryPrefill:
+        maybe_finish_refractory(r, now);
+        break;
+      case RState::Decode:
+      case RState::ShuttingDecode:
+        try_decode(r);
+        if (rep.m.state == RState::ShuttingDecode && !rep.busy && rep.decode_batches.empty() && rep.incoming == 0)
+          park(r, now);
+        break;
+      default: break;
+    }
+  }
+
+  bool try_prefill(int r, double now) {
+    Rep& rep = reps_[r];
+    if (rep.busy || queue_.empty()) return false;
+    if (rep.m.used_blocks > cfg_.max_blocks_per_replica) return false;
+    const uint32_t free_blocks = cfg_.max_blocks_per_replica - rep.m.used_blocks;
+    auto nb = queue_.next_batch(std::nullopt, cfg_.max_prefill_tokens, cfg_.max_total_tokens, free_blocks);
+    if (!nb) return false;
+    ResidentBatch rb;
+    rb.id = nb->batch.id; rb.request_ids = nb->batch.request_ids; rb.max_tokens = nb->batch.max_tokens;
+    rb.prompt_tokens = nb->batch.prompt_tokens; rb.blocks = nb->batch.max_tokens / cfg_.block_size;
+    rep.m.used_blocks += rb.blocks;
+    for (auto& e : nb->entries) requests_[e.id].t_batched = now;
+    rep.busy = true;
+    Action a = make_simple(ActionType::Prefill, r, rb.id);
+    a.op_id = new_op(ActionType::Prefill, r, -1, rb);
+    a.request_ids = rb.request_ids; a.max_tokens = rb.max_tokens;
+    out_.push_back(a);
+    return true;
+  }
+
+  void try_zag_prefill(int r, double now) {
+    Rep& rep = reps_[r];
+    // in-flight limit decays from `zigzag_req_limit` by one every `zigzag_decay_ms`, floor `zigzag_req_floor`
+    uint32_t limit = cfg_.zigzag_req_limit;
+    const uint32_t decay = static_cast<uint32_t>((now - rep.zag_started) * 1e3 / std::max(1.0, cfg_.zigzag_decay_ms));
+    limit = limit > decay ? limit - decay : 0;
+    limit = std::max(limit, cfg_.zigzag_req_floor);
+    if (rep.inflight_zag.size() >= limit || queue_.empty()) return;
+    if (rep.m.used_blocks > cfg_.max_blocks_per_replica) return;
+    auto nb = queue_.next_batch(std::nullopt, cfg_.max_prefill_tokens, cfg_.max_total_tokens,
+                                cfg_.max_blocks_per_replica - rep.m.used_blocks);
+    if (!nb) return;
+    ResidentBatch rb;
+    rb.id = nb->batch.id; rb.request_ids = nb->batch.request_ids; rb.max_tokens = nb->batch.max_tokens;
+    rb.prompt_tokens = nb->batch.prompt_tokens; rb.blocks = nb->batch.max_tokens / cfg_.block_size;
+    rep.m.used_blocks += rb.blocks;
+    for (auto& e : nb->entries) requests_[e.id].t_batched = now;
+    rep.inflight_zag.push_back(rb);
+    rep.busy = true;
+    Action a = make_simple(ActionType::ZagPrefill, r, rb.id);
+    a.op_id = new_op(ActionType::ZagPrefill, r, -1, rb);
+    a.request_ids = rb.request_ids; a.max_tokens = rb.max_tokens; a.zag_seq = rep.zag_seq++;
+    out_.push_back(a);
+  }
+
+  bool try_relay(int old, double now) {
+    (void)now;
+    Rep& orep = reps_[old];
+    if (orep.relay_wait) return true;
+    int neu = orep.partner;
+    if (neu < 0) return false;
+    Rep& nrep = reps_[neu];
+    const bool live = nrep.m.state == RState::NewPrefill || nrep.m.state == RState::RefractoryPrefill;
+    if (!live) {  // partner finished loading: leave the pairing
+      orep.partner = -1;
+      set_state(old, RState::Prefill);
+      return false;
+    }
+    if (nrep.inflight_zag.empty()) return false;
+    if (pick_decode_target(nrep.inflight_zag.front().blocks) < 0 && num_in_state(RState::Decode) > 0) return false;
+    orep.busy = true;
+    orep.relay_wait = true;
+    Action a = make_simple(ActionType::Relay, neu, 0);
+    a.peer = old;
+    a.op_id = new_op(ActionType::Relay, neu, old, ResidentBatch{});
+    a.src_ranks = steer_.ranks_of_replica(old);
+    // while draining, the head task is about to finish locally: take the second one
+    a.final = nrep.m.state == RState::RefractoryPrefill;
+    out_.push_back(a);
+    return true;
+  }
+
+  void maybe_finish_refractory(int r, double now) {
+    (void)now;
+    Rep& rep = reps_[r];
+    if (rep.m.state != RState::RefractoryPrefill || !rep.inflight_zag.empty()) return;
+    for (auto& op : ops_)
+      if (op.second.kind == ActionType::Relay && op.second.replica == r) return;  // a relay is still being answered
+    set_state(r, RState::Prefill);
+    rep.busy = false;
+    if (rep.partner >= 0) {
+      Rep& old = reps_[rep.partner];
+      if (old.m.state == RState::OldPrefill && !old.relay_wait) {
+        old.partner = -1;
+        set_state(rep.partner, RState::Prefill);
+      }
+      rep.partner = -1;
+    }
+  }
+
+  bool try_decode(int r) {
+    Rep& rep = reps_[r];
+    if (rep.busy || rep.decode_batches.empty()) return false;
+    Action a = make_simple(ActionType::Decode, r, rep.decode_batches.front().id);
+    ResidentBatch all;
+    all.id = rep.decode_batches.front().id;
+    for (auto& b : rep.decode_batches) {
+      b.in_step = true;
+      a.batch_ids.push_back(b.id);
+      all.request_ids.insert(all.request_ids.end(), b.request_ids.begin(), b.request_ids.end());
+    }
+    a.request_ids = all.request_ids;
+    a.op_id = new_op(ActionType::Decode, r, -1, all);
+    rep.busy = true;
+    out_.push_back(a);
+    return true;
+  }
+
+  void drive_migration(int src, double now) {
+    (void)now;
+    Rep& rep = reps_[src];
+    if (rep.migrating || rep.pending_migration.empty()) return;
+    ResidentBatch& b = rep.pending_migration.front();
+    const int dst = pick_decode_target(b.blocks);
+    if (dst < 0) return;
+    acquire_target(dst, b.blocks);
+    rep.migrating = true;
+    Action a = make_simple(ActionType::Migrate, src, b.id);
+    a.peer = dst; a.request_ids = b.request_ids; a.max_tokens = b.max_tokens;
+    a.src_ranks = steer_.ranks_of_replica(src); a.dst_ranks = steer_.ranks_of_replica(dst);
+    a.op_id = new_op(ActionType::Migrate, src, dst, b);
+    out_.push_back(a);
+    rep.pending_migration.pop_front();
+  }
+
+  void drive_relayed(double now) {
+    (void)now;
+    for (auto& kv : relayed_) {
+      Relayed& r = kv.second;
+      if (r.target < 0) {
+        r.target = pick_decode_target(r.blocks);
+        if (r.target < 0) continue;
+        acquire_target(r.target, r.blocks);
+      }
+      auto emit = [&](int part, int from) {
+        Action a = make_simple(ActionType::MigratePartial, from, r.batch.id);
+        a.peer = r.target; a.partial = part; a.num_layer = r.next_layer; a.request_ids = r.batch.request_ids;
+        a.max_tokens = r.batch.max_tokens;
+        a.src_ranks = steer_.ranks_of_replica(from); a.dst_ranks = steer_.ranks_of_replica(r.target);
+        Op op;
+        op.kind = ActionType::MigratePartial; op.replica = from; op.peer = r.target; op.partial = part; op.batch = r.batch;
+        ops_[++next_op_] = op;
+        a.op_id = next_op_;
+        out_.push_back(a);
+      };
+      if (!r.fst_started && !r.fst_done) {
+        r.fst_started = true;
+        reps_[r.new_replica].m.flying_partial += 1;
+        emit(1, r.new_replica);
+      }
+      if (r.pp_done && !r.snd_started) {
+        r.snd_started = true;
+        if (r.fst_done && r.next_layer == 0) release_blocks(r.new_replica, r.blocks);
+        emit(2, r.old_replica);
+      }
+    }
+  }
+
+  // ---------------- autoscaling
+  static bool is_prefill_side(RState s) {
+    return s == RState::Prefill || s == RState::NewPrefill || s == RState::OldPrefill || s == RState::RefractoryPrefill ||
+           s == RState::LoadingPrefill || s == RState::AusPrefill;
+  }
+  static bool is_decode_side(RState s) {
+    return s == RState::Decode || s == RState::AusDecode || s == RState::LoadingDecode || s == RState::MutatingToDecode;
+  }
+  void run_planner(double now) {
+    PlannerView v;
+    for (auto& r : reps_) {
+      if (is_prefill_side(r.m.state)) { v.num_prefill += 1; v.prefill_used_blocks += r.m.used_blocks; }
+      if (is_decode_side(r.m.state)) { v.num_decode += 1; v.decode_used_blocks += r.m.used_blocks; }
+    }
+    if (v.num_prefill == 0 || v.num_decode == 0) return;  // colocated deployments do not autoscale roles
+    v.waiting_prefill_tokens = queue_.waiting_prefill_tokens();
+    ScaleTarget t = plan_scale(cfg_.planner, v);
+    last_target_ = t;
+    gauges_["blitz_prefill_replica"] = v.num_prefill;
+    gauges_["blitz_decode_replica"] = v.num_decode;
+    if (t.d_prefill == 0 && t.d_decode == 0) { last_logged_ = {0, 0}; return; }
+    const bool changed = std::make_pair(t.d_prefill, t.d_decode) != last_logged_;
+    last_logged_ = {t.d_prefill, t.d_decode};
+    std::ostringstream s;
+    s << "Control signal: P" << std::showpos << t.d_prefill << " D" << t.d_decode << std::noshowpos << " | Prefill thpt : ["
+      << t.bands.prefill_thpt_min << "," << t.bands.prefill_thpt_max << "]; KV$ : [" << t.bands.prefill_kv_min << ","
+      << t.bands.prefill_kv_max << "] | Decode Mem : [" << t.bands.decode_mem_min << "," << t.bands.decode_mem_max
+      << "]; KV$ : [" << t.bands.decode_kv_min << "," << t.bands.decode_kv_max << "]";
+    if (changed) log_.push_back(s.str());  // a standing signal is logged once, not every tick
+    int dp = t.d_prefill, dd = t.d_decode;
+    // decode shortage with prefill surplus: mutate a prefill replica in place, no reload
+    if (dd > 0 && dp < 0 && features_.has("mutate")) {
+      for (int r = 0; r < num_replicas() && dd > 0 && dp < 0; ++r) {
+        if (reps_[r].m.state == RState::Prefill && !reps_[r].colocated && reps_[r].partner < 0) {
+          set_state(r, RState::MutatingToDecode);
+          dd -= 1; dp += 1;
+        }
+      }
+    }
+    for (; dp > 0; --dp) if (!scale_up(true, now)) break;
+    for (; dd > 0; --dd) if (!scale_up(false, now)) break;
+    if (dp < 0) scale_down(true, now);
+    if (dd < 0) scale_down(false, now);
+  }
+
+  bool scale_up(bool prefill, double now) {
+    // 1. revive a replica that is shutting down
+    const RState shutting = prefill ? RState::ShuttingPrefill : RState::ShuttingDecode;
+    for (int r = 0; r < num_replicas(); ++r)
+      if (reps_[r].m.state == shutting) { set_state(r, prefill ? RState::Prefill : RState::Decode); return true; }
+    // 2. reuse a parked replica whose weights are still resident
+    for (int r = 0; r < num_replicas(); ++r)
+      if (reps_[r].m.state == RState::ShuttingNull) { scale_up_one(r, prefill, now); return true; }
+    // 3. bring up an inactive replica
+    for (int r = 0; r < num_replicas(); ++r)
+      if (reps_[r].m.state == RState::Inactive) return scale_up_one(r, prefill, now);
+    return false;
+  }
+
+  bool scale_up_one(int r, bool prefill, double now) {
+    Rep& rep = reps_[r];
+    if (rep.m.state == RState::ShuttingNull) {
+      rep.m.shutting_since = -1;
+      if (prefill) set_state(r, RState::Prefill);
+      else { set_state(r, RState::AusDecode); set_state(r, RState::Decode); }
+      return true;
+    }
+    if (rep.m.state != RState::Inactive) return false;
+    Action a;
+    a.replica = r;
+    a.dst_ranks = steer_.ranks_of_replica(r);
+    a.mock = features_.has("mock_transfer") || features_.has("motiv");
+    Op op;
+    op.replica = r; op.targets = {r};
+    if (features_.has("impl_sllm")) {
+      a.type = ActionType::LoadParams;
+      const int machine = steer_.machine_of(r * cfg_.tp);
+      bool hit = features_.has("cache_all_hit") || (features_.has("cache_replace") && steer_.host_cache_hit(machine, now));
+      if (features_.has("cache_all_miss")) hit = false;
+      a.load_case = hit ? 0 : 1;
+      set_state(r, prefill ? RState::LoadingPrefill : RState::LoadingDecode);
+    } else {
+      // sources: decode-side replicas (their NVLink egress is idle: KV flows into them), parked replicas,
+      // and prefill replicas when `unidirect` is on (router_v2/src/replica/cybernetics/exec_blitz.rs:1200-1243)
+      std::vector<int> sources;
+      for (int s = 0; s < num_replicas(); ++s) {
+        const RState st = reps_[s].m.state;
+        const bool ok = st == RState::Decode || st == RState::ShuttingDecode || st == RState::ShuttingNull ||
+                        (features_.has("unidirect") && st == RState::Prefill) || reps_[s].colocated;
+        if (ok && reps_[s].m.model_loaded && !steer_.nvlink_busy(s)) sources.push_back(s);
+      }
+      if (sources.empty())
+        for (int s = 0; s < num_replicas(); ++s)  // last resort: any loaded replica
+          if (reps_[s].m.model_loaded && !steer_.nvlink_busy(s) && s != r) sources.push_back(s);
+      if (sources.empty()) return false;
+      const bool multi = features_.has("impl_tanz") && sources.size() > 1;
+      const bool nvl = features_.has("impl_nvl");
+      a.type = multi ? ActionType::TanzBroadcast : (nvl ? ActionType::NvlBroadcast : ActionType::RdmaBroadcast);
+      if (!multi) sources.resize(1);
+      for (int s : sources) {
+        steer_.set_nvlink_busy(s, true);
+        reps_[s].m.marker = multi ? RState::TanzCasting : (nvl ? RState::NvlCasting : RState::RdmaCasting);
+        for (int rk : steer_.ranks_of_replica(s)) a.src_ranks.push_back(rk);
+      }
+      op.sources = sources;
+      const bool live = prefill && features_.has("live");
+      a.live = live;
+      if (live) {
+        set_state(r, RState::NewPrefill);
+        rep.zag_started = now;
+        rep.zag_seq = 0;
+        // pair one normal prefill replica as the helper that finishes relayed batches
+        for (int o = 0; o < num_replicas(); ++o) {
+          if (reps_[o].m.state == RState::Prefill && reps_[o].partner < 0 && !reps_[o].colocated) {
+            set_state(o, RState::OldPrefill);
+            reps_[o].partner = r;
+            rep.partner = o;
+            break;
+          }
+        }
+      } else {
+        set_state(r, prefill ? RState::LoadingPrefill : RState::LoadingDecode);
+      }
+    }
+    op.kind = a.type;
+    ops_[++next_op_] = op;
+    a.op_id = next_op_;
+    out_.push_back(a);
+    return true;
+  }
+
+  void scale_down(bool prefill, double now) {
+    // one per planner turn, never the last one, never a replica in a live pairing
+    const RState want = prefill ? RState::Prefill : RState::Decode;
+    if (num_in_state(want) <= 1) return;
+    int pick = -1;
+    uint32_t least = UINT32_MAX;
+    for (int r = num_replicas() - 1; r >= 0; --r) {
+      if (reps_[r].m.state != want || reps_[r].partner >= 0 || reps_[r].colocated) continue;
+      if (reps_[r].m.used_blocks < least) { least = reps_[r].m.used_blocks; pick = r; }
+    }
+    if (pick >= 0) begin_shutdown(pick, now);
+  }
+  void begin_shutdown(int r, double now) {
+    if (reps_[r].m.state == RState::Prefill) set_state(r, RState::ShuttingPrefill);
+    else if (reps_[r].m.state == RState::Decode) set_state(r, RState::ShuttingDecode);
+    else if (reps_[r].m.state == RState::ShuttingNull) { reps_[r].m.shutting_since = now - 1e9; }
+  }
+  void park(int r, double now) {
+    set_state(r, RState::ShuttingNull);
+    reps_[r].m.shutting_since = now;
+  }
+  void expire_parked(double now) {
+    for (int r = 0; r < num_replicas(); ++r) {
+      Rep& rep = reps_[r];
+      if (rep.m.state != RState::ShuttingNull || rep.m.shutting_since < 0) continue;
+      if ((now - rep.m.shutting_since) * 1e3 < cfg_.planner.scale_down_threshold_ms) continue;
+      if (steer_.nvlink_busy(r)) continue;  // still feeding someone
+      set_state(r, RState::Inactive);
+      rep.m.model_loaded = false;
+      rep.m.shutting_since = -1;
+      steer_.record_model_unloaded(r, now);
+      log_.push_back("Replica<" + std::to_string(r) + "> >>= unload");
+      Action a = make_simple(ActionType::ResetStatus, r, 0);
+      a.dst_ranks = steer_.ranks_of_replica(r);
+      out_.push_back(a);
+    }
+  }
+
+  void lose_replica(int r, double now, Op* op) {
+    (void)now;
+    Rep& rep = reps_[r];
+    auto fail_batch = [&](const ResidentBatch& b) {
+      for (uint64_t id : b.request_ids) {
+        Action a;
+        a.type = ActionType::Fail; a.request_id = id; a.final = true;
+        out_.push_back(a);
+        requests_.erase(id);
+      }
+    };
+    if (op && (op->kind == ActionType::Prefill || op->kind == ActionType::ZagPrefill)) {
+      // nothing was delivered yet: the requests go back to the head of the queue
+      std::vector<RequestEntry> es;
+      for (uint64_t id : op->batch.request_ids)
+        if (requests_.count(id)) es.push_back(requests_[id]);
+      queue_.requeue_front(es);
+    } else if (op) {
+      fail_batch(op->batch);
+    }
+    for (auto& b : rep.pending_migration) fail_batch(b);
+    for (auto& b : rep.decode_batches) if (!b.in_step) fail_batch(b);
+    rep.pending_migration.clear();
+    rep.decode_batches.clear();
+    rep.inflight_zag.clear();
+    rep.busy = rep.migrating = rep.relay_wait = false;
+    rep.m.used_blocks = 0;
+    rep.m.model_loaded = false;
+    rep.partner = -1;
+    steer_.record_model_unloaded(r, now);
+    steer_.set_nvlink_busy(r, false);
+    if (rep.m.state != RState::Inactive) {
+      RState old = rep.m.state;
+      rep.m.state = RState::Inactive;
+      rep.m.dst_busy = true;
+      log_transition(r, old, RState::Inactive);
+    }
+  }
+
+  ControllerConfig cfg_;
+  FeatureSet features_;
+  BatchQueue queue_;
+  Steersman steer_;
+  std::vector<Rep> reps_;
+  std::map<uint64_t, RequestEntry> requests_, finished_;
+  std::map<uint64_t, Op> ops_;
+  std::map<uint64_t, Relayed> relayed_;
+  std::vector<Action> out_;
+  std::vector<std::string> log_;
+  std::map<std::string, double> counters_, gauges_;
+  uint64_t next_op_ = 0;
+  uint64_t stats_prefill_tokens_ = 0, stats_decode_tokens_ = 0;
+  double last_plan_ = -1e9;
+  ScaleTarget last_target_;
+  std::pair<int, int> last_logged_{0, 0};
+
+ public:
+  const std::map<uint64_t, RequestEntry>& finished() const { return finished_; }
+  const std::map<std::string, double>& gauges() const { return gauges_; }
+  Steersman& steersman() { return steer_; }
+};
+
+}  // namespace blitz

@@ -1,0 +1,347 @@
+"""CPU tests of the native orchestrator core: queue budgets, validation, feature flags, planner,
+state machine, steersman, and whole-cluster virtual-time simulations (scaling, live scaling,
+ServerlessLLM baseline, replica failure)."""
+import math
+
+import pytest
+
+from blitz_scale_b200.runtime import core
+
+
+def E(i, inp, new, t=0.0):
+    return core.RequestEntry(i, inp, new, t)
+
+
+# ------------------------------------------------------------------------------------------------ queue
+def test_queue_empty_and_fifo():
+    q = core.BatchQueue(block_size=1)
+    assert q.next_batch(None, 1, 1) is None and q.next_batch(1, 1, 1) is None
+    q.append(E(0, 0, 1))
+    q.append(E(1, 0, 1))
+    nb = q.next_batch(None, 2, 2)
+    assert nb.batch.id == 0 and nb.batch.request_ids == [0, 1] and nb.batch.size == 2
+    q.append(E(2, 0, 1))
+    nb = q.next_batch(None, 2, 2)
+    assert nb.batch.id == 1 and nb.batch.request_ids == [2]
+
+
+def test_queue_min_size_restores_entries_and_waiting_tokens():
+    q = core.BatchQueue(block_size=1)
+    q.append(E(0, 5, 1))
+    q.append(E(1, 7, 1))
+    assert q.next_batch(3, 100, 100) is None      # fewer queued than min_size
+    assert q.waiting_prefill_tokens == 12
+    # budget admits only the first entry -> below min_size -> everything restored
+    assert q.next_batch(2, 5, 100) is None
+    assert len(q) == 2 and q.waiting_prefill_tokens == 12
+    nb = q.next_batch(2, 100, 100)
+    assert nb.batch.size == 2 and q.waiting_prefill_tokens == 0
+
+
+def test_queue_token_and_block_budgets():
+    q = core.BatchQueue(block_size=16)
+    for i in range(3):
+        q.append(E(i, 20, 12))      # 32 tokens = 2 blocks each
+    nb = q.next_batch(None, 1000, 1000, block_budget=5)
+    assert nb.batch.size == 2 and nb.batch.max_tokens == 64 and nb.batch.prompt_tokens == 40
+    assert len(q) == 1
+    # prefill budget: a 20-token prompt does not fit in 19
+    assert q.next_batch(None, 19, 1000) is None
+    # a single request larger than the total-token budget is never admitted
+    assert q.next_batch(None, 1000, 31) is None
+    assert q.next_batch(None, 1000, 32).batch.size == 1
+
+
+def test_queue_speculate_and_dropped_client():
+    q = core.BatchQueue(block_size=1, speculate=2)
+    q.append(E(0, 1, 1))
+    assert q.next_batch(None, 10, 3) is None           # 2 + speculate(2) > 3
+    assert q.next_batch(None, 10, 4).batch.size == 1
+    q.append(E(1, 4, 1))
+    q.append(E(2, 4, 1))
+    q.mark_client_gone(1)
+    nb = q.next_batch(None, 100, 100)
+    assert nb.batch.request_ids == [2] and q.dropped == 1 and q.waiting_prefill_tokens == 0
+
+
+# ------------------------------------------------------------------------------------------------ validation / features
+def test_validation_rules():
+    lim = core.ValidationLimits()
+    p = core.GenerateParams()
+    p.input_len, p.max_new_tokens = 10, 20
+    assert core.validate_request(p, lim) == ""
+    p.max_new_tokens = 0
+    assert "max_new_tokens" in core.validate_request(p, lim)
+    p.max_new_tokens = 5000
+    assert "must be <=" in core.validate_request(p, lim)
+    p.max_new_tokens, p.input_len = 10, 5000
+    assert "inputs" in core.validate_request(p, lim)
+    p.input_len, p.best_of = 10, 2
+    assert "sampling" in core.validate_request(p, lim)
+    p.do_sample = True
+    assert core.validate_request(p, lim) == ""
+    p.best_of, p.top_p = 1, 1.5
+    assert "top_p" in core.validate_request(p, lim)
+    p.top_p, p.top_n_tokens = 1.0, 9
+    assert "top_n_tokens" in core.validate_request(p, lim)
+    p.top_n_tokens, p.temperature = 0, 0.0
+    assert "temperature" in core.validate_request(p, lim)
+
+
+def test_feature_flags():
+    f = core.FeatureSet.parse("impl_blitz,impl_fast_pro,impl_live_pro")
+    for name in ("impl_rdma", "mutate", "fast", "impl_tanz", "impl_nvl", "live"):
+        assert f.has(name)
+    assert set(core.FeatureSet.parse("eval_all").list()) - {"eval_all"} == set(f.list())
+    s = core.FeatureSet.parse("impl_sllm,cache_replace")
+    assert s.has("impl_sllm") and not s.has("fast")
+    for bad in ("impl_blitz,impl_sllm,cache_replace", "impl_sllm", "impl_blitz,cache_all_hit", "impl_sllm,cache_replace,fast",
+                "nonsense", ""):
+        with pytest.raises(ValueError):
+            core.FeatureSet.parse(bad)
+
+
+# ------------------------------------------------------------------------------------------------ planner / states / steersman
+def test_planner_equations():
+    c = core.PlannerConfig()
+    c.tokens_prefilled_per_sec, c.tokens_transferred_per_sec, c.max_blocks_per_replica, c.block_size = 15000, 96000, 1000, 64
+    v = core.PlannerView()
+    v.num_prefill, v.num_decode = 1, 1
+    t = core.plan_scale(c, v)
+    assert (t.d_prefill, t.d_decode) == (0, 0)
+    # prefill demand: 40000 waiting tokens -> [ceil(40000/.7/15000), ceil(40000/.5/15000)] = [4, 6] -> midpoint 5
+    v.waiting_prefill_tokens = 40000
+    t = core.plan_scale(c, v)
+    assert (t.bands.prefill_thpt_min, t.bands.prefill_thpt_max) == (4, 6) and t.d_prefill == (4 + 6 + 1) // 2 - 1
+    # decode memory: 2500 used blocks -> [ceil(2500/.95/1000), ceil(2500/.75/1000)] = [3, 4] -> up to 4
+    v.waiting_prefill_tokens, v.decode_used_blocks = 0, 2500
+    t = core.plan_scale(c, v)
+    assert (t.bands.decode_mem_min, t.bands.decode_mem_max) == (3, 4) and t.d_decode == 3
+    # scale down by at most one, never below one, clamped to the configured maximum
+    v.decode_used_blocks, v.num_decode, v.num_prefill = 0, 4, 3
+    t = core.plan_scale(c, v)
+    assert (t.d_prefill, t.d_decode) == (-1, -1)
+    v.num_decode = v.num_prefill = 1
+    assert core.plan_scale(c, v).d_decode == 0
+    v.decode_used_blocks, c.max_decode = 100000, 3
+    assert core.plan_scale(c, v).d_decode == 2
+    # KV bandwidth: tokens parked on prefill replicas
+    v.decode_used_blocks, v.prefill_used_blocks, c.max_decode = 0, 3000, 8     # 192000 tokens
+    t = core.plan_scale(c, v)
+    assert (t.bands.decode_kv_min, t.bands.decode_kv_max) == (math.ceil(192000 / .8 / 96000), math.ceil(192000 / .4 / 96000))
+
+
+def test_state_machine_table():
+    names = core.replica_state_names()
+    assert len(names) == 20 and names[0] == "Inactive"
+    ok = [("Inactive", "LoadingPrefill"), ("LoadingPrefill", "Prefill"), ("Inactive", "NewPrefill"),
+          ("NewPrefill", "RefractoryPrefill"), ("RefractoryPrefill", "Prefill"), ("Prefill", "OldPrefill"),
+          ("OldPrefill", "Prefill"), ("Prefill", "MutatingToDecode"), ("MutatingToDecode", "Decode"),
+          ("Prefill", "ShuttingPrefill"), ("ShuttingPrefill", "ShuttingNull"), ("Decode", "ShuttingDecode"),
+          ("ShuttingDecode", "ShuttingNull"), ("ShuttingNull", "Inactive"), ("ShuttingNull", "Prefill"),
+          ("ShuttingPrefill", "Prefill"), ("LoadingDecode", "AusDecode"), ("AusDecode", "Decode")]
+    for a, b in ok:
+        assert core.transition_allowed(a, b), (a, b)
+    for a, b in [("Inactive", "Prefill"), ("Inactive", "Decode"), ("Decode", "Prefill"), ("NewPrefill", "Decode"),
+                 ("ShuttingNull", "NewPrefill"), ("OldPrefill", "Decode")]:
+        assert not core.transition_allowed(a, b), (a, b)
+
+
+def test_steersman():
+    s = core.Steersman([0, 0, 0, 0, 1, 1, 1, 1], 2, 30.0)
+    assert s.ranks_of_replica(1) == [2, 3] and s.replica_of_rank(5) == 2
+    s.record_model_loaded(0)
+    s.record_model_loaded(2)
+    plan = s.assign_nvlink_chains([0, 2], [1, 3])
+    assert plan == {0: [1], 2: [3]}           # same-machine sources only
+    s.set_nvlink_busy(0, True)
+    assert s.assign_nvlink_chains([0, 2], [1, 3]) == {2: [3]}
+    s.set_nvlink_busy(0, False)
+    assert s.assign_tanz_chains([0, 2], [1]) == [([0], [1])]
+    # host cache TTL (ServerlessLLM baseline)
+    s.record_model_unloaded(0, 100.0)
+    assert s.host_cache_hit(0, 120.0) and not s.host_cache_hit(0, 131.0) and not s.host_cache_hit(1, 120.0)
+    s.register_model("llama3_8b", "/models/l3", 16.0)
+    assert s.model_info("llama3_8b") == ("/models/l3", 16.0) and s.model_info("x") is None
+
+
+# ------------------------------------------------------------------------------------------------ traces
+def test_trace_generators_are_seeded_and_calibrated():
+    spec = core.TraceSpec()
+    spec.phases = [core.RatePhase(0.0, 4.0)]
+    spec.duration, spec.seed = 500.0, 0
+    spec.input.kind, spec.input.a, spec.input.b = core.LengthDist.Kind.Uniform, 32, 512
+    spec.output.kind, spec.output.a, spec.output.b = core.LengthDist.Kind.Uniform, 16, 128
+    a, b = core.generate_trace(spec), core.generate_trace(spec)
+    assert [(x.t, x.input_len, x.output_len) for x in a] == [(x.t, x.input_len, x.output_len) for x in b]
+    assert abs(len(a) / 500.0 - 4.0) < 0.4
+    assert all(32 <= x.input_len <= 512 and 16 <= x.output_len <= 128 for x in a)
+    gaps = [a[i + 1].t - a[i].t for i in range(len(a) - 1)]
+    mean = sum(gaps) / len(gaps)
+    cv = (sum((g - mean) ** 2 for g in gaps) / len(gaps)) ** 0.5 / mean
+    assert abs(cv - 1.0) < 0.15                      # Poisson
+    spec.cv, spec.seed = 4.0, 1
+    spec.phases = [core.RatePhase(0.0, 2.0), core.RatePhase(250.0, 16.0)]
+    spec.input.kind, spec.input.a, spec.input.b, spec.input.max_len = core.LengthDist.Kind.LogNormal, 512, 1.0, 4096
+    g = core.generate_trace(spec)
+    early = sum(1 for x in g if x.t < 250) / 250.0
+    late = sum(1 for x in g if x.t >= 250) / 250.0
+    assert 0.8 < early < 3.5 and 10 < late < 22     # the rate step is visible
+    gaps = [g[i + 1].t - g[i].t for i in range(len(g) - 1) if g[i].t >= 250]
+    mean = sum(gaps) / len(gaps)
+    cv = (sum((x - mean) ** 2 for x in gaps) / len(gaps)) ** 0.5 / mean
+    assert cv > 2.5                                  # bursty
+    lens = sorted(x.input_len for x in g)
+    assert 380 < lens[len(lens) // 2] < 680 and lens[-1] <= 4096
+
+
+def test_csv_trace(tmp_path):
+    p = tmp_path / "t.csv"
+    p.write_text("timestamp,prefill,decode\n1000,100,20\n500,9000,5\n")
+    tr = core.load_trace_csv(str(p), 2.0, 4095)
+    assert [(x.t, x.input_len, x.output_len) for x in tr] == [(0.25, 4095, 5), (0.5, 100, 20)]
+
+
+# ------------------------------------------------------------------------------------------------ whole-cluster simulations
+def _cfg(states, features, **kw):
+    c = core.ControllerConfig()
+    c.num_ranks, c.tp = len(states), 1
+    c.init_states = states
+    c.features = features
+    c.max_blocks_per_replica = kw.get("blocks", 4000)
+    p = c.planner
+    p.tokens_prefilled_per_sec, p.tokens_transferred_per_sec = 15000, 96000
+    p.max_prefill, p.max_decode = kw.get("max_p", 4), kw.get("max_d", 4)
+    c.planner = p
+    for k, v in kw.items():
+        if hasattr(c, k):
+            setattr(c, k, v)
+    return c
+
+
+def _trace(rate_phases, duration, seed=0, cv=1.0, n=10 ** 9, inp=(32, 512), out=(16, 128)):
+    s = core.TraceSpec()
+    s.phases = [core.RatePhase(t, r) for t, r in rate_phases]
+    s.duration, s.seed, s.cv, s.max_requests = duration, seed, cv, n
+    s.input.kind, s.input.a, s.input.b = core.LengthDist.Kind.Uniform, inp[0], inp[1]
+    s.output.kind, s.output.a, s.output.b = core.LengthDist.Kind.Uniform, out[0], out[1]
+    return core.generate_trace(s)
+
+
+def _check_conservation(rep, trace):
+    assert rep.submitted == len(trace)
+    assert rep.completed + rep.failed == len(trace)
+    assert rep.leftover_blocks == 0
+    want = sum(x.output_len for x in trace)
+    if rep.failed == 0:
+        assert rep.delivered_tokens == want
+        by_id = {r.id: r for r in rep.requests}
+        for i, x in enumerate(trace):
+            assert by_id[i].output_len == x.output_len and by_id[i].ttft > 0
+
+
+def test_sim_static_pd_pair_serves_everything():
+    cfg = _cfg(["Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+    trace = _trace([(0, 4.0)], 50.0, n=200)
+    rep = core.ClusterSim(cfg, core.CostModel()).run(trace)
+    _check_conservation(rep, trace)
+    assert any("Replica<0> boot => Prefill" in l for l in rep.log)
+
+
+def test_sim_is_deterministic():
+    cfg = _cfg(["Prefill", "Decode", "Inactive", "Inactive"], "impl_blitz,impl_fast_pro,impl_live_pro")
+    trace = _trace([(0, 2.0), (5.0, 40.0)], 12.0, seed=3, cv=4.0, inp=(256, 2048))
+    a = core.ClusterSim(cfg, core.CostModel()).run(trace)
+    b = core.ClusterSim(cfg, core.CostModel()).run(trace)
+    assert a.log == b.log and [(r.id, r.ttft) for r in a.requests] == [(r.id, r.ttft) for r in b.requests]
+
+
+@pytest.mark.parametrize("features", ["impl_blitz,impl_nvl", "impl_blitz,impl_fast_pro", "impl_blitz,impl_fast_pro,impl_live_pro",
+                                      "impl_sllm,cache_replace", "impl_sllm,cache_all_hit,mutate"])
+def test_sim_burst_triggers_scale_out_and_conserves_requests(features):
+    cfg = _cfg(["Prefill", "Decode", "Inactive", "Inactive", "Inactive", "Inactive"], features)
+    cm = core.CostModel()
+    cm.prefill_tokens_per_s = 20000
+    trace = _trace([(0, 2.0), (4.0, 30.0), (10.0, 1.0)], 16.0, seed=1, inp=(512, 2048), out=(16, 64))
+    rep = core.ClusterSim(cfg, cm).run(trace)
+    _check_conservation(rep, trace)
+    ups = [l for l in rep.log if "Inactive =>" in l]
+    assert ups, "the burst must trigger a scale-out"
+    assert rep.scale_up_latency and all(v > 0 for v in rep.scale_up_latency.values())
+    if "live" in features or "impl_live_pro" in features:
+        assert any("=> NewPrefill" in l for l in rep.log) and any("=> OldPrefill" in l for l in rep.log)
+        assert any("RefractoryPrefill => Prefill" in l for l in rep.log)
+    if "impl_sllm" in features:
+        assert not any("NewPrefill" in l for l in rep.log)
+    # after the burst the planner parks replicas and later unloads them
+    assert any("=> ShuttingNull" in l for l in rep.log)
+
+
+def test_sim_live_scaling_serves_on_the_loading_replica():
+    states = ["Prefill", "Decode", "Inactive", "Inactive"]
+    cm = core.CostModel()
+    cm.prefill_tokens_per_s, cm.nvlink_gbs = 20000, 8.0       # slow transfer: 2 s per model
+    trace = _trace([(0, 1.0), (2.0, 25.0), (8.0, 1.0)], 12.0, seed=5, inp=(1024, 2048), out=(8, 16))
+    live = core.ClusterSim(_cfg(states, "impl_blitz,impl_fast_pro,impl_live_pro"), cm).run(trace)
+    stop = core.ClusterSim(_cfg(states, "impl_blitz,impl_fast_pro"), cm).run(trace)
+    _check_conservation(live, trace)
+    _check_conservation(stop, trace)
+    t_of = lambda rep, pat: min(float(l[1:l.index("]")]) for l in rep.log if pat in l)
+    # the new replica takes requests the moment scaling is triggered, not when its parameters have landed
+    assert t_of(live, "Inactive => NewPrefill") + 1.0 < t_of(live, "RefractoryPrefill => Prefill")
+    assert any("Prefill => OldPrefill" in l for l in live.log) and any("OldPrefill => Prefill" in l for l in live.log)
+    assert not any("NewPrefill" in l for l in stop.log)
+    mean = lambda rep: sum(r.ttft for r in rep.requests) / len(rep.requests)
+    assert mean(live) < 1.5 * mean(stop)
+
+
+def test_sim_sllm_host_cache_policy():
+    states = ["Prefill", "Decode", "Inactive"]
+    trace = _trace([(0, 1.0), (2.0, 30.0), (6.0, 0.5)], 9.0, seed=2, inp=(512, 2048), out=(8, 32))
+    cm = core.CostModel()
+    cm.prefill_tokens_per_s = 8000
+    miss = core.ClusterSim(_cfg(states, "impl_sllm,cache_all_miss"), cm).run(trace)
+    hit = core.ClusterSim(_cfg(states, "impl_sllm,cache_all_hit"), cm).run(trace)
+    _check_conservation(miss, trace)
+    _check_conservation(hit, trace)
+    assert min(hit.scale_up_latency.values()) < min(miss.scale_up_latency.values())
+
+
+def test_sim_replica_failure_requeues_or_fails_but_never_hangs():
+    cfg = _cfg(["Prefill", "Prefill", "Decode", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+    trace = _trace([(0, 20.0)], 6.0, seed=4, inp=(256, 1024), out=(8, 32))
+    rep = core.ClusterSim(cfg, core.CostModel()).run(trace, kill_replica=0, kill_at=2.0)
+    assert rep.submitted == len(trace) and rep.completed + rep.failed == len(trace)
+    assert rep.completed > 0.9 * len(trace)           # prefill work is re-queued, not lost
+    assert any("Replica<0> Prefill => Inactive" in l for l in rep.log)
+    assert rep.leftover_blocks == 0
+    rep = core.ClusterSim(cfg, core.CostModel()).run(trace, kill_replica=2, kill_at=2.0)
+    assert rep.completed + rep.failed == len(trace) and rep.failed > 0 and rep.leftover_blocks == 0
+
+
+def test_mutation_prefill_to_decode():
+    # a prompt burst keeps two prefill replicas busy; when it ends the long outputs still fill the single
+    # decode replica: prefill surplus + decode shortage with no spare GPU -> one prefill replica mutates
+    cfg = _cfg(["Prefill", "Prefill", "Decode"], "impl_blitz,impl_nvl", blocks=250, max_p=2)
+    cm = core.CostModel()
+    cm.prefill_tokens_per_s = 6000
+    trace = _trace([(0, 10.0), (3.0, 0.01)], 20.0, seed=6, inp=(1024, 2048), out=(400, 500))
+    rep = core.ClusterSim(cfg, cm).run(trace)
+    _check_conservation(rep, trace)
+    assert any("Prefill => MutatingToDecode" in l for l in rep.log)
+    assert any("MutatingToDecode => Decode" in l for l in rep.log)
+
+
+def test_manual_scale_and_log_lines():
+    cfg = _cfg(["Prefill", "Decode", "Inactive"], "impl_blitz,impl_nvl,manually_scale")
+    ctl = core.Controller(cfg)
+    assert ctl.manual_scale(2, "Decode", 0.0)
+    acts = ctl.step(0.0)
+    bc = [a for a in acts if a.type == core.ActionType.NvlBroadcast]
+    assert len(bc) == 1 and bc[0].dst_ranks == [2] and bc[0].src_ranks == [1]
+    assert ctl.state_name(2) == "LoadingDecode" and ctl.metric(1).marker == "NvlCasting"
+    ctl.on_params_done(bc[0].op_id, 0.05)
+    assert ctl.state_name(2) == "Decode" and ctl.metric(1).marker == "" and not ctl.metric(2).dst_busy
+    log = ctl.drain_log()
+    assert "Replica<2> Inactive => LoadingDecode" in log and "Replica<2> AusDecode => Decode" in log
+    assert ctl.system_metrics_line().startswith("System Metrics: prefill_tokens: 0, decode_tokens: 0")
