@@ -45,7 +45,7 @@ struct DecodeTcParams {
   int64_t out_stride;
   float* part_o;
   float* part_lse;
-  int q_heads, kv_heads, group, page_size, max_pages, num_splits, box_tokens;
+  int batch, q_heads, kv_heads, group, page_size, max_pages, num_splits, box_tokens;
   float scale_log2;
   int* status;
 };
@@ -87,6 +87,27 @@ struct TcCfg {
   static constexpr int kSmemBytes = kTcStages * kStageBytes + kMergeFloats * 4 + 1024 + 128;
 };
 
+// Work item = (sequence, kv head, split).  The kernel is persistent: each CTA walks items
+// blockIdx.x, blockIdx.x + gridDim.x, ... and the producer keeps streaming the next item's pages while
+// the consumers finish the current one, so the 4-stage pipeline never drains between items.
+struct DecItem {
+  int b, h, split, pg_beg, seq_len, c_beg, c_end;
+};
+__device__ __forceinline__ DecItem dec_item(const DecodeTcParams& p, int item) {
+  DecItem it;
+  it.split = item % p.num_splits;
+  it.h = (item / p.num_splits) % p.kv_heads;
+  it.b = item / (p.num_splits * p.kv_heads);
+  it.pg_beg = p.indptr[it.b];
+  const int npages = p.indptr[it.b + 1] - it.pg_beg;
+  it.seq_len = npages > 0 ? (npages - 1) * p.page_size + p.last_page_len[it.b] : 0;
+  const int nchunks = (it.seq_len + kTcChunk - 1) / kTcChunk;
+  const int cps = (nchunks + p.num_splits - 1) / p.num_splits;
+  it.c_beg = min(nchunks, it.split * cps);
+  it.c_end = min(nchunks, (it.split + 1) * cps);
+  return it;
+}
+
 template <typename T, int HD>
 __global__ void __launch_bounds__(kTcThreads)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcParams p) {
@@ -102,16 +123,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcPa
   uint64_t* empty_bar = full_bar + kTcStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kTcStages);
 
-  const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.group;
-
-  const int pg_beg = p.indptr[b];
-  const int npages = p.indptr[b + 1] - pg_beg;
-  const int seq_len = npages > 0 ? (npages - 1) * p.page_size + p.last_page_len[b] : 0;
-  const int nchunks = (seq_len + kTcChunk - 1) / kTcChunk;
-  const int cps = (nchunks + p.num_splits - 1) / p.num_splits;
-  const int c_beg = min(nchunks, split * cps), c_end = min(nchunks, (split + 1) * cps);
+  const int num_items = p.batch * p.kv_heads * p.num_splits;
 
   // zero the stages once: rows a short last chunk never fills must stay finite
   for (int i = threadIdx.x; i < kTcStages * Cfg::kStageBytes / 16; i += kTcThreads)
@@ -135,164 +149,175 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcPa
       const uint32_t box_bytes = static_cast<uint32_t>(bt) * 128u;
       int stage = 0;
       uint32_t phase = 0;
-      for (int c = c_beg; c < c_end; ++c) {
-        if (!ptx::bounded_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
-          if (p.status) atomicCAS(p.status, 0, kStatusTimeoutProducer);
-          break;
-        }
-        const int tok0 = c * kTcChunk;
-        const int ntok = min(kTcChunk, seq_len - tok0);
-        const int pieces = (ntok + bt - 1) / bt;
-        ptx::mbar_expect_tx(&full_bar[stage], static_cast<uint32_t>(pieces) * 2u * SL * box_bytes);
-        uint8_t* sb = smem + stage * Cfg::kStageBytes;
-        for (int i = 0; i < pieces; ++i) {
-          const int t = tok0 + i * bt;
-          int page = p.indices[pg_beg + t / p.page_size];
-          if (page < 0 || page >= p.max_pages) {
-            if (p.status) atomicCAS(p.status, 0, kStatusBadIndex);
-            page = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const DecItem it = dec_item(p, item);
+        for (int c = it.c_beg; c < it.c_end; ++c) {
+          if (!ptx::bounded_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+            if (p.status) atomicCAS(p.status, 0, kStatusTimeoutProducer);
+            ok = false;
+            break;
           }
-          const int z = page * 2 * p.page_size + (t % p.page_size);
+          const int tok0 = c * kTcChunk;
+          const int ntok = min(kTcChunk, it.seq_len - tok0);
+          const int pieces = (ntok + bt - 1) / bt;
+          ptx::mbar_expect_tx(&full_bar[stage], static_cast<uint32_t>(pieces) * 2u * SL * box_bytes);
+          uint8_t* sb = smem + stage * Cfg::kStageBytes;
+          for (int i = 0; i < pieces; ++i) {
+            const int t = tok0 + i * bt;
+            int page = p.indices[it.pg_beg + t / p.page_size];
+            if (page < 0 || page >= p.max_pages) {
+              if (p.status) atomicCAS(p.status, 0, kStatusBadIndex);
+              page = 0;
+            }
+            const int z = page * 2 * p.page_size + (t % p.page_size);
 #pragma unroll
-          for (int s = 0; s < SL; ++s) {
-            ptx::tma_load_3d(sb + s * kTcSlabBytes + i * box_bytes, &tmap, &full_bar[stage], s * 64, h, z);
-            ptx::tma_load_3d(sb + (SL + s) * kTcSlabBytes + i * box_bytes, &tmap, &full_bar[stage], s * 64, h,
-                             z + p.page_size);
+            for (int s = 0; s < SL; ++s) {
+              ptx::tma_load_3d(sb + s * kTcSlabBytes + i * box_bytes, &tmap, &full_bar[stage], s * 64, it.h, z);
+              ptx::tma_load_3d(sb + (SL + s) * kTcSlabBytes + i * box_bytes, &tmap, &full_bar[stage], s * 64, it.h,
+                               z + p.page_size);
+            }
+          }
+          if (++stage == kTcStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ consumers (128 threads, named barrier 1)
+    const int g = lane >> 2, t4 = lane & 3;
+    const int tokw = warp * 16;
+    const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: matrix index and row within it
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;  // after a timeout this warp stops waiting but keeps meeting the others at the barriers
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const DecItem it = dec_item(p, item);
+      // Q as A fragments (rows >= G are zero padding; rows 8..15 are never populated since G <= 8)
+      uint32_t qa0[HD / 16], qa2[HD / 16];
+      {
+        const T* qrow = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(it.b) * p.q_stride +
+                        static_cast<int64_t>(it.h * G + g) * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          qa0[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4) : 0u;
+          qa2[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8) : 0u;
+        }
+      }
+      float o[HD / 8][4];
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      float m = -INFINITY, l = 0.f;
+      for (int c = it.c_beg; c < it.c_end; ++c) {
+        if (ok && !ptx::bounded_mbar_wait(&full_bar[stage], phase, abort_flag)) {
+          if (p.status && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+          ok = false;
+        }
+        const int nvalid = min(kTcChunk, it.seq_len - c * kTcChunk);
+        if (ok && tokw < nvalid) {
+          const uint32_t kbase = ptx::smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t vbase = kbase + SL * kTcSlabBytes;
+          float s_lo[4] = {0.f, 0.f, 0.f, 0.f}, s_hi[4] = {0.f, 0.f, 0.f, 0.f};
+          {
+            const int tok = tokw + (mi >> 1) * 8 + mr;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+              const int ch = ks * 2 + (mi & 1);
+              const uint32_t addr = kbase + (ch >> 3) * kTcSlabBytes + tok * 128 + (((ch & 7) ^ (tok & 7)) << 4);
+              uint32_t b0, b1, b2, b3;
+              ldmatrix_x4(addr, b0, b1, b2, b3);
+              mma16816<T>(s_lo, qa0[ks], 0u, qa2[ks], 0u, b0, b1);
+              mma16816<T>(s_hi, qa0[ks], 0u, qa2[ks], 0u, b2, b3);
+            }
+          }
+          const int col = tokw + 2 * t4;
+          const bool v0 = col < nvalid, v1 = col + 1 < nvalid, v2 = col + 8 < nvalid, v3 = col + 9 < nvalid;
+          float mx = -INFINITY;
+          if (v0) mx = fmaxf(mx, s_lo[0]);
+          if (v1) mx = fmaxf(mx, s_lo[1]);
+          if (v2) mx = fmaxf(mx, s_hi[0]);
+          if (v3) mx = fmaxf(mx, s_hi[1]);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          const float m_new = fmaxf(m, mx * p.scale_log2);
+          const float alpha = exp2f(m - m_new);  // m = -inf -> 0
+          const float p0 = v0 ? exp2f(s_lo[0] * p.scale_log2 - m_new) : 0.f;
+          const float p1 = v1 ? exp2f(s_lo[1] * p.scale_log2 - m_new) : 0.f;
+          const float p2 = v2 ? exp2f(s_hi[0] * p.scale_log2 - m_new) : 0.f;
+          const float p3 = v3 ? exp2f(s_hi[1] * p.scale_log2 - m_new) : 0.f;
+          l = l * alpha + (p0 + p1 + p2 + p3);
+          m = m_new;
+          const uint32_t pa0 = pk2<T>(p0, p1), pa2 = pk2<T>(p2, p3);
+#pragma unroll
+          for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= alpha;
+            o[i][1] *= alpha;
+          }
+          {
+            const int tok = tokw + (mi & 1) * 8 + mr;
+#pragma unroll
+            for (int np = 0; np < HD / 16; ++np) {
+              const int ch = np * 2 + (mi >> 1);
+              const uint32_t addr = vbase + (ch >> 3) * kTcSlabBytes + tok * 128 + (((ch & 7) ^ (tok & 7)) << 4);
+              uint32_t b0, b1, b2, b3;
+              ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+              mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
+              mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&empty_bar[stage]);
         if (++stage == kTcStages) {
           stage = 0;
           phase ^= 1u;
         }
       }
-    }
-  } else {
-    // ------------------------------------------------------------ consumers
-    const int g = lane >> 2, t4 = lane & 3;
-    // Q as A fragments (rows >= G are zero padding; rows 8..15 are never populated since G <= 8)
-    uint32_t qa0[HD / 16], qa2[HD / 16];
-    {
-      const T* qrow = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(b) * p.q_stride +
-                      static_cast<int64_t>(h * G + g) * HD;
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        qa0[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4) : 0u;
-        qa2[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8) : 0u;
+      // per-warp partials -> shared memory (rows < 8 only), then the 4 warps combine them
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (t4 == 0) {
+        mrg_m[warp * 8 + g] = m;
+        mrg_l[warp * 8 + g] = l;
       }
-    }
-    float o[HD / 8][4];
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    const int tokw = warp * 16;
-    const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: matrix index and row within it
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int c = c_beg; c < c_end; ++c) {
-      if (!ptx::bounded_mbar_wait(&full_bar[stage], phase, abort_flag)) {
-        if (p.status && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
-        break;
+      for (int i = 0; i < HD / 8; ++i) {
+        float2 v = make_float2(o[i][0], o[i][1]);
+        *reinterpret_cast<float2*>(&mrg_o[(warp * 8 + g) * HD + i * 8 + 2 * t4]) = v;
       }
-      const int nvalid = min(kTcChunk, seq_len - c * kTcChunk);
-      if (tokw < nvalid) {
-        const uint32_t kbase = ptx::smem_u32(smem + stage * Cfg::kStageBytes);
-        const uint32_t vbase = kbase + SL * kTcSlabBytes;
-        float s_lo[4] = {0.f, 0.f, 0.f, 0.f}, s_hi[4] = {0.f, 0.f, 0.f, 0.f};
-        {
-          const int tok = tokw + (mi >> 1) * 8 + mr;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int e = threadIdx.x; e < G * HD; e += 128) {
+        const int gg = e / HD, d = e % HD;
+        float M = -INFINITY;
 #pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) {
-            const int ch = ks * 2 + (mi & 1);
-            const uint32_t addr = kbase + (ch >> 3) * kTcSlabBytes + tok * 128 + (((ch & 7) ^ (tok & 7)) << 4);
-            uint32_t b0, b1, b2, b3;
-            ldmatrix_x4(addr, b0, b1, b2, b3);
-            mma16816<T>(s_lo, qa0[ks], 0u, qa2[ks], 0u, b0, b1);
-            mma16816<T>(s_hi, qa0[ks], 0u, qa2[ks], 0u, b2, b3);
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mrg_m[w * 8 + gg]);
+        float L = 0.f, O = 0.f;
+        if (M > -INFINITY) {
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float sc = exp2f(mrg_m[w * 8 + gg] - M);
+            L += mrg_l[w * 8 + gg] * sc;
+            O += mrg_o[(w * 8 + gg) * HD + d] * sc;
           }
         }
-        const int col = tokw + 2 * t4;
-        const bool v0 = col < nvalid, v1 = col + 1 < nvalid, v2 = col + 8 < nvalid, v3 = col + 9 < nvalid;
-        float mx = -INFINITY;
-        if (v0) mx = fmaxf(mx, s_lo[0]);
-        if (v1) mx = fmaxf(mx, s_lo[1]);
-        if (v2) mx = fmaxf(mx, s_hi[0]);
-        if (v3) mx = fmaxf(mx, s_hi[1]);
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m, mx * p.scale_log2);
-        const float alpha = exp2f(m - m_new);  // m = -inf -> 0
-        const float p0 = v0 ? exp2f(s_lo[0] * p.scale_log2 - m_new) : 0.f;
-        const float p1 = v1 ? exp2f(s_lo[1] * p.scale_log2 - m_new) : 0.f;
-        const float p2 = v2 ? exp2f(s_hi[0] * p.scale_log2 - m_new) : 0.f;
-        const float p3 = v3 ? exp2f(s_hi[1] * p.scale_log2 - m_new) : 0.f;
-        l = l * alpha + (p0 + p1 + p2 + p3);
-        m = m_new;
-        const uint32_t pa0 = pk2<T>(p0, p1), pa2 = pk2<T>(p2, p3);
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-          o[i][0] *= alpha;
-          o[i][1] *= alpha;
-        }
-        {
-          const int tok = tokw + (mi & 1) * 8 + mr;
-#pragma unroll
-          for (int np = 0; np < HD / 16; ++np) {
-            const int ch = np * 2 + (mi >> 1);
-            const uint32_t addr = vbase + (ch >> 3) * kTcSlabBytes + tok * 128 + (((ch & 7) ^ (tok & 7)) << 4);
-            uint32_t b0, b1, b2, b3;
-            ldmatrix_x4_trans(addr, b0, b1, b2, b3);
-            mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
-            mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
-          }
+        const float val = L > 0.f ? O / L : 0.f;
+        const int head = it.h * G + gg;
+        if (p.num_splits == 1) {
+          T* op = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(it.b) * p.out_stride +
+                  static_cast<int64_t>(head) * HD;
+          if (std::is_same<T, __nv_bfloat16>::value)
+            reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16(val);
+          else
+            reinterpret_cast<__half*>(op)[d] = __float2half(val);
+        } else {
+          const int64_t base = (static_cast<int64_t>(it.b) * p.q_heads + head) * p.num_splits + it.split;
+          p.part_o[base * HD + d] = val;
+          if (d == 0) p.part_lse[base] = L > 0.f ? M + log2f(L) : -INFINITY;
         }
       }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&empty_bar[stage]);
-      if (++stage == kTcStages) {
-        stage = 0;
-        phase ^= 1u;
-      }
-    }
-    // per-warp partials -> shared memory (rows < 8 only)
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (t4 == 0) {
-      mrg_m[warp * 8 + g] = m;
-      mrg_l[warp * 8 + g] = l;
-    }
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-      float2 v = make_float2(o[i][0], o[i][1]);
-      *reinterpret_cast<float2*>(&mrg_o[(warp * 8 + g) * HD + i * 8 + 2 * t4]) = v;
-    }
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < G * HD; e += kTcThreads) {
-    const int gg = e / HD, d = e % HD;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, mrg_m[w * 8 + gg]);
-    float L = 0.f, O = 0.f;
-    if (M > -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float sc = exp2f(mrg_m[w * 8 + gg] - M);
-        L += mrg_l[w * 8 + gg] * sc;
-        O += mrg_o[(w * 8 + gg) * HD + d] * sc;
-      }
-    }
-    const float val = L > 0.f ? O / L : 0.f;
-    const int head = h * G + gg;
-    if (p.num_splits == 1) {
-      T* op = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(b) * p.out_stride + static_cast<int64_t>(head) * HD;
-      if (std::is_same<T, __nv_bfloat16>::value)
-        reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16(val);
-      else
-        reinterpret_cast<__half*>(op)[d] = __float2half(val);
-    } else {
-      const int64_t base = (static_cast<int64_t>(b) * p.q_heads + head) * p.num_splits + split;
-      p.part_o[base * HD + d] = val;
-      if (d == 0) p.part_lse[base] = L > 0.f ? M + log2f(L) : -INFINITY;
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // merge buffers are reused by the next item
     }
   }
 }
@@ -332,8 +357,9 @@ static int launch_tc(const CUtensorMap& tm, const DecodeTcParams& p, int batch, 
     if (e != cudaSuccess) return (int)e;
     attr = true;
   }
-  dim3 grid(batch, p.kv_heads, p.num_splits);
-  kern<<<grid, kTcThreads, TcCfg<HD>::kSmemBytes, stream>>>(tm, p);
+  const int items = batch * p.kv_heads * p.num_splits;
+  const int sms = device_sm_count();
+  kern<<<items < sms ? items : sms, kTcThreads, TcCfg<HD>::kSmemBytes, stream>>>(tm, p);
   return (int)cudaGetLastError();
 }
 
@@ -372,7 +398,7 @@ int blitz_attn_decode(const void* q, int64_t q_stride, const void* kv_layer, con
   p.out = out; p.out_stride = out_stride;
   p.part_o = reinterpret_cast<float*>(workspace);
   p.part_lse = p.part_o ? p.part_o + (int64_t)batch * q_heads * num_splits * head_dim : nullptr;
-  p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size; p.max_pages = max_pages;
+  p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size; p.max_pages = max_pages;
   p.num_splits = num_splits; p.box_tokens = bt; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
   int rc;
   if (dtype == 1)

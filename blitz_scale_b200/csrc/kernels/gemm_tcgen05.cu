@@ -62,7 +62,13 @@ struct GemmCfg {
     int s = (kUsableBytes - kABytes) / (a_stage_bytes(a_rows) + kBBytes);
     return s > kMaxStages ? kMaxStages : s;
   }
-  static constexpr int kTmemCols = 2 * BN;
+  // A tcgen05.mma that accumulates into the accumulator of the previous one waits for it (~140 cycles
+  // measured), which is longer than a 128xNx16 instruction runs when N < 256.  Narrow tiles therefore
+  // rotate their K steps over kSplit independent TMEM accumulators (summed in the epilogue) so the
+  // tensor pipe always has independent work: 4 accumulators for N = 64, 2 for N = 128.
+  static constexpr int kSplit = 256 / BN;
+  static constexpr int kAccCols = kSplit * BN;   // columns of one (double-buffered) accumulator set = 256
+  static constexpr int kTmemCols = 2 * kAccCols; // 512: the whole TMEM of the SM
 };
 
 template <typename T>
@@ -205,7 +211,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           break;
         }
         ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * Cfg::kAccCols);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::bounded_mbar_wait(&full_bar[stage], phase, abort_flag)) {
             if (p.status) atomicCAS(p.status, 0, kStatusTimeoutMma);
@@ -227,7 +233,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               // 8-K-row groups 1024 B apart (stride offset); 16 K-rows = 2048 B.
               bdesc = ptx::make_smem_desc(b_base + k * 2048, 8192, 1024, ptx::kLayoutSw128);
             }
-            ptx::umma_f16_ss(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            // K step k goes to sub-accumulator k % kSplit; its first use in a tile overwrites
+            ptx::umma_f16_ss(d_tmem + static_cast<uint32_t>((k % Cfg::kSplit) * BN), adesc, bdesc, kIdesc,
+                             (kb != 0 || k >= Cfg::kSplit) ? 1u : 0u);
           }
           ptx::umma_commit(&empty_bar[stage]);
           if (++stage == S) {
@@ -257,18 +265,39 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         break;
       }
       ptx::tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * Cfg::kAccCols);
       const int row = m0 + row_in_tile;
       const bool row_ok = row < p.M;
 #pragma unroll 1
       for (int c = 0; c < kOutCols; c += 32) {
         uint32_t v[32];
         ptx::tmem_ld_32x32(taddr + c, v);
+        if (Cfg::kSplit > 1) {  // sum the sub-accumulators
+#pragma unroll
+          for (int j = 1; j < Cfg::kSplit; ++j) {
+            uint32_t w[32];
+            ptx::tmem_ld_32x32(taddr + j * BN + c, w);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(w[i]));
+          }
+        }
         uint32_t out[16];
         if (EPI == kEpiSiluMul) {
           uint32_t u[32];
           ptx::tmem_ld_32x32(taddr + BN / 2 + c, u);
           ptx::tmem_ld_wait();
+          if (Cfg::kSplit > 1) {
+#pragma unroll
+            for (int j = 1; j < Cfg::kSplit; ++j) {
+              uint32_t w[32];
+              ptx::tmem_ld_32x32(taddr + j * BN + BN / 2 + c, w);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) u[i] = __float_as_uint(__uint_as_float(u[i]) + __uint_as_float(w[i]));
+            }
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             float g0 = __uint_as_float(v[2 * i]), g1 = __uint_as_float(v[2 * i + 1]);

@@ -340,6 +340,7 @@ class Controller {
     bool busy = false;        // an inference RPC is in flight
     bool migrating = false;   // this source has a migration in flight
     bool relay_wait = false;  // OldPrefill parked in the relay queue
+    bool last_was_decode = false;
     std::deque<ResidentBatch> pending_migration;
     std::vector<ResidentBatch> decode_batches;
     std::vector<ResidentBatch> inflight_zag;
@@ -490,9 +491,16 @@ class Controller {
       case RState::Prefill:
       case RState::ShuttingPrefill:
       case RState::MutatingToDecode:
-        if (rep.colocated && try_decode(r)) return;
-        if (rep.m.state == RState::Prefill) try_prefill(r, now);
-        if (rep.m.state == RState::ShuttingPrefill && !rep.busy && rep.pending_migration.empty() && !rep.migrating)
+        // A replica that also holds decode batches (colocated deployment, or no decode side exists)
+        // alternates: a waiting prompt goes first after a decode step, otherwise it keeps decoding.
+        if (!rep.busy && !rep.decode_batches.empty()) {
+          const bool prefill_first = rep.m.state == RState::Prefill && rep.last_was_decode && !queue_.empty();
+          if (prefill_first && try_prefill(r, now)) { rep.last_was_decode = false; return; }
+          if (try_decode(r)) { rep.last_was_decode = true; return; }
+        }
+        if (rep.m.state == RState::Prefill && try_prefill(r, now)) rep.last_was_decode = false;
+        if (rep.m.state == RState::ShuttingPrefill && !rep.busy && rep.pending_migration.empty() && !rep.migrating &&
+            rep.decode_batches.empty())
           park(r, now);
         if (rep.m.state == RState::MutatingToDecode && !rep.busy && !rep.migrating) {
           // flush the batches awaiting migration into itself, then serve as a decode replica

@@ -1,0 +1,262 @@
+"""Router runtime: the asyncio shell around the native orchestrator core.
+
+The core (`blitz_core.Controller`) decides; this module performs the IO: it turns each `Action` into
+the matching RPCs on every tensor-parallel rank of the replica (the reference's `join_all` over
+stubs, router_v2/src/replica/disaggregation.rs:944-963), reports completions back, and streams
+tokens to the per-request queues the HTTP layer reads.  A failed RPC is reported as a lost replica
+(the reference `unwrap()`s the result and dies, disaggregation.rs:960-963).  Transition and metric
+log lines keep the reference's grep-able formats (`Replica<i> A => B`,
+`System Metrics: prefill_tokens: .., decode_tokens: ..`, scripts/batch/utils.py:391-424).
+"""
+from __future__ import annotations
+
+import asyncio
+import logging
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+from ..pb.schema import pb
+from ..runtime import core
+from .stub import WorkerStub, encode_prefill_case
+
+log = logging.getLogger("blitz.router")
+A = core.ActionType
+
+
+@dataclass
+class LiveRequest:
+    id: int
+    proto: object                      # pb.Request
+    queue: asyncio.Queue = field(default_factory=asyncio.Queue)
+    t_submit: float = 0.0
+    tokens: List[int] = field(default_factory=list)
+    texts: List[str] = field(default_factory=list)
+
+
+class RouterRuntime:
+    def __init__(self, cfg: "core.ControllerConfig", worker_urls: List[str], model_layers: int = 32,
+                 model_path: str = ""):
+        self.cfg = cfg
+        self.ctl = core.Controller(cfg)
+        self.stubs = [WorkerStub(u) for u in worker_urls]
+        self.tp = cfg.tp
+        self.layers = model_layers
+        self.model_path = model_path
+        self.requests: Dict[int, LiveRequest] = {}
+        self.cached: Dict[tuple, object] = {}        # (replica, batch_id) -> pb.CachedBatch
+        self.first_tokens: Dict[int, Dict[int, int]] = {}  # batch_id -> {request_id: first token} until first decode
+        self.wake = asyncio.Event()
+        self.stopped = False
+        self.t0 = time.monotonic()
+        self._next_id = 0
+        self._tasks: set = set()
+        self.transitions: List[tuple] = []
+        self._zag_pp: Dict[int, int] = {}            # batch_id -> layer at which a relayed batch was handed over
+
+    # ------------------------------------------------------------------ submission
+    def now(self) -> float:
+        return time.monotonic() - self.t0
+
+    def submit(self, input_tokens: List[int], max_new_tokens: int, *, inputs: str = "", parameters=None,
+               ignore_eos: bool = True) -> LiveRequest:
+        rid = self._next_id
+        self._next_id += 1
+        r = pb.Request(id=rid, inputs=inputs, prefill_logprobs=False, top_n_tokens=0)
+        r.input_tokens.extend(input_tokens)
+        r.stopping_parameters.max_new_tokens = max_new_tokens
+        r.stopping_parameters.ignore_eos_token = ignore_eos
+        if parameters is not None:
+            r.parameters.CopyFrom(parameters)
+        lr = LiveRequest(rid, r, t_submit=self.now())
+        self.requests[rid] = lr
+        self.ctl.submit(core.RequestEntry(rid, len(input_tokens), max_new_tokens, lr.t_submit))
+        self.wake.set()
+        return lr
+
+    def client_gone(self, rid: int) -> None:
+        self.ctl.client_gone(rid)
+
+    # ------------------------------------------------------------------ main loop
+    async def run(self) -> None:
+        last_metrics = 0.0
+        while not self.stopped:
+            now = self.now()
+            actions = self.ctl.step(now)
+            for line in self.ctl.drain_log():
+                log.info(line)
+                if " => " in line:
+                    self.transitions.append((now, line))
+            for a in actions:
+                self._dispatch(a)
+            if now - last_metrics >= 1.0:
+                last_metrics = now
+                log.info(self.ctl.system_metrics_line())
+            if not actions:
+                self.wake.clear()
+                try:
+                    await asyncio.wait_for(self.wake.wait(), timeout=0.002)
+                except asyncio.TimeoutError:
+                    pass
+            else:
+                await asyncio.sleep(0)
+
+    async def stop(self) -> None:
+        self.stopped = True
+        self.wake.set()
+        for t in list(self._tasks):
+            t.cancel()
+        for s in self.stubs:
+            await s.close()
+
+    def _spawn(self, coro) -> None:
+        t = asyncio.get_running_loop().create_task(coro)
+        self._tasks.add(t)
+        t.add_done_callback(self._tasks.discard)
+
+    def _ranks(self, replica: int) -> List[int]:
+        return [replica * self.tp + i for i in range(self.tp)]
+
+    def _batch_proto(self, a) -> object:
+        b = pb.Batch(id=a.batch_id, size=len(a.request_ids), max_tokens=a.max_tokens)
+        for rid in a.request_ids:
+            lr = self.requests.get(rid)
+            if lr is not None:
+                b.requests.append(lr.proto)
+        return b
+
+    def _dispatch(self, a) -> None:
+        t = a.type
+        if t == A.Deliver or t == A.Fail:
+            lr = self.requests.get(a.request_id)
+            if lr is not None:
+                if t == A.Fail:
+                    lr.queue.put_nowait(("error", "replica lost"))
+                    self.requests.pop(a.request_id, None)
+                else:
+                    lr.tokens.append(a.token)
+                    lr.queue.put_nowait(("token", a.token, a.final))
+                    if a.final:
+                        self.requests.pop(a.request_id, None)
+            return
+        handler = {A.Prefill: self._do_prefill, A.ZagPrefill: self._do_prefill, A.PrefillPP: self._do_prefill,
+                   A.Decode: self._do_decode, A.Migrate: self._do_migrate, A.MigratePartial: self._do_migrate,
+                   A.Relay: self._do_relay, A.NvlBroadcast: self._do_params, A.TanzBroadcast: self._do_params,
+                   A.RdmaBroadcast: self._do_params, A.LoadParams: self._do_params, A.ResetStatus: self._do_simple,
+                   A.SetStatusReady: self._do_simple, A.ClearCache: self._do_simple}[t]
+        self._spawn(self._guard(a, handler))
+
+    async def _guard(self, a, handler) -> None:
+        try:
+            await handler(a)
+        except asyncio.CancelledError:
+            raise
+        except Exception as e:  # noqa: BLE001  an RPC failed: the replica is gone
+            log.error("RPC for %s on replica %d failed: %s", a.type.name, a.replica, e)
+            if a.op_id:
+                self.ctl.on_failure(a.op_id, self.now())
+        self.wake.set()
+
+    # ------------------------------------------------------------------ handlers
+    @staticmethod
+    def _tokens_out(generations) -> list:
+        out = []
+        for g in generations:
+            fin = g.HasField("generated_text")
+            out.append(core.TokenOut(g.request_id, int(g.tokens.ids[0]) if g.tokens.ids else -1, fin))
+        return out
+
+    async def _do_prefill(self, a) -> None:
+        batch = self._batch_proto(a)
+        ranks = self._ranks(a.replica)
+        if a.type == A.Prefill:
+            calls = [self.stubs[r].prefill_v2(batch, pb.PREFILL_CASE_NORMAL) for r in ranks]
+        elif a.type == A.ZagPrefill:
+            calls = [self.stubs[r].zag_prefill(batch, a.zag_seq, self.layers, pb.PREFILL_CASE_NAIVE_PP) for r in ranks]
+        else:
+            pp = pb.PipeParaInfo()
+            if a.num_layer <= 0:
+                pp.embedding_layer = 1
+            else:
+                pp.tfm_layer = a.num_layer
+            case = encode_prefill_case(pb.PREFILL_CASE_NAIVE_PP, pb.PREFILL_CASE_IMMIGRATE)
+            calls = [self.stubs[r].prefill_v2(batch, case, pp, a.dst_ranks) for r in ranks]
+        res = (await asyncio.gather(*calls))[0]
+        if a.type == A.ZagPrefill and not res.generations and res.HasField("pp_info"):
+            # taken over by a relay: the relay completion reports the hand-over to the core
+            which = res.pp_info.WhichOneof("start_layer")
+            self._zag_pp[a.batch_id] = res.pp_info.tfm_layer if which == "tfm_layer" else 0
+            return
+        if res.HasField("batch"):
+            self.cached[(a.replica, a.batch_id)] = res.batch
+        toks = self._tokens_out(res.generations)
+        self.first_tokens[a.batch_id] = {g.request_id: int(g.tokens.ids[0]) for g in res.generations if g.tokens.ids}
+        self.ctl.on_prefill_done(a.op_id, toks, self.now())
+
+    async def _do_decode(self, a) -> None:
+        batches, lasts = [], []
+        for bid in a.batch_ids:
+            cb = self.cached.get((a.replica, bid))
+            if cb is None:
+                continue
+            batches.append(cb)
+            t = pb.Tokens()
+            ft = self.first_tokens.pop(bid, None)
+            if ft is not None:  # first decode step of this batch here: hand over the tokens prefill produced
+                t.ids.extend(ft.get(rid, 0) for rid in cb.request_ids)
+            lasts.append(t)
+        ranks = self._ranks(a.replica)
+        res = (await asyncio.gather(*[self.stubs[r].decode_v2(batches, lasts) for r in ranks]))[0]
+        for bid in a.batch_ids:
+            self.cached.pop((a.replica, bid), None)
+        if res.HasField("batch"):
+            self.cached[(a.replica, res.batch.id)] = res.batch
+        self.ctl.on_decode_done(a.op_id, self._tokens_out(res.generations), self.now())
+
+    async def _do_migrate(self, a) -> None:
+        batch = self._batch_proto(a)
+        partial = a.partial if a.type == A.MigratePartial else 0
+        src, dst = list(a.src_ranks), list(a.dst_ranks)
+        calls = [self.stubs[r].migrate(batch, src, dst, partial, a.num_layer) for r in src] + \
+                [self.stubs[r].immigrate(batch, src, dst, partial, a.num_layer) for r in dst]
+        res = await asyncio.gather(*calls)
+        self.cached.pop((a.replica, a.batch_id), None)
+        self.cached[(a.peer, a.batch_id)] = res[-1].batch
+        self.ctl.on_migrate_done(a.op_id, self.now())
+
+    async def _do_relay(self, a) -> None:
+        new_ranks = self._ranks(a.replica)
+        res = (await asyncio.gather(*[self.stubs[r].relay(a.src_ranks[0], a.final) for r in new_ranks]))[0]
+        has = res.HasField("batch_id")
+        next_layer = 0
+        if has:
+            # the hand-over layer travels in the ZagPrefill response of that batch (bounded wait for it)
+            for _ in range(4000):
+                if res.batch_id in self._zag_pp:
+                    next_layer = self._zag_pp.pop(res.batch_id)
+                    break
+                await asyncio.sleep(0.0005)
+        self.ctl.on_relay_done(a.op_id, has, res.batch_id if has else 0, next_layer, self.now())
+
+    async def _do_params(self, a) -> None:
+        if a.mock:
+            await asyncio.sleep(self.cfg.mock_load_ms * 1e-3)
+            await asyncio.gather(*[self.stubs[r].set_status_ready() for r in a.dst_ranks])
+        elif a.type == A.LoadParams:
+            await asyncio.gather(*[self.stubs[r].load_params(a.load_case, self.cfg.model_name, self.model_path)
+                                   for r in a.dst_ranks])
+        else:
+            kind = {A.NvlBroadcast: "nvl", A.TanzBroadcast: "tanz", A.RdmaBroadcast: "rdma"}[a.type]
+            # every participant receives the same request and derives its role (src/service/service.cc:1341-1347)
+            ranks = list(a.src_ranks) + list(a.dst_ranks)
+            await asyncio.gather(*[self.stubs[r].broadcast(kind, a.src_ranks, a.dst_ranks) for r in ranks])
+        self.ctl.on_params_done(a.op_id, self.now())
+
+    async def _do_simple(self, a) -> None:
+        if a.type == A.ClearCache:
+            self.cached.pop((a.replica, a.batch_id), None)
+            await asyncio.gather(*[self.stubs[r].clear_cache(a.batch_id) for r in self._ranks(a.replica)])
+        elif a.type == A.ResetStatus:
+            await asyncio.gather(*[self.stubs[r].reset_status() for r in a.dst_ranks])
+        elif a.type == A.SetStatusReady:
+            await asyncio.gather(*[self.stubs[r].set_status_ready() for r in a.dst_ranks])

@@ -1,0 +1,347 @@
+"""HTTP front of the router (TGI-compatible surface of router_v2/src/server.rs:892-947).
+
+Routes: POST `/`, `/generate`, `/invocations` (JSON in, JSON out, timing headers), POST `/generate_stream`
+(server-sent events), GET `/info`, `/health`, `/ping`, `/metrics` (Prometheus text), `/docs` (OpenAPI
+summary), POST `/modify_cluster_state` (manual scaling, `manually_scale` feature only).  The timing
+headers are the ones the trace client consumes (router_v2/src/server.rs:252-349): x-first-token-time,
+x-queue-time, x-inference-time, x-{max,avg,p90,p95,p99}-time-between-tokens, x-first-decode-token-time,
+x-input-length, x-output-length, ...; TTFT is measured to the prefill-done event and the first
+inter-token interval is excluded from the TBT statistics (router_v2/src/infer.rs:324-333).
+
+Tokenization: without a tokenizer file the router uses a deterministic word-hash tokenizer (one id
+per whitespace-separated word), enough for trace replay; `input_tokens` may also be posted directly.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import logging
+import time
+import zlib
+from typing import List, Optional
+
+from aiohttp import web
+
+from ..runtime import core
+from .runtime import RouterRuntime
+
+log = logging.getLogger("blitz.router.http")
+
+
+class WordHashTokenizer:
+    def __init__(self, vocab: int = 32000):
+        self.vocab = vocab
+
+    def encode(self, text: str) -> List[int]:
+        return [zlib.crc32(w.encode()) % self.vocab for w in text.split()]
+
+    def decode(self, ids: List[int]) -> str:
+        return " ".join(f"<{i}>" for i in ids)
+
+
+def _pct(xs: List[float], q: float) -> float:
+    if not xs:
+        return 0.0
+    s = sorted(xs)
+    return s[min(len(s) - 1, int(q * len(s)))]
+
+
+class Metrics:
+    """Prometheus exposition with the reference's metric names (router_v2/src/server.rs:811-857)."""
+    BUCKETS = [0.005, 0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10, 30]
+
+    def __init__(self):
+        self.counters = {"blitz_request_count": 0, "blitz_request_success": 0, "blitz_request_failure": 0}
+        self.hist = {n: [] for n in ("blitz_request_duration", "blitz_request_validation_duration",
+                                     "blitz_request_queue_duration", "blitz_request_inference_duration",
+                                     "blitz_request_mean_time_per_token_duration", "blitz_request_generated_tokens",
+                                     "blitz_request_input_length", "blitz_request_max_new_tokens",
+                                     "blitz_batch_next_size")}
+
+    def observe(self, name: str, v: float) -> None:
+        self.hist[name].append(v)
+
+    def render(self, rt: RouterRuntime) -> str:
+        out = []
+        ctl = rt.ctl
+        merged = dict(self.counters)
+        for k, v in ctl.counters().items():
+            merged[k] = merged.get(k, 0) + v if k not in ("blitz_request_count",) else v
+        for k, v in sorted(merged.items()):
+            out += [f"# TYPE {k} counter", f"{k} {v}"]
+        gauges = dict(ctl.gauges())
+        gauges["blitz_queue_size"] = ctl.queue_size
+        for k, v in sorted(gauges.items()):
+            out += [f"# TYPE {k} gauge", f"{k} {v}"]
+        for name, xs in sorted(self.hist.items()):
+            out.append(f"# TYPE {name} histogram")
+            for b in self.BUCKETS:
+                out.append(f'{name}_bucket{{le="{b}"}} {sum(1 for x in xs if x <= b)}')
+            out.append(f'{name}_bucket{{le="+Inf"}} {len(xs)}')
+            out.append(f"{name}_sum {sum(xs)}")
+            out.append(f"{name}_count {len(xs)}")
+        return "\n".join(out) + "\n"
+
+
+class RouterApp:
+    def __init__(self, rt: RouterRuntime, *, model_name: str = "llama3_8b", max_input_length: int = 4095,
+                 max_total_tokens: int = 4096, max_concurrent: int = 4096, vocab: int = 32000):
+        self.rt = rt
+        self.tok = WordHashTokenizer(vocab)
+        self.limits = core.ValidationLimits()
+        self.limits.max_input_length, self.limits.max_total_tokens = max_input_length, max_total_tokens
+        self.model_name = model_name
+        self.sem = asyncio.Semaphore(max_concurrent)
+        self.metrics = Metrics()
+        self.app = web.Application(client_max_size=64 << 20)
+        r = self.app.router
+        for path in ("/", "/generate", "/invocations"):
+            r.add_post(path, self.generate)
+        r.add_post("/generate_stream", self.generate_stream)
+        r.add_get("/info", self.info)
+        r.add_get("/health", self.health)
+        r.add_get("/ping", self.health)
+        r.add_get("/metrics", self.prom)
+        r.add_get("/docs", self.docs)
+        r.add_post("/modify_cluster_state", self.modify_cluster_state)
+
+    # ------------------------------------------------------------------ request parsing
+    def _parse(self, body: dict):
+        p = body.get("parameters") or {}
+        if "input_tokens" in body:
+            toks = [int(t) for t in body["input_tokens"]]
+        else:
+            toks = self.tok.encode(body.get("inputs", ""))
+        g = core.GenerateParams()
+        g.input_len = len(toks)
+        g.max_new_tokens = int(p.get("max_new_tokens", 20))
+        g.best_of = int(p.get("best_of") or 1)
+        g.do_sample = bool(p.get("do_sample", False))
+        g.temperature = float(p.get("temperature") or 1.0)
+        g.repetition_penalty = float(p.get("repetition_penalty") or 1.0)
+        g.top_p = float(p.get("top_p") or 1.0)
+        g.typical_p = float(p.get("typical_p") or 1.0)
+        g.top_k = int(p.get("top_k") or 0)
+        g.top_n_tokens = int(p.get("top_n_tokens") or 0)
+        g.num_stop_sequences = len(p.get("stop") or [])
+        if p.get("truncate"):
+            g.truncate = int(p["truncate"])
+            toks = toks[-int(p["truncate"]):]
+        g.has_seed = p.get("seed") is not None
+        err = core.validate_request(g, self.limits)
+        return toks, g, err
+
+    async def _run(self, toks, g):
+        t_start = time.monotonic()
+        lr = self.rt.submit(toks, g.max_new_tokens)
+        out, t_first, t_first_dec, t_prev, tbt = [], None, None, None, []
+        while True:
+            ev = await lr.queue.get()
+            now = time.monotonic()
+            if ev[0] == "error":
+                raise web.HTTPServiceUnavailable(text=json.dumps({"error": ev[1], "error_type": "generation"}),
+                                                 content_type="application/json")
+            _, tok, final = ev
+            if t_first is None:
+                t_first = now
+            else:
+                if t_first_dec is None:
+                    t_first_dec = now
+                else:
+                    tbt.append(now - t_prev)
+            t_prev = now
+            out.append(tok)
+            yield tok, final, None
+            if final:
+                break
+        e = self.rt.ctl.finished().get(lr.id)
+        queue_s = (e.t_batched - e.t_arrival) if e is not None and e.t_batched >= 0 else 0.0
+        total = time.monotonic() - t_start
+        stats = {
+            "x-compute-type": "gpu+optimized", "x-total-time": int(total * 1e3), "x-validation-time": 0,
+            "x-queue-time": int(queue_s * 1e3), "x-inference-time": int((total - queue_s) * 1e3),
+            "x-first-token-time": int((t_first - t_start) * 1e3),
+            "x-first-decode-token-time": int(((t_first_dec or t_first) - t_start) * 1e3),
+            "x-time-per-token": int(total * 1e3 / max(1, len(out))),
+            "x-max-time-between-tokens": int(max(tbt, default=0.0) * 1e3),
+            "x-avg-time-between-tokens": int((sum(tbt) / len(tbt) if tbt else 0.0) * 1e3),
+            "x-p90-time-between-tokens": int(_pct(tbt, 0.90) * 1e3), "x-p95-time-between-tokens": int(_pct(tbt, 0.95) * 1e3),
+            "x-p99-time-between-tokens": int(_pct(tbt, 0.99) * 1e3),
+            "x-input-length": len(toks), "x-output-length": len(out), "x-generated-tokens": len(out),
+        }
+        m = self.metrics
+        m.observe("blitz_request_duration", total)
+        m.observe("blitz_request_queue_duration", queue_s)
+        m.observe("blitz_request_inference_duration", total - queue_s)
+        m.observe("blitz_request_mean_time_per_token_duration", total / max(1, len(out)))
+        m.observe("blitz_request_generated_tokens", len(out))
+        m.observe("blitz_request_input_length", len(toks))
+        m.observe("blitz_request_max_new_tokens", g.max_new_tokens)
+        yield None, True, (out, stats)
+
+    # ------------------------------------------------------------------ handlers
+    async def generate(self, req: web.Request) -> web.Response:
+        try:
+            body = await req.json()
+        except Exception:  # noqa: BLE001
+            return web.json_response({"error": "invalid JSON", "error_type": "validation"}, status=422)
+        toks, g, err = self._parse(body)
+        if err:
+            self.metrics.counters["blitz_request_failure"] += 1
+            return web.json_response({"error": err, "error_type": "validation"}, status=422)
+        if self.sem.locked():
+            return web.json_response({"error": "Model is overloaded", "error_type": "overloaded"}, status=429)
+        async with self.sem:
+            result = None
+            async for tok, final, done in self._run(toks, g):
+                if done is not None:
+                    result = done
+            out, stats = result
+        details = None
+        if (body.get("parameters") or {}).get("details"):
+            details = {"finish_reason": "length", "generated_tokens": len(out),
+                       "tokens": [{"id": t, "text": f"<{t}>", "logprob": 0.0, "special": False} for t in out]}
+        return web.json_response({"generated_text": self.tok.decode(out), "details": details},
+                                 headers={k: str(v) for k, v in stats.items()})
+
+    async def generate_stream(self, req: web.Request) -> web.StreamResponse:
+        body = await req.json()
+        toks, g, err = self._parse(body)
+        if err:
+            return web.json_response({"error": err, "error_type": "validation"}, status=422)
+        resp = web.StreamResponse(headers={"Content-Type": "text/event-stream", "Cache-Control": "no-cache"})
+        await resp.prepare(req)
+        n = 0
+        try:
+            async for tok, final, done in self._run(toks, g):
+                if done is not None:
+                    out, _ = done
+                    continue
+                n += 1
+                ev = {"token": {"id": tok, "text": f"<{tok}>", "logprob": 0.0, "special": False},
+                      "generated_text": None, "details": None}
+                if final:
+                    ev["details"] = {"finish_reason": "length", "generated_tokens": n}
+                await resp.write(f"data:{json.dumps(ev)}\n\n".encode())
+        except (ConnectionResetError, asyncio.CancelledError):
+            pass  # client went away; the queue entry is dropped by the core when it is still waiting
+        await resp.write_eof()
+        return resp
+
+    async def info(self, req):
+        return web.json_response({"model_id": self.model_name, "max_input_length": self.limits.max_input_length,
+                                  "max_total_tokens": self.limits.max_total_tokens, "version": "0.1.0",
+                                  "replicas": [self.rt.ctl.state_name(i) for i in range(self.rt.ctl.num_replicas)]})
+
+    async def health(self, req):
+        try:
+            await asyncio.gather(*[s.health() for s in self.rt.stubs])
+            return web.Response(text="ok")
+        except Exception as e:  # noqa: BLE001
+            return web.json_response({"error": f"unhealthy: {e}", "error_type": "healthcheck"}, status=503)
+
+    async def prom(self, req):
+        return web.Response(text=self.metrics.render(self.rt), content_type="text/plain")
+
+    async def docs(self, req):
+        paths = {p: {"post": {}} for p in ("/", "/generate", "/generate_stream", "/invocations", "/modify_cluster_state")}
+        paths.update({p: {"get": {}} for p in ("/info", "/health", "/ping", "/metrics")})
+        return web.json_response({"openapi": "3.0.3", "info": {"title": "blitz_scale_b200 router", "version": "0.1.0"},
+                                  "paths": paths})
+
+    async def modify_cluster_state(self, req):
+        if not self.rt.ctl.has_feature("manually_scale"):
+            return web.json_response({"error": "manually_scale is not enabled"}, status=403)
+        body = await req.json()
+        ok = self.rt.ctl.manual_scale(int(body["replica"]), str(body["state"]), self.rt.now())
+        self.rt.wake.set()
+        return web.json_response({"ok": bool(ok)}, status=200 if ok else 409)
+
+
+def controller_config_from_cluster(cluster: dict, tp: int, features: str, **overrides) -> "core.ControllerConfig":
+    """Cluster JSON {init_states, replicas, machines} -> controller config (src/server/disaggregate.cc:31-50)."""
+    cfg = core.ControllerConfig()
+    cfg.init_states = list(cluster["init_states"])
+    cfg.num_ranks = len(cfg.init_states)
+    cfg.tp = tp
+    cfg.machines = list(cluster.get("machines") or [0] * cfg.num_ranks)
+    cfg.features = features
+    planner = cfg.planner
+    for k, v in overrides.items():
+        if hasattr(cfg, k):
+            setattr(cfg, k, v)
+        elif hasattr(planner, k):
+            setattr(planner, k, v)
+    cfg.planner = planner
+    return cfg
+
+
+async def serve_router(rt: RouterRuntime, host: str, port: int, stop: Optional[asyncio.Event] = None, **kw) -> None:
+    app = RouterApp(rt, **kw)
+    runner = web.AppRunner(app.app, access_log=None)
+    await runner.setup()
+    site = web.TCPSite(runner, host, port)
+    await site.start()
+    loop_task = asyncio.get_running_loop().create_task(rt.run())
+    print(f"Router listening on {host}:{port}", flush=True)
+    try:
+        if stop is not None:
+            await stop.wait()
+        else:
+            await asyncio.Event().wait()
+    finally:
+        await rt.stop()
+        loop_task.cancel()
+        await runner.cleanup()
+
+
+def main(argv=None) -> None:
+    """CLI of the router binary (the subset of router_v2/src/main.rs:40-155 that applies to one NVSwitch box)."""
+    ap = argparse.ArgumentParser("blitz-router")
+    ap.add_argument("--hostname", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=3000)
+    ap.add_argument("--client-config", required=True, help="JSON list of worker URLs (host:port), rank order")
+    ap.add_argument("--deployment-config-path", required=True, help="cluster JSON {init_states, replicas, machines}")
+    ap.add_argument("--features", default="impl_blitz,impl_fast_pro,impl_live_pro")
+    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--model-name", default="llama3_8b")
+    ap.add_argument("--model-path", default="")
+    ap.add_argument("--max-input-length", type=int, default=4095)
+    ap.add_argument("--max-total-tokens", type=int, default=4096)
+    ap.add_argument("--max-batch-prefill-tokens", type=int, default=8192)
+    ap.add_argument("--max-blocks-per-replica", type=int, default=30000)
+    ap.add_argument("--tokens-prefilled-per-sec", type=int, default=15000)
+    ap.add_argument("--tokens-transferred-per-sec", type=int, default=96000)
+    for n, d in (("prefill-lower-bound", .5), ("prefill-upper-bound", .7), ("decode-lower-bound", .75),
+                 ("decode-upper-bound", .95), ("migration-lower-bound", .4), ("migration-upper-bound", .8)):
+        ap.add_argument("--" + n, type=float, default=d)
+    for n in ("min-prefill-num", "min-decode-num"):
+        ap.add_argument("--" + n, type=int, default=1)
+    for n in ("max-prefill-num", "max-decode-num"):
+        ap.add_argument("--" + n, type=int, default=8)
+    ap.add_argument("--scale-down-threshold-millis", type=float, default=333)
+    ap.add_argument("--mock-load-millis", type=float, default=0)
+    ap.add_argument("--log-level", default="INFO")
+    a = ap.parse_args(argv)
+    logging.basicConfig(level=a.log_level, format="%(asctime)s %(name)s %(message)s")
+    from ..models.config import get_config
+    cluster = json.load(open(a.deployment_config_path))
+    urls = json.loads(a.client_config) if a.client_config.strip().startswith("[") else json.load(open(a.client_config))
+    cfg = controller_config_from_cluster(
+        cluster, a.tensor_parallel_size, a.features, model_name=a.model_name,
+        max_prefill_tokens=a.max_batch_prefill_tokens, max_total_tokens=max(a.max_total_tokens, 16000),
+        max_blocks_per_replica=a.max_blocks_per_replica, mock_load_ms=a.mock_load_millis,
+        tokens_prefilled_per_sec=a.tokens_prefilled_per_sec, tokens_transferred_per_sec=a.tokens_transferred_per_sec,
+        prefill_lower=a.prefill_lower_bound, prefill_upper=a.prefill_upper_bound, decode_lower=a.decode_lower_bound,
+        decode_upper=a.decode_upper_bound, migration_lower=a.migration_lower_bound,
+        migration_upper=a.migration_upper_bound, min_prefill=a.min_prefill_num, max_prefill=a.max_prefill_num,
+        min_decode=a.min_decode_num, max_decode=a.max_decode_num, scale_down_threshold_ms=a.scale_down_threshold_millis)
+    layers = get_config(a.model_name).layers
+    rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path)
+    asyncio.run(serve_router(rt, a.hostname, a.port, model_name=a.model_name, max_input_length=a.max_input_length,
+                             max_total_tokens=a.max_total_tokens))
+
+
+if __name__ == "__main__":
+    main()

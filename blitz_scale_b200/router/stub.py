@@ -1,0 +1,114 @@
+"""Async gRPC client of one worker: one coroutine per RPC of the contract
+(the role of router_v2/src/stub.rs:34-487).  Requests and responses are the runtime-built
+protobuf classes; no generated code is involved."""
+from __future__ import annotations
+
+from typing import Iterable, Optional, Sequence
+
+import grpc
+
+from ..pb.schema import RPCS, method_path, pb
+
+
+def encode_prefill_case(*cases: int) -> int:
+    """Bit-or of PrefillCase values (router_v2/src/stub.rs:20-30)."""
+    v = 0
+    for c in cases:
+        v |= int(c)
+    return v
+
+
+class WorkerStub:
+    def __init__(self, url: str):
+        self.url = url
+        self.channel = grpc.aio.insecure_channel(url, options=[("grpc.max_receive_message_length", 256 << 20),
+                                                               ("grpc.max_send_message_length", 256 << 20)])
+        self._m = {}
+        for rpc, (req, res) in RPCS.items():
+            self._m[rpc] = self.channel.unary_unary(method_path(rpc),
+                                                    request_serializer=getattr(pb, req).SerializeToString,
+                                                    response_deserializer=getattr(pb, res).FromString)
+
+    async def call(self, rpc: str, request, timeout: Optional[float] = None, metadata=None):
+        return await self._m[rpc](request, timeout=timeout, metadata=metadata)
+
+    async def close(self):
+        await self.channel.close()
+
+    # ---- convenience wrappers
+    async def health(self, timeout=2.0):
+        return await self.call("Health", pb.HealthRequest(), timeout)
+
+    async def info(self):
+        return await self.call("Info", pb.InfoRequest())
+
+    async def clear_cache(self, batch_id: Optional[int] = None):
+        r = pb.ClearCacheRequest()
+        if batch_id is not None:
+            r.id = batch_id
+        return await self.call("ClearCache", r)
+
+    async def filter_batch(self, batch_id: int, request_ids: Iterable[int]):
+        return await self.call("FilterBatch", pb.FilterBatchRequest(batch_id=batch_id, request_ids=list(request_ids)))
+
+    async def warmup(self, max_input_length=2048, max_prefill_tokens=4096, max_total_tokens=4096):
+        return await self.call("Warmup", pb.WarmupRequest(max_input_length=max_input_length,
+                                                          max_prefill_tokens=max_prefill_tokens,
+                                                          max_total_tokens=max_total_tokens))
+
+    async def prefill_v2(self, batch, forward_case: int = 0, pp_info=None, pipe_peer: Sequence[int] = ()):
+        r = pb.PrefillV2Request(batch=batch, forward_case=forward_case, pipe_peer=list(pipe_peer))
+        if pp_info is not None:
+            r.pp_info.CopyFrom(pp_info)
+        return await self.call("PrefillV2", r)
+
+    async def zag_prefill(self, batch, zag_seq_num: int, zag_layers: int, forward_case: int = 4, pp_info=None):
+        r = pb.ZagPrefillRequest(batch=batch, forward_case=forward_case, zag_layers=zag_layers, zag_seq_num=zag_seq_num)
+        if pp_info is None:
+            r.pp_info.embedding_layer = 1
+        else:
+            r.pp_info.CopyFrom(pp_info)
+        return await self.call("ZagPrefill", r)
+
+    async def decode_v2(self, batches, last_iter_tokens):
+        return await self.call("DecodeV2", pb.DecodeV2Request(batches=list(batches), last_iter_tokens=list(last_iter_tokens)))
+
+    async def relay(self, rank: int, relax_not_head: bool):
+        return await self.call("Relay", pb.RelayRequest(rank=rank, relax_not_head=relax_not_head))
+
+    async def migrate(self, batch, src, dst, partial: int = 0, num_layer: int = 0):
+        if partial:
+            return await self.call("MigratePartial", pb.MigratePartialRequest(batch=batch, fst_or_snd=partial,
+                                                                              num_layer=num_layer, src=src, dst=dst))
+        return await self.call("Migrate", pb.MigrateRequest(batch=batch, src=src, dst=dst))
+
+    async def immigrate(self, batch, src, dst, partial: int = 0, num_layer: int = 0):
+        if partial:
+            return await self.call("ImmigratePartial", pb.ImmigratePartialRequest(batch=batch, fst_or_snd=partial,
+                                                                                  num_layer=num_layer, src=src, dst=dst))
+        return await self.call("Immigrate", pb.ImmigrateRequest(batch=batch, src=src, dst=dst))
+
+    async def broadcast(self, kind: str, src_ranks, dst_ranks):
+        rpc = {"nvl": "NvlBroadcast", "rdma": "RdmaBroadcast", "tanz": "TanzBroadcast"}[kind]
+        return await self.call(rpc, pb.BroadcastRequest(src_ranks=list(src_ranks), dst_ranks=list(dst_ranks)))
+
+    async def load_params(self, load_case: int, model_name: str, model_path: str = ""):
+        r = pb.LoadParamsRequest(load_case=load_case, model_name=model_name)
+        if model_path:
+            r.model_path = model_path
+        return await self.call("LoadParams", r)
+
+    async def send_params(self, dst: int):
+        return await self.call("SendParams", pb.SendParamsRequest(dst=dst))
+
+    async def recv_params(self, src: int):
+        return await self.call("RecvParams", pb.RecvParamsRequest(src=src))
+
+    async def wait_rdma_done(self):
+        return await self.call("WaitRdmaDone", pb.WaitRdmaDoneRequest())
+
+    async def reset_status(self):
+        return await self.call("ResetStatus", pb.ResetStatusRequest())
+
+    async def set_status_ready(self):
+        return await self.call("SetStatusReady", pb.SetStatusReadyRequest())

@@ -1,0 +1,200 @@
+"""CPU plumbing end to end: router (HTTP + native core) + trace client + two GPU-less workers over real gRPC.
+
+A scaled-down version of the first benchmark configuration: Poisson arrivals with uniform input/output lengths,
+one serving instance, a second one scaled out during the run.  Checks: every request completes with the
+right number of tokens, token streams are identical across two runs with the same seeds, the scale-out is
+visible in the transition log, /metrics and the timing headers are present, a worker that dies is detected.
+"""
+import asyncio
+import json
+import socket
+
+import pytest
+
+from blitz_scale_b200.pb.schema import RPCS, pb, render_proto
+from blitz_scale_b200.router.runtime import RouterRuntime
+from blitz_scale_b200.router.server import RouterApp, controller_config_from_cluster, serve_router
+from blitz_scale_b200.router.stub import WorkerStub
+from blitz_scale_b200.sim import request_sim
+from blitz_scale_b200.sim.stub_worker import StubBackend
+from blitz_scale_b200.worker.service import serve
+
+
+def _free_ports(n):
+    socks = [socket.socket() for _ in range(n)]
+    for s in socks:
+        s.bind(("127.0.0.1", 0))
+    ports = [s.getsockname()[1] for s in socks]
+    for s in socks:
+        s.close()
+    return ports
+
+
+def test_proto_contract_roundtrip():
+    assert len(RPCS) == 25
+    for rpc, (req, res) in RPCS.items():
+        for name in (req, res):
+            cls = getattr(pb, name)
+            m = cls()
+            # fill required scalar fields so serialisation is legal, then round-trip
+            for f in cls.DESCRIPTOR.fields:
+                if f.label == f.LABEL_REQUIRED and f.message_type is None:
+                    setattr(m, f.name, {f.TYPE_STRING: "x", f.TYPE_BOOL: True}.get(f.type, 1))
+            data = m.SerializeToString(deterministic=True) if m.IsInitialized() else None
+            if data is not None:
+                assert cls.FromString(data) == m
+    r = pb.PrefillV2Request(forward_case=pb.PREFILL_CASE_NAIVE_PP | pb.PREFILL_CASE_IMMIGRATE)
+    assert r.forward_case == 12
+    text = render_proto()
+    assert "service TextGenerationService" in text and "rpc TanzBroadcast(BroadcastRequest)" in text
+    assert "oneof start_layer" in text and "repeated uint32 input_tokens = 8;" in text
+
+
+async def _cluster(n_workers, states, features, seed=0, **kw):
+    ports = _free_ports(n_workers + 1)
+    stop = asyncio.Event()
+    backends = [StubBackend(r, n_workers, seed=seed, ready=(states[r] != "Inactive"), load_s=0.15) for r in range(n_workers)]
+    tasks = []
+    for r, b in enumerate(backends):
+        ready = asyncio.Event()
+        tasks.append(asyncio.create_task(serve(b, "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+        await ready.wait()
+    cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n_workers}, 1, features,
+                                         max_blocks_per_replica=4000, **kw)
+    rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports[:n_workers]], model_layers=2)
+    tasks.append(asyncio.create_task(serve_router(rt, "127.0.0.1", ports[-1], stop=stop)))
+    await asyncio.sleep(0.2)
+    return rt, backends, ports[-1], stop, tasks
+
+
+async def _shutdown(stop, tasks):
+    stop.set()
+    await asyncio.wait(tasks, timeout=5)
+
+
+async def _run_config1(seed):
+    rt, backends, port, stop, tasks = await _cluster(2, ["Normal", "Inactive"], "impl_blitz,impl_nvl,manually_scale", seed)
+    trace = request_sim.make_mock_trace(rate=40.0, duration=3.0, seed=0, input_rng=(32, 512), output_rng=(16, 64),
+                                        max_requests=80)
+
+    async def scale_later():
+        await asyncio.sleep(1.0)
+        import aiohttp
+        async with aiohttp.ClientSession() as s:
+            async with s.post(f"http://127.0.0.1:{port}/modify_cluster_state", json={"replica": 1, "state": "Prefill"}) as r:
+                assert r.status == 200
+    sc = asyncio.create_task(scale_later())
+    recs = await request_sim.replay(f"http://127.0.0.1:{port}/generate", trace, record_tokens=True)
+    await sc
+    import aiohttp
+    async with aiohttp.ClientSession() as s:
+        async with s.get(f"http://127.0.0.1:{port}/metrics") as r:
+            metrics = await r.text()
+        async with s.get(f"http://127.0.0.1:{port}/info") as r:
+            info = await r.json()
+        async with s.get(f"http://127.0.0.1:{port}/health") as r:
+            assert r.status == 200
+    transitions = [l for _, l in rt.transitions]
+    used = rt.ctl.total_used_blocks()
+    pages = [b.pool.used_pages for b in backends]
+    await _shutdown(stop, tasks)
+    return trace, recs, metrics, info, transitions, used, pages, backends
+
+
+def test_config1_cpu_plumbing_scale_out_and_determinism():
+    trace, recs, metrics, info, transitions, used, pages, backends = asyncio.run(_run_config1(seed=0))
+    assert len(recs) == len(trace) and all(r["status"] == "ok" for r in recs), [r for r in recs if r["status"] != "ok"][:3]
+    for r, item in zip(recs, trace):
+        assert r["generated_tokens"] == item.output_len and len(r["tokens"]) == item.output_len
+        assert r["first_token_time"] >= 0 and r["total_time"] >= r["first_token_time"]
+    assert any("Replica<1> Inactive => LoadingPrefill" in l for l in transitions)
+    assert any("Replica<1> LoadingPrefill => Prefill" in l for l in transitions)
+    assert backends[1].counters["prefill"] > 0, "the scaled-out instance must serve requests"
+    assert "blitz_request_count 80" in metrics and "blitz_request_duration_count 80" in metrics
+    assert info["replicas"] == ["Prefill", "Prefill"]
+    assert used == 0 and pages == [0, 0]
+    s = request_sim.summarize(recs)
+    assert s["ok"] == 80 and s["output_tokens"] == sum(i.output_len for i in trace)
+    # same seeds -> identical token streams (tokens depend on request id and position only)
+    _, recs2, *_ = asyncio.run(_run_config1(seed=0))
+    assert [r["tokens"] for r in recs] == [r["tokens"] for r in recs2]
+    _, recs3, *_ = asyncio.run(_run_config1(seed=1))
+    assert [r["tokens"] for r in recs] != [r["tokens"] for r in recs3]
+
+
+def test_pd_disaggregation_with_autoscaling_over_grpc():
+    async def go():
+        rt, backends, port, stop, tasks = await _cluster(
+            4, ["Prefill", "Decode", "Inactive", "Inactive"], "impl_blitz,impl_fast_pro,impl_live_pro",
+            tokens_prefilled_per_sec=3000, max_prefill=3, max_decode=2)
+        for b in backends:
+            b.prefill_rate = 20000.0
+        trace = request_sim.make_mock_trace(rate=6.0, duration=4.0, seed=2, input_rng=(256, 1024), output_rng=(8, 24),
+                                            rate_step=(1.0, 50.0), max_requests=120)
+        recs = await request_sim.replay(f"http://127.0.0.1:{port}/generate", trace)
+        transitions = [l for _, l in rt.transitions]
+        counters = [dict(b.counters) for b in backends]
+        await _shutdown(stop, tasks)
+        return trace, recs, transitions, counters
+    trace, recs, transitions, counters = asyncio.run(go())
+    assert all(r["status"] == "ok" for r in recs), [r for r in recs if r["status"] != "ok"][:3]
+    assert sum(r["generated_tokens"] for r in recs) == sum(i.output_len for i in trace)
+    assert counters[0]["migrate"] > 0 and counters[1]["immigrate"] > 0        # KV moved prefill -> decode
+    assert any("Inactive => NewPrefill" in l or "Inactive => LoadingPrefill" in l for l in transitions)
+
+
+def test_worker_failure_is_detected_not_hung():
+    async def go():
+        rt, backends, port, stop, tasks = await _cluster(2, ["Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+
+        def boom(*a, **k):
+            raise RuntimeError("injected worker fault")
+        backends[1].decode = boom       # the decode worker fails every step (host-side fault injection)
+        trace = request_sim.make_mock_trace(rate=20.0, duration=0.5, seed=3, input_rng=(16, 64), output_rng=(4, 8), max_requests=6)
+        recs = await asyncio.wait_for(request_sim.replay(f"http://127.0.0.1:{port}/generate", trace), timeout=30)
+        state = rt.ctl.state_name(1)
+        await _shutdown(stop, tasks)
+        return recs, state
+    recs, state = asyncio.run(go())
+    assert state == "Inactive"
+    assert any(r["status"] != "ok" for r in recs)      # surfaced as an error, not a hang
+
+
+def test_direct_rpcs_against_stub_worker():
+    async def go():
+        port = _free_ports(1)[0]
+        stop, ready = asyncio.Event(), asyncio.Event()
+        b = StubBackend(0, 1, ready=False)
+        t = asyncio.create_task(serve(b, "127.0.0.1", port, stop_event=stop, ready_event=ready))
+        await ready.wait()
+        s = WorkerStub(f"127.0.0.1:{port}")
+        assert (await s.health()).state == "loading"
+        await s.set_status_ready()
+        assert (await s.health()).state == "ready"
+        assert (await s.info()).dtype == "float32"
+        batch = pb.Batch(id=5, size=2, max_tokens=128)
+        for i, n in enumerate((7, 20)):
+            r = batch.requests.add()
+            r.id, r.inputs, r.prefill_logprobs, r.top_n_tokens = i, "", False, 0
+            r.input_tokens.extend(range(n))
+            r.stopping_parameters.max_new_tokens = 3 if i == 0 else 2
+            r.stopping_parameters.ignore_eos_token = True
+        res = await s.prefill_v2(batch)
+        assert len(res.generations) == 2 and res.batch.request_ids == [0, 1] and res.total_ns > 0
+        d1 = await s.decode_v2([res.batch], [pb.Tokens()])
+        assert [g.request_id for g in d1.generations] == [0, 1]
+        assert d1.generations[1].HasField("generated_text") and d1.batch.request_ids == [0]
+        f = await s.filter_batch(5, [0])
+        assert f.batch.request_ids == [0]
+        d2 = await s.decode_v2([d1.batch], [pb.Tokens()])
+        assert d2.generations[0].generated_text.generated_tokens == 3 and not d2.HasField("batch")
+        assert b.pool.used_pages == 0
+        with pytest.raises(Exception):
+            await s.call("Prefill", pb.PrefillRequest(batch=batch))     # v1 RPCs are rejected
+        await s.reset_status()
+        with pytest.raises(Exception):
+            await s.prefill_v2(batch)                                    # parameters not loaded
+        await s.close()
+        stop.set()
+        await asyncio.wait([t], timeout=5)
+    asyncio.run(go())
