@@ -1,0 +1,244 @@
+// Tensor-parallel glue kernels for the fused GEMM->reduce-scatter / all-gather->GEMM pair.
+//
+// Data flow of one row-parallel + column-parallel pair on `tp` GPUs (push model, no collective library):
+//
+//   GEMM (push epilogue)   every rank stores its bf16 partial rows straight into the staging slot
+//                          stage[owner][src_rank][local_row][:] of the rank that owns those rows
+//                          (sequence-sharded residual), then bumps flag_rs[owner][src] once per tile.
+//   rs_reduce_norm (here)  the owner waits (bounded) for all tiles of all sources, sums the partials in
+//                          rank order in fp32 (deterministic), adds its residual shard, writes the new
+//                          residual, applies RMSNorm and stores the normalised rows into the gathered
+//                          activation buffer xg[M][H] of EVERY rank (all-gather by push), bumping
+//                          flag_ag[dst][src] once per row.
+//   next GEMM (wait flags) its TMA producer waits for flag_ag from all sources, fences the async proxy
+//                          and then reads xg from local memory only.
+//
+// This is the AllReduce of src/layer/attn.h:217-233 and src/layer/glu.h:138-154 split into its
+// reduce-scatter and all-gather halves with the add+RMSNorm (src/kernel/norm.cu:24-39) in between.
+// Flags are counters that their single consumer resets after use, so a captured CUDA graph can be
+// replayed without changing any launch parameter.
+#include "../kernels/common.cuh"
+#include "../kernels/ptx.cuh"
+
+namespace blitz {
+
+constexpr int kMaxTp = 8;
+
+struct RsReduceParams {
+  const void* stage;        // local staging: [tp][rows_per_rank][H] partials from every source rank
+  uint32_t* flag_rs;        // local: [tp] tiles landed per source (reset here)
+  uint32_t expect_tiles;    // tiles each source pushes into this rank per call
+  void* residual;           // local residual shard [rows_per_rank][H] (in/out); may be null (no residual)
+  const void* norm_w;       // [H]
+  void* xg[kMaxTp];         // gathered activations [M][H] on every rank (peer pointers, self included)
+  uint32_t* flag_ag[kMaxTp];  // flag_ag[dst] + my_rank : rows this rank has delivered to dst
+  int tp, my_rank, rows_per_rank, rows_valid, hidden;
+  float eps;
+  uint64_t budget_ns;
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const RsReduceParams p) {
+  __shared__ float red[33];
+  __shared__ int s_ok;
+  const int row = blockIdx.x;  // local row
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int s = 0; s < p.tp; ++s)
+      if (!ptx::bounded_flag_wait_ge(p.flag_rs + s, p.expect_tiles, p.budget_ns)) ok = 0;
+    if (!ok && p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int H = p.hidden, nvec = H >> 3;
+  const T* stage = reinterpret_cast<const T*>(p.stage);
+  T* res = reinterpret_cast<T*>(p.residual);
+  const int64_t roff = static_cast<int64_t>(row) * H;
+  // pass 1: sum partials (+ residual), write residual, accumulate sum of squares
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < p.tp; ++s) {
+      float f[8];
+      unpack8<T>(ld_nc16(stage + (static_cast<int64_t>(s) * p.rows_per_rank + row) * H + i * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    if (res) {
+      float f[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(res + roff + i * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      const uint4 packed = pack8<T>(acc);
+      *reinterpret_cast<uint4*>(res + roff + i * 8) = packed;
+      unpack8<T>(packed, acc);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += acc[j] * acc[j];
+    if (!res) {  // keep the summed row for pass 2 in the (now consumed) first staging slot
+      *reinterpret_cast<uint4*>(const_cast<T*>(stage) + static_cast<int64_t>(row) * H + i * 8) = pack8<T>(acc);
+    }
+  }
+  ss = block_sum(ss, red);
+  const float scale = rsqrtf(ss / static_cast<float>(H) + p.eps);
+  const T* src = res ? res + roff : stage + static_cast<int64_t>(row) * H;
+  const T* w = reinterpret_cast<const T*>(p.norm_w);
+  const int64_t grow = static_cast<int64_t>(p.my_rank) * p.rows_per_rank + row;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float f[8], g[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(src + i * 8), f);
+    unpack8<T>(__ldg(reinterpret_cast<const uint4*>(w) + i), g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * scale * g[j];
+    const uint4 v = pack8<T>(f);
+    for (int d = 0; d < p.tp; ++d)
+      ptx::st_na_v4(reinterpret_cast<T*>(p.xg[d]) + grow * H + i * 8, v);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.tp) {
+    ptx::fence_acq_rel_sys();
+    ptx::red_add_release_sys(p.flag_ag[threadIdx.x] + p.my_rank, 1u);
+  }
+  // the last block to finish re-arms the reduce-scatter flags for the next call
+  if (threadIdx.x == 0) {
+    const uint32_t t = ptx::atom_add_acq_rel_gpu(p.flag_rs + kMaxTp, 1u);
+    if (t == gridDim.x - 1) {
+      for (int s = 0; s < p.tp; ++s) p.flag_rs[s] = 0;
+      p.flag_rs[kMaxTp] = 0;
+      __threadfence_system();
+    }
+  }
+}
+
+__global__ void flags_zero_kernel(uint32_t* flags, int n) {
+  if (threadIdx.x < n) flags[threadIdx.x] = 0;
+  __threadfence_system();
+}
+
+// One-shot all-reduce for small tensors over peer memory: every rank pushes its contribution to all
+// peers' slot [src], then sums the tp slots in rank order.  Used for the vocab-sharded embedding and as
+// the low-latency all-reduce at tiny M.
+struct OneShotParams {
+  const void* x;            // local contribution [n] elements
+  void* slots[kMaxTp];      // slots[d]: base of rank d's receive area [tp][n]
+  uint32_t* flags[kMaxTp];  // flags[d] + src
+  void* out;                // local result [n]
+  int tp, my_rank;
+  int64_t n;
+  uint32_t want;            // flag value after this call (counter, caller tracks it; 0 = reset mode)
+  uint64_t budget_ns;
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) oneshot_push_kernel(const OneShotParams p) {
+  const int64_t nvec = p.n >> 3;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 v = ld_nc16(reinterpret_cast<const T*>(p.x) + i * 8);
+    for (int d = 0; d < p.tp; ++d)
+      ptx::st_na_v4(reinterpret_cast<T*>(p.slots[d]) + static_cast<int64_t>(p.my_rank) * p.n + i * 8, v);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.tp) {
+    ptx::fence_acq_rel_sys();
+    ptx::red_add_release_sys(p.flags[threadIdx.x] + p.my_rank, 1u);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) oneshot_reduce_kernel(const OneShotParams p, uint32_t expect_blocks) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int s = 0; s < p.tp; ++s)
+      if (!ptx::bounded_flag_wait_ge(p.flags[p.my_rank] + s, expect_blocks, p.budget_ns)) ok = 0;
+    if (!ok && p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int64_t nvec = p.n >> 3;
+  const T* mine = reinterpret_cast<const T*>(p.slots[p.my_rank]);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < p.tp; ++s) {
+      float f[8];
+      unpack8<T>(ld_nc16(mine + static_cast<int64_t>(s) * p.n + i * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + i * 8) = pack8<T>(acc);
+  }
+}
+
+}  // namespace blitz
+
+extern "C" {
+using namespace blitz;
+
+// stage: local [tp][rows_per_rank][hidden]; flag_rs: local uint32[kMaxTp + 1] (zero at start; [kMaxTp] is a ticket);
+// xg / flag_ag: tp peer pointers each.  rows_valid <= rows_per_rank local rows are processed.
+int blitz_rs_reduce_norm(const void* stage, uint32_t* flag_rs, uint32_t expect_tiles, void* residual,
+                         const void* norm_w, void* const* xg, uint32_t* const* flag_ag, int tp, int my_rank,
+                         int rows_per_rank, int rows_valid, int hidden, float eps, uint64_t budget_ns, int* status,
+                         int dtype, cudaStream_t stream) {
+  if (rows_valid <= 0) return 0;
+  if (tp < 1 || tp > kMaxTp || (hidden & 7)) return -1;
+  RsReduceParams p;
+  p.stage = stage; p.flag_rs = flag_rs; p.expect_tiles = expect_tiles; p.residual = residual; p.norm_w = norm_w;
+  for (int d = 0; d < kMaxTp; ++d) {
+    p.xg[d] = d < tp ? xg[d] : nullptr;
+    p.flag_ag[d] = d < tp ? flag_ag[d] : nullptr;
+  }
+  p.tp = tp; p.my_rank = my_rank; p.rows_per_rank = rows_per_rank; p.rows_valid = rows_valid; p.hidden = hidden;
+  p.eps = eps; p.budget_ns = budget_ns; p.status = status;
+  if (dtype == 1) rs_reduce_norm_kernel<__nv_bfloat16><<<rows_valid, 256, 0, stream>>>(p);
+  else rs_reduce_norm_kernel<__half><<<rows_valid, 256, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+int blitz_flags_zero(uint32_t* flags, int n, cudaStream_t stream) {
+  if (n <= 0 || n > 1024) return -1;
+  flags_zero_kernel<<<1, 1024, 0, stream>>>(flags, n);
+  return (int)cudaGetLastError();
+}
+
+// One-shot all-reduce of n elements (multiple of 8).  slots[d]: peer pointer to rank d's receive area of tp * n
+// elements; flags[d]: peer pointer to rank d's uint32[tp] arrival counters.  `expect` = number of push blocks per
+// rank (returned through *blocks_out on the first call with expect = 0 is not needed: it equals the grid used here).
+int blitz_allreduce_oneshot(const void* x, void* const* slots, uint32_t* const* flags, void* out, int tp, int my_rank,
+                            int64_t n, uint64_t budget_ns, int* status, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (tp < 1 || tp > kMaxTp || (n & 7)) return -1;
+  OneShotParams p;
+  p.x = x; p.out = out; p.tp = tp; p.my_rank = my_rank; p.n = n; p.want = 0; p.budget_ns = budget_ns; p.status = status;
+  for (int d = 0; d < kMaxTp; ++d) {
+    p.slots[d] = d < tp ? slots[d] : nullptr;
+    p.flags[d] = d < tp ? flags[d] : nullptr;
+  }
+  const int64_t nvec = n >> 3;
+  int blocks = (int)((nvec + 255) / 256);
+  if (blocks > 64) blocks = 64;
+  if (dtype == 1) {
+    oneshot_push_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(p);
+    oneshot_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(p, (uint32_t)blocks);
+  } else {
+    oneshot_push_kernel<__half><<<blocks, 256, 0, stream>>>(p);
+    oneshot_reduce_kernel<__half><<<blocks, 256, 0, stream>>>(p, (uint32_t)blocks);
+  }
+  // consumer-side reset: after the reduce kernel (stream order) nobody reads the counters of this call any more
+  flags_zero_kernel<<<1, 1024, 0, stream>>>(flags[my_rank], tp);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,26 +1,29 @@
-// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a with fused epilogues and in-kernel split-K.
 //
 //   C[M,N] = A[M,K] * B          (16-bit inputs, fp32 accumulation in TMEM)
 //
-// A is row-major (K contiguous).  B is either the serving weight layout
-// [K,N] row-major ("in,out": N contiguous, an MN-major UMMA operand) or
-// [N,K] row-major (K-major operand).  Operands are staged by TMA into
-// 128-byte-swizzled shared memory; one elected thread issues tcgen05.mma with
-// the accumulator in TMEM (double buffered so the epilogue of tile i overlaps
-// the main loop of tile i+1); four epilogue warps read TMEM with tcgen05.ld
-// and apply the fused epilogue:
-//   store            C = acc
-//   add              C = acc + R                (residual add of o_proj / down_proj)
-//   silu_mul         C = silu(acc_gate) * acc_up  (gate||up projection; B holds
-//                    N gate columns followed by N up columns)
+// A is row-major (K contiguous).  B is either the serving weight layout [K,N] row-major ("in,out":
+// N contiguous, an MN-major UMMA operand) or [N,K] row-major (K-major operand).  Operands are staged
+// by TMA into 128-byte-swizzled shared memory; one elected thread issues tcgen05.mma with the
+// accumulator in TMEM (double buffered: the epilogue of one work item overlaps the main loop of the
+// next); four epilogue warps read TMEM with tcgen05.ld and apply the fused epilogue:
+//   store      C = acc
+//   add        C = acc + R                  (residual add of o_proj / down_proj)
+//   silu_mul   C = silu(acc_gate) * acc_up  (gate||up projection; B holds N gate columns, then N up columns)
 //
-// Replaces the cuBLAS wrapper of the reference (src/util/cublas_wrapper.h:31-141,
-// call sites src/layer/attn.h:137-215, src/layer/glu.h:109-136,
-// src/layer/lm_head.h:89-98); the silu_mul and add epilogues absorb
-// src/kernel/activation.cu:9-23 and src/kernel/add.cu:13-55.
+// Measured on B200: a 128-row tcgen05.mma of K = 16 occupies the tensor pipe for ~140 cycles whatever
+// its N (<= 256), so (1) tiles are always as wide as the epilogue allows (N = 256 per instruction) and
+// (2) the time of a skinny GEMM (decode: M <= 256) is (K / 16) x 140 cycles per CTA unless K is split.
+// Skinny GEMMs therefore split K across CTAs until every SM has work: each CTA stores its fp32
+// partial tile to a scratch buffer, takes a ticket, and the CTA that arrives last sums the partials
+// in split order (deterministic), applies the epilogue and resets the ticket.  No second kernel.
 //
-// Roles (192 threads): warp 0 = TMA producer, warp 1 = UMMA issuer + TMEM
-// owner, warps 2..5 = epilogue (TMEM lane quarter = warp_idx % 4).
+// Replaces the cuBLAS wrapper of the reference (src/util/cublas_wrapper.h:31-141, call sites
+// src/layer/attn.h:137-215, src/layer/glu.h:109-136, src/layer/lm_head.h:89-98); the silu_mul and add
+// epilogues absorb src/kernel/activation.cu:9-23 and src/kernel/add.cu:13-55.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = UMMA issuer + TMEM owner, warps 2..5 =
+// epilogue (TMEM lane quarter = warp_idx % 4).
 #include "ptx.cuh"
 #include "tmap.cuh"
 #include <type_traits>
@@ -30,29 +33,44 @@ namespace blitz {
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
+constexpr int kMaxSplitK = 16;
 
-enum GemmEpilogue : int { kEpiStore = 0, kEpiAdd = 1, kEpiSiluMul = 2 };
+enum GemmEpilogue : int { kEpiStore = 0, kEpiAdd = 1, kEpiSiluMul = 2, kEpiPushRS = 3 };
 
 struct GemmParams {
   void* C;
   const void* R;
   int64_t ldc;
-  int M, N, K;      // N = output columns
-  int a_box_rows;   // rows actually fetched per A tile (<= 128, multiple of 8)
-  int up_col_off;   // silu_mul: column of B where the "up" half starts
+  int M, N, K;        // N = output columns
+  int a_box_rows;     // rows actually fetched per A tile (<= 128, multiple of 8)
+  int up_col_off;     // silu_mul: column of B where the "up" half starts
   int tiles_m, tiles_n;
+  int split_k;        // CTAs sharing one output tile along K
+  int kb_per_split;   // 64-wide K blocks per split
+  float* ws;          // split-K partials: [tile][split][128][BN] fp32
+  unsigned* tickets;  // one per output tile, zero between launches
   int* status;
+  // Tensor-parallel fusion.  push epilogue (GEMM -> reduce-scatter): row r of the partial result belongs to
+  // rank r / rows_per_rank and is stored into that rank's staging area [src rank][local row][N] over NVLink;
+  // one counter per (owner, source) is bumped per finished tile.  wait_flags (all-gather -> GEMM): the TMA
+  // producer waits until each of n_wait counters reaches wait_value before its first load of A, whose rows
+  // other ranks have stored into local memory.
+  uint8_t* push_base[8];
+  uint32_t* push_flags[8];
+  int tp, tp_rank, rows_per_rank;
+  const uint32_t* wait_flags;
+  int n_wait;
+  uint32_t wait_value;
 };
 
 template <int BN>
 struct GemmCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
   // Shared memory is carved at run time: A stages are only as tall as the rows TMA actually fetches
-  // (small-M decode GEMMs then keep 2-3x more weight bytes in flight); all A stages come first so that
-  // the 128-row UMMA view of a short A stage still lies inside the allocation (the extra rows are
-  // garbage and their output rows are never stored).
+  // (small-M decode GEMMs then keep more weight bytes in flight); all A stages come first so that the
+  // 128-row UMMA view of a short A stage still lies inside the allocation (the extra rows are garbage
+  // and their output rows are never stored).
   static constexpr int kMaxStages = 24;
   static constexpr int kBarrierBytes = (2 * kMaxStages + 4) * 8 + 16;
   static constexpr int kSmemBytes = 227 * 1024;
@@ -62,13 +80,7 @@ struct GemmCfg {
     int s = (kUsableBytes - kABytes) / (a_stage_bytes(a_rows) + kBBytes);
     return s > kMaxStages ? kMaxStages : s;
   }
-  // A tcgen05.mma that accumulates into the accumulator of the previous one waits for it (~140 cycles
-  // measured), which is longer than a 128xNx16 instruction runs when N < 256.  Narrow tiles therefore
-  // rotate their K steps over kSplit independent TMEM accumulators (summed in the epilogue) so the
-  // tensor pipe always has independent work: 4 accumulators for N = 64, 2 for N = 128.
-  static constexpr int kSplit = 256 / BN;
-  static constexpr int kAccCols = kSplit * BN;   // columns of one (double-buffered) accumulator set = 256
-  static constexpr int kTmemCols = 2 * kAccCols; // 512: the whole TMEM of the SM
+  static constexpr int kTmemCols = 2 * BN;
 };
 
 template <typename T>
@@ -96,16 +108,72 @@ __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+// Epilogue of 32 consecutive output columns of one row: acc (and up for silu_mul) -> C.
+template <typename T, int EPI>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&acc)[32], const float (&up)[32], int row,
+                                            int col0, bool row_ok) {
+  uint32_t out[16];
+  if (EPI == kEpiSiluMul) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = pack2<T>(silu_f(acc[2 * i]) * up[2 * i], silu_f(acc[2 * i + 1]) * up[2 * i + 1]);
+  } else if (EPI == kEpiAdd) {
+    const T* Rp = reinterpret_cast<const T*>(p.R);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = col0 + j * 8;
+      uint4 r = make_uint4(0, 0, 0, 0);
+      if (row_ok && col < p.N) r = *reinterpret_cast<const uint4*>(Rp + static_cast<int64_t>(row) * p.ldc + col);
+      const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<T>(rr[i]);
+        out[j * 4 + i] = pack2<T>(acc[j * 8 + 2 * i] + f.x, acc[j * 8 + 2 * i + 1] + f.y);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = pack2<T>(acc[2 * i], acc[2 * i + 1]);
+  }
+  if (row_ok) {
+    T* dst;
+    if (EPI == kEpiPushRS) {
+      const int owner = row / p.rows_per_rank, lrow = row - owner * p.rows_per_rank;
+      dst = reinterpret_cast<T*>(p.push_base[owner]) +
+            (static_cast<int64_t>(p.tp_rank) * p.rows_per_rank + lrow) * p.N + col0;
+    } else {
+      dst = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc + col0;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col0 + j * 8 < p.N)
+        *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+    }
+  }
+}
+
+// After every epilogue thread has stored its rows of a tile: make them visible system-wide and tell each
+// owner rank that one more tile from this source has landed.
+__device__ __forceinline__ void push_signal(const GemmParams& p, int m0, int epi_tid) {
+  __threadfence_system();
+  asm volatile("bar.sync 2, 128;" ::: "memory");
+  if (epi_tid == 0) {
+    const int last_row = min(p.M, m0 + kBM) - 1;
+    ptx::fence_acq_rel_sys();
+    for (int o = m0 / p.rows_per_rank; o <= last_row / p.rows_per_rank; ++o)
+      ptx::red_add_release_sys(p.push_flags[o] + p.tp_rank, 1u);
+  }
+}
+
 template <typename T, int BN, bool B_KMAJOR, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
   using Cfg = GemmCfg<BN>;
+  constexpr int kOutCols = (EPI == kEpiSiluMul) ? BN / 2 : BN;  // output columns per tile
+  constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  constexpr uint32_t kIdesc = ptx::make_idesc_f16(kFmt, 0u, B_KMAJOR ? 0u : 1u, kBM, BN);
   const int S = Cfg::num_stages(p.a_box_rows);
   const int a_stage = Cfg::a_stage_bytes(p.a_box_rows);
-  constexpr int kOutCols = (EPI == kEpiSiluMul) ? BN / 2 : BN;  // output columns per tile
-  constexpr uint32_t kFmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-  constexpr uint32_t kIdesc = ptx::make_idesc_f16(kFmt, 0u, B_KMAJOR ? 0u : 1u, kBM, BN);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -113,17 +181,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + S * a_stage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kUsableBytes);
-  uint64_t* full_bar = bars;             // [S]
-  uint64_t* empty_bar = bars + Cfg::kMaxStages;        // [S]
-  uint64_t* tfull_bar = bars + 2 * Cfg::kMaxStages;    // [2]
-  uint64_t* tempty_bar = bars + 2 * Cfg::kMaxStages + 2;  // [2]
+  uint64_t* full_bar = bars;                               // [S]
+  uint64_t* empty_bar = bars + Cfg::kMaxStages;            // [S]
+  uint64_t* tfull_bar = bars + 2 * Cfg::kMaxStages;        // [2]
+  uint64_t* tempty_bar = bars + 2 * Cfg::kMaxStages + 2;   // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kMaxStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + kBK - 1) / kBK;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_items = num_tiles * p.split_k;  // item = tile * split_k + split
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -155,10 +225,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       const uint32_t tx_bytes = static_cast<uint32_t>(p.a_box_rows) * kBK * 2 + Cfg::kBBytes;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % p.tiles_m) * kBM;
-        const int n0 = (t / p.tiles_m) * kOutCols;
-        for (int kb = 0; kb < num_kb; ++kb) {
+      if (p.n_wait > 0) {
+        // rows of A arrive by peer stores (generic proxy); TMA reads them through the async proxy
+        for (int i = 0; i < p.n_wait && ok; ++i)
+          if (!ptx::bounded_flag_wait_ge(p.wait_flags + i, p.wait_value, ptx::kDefaultWaitNs)) ok = false;
+        if (!ok) {
+          *abort_flag = 1;
+          if (p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
+        }
+        ptx::fence_proxy_async_all();
+      }
+      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+        const int tile = w / p.split_k, split = w % p.split_k;
+        const int m0 = (tile % p.tiles_m) * kBM;
+        const int n0 = (tile / p.tiles_m) * kOutCols;
+        const int kb_beg = split * p.kb_per_split;
+        const int kb_end = min(num_kb, kb_beg + p.kb_per_split);
+        for (int kb = kb_beg; kb < kb_end; ++kb) {
           if (!ptx::bounded_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             if (p.status) atomicCAS(p.status, 0, kStatusTimeoutProducer);
             ok = false;
@@ -205,14 +288,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+        const int split = w % p.split_k;
+        const int kb_beg = split * p.kb_per_split;
+        const int kb_end = min(num_kb, kb_beg + p.kb_per_split);
         if (!ptx::bounded_mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) {
           if (p.status) atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
         ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * Cfg::kAccCols);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = kb_beg; kb < kb_end; ++kb) {
           if (!ptx::bounded_mbar_wait(&full_bar[stage], phase, abort_flag)) {
             if (p.status) atomicCAS(p.status, 0, kStatusTimeoutMma);
             ok = false;
@@ -233,9 +319,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               // 8-K-row groups 1024 B apart (stride offset); 16 K-rows = 2048 B.
               bdesc = ptx::make_smem_desc(b_base + k * 2048, 8192, 1024, ptx::kLayoutSw128);
             }
-            // K step k goes to sub-accumulator k % kSplit; its first use in a tile overwrites
-            ptx::umma_f16_ss(d_tmem + static_cast<uint32_t>((k % Cfg::kSplit) * BN), adesc, bdesc, kIdesc,
-                             (kb != 0 || k >= Cfg::kSplit) ? 1u : 0u);
+            ptx::umma_f16_ss(d_tmem, adesc, bdesc, kIdesc, (kb != kb_beg || k != 0) ? 1u : 0u);
           }
           ptx::umma_commit(&empty_bar[stage]);
           if (++stage == S) {
@@ -250,92 +334,109 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue warps
+    // ------------------------------------------------------------ epilogue warps (128 threads, named barrier 2)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int row_in_tile = q * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
     int acc = 0;
     uint32_t acc_phase = 0;
-    T* Cp = reinterpret_cast<T*>(p.C);
-    const T* Rp = reinterpret_cast<const T*>(p.R);
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const int m0 = (t % p.tiles_m) * kBM;
-      const int n0 = (t / p.tiles_m) * kOutCols;
+    for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
+      const int tile = w / p.split_k;
+      const int m0 = (tile % p.tiles_m) * kBM;
+      const int n0 = (tile / p.tiles_m) * kOutCols;
       if (!ptx::bounded_mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
         if (p.status && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
         break;
       }
       ptx::tc_fence_after_sync();
-      const uint32_t taddr =
-          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * Cfg::kAccCols);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
       const int row = m0 + row_in_tile;
       const bool row_ok = row < p.M;
+      if (p.split_k == 1) {
 #pragma unroll 1
-      for (int c = 0; c < kOutCols; c += 32) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(taddr + c, v);
-        if (Cfg::kSplit > 1) {  // sum the sub-accumulators
-#pragma unroll
-          for (int j = 1; j < Cfg::kSplit; ++j) {
-            uint32_t w[32];
-            ptx::tmem_ld_32x32(taddr + j * BN + c, w);
+        for (int c = 0; c < kOutCols; c += 32) {
+          uint32_t v[32];
+          float a[32], u[32];
+          ptx::tmem_ld_32x32(taddr + c, v);
+          if (EPI == kEpiSiluMul) {
+            uint32_t t[32];
+            ptx::tmem_ld_32x32(taddr + BN / 2 + c, t);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(w[i]));
+            for (int i = 0; i < 32; ++i) u[i] = __uint_as_float(t[i]);
+          } else {
+            ptx::tmem_ld_wait();
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = __uint_as_float(v[i]);
+          store_chunk<T, EPI>(p, a, u, row, n0 + c, row_ok);
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&tempty_bar[acc]);
+        if (EPI == kEpiPushRS) push_signal(p, m0, epi_tid);
+      } else {
+        // split-K: park the fp32 partial, the last CTA of the tile reduces and finishes it
+        // partial layout [BN/4][128 rows][4 floats]: the 32 lanes (= 32 rows) of a store write 512 contiguous bytes
+        float* part = p.ws + static_cast<size_t>(w) * (kBM * BN) + static_cast<size_t>(row_in_tile) * 4;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(taddr + c, v);
+          ptx::tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              __stcg(reinterpret_cast<uint4*>(part + static_cast<size_t>(c / 4 + j) * (kBM * 4)),
+                     make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
           }
         }
-        uint32_t out[16];
-        if (EPI == kEpiSiluMul) {
-          uint32_t u[32];
-          ptx::tmem_ld_32x32(taddr + BN / 2 + c, u);
-          ptx::tmem_ld_wait();
-          if (Cfg::kSplit > 1) {
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&tempty_bar[acc]);
+        __threadfence();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (epi_tid == 0) {
+          const unsigned old = atomicAdd(&p.tickets[tile], 1u);
+          const int last = (old == static_cast<unsigned>(p.split_k - 1)) ? 1 : 0;
+          if (last) p.tickets[tile] = 0;  // ready for the next launch
+          *last_flag = last;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          const float* base = p.ws + static_cast<size_t>(tile) * p.split_k * (kBM * BN) + static_cast<size_t>(row_in_tile) * 4;
+#pragma unroll 1
+          for (int c = 0; c < kOutCols; c += 32) {
+            float a[32], u[32];
 #pragma unroll
-            for (int j = 1; j < Cfg::kSplit; ++j) {
-              uint32_t w[32];
-              ptx::tmem_ld_32x32(taddr + j * BN + BN / 2 + c, w);
-              ptx::tmem_ld_wait();
+            for (int i = 0; i < 32; ++i) a[i] = u[i] = 0.f;
+            if (row_ok) {
+              for (int s = 0; s < p.split_k; ++s) {
+                const float* ps = base + static_cast<size_t>(s) * (kBM * BN);
+                float4 f[8];
 #pragma unroll
-              for (int i = 0; i < 32; ++i) u[i] = __float_as_uint(__uint_as_float(u[i]) + __uint_as_float(w[i]));
-            }
-          }
+                for (int j = 0; j < 8; ++j)
+                  f[j] = __ldcg(reinterpret_cast<const float4*>(ps + static_cast<size_t>(c / 4 + j) * (kBM * 4)));
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float g0 = __uint_as_float(v[2 * i]), g1 = __uint_as_float(v[2 * i + 1]);
-            float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
-            out[i] = pack2<T>(silu_f(g0) * u0, silu_f(g1) * u1);
-          }
-        } else {
-          ptx::tmem_ld_wait();
-          if (EPI == kEpiAdd) {
+                for (int j = 0; j < 8; ++j) {
+                  a[4 * j] += f[j].x; a[4 * j + 1] += f[j].y; a[4 * j + 2] += f[j].z; a[4 * j + 3] += f[j].w;
+                }
+                if (EPI == kEpiSiluMul) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int col = n0 + c + j * 8;
-              uint4 r = make_uint4(0, 0, 0, 0);
-              if (row_ok && col < p.N) r = *reinterpret_cast<const uint4*>(Rp + static_cast<int64_t>(row) * p.ldc + col);
-              const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+                  for (int j = 0; j < 8; ++j)
+                    f[j] = __ldcg(reinterpret_cast<const float4*>(ps + static_cast<size_t>((BN / 2 + c) / 4 + j) * (kBM * 4)));
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                float2 f = unpack2<T>(rr[i]);
-                out[j * 4 + i] = pack2<T>(__uint_as_float(v[j * 8 + 2 * i]) + f.x,
-                                          __uint_as_float(v[j * 8 + 2 * i + 1]) + f.y);
+                  for (int j = 0; j < 8; ++j) {
+                    u[4 * j] += f[j].x; u[4 * j + 1] += f[j].y; u[4 * j + 2] += f[j].z; u[4 * j + 3] += f[j].w;
+                  }
+                }
               }
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) out[i] = pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            store_chunk<T, EPI>(p, a, u, row, n0 + c, row_ok);
           }
+          if (EPI == kEpiPushRS) push_signal(p, m0, epi_tid);
         }
-        if (row_ok) {
-          T* dst = Cp + static_cast<int64_t>(row) * p.ldc + n0 + c;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (n0 + c + j * 8 < p.N)
-              *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-          }
-        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");  // last_flag is rewritten by the next item
       }
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&tempty_bar[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -383,45 +484,63 @@ static cudaError_t dispatch_epi(int epi, int bn, const CUtensorMap& ta, const CU
   switch (epi) {
     case kEpiAdd: return dispatch_bn<T, B_KMAJOR, kEpiAdd>(bn, ta, tb, p, grid, stream);
     case kEpiSiluMul: return dispatch_bn<T, B_KMAJOR, kEpiSiluMul>(bn, ta, tb, p, grid, stream);
+    case kEpiPushRS: return dispatch_bn<T, B_KMAJOR, kEpiPushRS>(bn, ta, tb, p, grid, stream);
     default: return dispatch_bn<T, B_KMAJOR, kEpiStore>(bn, ta, tb, p, grid, stream);
   }
-}
-
-// Tile width.  Measured on B200 at decode sizes: 128-wide tiles win once they give at least ~0.45 tiles per
-// SM; below that 64-wide tiles (more CTAs streaming weights) are better; 256-wide only when it still
-// fills the machine (large M) or for the gate||up GEMM, where a 256-wide tile yields 128 outputs.
-static int choose_bn(int M, int N, int epi, int sms) {
-  const int tiles_m = (M + kBM - 1) / kBM;
-  auto tiles = [&](int bn) {
-    const int out_cols = epi == kEpiSiluMul ? bn / 2 : bn;
-    return tiles_m * ((N + out_cols - 1) / out_cols);
-  };
-  if (tiles(256) >= sms) return 256;
-  if (epi == kEpiSiluMul) return 128;
-  if (tiles(128) * 100 >= sms * 45) return 128;
-  return 64;
 }
 
 }  // namespace blitz
 
 extern "C" {
 
-// dtype: 0 = fp16, 1 = bf16.  b_layout: 0 = B is [K, ldb>=Ncols] row-major
-// (weights stored in,out), 1 = B is [Ncols, ldb>=K] row-major.  epilogue: 0
-// store, 1 add residual R (same pitch as C), 2 silu(gate)*up where B carries N
-// gate columns followed (at column `up_col_off`) by N up columns.
-// bn_hint: 0 = choose, else 64/128/256.  Returns a cudaError_t value, or -1
-// for an argument the kernel cannot take, -2 when the TMA encoder is missing.
-int blitz_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc, const void* R, int M,
-               int N, int K, int b_layout, int epilogue, int up_col_off, int dtype, int bn_hint, int* status,
-               cudaStream_t stream) {
+// Scratch the split-K path needs for a problem: bytes of fp32 partials (tickets are separate: one
+// uint32 per output tile, zero-initialised once by the caller; the kernel leaves them zero).
+int64_t blitz_gemm_workspace_bytes(int sms) { return (int64_t)(sms + 16) * blitz::kBM * 256 * 4; }
+
+// dtype: 0 = fp16, 1 = bf16.  b_layout: 0 = B is [K, ldb>=Ncols] row-major (weights stored in,out),
+// 1 = B is [Ncols, ldb>=K] row-major.  epilogue: 0 store, 1 add residual R (same pitch as C),
+// 2 silu(gate)*up where B carries N gate columns followed (at column `up_col_off`) by N up columns.
+// bn_hint: 0 = 256-wide tiles, else 64/128/256.  split_hint: 0 = choose, 1 = never split, else the
+// number of K splits.  ws / ws_bytes: fp32 scratch for split-K partials, tickets / num_tickets:
+// zeroed uint32 array (both may be null: the GEMM then never splits).
+// Returns a cudaError_t value, or -1 for an argument the kernel cannot take, -2 when the TMA
+// encoder is missing.
+// Tile width the launcher uses for a problem (callers of the push epilogue need it to know how many tiles
+// each owner rank will receive: ceil(N / tile_n) per 128-row block that overlaps the owner's rows).
+int blitz_gemm_tile_n(int M, int N, int epilogue, int bn_hint) {
+  using namespace blitz;
+  const int sms = device_sm_count();
+  int bn = bn_hint;
+  if (!bn) {
+    const int oc256 = epilogue == kEpiSiluMul ? 128 : 256;
+    const int tiles256 = ((M + kBM - 1) / kBM) * ((N + oc256 - 1) / oc256);
+    bn = tiles256 >= sms ? 256 : 128;
+  }
+  if (epilogue == kEpiSiluMul && bn < 128) bn = 128;
+  return bn;
+}
+
+struct BlitzGemmTp {
+  void* push_base[8];      // kEpiPushRS: staging base of every rank (peer pointers), [tp][rows_per_rank][N] each
+  uint32_t* push_flags[8];  // flag array of every rank; entry [tp_rank] is bumped per tile
+  int tp, tp_rank, rows_per_rank;
+  const uint32_t* wait_flags;  // local counters to wait for before loading A (null: none)
+  int n_wait;
+  uint32_t wait_value;
+};
+
+static int gemm_impl(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc, const void* R, int M,
+                     int N, int K, int b_layout, int epilogue, int up_col_off, int dtype, int bn_hint, int split_hint,
+                     void* ws, int64_t ws_bytes, unsigned* tickets, int num_tickets, int* status,
+                     const BlitzGemmTp* tpa, cudaStream_t stream) {
   using namespace blitz;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N & 7) || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7)) return -1;
   if (epilogue == kEpiSiluMul && (up_col_off & 7)) return -1;
   const int sms = device_sm_count();
-  int bn = bn_hint ? bn_hint : choose_bn(M, N, epilogue, sms);
-  if (epilogue == kEpiSiluMul && bn < 128) bn = 128;
+  // 256-wide tiles are the most efficient per FLOP (a 128xNx16 instruction costs ~95 cycles at N = 64,
+  // ~105 at N = 128, ~150 at N = 256); when they would leave SMs idle, 128-wide tiles plus split-K win.
+  const int bn = blitz_gemm_tile_n(M, N, epilogue, bn_hint);
   const int out_cols = epilogue == kEpiSiluMul ? bn / 2 : bn;
   const int b_cols_total = epilogue == kEpiSiluMul ? up_col_off + N : N;
 
@@ -437,6 +556,35 @@ int blitz_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, 
   p.tiles_m = (M + kBM - 1) / kBM;
   p.tiles_n = (N + out_cols - 1) / out_cols;
   p.status = status;
+  p.tp = 1; p.tp_rank = 0; p.rows_per_rank = M; p.wait_flags = nullptr; p.n_wait = 0; p.wait_value = 0;
+  for (int i = 0; i < 8; ++i) { p.push_base[i] = nullptr; p.push_flags[i] = nullptr; }
+  if (tpa) {
+    p.tp = tpa->tp; p.tp_rank = tpa->tp_rank; p.rows_per_rank = tpa->rows_per_rank > 0 ? tpa->rows_per_rank : M;
+    p.wait_flags = tpa->wait_flags; p.n_wait = tpa->wait_flags ? tpa->n_wait : 0; p.wait_value = tpa->wait_value;
+    for (int i = 0; i < 8 && i < tpa->tp; ++i) {
+      p.push_base[i] = reinterpret_cast<uint8_t*>(tpa->push_base[i]);
+      p.push_flags[i] = tpa->push_flags[i];
+    }
+  }
+  if (epilogue == kEpiPushRS && (!tpa || tpa->tp < 1 || tpa->tp > 8 || p.rows_per_rank * tpa->tp < M)) return -1;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (K + kBK - 1) / kBK;
+
+  // split K until every SM has a work item (skinny decode GEMMs), bounded by the scratch we were given
+  int split = 1;
+  if (split_hint != 1 && ws && tickets && tiles <= num_tickets && tiles * 4 < sms * 3) {
+    // measured sweet spot: enough splits to fill the SMs but at most 4 (the reduction grows with the split count)
+    split = split_hint > 1 ? split_hint : (sms / tiles > 4 ? 4 : sms / tiles);
+    if (split > kMaxSplitK) split = kMaxSplitK;
+    if (split > num_kb) split = num_kb;
+    const int64_t per_item = (int64_t)kBM * bn * 4;
+    if ((int64_t)tiles * split * per_item > ws_bytes) split = (int)(ws_bytes / (tiles * per_item));
+    if (split < 1) split = 1;
+  }
+  p.kb_per_split = (num_kb + split - 1) / split;
+  p.split_k = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
+  p.ws = reinterpret_cast<float*>(ws);
+  p.tickets = tickets;
 
   CUtensorMap ta, tb;
   if (!get_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, kBK, (uint32_t)p.a_box_rows)) return -2;
@@ -449,8 +597,8 @@ int blitz_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, 
   }
   if (!okb) return -2;
 
-  const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sms ? tiles : sms;
+  const int items = tiles * p.split_k;
+  const int grid = items < sms ? items : sms;
   cudaError_t e;
   if (dtype == 1) {
     e = b_layout == 0 ? dispatch_epi<__nv_bfloat16, false>(epilogue, bn, ta, tb, p, grid, stream)
@@ -460,6 +608,24 @@ int blitz_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, 
                       : dispatch_epi<__half, true>(epilogue, bn, ta, tb, p, grid, stream);
   }
   return static_cast<int>(e);
+}
+
+int blitz_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc, const void* R, int M,
+               int N, int K, int b_layout, int epilogue, int up_col_off, int dtype, int bn_hint, int split_hint,
+               void* ws, int64_t ws_bytes, unsigned* tickets, int num_tickets, int* status, cudaStream_t stream) {
+  return gemm_impl(A, lda, B, ldb, C, ldc, R, M, N, K, b_layout, epilogue, up_col_off, dtype, bn_hint, split_hint, ws,
+                   ws_bytes, tickets, num_tickets, status, nullptr, stream);
+}
+
+// Tensor-parallel variant: epilogue 3 pushes the partial result to the owner ranks' staging areas
+// (GEMM -> reduce-scatter); a non-null tp->wait_flags makes the kernel wait for rows of A that other
+// ranks are storing into local memory (all-gather -> GEMM).  See BlitzGemmTp.
+int blitz_gemm_tp(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc, const void* R, int M,
+                  int N, int K, int b_layout, int epilogue, int up_col_off, int dtype, int bn_hint, int split_hint,
+                  void* ws, int64_t ws_bytes, unsigned* tickets, int num_tickets, int* status, const BlitzGemmTp* tp,
+                  cudaStream_t stream) {
+  return gemm_impl(A, lda, B, ldb, C, ldc, R, M, N, K, b_layout, epilogue, up_col_off, dtype, bn_hint, split_hint, ws,
+                   ws_bytes, tickets, num_tickets, status, tp, stream);
 }
 
 }  // extern "C"

@@ -57,6 +57,8 @@ def check_status(device=None, reset: bool = True) -> int:
     if code != 0:
         if reset:
             w.zero_()
+            for _, tickets in _gemm_ws.values():  # an aborted split-K GEMM may leave tickets behind
+                tickets.zero_()
         names = {1: "TMA producer wait timed out", 2: "MMA wait timed out", 3: "epilogue wait timed out",
                  4: "flag wait timed out", 5: "index out of range", 6: "size beyond the supported maximum"}
         raise RuntimeError(f"kernel status {code}: {names.get(code, 'unknown')}")
@@ -67,13 +69,29 @@ def check_status(device=None, reset: bool = True) -> int:
 _EPI = {"store": 0, "add": 1, "silu_mul": 2}
 
 
+_gemm_ws = {}
+GEMM_TICKETS = 4096
+
+
+def gemm_workspace(device=None):
+    """Per-device scratch of the split-K path: (fp32 partials as bytes, zeroed uint32 tickets)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.type, dev.index)
+    if key not in _gemm_ws:
+        n = int(lib().blitz_gemm_workspace_bytes(148))
+        _gemm_ws[key] = (torch.empty(n, dtype=torch.uint8, device=dev),
+                         torch.zeros(GEMM_TICKETS, dtype=torch.int32, device=dev))
+    return _gemm_ws[key]
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, residual=None,
-         epilogue: str = "store", b_layout: str = "kn", bn: int = 0) -> torch.Tensor:
+         epilogue: str = "store", b_layout: str = "kn", bn: int = 0, split_k: int = 0) -> torch.Tensor:
     """``out = a @ b`` on tcgen05 with a fused epilogue.
 
     a: [M, K].  b: [K, N] when ``b_layout == 'kn'`` (weights stored in,out) or [N, K] for ``'nk'``.
     epilogue 'add' adds ``residual`` ([M, N], same pitch as out); 'silu_mul' treats b as [gate | up] with
-    N_out = b_cols / 2 and returns silu(a@gate) * (a@up).
+    N_out = b_cols / 2 and returns silu(a@gate) * (a@up).  ``split_k``: 0 lets the kernel split K when the
+    GEMM is too skinny to fill the GPU, 1 forbids it, n > 1 forces n splits.
     """
     assert a.is_cuda and a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     M, K = a.shape
@@ -90,9 +108,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     assert out.shape == (M, N) and out.stride(1) == 1
     if epi == 1:
         assert residual is not None and residual.shape == (M, N) and residual.stride(0) == out.stride(0)
+    ws, tickets = gemm_workspace(a.device)
     rc = lib().blitz_gemm(_p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), _p(residual), M, N, K,
-                          0 if b_layout == "kn" else 1, epi, N if epi == 2 else 0, _dt(a), bn,
-                          _p(status_word(a.device)), _stream())
+                          0 if b_layout == "kn" else 1, epi, N if epi == 2 else 0, _dt(a), bn, split_k,
+                          _p(ws), ws.numel(), _p(tickets), tickets.numel(), _p(status_word(a.device)), _stream())
     _check(rc, "blitz_gemm")
     return out
 

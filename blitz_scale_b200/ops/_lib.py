@@ -53,7 +53,17 @@ def _declare(L: ctypes.CDLL) -> None:
             fn.argtypes = args
             fn.restype = res
 
-    sig("blitz_gemm", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_p])
+    sig("blitz_gemm", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_i64,
+                       c_p, c_i, c_p, c_p])
+    sig("blitz_gemm_workspace_bytes", [c_i], c_i64)
+    sig("blitz_gemm_tile_n", [c_i, c_i, c_i, c_i], c_i)
+    sig("blitz_gemm_tp", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_i64,
+                          c_p, c_i, c_p, c_p, c_p])
+    pp_ = ctypes.POINTER(c_p)
+    sig("blitz_rs_reduce_norm", [c_p, c_p, ctypes.c_uint32, c_p, c_p, pp_, pp_, c_i, c_i, c_i, c_i, c_i, c_f, c_u64, c_p,
+                                 c_i, c_p])
+    sig("blitz_flags_zero", [c_p, c_i, c_p])
+    sig("blitz_allreduce_oneshot", [c_p, pp_, pp_, c_p, c_i, c_i, c_i64, c_u64, c_p, c_i, c_p])
     sig("blitz_embedding", [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_i, c_p])
     sig("blitz_rms_norm", [c_p, c_p, c_p, c_i, c_i, c_f, c_i, c_p])
     sig("blitz_add_rms_norm", [c_p, c_p, c_p, c_p, c_i, c_i, c_f, c_i, c_p])

@@ -1,0 +1,230 @@
+"""Fused tensor-parallel layer path: GEMM -> reduce-scatter and all-gather -> GEMM over peer memory.
+
+`FusedTP` owns the symmetric buffers of one replica's TP group (two staging areas for the partial
+results of the row-parallel GEMMs, two gathered-activation buffers, the flag words, and a slot area
+for the one-shot all-reduce of the vocab-sharded embedding) and exposes the three launches of the
+data flow described in csrc/comm/tp_fused.cu:
+
+    gemm_rs(a, w, which)                      tcgen05 GEMM whose epilogue pushes partial rows to their owner rank
+    reduce_norm(which, residual, w, which_x)  owner sums partials + residual, RMSNorm, pushes rows to every rank
+    ag_gemm(which_x, w, ...)                  tcgen05 GEMM whose TMA producer waits for the gathered rows
+
+`LlamaRunnerTP` runs the Llama forward with those launches: the residual stream is sharded by rows
+between the row-parallel and column-parallel GEMMs (Megatron-style sequence parallelism falls out of
+the push model), and no collective library is called in the layer loop.  It replaces the
+AllReduce-after-GEMM structure of src/layer/attn.h:217-233 and src/layer/glu.h:138-154; the NCCL
+version of the same forward (`LlamaRunner` with `TPComm`) is kept as the comparison baseline.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..models.llama import LlamaRunner, StepMeta, TPComm
+from ..ops import _lib as _L
+from ..ops import _check, _dt, _p, _stream, gemm_workspace, status_word
+from .symm import SymmRegion
+
+
+class _GemmTp(ctypes.Structure):
+    _fields_ = [("push_base", ctypes.c_void_p * 8), ("push_flags", ctypes.c_void_p * 8), ("tp", ctypes.c_int),
+                ("tp_rank", ctypes.c_int), ("rows_per_rank", ctypes.c_int), ("wait_flags", ctypes.c_void_p),
+                ("n_wait", ctypes.c_int), ("wait_value", ctypes.c_uint32)]
+
+
+_EPI = {"store": 0, "add": 1, "silu_mul": 2, "push": 3}
+
+
+class FusedTP:
+    FLAG_WORDS = 128  # rs0: 0..15, rs1: 16..31, ag0: 32..39, ag1: 40..47, emb: 48..55
+
+    def __init__(self, group, hidden: int, max_rows: int, dtype=torch.bfloat16, device=None):
+        import torch.distributed as dist
+        self.group = group
+        self.tp = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.hidden, self.dtype = hidden, dtype
+        self.max_rows = (max_rows + self.tp * 8 - 1) // (self.tp * 8) * (self.tp * 8)
+        self.elem = 2
+        self.buf_bytes = self.max_rows * hidden * self.elem
+        # layout of the symmetric region
+        self.o_stage = [0, self.buf_bytes]
+        self.o_xg = [2 * self.buf_bytes, 3 * self.buf_bytes]
+        self.o_emb = 4 * self.buf_bytes                       # [tp][max_rows * hidden]
+        self.o_flags = self.o_emb + self.tp * self.buf_bytes
+        total = self.o_flags + self.FLAG_WORDS * 4
+        self.region = SymmRegion(total, group, device)
+        self.region.local[self.o_flags:].zero_()
+        torch.cuda.synchronize()
+        self.region.barrier()
+        self.ptrs = self.region.ptrs
+        self.device = self.region.local.device
+        self.budget_ns = int(2e9)
+
+    # ------------------------------------------------------------------ views / pointers
+    def xg(self, which: int, rows: int) -> torch.Tensor:
+        off = self.o_xg[which]
+        return self.region.local[off:off + rows * self.hidden * self.elem].view(self.dtype).view(rows, self.hidden)
+
+    def _flag_ptr(self, rank: int, word: int) -> int:
+        return self.ptrs[rank] + self.o_flags + word * 4
+
+    def _tp_struct(self) -> _GemmTp:
+        s = _GemmTp()
+        s.tp, s.tp_rank = self.tp, self.rank
+        return s
+
+    def _gemm(self, a, w, out, epi, tp_struct, residual=None, N=None):
+        M, K = a.shape
+        bcols = w.shape[1]
+        n_out = bcols // 2 if epi == 2 else bcols
+        ws, tickets = gemm_workspace(a.device)
+        rc = _L.lib().blitz_gemm_tp(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0) if out is not None else n_out,
+                                    _p(residual), M, n_out, K, 0, epi, n_out if epi == 2 else 0, _dt(a), 0, 0,
+                                    _p(ws), ws.numel(), _p(tickets), tickets.numel(), _p(status_word(a.device)),
+                                    ctypes.byref(tp_struct), _stream())
+        _check(rc, "blitz_gemm_tp")
+
+    # ------------------------------------------------------------------ the three launches
+    def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, which: int) -> int:
+        """Partial result of a row-parallel GEMM pushed to the owners' staging area `which`.  a: [M, K_local] with
+        M a multiple of tp.  Returns the number of tiles every owner receives from each source."""
+        M = a.shape[0]
+        assert M % self.tp == 0 and M <= self.max_rows
+        rpr = M // self.tp
+        s = self._tp_struct()
+        s.rows_per_rank = rpr
+        for r in range(self.tp):
+            s.push_base[r] = self.ptrs[r] + self.o_stage[which]
+            s.push_flags[r] = self._flag_ptr(r, 16 * which)
+        self._gemm(a, w, None, 3, s)
+        bn = int(_L.lib().blitz_gemm_tile_n(M, w.shape[1], 3, 0))
+        tiles_n = (w.shape[1] + bn - 1) // bn
+        lo, hi = self.rank * rpr, (self.rank + 1) * rpr - 1
+        return tiles_n * (hi // 128 - lo // 128 + 1)
+
+    def reduce_norm(self, which: int, expect_tiles: int, rows_per_rank: int, residual: Optional[torch.Tensor],
+                    norm_w: torch.Tensor, which_x: int, eps: float) -> None:
+        """Owner side: sum the partials of staging area `which` (+ residual shard, updated in place), RMSNorm, push the
+        normalised rows into gathered buffer `which_x` of every rank."""
+        xg = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + self.o_xg[which_x] for r in range(self.tp)])
+        fl = (ctypes.c_void_p * self.tp)(*[self._flag_ptr(r, 32 + 8 * which_x) for r in range(self.tp)])
+        rc = _L.lib().blitz_rs_reduce_norm(
+            ctypes.c_void_p(self.ptrs[self.rank] + self.o_stage[which]), ctypes.c_void_p(self._flag_ptr(self.rank, 16 * which)),
+            expect_tiles, _p(residual), _p(norm_w), xg, fl, self.tp, self.rank, rows_per_rank, rows_per_rank, self.hidden,
+            eps, self.budget_ns, _p(status_word(self.device)), 1 if self.dtype == torch.bfloat16 else 0, _stream())
+        _check(rc, "blitz_rs_reduce_norm")
+
+    def ag_gemm(self, which_x: int, rows: int, w: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
+                wait: bool = True) -> torch.Tensor:
+        """Column-parallel GEMM on the gathered activations; waits in-kernel for every source's rows, then re-arms the flags."""
+        a = self.xg(which_x, rows)
+        s = self._tp_struct()
+        s.rows_per_rank = rows
+        if wait:
+            s.wait_flags = self._flag_ptr(self.rank, 32 + 8 * which_x)
+            s.n_wait = self.tp
+            s.wait_value = rows // self.tp
+        self._gemm(a, w, out, _EPI[epilogue], s)
+        if wait:
+            _check(_L.lib().blitz_flags_zero(ctypes.c_void_p(self._flag_ptr(self.rank, 32 + 8 * which_x)), self.tp, _stream()),
+                   "blitz_flags_zero")
+        return out
+
+    def wait_gathered(self, which_x: int, rows: int) -> None:
+        """Stream-ordered wait for gathered buffer `which_x` (for consumers that are not GEMMs), then re-arm."""
+        for sidx in range(self.tp):
+            _check(_L.lib().blitz_flag_wait(ctypes.c_void_p(self._flag_ptr(self.rank, 32 + 8 * which_x + sidx)),
+                                            rows // self.tp, self.budget_ns, _p(status_word(self.device)), _stream()),
+                   "blitz_flag_wait")
+        _check(_L.lib().blitz_flags_zero(ctypes.c_void_p(self._flag_ptr(self.rank, 32 + 8 * which_x)), self.tp, _stream()),
+               "blitz_flags_zero")
+
+    def allreduce_oneshot(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        n = x.numel()
+        assert n * self.elem <= self.buf_bytes and x.is_contiguous()
+        slots = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + self.o_emb for r in range(self.tp)])
+        fl = (ctypes.c_void_p * self.tp)(*[self._flag_ptr(r, 48) for r in range(self.tp)])
+        rc = _L.lib().blitz_allreduce_oneshot(_p(x), slots, fl, _p(out), self.tp, self.rank, n, self.budget_ns,
+                                              _p(status_word(self.device)), 1 if self.dtype == torch.bfloat16 else 0, _stream())
+        _check(rc, "blitz_allreduce_oneshot")
+        return out
+
+
+class LlamaRunnerTP(LlamaRunner):
+    """Llama forward on one TP rank with the fused peer-memory path (no collective library in the layer loop)."""
+
+    def __init__(self, seg, kv_cache, max_tokens, max_batch, comm: TPComm, fused: FusedTP):
+        super().__init__(seg, kv_cache, max_tokens, max_batch, comm=comm)
+        self.fused = fused
+        self.res_shard = torch.empty(fused.max_rows // fused.tp, self.cfg.hidden, dtype=seg.dtype, device=self.res.device)
+        self._pad_ids = torch.zeros(fused.max_rows, dtype=torch.int32, device=self.res.device)
+
+    def _rows(self, m: StepMeta):
+        tp = self.fused.tp
+        Tp = (m.num_tokens + tp - 1) // tp * tp
+        return Tp, Tp // tp
+
+    def embed(self, m: StepMeta) -> None:
+        T = m.num_tokens
+        Tp, rpr = self._rows(m)
+        vs = self.cfg.vocab // self.tp
+        self._pad_ids[:Tp].zero_()
+        self._pad_ids[:T].copy_(m.ids[:T])
+        ops.embedding(self._pad_ids[:Tp], self.seg["embed"], self.tmp[:Tp], vocab_start=self.seg.tp_rank * vs,
+                      zero_missing=True)
+        self.fused.allreduce_oneshot(self.tmp[:Tp], self.res[:Tp])
+        r = self.fused.rank
+        self.res_shard[:rpr].copy_(self.res[r * rpr:(r + 1) * rpr])
+        # first layer's input norm: every rank has the full rows, no exchange needed
+        ops.rms_norm(self.res[:Tp], self._w(0, "input_ln"), self.cfg.rms_eps, out=self.fused.xg(0, Tp))
+        self._first = True
+
+    def attention_block(self, l: int, m: StepMeta) -> None:
+        T, c, f = m.num_tokens, self.cfg, self.fused
+        Tp, rpr = self._rows(m)
+        f.ag_gemm(0, Tp, self._w(l, "qkv"), self.qkv[:Tp], wait=not self._first)
+        self._first = False
+        ops.rope_kv_store(self.qkv[:T], m.pos[:T], m.slot[:T], self.kv[l], q_heads=self.qh, kv_heads=self.kvh,
+                          head_dim=self.hd, page_size=self.page_size, rope_theta=c.rope_theta)
+        if m.is_prefill:
+            ops.attn_prefill(self.qkv[:T], m.tok_indptr, m.seq_lens_host, q_heads=self.qh, kv_heads=self.kvh,
+                             head_dim=self.hd, out=self.attn[:T])
+        else:
+            ops.attn_decode(self.qkv[:T], self.kv[l], m.page_indices, m.page_indptr, m.last_page_len,
+                            q_heads=self.qh, kv_heads=self.kvh, head_dim=self.hd, page_size=self.page_size,
+                            num_splits=m.num_splits, workspace=self._workspace(m.batch, m.num_splits), out=self.attn[:T])
+        if Tp > T:
+            self.attn[T:Tp].zero_()
+        exp = f.gemm_rs(self.attn[:Tp], self._w(l, "o"), 0)
+        f.reduce_norm(0, exp, rpr, self.res_shard, self._w(l, "post_ln"), 1, c.rms_eps)
+
+    def ffn_block(self, l: int, m: StepMeta) -> None:
+        c, f = self.cfg, self.fused
+        Tp, rpr = self._rows(m)
+        f.ag_gemm(1, Tp, self._w(l, "gate_up"), self.act[:Tp], epilogue="silu_mul")
+        exp = f.gemm_rs(self.act[:Tp], self._w(l, "down"), 1)
+        nw = self._w(l + 1, "input_ln") if l + 1 < c.layers else self.seg["final_norm"]
+        f.reduce_norm(1, exp, rpr, self.res_shard, nw, 0, c.rms_eps)
+
+    def head(self, m: StepMeta) -> torch.Tensor:
+        B, T, c, f = m.batch, m.num_tokens, self.cfg, self.fused
+        Tp, _ = self._rows(m)
+        f.wait_gathered(0, Tp)     # final-norm rows of every rank are in gathered buffer 0
+        xn = f.xg(0, Tp)
+        if m.is_prefill:
+            ops.gather_last(xn[:T], m.tok_indptr, out=self.last[:B])
+            src = self.last[:B]
+        else:
+            src = xn[:B]
+        ops.gemm(src, self.seg["lm_head"], out=self.logits[:B])
+        vs = c.vocab // self.tp
+        ops.argmax(self.logits[:B], out=self.tokens[:B], out_val=self.maxval[:B], idx_offset=self.seg.tp_rank * vs)
+        vals = self.comm.all_gather(self.maxval[:B])
+        idxs = self.comm.all_gather(self.tokens[:B])
+        best = vals.argmax(0, keepdim=True)
+        self.tokens[:B].copy_(idxs.gather(0, best)[0])
+        return self.tokens[:B]

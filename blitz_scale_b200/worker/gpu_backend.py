@@ -1,0 +1,426 @@
+"""GPU worker backend: the engine plus the peer-memory data paths behind the RPC surface.
+
+One instance per process / GPU.  Counterpart of the reference's engine facade and managers
+(src/blitz/stub.h:68-1604, migration_manager.h, activation_manager.h, zigzag_manager.h,
+nccl_bcastor.h), with every inter-GPU transfer done by this GPU's own kernels over symmetric
+memory (`parallel/symm.py`) instead of RDMA / NCCL calls:
+
+* parameters: a source streams `embed | layer i | head` units into the destinations' weight
+  segments and bumps per-unit flags; a destination only polls its flag pad and marks units
+  ready in order, so it can serve layers as they land (live execution);
+* KV migration: `Immigrate` reserves pages on the decode GPU and publishes their ids in its
+  control region; `Migrate` on the prefill GPU waits for that, then stores the prompt pages
+  straight into the decode GPU's paged pool (all layers, or the first k / the remaining ones);
+* live execution: ZagPrefill tasks run layer by layer under the native scheduler; `Relay` ships the
+  residual stream of the head task into the old instance's mailbox slot, which continues from
+  that layer inside `PrefillV2(NAIVE_PP | IMMIGRATE)`.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from concurrent.futures import Future
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..models.config import get_config
+from ..models.llama import TPComm
+from ..models.weights import WeightSegment
+from ..parallel import symm
+from ..pb.schema import pb
+from ..runtime import core
+from ..runtime.engine import Engine
+from .service import Backend, make_generation
+
+CTL_SLOT_WORDS = 16384  # page ids one transfer slot can publish
+
+
+class GpuBackend(Backend):
+    def __init__(self, rank: int, world: int, model: str, *, tp: int = 1, num_pages: int = 2048, page_size: int = 64,
+                 max_batch: int = 256, max_batch_tokens: int = 8192, ready: bool = True, use_fabric: bool = True,
+                 tp_group=None, model_path: str = "", seed: int = 0, use_multimem: bool = False, copy_ctas: int = 64):
+        self.rank, self.world, self.tp = rank, world, tp
+        self.cfg = get_config(model)
+        self.model, self.model_path = model, model_path
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.lock = threading.RLock()
+        self.use_multimem, self.copy_ctas = use_multimem, copy_ctas
+        dt = torch.bfloat16
+        probe = WeightSegment(self.cfg, tp, rank % tp, dt, device="meta")
+        kvh = self.cfg.kv_heads // tp
+        self.page_bytes = 2 * page_size * kvh * self.cfg.head_dim * 2
+        self.kv_layer_stride = num_pages * self.page_bytes
+        kv_bytes = self.cfg.layers * self.kv_layer_stride
+        self.slot_bytes = max_batch_tokens * self.cfg.hidden * 2
+        self.fabric: Optional[symm.PeerFabric] = None
+        seg_buf = kv_buf = None
+        if use_fabric and world > 1:
+            self.fabric = symm.PeerFabric(symm.FabricSizes(weight_bytes=probe.layout.total_bytes, kv_bytes=kv_bytes,
+                                                           mailbox_slots=4, mailbox_slot_bytes=self.slot_bytes))
+            seg_buf, kv_buf = self.fabric.weights.local, self.fabric.kv.local
+            self.ctl = symm.SymmRegion(symm.KV_SLOTS * CTL_SLOT_WORDS * 4 + symm.KV_SLOTS * 4)
+            self.ctl.local.zero_()
+        comm = TPComm(tp_group) if tp > 1 else None
+        self.engine = Engine(self.cfg, num_pages=num_pages, page_size=page_size, max_batch=max_batch,
+                             max_batch_tokens=max_batch_tokens, tp=tp, tp_rank=rank % tp, dtype=dt, comm=comm,
+                             seg_buffer=seg_buf, kv_buffer=kv_buf, ready=ready, seed=seed)
+        self.units = [(n, o, b) for n, o, b in self.engine.seg.layout.units]
+        self.batches: Dict[int, "core.Batch"] = {}
+        self.param_expected = 0      # cumulative flag value that means "all stripes of the current transfer landed"
+        self.kv_slot_count = [0] * symm.KV_SLOTS
+        self.host_mirror: Optional[torch.Tensor] = None
+        # live execution
+        L = self.cfg.layers
+        self.zag = core.ZigzagScheduler(L, 4)
+        self.zag_tasks: Dict[int, dict] = {}
+        self.zag_slots = torch.empty(4, max_batch_tokens, self.cfg.hidden, dtype=dt, device=self.device)
+        self.zag_cv = threading.Condition(self.lock)
+        self._stop = False
+        self.zag_thread = threading.Thread(target=self._zag_loop, daemon=True)
+        self.zag_thread.start()
+        self.transfer_thread: Optional[threading.Thread] = None
+        torch.cuda.synchronize()
+
+    # ------------------------------------------------------------------ helpers
+    def info(self) -> dict:
+        return {"ready": self.engine.status.fully_loaded(), "dtype": "bfloat16", "device_type": "cuda",
+                "ranks": {"rank": self.rank, "world": self.world, "tp": self.tp}}
+
+    def _specs(self, batch) -> List["core.SeqSpec"]:
+        return [core.SeqSpec(r.id, list(r.input_tokens) or [1], r.stopping_parameters.max_new_tokens,
+                             r.stopping_parameters.ignore_eos_token, -1) for r in batch.requests]
+
+    def _cached(self, b):
+        ids = b.unfinished_ids()
+        return pb.CachedBatch(id=b.id, request_ids=ids, size=len(ids), max_tokens=b.max_tokens()) if ids else None
+
+    def _emit(self, b, toks):
+        return [make_generation(s.spec.id, t, f"<{t}>", None if s.finish < 0 else s.finish, len(s.generated))
+                for s, t in zip(b.seqs, toks)]
+
+    def _finish_step(self, b, toks):
+        gens = self._emit(b, toks)
+        b.filter(b.unfinished_ids())
+        if b.size:
+            self.batches[b.id] = b
+        else:
+            self.batches.pop(b.id, None)
+        return gens, (self._cached(b) if b.size else None)
+
+    # ------------------------------------------------------------------ inference
+    def prefill(self, batch, forward_case, pp_info, pipe_peer):
+        with self.lock:
+            if not self.engine.status.fully_loaded():
+                raise RuntimeError("model parameters are not loaded")
+            b = self.engine.new_batch(batch.id, self._specs(batch))
+            if b is None:
+                raise RuntimeError("out of KV pages")
+            if forward_case & pb.PREFILL_CASE_NAIVE_PP:
+                start = 0
+                if pp_info is not None and pp_info.WhichOneof("start_layer") == "tfm_layer":
+                    start = int(pp_info.tfm_layer)
+                toks = self._continue_relayed(b, start)
+            else:
+                toks = self.engine.prefill(b)
+            ops.check_status()
+            gens, cb = self._finish_step(b, toks)
+            return gens, cb, None
+
+    def _continue_relayed(self, b, start_layer: int) -> List[int]:
+        """Old-instance half of a relayed batch: take the residual stream from the mailbox and run layers [k, L)."""
+        eng = self.engine
+        T, P = b.fill_prefill(eng.host_np, eng.layout)
+        eng._h2d(eng.layout.page_indices + P)
+        m = eng._views(T, b.size, P, True, [len(s.spec.prompt) for s in b.seqs])
+        if start_layer > 0:
+            slot = b.id % 4
+            self.fabric.wait_flag(symm.MAILBOX_FLAG0 + slot, int(b.id) + 1, budget_ms=5000)
+            src = self.fabric.mailbox.local[slot * self.slot_bytes:(slot + 1) * self.slot_bytes]
+            eng.runner.res[:T].copy_(src.view(torch.bfloat16).view(-1, self.cfg.hidden)[:T])
+            toks = eng.runner.forward(m, lo=start_layer, with_embed=False)
+        else:
+            toks = eng.runner.forward(m)
+        out = eng._tokens_to_host(toks, b.size)
+        b.mark_prefilled()
+        b.append_tokens(out, False)
+        b.decode = True
+        return out
+
+    def decode(self, batches, last_iter_tokens):
+        with self.lock:
+            for i, cb in enumerate(batches):
+                ids = list(last_iter_tokens[i].ids) if i < len(last_iter_tokens) else []
+                bi = self.batches[cb.id]
+                if ids and len(ids) == bi.size and all(len(s.generated) == 0 for s in bi.seqs):
+                    bi.append_tokens(ids, False)
+            b = self.batches[batches[0].id]
+            for cb in batches[1:]:
+                b.extend(self.batches.pop(cb.id))
+            toks = self.engine.decode(b)
+            gens, cb = self._finish_step(b, toks)
+            return gens, cb
+
+    def clear_cache(self, batch_id):
+        with self.lock:
+            for i in ([batch_id] if batch_id is not None else list(self.batches)):
+                b = self.batches.pop(i, None)
+                if b is not None:
+                    b.clear()
+
+    def filter_batch(self, batch_id, request_ids):
+        with self.lock:
+            b = self.batches[batch_id]
+            b.filter(list(request_ids))
+            return pb.CachedBatch(id=b.id, request_ids=b.unfinished_ids(), size=b.size, max_tokens=b.max_tokens())
+
+    def warmup(self, req) -> int:
+        return self.engine.pool.total_pages * self.engine.page_size
+
+    # ------------------------------------------------------------------ live execution (ZigZag)
+    def zag_prefill(self, batch, forward_case, pp_info, zag_layers, zag_seq):
+        fut: Future = Future()
+        with self.lock:
+            b = self.engine.new_batch(batch.id, self._specs(batch))
+            if b is None:
+                raise RuntimeError("out of KV pages")
+            slot = self.zag.add_task(batch.id, zag_seq, b.num_prompt_tokens())
+            if slot < 0:
+                b.clear()
+                raise RuntimeError("no activation slot free")
+            self.zag_tasks[batch.id] = {"batch": b, "future": fut, "slot": slot, "meta": None}
+            self.zag_cv.notify_all()
+        return fut.result(timeout=120)
+
+    def _zag_loop(self) -> None:
+        torch.cuda.set_device(self.device)
+        while not self._stop:
+            with self.lock:
+                st = self.engine.status
+                self.zag.set_loaded(st.embed_ready, st.layers_ready, st.head_ready)
+                d = self.zag.next()
+                if d.step in (core.ZagStep.Idle, core.ZagStep.Blocked):
+                    self.zag_cv.wait(0.0005)
+                    continue
+                task = self.zag_tasks[d.batch_id]
+                eng, b = self.engine, task["batch"]
+                if task["meta"] is None:
+                    T, P = b.fill_prefill(eng.host_np, eng.layout)
+                    eng._h2d(eng.layout.page_indices + P)
+                    # the staging arrays are shared: keep a private device copy of this task's inputs
+                    dev_copy = eng.dev[:eng.layout.page_indices + P].clone()
+                    task["meta"] = (T, P, dev_copy)
+                T, P, dev_copy = task["meta"]
+                eng.dev[:dev_copy.numel()].copy_(dev_copy)
+                m = eng._views(T, b.size, P, True, [len(s.spec.prompt) for s in b.seqs])
+                saved = eng.runner.res
+                eng.runner.res = self.zag_slots[task["slot"]]
+                try:
+                    if d.step == core.ZagStep.Embed:
+                        eng.runner.embed(m)
+                    elif d.step == core.ZagStep.Layer:
+                        eng.runner.run_layer(d.layer, m)
+                    else:
+                        toks = eng._tokens_to_host(eng.runner.head(m), b.size)
+                    torch.cuda.current_stream().synchronize()
+                finally:
+                    eng.runner.res = saved
+                done = self.zag.complete(d)
+                if done:
+                    b.mark_prefilled()
+                    b.append_tokens(toks, False)
+                    b.decode = True
+                    gens, cb = self._finish_step(b, toks)
+                    self.zag_tasks.pop(d.batch_id)["future"].set_result((gens, cb, None))
+
+    def relay(self, rank, relax_not_head):
+        with self.lock:
+            r = self.zag.relay(bool(relax_not_head))
+            if r is None:
+                return None
+            task = self.zag_tasks.pop(r.batch_id)
+            b = task["batch"]
+            k = max(0, r.next_layer)
+            if k > 0:
+                # ship the residual stream [T, hidden] into the old instance's mailbox slot and flag it
+                T = r.num_tokens
+                nbytes = T * self.cfg.hidden * 2
+                nbytes = (nbytes + 15) // 16 * 16
+                slot = r.batch_id % 4
+                stage = self.fabric.mailbox.local[slot * self.slot_bytes:slot * self.slot_bytes + nbytes]
+                stage.copy_(self.zag_slots[task["slot"]].view(torch.uint8).view(-1)[:nbytes])
+                self.fabric.copy_units(self.fabric.mailbox, [rank], [slot * self.slot_bytes], [nbytes],
+                                       symm.MAILBOX_FLAG0 + slot, num_ctas=16)
+                # the flag is a counter; publish the batch tag on top so the reader can wait for ">= id + 1"
+                self.fabric.set_flag(rank, symm.MAILBOX_FLAG0 + slot, int(r.batch_id) + 1, add=False)
+                torch.cuda.current_stream().synchronize()
+            self.zag.release_slot(task["slot"])
+            pp = pb.PipeParaInfo()
+            if r.next_layer <= 0:
+                pp.embedding_layer = 1
+            else:
+                pp.tfm_layer = k
+            # layers [0, k) of this batch's KV stay here until MigratePartial(FIRST) moves them
+            b.mark_prefilled()
+            self.batches[b.id] = b
+            cb = pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+            task["future"].set_result(([], cb, pp))
+            return r.batch_id, r.seq_num
+
+    # ------------------------------------------------------------------ KV migration
+    def _layer_range(self, partial, num_layer):
+        L = self.cfg.layers
+        if partial == pb.PARTIAL_CASE_FIRST:
+            return 0, min(num_layer, L)
+        if partial == pb.PARTIAL_CASE_SECOND:
+            return min(num_layer, L), L
+        return 0, L
+
+    def immigrate(self, batch, src, dst, partial=0, num_layer=0):
+        with self.lock:
+            slot = batch.id % symm.KV_SLOTS
+            b = self.batches.get(batch.id)
+            if b is None:
+                b = self.engine.new_batch(batch.id, self._specs(batch))
+                if b is None:
+                    raise RuntimeError("out of KV pages")
+                b.mark_prefilled()
+                b.decode = True
+                self.batches[batch.id] = b
+            lo, hi = self._layer_range(partial, num_layer)
+            if hi > lo and self.fabric is not None:
+                # publish the destination page ids of the prompt pages, then wait for the layers to land
+                ps = self.engine.page_size
+                ids = [p for s in b.seqs for p in s.pages[:(len(s.spec.prompt) + ps - 1) // ps]]
+                words = self.ctl.local.view(torch.int32)
+                words[slot * CTL_SLOT_WORDS:slot * CTL_SLOT_WORDS + len(ids)].copy_(
+                    torch.tensor(ids, dtype=torch.int32), non_blocking=False)
+                tag_index = symm.KV_SLOTS * CTL_SLOT_WORDS + slot
+                self._ctl_set(self.rank, tag_index, int(batch.id) + 1)
+                want = self._kv_want(slot, lo, hi)
+                for l in (hi - 1,):
+                    self.fabric.wait_flag(symm.KV_FLAG0 + slot * symm.MAX_LAYERS + l, want[l], budget_ms=10000)
+                torch.cuda.current_stream().synchronize()
+                ops.check_status()
+            return pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+
+    def _kv_want(self, slot, lo, hi):
+        if not hasattr(self, "_kv_layer_count"):
+            self._kv_layer_count = [[0] * symm.MAX_LAYERS for _ in range(symm.KV_SLOTS)]
+        for l in range(lo, hi):
+            self._kv_layer_count[slot][l] += 1
+        return self._kv_layer_count[slot]
+
+    def _ctl_set(self, rank, word_index, value):
+        import ctypes
+        ptr = self.ctl.ptrs[rank] + word_index * 4
+        symm._check(symm._L.lib().blitz_flag_set(ctypes.c_void_p(ptr), value, 0, symm._stream()), "blitz_flag_set")
+
+    def migrate(self, batch, src, dst, partial=0, num_layer=0):
+        with self.lock:
+            b = self.batches.get(batch.id)
+            if b is None:
+                raise KeyError(f"batch {batch.id} not cached on rank {self.rank}")
+            lo, hi = self._layer_range(partial, num_layer)
+            my = src.index(self.rank) if self.rank in src else self.rank % self.tp
+            peer = dst[my]
+            slot = batch.id % symm.KV_SLOTS
+            if hi > lo:
+                import ctypes
+                ps = self.engine.page_size
+                src_ids = [p for s in b.seqs for p in s.pages[:(len(s.spec.prompt) + ps - 1) // ps]]
+                src_pages = torch.tensor(src_ids, dtype=torch.int32, device=self.device)
+                # wait until the destination has published its page ids for this batch
+                tag_ptr = self.ctl.ptrs[peer] + (symm.KV_SLOTS * CTL_SLOT_WORDS + slot) * 4
+                symm._check(symm._L.lib().blitz_flag_wait(ctypes.c_void_p(tag_ptr), int(batch.id) + 1, int(10e9),
+                                                          ctypes.c_void_p(ops.status_word().data_ptr()), symm._stream()),
+                            "blitz_flag_wait")
+                dst_pages_ptr = self.ctl.ptrs[peer] + slot * CTL_SLOT_WORDS * 4
+                nl = hi - lo
+                tick = self.fabric.tickets[1024:1024 + nl]
+                tick.zero_()
+                flags = self.fabric.flags.ptrs[peer] + (symm.KV_FLAG0 + slot * symm.MAX_LAYERS) * 4
+                rc = symm._L.lib().blitz_kv_push(
+                    ctypes.c_void_p(self.fabric.kv.ptrs[self.rank]), ctypes.c_void_p(self.fabric.kv.ptrs[peer]),
+                    ctypes.c_void_p(src_pages.data_ptr()), ctypes.c_void_p(dst_pages_ptr), len(src_ids), lo, hi,
+                    self.page_bytes, self.kv_layer_stride, self.kv_layer_stride, self.engine.num_pages,
+                    self.engine.num_pages, ctypes.c_void_p(flags), ctypes.c_void_p(tick.data_ptr()), 0,
+                    ctypes.c_void_p(ops.status_word().data_ptr()), symm._stream())
+                symm._check(rc, "blitz_kv_push")
+                torch.cuda.current_stream().synchronize()
+                ops.check_status()
+            cb = pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+            self.batches.pop(batch.id, None)
+            b.clear()
+            return cb
+
+    # ------------------------------------------------------------------ parameters
+    def _shard_peers(self, ranks):
+        t = self.rank % self.tp
+        return [r for r in ranks if r % self.tp == t]
+
+    def broadcast(self, kind, src_ranks, dst_ranks):
+        sources, dests = self._shard_peers(src_ranks), self._shard_peers(dst_ranks)
+        if self.rank in sources:
+            offs = [o for _, o, _ in self.units]
+            lens = [(b + 15) // 16 * 16 for _, _, b in self.units]
+            self.fabric.copy_units(self.fabric.weights, dests, offs, lens, symm.PARAM_FLAG0, stripe=sources.index(self.rank),
+                                   n_stripes=len(sources), use_multimem=self.use_multimem, num_ctas=self.copy_ctas)
+            torch.cuda.current_stream().synchronize()
+        elif self.rank in dests:
+            self._receive_params(len(sources))
+
+    def _receive_params(self, n_stripes: int, timeout_s: float = 120.0) -> None:
+        """Poll this GPU's own flag pad and mark units ready in arrival order."""
+        with self.lock:
+            self.engine.status.reset()
+            base = self.param_expected
+            self.param_expected += n_stripes
+        want, n_units, nxt = base + n_stripes, len(self.units), 0
+        t0 = time.monotonic()
+        side = torch.cuda.Stream(device=self.device)
+        while nxt < n_units:
+            with torch.cuda.stream(side):
+                flags = self.fabric.read_flags(symm.PARAM_FLAG0, n_units)
+            while nxt < n_units and flags[nxt] >= want:
+                with self.lock:
+                    self.engine.status.unit_arrived(nxt)
+                    self.zag_cv.notify_all()
+                nxt += 1
+            if nxt < n_units:
+                if time.monotonic() - t0 > timeout_s:
+                    raise RuntimeError(f"parameter transfer stalled at unit {nxt}")
+                time.sleep(0.0002)
+
+    def send_params(self, dst):
+        self.broadcast("p2p", [self.rank], [dst])
+
+    def recv_params(self, src):
+        self.transfer_thread = threading.Thread(target=self._receive_params, args=(1,), daemon=True)
+        self.transfer_thread.start()
+
+    def wait_transfer_done(self):
+        if self.transfer_thread is not None:
+            self.transfer_thread.join()
+            self.transfer_thread = None
+
+    def load_params(self, load_case, model_name, model_path):
+        path = model_path or self.model_path
+        with self.lock:
+            if load_case == pb.LOAD_FROM_HOST_MEM and self.host_mirror is not None:
+                self.engine.load_params_from_host(self.host_mirror)
+            else:
+                res = self.engine.load_params_from_disk(path, self.host_mirror)
+                self.host_mirror = res["host_mirror"]
+
+    def reset_status(self):
+        with self.lock:
+            self.engine.reset_status()
+
+    def set_status_ready(self):
+        with self.lock:
+            self.engine.set_status_ready()
+
+    def close(self):
+        self._stop = True

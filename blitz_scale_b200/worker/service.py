@@ -50,7 +50,7 @@ class TextGenerationService:
     def __init__(self, backend: Backend, urls=None):
         self.b = backend
         self.urls = list(urls or [])
-        self.pool = ThreadPoolExecutor(max_workers=4, thread_name_prefix=f"worker{backend.rank}")
+        self.pool = ThreadPoolExecutor(max_workers=32, thread_name_prefix=f"worker{backend.rank}")
         self._zag_next = 0
         self._zag_cv = asyncio.Condition()
 

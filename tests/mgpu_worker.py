@@ -126,6 +126,76 @@ def main():
             assert float(torch.ones(8, device="cuda").sum()) == 8.0
         torch.cuda.synchronize()
         dist.barrier()
+    elif case == "tp_fused":
+        # TP forward with the fused GEMM->reduce-scatter / all-gather->GEMM path vs the unsharded fp32 oracle and
+        # vs the NCCL all-reduce version of the same forward
+        from blitz_scale_b200.models.config import get_config
+        from blitz_scale_b200.models.llama import LlamaRunner, TPComm
+        from blitz_scale_b200.models.oracle import LlamaOracle
+        from blitz_scale_b200.models.weights import WeightSegment, shard_from_full
+        from blitz_scale_b200.parallel.tp import FusedTP, LlamaRunnerTP
+        from blitz_scale_b200.runtime.meta import MetaBuilder
+        cfg = get_config("tiny_gpu")
+        tp = world
+        full = WeightSegment(cfg, dtype=torch.bfloat16, device="cuda").random_init_(seed=5)
+        seg = shard_from_full(full, tp, rank)
+        page, max_pages = 16, 64
+        kvshape = (cfg.layers, max_pages, 2, page, cfg.kv_heads // tp, cfg.head_dim)
+        comm = TPComm(dist.group.WORLD)
+        fused = FusedTP(dist.group.WORLD, cfg.hidden, 1024)
+        r_fused = LlamaRunnerTP(seg, torch.zeros(kvshape, dtype=torch.bfloat16, device="cuda"), 1024, 16, comm, fused)
+        r_nccl = LlamaRunner(seg, torch.zeros(kvshape, dtype=torch.bfloat16, device="cuda"), 1024, 16, comm=comm)
+        mb = MetaBuilder(1024, 16, max_pages, page)
+        g = torch.Generator().manual_seed(3)
+        lens = [5, 131, 77]
+        prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in lens]
+        new = 4
+        tables, nxt = [], 1
+        for n in lens:
+            need = (n + new) // page + 1
+            tables.append(list(range(nxt, nxt + need)))
+            nxt += need
+        oracle = LlamaOracle(full, compute_dtype=torch.float32)
+        ref_tokens, ref_logits = oracle.generate(prompts, new, return_logits=True)
+
+        def full_logits(runner):
+            parts = comm.all_gather(runner.logits[:3].contiguous())      # [tp, B, vocab/tp]
+            return torch.cat([parts[i] for i in range(tp)], dim=1).float().cpu()
+
+        for name, runner in (("fused", r_fused), ("nccl", r_nccl)):
+            seq = list(lens)
+            for step in range(new):
+                if step == 0:
+                    m = mb.prefill(prompts, tables)
+                else:
+                    m = mb.decode([ref_tokens[b][step - 1] for b in range(3)], seq, tables)
+                toks = runner.forward(m).tolist()
+                torch.cuda.synchronize()
+                ops.check_status()
+                lg = full_logits(runner)
+                for b in range(3):
+                    r = ref_logits[b][step]
+                    err = float((lg[b] - r).norm() / r.norm())
+                    assert err < 3e-2, (name, b, step, err)
+                    if toks[b] != ref_tokens[b][step]:
+                        assert float(r.max() - r[toks[b]]) < 0.05 * float(r.abs().max()), (name, b, step)
+                if step > 0:
+                    seq = [n + 1 for n in seq]
+        # the fused path must also replay from a CUDA graph (flags are re-armed by their consumers)
+        m = mb.decode([ref_tokens[b][new - 1] for b in range(3)], [n + new - 1 for n in lens], tables, pad_to=4)
+        r_fused.forward(m)
+        torch.cuda.synchronize()
+        gph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gph):
+            r_fused.forward(m)
+        first = None
+        for _ in range(3):
+            gph.replay()
+            torch.cuda.synchronize()
+            ops.check_status()
+            cur = r_fused.tokens[:3].clone()
+            first = cur if first is None else first
+            assert torch.equal(cur, first)
     else:
         raise SystemExit(f"unknown case {case}")
     torch.cuda.synchronize()

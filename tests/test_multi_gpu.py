@@ -24,7 +24,7 @@ def _run(case, nproc, extra_env=None):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
-@pytest.mark.parametrize("case", ["multicast", "multicast_multimem", "kv_push", "mailbox_and_timeout"])
+@pytest.mark.parametrize("case", ["multicast", "multicast_multimem", "kv_push", "mailbox_and_timeout", "tp_fused"])
 def test_peer_kernels(case):
     n = min(_ngpu(), 4) if case.startswith("multicast") else 2
     out = _run(case, n)
