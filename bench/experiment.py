@@ -1,0 +1,194 @@
+"""Experiment runner: template TOML -> instance runs -> client.jsonl + SLO summary, with resume.
+
+The counterpart of the reference's batch job runner (scripts/batch/main.py:62-252, parser.py:24-114,
+runner.py:124-790): a *template* lists models, datasets, feature sets and router options; every list-valued
+`[router]` key fans out, the cartesian product over models x datasets x features x router options gives the
+*instances*; each instance writes `config-server.json` (cluster layout), `config-router.json`,
+`config-stubs.json`, starts workers (GPU workers under torch.distributed.run, or GPU-less stub workers),
+the router and the trace client, waits, tears down, summarises (`summary.json`) and appends its path to
+`checkpoint.txt` so `--checkpoint` skips finished instances.  `--dry-run` only writes the configs and the
+command lines.
+
+    python bench/experiment.py --template bench/templates/cpu_plumbing.toml --out runs/ [--dry-run] [--force]
+"""
+from __future__ import annotations
+
+import argparse
+import itertools
+import json
+import os
+import shlex
+import signal
+import subprocess
+import sys
+import time
+import tomllib
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+def expand(template: dict) -> list:
+    """Cartesian product over models, datasets, feature sets and list-valued router keys."""
+    router = template.get("router", {})
+    fan_keys = [k for k, v in router.items() if isinstance(v, list)]
+    fan_vals = [router[k] for k in fan_keys]
+    models = template.get("models", {"default": {}})
+    datasets = template.get("datasets", {"default": {}})
+    features = template.get("features", {}).get("sets", ["impl_blitz,impl_fast_pro,impl_live_pro"])
+    out = []
+    for (mname, m), (dname, d), feat in itertools.product(models.items(), datasets.items(), features):
+        for combo in itertools.product(*fan_vals) if fan_vals else [()]:
+            r = dict(router)
+            r.update(dict(zip(fan_keys, combo)))
+            tag = "-".join([mname, dname, feat.replace(",", "+")] + [f"{k}={v}" for k, v in zip(fan_keys, combo)])
+            out.append({"tag": tag, "model": dict(m, name=mname), "dataset": dict(d, name=dname), "features": feat,
+                        "router": r, "global": template.get("global", {}), "server": template.get("server", {}),
+                        "envs": template.get("extra-envs", {})})
+    return out
+
+
+def cluster_json(inst: dict) -> dict:
+    g = inst["global"]
+    n, tp = int(g.get("num_gpus", 2)), int(inst["model"].get("tp", 1))
+    states = list(g.get("init_states", ["Prefill", "Decode"] + ["Inactive"] * (n // tp - 2)))
+    per_rank = [s for s in states for _ in range(tp)]
+    return {"init_states": per_rank, "replicas": [list(range(r * tp, (r + 1) * tp)) for r in range(n // tp)],
+            "machines": [0] * n}
+
+
+def commands(inst: dict, d: Path) -> dict:
+    g, m, r, ds = inst["global"], inst["model"], inst["router"], inst["dataset"]
+    n, tp = int(g.get("num_gpus", 2)), int(m.get("tp", 1))
+    base = int(g.get("worker_port", 50051))
+    urls = [f"127.0.0.1:{base + i}" for i in range(n)]
+    (d / "config-stubs.json").write_text(json.dumps(urls))
+    py = sys.executable
+    if g.get("stub_workers", False):
+        workers = [f"{py} -m blitz_scale_b200.sim.stub_worker --rank {i} --world {n} --port {base + i} "
+                   f"--config {d / 'config-server.json'} --seed {g.get('seed', 0)} --layers {m.get('layers', 2)}" for i in range(n)]
+    else:
+        workers = [f"{py} -m torch.distributed.run --nnodes=1 --nproc-per-node {n} --master-addr 127.0.0.1 "
+                   f"--master-port {g.get('master_port', 29600)} -m blitz_scale_b200.worker.launcher --model-name {m['name']} "
+                   f"--config {d / 'config-server.json'} --port {base} -TP {tp} "
+                   f"--num-total-blocks {m.get('num_available_blocks', 4096)} --log-dir {d / 'worker-logs'}"]
+    router_args = {
+        "--port": r.get("port", 3000), "--client-config": str(d / "config-stubs.json"),
+        "--deployment-config-path": str(d / "config-server.json"), "--features": inst["features"],
+        "--tensor-parallel-size": tp, "--model-name": m["name"],
+        "--max-blocks-per-replica": m.get("num_available_blocks", 4096),
+        "--tokens-prefilled-per-sec": m.get("tokens_prefilled_per_sec", 15000),
+        "--tokens-transferred-per-sec": m.get("tokens_transferred_per_sec", 96000),
+    }
+    for k in ("prefill-lower-bound", "prefill-upper-bound", "decode-lower-bound", "decode-upper-bound",
+              "migration-lower-bound", "migration-upper-bound", "min-prefill-num", "max-prefill-num", "min-decode-num",
+              "max-decode-num", "scale-down-threshold-millis", "mock-load-millis", "max-input-length", "max-total-tokens"):
+        kk = k.replace("-", "_")
+        if kk in r:
+            router_args["--" + k] = r[kk]
+    (d / "config-router.json").write_text(json.dumps(router_args, indent=1))
+    router = f"{py} -m blitz_scale_b200.router.server " + " ".join(f"{k} {shlex.quote(str(v))}" for k, v in router_args.items())
+    client = (f"{py} -m blitz_scale_b200.sim.request_sim --endpoint http://127.0.0.1:{r.get('port', 3000)}/generate --protocol st "
+              f"--replay-mode --scale-factor {ds.get('scale_factor', 1.0)} --output-path {d / 'client.jsonl'} ")
+    if ds.get("path"):
+        client += f"--dataset-type csv --dataset-path {ds['path']} --time-in-secs {ds.get('time_in_secs', 60)}"
+    else:
+        client += (f"--dataset-type mock --rate {ds.get('rate', 4.0)} --cv {ds.get('cv', 1.0)} --duration {ds.get('duration', 50)} "
+                   f"--num-requests {ds.get('num_requests', 200)} --seed {ds.get('seed', 0)}")
+    return {"workers": workers, "router": router, "client": client}
+
+
+def wait_for(path: Path, needle: str, count: int, timeout: float) -> bool:
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        if path.exists() and path.read_text(errors="ignore").count(needle) >= count:
+            return True
+        time.sleep(0.2)
+    return False
+
+
+def run_instance(inst: dict, d: Path, dry: bool) -> dict:
+    d.mkdir(parents=True, exist_ok=True)
+    (d / "config-server.json").write_text(json.dumps(cluster_json(inst)))
+    cmds = commands(inst, d)
+    (d / "commands.json").write_text(json.dumps(cmds, indent=1))
+    if dry:
+        return {"tag": inst["tag"], "dry_run": True}
+    env = dict(os.environ, PYTHONPATH=str(ROOT), **{k: str(v) for k, v in inst["envs"].items()})
+    procs, logs = [], []
+    try:
+        wl = open(d / "workers.log", "w")
+        logs.append(wl)
+        for c in cmds["workers"]:
+            procs.append(subprocess.Popen(shlex.split(c), stdout=wl, stderr=subprocess.STDOUT, env=env, start_new_session=True))
+        n = int(inst["global"].get("num_gpus", 2))
+        if not wait_for(d / "workers.log", "Start gRPC server", n, float(inst["global"].get("boot_timeout", 600))):
+            raise RuntimeError("workers did not start")
+        rl = open(d / "router.log", "w")
+        logs.append(rl)
+        procs.append(subprocess.Popen(shlex.split(cmds["router"]), stdout=rl, stderr=subprocess.STDOUT, env=env, start_new_session=True))
+        if not wait_for(d / "router.log", "Router listening", 1, 60):
+            raise RuntimeError("router did not start")
+        cl = open(d / "client.log", "w")
+        logs.append(cl)
+        rc = subprocess.call(shlex.split(cmds["client"]), stdout=cl, stderr=subprocess.STDOUT, env=env,
+                             timeout=float(inst["global"].get("client_timeout", 3600)))
+        if rc != 0:
+            raise RuntimeError(f"client exited with {rc}")
+    finally:
+        for p in reversed(procs):
+            try:
+                os.killpg(p.pid, signal.SIGTERM)   # the exact process groups started above
+            except ProcessLookupError:
+                pass
+        for p in procs:
+            try:
+                p.wait(timeout=20)
+            except subprocess.TimeoutExpired:
+                os.killpg(p.pid, signal.SIGKILL)
+        for f in logs:
+            f.close()
+    from blitz_scale_b200.utils import analysis
+    recs = analysis.load_jsonl(str(d / "client.jsonl"))
+    log = analysis.parse_router_log(open(d / "router.log", errors="ignore"))
+    summary = {"tag": inst["tag"], "slo": analysis.slo_table(recs), "scale_out": analysis.scale_out_latencies(log["transitions"]),
+               "transitions": len(log["transitions"])}
+    (d / "summary.json").write_text(json.dumps(summary, indent=1))
+    return summary
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--template", "--templates", required=True)
+    ap.add_argument("--out", default="runs")
+    ap.add_argument("--dry-run", action="store_true")
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--checkpoint", default="")
+    a = ap.parse_args()
+    tpl = tomllib.load(open(a.template, "rb"))
+    out = Path(a.out)
+    out.mkdir(parents=True, exist_ok=True)
+    ck = Path(a.checkpoint) if a.checkpoint else out / "checkpoint.txt"
+    if a.force and ck.exists():
+        ck.unlink()
+    done = set(ck.read_text().split()) if ck.exists() else set()
+    results = []
+    for inst in expand(tpl):
+        d = out / inst["tag"]
+        if str(d) in done:
+            continue
+        try:
+            results.append(run_instance(inst, d, a.dry_run))
+            if not a.dry_run:
+                with open(ck, "a") as f:
+                    f.write(str(d) + "\n")
+        except Exception as e:  # noqa: BLE001
+            with open(out / "error.log", "a") as f:
+                f.write(f"{inst['tag']}: {e}\n")
+            results.append({"tag": inst["tag"], "error": str(e)})
+    print(json.dumps(results, indent=1))
+
+
+if __name__ == "__main__":
+    main()

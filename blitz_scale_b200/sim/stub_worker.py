@@ -276,3 +276,39 @@ class StubBackend(Backend):
 
     def warmup(self, req) -> int:
         return self.pool.total_pages * self.pool.page_size
+
+
+def main(argv=None) -> None:
+    """`python -m blitz_scale_b200.sim.stub_worker --rank R --world N --port P --config cluster.json`"""
+    import argparse
+    import asyncio
+    import json
+    import signal
+
+    from ..worker.service import serve
+    ap = argparse.ArgumentParser("blitz-stub-worker")
+    ap.add_argument("--rank", type=int, default=0)
+    ap.add_argument("--world", type=int, default=1)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, required=True)
+    ap.add_argument("--config", default="")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--load-seconds", type=float, default=0.2)
+    a = ap.parse_args(argv)
+    ready = True
+    if a.config:
+        ready = json.load(open(a.config))["init_states"][a.rank] != "Inactive"
+    backend = StubBackend(a.rank, a.world, seed=a.seed, layers=a.layers, ready=ready, load_s=a.load_seconds)
+
+    async def run():
+        stop = asyncio.Event()
+        loop = asyncio.get_running_loop()
+        for sig in (signal.SIGINT, signal.SIGTERM):
+            loop.add_signal_handler(sig, stop.set)
+        await serve(backend, a.host, a.port, stop_event=stop)
+    asyncio.run(run())
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,99 @@
+"""Log analytics and sizing helpers (text only, no plotting library needed).
+
+* `parse_router_log`: state transitions (`Replica<i> A => B`), control signals, `System Metrics` token lines and
+  the `>>= unload` marker, the grep-able protocol the reference's tools rely on (scripts/batch/utils.py:387-502,
+  scripts/debug/awesome_grep.py:6-13).
+* `replica_timeline`: per-replica state intervals (the data behind the reference's stacked GPU-usage chart,
+  scripts/debug/pipe_gpu_usage.py).
+* `slo_table`: TTFT / TBT violation rates with the reference's thresholds (TTFT > max(300 ms, 0.375 ms x input
+  length), max-TBT bar 100 ms; scripts/batch/plot.py:8-12,116-119).
+* `kv_sizing`: KV bytes per token / per block, blocks that fit in a memory budget, tokens/s a link sustains
+  (scripts/util/calculate_hyper_params.py:61-87), with B200 defaults.
+"""
+from __future__ import annotations
+
+import json
+import re
+from typing import Dict, Iterable, List, Tuple
+
+from ..models.config import get_config
+
+_TRANS = re.compile(r"Replica<(\d+)> (\w+) => (\w+)")
+_METRIC = re.compile(r"System Metrics: prefill_tokens: (\d+), decode_tokens: (\d+)")
+_SIGNAL = re.compile(r"Control signal: P([+-]\d+) D([+-]\d+)")
+_STAMP = re.compile(r"^\[?(\d+\.\d+)\]?")
+
+
+def parse_router_log(lines: Iterable[str]) -> dict:
+    out = {"transitions": [], "signals": [], "metrics": [], "unloads": [], "client_start": None}
+    for ln in lines:
+        m = _STAMP.match(ln.strip())
+        t = float(m.group(1)) if m else None
+        tr = _TRANS.search(ln)
+        if tr:
+            out["transitions"].append((t, int(tr.group(1)), tr.group(2), tr.group(3)))
+        sg = _SIGNAL.search(ln)
+        if sg:
+            out["signals"].append((t, int(sg.group(1)), int(sg.group(2))))
+        me = _METRIC.search(ln)
+        if me:
+            out["metrics"].append((t, int(me.group(1)), int(me.group(2))))
+        if ">>= unload" in ln:
+            out["unloads"].append(t)
+        if "Client start" in ln and out["client_start"] is None:
+            out["client_start"] = t
+    return out
+
+
+def replica_timeline(transitions: List[Tuple[float, int, str, str]], t_end: float) -> Dict[int, List[Tuple[float, float, str]]]:
+    cur: Dict[int, Tuple[float, str]] = {}
+    spans: Dict[int, List[Tuple[float, float, str]]] = {}
+    for t, r, _a, b in transitions:
+        t = 0.0 if t is None else t
+        if r in cur:
+            spans.setdefault(r, []).append((cur[r][0], t, cur[r][1]))
+        cur[r] = (t, b)
+    for r, (t0, s) in cur.items():
+        spans.setdefault(r, []).append((t0, t_end, s))
+    return spans
+
+
+def scale_out_latencies(transitions) -> List[Tuple[int, float]]:
+    """(replica, seconds) from leaving Inactive to reaching Prefill or Decode."""
+    start, out = {}, []
+    for t, r, a, b in transitions:
+        if a == "Inactive":
+            start[r] = t
+        if b in ("Prefill", "Decode") and r in start and t is not None and start[r] is not None:
+            out.append((r, t - start.pop(r)))
+    return out
+
+
+def slo_table(records: Iterable[dict]) -> dict:
+    ok = [r for r in records if r.get("status") == "ok"]
+    n = max(1, len(ok))
+    pct = lambda xs, q: sorted(xs)[min(len(xs) - 1, int(q * len(xs)))] if xs else 0.0
+    ttft = [r["first_token_time"] for r in ok]
+    tbt = [r["max_time_between_tokens"] for r in ok]
+    return {
+        "requests": len(ok),
+        "ttft_ms": {"p50": pct(ttft, .5), "p90": pct(ttft, .9), "p99": pct(ttft, .99)},
+        "max_tbt_ms": {"p50": pct(tbt, .5), "p90": pct(tbt, .9), "p99": pct(tbt, .99)},
+        "ttft_violation_rate": sum(1 for r in ok if r["first_token_time"] > max(300.0, 0.375 * r["input_length"])) / n,
+        "tbt_violation_rate": sum(1 for x in tbt if x > 100.0) / n,
+    }
+
+
+def load_jsonl(path: str) -> List[dict]:
+    return [json.loads(l) for l in open(path) if l.strip()]
+
+
+def kv_sizing(model: str, tp: int = 1, page_size: int = 64, mem_budget_gb: float = 150.0, link_gbs: float = 770.0,
+              elem_bytes: int = 2) -> dict:
+    c = get_config(model)
+    per_token = c.kv_bytes_per_token(tp, elem_bytes)
+    block = per_token * page_size
+    weights_gb = c.param_gb / tp
+    free = max(0.0, mem_budget_gb - weights_gb) * 1e9
+    return {"kv_bytes_per_token": per_token, "block_bytes": block, "blocks_in_budget": int(free // block),
+            "tokens_in_budget": int(free // per_token), "tokens_per_sec_at_link": link_gbs * 1e9 / per_token}

@@ -6,6 +6,7 @@ right number of tokens, token streams are identical across two runs with the sam
 visible in the transition log, /metrics and the timing headers are present, a worker that dies is detected.
 """
 import asyncio
+import os
 import json
 import socket
 
@@ -198,3 +199,45 @@ def test_direct_rpcs_against_stub_worker():
         stop.set()
         await asyncio.wait([t], timeout=5)
     asyncio.run(go())
+
+
+def test_experiment_runner_expansion_and_dry_run(tmp_path):
+    import subprocess
+    import sys
+    import tomllib
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench"))
+    import experiment
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tpl = tomllib.load(open(os.path.join(root, "bench/templates/llama3_8b_pd.toml"), "rb"))
+    inst = experiment.expand(tpl)
+    assert len(inst) == 3 * 2     # three feature sets x two scale-down thresholds
+    assert {i["router"]["scale_down_threshold_millis"] for i in inst} == {333, 1500}
+    cj = experiment.cluster_json(inst[0])
+    assert cj["init_states"] == ["Prefill", "Decode", "Inactive", "Inactive"] and cj["replicas"] == [[0], [1], [2], [3]]
+    res = subprocess.run([sys.executable, os.path.join(root, "bench/experiment.py"), "--template",
+                          os.path.join(root, "bench/templates/cpu_plumbing.toml"), "--out", str(tmp_path), "--dry-run"],
+                         capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0, res.stderr[-2000:]
+    d = next(p for p in tmp_path.iterdir() if p.is_dir())
+    cmds = json.load(open(d / "commands.json"))
+    assert len(cmds["workers"]) == 2 and "request_sim" in cmds["client"] and "--features" in cmds["router"]
+    assert json.load(open(d / "config-server.json"))["init_states"] == ["Normal", "Inactive"]
+
+
+def test_log_analysis_and_sizing():
+    from blitz_scale_b200.utils import analysis
+    log = ["[0.000000] Replica<0> boot => Prefill", "[1.5] Replica<2> Inactive => LoadingPrefill",
+           "[1.9] Replica<2> LoadingPrefill => Prefill", "[2.0] Control signal: P+1 D+0 | x",
+           "[3.0] System Metrics: prefill_tokens: 100, decode_tokens: 7", "[4.0] Replica<2> >>= unload", "Client start"]
+    p = analysis.parse_router_log(log)
+    assert p["transitions"][1] == (1.5, 2, "Inactive", "LoadingPrefill") and p["signals"] == [(2.0, 1, 0)]
+    assert p["metrics"] == [(3.0, 100, 7)] and p["unloads"] == [4.0]
+    assert analysis.scale_out_latencies(p["transitions"]) == [(2, pytest.approx(0.4))]
+    tl = analysis.replica_timeline(p["transitions"], 5.0)
+    assert tl[2] == [(1.5, 1.9, "LoadingPrefill"), (1.9, 5.0, "Prefill")]
+    recs = [{"status": "ok", "first_token_time": 100.0, "max_time_between_tokens": 20.0, "input_length": 100},
+            {"status": "ok", "first_token_time": 900.0, "max_time_between_tokens": 150.0, "input_length": 1000}]
+    s = analysis.slo_table(recs)
+    assert s["ttft_violation_rate"] == 0.5 and s["tbt_violation_rate"] == 0.5
+    z = analysis.kv_sizing("llama3_8b", tp=1, page_size=64)
+    assert z["kv_bytes_per_token"] == 2 * 8 * 128 * 2 * 32 and z["block_bytes"] == z["kv_bytes_per_token"] * 64

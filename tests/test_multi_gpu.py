@@ -18,9 +18,22 @@ def _run(case, nproc, extra_env=None):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(HERE, "mgpu_worker.py"), case]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     return res.stdout
+
+
+@pytest.mark.parametrize("case,n", [("pd", 2), ("scale", 3), ("live", 3)])
+def test_gpu_cluster_end_to_end(case, n):
+    """GPU workers over gRPC + router runtime: PD with in-kernel KV push, scale-out by parameter multicast, live scaling."""
+    if _ngpu() < n:
+        pytest.skip(f"needs >= {n} GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29527", os.path.join(HERE, "gpu_cluster_e2e.py"), case]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "OK" in res.stdout
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
