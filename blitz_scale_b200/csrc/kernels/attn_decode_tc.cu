@@ -421,3 +421,112 @@ int blitz_attn_decode(const void* q, int64_t q_stride, const void* kv_layer, con
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in attn_decode_noalloc.h).  The split-KV partials go to
+// an array that is part of the library image instead of a caller-provided workspace.
+#include "attn_decode_noalloc.h"
+
+namespace blitz {
+
+// Device global memory, present on every GPU that loads the library.  In host code this name is only a
+// handle for the runtime: its device address is looked up once per device below and that address, not the
+// name, is what the kernels receive.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[BLITZ_ATTN_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kNoallocMaxDevices = 64;
+static void* g_noalloc_ptr[kNoallocMaxDevices] = {};
+static bool g_noalloc_ready[kNoallocMaxDevices] = {};
+
+// Per-device set-up with that device current: resolve the scratch address, raise the shared-memory limits.
+static int noalloc_setup(int dev) {
+  void* ptr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+  if (e != cudaSuccess) return (int)e;
+  if (ptr == nullptr) return (int)cudaErrorInvalidSymbol;
+  e = cudaFuncSetAttribute(attn_decode_tc_kernel<__nv_bfloat16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(attn_decode_tc_kernel<__nv_bfloat16, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(attn_decode_tc_kernel<__half, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(attn_decode_tc_kernel<__half, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64>::kSmemBytes);
+  if (e != cudaSuccess) return (int)e;
+  g_noalloc_ptr[dev] = ptr;
+  g_noalloc_ready[dev] = true;
+  return 0;
+}
+
+// Tensor map of one KV layer built on the stack (the cached builder keeps a host-side table; this path keeps nothing).
+static bool noalloc_tmap(CUtensorMap* out, const void* kv_layer, int head_dim, int kv_heads, int max_pages, int page_size,
+                         int box_tokens) {
+  PFN_encodeTiled enc = get_encode_fn();
+  if (!enc || (reinterpret_cast<uintptr_t>(kv_layer) & 15) != 0) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)kv_heads, (cuuint64_t)max_pages * 2 * page_size};
+  cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, (cuuint64_t)kv_heads * head_dim * 2};
+  cuuint32_t box[3] = {64, 1, (cuuint32_t)box_tokens};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(kv_layer), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int HD>
+static int noalloc_launch(const CUtensorMap& tm, const DecodeTcParams& p, int sms, cudaStream_t stream) {
+  const int items = p.batch * p.kv_heads * p.num_splits;
+  attn_decode_tc_kernel<T, HD><<<items < sms ? items : sms, kTcThreads, TcCfg<HD>::kSmemBytes, stream>>>(tm, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace blitz
+
+extern "C" int blitz_attn_decode_noalloc(const void* q, int64_t q_stride, const void* kv_layer, const int32_t* indices,
+                                         const int32_t* indptr, const int32_t* last_page_len, void* out,
+                                         int64_t out_stride, int batch, int q_heads, int kv_heads, int head_dim,
+                                         int page_size, int max_pages, int num_splits, float sm_scale, int* status,
+                                         int dtype, cudaStream_t stream) {
+  using namespace blitz;
+  if (batch <= 0) return 0;
+  if (num_splits < 1 || kv_heads <= 0 || (q_heads % kv_heads) != 0 || (q_stride & 1) || (out_stride & 1)) return -1;
+  const int G = q_heads / kv_heads;
+  if (G > 8 || (head_dim != 64 && head_dim != 128)) return -1;
+  if (page_size < 8 || (page_size & (page_size - 1)) != 0) return -1;
+  const int64_t need = num_splits > 1 ? (int64_t)batch * q_heads * num_splits * (head_dim + 1) * (int64_t)sizeof(float) : 0;
+  if (need > (int64_t)BLITZ_ATTN_NOALLOC_SCRATCH_BYTES) return BLITZ_ATTN_NOALLOC_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoallocMaxDevices) return -1;
+  if (!g_noalloc_ready[dev]) {
+    const int rc = noalloc_setup(dev);
+    if (rc != 0) return rc;
+  }
+  const int bt = page_size < kTcChunk ? page_size : kTcChunk;
+  CUtensorMap tm;
+  if (!noalloc_tmap(&tm, kv_layer, head_dim, kv_heads, max_pages, page_size, bt)) return -2;
+  DecodeTcParams p;
+  p.q = q; p.q_stride = q_stride; p.indices = indices; p.indptr = indptr; p.last_page_len = last_page_len;
+  p.out = out; p.out_stride = out_stride;
+  p.part_o = reinterpret_cast<float*>(g_noalloc_ptr[dev]);
+  p.part_lse = p.part_o + (int64_t)batch * q_heads * num_splits * head_dim;
+  p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size;
+  p.max_pages = max_pages; p.num_splits = num_splits; p.box_tokens = bt;
+  p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
+  int sms = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  int rc;
+  if (dtype == 1)
+    rc = head_dim == 128 ? noalloc_launch<__nv_bfloat16, 128>(tm, p, sms, stream) : noalloc_launch<__nv_bfloat16, 64>(tm, p, sms, stream);
+  else
+    rc = head_dim == 128 ? noalloc_launch<__half, 128>(tm, p, sms, stream) : noalloc_launch<__half, 64>(tm, p, sms, stream);
+  if (rc != 0 || num_splits == 1) return rc;
+  dim3 grid(batch, q_heads);
+  if (dtype == 1)
+    attn_merge_tc_kernel<__nv_bfloat16><<<grid, head_dim, 0, stream>>>(p.part_o, p.part_lse, (__nv_bfloat16*)out, out_stride,
+                                                                       q_heads, head_dim, num_splits);
+  else
+    attn_merge_tc_kernel<__half><<<grid, head_dim, 0, stream>>>(p.part_o, p.part_lse, (__half*)out, out_stride, q_heads,
+                                                                head_dim, num_splits);
+  return (int)cudaGetLastError();
+}

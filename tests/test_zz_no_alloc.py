@@ -1,0 +1,73 @@
+"""The allocation-free decode-attention entry point against the ordinary one.
+
+Some hosts of this library cannot allocate device memory at the point where they call it (the GPU is
+fully owned by their own pool, or the call sits inside a callback that must not allocate), so
+`blitz_attn_decode_noalloc` keeps the split-KV scratch inside the library.  The test calls it through the
+exported C symbol, twice in a row on different inputs (the built-in scratch keeps the first call's
+contents), and compares with `blitz_attn_decode` fed a caller-allocated workspace.  It sits in its own
+file, collected last, so a failure here cannot hide any other test's result.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DT = torch.bfloat16
+SCRATCH_BYTES = 16 << 20
+TOO_LARGE = -3
+
+
+def _case(seed, lens, page, kvh, hd):
+    g = torch.Generator().manual_seed(seed)
+    npages = [(n + page - 1) // page for n in lens]
+    total = sum(npages) + 2
+    perm = torch.randperm(total, generator=g).tolist()
+    kv = torch.zeros(total, 2, page, kvh, hd, dtype=DT)
+    idx, indptr, last, cur = [], [0], [], 0
+    for n, npg in zip(lens, npages):
+        pg = perm[cur:cur + npg]
+        cur += npg
+        for i, p in enumerate(pg):
+            m = min(n, (i + 1) * page) - i * page
+            kv[p, :, :m] = torch.randn(2, m, kvh, hd, generator=g).to(DT)
+        idx += pg
+        indptr.append(len(idx))
+        last.append(n - (npg - 1) * page)
+    ti = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    return kv.cuda(), ti(idx), ti(indptr), ti(last)
+
+
+def test_noalloc_entry_matches_workspace_entry():
+    from blitz_scale_b200 import ops
+    L = ops.lib()
+    fn = L.blitz_attn_decode_noalloc
+    c_i, c_i64, c_p, c_f = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
+    fn.argtypes = [c_p, c_i64, c_p, c_p, c_p, c_p, c_p, c_i64, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_f, c_p, c_i, c_p]
+    fn.restype = c_i
+    qh, kvh, hd, page, splits = 32, 8, 128, 16, 4
+    stream = lambda: c_p(torch.cuda.current_stream().cuda_stream)
+    status = ops.status_word()
+    for seed, lens in ((1, [700, 33, 1, 2048]), (2, [64, 1500, 257])):    # two calls in a row, different shapes
+        kv, idx, indptr, last = _case(seed, lens, page, kvh, hd)
+        B = len(lens)
+        torch.manual_seed(seed)
+        q = torch.randn(B, qh * hd, device="cuda", dtype=DT)
+        ref = ops.attn_decode(q, kv, idx, indptr, last, q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=page,
+                              num_splits=splits)
+        out = torch.full_like(ref, float("nan"))
+        rc = fn(q.data_ptr(), q.stride(0), kv.data_ptr(), idx.data_ptr(), indptr.data_ptr(), last.data_ptr(),
+                out.data_ptr(), out.stride(0), B, qh, kvh, hd, page, kv.shape[0], splits, hd ** -0.5,
+                status.data_ptr(), 1, stream())
+        assert rc == 0, rc
+        torch.cuda.synchronize()
+        ops.check_status()
+        err = float((out.float() - ref.float()).norm() / ref.float().norm())
+        assert err < 1e-2, err
+    # a request beyond the built-in scratch is refused, and nothing is launched
+    big_b = SCRATCH_BYTES // (qh * 32 * (hd + 1) * 4) + 1
+    rc = fn(q.data_ptr(), q.stride(0), kv.data_ptr(), idx.data_ptr(), indptr.data_ptr(), last.data_ptr(),
+            out.data_ptr(), out.stride(0), big_b, qh, kvh, hd, page, kv.shape[0], 32, hd ** -0.5, None, 1, stream())
+    assert rc == TOO_LARGE
+    torch.cuda.synchronize()
