@@ -72,7 +72,16 @@ def bench_gemm(shapes, out):
         bs = [torch.randn(K, bcols, device="cuda", dtype=torch.bfloat16) * K ** -0.5 for _ in range(nc)]
         r = torch.randn(M, N, device="cuda", dtype=torch.bfloat16) if epi == "add" else None
         c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        t = timeit(lambda i: ops.gemm(a, bs[i], out=c, residual=r, epilogue=epi), copies=nc)
+        extra = {}
+        if M <= 256:
+            # decode sizes: weight-streaming kernel as the model runs it (weights static -> prefetched under the
+            # previous kernel's tail), the same without that promise, and the general tiled kernel
+            t = timeit(lambda i: ops.gemm(a, bs[i], out=c, residual=r, epilogue=epi, static_b=True), copies=nc)
+            t_ns = timeit(lambda i: ops.gemm(a, bs[i], out=c, residual=r, epilogue=epi), copies=nc)
+            t_gen = timeit(lambda i: ops.gemm(a, bs[i], out=c, residual=r, epilogue=epi, decode_path=False), copies=nc)
+            extra = dict(kernel="decode", us_no_prefetch=t_ns * 1e6, us_general_kernel=t_gen * 1e6)
+        else:
+            t = timeit(lambda i: ops.gemm(a, bs[i], out=c, residual=r, epilogue=epi), copies=nc)
         ops.check_status()
         cref = torch.empty(M, bcols, device="cuda", dtype=torch.bfloat16)
         t_ref = timeit(lambda i: torch.matmul(a, bs[i], out=cref), copies=nc)
@@ -80,7 +89,8 @@ def bench_gemm(shapes, out):
         by = 2.0 * (M * K + K * bcols + M * N)
         roof = max(fl / flops_peak, by / hbm)
         row = dict(kind="gemm", M=M, N=N, K=K, epilogue=epi, us=t * 1e6, cublas_us=t_ref * 1e6,
-                   tflops=fl / t / 1e12, gbs=by / t / 1e9, roofline_frac=roof / t, vs_cublas=t_ref / t, peaks=src)
+                   tflops=fl / t / 1e12, gbs=by / t / 1e9, roofline_frac=roof / t, vs_cublas=t_ref / t, peaks=src,
+                   **extra)
         out.append(row)
         print(json.dumps(row), flush=True)
 
@@ -132,7 +142,7 @@ def main():
     args = ap.parse_args()
     out = []
     # Llama-3-8B layer GEMMs at decode (M = batch) and prefill (M = tokens) sizes
-    ms = [16, 256] if args.quick else [16, 64, 256, 1024, 4096, 8192]
+    ms = [16, 128, 256] if args.quick else [16, 64, 128, 256, 1024, 4096, 8192]
     shapes = []
     for M in ms:
         shapes += [(M, 6144, 4096, "store"), (M, 4096, 4096, "add"), (M, 14336, 4096, "silu_mul"),

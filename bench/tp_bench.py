@@ -116,7 +116,8 @@ def main():
         os.makedirs(os.path.dirname(os.path.abspath(a.json)), exist_ok=True)
         json.dump(out, open(a.json, "w"), indent=1)
     dist.barrier()
-    dist.destroy_process_group()
+    sys.stdout.flush()
+    os._exit(0)      # skip symmetric-memory / NCCL teardown, which can block for minutes with live graphs
 
 
 if __name__ == "__main__":

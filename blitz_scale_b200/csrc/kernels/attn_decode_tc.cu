@@ -24,6 +24,7 @@
 //
 // Replaces src/kernel/attention_decode.cu:13-40 and the host-side plan of
 // src/kernel/flashinfer_types.cu:52-80.
+#include "launch.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
 #include "common.cuh"
@@ -141,6 +142,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcPa
   }
   ptx::fence_proxy_async_smem();
   __syncthreads();
+  // programmatic dependent launch: the set-up above may overlap the previous kernel; q and the KV pages
+  // are its outputs, so wait before the first load
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
 
   if (warp == 4) {
     // ------------------------------------------------------------ producer
@@ -359,8 +364,7 @@ static int launch_tc(const CUtensorMap& tm, const DecodeTcParams& p, int batch, 
   }
   const int items = batch * p.kv_heads * p.num_splits;
   const int sms = device_sm_count();
-  kern<<<items < sms ? items : sms, kTcThreads, TcCfg<HD>::kSmemBytes, stream>>>(tm, p);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(kern, dim3(items < sms ? items : sms), dim3(kTcThreads), TcCfg<HD>::kSmemBytes, stream, tm, p);
 }
 
 }  // namespace blitz

@@ -8,6 +8,8 @@
 // src/kernel/sampler.cu:7-141, src/kernel/page.cu:21-115.  All kernels move
 // 16 bytes per thread access and keep reductions in fp32.
 #include "common.cuh"
+#include "launch.cuh"
+#include "ptx.cuh"
 
 namespace blitz {
 
@@ -20,6 +22,8 @@ template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
                                  int hidden, int vocab_start, int vocab_rows, int zero_missing,
                                  const int32_t* __restrict__ dst_rows) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   const int t = blockIdx.x;
   const int id = ids[t] - vocab_start;
   const int row = dst_rows ? dst_rows[t] : t;
@@ -39,6 +43,8 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __res
 template <typename T, bool ADD>
 __global__ void rms_norm_kernel(const T* __restrict__ x, T* __restrict__ residual, const T* __restrict__ w,
                                 T* __restrict__ out, int hidden, float eps) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   __shared__ float red[33];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * hidden;
   const int nvec = hidden >> 3;
@@ -78,6 +84,8 @@ __global__ void rms_norm_kernel(const T* __restrict__ x, T* __restrict__ residua
 // ------------------------------------------------------------------ SiLU * mul, residual add
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int64_t in_stride) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   const int64_t t = blockIdx.x;
   const uint4* g = reinterpret_cast<const uint4*>(in + t * in_stride);
   const uint4* u = reinterpret_cast<const uint4*>(in + t * in_stride + inter);
@@ -94,6 +102,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
 
 template <typename T>
 __global__ void add_kernel(T* __restrict__ residual, const T* __restrict__ x, int64_t nvec) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     float a[8], b[8];
@@ -109,6 +119,8 @@ __global__ void add_kernel(T* __restrict__ residual, const T* __restrict__ x, in
 template <typename T>
 __global__ void gather_last_kernel(const T* __restrict__ x, const int32_t* __restrict__ indptr, T* __restrict__ out,
                                    int hidden) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   const int b = blockIdx.x;
   const int64_t row = static_cast<int64_t>(indptr[b + 1]) - 1;
   const uint4* src = reinterpret_cast<const uint4*>(x + row * hidden);
@@ -122,6 +134,8 @@ __global__ void gather_last_kernel(const T* __restrict__ x, const int32_t* __res
 template <typename T>
 __global__ void argmax_kernel(const T* __restrict__ logits, int vocab, int64_t stride, int32_t* __restrict__ out_idx,
                               float* __restrict__ out_val, int idx_offset) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   __shared__ float sval[32];
   __shared__ int sidx[32];
   const T* row = logits + static_cast<int64_t>(blockIdx.x) * stride;
@@ -199,6 +213,8 @@ template <typename T>
 __global__ void sample_kernel(const T* __restrict__ logits, int vocab, int64_t stride, const float* __restrict__ temp,
                               const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
                               const uint64_t* __restrict__ seeds, uint64_t step, int32_t* __restrict__ out_idx) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   __shared__ float red[33];
   __shared__ float scan[1025];
   __shared__ int chosen;
@@ -300,6 +316,8 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int32_t* __restr
                                      const int32_t* __restrict__ slot, T* __restrict__ kv_layer, int q_heads,
                                      int kv_heads, int head_dim, int page_size, int max_pages, float log2_theta,
                                      int* __restrict__ status) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   const int t = blockIdx.x;
   const int half = head_dim >> 1;
   const int vec_per_half = half >> 3;
@@ -366,19 +384,21 @@ int blitz_embedding(const int32_t* ids, const void* table, void* out, int num_to
                     int vocab_rows, int zero_missing, const int32_t* dst_rows, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (hidden & 7) return -1;
-  BLITZ_DISPATCH_DTYPE(dtype, (embedding_kernel<T><<<num_tokens, pick_threads(hidden >> 3), 0, stream>>>(
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(embedding_kernel<T>, dim3(num_tokens), dim3(pick_threads(hidden >> 3)), 0, stream,
                                   ids, (const T*)table, (T*)out, hidden, vocab_start, vocab_rows, zero_missing,
                                   dst_rows)));
-  return (int)cudaGetLastError();
+  return (int)blitz_last;
 }
 
 int blitz_rms_norm(const void* x, const void* w, void* out, int num_tokens, int hidden, float eps, int dtype,
                    cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (hidden & 7) return -1;
-  BLITZ_DISPATCH_DTYPE(dtype, (rms_norm_kernel<T, false><<<num_tokens, pick_threads(hidden >> 3), 0, stream>>>(
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(rms_norm_kernel<T, false>, dim3(num_tokens), dim3(pick_threads(hidden >> 3)), 0, stream,
                                   (const T*)x, nullptr, (const T*)w, (T*)out, hidden, eps)));
-  return (int)cudaGetLastError();
+  return (int)blitz_last;
 }
 
 // residual += x ; out = RMSNorm(residual) * w.  `out` may alias `x`.
@@ -386,18 +406,20 @@ int blitz_add_rms_norm(const void* x, void* residual, const void* w, void* out, 
                        int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (hidden & 7) return -1;
-  BLITZ_DISPATCH_DTYPE(dtype, (rms_norm_kernel<T, true><<<num_tokens, pick_threads(hidden >> 3), 0, stream>>>(
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(rms_norm_kernel<T, true>, dim3(num_tokens), dim3(pick_threads(hidden >> 3)), 0, stream,
                                   (const T*)x, (T*)residual, (const T*)w, (T*)out, hidden, eps)));
-  return (int)cudaGetLastError();
+  return (int)blitz_last;
 }
 
 int blitz_silu_mul(const void* in, void* out, int num_tokens, int inter, int64_t in_stride, int dtype,
                    cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if ((inter & 7) || (in_stride & 7)) return -1;
-  BLITZ_DISPATCH_DTYPE(dtype, (silu_mul_kernel<T><<<num_tokens, pick_threads(inter >> 3), 0, stream>>>(
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(silu_mul_kernel<T>, dim3(num_tokens), dim3(pick_threads(inter >> 3)), 0, stream,
                                   (const T*)in, (T*)out, inter, in_stride)));
-  return (int)cudaGetLastError();
+  return (int)blitz_last;
 }
 
 int blitz_add_residual(void* residual, const void* x, int64_t numel, int dtype, cudaStream_t stream) {
@@ -406,36 +428,40 @@ int blitz_add_residual(void* residual, const void* x, int64_t numel, int dtype, 
   const int64_t nvec = numel >> 3;
   int blocks = (int)((nvec + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  BLITZ_DISPATCH_DTYPE(dtype, (add_kernel<T><<<blocks, 256, 0, stream>>>((T*)residual, (const T*)x, nvec)));
-  return (int)cudaGetLastError();
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(add_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)residual, (const T*)x, nvec)));
+  return (int)blitz_last;
 }
 
 int blitz_gather_last(const void* x, const int32_t* indptr, void* out, int batch, int hidden, int dtype,
                       cudaStream_t stream) {
   if (batch <= 0) return 0;
   if (hidden & 7) return -1;
-  BLITZ_DISPATCH_DTYPE(dtype, (gather_last_kernel<T><<<batch, pick_threads(hidden >> 3), 0, stream>>>(
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(gather_last_kernel<T>, dim3(batch), dim3(pick_threads(hidden >> 3)), 0, stream,
                                   (const T*)x, indptr, (T*)out, hidden)));
-  return (int)cudaGetLastError();
+  return (int)blitz_last;
 }
 
 int blitz_argmax(const void* logits, int batch, int vocab, int64_t stride, int32_t* out_idx, float* out_val,
                  int idx_offset, int dtype, cudaStream_t stream) {
   if (batch <= 0) return 0;
   if (stride & 7) return -1;
-  BLITZ_DISPATCH_DTYPE(dtype, (argmax_kernel<T><<<batch, 1024, 0, stream>>>((const T*)logits, vocab, stride, out_idx,
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(argmax_kernel<T>, dim3(batch), dim3(1024), 0, stream, (const T*)logits, vocab, stride, out_idx,
                                                                             out_val, idx_offset)));
-  return (int)cudaGetLastError();
+  return (int)blitz_last;
 }
 
 int blitz_sample(const void* logits, int batch, int vocab, int64_t stride, const float* temperature,
                  const int32_t* top_k, const float* top_p, const uint64_t* seeds, uint64_t step, int32_t* out_idx,
                  int dtype, cudaStream_t stream) {
   if (batch <= 0) return 0;
-  BLITZ_DISPATCH_DTYPE(dtype, (sample_kernel<T><<<batch, 1024, 0, stream>>>((const T*)logits, vocab, stride,
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(sample_kernel<T>, dim3(batch), dim3(1024), 0, stream, (const T*)logits, vocab, stride,
                                                                             temperature, top_k, top_p, seeds, step,
                                                                             out_idx)));
-  return (int)cudaGetLastError();
+  return (int)blitz_last;
 }
 
 int blitz_rope_kv_store(void* qkv, const int32_t* pos, const int32_t* slot, void* kv_layer, int num_tokens,
@@ -444,10 +470,11 @@ int blitz_rope_kv_store(void* qkv, const int32_t* pos, const int32_t* slot, void
   if (num_tokens <= 0) return 0;
   if (head_dim & 15) return -1;
   const float log2_theta = log2f(rope_theta);
-  BLITZ_DISPATCH_DTYPE(dtype, (rope_kv_store_kernel<T><<<num_tokens, 256, 0, stream>>>(
+  cudaError_t blitz_last = cudaSuccess;
+  BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(rope_kv_store_kernel<T>, dim3(num_tokens), dim3(256), 0, stream,
                                   (T*)qkv, pos, slot, (T*)kv_layer, q_heads, kv_heads, head_dim, page_size, max_pages,
                                   log2_theta, status)));
-  return (int)cudaGetLastError();
+  return (int)blitz_last;
 }
 
 }  // extern "C"

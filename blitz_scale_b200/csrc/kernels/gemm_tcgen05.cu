@@ -11,10 +11,11 @@
 //   add        C = acc + R                  (residual add of o_proj / down_proj)
 //   silu_mul   C = silu(acc_gate) * acc_up  (gate||up projection; B holds N gate columns, then N up columns)
 //
-// Measured on B200: a 128-row tcgen05.mma of K = 16 occupies the tensor pipe for ~140 cycles whatever
-// its N (<= 256), so (1) tiles are always as wide as the epilogue allows (N = 256 per instruction) and
-// (2) the time of a skinny GEMM (decode: M <= 256) is (K / 16) x 140 cycles per CTA unless K is split.
-// Skinny GEMMs therefore split K across CTAs until every SM has work: each CTA stores its fp32
+// Measured on B200: a 128-row tcgen05.mma of K = 16 occupies the tensor pipe for ~95 / 105 / 150 cycles at
+// N = 64 / 128 / 256, so (1) wide tiles are the most efficient per FLOP and (2) the time of a skinny GEMM
+// is (K / 16) x that cost per CTA unless K is split.  Skinny GEMMs that do not qualify for the
+// weight-streaming decode kernel (gemm_decode.cu: M <= 256, [K,N] weights) split K across CTAs until
+// every SM has work: each CTA stores its fp32
 // partial tile to a scratch buffer, takes a ticket, and the CTA that arrives last sums the partials
 // in split order (deterministic), applies the epilogue and resets the ticket.  No second kernel.
 //
@@ -24,6 +25,7 @@
 //
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = UMMA issuer + TMEM owner, warps 2..5 =
 // epilogue (TMEM lane quarter = warp_idx % 4).
+#include "launch.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
 #include <type_traits>
@@ -217,6 +219,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // programmatic dependent launch: set-up above overlapped the previous kernel's tail; from here on we
+  // touch memory that earlier kernels may have written
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -462,8 +468,7 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
-  return cudaGetLastError();
+  return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, ta, tb, p);
 }
 
 template <typename T, bool B_KMAJOR, int EPI>

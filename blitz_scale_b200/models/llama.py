@@ -118,7 +118,7 @@ class LlamaRunner:
     def attention_block(self, l: int, m: StepMeta) -> None:
         T, c = m.num_tokens, self.cfg
         ops.rms_norm(self.res[:T], self._w(l, "input_ln"), c.rms_eps, out=self.normed[:T])
-        ops.gemm(self.normed[:T], self._w(l, "qkv"), out=self.qkv[:T])
+        ops.gemm(self.normed[:T], self._w(l, "qkv"), static_b=True, out=self.qkv[:T])
         ops.rope_kv_store(self.qkv[:T], m.pos[:T], m.slot[:T], self.kv[l], q_heads=self.qh, kv_heads=self.kvh,
                           head_dim=self.hd, page_size=self.page_size, rope_theta=c.rope_theta)
         if m.is_prefill:
@@ -130,9 +130,9 @@ class LlamaRunner:
                             num_splits=m.num_splits, workspace=self._workspace(m.batch, m.num_splits),
                             out=self.attn[:T])
         if self.tp == 1:
-            ops.gemm(self.attn[:T], self._w(l, "o"), out=self.res[:T], residual=self.res[:T], epilogue="add")
+            ops.gemm(self.attn[:T], self._w(l, "o"), static_b=True, out=self.res[:T], residual=self.res[:T], epilogue="add")
         else:
-            ops.gemm(self.attn[:T], self._w(l, "o"), out=self.tmp[:T])
+            ops.gemm(self.attn[:T], self._w(l, "o"), static_b=True, out=self.tmp[:T])
             self.comm.all_reduce_(self.tmp[:T])
 
     def ffn_block(self, l: int, m: StepMeta) -> None:
@@ -141,11 +141,11 @@ class LlamaRunner:
             ops.rms_norm(self.res[:T], self._w(l, "post_ln"), c.rms_eps, out=self.normed[:T])
         else:
             ops.add_rms_norm(self.tmp[:T], self.res[:T], self._w(l, "post_ln"), c.rms_eps, out=self.normed[:T])
-        ops.gemm(self.normed[:T], self._w(l, "gate_up"), out=self.act[:T], epilogue="silu_mul")
+        ops.gemm(self.normed[:T], self._w(l, "gate_up"), static_b=True, out=self.act[:T], epilogue="silu_mul")
         if self.tp == 1:
-            ops.gemm(self.act[:T], self._w(l, "down"), out=self.res[:T], residual=self.res[:T], epilogue="add")
+            ops.gemm(self.act[:T], self._w(l, "down"), static_b=True, out=self.res[:T], residual=self.res[:T], epilogue="add")
         else:
-            ops.gemm(self.act[:T], self._w(l, "down"), out=self.tmp[:T])
+            ops.gemm(self.act[:T], self._w(l, "down"), static_b=True, out=self.tmp[:T])
             self.comm.all_reduce_(self.tmp[:T])
             ops.add_residual(self.res[:T], self.tmp[:T])
 
@@ -161,7 +161,7 @@ class LlamaRunner:
         else:
             src = self.res[:B]
         ops.rms_norm(src, self.seg["final_norm"], c.rms_eps, out=self.normed[:B])
-        ops.gemm(self.normed[:B], self.seg["lm_head"], out=self.logits[:B])
+        ops.gemm(self.normed[:B], self.seg["lm_head"], static_b=True, out=self.logits[:B])
         vs = c.vocab // self.tp
         if self.tp == 1:
             ops.argmax(self.logits[:B], out=self.tokens[:B])

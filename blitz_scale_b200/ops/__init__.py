@@ -71,6 +71,7 @@ _EPI = {"store": 0, "add": 1, "silu_mul": 2}
 
 _gemm_ws = {}
 GEMM_TICKETS = 4096
+DECODE_GEMM_MAX_M = 128
 
 
 def gemm_workspace(device=None):
@@ -85,13 +86,20 @@ def gemm_workspace(device=None):
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, residual=None,
-         epilogue: str = "store", b_layout: str = "kn", bn: int = 0, split_k: int = 0) -> torch.Tensor:
+         epilogue: str = "store", b_layout: str = "kn", bn: int = 0, split_k: int = 0, static_b: bool = False,
+         decode_path: Optional[bool] = None, decode_split: int = 0) -> torch.Tensor:
     """``out = a @ b`` on tcgen05 with a fused epilogue.
 
     a: [M, K].  b: [K, N] when ``b_layout == 'kn'`` (weights stored in,out) or [N, K] for ``'nk'``.
     epilogue 'add' adds ``residual`` ([M, N], same pitch as out); 'silu_mul' treats b as [gate | up] with
     N_out = b_cols / 2 and returns silu(a@gate) * (a@up).  ``split_k``: 0 lets the kernel split K when the
     GEMM is too skinny to fill the GPU, 1 forbids it, n > 1 forces n splits.
+
+    Up to 256 rows of ``a`` with 'kn' weights go to the weight-streaming decode kernel (operands swapped on
+    the tensor core, K split over a thread-block cluster with the reduction in distributed shared memory);
+    ``decode_path`` forces (True) or forbids (False) that choice and ``decode_split`` caps its cluster size.  ``static_b=True`` promises that ``b`` is not written by kernels still
+    running in this stream (model weights), so the decode kernel may start streaming it before its
+    predecessor has finished.
     """
     assert a.is_cuda and a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     M, K = a.shape
@@ -109,6 +117,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     if epi == 1:
         assert residual is not None and residual.shape == (M, N) and residual.stride(0) == out.stride(0)
     ws, tickets = gemm_workspace(a.device)
+    # the decode kernel re-reads the activation tile with every weight tile, which the SM's load path cannot keep up
+    # with beyond ~128 rows; from there on the tiled kernel is faster
+    use_dec = M <= DECODE_GEMM_MAX_M and bn == 0 and split_k == 0 and \
+        bool(lib().blitz_gemm_decode_supported(M, N, K, 0 if b_layout == "kn" else 1, epi))
+    if decode_path is not None:
+        assert not decode_path or lib().blitz_gemm_decode_supported(M, N, K, 0 if b_layout == "kn" else 1, epi)
+        use_dec = decode_path
+    if use_dec:
+        rc = lib().blitz_gemm_decode(_p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), _p(residual), M, N,
+                                     K, epi, N if epi == 2 else 0, _dt(a), int(static_b), decode_split,
+                                     _p(status_word(a.device)), _stream())
+        _check(rc, "blitz_gemm_decode")
+        return out
     rc = lib().blitz_gemm(_p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), _p(residual), M, N, K,
                           0 if b_layout == "kn" else 1, epi, N if epi == 2 else 0, _dt(a), bn, split_k,
                           _p(ws), ws.numel(), _p(tickets), tickets.numel(), _p(status_word(a.device)), _stream())

@@ -56,6 +56,10 @@ def _declare(L: ctypes.CDLL) -> None:
     sig("blitz_gemm", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_i64,
                        c_p, c_i, c_p, c_p])
     sig("blitz_gemm_workspace_bytes", [c_i], c_i64)
+    sig("blitz_gemm_decode", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_p])
+    sig("blitz_gemm_decode_supported", [c_i, c_i, c_i, c_i, c_i], c_i)
+    sig("blitz_set_pdl", [c_i], None)
+    sig("blitz_get_pdl", [], c_i)
     sig("blitz_gemm_tile_n", [c_i, c_i, c_i, c_i], c_i)
     sig("blitz_gemm_tp", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_i64,
                           c_p, c_i, c_p, c_p, c_p])

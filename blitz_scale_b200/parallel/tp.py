@@ -220,7 +220,7 @@ class LlamaRunnerTP(LlamaRunner):
             src = self.last[:B]
         else:
             src = xn[:B]
-        ops.gemm(src, self.seg["lm_head"], out=self.logits[:B])
+        ops.gemm(src, self.seg["lm_head"], static_b=True, out=self.logits[:B])
         vs = c.vocab // self.tp
         ops.argmax(self.logits[:B], out=self.tokens[:B], out_val=self.maxval[:B], idx_offset=self.seg.tp_rank * vs)
         vals = self.comm.all_gather(self.maxval[:B])

@@ -88,6 +88,45 @@ def test_gemm_split_k(ops, M, N, K):
     assert rel_err(ops.gemm(a, gu, epilogue="silu_mul", split_k=4), ref2) < 1e-2
 
 
+@pytest.mark.parametrize("M", [1, 7, 16, 33, 100, 128, 200, 256])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1088, 520), (6144, 1024)])
+def test_gemm_decode_path(ops, M, N, K):
+    """Weight-streaming decode GEMM (swapped operands, cluster split-K with the reduction in distributed shared
+    memory): every cluster size gives the right result, and the same one on every run."""
+    torch.manual_seed(13)
+    a = torch.randn(M, K, device="cuda", dtype=DT)
+    b = torch.randn(K, N, device="cuda", dtype=DT) * K ** -0.5
+    r = torch.randn(M, N, device="cuda", dtype=DT)
+    ref = a.float() @ b.float()
+    gu = torch.randn(K, 2 * N, device="cuda", dtype=DT) * K ** -0.5
+    acc = a.float() @ gu.float()
+    ref2 = torch.nn.functional.silu(acc[:, :N]) * acc[:, N:]
+    for split in (0, 1, 2, 3, 8):
+        out = ops.gemm(a, b, decode_path=True, decode_split=split)
+        assert rel_err(out, ref) < 1e-2, (split, rel_err(out, ref))
+        assert torch.equal(out, ops.gemm(a, b, decode_path=True, decode_split=split, static_b=True)), "must be deterministic"
+        r2 = r.clone()
+        ops.gemm(a, b, out=r2, residual=r2, epilogue="add", decode_path=True, decode_split=split)
+        assert rel_err(r2, ref + r.float()) < 1e-2, split
+        assert rel_err(ops.gemm(a, gu, epilogue="silu_mul", decode_path=True, decode_split=split), ref2) < 1e-2, split
+    ops.check_status()
+
+
+def test_gemm_decode_fp16_and_pdl_chain(ops):
+    torch.manual_seed(14)
+    a = torch.randn(48, 768, device="cuda", dtype=torch.float16)
+    w1 = torch.randn(768, 1536, device="cuda", dtype=torch.float16) / 28
+    w2 = torch.randn(1536, 768, device="cuda", dtype=torch.float16) / 39
+    torch.cuda.synchronize()
+    # back-to-back dependent launches: the second GEMM prefetches its weights before the first has finished
+    h = ops.gemm(a, w1, decode_path=True, static_b=True)
+    y = ops.gemm(h, w2, decode_path=True, static_b=True)
+    ref_h = (a.float() @ w1.float()).to(torch.float16)
+    assert rel_err(h, a.float() @ w1.float()) < 5e-3
+    assert rel_err(y, ref_h.float() @ w2.float()) < 5e-3
+    ops.check_status()
+
+
 def test_gemm_fp16(ops):
     torch.manual_seed(2)
     a = torch.randn(96, 256, device="cuda", dtype=torch.float16)
