@@ -17,6 +17,8 @@
 #include <thread>
 #include <vector>
 
+#include "../util/log.h"
+
 namespace blitz {
 
 struct LoadResult {
@@ -79,6 +81,8 @@ inline LoadResult load_file_to_host(const std::string& path, uintptr_t dst_addr,
   res.bytes = total;
   res.seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
   res.direct_io = direct;
+  BZ_DEBUG("loaded %s: %.3f GB in %.3f s (%.2f GB/s, %s, %d threads)", path.c_str(), total / 1e9, res.seconds,
+           total / 1e9 / (res.seconds > 0 ? res.seconds : 1e-9), direct ? "O_DIRECT" : "buffered", threads);
   return res;
 }
 

@@ -1,0 +1,355 @@
+// Native BPE tokenizer reading the Hugging Face `tokenizer.json` format.
+//
+// Two families are covered, which is what the served model zoo needs:
+//   * byte-level BPE (GPT-2 / Llama-3 / Qwen / Mistral-v3 style): text is cut into words by a scanner that follows the
+//     GPT-2 pattern (contractions, letter runs, digit runs of at most `max_digits`, punctuation runs, white space),
+//     every byte is mapped to a printable code point, and merges are applied by rank;
+//   * SentencePiece-style BPE (Llama-2 / Mistral-v1): spaces become U+2581, the text is merged as one piece, unknown
+//     characters fall back to <0xNN> byte tokens.
+// Added (special) tokens are matched literally before anything else.  Counterpart of the reference's tokenizer
+// binding (Rust `tokenizers` behind a C ABI: create_tokenizer_from_file / encode / decode / num_ids / get_id,
+// src/tokenizer/): the same five operations are exported with C linkage by the core module.
+//
+// The scanner treats every non-ASCII character as a letter; for scripts where Unicode classes matter (digits or
+// punctuation outside ASCII) the split can differ from the regex engine's, which changes token boundaries but never
+// loses bytes: decode(encode(s)) == s always holds for byte-level models.
+#pragma once
+#include <cstdint>
+#include <cstdio>
+#include <fstream>
+#include <limits>
+#include <memory>
+#include <mutex>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <string_view>
+#include <unordered_map>
+#include <utility>
+#include <vector>
+
+#include "../util/minijson.h"
+
+namespace blitz {
+
+class Tokenizer {
+ public:
+  static Tokenizer from_file(const std::string& path) {
+    std::ifstream f(path, std::ios::binary);
+    if (!f) throw std::runtime_error("tokenizer: cannot open " + path);
+    std::stringstream ss;
+    ss << f.rdbuf();
+    return from_json(ss.str());
+  }
+
+  static Tokenizer from_json(const std::string& text) {
+    const json::Value root = json::parse(text);
+    Tokenizer t;
+    const json::Value& model = root.at("model");
+    if (const json::Value* ty = model.find("type"))
+      if (ty->type == json::Value::String && ty->str != "BPE") throw std::runtime_error("tokenizer: only BPE models");
+    for (const auto& kv : model.at("vocab").obj) t.add_token(kv.first, static_cast<int32_t>(kv.second.as_int()));
+    int rank = 0;
+    for (const json::Value& m : model.at("merges").arr) {
+      std::string a, b;
+      if (m.type == json::Value::String) {
+        const size_t sp = m.str.find(' ');
+        if (sp == std::string::npos) continue;
+        a = m.str.substr(0, sp);
+        b = m.str.substr(sp + 1);
+      } else if (m.type == json::Value::Array && m.arr.size() == 2) {
+        a = m.arr[0].str;
+        b = m.arr[1].str;
+      } else {
+        continue;
+      }
+      t.merges_.emplace(a + '\x01' + b, rank++);
+    }
+    if (const json::Value* bf = model.find("byte_fallback")) t.byte_fallback_ = bf->type == json::Value::Bool && bf->b;
+    if (const json::Value* unk = model.find("unk_token"))
+      if (unk->type == json::Value::String) {
+        auto it = t.vocab_.find(unk->str);
+        if (it != t.vocab_.end()) t.unk_id_ = it->second;
+      }
+    // byte-level if the pre-tokenizer or decoder says so; otherwise SentencePiece conventions
+    t.byte_level_ = mentions(root.find("pre_tokenizer"), "ByteLevel") || mentions(root.find("decoder"), "ByteLevel");
+    t.max_digits_ = text.find("\\\\p{N}{1,3}") != std::string::npos || text.find("\\p{N}{1,3}") != std::string::npos
+                        ? 3
+                        : std::numeric_limits<int>::max();
+    if (const json::Value* add = root.find("added_tokens"))
+      for (const json::Value& a : add->arr) {
+        const std::string& content = a.at("content").str;
+        const int32_t id = static_cast<int32_t>(a.at("id").as_int());
+        t.add_token(content, id);
+        bool special = false;
+        if (const json::Value* sp = a.find("special")) special = sp->type == json::Value::Bool && sp->b;
+        t.added_.push_back({content, id, special});
+      }
+    t.init_byte_maps();
+    return t;
+  }
+
+  int32_t num_ids() const { return static_cast<int32_t>(id_to_token_.size()); }
+  // -1 when the token string is unknown.
+  int32_t get_id(const std::string& token) const {
+    auto it = vocab_.find(token);
+    return it == vocab_.end() ? -1 : it->second;
+  }
+  const std::string& token(int32_t id) const {
+    static const std::string empty;
+    return id >= 0 && id < num_ids() ? id_to_token_[id] : empty;
+  }
+
+  std::vector<int32_t> encode(std::string_view text) const {
+    std::vector<int32_t> out;
+    size_t pos = 0;
+    while (pos < text.size()) {
+      // earliest added token at or after pos (longest on ties)
+      size_t best = std::string_view::npos, best_len = 0;
+      int32_t best_id = -1;
+      for (const Added& a : added_) {
+        if (a.content.empty()) continue;
+        const size_t f = text.find(a.content, pos);
+        if (f != std::string_view::npos && (f < best || (f == best && a.content.size() > best_len))) {
+          best = f;
+          best_len = a.content.size();
+          best_id = a.id;
+        }
+      }
+      const size_t end = best == std::string_view::npos ? text.size() : best;
+      if (end > pos) encode_plain(text.substr(pos, end - pos), out);
+      if (best == std::string_view::npos) break;
+      out.push_back(best_id);
+      pos = best + best_len;
+    }
+    return out;
+  }
+
+  std::string decode(const std::vector<int32_t>& ids, bool skip_special = true) const {
+    std::string out, pending;
+    auto flush = [&]() {
+      if (pending.empty()) return;
+      if (byte_level_) {
+        size_t i = 0;
+        while (i < pending.size()) {
+          uint32_t cp;
+          const size_t n = utf8_decode(pending, i, cp);
+          i += n;
+          auto it = cp_to_byte_.find(cp);
+          if (it != cp_to_byte_.end()) out.push_back(static_cast<char>(it->second));
+          else json_put(out, cp);
+        }
+      } else {
+        // U+2581 -> space
+        size_t i = 0;
+        while (i < pending.size()) {
+          if (pending.compare(i, 3, "\xE2\x96\x81") == 0) { out.push_back(' '); i += 3; }
+          else out.push_back(pending[i++]);
+        }
+      }
+      pending.clear();
+    };
+    for (int32_t id : ids) {
+      if (id < 0 || id >= num_ids()) continue;
+      if (is_added(id)) {
+        flush();
+        if (!(skip_special && is_special(id))) out += id_to_token_[id];
+        continue;
+      }
+      const std::string& tk = id_to_token_[id];
+      if (!byte_level_ && tk.size() == 6 && tk.compare(0, 3, "<0x") == 0 && tk[5] == '>') {
+        flush();
+        out.push_back(static_cast<char>(std::stoi(tk.substr(3, 2), nullptr, 16)));
+        continue;
+      }
+      pending += tk;
+    }
+    flush();
+    if (!byte_level_ && !out.empty() && out[0] == ' ') out.erase(0, 1);  // the prepended word boundary
+    return out;
+  }
+
+ private:
+  struct Added { std::string content; int32_t id; bool special; };
+  std::unordered_map<std::string, int32_t> vocab_;
+  std::vector<std::string> id_to_token_;
+  std::unordered_map<std::string, int> merges_;
+  std::vector<Added> added_;
+  bool byte_level_ = true, byte_fallback_ = false;
+  int32_t unk_id_ = -1;
+  int max_digits_ = std::numeric_limits<int>::max();
+  std::string byte_to_str_[256];
+  std::unordered_map<uint32_t, uint8_t> cp_to_byte_;
+  mutable std::unique_ptr<std::mutex> cache_mu_ = std::make_unique<std::mutex>();
+  mutable std::unordered_map<std::string, std::vector<int32_t>> cache_;
+
+  void add_token(const std::string& s, int32_t id) {
+    if (id < 0) return;
+    vocab_[s] = id;
+    if (static_cast<size_t>(id) >= id_to_token_.size()) id_to_token_.resize(id + 1);
+    id_to_token_[id] = s;
+  }
+  bool is_added(int32_t id) const {
+    for (const Added& a : added_) if (a.id == id) return true;
+    return false;
+  }
+  bool is_special(int32_t id) const {
+    for (const Added& a : added_) if (a.id == id) return a.special;
+    return false;
+  }
+  static bool mentions(const json::Value* v, const char* what) {
+    if (!v) return false;
+    if (v->type == json::Value::String) return v->str == what;
+    for (const auto& kv : v->obj) if (mentions(&kv.second, what)) return true;
+    for (const auto& e : v->arr) if (mentions(&e, what)) return true;
+    return false;
+  }
+  static void json_put(std::string& o, uint32_t cp) {
+    if (cp < 0x80) o.push_back(static_cast<char>(cp));
+    else if (cp < 0x800) { o.push_back(static_cast<char>(0xC0 | (cp >> 6))); o.push_back(static_cast<char>(0x80 | (cp & 0x3F))); }
+    else if (cp < 0x10000) {
+      o.push_back(static_cast<char>(0xE0 | (cp >> 12)));
+      o.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F)));
+      o.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+    } else {
+      o.push_back(static_cast<char>(0xF0 | (cp >> 18)));
+      o.push_back(static_cast<char>(0x80 | ((cp >> 12) & 0x3F)));
+      o.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F)));
+      o.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+    }
+  }
+  static size_t utf8_len(unsigned char c) { return c < 0x80 ? 1 : (c >> 5) == 6 ? 2 : (c >> 4) == 14 ? 3 : (c >> 3) == 30 ? 4 : 1; }
+  static size_t utf8_decode(const std::string& s, size_t i, uint32_t& cp) {
+    const unsigned char c = s[i];
+    size_t n = utf8_len(c);
+    if (i + n > s.size()) n = 1;
+    if (n == 1) { cp = c; return 1; }
+    cp = c & (0xFF >> (n + 1));
+    for (size_t k = 1; k < n; ++k) cp = (cp << 6) | (static_cast<unsigned char>(s[i + k]) & 0x3F);
+    return n;
+  }
+  // GPT-2 byte <-> printable code point table: printable Latin-1 bytes map to themselves, the rest to U+0100...
+  void init_byte_maps() {
+    int extra = 0;
+    for (int b = 0; b < 256; ++b) {
+      const bool keep = (b >= 33 && b <= 126) || (b >= 161 && b <= 172) || (b >= 174 && b <= 255);
+      const uint32_t cp = keep ? static_cast<uint32_t>(b) : 256u + static_cast<uint32_t>(extra++);
+      std::string s;
+      json_put(s, cp);
+      byte_to_str_[b] = s;
+      cp_to_byte_[cp] = static_cast<uint8_t>(b);
+    }
+  }
+
+  static bool is_letter(unsigned char c) { return (c >= 'a' && c <= 'z') || (c >= 'A' && c <= 'Z') || c >= 0x80; }
+  static bool is_digit(unsigned char c) { return c >= '0' && c <= '9'; }
+  static bool is_space(unsigned char c) { return c == ' ' || c == '\t' || c == '\n' || c == '\r' || c == '\v' || c == '\f'; }
+
+  // GPT-2 style word boundaries; returns the end of the word starting at i.
+  size_t next_word(std::string_view s, size_t i) const {
+    const size_t n = s.size();
+    if (s[i] == '\'' && i + 1 < n) {
+      static const char* kContr[] = {"'s", "'t", "'re", "'ve", "'m", "'ll", "'d"};
+      for (const char* c : kContr) {
+        const size_t l = std::char_traits<char>::length(c);
+        if (s.compare(i, l, c) == 0) return i + l;
+      }
+    }
+    size_t j = i;
+    if (s[j] == ' ' && j + 1 < n && !is_space(s[j + 1])) ++j;  // optional leading space
+    const unsigned char c = s[j];
+    if (is_letter(c)) {
+      while (j < n && is_letter(s[j])) ++j;
+      return j;
+    }
+    if (is_digit(c)) {
+      int d = 0;
+      while (j < n && is_digit(s[j]) && d < max_digits_) { ++j; ++d; }
+      return j;
+    }
+    if (!is_space(c)) {
+      while (j < n && !is_space(s[j]) && !is_letter(s[j]) && !is_digit(s[j])) ++j;
+      return j;
+    }
+    // white space: a run, leaving its last blank to prefix the next word when one follows
+    j = i;
+    while (j < n && is_space(s[j])) ++j;
+    if (j < n && j - i > 1 && s[j - 1] == ' ') --j;
+    return j;
+  }
+
+  void bpe(std::vector<std::string>& sym) const {
+    while (sym.size() > 1) {
+      int best = std::numeric_limits<int>::max();
+      size_t at = 0;
+      for (size_t k = 0; k + 1 < sym.size(); ++k) {
+        auto it = merges_.find(sym[k] + '\x01' + sym[k + 1]);
+        if (it != merges_.end() && it->second < best) { best = it->second; at = k; }
+      }
+      if (best == std::numeric_limits<int>::max()) break;
+      sym[at] += sym[at + 1];
+      sym.erase(sym.begin() + static_cast<long>(at) + 1);
+    }
+  }
+
+  void emit(const std::vector<std::string>& sym, std::vector<int32_t>& out) const {
+    for (const std::string& s : sym) {
+      auto it = vocab_.find(s);
+      if (it != vocab_.end()) { out.push_back(it->second); continue; }
+      if (byte_fallback_) {
+        bool ok = true;
+        std::vector<int32_t> tmp;
+        for (unsigned char c : s) {
+          char buf[8];
+          std::snprintf(buf, sizeof buf, "<0x%02X>", c);
+          auto bt = vocab_.find(buf);
+          if (bt == vocab_.end()) { ok = false; break; }
+          tmp.push_back(bt->second);
+        }
+        if (ok) { out.insert(out.end(), tmp.begin(), tmp.end()); continue; }
+      }
+      if (unk_id_ >= 0) out.push_back(unk_id_);
+    }
+  }
+
+  void encode_plain(std::string_view text, std::vector<int32_t>& out) const {
+    if (byte_level_) {
+      size_t i = 0;
+      while (i < text.size()) {
+        const size_t j = next_word(text, i);
+        const std::string word(text.substr(i, j - i));
+        i = j;
+        {
+          std::lock_guard<std::mutex> g(*cache_mu_);
+          auto it = cache_.find(word);
+          if (it != cache_.end()) { out.insert(out.end(), it->second.begin(), it->second.end()); continue; }
+        }
+        std::vector<std::string> sym;
+        sym.reserve(word.size());
+        for (unsigned char c : word) sym.push_back(byte_to_str_[c]);
+        bpe(sym);
+        std::vector<int32_t> ids;
+        emit(sym, ids);
+        out.insert(out.end(), ids.begin(), ids.end());
+        std::lock_guard<std::mutex> g(*cache_mu_);
+        if (cache_.size() < 200000) cache_.emplace(word, std::move(ids));
+      }
+    } else {
+      std::string norm = "\xE2\x96\x81";
+      for (char c : text) {
+        if (c == ' ') norm += "\xE2\x96\x81";
+        else norm.push_back(c);
+      }
+      std::vector<std::string> sym;
+      for (size_t i = 0; i < norm.size();) {
+        const size_t n = utf8_len(static_cast<unsigned char>(norm[i]));
+        sym.push_back(norm.substr(i, n));
+        i += n;
+      }
+      bpe(sym);
+      emit(sym, out);
+    }
+  }
+};
+
+}  // namespace blitz

@@ -18,7 +18,8 @@ from typing import Dict, List, Optional
 
 from ..pb.schema import pb
 from ..runtime import core
-from .stub import WorkerStub, encode_prefill_case
+from ..utils.tracing import child_traceparent, new_traceparent
+from .stub import CURRENT_TRACE, WorkerStub, encode_prefill_case
 
 log = logging.getLogger("blitz.router")
 A = core.ActionType
@@ -49,6 +50,7 @@ class RouterRuntime:
         self.wake = asyncio.Event()
         self.stopped = False
         self.t0 = time.monotonic()
+        self.root_trace = new_traceparent()
         self._next_id = 0
         self._tasks: set = set()
         self.transitions: List[tuple] = []
@@ -148,6 +150,7 @@ class RouterRuntime:
 
     async def _guard(self, a, handler) -> None:
         try:
+            CURRENT_TRACE.set(child_traceparent(self.root_trace))     # one span per dispatched operation
             await handler(a)
         except asyncio.CancelledError:
             raise

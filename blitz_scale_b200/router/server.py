@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import asyncio
+from concurrent.futures import ThreadPoolExecutor
 import json
 import logging
 import time
@@ -38,6 +39,27 @@ class WordHashTokenizer:
 
     def decode(self, ids: List[int]) -> str:
         return " ".join(f"<{i}>" for i in ids)
+
+    def piece(self, tid: int) -> str:
+        return f"<{tid}>"
+
+
+class NativeTokenizer:
+    """tokenizer.json through the native BPE tokenizer (the reference runs a pool of tokenizer workers,
+    router_v2/src/validation.rs:152-305; here `encode` releases the GIL and runs on the router's thread pool)."""
+
+    def __init__(self, path: str):
+        self.t = core.Tokenizer.from_file(path)
+        self.vocab = self.t.num_ids()
+
+    def encode(self, text: str) -> List[int]:
+        return list(self.t.encode(text))
+
+    def decode(self, ids: List[int]) -> str:
+        return self.t.decode(list(ids), True)
+
+    def piece(self, tid: int) -> str:
+        return self.t.decode([tid], False)
 
 
 def _pct(xs: List[float], q: float) -> float:
@@ -86,9 +108,11 @@ class Metrics:
 
 class RouterApp:
     def __init__(self, rt: RouterRuntime, *, model_name: str = "llama3_8b", max_input_length: int = 4095,
-                 max_total_tokens: int = 4096, max_concurrent: int = 4096, vocab: int = 32000):
+                 max_total_tokens: int = 4096, max_concurrent: int = 4096, vocab: int = 32000,
+                 tokenizer_path: str = "", tokenizer_workers: int = 2):
         self.rt = rt
-        self.tok = WordHashTokenizer(vocab)
+        self.tok = NativeTokenizer(tokenizer_path) if tokenizer_path else WordHashTokenizer(vocab)
+        self.tok_pool = ThreadPoolExecutor(max_workers=max(1, tokenizer_workers), thread_name_prefix="tokenizer")
         self.limits = core.ValidationLimits()
         self.limits.max_input_length, self.limits.max_total_tokens = max_input_length, max_total_tokens
         self.model_name = model_name
@@ -107,12 +131,12 @@ class RouterApp:
         r.add_post("/modify_cluster_state", self.modify_cluster_state)
 
     # ------------------------------------------------------------------ request parsing
-    def _parse(self, body: dict):
+    async def _parse(self, body: dict):
         p = body.get("parameters") or {}
         if "input_tokens" in body:
             toks = [int(t) for t in body["input_tokens"]]
         else:
-            toks = self.tok.encode(body.get("inputs", ""))
+            toks = await asyncio.get_running_loop().run_in_executor(self.tok_pool, self.tok.encode, body.get("inputs", ""))
         g = core.GenerateParams()
         g.input_len = len(toks)
         g.max_new_tokens = int(p.get("max_new_tokens", 20))
@@ -186,7 +210,7 @@ class RouterApp:
             body = await req.json()
         except Exception:  # noqa: BLE001
             return web.json_response({"error": "invalid JSON", "error_type": "validation"}, status=422)
-        toks, g, err = self._parse(body)
+        toks, g, err = await self._parse(body)
         if err:
             self.metrics.counters["blitz_request_failure"] += 1
             return web.json_response({"error": err, "error_type": "validation"}, status=422)
@@ -201,13 +225,13 @@ class RouterApp:
         details = None
         if (body.get("parameters") or {}).get("details"):
             details = {"finish_reason": "length", "generated_tokens": len(out),
-                       "tokens": [{"id": t, "text": f"<{t}>", "logprob": 0.0, "special": False} for t in out]}
+                       "tokens": [{"id": t, "text": self.tok.piece(t), "logprob": 0.0, "special": False} for t in out]}
         return web.json_response({"generated_text": self.tok.decode(out), "details": details},
                                  headers={k: str(v) for k, v in stats.items()})
 
     async def generate_stream(self, req: web.Request) -> web.StreamResponse:
         body = await req.json()
-        toks, g, err = self._parse(body)
+        toks, g, err = await self._parse(body)
         if err:
             return web.json_response({"error": err, "error_type": "validation"}, status=422)
         resp = web.StreamResponse(headers={"Content-Type": "text/event-stream", "Cache-Control": "no-cache"})
@@ -219,7 +243,7 @@ class RouterApp:
                     out, _ = done
                     continue
                 n += 1
-                ev = {"token": {"id": tok, "text": f"<{tok}>", "logprob": 0.0, "special": False},
+                ev = {"token": {"id": tok, "text": self.tok.piece(tok), "logprob": 0.0, "special": False},
                       "generated_text": None, "details": None}
                 if final:
                     ev["details"] = {"finish_reason": "length", "generated_tokens": n}
@@ -307,6 +331,8 @@ def main(argv=None) -> None:
     ap.add_argument("--tensor-parallel-size", type=int, default=1)
     ap.add_argument("--model-name", default="llama3_8b")
     ap.add_argument("--model-path", default="")
+    ap.add_argument("--tokenizer-path", default="", help="tokenizer.json; without it words are hashed to ids")
+    ap.add_argument("--validation-workers", type=int, default=2)
     ap.add_argument("--max-input-length", type=int, default=4095)
     ap.add_argument("--max-total-tokens", type=int, default=4096)
     ap.add_argument("--max-batch-prefill-tokens", type=int, default=8192)
@@ -340,7 +366,8 @@ def main(argv=None) -> None:
     layers = get_config(a.model_name).layers
     rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path)
     asyncio.run(serve_router(rt, a.hostname, a.port, model_name=a.model_name, max_input_length=a.max_input_length,
-                             max_total_tokens=a.max_total_tokens))
+                             max_total_tokens=a.max_total_tokens, tokenizer_path=a.tokenizer_path,
+                             tokenizer_workers=a.validation_workers))
 
 
 if __name__ == "__main__":

@@ -3,11 +3,15 @@
 protobuf classes; no generated code is involved."""
 from __future__ import annotations
 
+import contextvars
 from typing import Iterable, Optional, Sequence
 
 import grpc
 
 from ..pb.schema import RPCS, method_path, pb
+from ..utils.tracing import grpc_metadata
+
+CURRENT_TRACE: contextvars.ContextVar = contextvars.ContextVar("blitz_traceparent", default=None)
 
 
 def encode_prefill_case(*cases: int) -> int:
@@ -30,6 +34,9 @@ class WorkerStub:
                                                     response_deserializer=getattr(pb, res).FromString)
 
     async def call(self, rpc: str, request, timeout: Optional[float] = None, metadata=None):
+        if metadata is None:
+            # trace context of the operation this call belongs to (set by the router runtime per dispatched op)
+            metadata = grpc_metadata(CURRENT_TRACE.get())
         return await self._m[rpc](request, timeout=timeout, metadata=metadata)
 
     async def close(self):

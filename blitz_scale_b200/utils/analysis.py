@@ -21,7 +21,7 @@ from ..models.config import get_config
 _TRANS = re.compile(r"Replica<(\d+)> (\w+) => (\w+)")
 _METRIC = re.compile(r"System Metrics: prefill_tokens: (\d+), decode_tokens: (\d+)")
 _SIGNAL = re.compile(r"Control signal: P([+-]\d+) D([+-]\d+)")
-_STAMP = re.compile(r"^\[?(\d+\.\d+)\]?")
+_STAMP = re.compile(r"^\[?\s*(\d+\.\d+)\]?")
 
 
 def parse_router_log(lines: Iterable[str]) -> dict:

@@ -17,6 +17,7 @@ memory (`parallel/symm.py`) instead of RDMA / NCCL calls:
 """
 from __future__ import annotations
 
+import logging
 import threading
 import time
 from concurrent.futures import Future
@@ -35,6 +36,7 @@ from ..runtime.engine import Engine
 from .service import Backend, make_generation
 
 CTL_SLOT_WORDS = 16384  # page ids one transfer slot can publish
+log = logging.getLogger("blitz.worker")
 
 
 class GpuBackend(Backend):
@@ -69,7 +71,6 @@ class GpuBackend(Backend):
         self.units = [(n, o, b) for n, o, b in self.engine.seg.layout.units]
         self.batches: Dict[int, "core.Batch"] = {}
         self.param_expected = 0      # cumulative flag value that means "all stripes of the current transfer landed"
-        self.kv_slot_count = [0] * symm.KV_SLOTS
         self.host_mirror: Optional[torch.Tensor] = None
         # live execution
         L = self.cfg.layers
@@ -84,6 +85,10 @@ class GpuBackend(Backend):
         torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ helpers
+    def thread_init(self) -> None:
+        # the CUDA current device is per thread and defaults to device 0
+        torch.cuda.set_device(self.device)
+
     def info(self) -> dict:
         return {"ready": self.engine.status.fully_loaded(), "dtype": "bfloat16", "device_type": "cuda",
                 "ranks": {"rank": self.rank, "world": self.world, "tp": self.tp}}
@@ -218,10 +223,13 @@ class GpuBackend(Backend):
                 eng.runner.res = self.zag_slots[task["slot"]]
                 try:
                     if d.step == core.ZagStep.Embed:
+                        log.debug("zag embed batch=%d", d.batch_id)
                         eng.runner.embed(m)
                     elif d.step == core.ZagStep.Layer:
+                        log.debug("zag layer batch=%d layer=%d", d.batch_id, d.layer)
                         eng.runner.run_layer(d.layer, m)
                     else:
+                        log.debug("zag head batch=%d", d.batch_id)
                         toks = eng._tokens_to_host(eng.runner.head(m), b.size)
                     torch.cuda.current_stream().synchronize()
                 finally:
@@ -242,6 +250,7 @@ class GpuBackend(Backend):
             task = self.zag_tasks.pop(r.batch_id)
             b = task["batch"]
             k = max(0, r.next_layer)
+            log.info("zag relay batch=%d layer=%d +>+> rank %d", r.batch_id, k, rank)
             if k > 0:
                 # ship the residual stream [T, hidden] into the old instance's mailbox slot and flag it
                 T = r.num_tokens
@@ -289,6 +298,8 @@ class GpuBackend(Backend):
                 b.decode = True
                 self.batches[batch.id] = b
             lo, hi = self._layer_range(partial, num_layer)
+            half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
+            log.info("batch %d immigrate start%s layers [%d,%d) <~- rank %s", batch.id, half, lo, hi, list(src))
             if hi > lo and self.fabric is not None:
                 # publish the destination page ids of the prompt pages, then wait for the layers to land
                 ps = self.engine.page_size
@@ -303,6 +314,7 @@ class GpuBackend(Backend):
                     self.fabric.wait_flag(symm.KV_FLAG0 + slot * symm.MAX_LAYERS + l, want[l], budget_ms=10000)
                 torch.cuda.current_stream().synchronize()
                 ops.check_status()
+            log.info("batch %d immigrate done%s", batch.id, half)
             return pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
 
     def _kv_want(self, slot, lo, hi):
@@ -326,6 +338,8 @@ class GpuBackend(Backend):
             my = src.index(self.rank) if self.rank in src else self.rank % self.tp
             peer = dst[my]
             slot = batch.id % symm.KV_SLOTS
+            half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
+            log.info("batch %d migrate start%s layers [%d,%d) -~> rank %d", batch.id, half, lo, hi, peer)
             if hi > lo:
                 import ctypes
                 ps = self.engine.page_size
@@ -351,6 +365,7 @@ class GpuBackend(Backend):
                 torch.cuda.current_stream().synchronize()
                 ops.check_status()
             cb = pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+            log.info("batch %d migrate done%s", batch.id, half)
             self.batches.pop(batch.id, None)
             b.clear()
             return cb
@@ -373,6 +388,7 @@ class GpuBackend(Backend):
 
     def _receive_params(self, n_stripes: int, timeout_s: float = 120.0) -> None:
         """Poll this GPU's own flag pad and mark units ready in arrival order."""
+        torch.cuda.set_device(self.device)
         with self.lock:
             self.engine.status.reset()
             base = self.param_expected

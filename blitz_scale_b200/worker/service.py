@@ -12,6 +12,7 @@ iteration that travelled with a migrated batch, then merges all named batches in
 from __future__ import annotations
 
 import asyncio
+import logging
 import time
 from concurrent.futures import ThreadPoolExecutor
 from typing import Dict, Optional
@@ -21,11 +22,17 @@ import grpc
 from ..pb.schema import FULL_SERVICE, RPCS, pb
 
 
+log = logging.getLogger("blitz.worker.rpc")
+
+
 class Backend:
     """What a worker must be able to do; see gpu_backend.GpuBackend and sim.stub_worker.StubBackend."""
 
     rank = 0
     world = 1
+
+    def thread_init(self) -> None:
+        """Runs once in every handler thread (a GPU backend binds the thread to its device)."""
 
     def info(self) -> dict: ...
     def prefill(self, batch, forward_case: int, pp_info, pipe_peer): ...
@@ -50,7 +57,8 @@ class TextGenerationService:
     def __init__(self, backend: Backend, urls=None):
         self.b = backend
         self.urls = list(urls or [])
-        self.pool = ThreadPoolExecutor(max_workers=32, thread_name_prefix=f"worker{backend.rank}")
+        self.pool = ThreadPoolExecutor(max_workers=32, thread_name_prefix=f"worker{backend.rank}",
+                                       initializer=backend.thread_init)
         self._zag_next = 0
         self._zag_cv = asyncio.Condition()
 
@@ -222,9 +230,19 @@ class TextGenerationService:
     # ------------------------------------------------------------------ wiring
     def generic_handler(self) -> grpc.GenericRpcHandler:
         handlers = {}
+        def traced(rpc, fn):
+            # the router sends a W3C traceparent with every call; one debug line per RPC lets merged logs follow a
+            # request across processes
+            async def call(req, ctx):
+                if log.isEnabledFor(logging.DEBUG):
+                    tp = dict(ctx.invocation_metadata() or ()).get("traceparent", "")
+                    log.debug("rpc %s rank=%d traceparent=%s", rpc, self.b.rank, tp)
+                return await fn(req, ctx)
+            return call
+
         for rpc, (req, res) in RPCS.items():
             handlers[rpc] = grpc.unary_unary_rpc_method_handler(
-                getattr(self, rpc), request_deserializer=getattr(pb, req).FromString,
+                traced(rpc, getattr(self, rpc)), request_deserializer=getattr(pb, req).FromString,
                 response_serializer=getattr(pb, res).SerializeToString)
         return grpc.method_handlers_generic_handler(FULL_SERVICE, handlers)
 

@@ -1,0 +1,196 @@
+// Host-side stress of the native core, meant to be built with -fsanitize=address,undefined and with
+// -fsanitize=thread (tests/test_sanitizers.py does both):
+//   1. page pool: random allocate / release with the accounting invariants checked at every step;
+//   2. controller inside the virtual-time cluster simulator: a bursty trace with live scaling and a replica
+//      failure in the middle; every request must finish, no KV block may leak;
+//   3. the device protocols, emulated with CPU threads on std::atomic (what the kernels do with
+//      st.release / ld.acquire and tickets):
+//        a. unit copy: producer writes a unit, then release-adds 1 to its flag; consumers acquire-poll with a
+//           bounded spin, read the unit, and the single consumer that owns the flag resets it;
+//        b. split-K tickets: every contributor stores its partial, takes a ticket (acq_rel); the last one sums the
+//           partials in index order and resets the ticket.
+//      ThreadSanitizer checks that the data accesses are ordered by those atomics.
+#include <atomic>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <thread>
+#include <vector>
+
+#include "runtime/kv_pool.h"
+#include "sim/cluster_sim.h"
+#include "sim/trace.h"
+
+using namespace blitz;
+
+#define CHECK(cond)                                                            \
+  do {                                                                         \
+    if (!(cond)) {                                                             \
+      std::fprintf(stderr, "CHECK failed: %s (%s:%d)\n", #cond, __FILE__, __LINE__); \
+      std::exit(1);                                                            \
+    }                                                                          \
+  } while (0)
+
+static void pool_fuzz() {
+  PagePool pool(257, 16);
+  std::mt19937 rng(5);
+  std::vector<std::vector<int32_t>> held;
+  int used = 0;
+  for (int it = 0; it < 20000; ++it) {
+    if (held.empty() || rng() % 3) {
+      const int n = static_cast<int>(rng() % 9);
+      std::vector<int32_t> got;
+      const bool ok = pool.allocate(n, got);
+      CHECK(ok == (n <= 257 - used));
+      if (ok) {
+        for (int32_t p : got) CHECK(pool.is_used(p));
+        used += n;
+        held.push_back(std::move(got));
+      }
+    } else {
+      const size_t i = rng() % held.size();
+      pool.release(held[i]);
+      used -= static_cast<int>(held[i].size());
+      held.erase(held.begin() + static_cast<long>(i));
+    }
+    CHECK(pool.used_pages() == used && pool.free_pages() == 257 - used);
+  }
+  bool threw = false;
+  try {
+    pool.release(std::vector<int32_t>(2, 0));   // page 0 is not held (everything was released or never handed out twice)
+  } catch (const std::logic_error&) {
+    threw = true;
+  }
+  CHECK(threw);
+}
+
+static void controller_sim() {
+  ControllerConfig cc;
+  cc.num_ranks = 6;
+  cc.tp = 1;
+  cc.init_states = {"Prefill", "Decode", "Inactive", "Inactive", "Inactive", "Inactive"};
+  cc.features = "impl_blitz,impl_nvl,impl_live";
+  CostModel cm;
+  TraceSpec ts;
+  ts.phases = {{0.0, 4.0}, {3.0, 40.0}, {8.0, 4.0}};
+  ts.cv = 2.0;
+  ts.duration = 12.0;
+  ts.input.a = 400;
+  ts.output.a = 24;
+  ts.seed = 9;
+  const std::vector<TraceItem> trace = generate_trace(ts);
+  {
+    ClusterSim sim(cc, cm);
+    const SimReport rep = sim.run(trace, 0.001, 120.0);
+    CHECK(rep.submitted == trace.size() && rep.completed == rep.submitted && rep.failed == 0);
+    CHECK(rep.leftover_blocks == 0);
+  }
+  {
+    ClusterSim sim(cc, cm);
+    const SimReport rep = sim.run(trace, 0.001, 120.0, /*kill_replica=*/1, /*kill_at=*/5.0);
+    CHECK(rep.submitted == trace.size() && rep.completed + rep.failed == rep.submitted);
+    CHECK(rep.leftover_blocks == 0);
+  }
+}
+
+// ---- 3a: unit copy with per-unit flags -------------------------------------------------------------------
+static void flag_protocol() {
+  constexpr int kUnits = 64, kWords = 1024, kRounds = 20, kReaders = 3;
+  std::vector<uint32_t> buf(static_cast<size_t>(kUnits) * kWords);
+  std::vector<std::atomic<uint32_t>> flags(kUnits);
+  std::atomic<int> readers_done{0};
+  std::atomic<uint32_t> round_go{0};
+  std::atomic<bool> failed{false};
+  for (auto& f : flags) f.store(0);
+
+  auto bounded_wait = [&](std::atomic<uint32_t>& f, uint32_t want) {
+    const auto t0 = std::chrono::steady_clock::now();
+    while (f.load(std::memory_order_acquire) < want) {
+      if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(20)) return false;
+      std::this_thread::yield();
+    }
+    return true;
+  };
+  std::thread producer([&] {
+    for (int r = 1; r <= kRounds; ++r) {
+      // the flag owner re-armed every flag of the previous round before it let us go on
+      if (!bounded_wait(round_go, static_cast<uint32_t>(r - 1))) { failed = true; return; }
+      for (int u = 0; u < kUnits; ++u) {
+        for (int w = 0; w < kWords; ++w) buf[static_cast<size_t>(u) * kWords + w] = static_cast<uint32_t>(r * 1000003 + u * 131 + w);
+        flags[u].fetch_add(1, std::memory_order_release);
+      }
+    }
+  });
+  std::vector<std::thread> readers;
+  for (int k = 0; k < kReaders; ++k)
+    readers.emplace_back([&, k] {
+      for (int r = 1; r <= kRounds; ++r) {
+        for (int u = 0; u < kUnits; ++u) {
+          if (!bounded_wait(flags[u], 1)) { failed = true; return; }
+          for (int w = k; w < kWords; w += 97)
+            if (buf[static_cast<size_t>(u) * kWords + w] != static_cast<uint32_t>(r * 1000003 + u * 131 + w)) failed = true;
+        }
+        // readers meet; reader 0 owns the flags: it re-arms them, then releases the producer into the next round
+        readers_done.fetch_add(1, std::memory_order_acq_rel);
+        while (readers_done.load(std::memory_order_acquire) < kReaders * r) std::this_thread::yield();
+        if (k == 0) {
+          for (auto& f : flags) f.store(0, std::memory_order_relaxed);
+          round_go.store(static_cast<uint32_t>(r), std::memory_order_release);
+        } else {
+          if (!bounded_wait(round_go, static_cast<uint32_t>(r))) { failed = true; return; }
+        }
+      }
+    });
+  producer.join();
+  for (auto& t : readers) t.join();
+  CHECK(!failed.load());
+  // a flag nobody sets: the bounded wait gives up and reports it
+  std::atomic<uint32_t> never{0};
+  const auto t0 = std::chrono::steady_clock::now();
+  while (never.load(std::memory_order_acquire) < 1 && std::chrono::steady_clock::now() - t0 < std::chrono::milliseconds(20)) {}
+  CHECK(never.load() == 0);
+}
+
+// ---- 3b: split-K tickets ---------------------------------------------------------------------------------
+static void ticket_protocol() {
+  constexpr int kSplit = 4, kTiles = 32, kElems = 256, kLaunches = 30;
+  std::vector<float> ws(static_cast<size_t>(kTiles) * kSplit * kElems);
+  std::vector<float> out(static_cast<size_t>(kTiles) * kElems);
+  std::vector<std::atomic<uint32_t>> tickets(kTiles);
+  for (auto& t : tickets) t.store(0);
+  for (int launch = 0; launch < kLaunches; ++launch) {
+    std::vector<std::thread> ctas;
+    for (int s = 0; s < kSplit; ++s)
+      ctas.emplace_back([&, s] {
+        for (int tile = 0; tile < kTiles; ++tile) {
+          float* part = &ws[(static_cast<size_t>(tile) * kSplit + s) * kElems];
+          for (int i = 0; i < kElems; ++i) part[i] = static_cast<float>((launch + 1) * (s + 1)) + 0.25f * static_cast<float>(i % 4);
+          const uint32_t old = tickets[tile].fetch_add(1, std::memory_order_acq_rel);
+          if (old == kSplit - 1) {
+            tickets[tile].store(0, std::memory_order_relaxed);  // ready for the next launch
+            for (int i = 0; i < kElems; ++i) {
+              float acc = 0.f;
+              for (int k = 0; k < kSplit; ++k) acc += ws[(static_cast<size_t>(tile) * kSplit + k) * kElems + i];
+              out[static_cast<size_t>(tile) * kElems + i] = acc;
+            }
+          }
+        }
+      });
+    for (auto& t : ctas) t.join();
+    for (int tile = 0; tile < kTiles; ++tile)
+      for (int i = 0; i < kElems; ++i)
+        CHECK(out[static_cast<size_t>(tile) * kElems + i] == static_cast<float>((launch + 1) * 10) + static_cast<float>(i % 4));
+    for (auto& t : tickets) CHECK(t.load() == 0);
+  }
+}
+
+int main(int argc, char** argv) {
+  const std::string what = argc > 1 ? argv[1] : "all";
+  if (what == "all" || what == "pool") pool_fuzz();
+  if (what == "all" || what == "sim") controller_sim();
+  if (what == "all" || what == "flags") flag_protocol();
+  if (what == "all" || what == "tickets") ticket_protocol();
+  std::printf("core_stress %s: OK\n", what.c_str());
+  return 0;
+}

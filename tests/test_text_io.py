@@ -1,0 +1,135 @@
+"""Native tokenizer, safetensors reader and the Hugging Face -> weight-segment converter (CPU)."""
+import ctypes
+import json
+import os
+
+import pytest
+import torch
+
+from blitz_scale_b200.runtime import core
+
+CORPUS = ["The quick brown fox jumps over the lazy dog. " * 3,
+          "Hello, world! It's 2024 and we're testing tokenizers: 12345 67 8.",
+          "def foo(x):\n    return x + 1\n\n# comment   with   spaces",
+          "naïve café — ünïcödé ✓ 日本語"] * 5
+PROBES = CORPUS[:4] + ["  leading spaces", "tabs\tand\nnewlines\n\n  x", "<|begin|>hi there<|end|>",
+                       "it's we'll I'd 'quoted'", "a1b22c333d4444", "end with space ", "x  y   z", ""]
+
+
+@pytest.fixture(scope="module")
+def trained(tmp_path_factory):
+    tk = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    tok.decoder = decoders.ByteLevel()
+    tr = trainers.BpeTrainer(vocab_size=600, special_tokens=["<|begin|>", "<|end|>"],
+                             initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(CORPUS, tr)
+    p = str(tmp_path_factory.mktemp("tok") / "tokenizer.json")
+    tok.save(p)
+    return tok, p
+
+
+def test_byte_level_bpe_matches_reference_library(trained):
+    """Same ids as the Hugging Face `tokenizers` library on the same tokenizer.json; lossless round trip."""
+    ref, path = trained
+    t = core.Tokenizer.from_file(path)
+    assert t.num_ids() == ref.get_vocab_size()
+    for s in PROBES:
+        ids = t.encode(s)
+        assert ids == ref.encode(s).ids, s
+        assert t.decode(ids, False) == s
+    assert t.decode(t.encode("<|begin|>hi<|end|>"), True) == "hi"
+    assert t.get_id("<|end|>") == ref.token_to_id("<|end|>") and t.get_id("no such token") == -1
+
+
+def test_tokenizer_c_abi(trained):
+    _, path = trained
+    lib = ctypes.CDLL(core._m.__file__)     # the C ABI lives in the same shared object as the Python module
+    lib.blitz_tokenizer_create_from_file.restype = ctypes.c_void_p
+    lib.blitz_tokenizer_encode.restype = ctypes.c_int64
+    lib.blitz_tokenizer_decode.restype = ctypes.c_int64
+    h = ctypes.c_void_p(lib.blitz_tokenizer_create_from_file(path.encode()))
+    assert h.value
+    text = "Hello, world! 123".encode()
+    buf = (ctypes.c_int32 * 64)()
+    n = lib.blitz_tokenizer_encode(h, text, ctypes.c_int64(len(text)), buf, ctypes.c_int64(64))
+    assert 0 < n <= 64 and list(buf[:n]) == core.Tokenizer.from_file(path).encode(text.decode())
+    out = ctypes.create_string_buffer(256)
+    m = lib.blitz_tokenizer_decode(h, buf, ctypes.c_int64(n), 1, out, ctypes.c_int64(256))
+    assert out.raw[:m] == text
+    assert lib.blitz_tokenizer_num_ids(h) > 256
+    lib.blitz_tokenizer_free(h)
+    assert lib.blitz_tokenizer_create_from_file(b"/nonexistent/tokenizer.json") is None
+
+
+def test_sentencepiece_style_bpe_with_byte_fallback():
+    vocab = {"<unk>": 0, "<s>": 1, "</s>": 2}
+    for b in range(256):
+        vocab[f"<0x{b:02X}>"] = 3 + b
+    for i, tok in enumerate(["▁", "h", "e", "l", "o", "w", "r", "d", "he", "ll", "hell", "hello", "▁hello",
+                             "▁w", "or", "▁wor", "ld", "▁world"]):
+        vocab[tok] = 259 + i
+    merges = ["h e", "l l", "he ll", "hell o", "▁ hello", "▁ w", "o r", "▁w or", "l d", "▁wor ld"]
+    js = {"model": {"type": "BPE", "vocab": vocab, "merges": merges, "byte_fallback": True, "unk_token": "<unk>"},
+          "normalizer": {"type": "Sequence"}, "pre_tokenizer": None, "decoder": {"type": "Sequence"},
+          "added_tokens": [{"id": 1, "content": "<s>", "special": True}, {"id": 2, "content": "</s>", "special": True}]}
+    t = core.Tokenizer.from_json(json.dumps(js))
+    ids = t.encode("hello world")
+    assert ids == [vocab["▁hello"], vocab["▁world"]]
+    assert t.decode(ids) == "hello world"
+    z = t.encode("hello Z")       # 'Z' is not in the vocabulary -> byte token
+    assert z[-1] == vocab["<0x5A>"] and t.decode(z) == "hello Z"
+    assert t.encode("<s>hello")[0] == 1
+
+
+def test_safetensors_reader_and_hf_conversion(tmp_path):
+    from blitz_scale_b200.models import convert
+    from blitz_scale_b200.models.config import get_config
+    from blitz_scale_b200.models.weights import WeightSegment, shard_from_full
+    cfg = get_config("tiny")
+    seg = WeightSegment(cfg, dtype=torch.bfloat16).random_init_(seed=3)
+    hf = convert.segment_to_hf(seg)
+    # two shard files, like a real checkpoint
+    names = list(hf)
+    convert.write_safetensors(tmp_path / "model-00001-of-00002.safetensors", {n: hf[n] for n in names[:5]}, {"format": "pt"})
+    convert.write_safetensors(tmp_path / "model-00002-of-00002.safetensors", {n: hf[n] for n in names[5:]})
+    f = core.SafeTensorsFile(str(tmp_path / "model-00001-of-00002.safetensors"))
+    assert f.metadata() == [("format", "pt")] and f.names() == names[:5]
+    info = f.info("model.embed_tokens.weight")
+    assert info.dtype == "BF16" and list(info.shape) == [cfg.vocab, cfg.hidden] and info.nbytes == cfg.vocab * cfg.hidden * 2
+    with pytest.raises(KeyError):
+        f.info("missing")
+    back = convert.hf_to_segment(convert.CheckpointReader(tmp_path), cfg)
+    assert torch.equal(back.buffer, seg.buffer)             # byte-exact round trip through HF names and layout
+    paths = convert.convert(tmp_path, "tiny", tmp_path / "out", tp=2)
+    assert len(paths) == 2
+    for r, p in enumerate(paths):
+        want = shard_from_full(seg, 2, r, device="cpu")
+        got = torch.from_file(str(p), size=want.layout.total_bytes, dtype=torch.uint8)
+        assert torch.equal(got, want.buffer[:want.layout.total_bytes])
+        WeightSegment.check_sidecar(p.parent, cfg, 2, r, torch.bfloat16)
+    # a truncated file is rejected, not mis-read
+    raw = (tmp_path / "model-00002-of-00002.safetensors").read_bytes()
+    (tmp_path / "bad.safetensors").write_bytes(raw[:len(raw) // 2])
+    with pytest.raises(RuntimeError):
+        core.SafeTensorsFile(str(tmp_path / "bad.safetensors"))
+
+
+def test_native_logger_and_contracts(tmp_path):
+    import subprocess
+    import sys
+    code = ("from blitz_scale_b200.runtime import core\n"
+            "core.native_log(2, 'hello info'); core.native_log(1, 'hidden debug'); core.native_log(4, 'bad thing')\n"
+            "assert core.native_log_enabled(2) and not core.native_log_enabled(1)\n"
+            "core.set_native_log_level('trace'); core.native_log(0, 'now visible')\n"
+            "core.check_precondition(True)\n"
+            "try:\n    core.check_precondition(False)\n    raise SystemExit(3)\nexcept RuntimeError as e:\n    assert 'precondition failed: ok' in str(e)\n")
+    logf = tmp_path / "rank0.log"
+    env = dict(__import__("os").environ, BLITZ_LOG_FILE=str(logf), LOG_LEVEL="info")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    text = logf.read_text()
+    assert "INFO  python:0 hello info" in text and "hidden debug" not in text and "ERROR python:0 bad thing" in text
+    assert "TRACE python:0 now visible" in text and "precondition failed" in text
