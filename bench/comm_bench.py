@@ -51,7 +51,7 @@ def timed(fn, rank_world, iters=3, warmup=1):
     return best
 
 
-def bench_multicast(fab, rank, world, total_bytes, out, ctas_list=(32, 64, 128)):
+def bench_multicast(fab, rank, world, total_bytes, out, ctas_list=(64, 128, 256)):
     unit = 256 << 20
     n_units = max(1, total_bytes // unit)
     offs = [u * unit for u in range(n_units)]
@@ -99,12 +99,20 @@ def bench_multicast(fab, rank, world, total_bytes, out, ctas_list=(32, 64, 128))
             fab.reset_param_flags()
             torch.cuda.synchronize()
             dist.barrier()
-            t = run(n_dst, "peer_st", 64, n_src=2)
-            if rank == 0:
-                row = dict(kind="multicast", mode="two_source_stripes", n_dst=n_dst, ctas=64, gb=total_bytes / 1e9,
-                           ms=t * 1e3, gbs_per_dst=total_bytes / t / 1e9, frac_of_900=total_bytes / t / LINK_NOMINAL)
-                out.append(row)
-                print(json.dumps(row), flush=True)
+            for mode, name in (("peer_st", "two_source_stripes"), ("multimem", "two_source_multimem")):
+                if mode == "multimem" and not fab.weights.mc_ptr:
+                    continue
+                fab.reset_param_flags()
+                torch.cuda.synchronize()
+                dist.barrier()
+                t = run(n_dst, mode, 128, n_src=2)
+                ops.check_status()
+                if rank == 0:
+                    row = dict(kind="multicast", mode=name, n_dst=n_dst, ctas=128, gb=total_bytes / 1e9,
+                               ms=t * 1e3, gbs_per_dst=total_bytes / t / 1e9, frac_of_900=total_bytes / t / LINK_NOMINAL,
+                               frac_of_measured_770=total_bytes / t / LINK_MEASURED)
+                    out.append(row)
+                    print(json.dumps(row), flush=True)
         # baselines on the same buffer
         buf = fab.weights.local[:total_bytes]
         chain = list(range(0, n_dst + 1))

@@ -31,6 +31,7 @@
 #include "launch.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
+#include <cstdlib>
 #include <type_traits>
 
 namespace blitz {
@@ -54,17 +55,19 @@ struct DecGemmParams {
   int kb_per_split;  // K blocks per CTA of a cluster
   int slice;         // tokens each cluster rank reduces and stores (multiple of 32: TMEM is read 32 columns at a time)
   int static_w;      // weights do not depend on earlier kernels of the stream
+  int smem_bytes;    // dynamic shared memory of this launch (227 KB, or about half of it for two CTAs per SM)
   int* status;
 };
 
 struct DecCfg {
   static constexpr int kMaxStages = 12;
   static constexpr int kBarrierBytes = (2 * kMaxStages + 4) * 8 + 16;
-  static constexpr int kSmemBytes = 227 * 1024;
-  static constexpr int kUsableBytes = kSmemBytes - 1024 - kBarrierBytes;
+  static constexpr int kSmemBytes = 227 * 1024;       // one CTA per SM
+  static constexpr int kSmemBytesHalf = 113 * 1024;   // two CTAs per SM
+  __host__ __device__ static int usable_bytes(int smem_bytes) { return smem_bytes - 1024 - kBarrierBytes; }
   __host__ __device__ static int x_stage_bytes(int npad) { return (npad * kDecBK * 2 + 1023) & ~1023; }
-  __host__ __device__ static int num_stages(int npad, int w_bytes) {
-    const int s = kUsableBytes / (x_stage_bytes(npad) + w_bytes);
+  __host__ __device__ static int num_stages(int npad, int w_bytes, int smem_bytes) {
+    const int s = usable_bytes(smem_bytes) / (x_stage_bytes(npad) + w_bytes);
     return s > kMaxStages ? kMaxStages : s;
   }
   // The epilogue reads TMEM 32 columns at a time, so an accumulator is read up to `extent` columns from its
@@ -134,7 +137,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   const int cols = kHalves * p.npad;  // TMEM columns per accumulator
   const int num_acc = Cfg::num_acc(p.M, p.npad, kHalves, p.split);
   const int tmem_cols = Cfg::tmem_cols(p.M, p.npad, kHalves, p.split);
-  const int S = Cfg::num_stages(p.npad, kWBytes);
+  const int S = Cfg::num_stages(p.npad, kWBytes, p.smem_bytes);
   const int x_stage = Cfg::x_stage_bytes(p.npad);
   const uint32_t idesc = ptx::make_idesc_f16(kFmt, 1u, 0u, kDecTile, static_cast<uint32_t>(p.npad));
 
@@ -143,7 +146,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
   uint8_t* smem_x = smem;
   uint8_t* smem_w = smem + S * x_stage;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kUsableBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::usable_bytes(p.smem_bytes));
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Cfg::kMaxStages;
   uint64_t* tfull_bar = bars + 2 * Cfg::kMaxStages;
@@ -450,28 +453,40 @@ static cudaError_t launch_dec(const CUtensorMap& tx, const CUtensorMap& tw, DecG
                               cudaStream_t stream) {
   auto kern = gemm_decode_kernel<T, EPI>;
   static bool attr_set = false;
-  static int max_clusters[kDecMaxSplit + 1];
+  static int max_clusters[2][kDecMaxSplit + 1];
+  static int occ_env = -1;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DecCfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    for (int s = 2; s <= kDecMaxSplit; ++s)
-      max_clusters[s] = max_active_clusters(kern, dim3(kDecThreads), DecCfg::kSmemBytes, s);
+    for (int s = 2; s <= kDecMaxSplit; ++s) {
+      max_clusters[0][s] = max_active_clusters(kern, dim3(kDecThreads), DecCfg::kSmemBytes, s);
+      max_clusters[1][s] = max_active_clusters(kern, dim3(kDecThreads), DecCfg::kSmemBytesHalf, s);
+    }
+    const char* env = std::getenv("BLITZ_DECODE_OCC");
+    occ_env = env ? std::atoi(env) : 0;
     attr_set = true;
   }
+  const int halves = EPI == 2 ? 2 : 1;
+  const int stage_bytes = DecCfg::x_stage_bytes(p.npad) + halves * kDecTile * kDecBK * 2;
+  // One CTA per SM.  BLITZ_DECODE_OCC=2 runs two CTAs per SM on half the shared memory each (so that one CTA's
+  // set-up or reduction overlaps the other's weight stream); measured on B200 it changes nothing (15.2 vs 15.3 us
+  // at M=16, N=6144, K=4096), so it stays an experiment switch.
+  int occ = 1;
+  if (occ_env == 1 || occ_env == 2) occ = occ_env;
+  if (DecCfg::num_stages(p.npad, halves * kDecTile * kDecBK * 2, DecCfg::kSmemBytesHalf) < 2) occ = 1;
+  p.smem_bytes = occ == 2 ? DecCfg::kSmemBytesHalf : DecCfg::kSmemBytes;
   // K split = cluster size: as many CTAs per tile as it takes to put (nearly) every SM to work, provided all
   // clusters are resident at once and the landing zone of the reduction fits over the pipeline stages
-  const int halves = EPI == 2 ? 2 : 1;
-  int split = split_hint > 0 ? split_hint : sms / p.tiles;
+  int split = split_hint > 0 ? split_hint : (sms * occ) / p.tiles;
   if (split > kDecMaxSplit) split = kDecMaxSplit;
   if (split > p.num_kb) split = p.num_kb;
-  const int stage_area = DecCfg::num_stages(p.npad, halves * kDecTile * kDecBK * 2) *
-                         (DecCfg::x_stage_bytes(p.npad) + halves * kDecTile * kDecBK * 2);
+  const int stage_area = DecCfg::num_stages(p.npad, halves * kDecTile * kDecBK * 2, p.smem_bytes) * stage_bytes;
   while (split > 1) {
     const int slice = (((p.M + split - 1) / split) + 31) & ~31;
     const int64_t zone = (int64_t)split * halves * (slice / 4) * kDecTile * 16;
     const int kbs = (p.num_kb + split - 1) / split;
     const bool every_rank_has_work = (int64_t)kbs * (split - 1) < p.num_kb;
-    if (p.tiles <= max_clusters[split] && zone <= stage_area && every_rank_has_work) break;
+    if (p.tiles <= max_clusters[occ - 1][split] && zone <= stage_area && every_rank_has_work) break;
     --split;
   }
   if (split < 1) split = 1;
@@ -482,9 +497,9 @@ static cudaError_t launch_dec(const CUtensorMap& tx, const CUtensorMap& tw, DecG
   if (split > 1) {
     grid = p.tiles * split;
   } else {
-    grid = p.tiles < sms ? p.tiles : sms;
+    grid = p.tiles < sms * occ ? p.tiles : sms * occ;
   }
-  return launch_pdl_cluster(kern, dim3(grid), dim3(kDecThreads), DecCfg::kSmemBytes, (unsigned)split, stream, tx, tw, p);
+  return launch_pdl_cluster(kern, dim3(grid), dim3(kDecThreads), (size_t)p.smem_bytes, (unsigned)split, stream, tx, tw, p);
 }
 
 }  // namespace blitz

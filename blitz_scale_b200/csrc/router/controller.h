@@ -313,6 +313,7 @@ class Controller {
     s << "System Metrics: prefill_tokens: " << stats_prefill_tokens_ << ", decode_tokens: " << stats_decode_tokens_;
     return s.str();
   }
+  std::pair<uint64_t, uint64_t> token_counts() const { return {stats_prefill_tokens_, stats_decode_tokens_}; }
   size_t inflight_ops() const { return ops_.size(); }
   bool idle() const {
     if (!queue_.empty() || !ops_.empty() || !relayed_.empty()) return false;

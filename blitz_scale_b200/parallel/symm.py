@@ -12,6 +12,7 @@ Flag pad layout (uint32 counters, all zero at boot):
     [0, 128)                      parameter units: embed | layer 0.. | head   (+1 per source stripe)
     [128, 128 + 16)               activation mailbox slots                    (value = sequence tag)
     [256, 256 + KV_SLOTS*LAYERS)  KV push: per (transfer slot, layer)         (+1 per push)
+    [AGREE_FLAG0, +16)            loaded-unit counts published by the TP shards of the replica (plain stores)
 """
 from __future__ import annotations
 
@@ -30,7 +31,8 @@ MAILBOX_FLAG0 = 128
 KV_FLAG0 = 256
 KV_SLOTS = 8
 MAX_LAYERS = 128
-FLAG_WORDS = KV_FLAG0 + KV_SLOTS * MAX_LAYERS
+AGREE_FLAG0 = KV_FLAG0 + KV_SLOTS * MAX_LAYERS    # loaded-unit count of every TP shard of this replica (<= 16)
+FLAG_WORDS = AGREE_FLAG0 + 16
 
 
 def _stream() -> ctypes.c_void_p:

@@ -37,8 +37,13 @@ class LiveRequest:
 
 class RouterRuntime:
     def __init__(self, cfg: "core.ControllerConfig", worker_urls: List[str], model_layers: int = 32,
-                 model_path: str = ""):
+                 model_path: str = "", stat_csv: str = ""):
         self.cfg = cfg
+        # 500 ms CSV of prefill / decode token deltas (router_v2/src/statistic.rs:26-63)
+        self.stat_csv = open(stat_csv, "w", buffering=1) if stat_csv else None
+        if self.stat_csv:
+            self.stat_csv.write("time_s,prefill_tokens,decode_tokens\n")
+        self._stat_last = (0.0, 0, 0)
         self.ctl = core.Controller(cfg)
         self.stubs = [WorkerStub(u) for u in worker_urls]
         self.tp = cfg.tp
@@ -91,9 +96,18 @@ class RouterRuntime:
                     self.transitions.append((now, line))
             for a in actions:
                 self._dispatch(a)
+            if self.stat_csv is not None and now - self._stat_last[0] >= 0.5:
+                p_tok, d_tok = self.ctl.token_counts()
+                self.stat_csv.write(f"{now:.3f},{p_tok - self._stat_last[1]},{d_tok - self._stat_last[2]}\n")
+                self._stat_last = (now, p_tok, d_tok)
             if now - last_metrics >= 1.0:
                 last_metrics = now
                 log.info(self.ctl.system_metrics_line())
+                if log.isEnabledFor(logging.DEBUG):
+                    for r in range(self.ctl.num_replicas):
+                        m = self.ctl.metric(r)
+                        log.debug("Replica<%d> state=%s used_blocks=%d model_loaded=%s", r, self.ctl.state_name(r),
+                                  m.used_blocks, m.model_loaded)
             if not actions:
                 self.wake.clear()
                 try:

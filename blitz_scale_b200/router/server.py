@@ -349,6 +349,7 @@ def main(argv=None) -> None:
     ap.add_argument("--scale-down-threshold-millis", type=float, default=333)
     ap.add_argument("--mock-load-millis", type=float, default=0)
     ap.add_argument("--log-level", default="INFO")
+    ap.add_argument("--statistic-csv", default="", help="write prefill/decode token deltas every 500 ms to this file")
     a = ap.parse_args(argv)
     logging.basicConfig(level=a.log_level, format="%(asctime)s %(name)s %(message)s")
     from ..models.config import get_config
@@ -364,7 +365,7 @@ def main(argv=None) -> None:
         migration_upper=a.migration_upper_bound, min_prefill=a.min_prefill_num, max_prefill=a.max_prefill_num,
         min_decode=a.min_decode_num, max_decode=a.max_decode_num, scale_down_threshold_ms=a.scale_down_threshold_millis)
     layers = get_config(a.model_name).layers
-    rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path)
+    rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv)
     asyncio.run(serve_router(rt, a.hostname, a.port, model_name=a.model_name, max_input_length=a.max_input_length,
                              max_total_tokens=a.max_total_tokens, tokenizer_path=a.tokenizer_path,
                              tokenizer_workers=a.validation_workers))

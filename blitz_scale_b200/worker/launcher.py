@@ -44,6 +44,9 @@ def parse_args(argv=None):
     ap.add_argument("--log-dir", default="")
     ap.add_argument("--time-to-live", type=float, default=0.0, help="exit after this many seconds (0 = run until signalled)")
     ap.add_argument("--multimem", action="store_true", help="multicast parameter stores through NVLS when available")
+    ap.add_argument("--ibv-rate", type=int, default=0, help="accepted for command-line compatibility; an NVSwitch box has "
+                    "no NIC to rate-limit")
+    ap.add_argument("--no-numa-bind", action="store_true", help="do not pin host threads to the CPU cores next to the GPU")
     return ap.parse_args(argv)
 
 
@@ -61,6 +64,12 @@ def main(argv=None) -> int:
         os.dup2(f.fileno(), 2)
     logging.basicConfig(level=os.environ.get("LOG_LEVEL", "INFO").upper(), format="%(asctime)s %(name)s %(message)s")
     torch.cuda.set_device(local)
+    if not a.no_numa_bind:
+        # host threads, pinned staging buffers and the disk loader should live on the GPU's NUMA node (the reference
+        # binds ranks 0-3 / 4-7 to node 0 / 1, src/server/disaggregate.cc)
+        from ..utils.topology import bind_to_gpu_cpus
+        cpus = bind_to_gpu_cpus(local)
+        logging.getLogger("blitz.worker").info("rank %d bound to %d CPU cores next to GPU %d", rank, len(cpus), local)
     cluster = json.load(open(a.config))
     states = cluster["init_states"]
     if len(states) != world:
@@ -80,7 +89,7 @@ def main(argv=None) -> int:
     backend = GpuBackend(rank, world, a.model_name, tp=tp, num_pages=a.num_total_blocks, page_size=a.page_size,
                          max_batch=a.max_batch_size, max_batch_tokens=a.max_batch_tokens,
                          ready=states[rank] != "Inactive", tp_group=tp_group, model_path=a.model_path,
-                         seed=rank // tp if False else 0, use_multimem=a.multimem)
+                         seed=0, use_multimem=a.multimem)
     urls = [f"{a.host}:{a.port + r}" for r in range(world)]
 
     async def run():
@@ -94,8 +103,10 @@ def main(argv=None) -> int:
 
     asyncio.run(run())
     backend.close()
+    sys.stdout.flush()
+    sys.stderr.flush()
     if world > 1:
-        dist.destroy_process_group()
+        os._exit(0)      # tearing down NCCL / symmetric memory with live CUDA graphs can block for minutes
     return 0
 
 

@@ -46,6 +46,7 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    host_group = dist.new_group(backend="gloo")     # host-side rendezvous that keeps no kernel spinning on the GPUs
     from blitz_scale_b200.worker.gpu_backend import GpuBackend
     from blitz_scale_b200.worker.service import serve
     states = {"pd": ["Prefill", "Decode"], "scale": ["Prefill", "Decode", "Inactive"],
@@ -86,12 +87,12 @@ def main():
             import traceback
             traceback.print_exc()
             ok = 0
-    flag = torch.tensor([ok], device="cuda")
-    dist.broadcast(flag, 0)      # the other ranks keep serving until rank 0 is done
+    flag = torch.tensor([ok])
+    dist.broadcast(flag, 0, group=host_group)      # blocks on the host: the other ranks keep serving until rank 0 is done
     stop_holder["loop"].call_soon_threadsafe(stop_holder["stop"].set)
     th.join(10)
     backend.close()
-    dist.barrier()
+    dist.barrier(group=host_group)
     good = int(flag) == 1
     if rank == 0 and good:
         print(f"cluster {case}: OK on {world} GPUs", flush=True)

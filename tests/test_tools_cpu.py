@@ -157,3 +157,33 @@ def test_tracing_helpers(tmp_path):
     p.write_text("\n".join(log))
     assert tracing.main([str(p), "-o", str(tmp_path / "t.json")]) == 0
     assert json.loads((tmp_path / "t.json").read_text())["traceEvents"]
+
+
+def test_tp_load_agreement():
+    """Shards of a replica act on the minimum of their published loaded-unit counts."""
+    from blitz_scale_b200.parallel.agreement import LoadAgreement
+
+    class FakeFabric:
+        def __init__(self, world, rank, pads):
+            self.rank, self.pads = rank, pads
+        def set_flag(self, rank, index, value, add=False):
+            self.pads[rank][index] = self.pads[rank].get(index, 0) + value if add else value
+        def read_flags(self, start, count):
+            return [self.pads[self.rank].get(start + i, 0) for i in range(count)]
+
+    pads = {r: {} for r in range(4)}
+    L, F0 = 4, 1000
+    a = [LoadAgreement(FakeFabric(4, r, pads), [2, 3], r, F0, L) for r in (2, 3)]
+    for x in a:
+        x.publish(0)
+    assert a[0].agreed_state() == (False, 0, False)
+    a[0].publish(3)                      # shard 0 has embed + 2 layers, shard 1 nothing yet
+    assert a[0].agreed_units() == 0 and a[1].agreed_units() == 0
+    a[1].publish(2)
+    assert a[0].agreed_state() == (True, 1, False) and a[1].agreed_state() == (True, 1, False)
+    a[0].publish(L + 2)
+    a[1].publish(L + 1)
+    assert a[1].agreed_state() == (True, L, False)
+    a[1].publish(L + 2)
+    assert a[0].agreed_state() == (True, L, True)
+    assert 0 not in pads[0] and F0 not in pads[0]          # nothing leaks to other replicas' pads
