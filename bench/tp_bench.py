@@ -103,13 +103,30 @@ def main():
         err = float((y.float() - ref.float()).norm() / ref.float().norm())
         t_f = graph_time(run_fused)
         ops.check_status()
+        # where the fused chain spends its time: events between the three launches (eager, so each stage carries a
+        # host launch; meaningful for the large case)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        dist.barrier()
+        torch.cuda.synchronize()
+        ev[0].record()
+        exp = fused.gemm_rs(x, w_row, 0)
+        ev[1].record()
+        fused.reduce_norm(0, exp, rpr, res, norm_w, 1, 1e-5)
+        ev[2].record()
+        fused.ag_gemm(1, M, w_col, y)
+        ev[3].record()
+        torch.cuda.synchronize()
+        stages = torch.tensor([ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(3)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(stages, op=dist.ReduceOp.MAX)
+        stages = [round(float(v), 1) for v in stages]
         t_n = graph_time(run_nccl)
         fl = 2.0 * M * H * (H // tp) * 2            # two GEMMs per rank
         wire = (M * H * 2) * (tp - 1) / tp * 2      # reduce-scatter out + all-gather out, bytes each GPU sends
         roof = max(fl / flops_peak, wire / 770e9)
         if rank == 0:
             row = dict(kind="tp_pair", tp=tp, M=M, K=H, N=H, fused_us=t_f * 1e6, nccl_us=t_n * 1e6, speedup=t_n / t_f,
-                       roofline_us=roof * 1e6, fused_frac_of_roofline=roof / t_f, rel_err_vs_nccl=err, peaks=src)
+                       roofline_us=roof * 1e6, fused_frac_of_roofline=roof / t_f, rel_err_vs_nccl=err, peaks=src,
+                       stage_us_gemm_rs_reduce_norm_ag_gemm=stages)
             out.append(row)
             print(json.dumps(row), flush=True)
     if rank == 0 and a.json:

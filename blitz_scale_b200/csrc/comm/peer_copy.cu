@@ -54,14 +54,18 @@ peer_copy_units_kernel(const uint8_t* __restrict__ src_base, PeerPtrs dst, int n
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x * kUnroll;
     for (int64_t base = v_beg + static_cast<int64_t>(blockIdx.x) * blockDim.x * kUnroll; base < v_end; base += step) {
       uint4 v[kUnroll];
+      // multimem: every warp owns one contiguous 4 KB run (the switch replicates larger contiguous bursts better);
+      // peer stores: the CTA's threads interleave 512-byte rows
+      const int64_t t0 = MULTIMEM ? base + (threadIdx.x >> 5) * (32 * kUnroll) + (threadIdx.x & 31) : base + threadIdx.x;
+      const int64_t tstep = MULTIMEM ? 32 : blockDim.x;
 #pragma unroll
       for (int k = 0; k < kUnroll; ++k) {
-        const int64_t i = base + k * blockDim.x + threadIdx.x;
+        const int64_t i = t0 + k * tstep;
         if (i < v_end) v[k] = ptx::ld_nc_na_v4(src + i);
       }
 #pragma unroll
       for (int k = 0; k < kUnroll; ++k) {
-        const int64_t i = base + k * blockDim.x + threadIdx.x;
+        const int64_t i = t0 + k * tstep;
         if (i < v_end) {
           if (MULTIMEM) {
             ptx::multimem_st_v4(mc_base + units.offset[u] + (i << 4), v[k]);

@@ -20,6 +20,7 @@ from .. import ops
 from ..models.config import ModelConfig, get_config
 from ..models.llama import LlamaRunner, StepMeta, TPComm
 from ..models.weights import WeightSegment
+from ..utils.tracing import nvtx_range
 from . import core
 
 _BUCKETS = [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024]
@@ -122,7 +123,8 @@ class Engine:
         self._h2d(self.layout.page_indices + P)
         lens = [len(s.spec.prompt) for s in batch.seqs]
         m = self._views(T, batch.size, P, True, lens)
-        toks = self.runner.forward(m)
+        with nvtx_range("prefill"):
+            toks = self.runner.forward(m)
         out = self._tokens_to_host(toks, batch.size)
         batch.mark_prefilled()
         batch.append_tokens(out, False)

@@ -151,6 +151,9 @@ class GpuBackend(Backend):
             self.fabric.wait_flag(symm.MAILBOX_FLAG0 + slot, int(b.id) + 1, budget_ms=5000)
             src = self.fabric.mailbox.local[slot * self.slot_bytes:(slot + 1) * self.slot_bytes]
             eng.runner.res[:T].copy_(src.view(torch.bfloat16).view(-1, self.cfg.hidden)[:T])
+            # the slot is consumed: re-arm its flag (stream-ordered after the copy) so that a later batch with a
+            # smaller id cannot pass the wait on a stale value
+            self.fabric.set_flag(self.rank, symm.MAILBOX_FLAG0 + slot, 0, add=False)
             toks = eng.runner.forward(m, lo=start_layer, with_embed=False)
         else:
             toks = eng.runner.forward(m)
