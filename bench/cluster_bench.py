@@ -1,0 +1,201 @@
+"""Whole-system benchmark on real GPUs: scale-out latency and TTFT / TBT under a burst, one rank per GPU.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 4 --master-addr 127.0.0.1 bench/cluster_bench.py \
+        --model llama3_8b --mode live --json out.json
+
+Every rank runs a GPU worker (gRPC service over `GpuBackend`) in a background thread; rank 0 also runs the router
+runtime in-process and replays a synthetic trace through it: a base load on 1 prefill + 1 decode replica, then a
+burst, at the start of which the remaining GPUs are scaled out as prefill replicas.  `--mode`:
+
+    stop   parameters are multicast into the new GPUs, which serve once everything has arrived (impl_blitz + impl_nvl)
+    live   the new GPUs serve while loading (ZigZag: layers they hold run there, the rest on the old instance)
+    sllm   the stand-in for the ServerlessLLM baseline: the new GPUs load the segment file from disk / the host cache
+
+Reported (rank 0, one JSON line): scale-out latency per new replica (manual trigger -> replica takes work; in
+`live` mode that is before its parameters have arrived) and the time until it is fully loaded, router clock,
+parameter bytes per replica, TTFT p50/p99 and TBT p50/p99 over the burst, decode tokens/s.
+Weights are random (same seed everywhere); prompts are random token ids.
+"""
+import argparse
+import asyncio
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def pct(xs, q):
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(q * len(xs)))] if xs else 0.0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama3_8b")
+    ap.add_argument("--mode", default="stop", choices=["stop", "live", "sllm"])
+    ap.add_argument("--base-rate", type=float, default=4.0)
+    ap.add_argument("--burst-rate", type=float, default=24.0)
+    ap.add_argument("--base-s", type=float, default=2.0)
+    ap.add_argument("--burst-s", type=float, default=4.0)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=32)
+    ap.add_argument("--pages", type=int, default=4096)
+    ap.add_argument("--model-path", default="")
+    ap.add_argument("--multimem", action="store_true")
+    ap.add_argument("--port", type=int, default=50600)
+    ap.add_argument("--json", default="")
+    a = ap.parse_args()
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    host_group = dist.new_group(backend="gloo")
+    from blitz_scale_b200.models.config import get_config
+    from blitz_scale_b200.worker.gpu_backend import GpuBackend
+    from blitz_scale_b200.worker.service import serve
+    cfg_model = get_config(a.model)
+    states = ["Prefill", "Decode"] + ["Inactive"] * (world - 2)
+    backend = GpuBackend(rank, world, a.model, tp=1, num_pages=a.pages, page_size=64, max_batch=256, max_batch_tokens=8192,
+                         ready=states[rank] != "Inactive", seed=0, use_multimem=a.multimem, model_path=a.model_path)
+    if states[rank] == "Inactive":
+        backend.engine.seg.buffer.zero_()
+    if a.mode == "sllm" and a.model_path and rank == 0:
+        backend.engine.seg.save(a.model_path)          # the file the cold replicas will load
+    torch.cuda.synchronize()
+    dist.barrier()
+
+    holder, started = {}, threading.Event()
+
+    def serve_thread():
+        async def run():
+            holder["loop"] = asyncio.get_running_loop()
+            holder["stop"] = asyncio.Event()
+            ready = asyncio.Event()
+            t = asyncio.create_task(serve(backend, "127.0.0.1", a.port + rank, stop_event=holder["stop"], ready_event=ready))
+            await ready.wait()
+            started.set()
+            await t
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+        asyncio.run(run())
+
+    th = threading.Thread(target=serve_thread, daemon=True)
+    th.start()
+    started.wait(120)
+    dist.barrier(group=host_group)
+
+    result = None
+    if rank == 0:
+        try:
+            result = run_router(a, world, states, cfg_model, backend)
+        except Exception:  # noqa: BLE001
+            import traceback
+            traceback.print_exc()
+    flag = torch.tensor([1 if result else 0])
+    dist.broadcast(flag, 0, group=host_group)
+    holder["loop"].call_soon_threadsafe(holder["stop"].set)
+    th.join(10)
+    backend.close()
+    dist.barrier(group=host_group)
+    if rank == 0 and result:
+        print(json.dumps(result), flush=True)
+        if a.json:
+            os.makedirs(os.path.dirname(os.path.abspath(a.json)), exist_ok=True)
+            json.dump(result, open(a.json, "w"), indent=1)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0 if int(flag) else 1)
+
+
+def run_router(a, world, states, cfg_model, backend):
+    from blitz_scale_b200.router.runtime import RouterRuntime
+    from blitz_scale_b200.router.server import controller_config_from_cluster
+    feats = {"stop": "impl_blitz,impl_nvl,manually_scale", "live": "impl_blitz,impl_nvl,impl_live,manually_scale",
+             "sllm": "impl_sllm,manually_scale"}[a.mode]
+    cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
+                                         max_blocks_per_replica=a.pages - 64, block_size=64, max_prefill_tokens=8192,
+                                         model_layers=cfg_model.layers)
+    g = torch.Generator().manual_seed(5)
+    n_base, n_burst = int(a.base_rate * a.base_s), int(a.burst_rate * a.burst_s)
+    arrivals = [i / a.base_rate for i in range(n_base)] + [a.base_s + i / a.burst_rate for i in range(n_burst)]
+    prompts = [torch.randint(0, cfg_model.vocab, (a.prompt_len,), generator=g).tolist() for _ in arrivals]
+
+    async def go():
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{a.port + r}" for r in range(world)], model_layers=cfg_model.layers,
+                           model_path=a.model_path)
+        loop_task = asyncio.create_task(rt.run())
+        # warm both serving replicas (graph capture, first-use work) outside the measurement
+        warm = rt.submit(prompts[0], 4)
+        while True:
+            ev = await asyncio.wait_for(warm.queue.get(), timeout=300)
+            if ev[0] == "error" or ev[2]:
+                break
+        records = []
+
+        async def one(i, t_arr):
+            await asyncio.sleep(max(0.0, t_arr - (rt.now() - t_start)))
+            t0 = rt.now()
+            lr = rt.submit(prompts[i], a.new_tokens)
+            times = []
+            while True:
+                ev = await asyncio.wait_for(lr.queue.get(), timeout=300)
+                if ev[0] == "error":
+                    records.append({"i": i, "ok": False})
+                    return
+                times.append(rt.now())
+                if ev[2]:
+                    break
+            tbt = [b - c for b, c in zip(times[1:], times[:-1])]
+            records.append({"i": i, "ok": True, "burst": t_arr >= a.base_s, "ttft": times[0] - t0, "tbt": tbt,
+                            "tokens": len(times), "done": times[-1]})
+
+        t_start = rt.now()
+        tasks = [asyncio.create_task(one(i, t)) for i, t in enumerate(arrivals)]
+        await asyncio.sleep(a.base_s)
+        t_trigger = rt.now()
+        for r in range(2, world):
+            assert rt.ctl.manual_scale(r, "Prefill", rt.now())
+        rt.wake.set()
+        await asyncio.gather(*tasks)
+        t_end = rt.now()
+        scale, loaded = {}, {}
+        for t, line in rt.transitions:
+            for r in range(2, world):
+                if f"Replica<{r}>" not in line or t < t_trigger:
+                    continue
+                if r not in scale and line.rstrip().endswith(("=> Prefill", "=> NewPrefill")):
+                    scale[r] = t - t_trigger              # first moment the replica takes work
+                if line.rstrip().endswith("=> Prefill"):
+                    loaded[r] = t - t_trigger             # all parameters resident, ordinary prefill replica
+        scale = {"serving": scale, "loaded": loaded}
+        await rt.stop()
+        loop_task.cancel()
+        return records, scale, t_start, t_end, [l for _, l in rt.transitions if "boot" not in l]
+
+    records, scale, t_start, t_end, transitions = asyncio.run(go())
+    ok = [r for r in records if r["ok"]]
+    burst = [r for r in ok if r["burst"]]
+    tbt_all = [x for r in burst for x in r["tbt"]]
+    seg_bytes = backend.engine.seg.layout.total_bytes
+    out = {"bench": "cluster_scale_out", "model": a.model, "mode": a.mode, "gpus": world, "requests": len(records),
+           "failed": len(records) - len(ok), "prompt_len": a.prompt_len, "new_tokens": a.new_tokens,
+           "base_rate": a.base_rate, "burst_rate": a.burst_rate,
+           "scale_out_latency_ms": {str(r): round(v * 1e3, 2) for r, v in sorted(scale["serving"].items())},
+           "fully_loaded_ms": {str(r): round(v * 1e3, 2) for r, v in sorted(scale["loaded"].items())},
+           "param_gb_per_replica": round(seg_bytes / 1e9, 3),
+           "effective_gbs_per_replica": {str(r): round(seg_bytes / v / 1e9, 1) for r, v in sorted(scale["loaded"].items()) if v > 0},
+           "ttft_ms_p50": round(pct([r["ttft"] for r in burst], 0.5) * 1e3, 2),
+           "ttft_ms_p99": round(pct([r["ttft"] for r in burst], 0.99) * 1e3, 2),
+           "tbt_ms_p50": round(pct(tbt_all, 0.5) * 1e3, 2), "tbt_ms_p99": round(pct(tbt_all, 0.99) * 1e3, 2),
+           "tokens_per_s": round(sum(r["tokens"] for r in ok) / max(1e-9, t_end - t_start), 1),
+           "transitions": transitions[:24], "timing": "router wall clock (host), one box"}
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -51,7 +51,7 @@ def timed(fn, rank_world, iters=3, warmup=1):
     return best
 
 
-def bench_multicast(fab, rank, world, total_bytes, out, ctas_list=(64, 128, 256)):
+def bench_multicast(fab, rank, world, total_bytes, out, ctas_list=(64, 128, 256), dst_list=None):
     unit = 256 << 20
     n_units = max(1, total_bytes // unit)
     offs = [u * unit for u in range(n_units)]
@@ -78,7 +78,7 @@ def bench_multicast(fab, rank, world, total_bytes, out, ctas_list=(64, 128, 256)
     fab.reset_param_flags()
     torch.cuda.synchronize()
     dist.barrier()
-    for n_dst in range(1, world):
+    for n_dst in (dst_list or range(1, world)):
         for mode in ("peer_st", "multimem"):
             if mode == "multimem" and not fab.weights.mc_ptr:
                 continue
@@ -174,6 +174,8 @@ def main():
     ap.add_argument("--what", default="multicast,kv_push")
     ap.add_argument("--total-gb", type=float, default=4.0)
     ap.add_argument("--json", default="")
+    ap.add_argument("--dst-list", default="", help="destination counts to run (default: 1..world-1)")
+    ap.add_argument("--ctas", default="64,128,256")
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -186,7 +188,8 @@ def main():
         print(json.dumps(dict(kind="info", world=world, multicast_ptr=bool(fab.weights.mc_ptr), total_gb=total / 1e9)), flush=True)
     out = []
     if "multicast" in a.what:
-        bench_multicast(fab, rank, world, total, out)
+        bench_multicast(fab, rank, world, total, out, tuple(int(x) for x in a.ctas.split(",")),
+                        [int(x) for x in a.dst_list.split(",") if x and int(x) < world] or None)
     if "kv_push" in a.what and world >= 2:
         bench_kv_push(fab, rank, world, out)
     if rank == 0 and a.json:

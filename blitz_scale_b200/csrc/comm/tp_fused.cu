@@ -3,7 +3,7 @@
 // Data flow of one row-parallel + column-parallel pair on `tp` GPUs (push model, no collective library):
 //
 //   GEMM (push epilogue)   every rank stores its bf16 partial rows straight into the staging slot
-//                          stage[owner][src_rank][local_row][:] of the rank that owns those rows
+//                          stage[owner][src_rank][column / 8][local_row][8] of the rank that owns those rows
 //                          (sequence-sharded residual), then bumps flag_rs[owner][src] once per tile.
 //   rs_reduce_norm (here)  the owner waits (bounded) for all tiles of all sources, sums the partials in
 //                          rank order in fp32 (deterministic), adds its residual shard, writes the new
@@ -25,7 +25,7 @@ namespace blitz {
 constexpr int kMaxTp = 8;
 
 struct RsReduceParams {
-  const void* stage;        // local staging: [tp][rows_per_rank][H] partials from every source rank
+  const void* stage;        // local staging: [tp][H/8][rows_per_rank][8] partials from every source rank
   uint32_t* flag_rs;        // local: [tp] tiles landed per source (reset here)
   uint32_t expect_tiles;    // tiles each source pushes into this rank per call
   void* residual;           // local residual shard [rows_per_rank][H] (in/out); may be null (no residual)
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const RsReduceParam
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int s = 0; s < p.tp; ++s) {
       float f[8];
-      unpack8<T>(ld_nc16(stage + (static_cast<int64_t>(s) * p.rows_per_rank + row) * H + i * 8), f);
+      unpack8<T>(ld_nc16(stage + ((static_cast<int64_t>(s) * nvec + i) * p.rows_per_rank + row) * 8), f);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] += f[j];
     }
@@ -79,18 +79,19 @@ __global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const RsReduceParam
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) ss += acc[j] * acc[j];
-    if (!res) {  // keep the summed row for pass 2 in the (now consumed) first staging slot
-      *reinterpret_cast<uint4*>(const_cast<T*>(stage) + static_cast<int64_t>(row) * H + i * 8) = pack8<T>(acc);
+    if (!res) {  // keep the summed row for pass 2 where source 0's vector (consumed just above) was
+      *reinterpret_cast<uint4*>(const_cast<T*>(stage) + (static_cast<int64_t>(i) * p.rows_per_rank + row) * 8) = pack8<T>(acc);
     }
   }
   ss = block_sum(ss, red);
   const float scale = rsqrtf(ss / static_cast<float>(H) + p.eps);
-  const T* src = res ? res + roff : stage + static_cast<int64_t>(row) * H;
+  const bool from_stage = res == nullptr;
   const T* w = reinterpret_cast<const T*>(p.norm_w);
   const int64_t grow = static_cast<int64_t>(p.my_rank) * p.rows_per_rank + row;
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
     float f[8], g[8];
-    unpack8<T>(*reinterpret_cast<const uint4*>(src + i * 8), f);
+    const T* src = from_stage ? stage + (static_cast<int64_t>(i) * p.rows_per_rank + row) * 8 : res + roff + i * 8;
+    unpack8<T>(*reinterpret_cast<const uint4*>(src), f);
     unpack8<T>(__ldg(reinterpret_cast<const uint4*>(w) + i), g);
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] = f[j] * scale * g[j];
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__(256) oneshot_reduce_kernel(const OneShotParams
 extern "C" {
 using namespace blitz;
 
-// stage: local [tp][rows_per_rank][hidden]; flag_rs: local uint32[kMaxTp + 1] (zero at start; [kMaxTp] is a ticket);
+// stage: local [tp][hidden / 8][rows_per_rank][8] (the layout the GEMM push epilogue writes); flag_rs: local uint32[kMaxTp + 1] (zero at start; [kMaxTp] is a ticket);
 // xg / flag_ag: tp peer pointers each.  rows_valid <= rows_per_rank local rows are processed.
 int blitz_rs_reduce_norm(const void* stage, uint32_t* flag_rs, uint32_t expect_tiles, void* residual,
                          const void* norm_w, void* const* xg, uint32_t* const* flag_ag, int tp, int my_rank,

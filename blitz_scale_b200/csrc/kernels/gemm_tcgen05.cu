@@ -53,7 +53,7 @@ struct GemmParams {
   unsigned* tickets;  // one per output tile, zero between launches
   int* status;
   // Tensor-parallel fusion.  push epilogue (GEMM -> reduce-scatter): row r of the partial result belongs to
-  // rank r / rows_per_rank and is stored into that rank's staging area [src rank][local row][N] over NVLink;
+  // rank r / rows_per_rank and is stored into that rank's staging area [src rank][N/8][local row][8] over NVLink;
   // one counter per (owner, source) is bumped per finished tile.  wait_flags (all-gather -> GEMM): the TMA
   // producer waits until each of n_wait counters reaches wait_value before its first load of A, whose rows
   // other ranks have stored into local memory.
@@ -137,18 +137,27 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&a
     for (int i = 0; i < 16; ++i) out[i] = pack2<T>(acc[2 * i], acc[2 * i + 1]);
   }
   if (row_ok) {
-    T* dst;
     if (EPI == kEpiPushRS) {
+      // staging layout of the owner: [source rank][8-column vector][local row][8 elements].  The 32 lanes of a warp
+      // hold 32 consecutive rows, so each of these stores is 512 contiguous bytes on the wire (a row-major
+      // staging area would make it 32 separate 16-byte pieces)
       const int owner = row / p.rows_per_rank, lrow = row - owner * p.rows_per_rank;
-      dst = reinterpret_cast<T*>(p.push_base[owner]) +
-            (static_cast<int64_t>(p.tp_rank) * p.rows_per_rank + lrow) * p.N + col0;
-    } else {
-      dst = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc + col0;
-    }
+      const int64_t nvec = p.N >> 3;
+      T* base = reinterpret_cast<T*>(p.push_base[owner]);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (col0 + j * 8 < p.N)
-        *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+      for (int j = 0; j < 4; ++j) {
+        const int64_t vc = (col0 >> 3) + j;
+        if (col0 + j * 8 < p.N)
+          ptx::st_na_v4(base + ((static_cast<int64_t>(p.tp_rank) * nvec + vc) * p.rows_per_rank + lrow) * 8,
+                        make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]));
+      }
+    } else {
+      T* dst = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc + col0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (col0 + j * 8 < p.N)
+          *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+      }
     }
   }
 }

@@ -334,7 +334,7 @@ __device__ __forceinline__ void st_na_v4(void* p, uint4 v) {
 }
 // NVLS: one store replicated by the switch to every GPU bound to the multicast address.
 __device__ __forceinline__ void multimem_st_v4(void* mc_ptr, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y),
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w)
                : "memory");
 }
