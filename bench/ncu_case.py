@@ -41,6 +41,23 @@ def main():
         indptr = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
         for _ in range(3):
             ops.attn_prefill(qkv, indptr, [n] * B, q_heads=32, kv_heads=8, head_dim=128)
+    elif kind == "decode_step":
+        # two eager decode steps of the full model (no CUDA graph), for a per-kernel launch list of one step:
+        #   ncu --metrics gpu__time_duration.sum -k regex:"blitz|gemm|attn|rms|rope|argmax|embedding|sample" ...
+        # The KV pool stays zero (no prefill): the step does the same work on any data.
+        from blitz_scale_b200.runtime import core
+        from blitz_scale_b200.runtime.engine import Engine
+        model = sys.argv[2]
+        B, ctx = map(int, sys.argv[3:5])
+        ps = 64
+        eng = Engine(model, num_pages=B * ((ctx + 16 + ps) // ps + 1) + 8, page_size=ps, max_batch=max(B, 8),
+                     max_batch_tokens=8192, seed=0, use_graphs=False)
+        batch = eng.new_batch(0, [core.SeqSpec(i, [1] * ctx, 16) for i in range(B)])
+        batch.mark_prefilled()
+        batch.append_tokens([1] * B, False)
+        batch.decode = True
+        for _ in range(2):
+            eng.decode(batch)
     torch.cuda.synchronize()
     ops.check_status()
     print("ok")

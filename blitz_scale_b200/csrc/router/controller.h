@@ -273,6 +273,11 @@ class Controller {
       last_plan_ = now;
       run_planner(now);
     }
+    if (!pending_scale_.empty()) {
+      std::vector<std::pair<int, bool>> group;
+      for (auto& pr : pending_scale_) if (reps_[pr.first].m.state == RState::Inactive) group.push_back(pr);
+      if (group.empty() || scale_up_group(group, now)) pending_scale_.clear();  // else: no idle source yet, retry
+    }
     expire_parked(now);
     for (int r = 0; r < num_replicas(); ++r) drive_replica(r, now);
     for (int r = 0; r < num_replicas(); ++r) drive_migration(r, now);
@@ -288,7 +293,10 @@ class Controller {
     if (!st || replica < 0 || replica >= num_replicas()) return false;
     if (*st == RState::Prefill || *st == RState::Decode) {
       if (reps_[replica].m.state != RState::Inactive && reps_[replica].m.state != RState::ShuttingNull) return false;
-      scale_up_one(replica, *st == RState::Prefill, now);
+      if (reps_[replica].m.state == RState::ShuttingNull) { scale_up_one(replica, *st == RState::Prefill, now); return true; }
+      // requests made before the next step() are served by ONE parameter multicast (1 -> N through the switch)
+      for (auto& pr : pending_scale_) if (pr.first == replica) return true;
+      pending_scale_.emplace_back(replica, *st == RState::Prefill);
       return true;
     }
     if (*st == RState::Inactive) { begin_shutdown(replica, now); return true; }
@@ -730,13 +738,16 @@ class Controller {
         }
       }
     }
-    for (; dp > 0; --dp) if (!scale_up(true, now)) break;
-    for (; dd > 0; --dd) if (!scale_up(false, now)) break;
+    std::vector<std::pair<int, bool>> group;
+    for (; dp > 0; --dp) if (!scale_up(true, now, &group)) break;
+    for (; dd > 0; --dd) if (!scale_up(false, now, &group)) break;
+    if (!group.empty()) scale_up_group(group, now);
     if (dp < 0) scale_down(true, now);
     if (dd < 0) scale_down(false, now);
   }
 
-  bool scale_up(bool prefill, double now) {
+  // `group`: inactive replicas chosen so far in this planner turn; they start together (one multicast).
+  bool scale_up(bool prefill, double now, std::vector<std::pair<int, bool>>* group = nullptr) {
     // 1. revive a replica that is shutting down
     const RState shutting = prefill ? RState::ShuttingPrefill : RState::ShuttingDecode;
     for (int r = 0; r < num_replicas(); ++r)
@@ -745,9 +756,86 @@ class Controller {
     for (int r = 0; r < num_replicas(); ++r)
       if (reps_[r].m.state == RState::ShuttingNull) { scale_up_one(r, prefill, now); return true; }
     // 3. bring up an inactive replica
-    for (int r = 0; r < num_replicas(); ++r)
-      if (reps_[r].m.state == RState::Inactive) return scale_up_one(r, prefill, now);
+    for (int r = 0; r < num_replicas(); ++r) {
+      if (reps_[r].m.state != RState::Inactive) continue;
+      if (!group) return scale_up_one(r, prefill, now);
+      bool taken = false;
+      for (auto& pr : *group) taken = taken || pr.first == r;
+      if (taken) continue;
+      group->emplace_back(r, prefill);
+      return true;
+    }
     return false;
+  }
+
+  // Bring several inactive replicas up with one parameter transfer: every idle loaded source (at most two) streams
+  // a stripe of every unit to ALL destinations at once (the worker uses one multimem store per 16 bytes when there
+  // is more than one destination), so the time is that of one transfer whatever the fan-out.  The reference builds
+  // chains and per-destination sends instead (router_v2/src/replica/cybernetics/exec_blitz.rs:21-1198).
+  bool scale_up_group(const std::vector<std::pair<int, bool>>& targets, double now) {
+    if (targets.size() == 1 || features_.has("impl_sllm")) {
+      bool any = false;
+      for (auto& t : targets) any = scale_up_one(t.first, t.second, now) || any;
+      return any;
+    }
+    std::vector<int> sources;
+    auto is_target = [&](int s) { for (auto& t : targets) if (t.first == s) return true; return false; };
+    for (int pass = 0; pass < 2 && sources.empty(); ++pass)
+      for (int s = 0; s < num_replicas(); ++s) {
+        const RState st = reps_[s].m.state;
+        const bool preferred = st == RState::Decode || st == RState::ShuttingDecode || st == RState::ShuttingNull ||
+                               (features_.has("unidirect") && st == RState::Prefill) || reps_[s].colocated;
+        if ((pass == 1 || preferred) && reps_[s].m.model_loaded && !steer_.nvlink_busy(s) && !is_target(s)) sources.push_back(s);
+      }
+    if (sources.empty()) return false;
+    if (sources.size() < 2)  // a second source doubles what each destination can receive
+      for (int s = 0; s < num_replicas() && sources.size() < 2; ++s)
+        if (reps_[s].m.model_loaded && !steer_.nvlink_busy(s) && !is_target(s) && s != sources[0]) sources.push_back(s);
+    if (sources.size() > 2) sources.resize(2);
+    const bool multi = sources.size() > 1;
+    const bool nvl = features_.has("impl_nvl");
+    Action a;
+    a.replica = targets.front().first;
+    a.mock = features_.has("mock_transfer") || features_.has("motiv");
+    a.type = multi ? ActionType::TanzBroadcast : (nvl ? ActionType::NvlBroadcast : ActionType::RdmaBroadcast);
+    Op op;
+    op.replica = a.replica;
+    for (int s2 : sources) {
+      steer_.set_nvlink_busy(s2, true);
+      reps_[s2].m.marker = multi ? RState::TanzCasting : (nvl ? RState::NvlCasting : RState::RdmaCasting);
+      for (int rk : steer_.ranks_of_replica(s2)) a.src_ranks.push_back(rk);
+    }
+    op.sources = sources;
+    bool any_live = false;
+    for (auto& t : targets) {
+      const int r = t.first;
+      Rep& rep = reps_[r];
+      for (int rk : steer_.ranks_of_replica(r)) a.dst_ranks.push_back(rk);
+      op.targets.push_back(r);
+      const bool live = t.second && features_.has("live");
+      if (live) {
+        any_live = true;
+        set_state(r, RState::NewPrefill);
+        rep.zag_started = now;
+        rep.zag_seq = 0;
+        for (int o = 0; o < num_replicas(); ++o) {
+          if (reps_[o].m.state == RState::Prefill && reps_[o].partner < 0 && !reps_[o].colocated) {
+            set_state(o, RState::OldPrefill);
+            reps_[o].partner = r;
+            rep.partner = o;
+            break;
+          }
+        }
+      } else {
+        set_state(r, t.second ? RState::LoadingPrefill : RState::LoadingDecode);
+      }
+    }
+    a.live = any_live;
+    op.kind = a.type;
+    ops_[++next_op_] = op;
+    a.op_id = next_op_;
+    out_.push_back(a);
+    return true;
   }
 
   bool scale_up_one(int r, bool prefill, double now) {
@@ -911,6 +999,7 @@ class Controller {
   std::vector<std::string> log_;
   std::map<std::string, double> counters_, gauges_;
   uint64_t next_op_ = 0;
+  std::vector<std::pair<int, bool>> pending_scale_;  // (replica, as prefill) requested since the last step
   uint64_t stats_prefill_tokens_ = 0, stats_decode_tokens_ = 0;
   double last_plan_ = -1e9;
   ScaleTarget last_target_;

@@ -395,7 +395,9 @@ class GpuBackend(Backend):
             lens = [(b + 15) // 16 * 16 for _, _, b in self.units]
             # one destination: plain peer stores are the fastest (92 % of the measured link rate); several: one
             # multimem store per 16 bytes keeps the source's egress at 1x whatever the fan-out
-            mm = self.use_multimem and len(dests) >= 2 and bool(self.fabric.weights.mc_ptr)
+            # (the multicast address covers every GPU of the box, so it is only usable when all of them hold the
+            # same bytes: with tp > 1 the shards differ between ranks and the copy stays on peer stores)
+            mm = self.use_multimem and self.tp == 1 and len(dests) >= 2 and bool(self.fabric.weights.mc_ptr)
             self.fabric.copy_units(self.fabric.weights, dests, offs, lens, symm.PARAM_FLAG0, stripe=sources.index(self.rank),
                                    n_stripes=len(sources), use_multimem=mm, num_ctas=self.copy_ctas)
             torch.cuda.current_stream().synchronize()

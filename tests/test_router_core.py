@@ -345,3 +345,30 @@ def test_manual_scale_and_log_lines():
     log = ctl.drain_log()
     assert "Replica<2> Inactive => LoadingDecode" in log and "Replica<2> AusDecode => Decode" in log
     assert ctl.system_metrics_line().startswith("System Metrics: prefill_tokens: 0, decode_tokens: 0")
+
+
+def test_simultaneous_scale_ups_share_one_multicast():
+    """Scale-ups requested together become ONE striped multicast: two sources, every new replica a destination."""
+    cfg = _cfg(["Prefill", "Decode"] + ["Inactive"] * 4, "impl_blitz,impl_nvl,manually_scale")
+    ctl = core.Controller(cfg)
+    for r in (2, 3, 4):
+        assert ctl.manual_scale(r, "Prefill", 0.0)
+    assert ctl.manual_scale(5, "Decode", 0.0) and ctl.manual_scale(5, "Decode", 0.0)      # repeated request: once
+    acts = [a for a in ctl.step(0.0) if a.type in (core.ActionType.NvlBroadcast, core.ActionType.TanzBroadcast)]
+    assert len(acts) == 1
+    a = acts[0]
+    assert a.type == core.ActionType.TanzBroadcast and sorted(a.src_ranks) == [0, 1] and a.dst_ranks == [2, 3, 4, 5]
+    assert [ctl.state_name(r) for r in range(2, 6)] == ["LoadingPrefill"] * 3 + ["LoadingDecode"]
+    assert ctl.metric(0).marker == "TanzCasting" and ctl.metric(1).marker == "TanzCasting"
+    assert not [x for x in ctl.step(0.01) if x.type == core.ActionType.TanzBroadcast]              # nothing is re-issued
+    ctl.on_params_done(a.op_id, 0.03)
+    assert [ctl.state_name(r) for r in range(2, 6)] == ["Prefill"] * 3 + ["Decode"]
+    assert ctl.metric(0).marker == "" and ctl.metric(1).marker == ""
+    # live variant: every new prefill replica serves at once; one old prefill replica is paired as the helper
+    cfg = _cfg(["Prefill", "Decode"] + ["Inactive"] * 2, "impl_blitz,impl_nvl,impl_live,manually_scale")
+    ctl = core.Controller(cfg)
+    for r in (2, 3):
+        assert ctl.manual_scale(r, "Prefill", 0.0)
+    acts = [a for a in ctl.step(0.0) if a.type == core.ActionType.TanzBroadcast]
+    assert len(acts) == 1 and acts[0].live and acts[0].dst_ranks == [2, 3]
+    assert ctl.state_name(2) == "NewPrefill" and ctl.state_name(3) == "NewPrefill" and ctl.state_name(0) == "OldPrefill"
