@@ -80,6 +80,10 @@ class GpuBackend(Backend):
         self.zag_slots = torch.empty(4, max_batch_tokens, self.cfg.hidden, dtype=dt, device=self.device)
         self.zag_cv = threading.Condition(self.lock)
         self._stop = False
+        # transfers (parameter copies, KV push / arrival waits, relays) run on their own high-priority stream so that
+        # they overlap the serving kernels of the default stream instead of queueing between decode steps
+        self.side = torch.cuda.Stream(device=self.device, priority=-1)
+        self.xfer_lock = threading.Lock()      # one transfer at a time uses the side stream, the ticket words and a KV slot
         # TP shards of a replica act on the minimum of their loaded-unit counts
         self.agree: Optional[LoadAgreement] = None
         if tp > 1 and self.fabric is not None:
@@ -270,13 +274,14 @@ class GpuBackend(Backend):
                 nbytes = T * self.cfg.hidden * 2
                 nbytes = (nbytes + 15) // 16 * 16
                 slot = r.batch_id % 4
-                stage = self.fabric.mailbox.local[slot * self.slot_bytes:slot * self.slot_bytes + nbytes]
-                stage.copy_(self.zag_slots[task["slot"]].view(torch.uint8).view(-1)[:nbytes])
-                self.fabric.copy_units(self.fabric.mailbox, [rank], [slot * self.slot_bytes], [nbytes],
-                                       symm.MAILBOX_FLAG0 + slot, num_ctas=16)
-                # the flag is a counter; publish the batch tag on top so the reader can wait for ">= id + 1"
-                self.fabric.set_flag(rank, symm.MAILBOX_FLAG0 + slot, int(r.batch_id) + 1, add=False)
-                torch.cuda.current_stream().synchronize()
+                with self.xfer_lock, torch.cuda.stream(self.side):
+                    stage = self.fabric.mailbox.local[slot * self.slot_bytes:slot * self.slot_bytes + nbytes]
+                    stage.copy_(self.zag_slots[task["slot"]].view(torch.uint8).view(-1)[:nbytes])
+                    self.fabric.copy_units(self.fabric.mailbox, [rank], [slot * self.slot_bytes], [nbytes],
+                                           symm.MAILBOX_FLAG0 + slot, num_ctas=16)
+                    # the flag is a counter; publish the batch tag on top so the reader can wait for ">= id + 1"
+                    self.fabric.set_flag(rank, symm.MAILBOX_FLAG0 + slot, int(r.batch_id) + 1, add=False)
+                    self.side.synchronize()
             self.zag.release_slot(task["slot"])
             pp = pb.PipeParaInfo()
             if r.next_layer <= 0:
@@ -313,22 +318,26 @@ class GpuBackend(Backend):
             lo, hi = self._layer_range(partial, num_layer)
             half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
             log.info("batch %d immigrate start%s layers [%d,%d) <~- rank %s", batch.id, half, lo, hi, list(src))
+            cb = pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+            want = None
             if hi > lo and self.fabric is not None:
-                # publish the destination page ids of the prompt pages, then wait for the layers to land
+                # publish the destination page ids of the prompt pages
                 ps = self.engine.page_size
                 ids = [p for s in b.seqs for p in s.pages[:(len(s.spec.prompt) + ps - 1) // ps]]
+                want = list(self._kv_want(slot, lo, hi))
+        if want is not None:
+            # ... then wait for the layers to land, without holding the lock: decode steps of other batches go on
+            with self.xfer_lock, torch.cuda.stream(self.side):
                 words = self.ctl.local.view(torch.int32)
                 words[slot * CTL_SLOT_WORDS:slot * CTL_SLOT_WORDS + len(ids)].copy_(
                     torch.tensor(ids, dtype=torch.int32), non_blocking=False)
                 tag_index = symm.KV_SLOTS * CTL_SLOT_WORDS + slot
                 self._ctl_set(self.rank, tag_index, int(batch.id) + 1)
-                want = self._kv_want(slot, lo, hi)
-                for l in (hi - 1,):
-                    self.fabric.wait_flag(symm.KV_FLAG0 + slot * symm.MAX_LAYERS + l, want[l], budget_ms=10000)
-                torch.cuda.current_stream().synchronize()
-                ops.check_status()
-            log.info("batch %d immigrate done%s", batch.id, half)
-            return pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+                self.fabric.wait_flag(symm.KV_FLAG0 + slot * symm.MAX_LAYERS + hi - 1, want[hi - 1], budget_ms=10000)
+                self.side.synchronize()
+            ops.check_status()
+        log.info("batch %d immigrate done%s", batch.id, half)
+        return cb
 
     def _kv_want(self, slot, lo, hi):
         if not hasattr(self, "_kv_layer_count"):
@@ -353,10 +362,13 @@ class GpuBackend(Backend):
             slot = batch.id % symm.KV_SLOTS
             half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
             log.info("batch %d migrate start%s layers [%d,%d) -~> rank %d", batch.id, half, lo, hi, peer)
-            if hi > lo:
+            ps = self.engine.page_size
+            src_ids = [p for s in b.seqs for p in s.pages[:(len(s.spec.prompt) + ps - 1) // ps]]
+        # the push itself runs outside the lock, on the transfer stream: this batch is parked until it has migrated,
+        # and prefills of other batches continue meanwhile
+        if hi > lo:
+            with self.xfer_lock, torch.cuda.stream(self.side):
                 import ctypes
-                ps = self.engine.page_size
-                src_ids = [p for s in b.seqs for p in s.pages[:(len(s.spec.prompt) + ps - 1) // ps]]
                 src_pages = torch.tensor(src_ids, dtype=torch.int32, device=self.device)
                 # wait until the destination has published its page ids for this batch
                 tag_ptr = self.ctl.ptrs[peer] + (symm.KV_SLOTS * CTL_SLOT_WORDS + slot) * 4
@@ -375,8 +387,9 @@ class GpuBackend(Backend):
                     self.engine.num_pages, ctypes.c_void_p(flags), ctypes.c_void_p(tick.data_ptr()), 0,
                     ctypes.c_void_p(ops.status_word().data_ptr()), symm._stream())
                 symm._check(rc, "blitz_kv_push")
-                torch.cuda.current_stream().synchronize()
-                ops.check_status()
+                self.side.synchronize()
+            ops.check_status()
+        with self.lock:
             cb = pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
             log.info("batch %d migrate done%s", batch.id, half)
             self.batches.pop(batch.id, None)
@@ -398,9 +411,12 @@ class GpuBackend(Backend):
             # (the multicast address covers every GPU of the box, so it is only usable when all of them hold the
             # same bytes: with tp > 1 the shards differ between ranks and the copy stays on peer stores)
             mm = self.use_multimem and self.tp == 1 and len(dests) >= 2 and bool(self.fabric.weights.mc_ptr)
-            self.fabric.copy_units(self.fabric.weights, dests, offs, lens, symm.PARAM_FLAG0, stripe=sources.index(self.rank),
-                                   n_stripes=len(sources), use_multimem=mm, num_ctas=self.copy_ctas)
-            torch.cuda.current_stream().synchronize()
+            with self.xfer_lock:
+                with torch.cuda.stream(self.side):
+                    self.fabric.copy_units(self.fabric.weights, dests, offs, lens, symm.PARAM_FLAG0,
+                                           stripe=sources.index(self.rank), n_stripes=len(sources), use_multimem=mm,
+                                           num_ctas=self.copy_ctas)
+                self.side.synchronize()
         elif self.rank in dests:
             self._receive_params(len(sources))
 
