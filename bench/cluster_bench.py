@@ -9,7 +9,8 @@ burst, at the start of which the remaining GPUs are scaled out as prefill replic
 
     stop   parameters are multicast into the new GPUs, which serve once everything has arrived (impl_blitz + impl_nvl)
     live   the new GPUs serve while loading (ZigZag: layers they hold run there, the rest on the old instance)
-    sllm   the stand-in for the ServerlessLLM baseline: the new GPUs load the segment file from disk / the host cache
+    sllm   the stand-in for the ServerlessLLM baseline: the new GPUs load the weights from pinned host memory (host-cache
+           hit, the baseline's best case) or, with --model-path, from the segment file on disk
 
 Reported (rank 0, one JSON line): scale-out latency per new replica (manual trigger -> replica takes work; in
 `live` mode that is before its parameters have arrived) and the time until it is fully loaded, router clock,
@@ -64,6 +65,11 @@ def main():
     backend = GpuBackend(rank, world, a.model, tp=1, num_pages=a.pages, page_size=64, max_batch=256, max_batch_tokens=8192,
                          ready=states[rank] != "Inactive", seed=0, use_multimem=a.multimem, model_path=a.model_path)
     if states[rank] == "Inactive":
+        if a.mode == "sllm" and not a.model_path:
+            # best case of the host-cache baseline: the weights already sit in pinned host memory on this machine
+            n = backend.engine.seg.layout.total_bytes
+            backend.host_mirror = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+            backend.host_mirror.copy_(backend.engine.seg.buffer[:n])
         backend.engine.seg.buffer.zero_()
     if a.mode == "sllm" and a.model_path and rank == 0:
         backend.engine.seg.save(a.model_path)          # the file the cold replicas will load
@@ -116,7 +122,7 @@ def run_router(a, world, states, cfg_model, backend):
     from blitz_scale_b200.router.runtime import RouterRuntime
     from blitz_scale_b200.router.server import controller_config_from_cluster
     feats = {"stop": "impl_blitz,impl_nvl,manually_scale", "live": "impl_blitz,impl_nvl,impl_live,manually_scale",
-             "sllm": "impl_sllm,manually_scale"}[a.mode]
+             "sllm": "impl_sllm,manually_scale" if a.model_path else "impl_sllm,cache_all_hit,manually_scale"}[a.mode]
     cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
                                          max_blocks_per_replica=a.pages - 64, block_size=64, max_prefill_tokens=8192,
                                          model_layers=cfg_model.layers)

@@ -365,10 +365,14 @@ def main(argv=None) -> None:
         migration_upper=a.migration_upper_bound, min_prefill=a.min_prefill_num, max_prefill=a.max_prefill_num,
         min_decode=a.min_decode_num, max_decode=a.max_decode_num, scale_down_threshold_ms=a.scale_down_threshold_millis)
     layers = get_config(a.model_name).layers
-    rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv)
-    asyncio.run(serve_router(rt, a.hostname, a.port, model_name=a.model_name, max_input_length=a.max_input_length,
-                             max_total_tokens=a.max_total_tokens, tokenizer_path=a.tokenizer_path,
-                             tokenizer_workers=a.validation_workers))
+    async def amain():
+        # the gRPC channels of the runtime belong to the event loop that creates them: build it inside the loop
+        rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv)
+        await serve_router(rt, a.hostname, a.port, model_name=a.model_name, max_input_length=a.max_input_length,
+                           max_total_tokens=a.max_total_tokens, tokenizer_path=a.tokenizer_path,
+                           tokenizer_workers=a.validation_workers)
+
+    asyncio.run(amain())
 
 
 if __name__ == "__main__":

@@ -241,3 +241,24 @@ def test_log_analysis_and_sizing():
     assert s["ttft_violation_rate"] == 0.5 and s["tbt_violation_rate"] == 0.5
     z = analysis.kv_sizing("llama3_8b", tp=1, page_size=64)
     assert z["kv_bytes_per_token"] == 2 * 8 * 128 * 2 * 32 and z["block_bytes"] == z["kv_bytes_per_token"] * 64
+
+
+def test_experiment_runs_processes_end_to_end(tmp_path):
+    """The deployment path as separate processes: two stub workers, the router CLI, the trace client CLI."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tpl = open(os.path.join(root, "bench/templates/cpu_plumbing.toml")).read()
+    p0, p1, p2 = _free_ports(3)
+    tpl = tpl.replace("worker_port = 50151", f"worker_port = {p0}").replace("port = 3100", f"port = {p2}")
+    tpl = tpl.replace("duration = 50", "duration = 4").replace("num_requests = 200", "num_requests = 16")
+    (tmp_path / "t.toml").write_text(tpl)
+    res = subprocess.run([sys.executable, os.path.join(root, "bench/experiment.py"), "--template", str(tmp_path / "t.toml"),
+                          "--out", str(tmp_path / "out"), "--force"], capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    d = next(p for p in (tmp_path / "out").iterdir() if p.is_dir())
+    recs = [json.loads(l) for l in open(d / "client.jsonl")]
+    assert len(recs) >= 8 and all(r.get("status") == "ok" for r in recs), recs[:2]
+    summary = json.load(open(d / "summary.json"))
+    assert "slo" in summary
+    assert "attached to a different loop" not in open(d / "router.log").read()
