@@ -99,10 +99,13 @@ def commands(inst: dict, d: Path) -> dict:
     return {"workers": workers, "router": router, "client": client}
 
 
-def wait_for(path: Path, needle: str, count: int, timeout: float) -> bool:
+def wait_for(path: Path, needle: str, count: int, timeout: float, also_glob: str = "") -> bool:
+    """Wait until `needle` occurs `count` times in `path` plus the files matching `also_glob` (workers started with
+    --log-dir write one file per rank instead of their stdout)."""
     t0 = time.time()
     while time.time() - t0 < timeout:
-        if path.exists() and path.read_text(errors="ignore").count(needle) >= count:
+        files = [path] + (sorted(path.parent.glob(also_glob)) if also_glob else [])
+        if sum(f.read_text(errors="ignore").count(needle) for f in files if f.exists()) >= count:
             return True
         time.sleep(0.2)
     return False
@@ -123,13 +126,34 @@ def run_instance(inst: dict, d: Path, dry: bool) -> dict:
         for c in cmds["workers"]:
             procs.append(subprocess.Popen(shlex.split(c), stdout=wl, stderr=subprocess.STDOUT, env=env, start_new_session=True))
         n = int(inst["global"].get("num_gpus", 2))
-        if not wait_for(d / "workers.log", "Start gRPC server", n, float(inst["global"].get("boot_timeout", 600))):
+        if not wait_for(d / "workers.log", "Start gRPC server", n, float(inst["global"].get("boot_timeout", 600)),
+                        also_glob="worker-logs/*.log"):
             raise RuntimeError("workers did not start")
         rl = open(d / "router.log", "w")
         logs.append(rl)
         procs.append(subprocess.Popen(shlex.split(cmds["router"]), stdout=rl, stderr=subprocess.STDOUT, env=env, start_new_session=True))
         if not wait_for(d / "router.log", "Router listening", 1, 60):
             raise RuntimeError("router did not start")
+        # scripted manual scaling: [[global.manual_scale]] at_s = 20, replica = 2, state = "Prefill"  (needs the
+        # manually_scale feature; entries with the same at_s reach the router before its next step and therefore
+        # share one parameter multicast)
+        events = sorted(inst["global"].get("manual_scale", []), key=lambda e: float(e["at_s"]))
+        if events:
+            import threading
+            import urllib.request
+            url = f"http://127.0.0.1:{inst['router'].get('port', 3000)}/modify_cluster_state"
+            t_begin = time.time()
+
+            def fire():
+                for e in events:
+                    time.sleep(max(0.0, float(e["at_s"]) - (time.time() - t_begin)))
+                    body = json.dumps({"replica": int(e["replica"]), "state": str(e["state"])}).encode()
+                    try:
+                        urllib.request.urlopen(urllib.request.Request(url, data=body, headers={"Content-Type": "application/json"}),
+                                               timeout=10).read()
+                    except Exception as ex:  # noqa: BLE001 - recorded, the run goes on
+                        print(f"manual_scale {e} failed: {ex}", flush=True)
+            threading.Thread(target=fire, daemon=True).start()
         cl = open(d / "client.log", "w")
         logs.append(cl)
         rc = subprocess.call(shlex.split(cmds["client"]), stdout=cl, stderr=subprocess.STDOUT, env=env,
@@ -158,7 +182,12 @@ def run_instance(inst: dict, d: Path, dry: bool) -> dict:
     return summary
 
 
+def _terminate(signum, frame):
+    raise KeyboardInterrupt      # run the `finally` blocks: the worker / router process groups must not outlive us
+
+
 def main():
+    signal.signal(signal.SIGTERM, _terminate)
     ap = argparse.ArgumentParser()
     ap.add_argument("--template", "--templates", required=True)
     ap.add_argument("--out", default="runs")

@@ -24,11 +24,34 @@ _SIGNAL = re.compile(r"Control signal: P([+-]\d+) D([+-]\d+)")
 _STAMP = re.compile(r"^\[?\s*(\d+\.\d+)\]?")
 
 
+_ISO = re.compile(r"^\[?(\d{4}-\d{2}-\d{2})[T ](\d{2}):(\d{2}):(\d{2})(?:[.,](\d+))?")
+
+
+def line_time(ln: str):
+    """Seconds from a log line's stamp: `[  12.345]` / `12.345 ...` (seconds) or `2024-01-01 10:00:00,123` (the
+    `logging` default; returned as seconds since midnight of the line's own date plus the day number * 86400)."""
+    ln = ln.strip()
+    m = _STAMP.match(ln)
+    if m and not _ISO.match(ln):
+        return float(m.group(1))
+    m = _ISO.match(ln)
+    if m:
+        import datetime
+        day = datetime.date.fromisoformat(m.group(1)).toordinal()
+        frac = float("0." + m.group(5)) if m.group(5) else 0.0
+        return day * 86400.0 + int(m.group(2)) * 3600 + int(m.group(3)) * 60 + int(m.group(4)) + frac
+    return None
+
+
 def parse_router_log(lines: Iterable[str]) -> dict:
+    """Times are relative to the first stamped line when the log carries wall-clock stamps."""
     out = {"transitions": [], "signals": [], "metrics": [], "unloads": [], "client_start": None}
+    t0 = None
     for ln in lines:
-        m = _STAMP.match(ln.strip())
-        t = float(m.group(1)) if m else None
+        t = line_time(ln)
+        if t is not None and t > 1e6:          # wall-clock stamp: make it relative
+            t0 = t if t0 is None else t0
+            t -= t0
         tr = _TRANS.search(ln)
         if tr:
             out["transitions"].append((t, int(tr.group(1)), tr.group(2), tr.group(3)))

@@ -220,8 +220,8 @@ def test_experiment_runner_expansion_and_dry_run(tmp_path):
     assert res.returncode == 0, res.stderr[-2000:]
     d = next(p for p in tmp_path.iterdir() if p.is_dir())
     cmds = json.load(open(d / "commands.json"))
-    assert len(cmds["workers"]) == 2 and "request_sim" in cmds["client"] and "--features" in cmds["router"]
-    assert json.load(open(d / "config-server.json"))["init_states"] == ["Normal", "Inactive"]
+    assert len(cmds["workers"]) == 3 and "request_sim" in cmds["client"] and "--features" in cmds["router"]
+    assert json.load(open(d / "config-server.json"))["init_states"] == ["Prefill", "Decode", "Inactive"]
 
 
 def test_log_analysis_and_sizing():
