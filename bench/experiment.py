@@ -72,7 +72,8 @@ def commands(inst: dict, d: Path) -> dict:
         workers = [f"{py} -m torch.distributed.run --nnodes=1 --nproc-per-node {n} --master-addr 127.0.0.1 "
                    f"--master-port {g.get('master_port', 29600)} -m blitz_scale_b200.worker.launcher --model-name {m['name']} "
                    f"--config {d / 'config-server.json'} --port {base} -TP {tp} "
-                   f"--num-total-blocks {m.get('num_available_blocks', 4096)} --log-dir {d / 'worker-logs'}"]
+                   f"--num-total-blocks {m.get('num_available_blocks', 4096)} --page-size {m.get('page_size', 64)} "
+                   f"--log-dir {d / 'worker-logs'}"]
     router_args = {
         "--port": r.get("port", 3000), "--client-config": str(d / "config-stubs.json"),
         "--deployment-config-path": str(d / "config-server.json"), "--features": inst["features"],
@@ -80,6 +81,7 @@ def commands(inst: dict, d: Path) -> dict:
         "--max-blocks-per-replica": m.get("num_available_blocks", 4096),
         "--tokens-prefilled-per-sec": m.get("tokens_prefilled_per_sec", 15000),
         "--tokens-transferred-per-sec": m.get("tokens_transferred_per_sec", 96000),
+        "--block-size": m.get("page_size", 64),
     }
     for k in ("prefill-lower-bound", "prefill-upper-bound", "decode-lower-bound", "decode-upper-bound",
               "migration-lower-bound", "migration-upper-bound", "min-prefill-num", "max-prefill-num", "min-decode-num",
@@ -90,7 +92,8 @@ def commands(inst: dict, d: Path) -> dict:
     (d / "config-router.json").write_text(json.dumps(router_args, indent=1))
     router = f"{py} -m blitz_scale_b200.router.server " + " ".join(f"{k} {shlex.quote(str(v))}" for k, v in router_args.items())
     client = (f"{py} -m blitz_scale_b200.sim.request_sim --endpoint http://127.0.0.1:{r.get('port', 3000)}/generate --protocol st "
-              f"--replay-mode --scale-factor {ds.get('scale_factor', 1.0)} --output-path {d / 'client.jsonl'} ")
+              f"--replay-mode --scale-factor {ds.get('scale_factor', 1.0)} --output-path {d / 'client.jsonl'} "
+              f"--vocab {m.get('vocab', 32000)} ")
     if ds.get("path"):
         client += f"--dataset-type csv --dataset-path {ds['path']} --time-in-secs {ds.get('time_in_secs', 60)}"
     else:

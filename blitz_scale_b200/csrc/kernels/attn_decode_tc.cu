@@ -15,8 +15,15 @@
 // per SM for head_dim 128).  Four consumer warps each own 16 of the 64 tokens
 // of a stage: S = Q K^T via ldmatrix + mma, online softmax in registers
 // (exp2, fp32), O += P V via ldmatrix.trans + mma.  Warps merge their partial
-// (m, l, O) through shared memory; with num_splits > 1 each CTA writes an fp32
+// (m, l, O) through shared memory; with num_splits > 1 each item writes an fp32
 // partial and a merge kernel combines the splits (flash-decoding).
+//
+// The kernel is persistent: one CTA per SM walks the work items (sequence,
+// KV head, split) in a grid-stride loop and the TMA pipeline runs across item
+// boundaries, so it never drains between sequences (5.6 TB/s at batch 256,
+// context 1024).  It is launched with programmatic dependent launch: shared
+// memory is cleared and the barriers are set up while the previous kernel is
+// still running; the first load waits for it.
 //
 // The cache must hold finite values in every slot of an allocated page (the
 // pool is zero-filled at creation): masked positions get probability 0, and

@@ -116,6 +116,13 @@ class RouterApp:
         self.limits = core.ValidationLimits()
         self.limits.max_input_length, self.limits.max_total_tokens = max_input_length, max_total_tokens
         self.model_name = model_name
+        try:
+            from ..models.config import get_config
+            self.model_vocab = get_config(model_name).vocab
+        except Exception:  # noqa: BLE001 - unknown model name: no id range to enforce
+            self.model_vocab = 0
+        if not tokenizer_path and self.model_vocab:
+            self.tok = WordHashTokenizer(min(vocab, self.model_vocab))
         self.sem = asyncio.Semaphore(max_concurrent)
         self.metrics = Metrics()
         self.app = web.Application(client_max_size=64 << 20)
@@ -135,6 +142,9 @@ class RouterApp:
         p = body.get("parameters") or {}
         if "input_tokens" in body:
             toks = [int(t) for t in body["input_tokens"]]
+            if self.model_vocab and any(t < 0 or t >= self.model_vocab for t in toks):
+                # an id outside the embedding table would make the worker's lookup fail the whole batch
+                return toks, None, f"input_tokens must lie in [0, {self.model_vocab})"
         else:
             toks = await asyncio.get_running_loop().run_in_executor(self.tok_pool, self.tok.encode, body.get("inputs", ""))
         g = core.GenerateParams()
@@ -337,6 +347,7 @@ def main(argv=None) -> None:
     ap.add_argument("--max-total-tokens", type=int, default=4096)
     ap.add_argument("--max-batch-prefill-tokens", type=int, default=8192)
     ap.add_argument("--max-blocks-per-replica", type=int, default=30000)
+    ap.add_argument("--block-size", type=int, default=64, help="tokens per KV page; must equal the workers' --page-size")
     ap.add_argument("--tokens-prefilled-per-sec", type=int, default=15000)
     ap.add_argument("--tokens-transferred-per-sec", type=int, default=96000)
     for n, d in (("prefill-lower-bound", .5), ("prefill-upper-bound", .7), ("decode-lower-bound", .75),
@@ -358,7 +369,7 @@ def main(argv=None) -> None:
     cfg = controller_config_from_cluster(
         cluster, a.tensor_parallel_size, a.features, model_name=a.model_name,
         max_prefill_tokens=a.max_batch_prefill_tokens, max_total_tokens=max(a.max_total_tokens, 16000),
-        max_blocks_per_replica=a.max_blocks_per_replica, mock_load_ms=a.mock_load_millis,
+        max_blocks_per_replica=a.max_blocks_per_replica, block_size=a.block_size, mock_load_ms=a.mock_load_millis,
         tokens_prefilled_per_sec=a.tokens_prefilled_per_sec, tokens_transferred_per_sec=a.tokens_transferred_per_sec,
         prefill_lower=a.prefill_lower_bound, prefill_upper=a.prefill_upper_bound, decode_lower=a.decode_lower_bound,
         decode_upper=a.decode_upper_bound, migration_lower=a.migration_lower_bound,

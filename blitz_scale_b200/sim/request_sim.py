@@ -130,12 +130,13 @@ def main(argv=None) -> None:
     ap.add_argument("--duration", type=float, default=50.0)
     ap.add_argument("--num-requests", type=int, default=200)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--vocab", type=int, default=32000, help="synthetic token ids are drawn from [0, vocab)")
     a = ap.parse_args(argv)
     if a.dataset_type == "csv" or a.dataset_path:
         trace = core.load_trace_csv(a.dataset_path, 1.0, a.truncate)
     else:
         trace = make_mock_trace(a.rate, a.duration, a.seed, a.cv, max_requests=a.num_requests)
-    recs = asyncio.run(replay(a.endpoint, trace, a.output_path, a.scale_factor, a.time_in_secs))
+    recs = asyncio.run(replay(a.endpoint, trace, a.output_path, a.scale_factor, a.time_in_secs, vocab=a.vocab))
     print(json.dumps(summarize(recs)))
 
 
