@@ -89,6 +89,9 @@ def main():
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree of every replica (GPUs / tp replicas)")
+    ap.add_argument("--no-fused-tp", action="store_true", help="tp > 1: NCCL all-reduce layers (the baseline) instead of the "
+                    "fused peer-memory kernels")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -111,10 +114,22 @@ def main():
     B, ctx, ps = args.batch, args.ctx, args.page_size
     total_steps = args.warmup + args.steps + 8
     pages_per_seq = (ctx + total_steps + ps) // ps + 1
+    tp = max(1, args.tp)
+    assert world % tp == 0, "--gpus must be a multiple of --tp"
+    comm = None
+    if tp > 1:
+        from blitz_scale_b200.models.llama import TPComm
+        group = None
+        for r0 in range(0, world, tp):          # every rank creates every group, in the same order
+            g_ = dist.new_group(list(range(r0, r0 + tp)))
+            if r0 <= rank < r0 + tp:
+                group = g_
+        comm = TPComm(group)
     eng = Engine(args.model, num_pages=B * pages_per_seq + 8, page_size=ps, max_batch=max(B, 8),
-                 max_batch_tokens=8192, seed=rank)
+                 max_batch_tokens=8192, seed=rank // tp, tp=tp, tp_rank=rank % tp, comm=comm,
+                 fused_tp=not args.no_fused_tp)
     # synthetic prompts, prefilled through the engine in chunks that fit the activation workspace
-    g = torch.Generator().manual_seed(1234 + rank)
+    g = torch.Generator().manual_seed(1234 + rank // tp)      # the ranks of one replica see the same prompts
     per = max(1, 8192 // ctx)
     batch = None
     bid = 0
@@ -176,14 +191,16 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_s, e2e_s = float(t[0]), float(t[1])
     if rank == 0:
-        tokens = world * B * args.steps
+        replicas = world // tp
+        tokens = replicas * B * args.steps
         out = {
             "metric": "decode_tokens_per_s", "value": tokens / dev_s, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic token ids, random-init weights",
-            "config": {"model": args.model, "global_batch": world * B, "seq_len": ctx, "parallelism": f"dp{world}",
-                       "tp": 1, "page_size": ps, "l2": "per-step working set (weights + KV) >> 126 MB L2, no flush",
+            "config": {"model": args.model, "global_batch": replicas * B, "seq_len": ctx,
+                       "parallelism": f"dp{replicas}" + (f"xtp{tp}" + ("" if eng.fused is not None else "-nccl") if tp > 1 else ""),
+                       "tp": tp, "page_size": ps, "l2": "per-step working set (weights + KV) >> 126 MB L2, no flush",
                        "timing": "CUDA events around K graph replays, max over ranks"},
             "clocks": clocks,
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "ms_per_step": e2e_s / args.steps * 1e3,
@@ -192,6 +209,9 @@ def main():
         }
         print(json.dumps(out))
     if world > 1:
+        sys.stdout.flush()
+        if tp > 1:
+            os._exit(0)      # symmetric-memory teardown with live graphs can block for minutes
         dist.destroy_process_group()
     return 0
 

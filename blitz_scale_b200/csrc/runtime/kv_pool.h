@@ -151,7 +151,7 @@ class Batch {
 
   // Append one sampled token per live request (order = seqs()), evaluate stop criteria and
   // make sure the page that will hold the token's K/V on the next step exists.
-  // Returns false if the pool ran out of pages (the token is still recorded).
+  // Returns false if the pool ran out of pages (the token is still recorded and the request is finished).
   bool append_tokens(const std::vector<int32_t>& tokens, bool count_cached) {
     if (tokens.size() != seqs_.size()) throw std::invalid_argument("append_tokens: size mismatch");
     const int ps = pool_->page_size();
@@ -170,6 +170,9 @@ class Batch {
         const int need = (s.total_len() + ps - 1) / ps;
         while (static_cast<int>(s.pages.size()) < need) {
           if (!pool_->allocate(1, s.pages)) {
+            // no page for the next position: the request ends here (reported as a length stop) instead of writing its
+            // next K/V outside its pages; callers that budget blocks up front (the router does) never get here
+            s.finish = kFinishLength;
             ok = false;
             break;
           }

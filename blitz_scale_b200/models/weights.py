@@ -51,9 +51,10 @@ class WeightSegment:
     def random_init_(self, seed: int = 0) -> "WeightSegment":
         """Deterministic random weights with activations of order one (norm gains near 1, matrices ~ N(0, 1/in))."""
         gen = torch.Generator(device="cpu").manual_seed(seed * 1000003 + self.tp_rank)
+        shared = torch.Generator(device="cpu").manual_seed(seed * 1000003 + 7919)   # replicated tensors: same on every rank
         for name, v in self._views.items():
             if v.dim() == 1:
-                val = 1.0 + 0.05 * torch.randn(v.shape, generator=gen)
+                val = 1.0 + 0.05 * torch.randn(v.shape, generator=shared)
             elif name == "embed":
                 val = torch.randn(v.shape, generator=gen)
             else:
@@ -64,9 +65,11 @@ class WeightSegment:
     def random_init_fast_(self, seed: int = 0) -> "WeightSegment":
         """Random fill generated on the segment's own device (for multi-GB models)."""
         gen = torch.Generator(device=self.buffer.device).manual_seed(seed * 1000003 + self.tp_rank)
+        # norm gains are replicated across the TP ranks of a replica: they must not depend on the rank
+        shared = torch.Generator(device=self.buffer.device).manual_seed(seed * 1000003 + 7919)
         for name, v in self._views.items():
             if v.dim() == 1:
-                v.copy_((1.0 + 0.05 * torch.randn(v.shape, generator=gen, device=v.device)).to(self.dtype))
+                v.copy_((1.0 + 0.05 * torch.randn(v.shape, generator=shared, device=v.device)).to(self.dtype))
             else:
                 scale = 1.0 if name == "embed" else v.shape[0] ** -0.5
                 rows = max(1, (64 << 20) // max(1, v.shape[1] * 4))

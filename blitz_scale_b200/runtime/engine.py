@@ -38,7 +38,7 @@ class Engine:
                  max_batch_tokens: int = 8192, tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16,
                  device: Optional[torch.device] = None, comm: Optional[TPComm] = None, use_graphs: bool = True,
                  seg_buffer: Optional[torch.Tensor] = None, kv_buffer: Optional[torch.Tensor] = None,
-                 ready: bool = True, seed: int = 0):
+                 ready: bool = True, seed: int = 0, fused_tp: bool = True):
         self.cfg = get_config(model) if isinstance(model, str) else model
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.dtype, self.tp, self.tp_rank = dtype, tp, tp_rank
@@ -53,8 +53,16 @@ class Engine:
             self.kv = torch.zeros(kv_shape, dtype=dtype, device=self.device)
         else:
             self.kv = kv_buffer.view(dtype)[:int(np.prod(kv_shape))].view(kv_shape)
-        self.runner = LlamaRunner(self.seg, self.kv, max_tokens=max(max_batch_tokens, max_batch), max_batch=max_batch,
-                                  comm=comm)
+        self.fused = None
+        if tp > 1 and comm is not None and fused_tp:
+            # tensor-parallel layers through the fused peer-memory kernels (GEMM -> reduce-scatter push, reduce + norm +
+            # all-gather push, flag-gated GEMM); the NCCL all-reduce runner is the baseline (`fused_tp=False`)
+            from ..parallel.tp import FusedTP, LlamaRunnerTP
+            self.fused = FusedTP(comm.group, c.hidden, max(max_batch_tokens, max_batch), dtype=dtype)
+            self.runner = LlamaRunnerTP(self.seg, self.kv, max(max_batch_tokens, max_batch), max_batch, comm, self.fused)
+        else:
+            self.runner = LlamaRunner(self.seg, self.kv, max_tokens=max(max_batch_tokens, max_batch), max_batch=max_batch,
+                                      comm=comm)
         self.pool = core.PagePool(num_pages, page_size)
         self.layout = core.MetaLayout.make(max(max_batch_tokens, max_batch), max_batch, num_pages)
         self.host = torch.zeros(self.layout.total, dtype=torch.int32, pin_memory=True)

@@ -43,7 +43,8 @@ log = logging.getLogger("blitz.worker")
 class GpuBackend(Backend):
     def __init__(self, rank: int, world: int, model: str, *, tp: int = 1, num_pages: int = 2048, page_size: int = 64,
                  max_batch: int = 256, max_batch_tokens: int = 8192, ready: bool = True, use_fabric: bool = True,
-                 tp_group=None, model_path: str = "", seed: int = 0, use_multimem: bool = False, copy_ctas: int = 128):
+                 tp_group=None, model_path: str = "", seed: int = 0, use_multimem: bool = False, copy_ctas: int = 128,
+                 fused_tp: bool = True):
         self.rank, self.world, self.tp = rank, world, tp
         self.cfg = get_config(model)
         self.model, self.model_path = model, model_path
@@ -68,7 +69,7 @@ class GpuBackend(Backend):
         comm = TPComm(tp_group) if tp > 1 else None
         self.engine = Engine(self.cfg, num_pages=num_pages, page_size=page_size, max_batch=max_batch,
                              max_batch_tokens=max_batch_tokens, tp=tp, tp_rank=rank % tp, dtype=dt, comm=comm,
-                             seg_buffer=seg_buf, kv_buffer=kv_buf, ready=ready, seed=seed)
+                             seg_buffer=seg_buf, kv_buffer=kv_buf, ready=ready, seed=seed, fused_tp=fused_tp)
         self.units = [(n, o, b) for n, o, b in self.engine.seg.layout.units]
         self.batches: Dict[int, "core.Batch"] = {}
         self.param_expected = 0      # cumulative flag value that means "all stripes of the current transfer landed"
@@ -199,6 +200,10 @@ class GpuBackend(Backend):
 
     # ------------------------------------------------------------------ live execution (ZigZag)
     def zag_prefill(self, batch, forward_case, pp_info, zag_layers, zag_seq):
+        if self.engine.fused is not None:
+            # the fused TP runner keeps the residual stream sharded by rows inside its own buffers; interleaving several
+            # live-execution tasks layer by layer needs per-task copies of that state, which only the all-reduce runner has
+            raise RuntimeError("live execution with tp > 1 needs workers started with --no-fused-tp")
         fut: Future = Future()
         with self.lock:
             b = self.engine.new_batch(batch.id, self._specs(batch))

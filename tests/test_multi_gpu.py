@@ -37,7 +37,8 @@ def test_gpu_cluster_end_to_end(case, n):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
-@pytest.mark.parametrize("case", ["multicast", "multicast_multimem", "kv_push", "mailbox_and_timeout", "tp_fused"])
+@pytest.mark.parametrize("case", ["multicast", "multicast_multimem", "kv_push", "mailbox_and_timeout", "tp_fused",
+                                  "engine_tp"])
 def test_peer_kernels(case):
     n = min(_ngpu(), 4) if case.startswith("multicast") else 2
     out = _run(case, n)
