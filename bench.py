@@ -90,6 +90,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree of every replica (GPUs / tp replicas)")
+    ap.add_argument("--oneshot-max-rows", type=int, default=1024, help="tp > 1: steps of at most this many rows use the one-shot "
+                    "peer-memory all-reduce instead of the reduce-scatter / all-gather pipeline")
     ap.add_argument("--no-fused-tp", action="store_true", help="tp > 1: NCCL all-reduce layers (the baseline) instead of the "
                     "fused peer-memory kernels")
     args = ap.parse_args()
@@ -127,7 +129,7 @@ def main():
         comm = TPComm(group)
     eng = Engine(args.model, num_pages=B * pages_per_seq + 8, page_size=ps, max_batch=max(B, 8),
                  max_batch_tokens=8192, seed=rank // tp, tp=tp, tp_rank=rank % tp, comm=comm,
-                 fused_tp=not args.no_fused_tp)
+                 fused_tp=not args.no_fused_tp, oneshot_max_rows=args.oneshot_max_rows)
     # synthetic prompts, prefilled through the engine in chunks that fit the activation workspace
     g = torch.Generator().manual_seed(1234 + rank // tp)      # the ranks of one replica see the same prompts
     per = max(1, 8192 // ctx)

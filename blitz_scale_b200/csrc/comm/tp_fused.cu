@@ -180,11 +180,98 @@ __global__ void __launch_bounds__(256) oneshot_reduce_kernel(const OneShotParams
     }
     *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + i * 8) = pack8<T>(acc);
   }
+  // consumer-side reset: the block that finishes last re-arms this rank's arrival counters (nobody reads them any
+  // more for this call; the peers' next pushes into this parity come only after they have seen our next push)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* ticket = p.flags[p.my_rank] + kMaxTp;
+    const uint32_t t = ptx::atom_add_acq_rel_gpu(ticket, 1u);
+    if (t == gridDim.x - 1) {
+      for (int s2 = 0; s2 < p.tp; ++s2) p.flags[p.my_rank][s2] = 0;
+      *ticket = 0;
+      __threadfence_system();
+    }
+  }
+}
+
+// One-kernel form of the one-shot all-reduce.  Block b owns one contiguous chunk of the vector: it pushes its chunk
+// of the local contribution into every rank's slot, bumps counter [src = me][b] on every rank, waits (bounded) until
+// counter [s][b] of every source s has arrived here, sums the tp slots of its chunk in rank order, and re-arms the
+// counters it consumed.  Blocks with the same index on the tp GPUs thus rendezvous pairwise: there is no grid-wide
+// wait and no second launch, and a chunk is summed as soon as its tp pieces are in.  (The blocks wait on blocks
+// of OTHER GPUs' kernels only, never on blocks of their own grid.)
+constexpr int kArBlocks = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256) allreduce_fused_kernel(const OneShotParams p) {
+  __shared__ int s_ok;
+  const int64_t nvec = p.n >> 3;
+  const int64_t chunk = (nvec + gridDim.x - 1) / gridDim.x;
+  const int64_t v0 = static_cast<int64_t>(blockIdx.x) * chunk;
+  const int64_t v1 = min(nvec, v0 + chunk);
+  const T* x = reinterpret_cast<const T*>(p.x);
+  for (int64_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+    const uint4 v = ld_nc16(x + i * 8);
+    for (int d = 0; d < p.tp; ++d)
+      ptx::st_na_v4(reinterpret_cast<T*>(p.slots[d]) + static_cast<int64_t>(p.my_rank) * p.n + i * 8, v);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.tp) {
+    ptx::fence_acq_rel_sys();
+    ptx::red_add_release_sys(p.flags[threadIdx.x] + p.my_rank * kArBlocks + blockIdx.x, 1u);
+  }
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int s = 0; s < p.tp; ++s)
+      if (!ptx::bounded_flag_wait_ge(p.flags[p.my_rank] + s * kArBlocks + blockIdx.x, 1u, p.budget_ns)) ok = 0;
+    if (!ok && p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const T* mine = reinterpret_cast<const T*>(p.slots[p.my_rank]);
+  for (int64_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < p.tp; ++s) {
+      float f[8];
+      unpack8<T>(__ldcg(reinterpret_cast<const uint4*>(mine + static_cast<int64_t>(s) * p.n + i * 8)), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + i * 8) = pack8<T>(acc);
+  }
+  __syncthreads();
+  if (threadIdx.x < p.tp) p.flags[p.my_rank][threadIdx.x * kArBlocks + blockIdx.x] = 0;  // consumed: re-arm
 }
 
 }  // namespace blitz
 
 extern "C" {
+
+// One-kernel one-shot all-reduce (see allreduce_fused_kernel).  flags[d]: peer pointer to rank d's uint32[tp][64]
+// per-block arrival counters, zero at start.  Same slots / parity rules as blitz_allreduce_oneshot.
+int blitz_allreduce_fused(const void* x, void* const* slots, uint32_t* const* flags, void* out, int tp, int my_rank,
+                          int64_t n, uint64_t budget_ns, int* status, int dtype, cudaStream_t stream) {
+  using namespace blitz;
+  if (n <= 0) return 0;
+  if (tp < 1 || tp > kMaxTp || (n & 7)) return -1;
+  OneShotParams p;
+  p.x = x; p.out = out; p.tp = tp; p.my_rank = my_rank; p.n = n; p.want = 0; p.budget_ns = budget_ns; p.status = status;
+  for (int d = 0; d < kMaxTp; ++d) {
+    p.slots[d] = d < tp ? slots[d] : nullptr;
+    p.flags[d] = d < tp ? flags[d] : nullptr;
+  }
+  const int64_t nvec = n >> 3;
+  int blocks = (int)((nvec + 255) / 256);
+  if (blocks > kArBlocks) blocks = kArBlocks;
+  if (dtype == 1) allreduce_fused_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(p);
+  else allreduce_fused_kernel<__half><<<blocks, 256, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
 using namespace blitz;
 
 // stage: local [tp][hidden / 8][rows_per_rank][8] (the layout the GEMM push epilogue writes); flag_rs: local uint32[kMaxTp + 1] (zero at start; [kMaxTp] is a ticket);
@@ -215,7 +302,7 @@ int blitz_flags_zero(uint32_t* flags, int n, cudaStream_t stream) {
 }
 
 // One-shot all-reduce of n elements (multiple of 8).  slots[d]: peer pointer to rank d's receive area of tp * n
-// elements; flags[d]: peer pointer to rank d's uint32[tp] arrival counters.  `expect` = number of push blocks per
+// elements; flags[d]: peer pointer to rank d's uint32[kMaxTp + 1] arrival counters (+ a ticket word), zero at start.  `expect` = number of push blocks per
 // rank (returned through *blocks_out on the first call with expect = 0 is not needed: it equals the grid used here).
 int blitz_allreduce_oneshot(const void* x, void* const* slots, uint32_t* const* flags, void* out, int tp, int my_rank,
                             int64_t n, uint64_t budget_ns, int* status, int dtype, cudaStream_t stream) {
@@ -237,8 +324,6 @@ int blitz_allreduce_oneshot(const void* x, void* const* slots, uint32_t* const* 
     oneshot_push_kernel<__half><<<blocks, 256, 0, stream>>>(p);
     oneshot_reduce_kernel<__half><<<blocks, 256, 0, stream>>>(p, (uint32_t)blocks);
   }
-  // consumer-side reset: after the reduce kernel (stream order) nobody reads the counters of this call any more
-  flags_zero_kernel<<<1, 1024, 0, stream>>>(flags[my_rank], tp);
   return (int)cudaGetLastError();
 }
 

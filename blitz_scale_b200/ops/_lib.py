@@ -68,6 +68,7 @@ def _declare(L: ctypes.CDLL) -> None:
                                  c_i, c_p])
     sig("blitz_flags_zero", [c_p, c_i, c_p])
     sig("blitz_allreduce_oneshot", [c_p, pp_, pp_, c_p, c_i, c_i, c_i64, c_u64, c_p, c_i, c_p])
+    sig("blitz_allreduce_fused", [c_p, pp_, pp_, c_p, c_i, c_i, c_i64, c_u64, c_p, c_i, c_p])
     sig("blitz_embedding", [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_i, c_p])
     sig("blitz_rms_norm", [c_p, c_p, c_p, c_i, c_i, c_f, c_i, c_p])
     sig("blitz_add_rms_norm", [c_p, c_p, c_p, c_p, c_i, c_i, c_f, c_i, c_p])

@@ -39,7 +39,7 @@ _EPI = {"store": 0, "add": 1, "silu_mul": 2, "push": 3}
 
 
 class FusedTP:
-    FLAG_WORDS = 128  # rs0: 0..15, rs1: 16..31, ag0: 32..39, ag1: 40..47, emb: 48..55
+    FLAG_WORDS = 128  # rs0: 0..15, rs1: 16..31, ag0: 32..39, ag1: 40..47, one-shot all-reduce: 48..56 and 64..72
 
     def __init__(self, group, hidden: int, max_rows: int, dtype=torch.bfloat16, device=None):
         import torch.distributed as dist
@@ -53,9 +53,12 @@ class FusedTP:
         # layout of the symmetric region
         self.o_stage = [0, self.buf_bytes]
         self.o_xg = [2 * self.buf_bytes, 3 * self.buf_bytes]
-        self.o_emb = 4 * self.buf_bytes                       # [tp][max_rows * hidden]
-        self.o_flags = self.o_emb + self.tp * self.buf_bytes
-        total = self.o_flags + self.FLAG_WORDS * 4
+        self.o_emb = 4 * self.buf_bytes                       # one-shot all-reduce slots: [parity 2][tp][max_rows * hidden]
+        self.o_flags = self.o_emb + 2 * self.tp * self.buf_bytes
+        self._ar_parity = 0
+        self.fused_allreduce = True                           # one-kernel all-reduce (per-block rendezvous)
+        self.o_cflags = self.o_flags + self.FLAG_WORDS * 4    # per-block counters of it: [parity 2][tp 8][64 blocks]
+        total = self.o_cflags + 2 * 8 * 64 * 4
         self.region = SymmRegion(total, group, device)
         self.region.local[self.o_flags:].zero_()
         torch.cuda.synchronize()
@@ -143,23 +146,61 @@ class FusedTP:
         _check(_L.lib().blitz_flags_zero(ctypes.c_void_p(self._flag_ptr(self.rank, 32 + 8 * which_x)), self.tp, _stream()),
                "blitz_flags_zero")
 
+    def reset_allreduce_parity(self) -> None:
+        """Call at the same point of the program on every rank (the runner does it at the start of a forward)."""
+        self._ar_parity = 0
+
     def allreduce_oneshot(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out = sum over ranks of x (out may be x).  Every rank stores its contribution into every rank's slot and
+        sums the tp slots in rank order.  Consecutive calls alternate between two slot / counter sets, so a rank
+        that runs one call ahead never overwrites data its peer is still summing."""
         n = x.numel()
         assert n * self.elem <= self.buf_bytes and x.is_contiguous()
-        slots = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + self.o_emb for r in range(self.tp)])
-        fl = (ctypes.c_void_p * self.tp)(*[self._flag_ptr(r, 48) for r in range(self.tp)])
+        par = self._ar_parity
+        self._ar_parity ^= 1
+        base = self.o_emb + par * self.tp * self.buf_bytes
+        slots = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + base for r in range(self.tp)])
+        if self.fused_allreduce:
+            cf = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + self.o_cflags + par * 8 * 64 * 4 for r in range(self.tp)])
+            rc = _L.lib().blitz_allreduce_fused(_p(x), slots, cf, _p(out), self.tp, self.rank, n, self.budget_ns,
+                                                _p(status_word(self.device)), 1 if self.dtype == torch.bfloat16 else 0,
+                                                _stream())
+            _check(rc, "blitz_allreduce_fused")
+            return out
+        fl = (ctypes.c_void_p * self.tp)(*[self._flag_ptr(r, 48 + 16 * par) for r in range(self.tp)])
         rc = _L.lib().blitz_allreduce_oneshot(_p(x), slots, fl, _p(out), self.tp, self.rank, n, self.budget_ns,
                                               _p(status_word(self.device)), 1 if self.dtype == torch.bfloat16 else 0, _stream())
         _check(rc, "blitz_allreduce_oneshot")
         return out
 
 
+class _PeerAllReduce:
+    """The collective interface of `TPComm` with the sum done by the one-shot peer-memory kernels; the tiny
+    (value, index) all-gather of the sharded argmax stays on the library."""
+
+    def __init__(self, comm: TPComm, fused: FusedTP):
+        self.comm, self.fused = comm, fused
+        self.size, self.rank, self.group = comm.size, comm.rank, comm.group
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        return self.fused.allreduce_oneshot(t, t)
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        return self.comm.all_gather(t)
+
+
 class LlamaRunnerTP(LlamaRunner):
     """Llama forward on one TP rank with the fused peer-memory path (no collective library in the layer loop)."""
 
-    def __init__(self, seg, kv_cache, max_tokens, max_batch, comm: TPComm, fused: FusedTP):
+    def __init__(self, seg, kv_cache, max_tokens, max_batch, comm: TPComm, fused: FusedTP, oneshot_max_rows: int = 0):
         super().__init__(seg, kv_cache, max_tokens, max_batch, comm=comm)
         self.fused = fused
+        # Steps of at most this many rows skip the reduce-scatter / all-gather split: every partial sum goes through
+        # the one-shot peer-memory all-reduce (each rank pushes its partial rows into every rank's slot and sums),
+        # which is one hop instead of two dependent ones; the row-sharded pipeline wins once rows are many.
+        self.oneshot_max_rows = oneshot_max_rows
+        self._nccl_comm = comm
+        self._peer_comm = _PeerAllReduce(comm, fused)
         self.res_shard = torch.empty(fused.max_rows // fused.tp, self.cfg.hidden, dtype=seg.dtype, device=self.res.device)
         self._pad_ids = torch.zeros(fused.max_rows, dtype=torch.int32, device=self.res.device)
 
@@ -168,7 +209,15 @@ class LlamaRunnerTP(LlamaRunner):
         Tp = (m.num_tokens + tp - 1) // tp * tp
         return Tp, Tp // tp
 
+    def _small(self, m: StepMeta) -> bool:
+        return m.num_tokens <= self.oneshot_max_rows
+
     def embed(self, m: StepMeta) -> None:
+        self.fused.reset_allreduce_parity()
+        if self._small(m):
+            self.comm = self._peer_comm
+            return LlamaRunner.embed(self, m)
+        self.comm = self._nccl_comm
         T = m.num_tokens
         Tp, rpr = self._rows(m)
         vs = self.cfg.vocab // self.tp
@@ -184,6 +233,8 @@ class LlamaRunnerTP(LlamaRunner):
         self._first = True
 
     def attention_block(self, l: int, m: StepMeta) -> None:
+        if self._small(m):
+            return LlamaRunner.attention_block(self, l, m)
         T, c, f = m.num_tokens, self.cfg, self.fused
         Tp, rpr = self._rows(m)
         f.ag_gemm(0, Tp, self._w(l, "qkv"), self.qkv[:Tp], wait=not self._first)
@@ -203,6 +254,8 @@ class LlamaRunnerTP(LlamaRunner):
         f.reduce_norm(0, exp, rpr, self.res_shard, self._w(l, "post_ln"), 1, c.rms_eps)
 
     def ffn_block(self, l: int, m: StepMeta) -> None:
+        if self._small(m):
+            return LlamaRunner.ffn_block(self, l, m)
         c, f = self.cfg, self.fused
         Tp, rpr = self._rows(m)
         f.ag_gemm(1, Tp, self._w(l, "gate_up"), self.act[:Tp], epilogue="silu_mul")
@@ -211,6 +264,8 @@ class LlamaRunnerTP(LlamaRunner):
         f.reduce_norm(1, exp, rpr, self.res_shard, nw, 0, c.rms_eps)
 
     def head(self, m: StepMeta) -> torch.Tensor:
+        if self._small(m):
+            return LlamaRunner.head(self, m)
         B, T, c, f = m.batch, m.num_tokens, self.cfg, self.fused
         Tp, _ = self._rows(m)
         f.wait_gathered(0, Tp)     # final-norm rows of every rank are in gathered buffer 0

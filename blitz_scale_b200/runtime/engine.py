@@ -38,7 +38,7 @@ class Engine:
                  max_batch_tokens: int = 8192, tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16,
                  device: Optional[torch.device] = None, comm: Optional[TPComm] = None, use_graphs: bool = True,
                  seg_buffer: Optional[torch.Tensor] = None, kv_buffer: Optional[torch.Tensor] = None,
-                 ready: bool = True, seed: int = 0, fused_tp: bool = True):
+                 ready: bool = True, seed: int = 0, fused_tp: bool = True, oneshot_max_rows: int = 1024):
         self.cfg = get_config(model) if isinstance(model, str) else model
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.dtype, self.tp, self.tp_rank = dtype, tp, tp_rank
@@ -59,7 +59,8 @@ class Engine:
             # all-gather push, flag-gated GEMM); the NCCL all-reduce runner is the baseline (`fused_tp=False`)
             from ..parallel.tp import FusedTP, LlamaRunnerTP
             self.fused = FusedTP(comm.group, c.hidden, max(max_batch_tokens, max_batch), dtype=dtype)
-            self.runner = LlamaRunnerTP(self.seg, self.kv, max(max_batch_tokens, max_batch), max_batch, comm, self.fused)
+            self.runner = LlamaRunnerTP(self.seg, self.kv, max(max_batch_tokens, max_batch), max_batch, comm, self.fused,
+                                        oneshot_max_rows=oneshot_max_rows)
         else:
             self.runner = LlamaRunner(self.seg, self.kv, max_tokens=max(max_batch_tokens, max_batch), max_batch=max_batch,
                                       comm=comm)
