@@ -35,7 +35,7 @@ sys.path.insert(0, ROOT)
 def reference_arm():
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a C++/Rust/CMake project with empty submodules: pip reports "
-                                     "'/root/reference is not installable: neither setup.py nor pyproject.toml found'"}))
+                                     "'Directory is not installable. Neither setup.py nor pyproject.toml found'"}))
     return 0
 
 

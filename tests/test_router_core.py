@@ -372,3 +372,18 @@ def test_simultaneous_scale_ups_share_one_multicast():
     acts = [a for a in ctl.step(0.0) if a.type == core.ActionType.TanzBroadcast]
     assert len(acts) == 1 and acts[0].live and acts[0].dst_ranks == [2, 3]
     assert ctl.state_name(2) == "NewPrefill" and ctl.state_name(3) == "NewPrefill" and ctl.state_name(0) == "OldPrefill"
+
+
+def test_calibrated_autoscaling_study_orders_the_policies():
+    """Virtual-time replay with the measured B200 cost model: faster parameter delivery -> lower p99 TTFT."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench"))
+    import sim_study
+    out = sim_study.run("llama3_8b", 6.0, 100.0)
+    rows = {r["policy"].split(" (")[0]: r for r in out["rows"]}
+    mc, host, disk = rows["multicast, stop-the-world load"], rows["host-cache load"], rows["disk load"]
+    assert all(r["failed"] == 0 and r["requests"] == out["trace_requests"] for r in out["rows"])
+    assert mc["scale_outs"] >= 2 and mc["scale_out_latency_ms"] < host["scale_out_latency_ms"] < disk["scale_out_latency_ms"]
+    assert mc["ttft_ms_p99"] < host["ttft_ms_p99"] < disk["ttft_ms_p99"]
+    assert mc["ttft_violation_rate"] <= host["ttft_violation_rate"] <= disk["ttft_violation_rate"]
