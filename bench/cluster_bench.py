@@ -12,6 +12,9 @@ burst, at the start of which the remaining GPUs are scaled out as prefill replic
     sllm   the stand-in for the ServerlessLLM baseline: the new GPUs load the weights from pinned host memory (host-cache
            hit, the baseline's best case) or, with --model-path, from the segment file on disk
 
+With --autoscale nothing is triggered by hand: the planner sees the queue grow and scales out (and back in) itself;
+the latencies are then measured from the start of the burst.
+
 Reported (rank 0, one JSON line): scale-out latency per new replica (manual trigger -> replica takes work; in
 `live` mode that is before its parameters have arrived) and the time until it is fully loaded, router clock,
 parameter bytes per replica, TTFT p50/p99 and TBT p50/p99 over the burst, decode tokens/s.
@@ -49,6 +52,9 @@ def main():
     ap.add_argument("--pages", type=int, default=4096)
     ap.add_argument("--model-path", default="")
     ap.add_argument("--multimem", action="store_true")
+    ap.add_argument("--autoscale", action="store_true", help="let the planner decide when and how far to scale (no manual trigger)")
+    ap.add_argument("--prefill-rate", type=float, default=60000.0, help="autoscale: prefill tokens/s one replica sustains")
+    ap.add_argument("--horizon-ms", type=float, default=100.0, help="autoscale: queue the planner tolerates, as time")
     ap.add_argument("--port", type=int, default=50600)
     ap.add_argument("--json", default="")
     a = ap.parse_args()
@@ -123,9 +129,14 @@ def run_router(a, world, states, cfg_model, backend):
     from blitz_scale_b200.router.server import controller_config_from_cluster
     feats = {"stop": "impl_blitz,impl_nvl,manually_scale", "live": "impl_blitz,impl_nvl,impl_live,manually_scale",
              "sllm": "impl_sllm,manually_scale" if a.model_path else "impl_sllm,cache_all_hit,manually_scale"}[a.mode]
+    extra = {}
+    if getattr(a, "autoscale", False):
+        feats = feats.replace(",manually_scale", "")
+        extra = dict(tokens_prefilled_per_sec=max(1, int(a.prefill_rate * a.horizon_ms * 1e-3)),
+                     tokens_transferred_per_sec=5000000, max_prefill=world - 1, max_decode=1, min_prefill=1, min_decode=1)
     cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
                                          max_blocks_per_replica=a.pages - 64, block_size=64, max_prefill_tokens=8192,
-                                         model_layers=cfg_model.layers)
+                                         model_layers=cfg_model.layers, **extra)
     g = torch.Generator().manual_seed(5)
     n_base, n_burst = int(a.base_rate * a.base_s), int(a.burst_rate * a.burst_s)
     arrivals = [i / a.base_rate for i in range(n_base)] + [a.base_s + i / a.burst_rate for i in range(n_burst)]
@@ -164,9 +175,10 @@ def run_router(a, world, states, cfg_model, backend):
         tasks = [asyncio.create_task(one(i, t)) for i, t in enumerate(arrivals)]
         await asyncio.sleep(a.base_s)
         t_trigger = rt.now()
-        for r in range(2, world):
-            assert rt.ctl.manual_scale(r, "Prefill", rt.now())
-        rt.wake.set()
+        if not getattr(a, "autoscale", False):
+            for r in range(2, world):
+                assert rt.ctl.manual_scale(r, "Prefill", rt.now())
+            rt.wake.set()
         await asyncio.gather(*tasks)
         t_end = rt.now()
         scale, loaded = {}, {}
@@ -176,7 +188,7 @@ def run_router(a, world, states, cfg_model, backend):
                     continue
                 if r not in scale and line.rstrip().endswith(("=> Prefill", "=> NewPrefill")):
                     scale[r] = t - t_trigger              # first moment the replica takes work
-                if line.rstrip().endswith("=> Prefill"):
+                if r not in loaded and line.rstrip().endswith("=> Prefill"):
                     loaded[r] = t - t_trigger             # all parameters resident, ordinary prefill replica
         scale = {"serving": scale, "loaded": loaded}
         await rt.stop()
@@ -186,9 +198,13 @@ def run_router(a, world, states, cfg_model, backend):
     records, scale, t_start, t_end, transitions = asyncio.run(go())
     ok = [r for r in records if r["ok"]]
     burst = [r for r in ok if r["burst"]]
-    tbt_all = [x for r in burst for x in r["tbt"]]
+    # as in the reference's statistics, the interval between the prefill token and the first decode token (which
+    # contains the KV migration) is not a time-between-tokens sample; it is reported on its own
+    tbt_all = [x for r in burst for x in r["tbt"][1:]]
+    first_gap = [r["tbt"][0] for r in burst if r["tbt"]]
     seg_bytes = backend.engine.seg.layout.total_bytes
-    out = {"bench": "cluster_scale_out", "model": a.model, "mode": a.mode, "gpus": world, "requests": len(records),
+    out = {"bench": "cluster_scale_out", "model": a.model, "mode": a.mode + ("+autoscale" if getattr(a, "autoscale", False) else ""),
+           "gpus": world, "requests": len(records),
            "failed": len(records) - len(ok), "prompt_len": a.prompt_len, "new_tokens": a.new_tokens,
            "base_rate": a.base_rate, "burst_rate": a.burst_rate,
            "scale_out_latency_ms": {str(r): round(v * 1e3, 2) for r, v in sorted(scale["serving"].items())},
@@ -198,6 +214,8 @@ def run_router(a, world, states, cfg_model, backend):
            "ttft_ms_p50": round(pct([r["ttft"] for r in burst], 0.5) * 1e3, 2),
            "ttft_ms_p99": round(pct([r["ttft"] for r in burst], 0.99) * 1e3, 2),
            "tbt_ms_p50": round(pct(tbt_all, 0.5) * 1e3, 2), "tbt_ms_p99": round(pct(tbt_all, 0.99) * 1e3, 2),
+           "first_decode_gap_ms_p50": round(pct(first_gap, 0.5) * 1e3, 2),
+           "first_decode_gap_ms_p99": round(pct(first_gap, 0.99) * 1e3, 2),
            "tokens_per_s": round(sum(r["tokens"] for r in ok) / max(1e-9, t_end - t_start), 1),
            "transitions": transitions[:24], "timing": "router wall clock (host), one box"}
     return out

@@ -742,8 +742,13 @@ class Controller {
     for (; dp > 0; --dp) if (!scale_up(true, now, &group)) break;
     for (; dd > 0; --dd) if (!scale_up(false, now, &group)) break;
     if (!group.empty()) scale_up_group(group, now);
-    if (dp < 0) scale_down(true, now);
-    if (dd < 0) scale_down(false, now);
+    // scale down only on a signal that has persisted for the scale-down threshold: with short planner horizons the
+    // raw signal flips within milliseconds and replicas would bounce between serving and draining
+    const double patience = cfg_.planner.scale_down_threshold_ms * 1e-3;
+    if (dp < 0) { if (down_since_p_ < 0) down_since_p_ = now; } else down_since_p_ = -1;
+    if (dd < 0) { if (down_since_d_ < 0) down_since_d_ = now; } else down_since_d_ = -1;
+    if (dp < 0 && now - down_since_p_ >= patience) scale_down(true, now);
+    if (dd < 0 && now - down_since_d_ >= patience) scale_down(false, now);
   }
 
   // `group`: inactive replicas chosen so far in this planner turn; they start together (one multicast).
@@ -999,6 +1004,7 @@ class Controller {
   std::vector<std::string> log_;
   std::map<std::string, double> counters_, gauges_;
   uint64_t next_op_ = 0;
+  double down_since_p_ = -1, down_since_d_ = -1;      // since when the planner has been asking for fewer replicas
   std::vector<std::pair<int, bool>> pending_scale_;  // (replica, as prefill) requested since the last step
   uint64_t stats_prefill_tokens_ = 0, stats_decode_tokens_ = 0;
   double last_plan_ = -1e9;
