@@ -110,6 +110,8 @@ def test_safetensors_reader_and_hf_conversion(tmp_path):
         got = torch.from_file(str(p), size=want.layout.total_bytes, dtype=torch.uint8)
         assert torch.equal(got, want.buffer[:want.layout.total_bytes])
         WeightSegment.check_sidecar(p.parent, cfg, 2, r, torch.bfloat16)
+    assert convert.main(["--src", str(tmp_path), "--model", "tiny", "--out", str(tmp_path / "cli")]) == 0
+    assert (tmp_path / "cli" / "segment.0.bin").stat().st_size == seg.layout.total_bytes
     # a truncated file is rejected, not mis-read
     raw = (tmp_path / "model-00002-of-00002.safetensors").read_bytes()
     (tmp_path / "bad.safetensors").write_bytes(raw[:len(raw) // 2])
@@ -133,3 +135,54 @@ def test_native_logger_and_contracts(tmp_path):
     text = logf.read_text()
     assert "INFO  python:0 hello info" in text and "hidden debug" not in text and "ERROR python:0 bad thing" in text
     assert "TRACE python:0 now visible" in text and "precondition failed" in text
+
+
+def test_router_http_with_native_tokenizer(trained):
+    """Text in -> native tokenizer -> generation -> text out, over the HTTP API against a stub worker."""
+    import asyncio
+    import socket
+
+    import aiohttp
+
+    from blitz_scale_b200.router.runtime import RouterRuntime
+    from blitz_scale_b200.router.server import controller_config_from_cluster, serve_router
+    from blitz_scale_b200.sim.stub_worker import StubBackend
+    from blitz_scale_b200.worker.service import serve
+    ref, path = trained
+    socks = [socket.socket() for _ in range(2)]
+    for s_ in socks:
+        s_.bind(("127.0.0.1", 0))
+    wport, hport = [s_.getsockname()[1] for s_ in socks]
+    for s_ in socks:
+        s_.close()
+
+    async def go():
+        stop, ready = asyncio.Event(), asyncio.Event()
+        b = StubBackend(0, 1, vocab=ref.get_vocab_size())
+        tasks = [asyncio.create_task(serve(b, "127.0.0.1", wport, stop_event=stop, ready_event=ready))]
+        await ready.wait()
+        cfg = controller_config_from_cluster({"init_states": ["Normal"], "machines": [0]}, 1, "impl_blitz,manually_scale",
+                                             max_blocks_per_replica=4000)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{wport}"], model_layers=2)
+        tasks.append(asyncio.create_task(serve_router(rt, "127.0.0.1", hport, stop=stop, model_name="tiny",
+                                                      tokenizer_path=path, tokenizer_workers=2)))
+        await asyncio.sleep(0.3)
+        text = "Hello, world! It's 2024 and we're testing tokenizers."
+        async with aiohttp.ClientSession() as s:
+            async with s.post(f"http://127.0.0.1:{hport}/generate",
+                              json={"inputs": text, "parameters": {"max_new_tokens": 5, "details": True}}) as r:
+                assert r.status == 200, await r.text()
+                body = await r.json()
+                hdr = dict(r.headers)
+            async with s.post(f"http://127.0.0.1:{hport}/generate", json={"input_tokens": [10 ** 6], "parameters": {}}) as r:
+                assert r.status == 422 and "input_tokens" in (await r.json())["error"]
+        stop.set()
+        await asyncio.wait(tasks, timeout=5)
+        return text, body, hdr
+
+    text, body, hdr = asyncio.run(go())
+    t = core.Tokenizer.from_file(path)
+    assert int(hdr["x-input-length"]) == len(t.encode(text)) == len(ref.encode(text).ids)
+    ids = [tk["id"] for tk in body["details"]["tokens"]]
+    assert len(ids) == 5 and body["generated_text"] == t.decode(ids, True)
+    assert [tk["text"] for tk in body["details"]["tokens"]] == [t.decode([i], False) for i in ids]
