@@ -65,6 +65,7 @@ struct ControllerConfig {
   std::string features = "impl_blitz,impl_fast_pro,impl_live_pro";
   bool autoscale = true;
   double mock_load_ms = 0;
+  double param_gb = 0;   // parameter bytes per replica in GB (0: unknown); only used for the transfer-rate metric
 };
 
 class Controller {
@@ -200,6 +201,15 @@ class Controller {
   // A parameter transfer / load finished on `replica` (its op may cover several destinations).
   void on_params_done(uint64_t op_id, double now) {
     Op op = take_op(op_id);
+    if (op.started >= 0 && !op.targets.empty()) {
+      // first-class scale-out metrics: how long the parameter transfer took and what each destination received
+      const double dt = std::max(1e-9, now - op.started);
+      counters_["blitz_scale_out_total"] += static_cast<double>(op.targets.size());
+      counters_["blitz_scale_out_seconds_sum"] += dt;
+      gauges_["blitz_last_scale_out_seconds"] = dt;
+      gauges_["blitz_last_scale_out_fanout"] = static_cast<double>(op.targets.size());
+      if (cfg_.param_gb > 0) gauges_["blitz_last_param_transfer_gbs_per_replica"] = cfg_.param_gb / dt;
+    }
     for (int s : op.sources) {
       steer_.set_nvlink_busy(s, false);
       reps_[s].m.marker.reset();
@@ -363,6 +373,7 @@ class Controller {
     int replica = -1, peer = -1, partial = 0;
     ResidentBatch batch;
     std::vector<int> sources, targets;
+    double started = -1;   // parameter transfers: when the operation was issued
   };
   struct Relayed {
     ResidentBatch batch;
@@ -837,6 +848,7 @@ class Controller {
     }
     a.live = any_live;
     op.kind = a.type;
+    op.started = now;
     ops_[++next_op_] = op;
     a.op_id = next_op_;
     out_.push_back(a);
@@ -909,6 +921,7 @@ class Controller {
       }
     }
     op.kind = a.type;
+    op.started = now;
     ops_[++next_op_] = op;
     a.op_id = next_op_;
     out_.push_back(a);

@@ -381,6 +381,11 @@ def main(argv=None) -> None:
         migration_upper=a.migration_upper_bound, min_prefill=a.min_prefill_num, max_prefill=a.max_prefill_num,
         min_decode=a.min_decode_num, max_decode=a.max_decode_num, scale_down_threshold_ms=a.scale_down_threshold_millis)
     layers = get_config(a.model_name).layers
+    try:
+        from ..runtime import core as _core
+        cfg.param_gb = _core.build_segment_layout(a.model_name, a.tensor_parallel_size, 2).total_bytes * a.tensor_parallel_size / 1e9
+    except Exception:  # noqa: BLE001 - only feeds a metric
+        pass
     async def amain():
         # the gRPC channels of the runtime belong to the event loop that creates them: build it inside the loop
         rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv)

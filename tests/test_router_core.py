@@ -363,6 +363,9 @@ def test_simultaneous_scale_ups_share_one_multicast():
     assert not [x for x in ctl.step(0.01) if x.type == core.ActionType.TanzBroadcast]              # nothing is re-issued
     ctl.on_params_done(a.op_id, 0.03)
     assert [ctl.state_name(r) for r in range(2, 6)] == ["Prefill"] * 3 + ["Decode"]
+    g, c = dict(ctl.gauges()), dict(ctl.counters())
+    assert g["blitz_last_scale_out_seconds"] == pytest.approx(0.03) and g["blitz_last_scale_out_fanout"] == 4
+    assert c["blitz_scale_out_total"] == 4 and c["blitz_scale_out_seconds_sum"] == pytest.approx(0.03)
     assert ctl.metric(0).marker == "" and ctl.metric(1).marker == ""
     # live variant: every new prefill replica serves at once; one old prefill replica is paired as the helper
     cfg = _cfg(["Prefill", "Decode"] + ["Inactive"] * 2, "impl_blitz,impl_nvl,impl_live,manually_scale")
