@@ -228,7 +228,9 @@ class GpuBackend(Backend):
                     self.zag.set_loaded(st.embed_ready, st.layers_ready, st.head_ready)
                 d = self.zag.next()
                 if d.step in (core.ZagStep.Idle, core.ZagStep.Blocked):
-                    self.zag_cv.wait(0.0005)
+                    # nothing to run: sleep until a task or a parameter unit arrives (both notify the condition); the
+                    # short timeout only bounds the wait while layers are still landing
+                    self.zag_cv.wait(0.0005 if d.step == core.ZagStep.Blocked else 0.05)
                     continue
                 task = self.zag_tasks[d.batch_id]
                 eng, b = self.engine, task["batch"]
