@@ -143,7 +143,7 @@ void bind_router(py::module_& m) {
       .def_property_readonly("waiting_prefill_tokens", &Controller::waiting_prefill_tokens)
       .def("counters", &Controller::counters).def("gauges", &Controller::gauges).def("drain_log", &Controller::drain_log)
       .def("system_metrics_line", &Controller::system_metrics_line).def("idle", &Controller::idle)
-      .def("token_counts", &Controller::token_counts)
+      .def("token_counts", &Controller::token_counts).def("on_replica_unhealthy", &Controller::on_replica_unhealthy)
       .def("inflight_ops", &Controller::inflight_ops).def("total_used_blocks", &Controller::total_used_blocks)
       .def("request", [](const Controller& c, uint64_t id) -> py::object {
         const RequestEntry* e = c.request(id); if (!e) return py::none(); return py::cast(*e); })

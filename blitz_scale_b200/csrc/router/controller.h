@@ -277,6 +277,16 @@ class Controller {
     lose_replica(op.replica, now, &op);
   }
 
+  // Failure detector verdict (missed heartbeats): the replica is gone even if no operation was in flight on it.
+  // Requests it held are failed or re-queued exactly as after a failed RPC; operations still in flight on it fail
+  // on their own later and find the replica already inactive.
+  bool on_replica_unhealthy(int replica, double now) {
+    if (replica < 0 || replica >= num_replicas() || reps_[replica].m.state == RState::Inactive) return false;
+    counters_["blitz_replica_lost"] += 1;
+    lose_replica(replica, now, nullptr);
+    return true;
+  }
+
   // ------------------------------------------------------------------------------------ step
   std::vector<Action> step(double now) {
     if (cfg_.autoscale && !features_.has("manually_scale") && now - last_plan_ >= cfg_.planner_interval_ms * 1e-3) {

@@ -37,8 +37,13 @@ class LiveRequest:
 
 class RouterRuntime:
     def __init__(self, cfg: "core.ControllerConfig", worker_urls: List[str], model_layers: int = 32,
-                 model_path: str = "", stat_csv: str = ""):
+                 model_path: str = "", stat_csv: str = "", health_interval_s: float = 0.0, health_misses: int = 2):
         self.cfg = cfg
+        # failure detector: every `health_interval_s` each active replica's ranks are pinged with the Health RPC;
+        # `health_misses` consecutive misses (error or no answer within the interval) declare the replica lost.
+        # The reference has no detector (its Health is a stub and a failed RPC panics the replica task).
+        self.health_interval_s, self.health_misses = health_interval_s, max(1, health_misses)
+        self._missed: Dict[int, int] = {}
         # 500 ms CSV of prefill / decode token deltas (router_v2/src/statistic.rs:26-63)
         self.stat_csv = open(stat_csv, "w", buffering=1) if stat_csv else None
         if self.stat_csv:
@@ -85,8 +90,29 @@ class RouterRuntime:
         self.ctl.client_gone(rid)
 
     # ------------------------------------------------------------------ main loop
+    async def _health_loop(self) -> None:
+        while not self.stopped:
+            await asyncio.sleep(self.health_interval_s)
+            for rep in range(self.ctl.num_replicas):
+                if self.ctl.state_name(rep) == "Inactive":
+                    self._missed.pop(rep, None)
+                    continue
+                try:
+                    await asyncio.wait_for(asyncio.gather(*[self.stubs[r].health(timeout=self.health_interval_s)
+                                                            for r in self._ranks(rep)]), timeout=self.health_interval_s)
+                    self._missed[rep] = 0
+                except Exception:  # noqa: BLE001 - any failure to answer counts as a miss
+                    self._missed[rep] = self._missed.get(rep, 0) + 1
+                    if self._missed[rep] >= self.health_misses:
+                        log.error("replica %d missed %d heartbeats: declared lost", rep, self._missed[rep])
+                        self.ctl.on_replica_unhealthy(rep, self.now())
+                        self._missed[rep] = 0
+                        self.wake.set()
+
     async def run(self) -> None:
         last_metrics = 0.0
+        if self.health_interval_s > 0:
+            self._spawn(self._health_loop())
         while not self.stopped:
             now = self.now()
             actions = self.ctl.step(now)

@@ -364,6 +364,8 @@ def main(argv=None) -> None:
     ap.add_argument("--scale-down-threshold-millis", type=float, default=333)
     ap.add_argument("--mock-load-millis", type=float, default=0)
     ap.add_argument("--log-level", default="INFO")
+    ap.add_argument("--health-interval-ms", type=float, default=0.0, help="ping every active replica this often (0 = off)")
+    ap.add_argument("--health-misses", type=int, default=2, help="consecutive missed pings that declare a replica lost")
     ap.add_argument("--statistic-csv", default="", help="write prefill/decode token deltas every 500 ms to this file")
     a = ap.parse_args(argv)
     logging.basicConfig(level=a.log_level, format="%(asctime)s %(name)s %(message)s")
@@ -388,7 +390,8 @@ def main(argv=None) -> None:
         pass
     async def amain():
         # the gRPC channels of the runtime belong to the event loop that creates them: build it inside the loop
-        rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv)
+        rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv,
+                           health_interval_s=a.health_interval_ms * 1e-3, health_misses=a.health_misses)
         await serve_router(rt, a.hostname, a.port, model_name=a.model_name, max_input_length=a.max_input_length,
                            max_total_tokens=a.max_total_tokens, tokenizer_path=a.tokenizer_path,
                            tokenizer_workers=a.validation_workers)

@@ -262,3 +262,46 @@ def test_experiment_runs_processes_end_to_end(tmp_path):
     summary = json.load(open(d / "summary.json"))
     assert "slo" in summary
     assert "attached to a different loop" not in open(d / "router.log").read()
+
+
+def test_heartbeat_failure_detector_marks_idle_replica_lost():
+    """A worker that stops answering Health is declared lost although no operation was in flight on it; traffic
+    then goes to the surviving prefill replica only (host-side failure: the worker's server is shut down)."""
+    async def go():
+        ports = _free_ports(3)
+        stops, tasks = [], []
+        states = ["Prefill", "Decode", "Prefill"]
+        backends = [StubBackend(r, 3, ready=True) for r in range(3)]
+        for r, b in enumerate(backends):
+            ready, stop = asyncio.Event(), asyncio.Event()
+            tasks.append(asyncio.create_task(serve(b, "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            await ready.wait()
+            stops.append(stop)
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * 3}, 1, "impl_blitz,impl_nvl,manually_scale",
+                                             max_blocks_per_replica=4000)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, health_interval_s=0.1, health_misses=2)
+        lt = asyncio.create_task(rt.run())
+        await asyncio.sleep(0.35)
+        assert rt.ctl.state_name(2) == "Prefill"          # healthy so far
+        stops[2].set()                                     # the third worker goes away while idle
+        for _ in range(60):
+            await asyncio.sleep(0.1)
+            if rt.ctl.state_name(2) == "Inactive":
+                break
+        assert rt.ctl.state_name(2) == "Inactive" and dict(rt.ctl.counters()).get("blitz_replica_lost") == 1
+        # the cluster keeps serving on the remaining replicas
+        lr = rt.submit(list(range(40)), 4)
+        toks = []
+        while True:
+            ev = await asyncio.wait_for(lr.queue.get(), timeout=10)
+            assert ev[0] != "error"
+            toks.append(ev[1])
+            if ev[2]:
+                break
+        assert len(toks) == 4 and rt.ctl.state_name(0) == "Prefill" and rt.ctl.state_name(1) == "Decode"
+        await rt.stop()
+        lt.cancel()
+        for s in stops:
+            s.set()
+        await asyncio.wait(tasks, timeout=5)
+    asyncio.run(go())
