@@ -121,6 +121,11 @@ def build_all(force: bool = False):
     return k, h
 
 
-if __name__ == "__main__":
+def main() -> int:
     k, h = build_all(force="--force" in sys.argv)
     print("built", k, h)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

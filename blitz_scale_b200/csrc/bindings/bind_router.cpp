@@ -123,7 +123,7 @@ void bind_router(py::module_& m) {
       .def_readwrite("planner_interval_ms", &ControllerConfig::planner_interval_ms)
       .def_readwrite("model_layers", &ControllerConfig::model_layers).def_readwrite("model_name", &ControllerConfig::model_name)
       .def_readwrite("planner", &ControllerConfig::planner).def_readwrite("features", &ControllerConfig::features)
-      .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
+      .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("quarantine_ms", &ControllerConfig::quarantine_ms).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
   py::class_<Controller::TokenOut>(m, "TokenOut")
       .def(py::init([](uint64_t id, int32_t tok, bool fin) { return Controller::TokenOut{id, tok, fin}; }));
   py::class_<ReplicaMetric>(m, "ReplicaMetric")
@@ -136,7 +136,7 @@ void bind_router(py::module_& m) {
       .def("submit", &Controller::submit).def("client_gone", &Controller::client_gone)
       .def("on_prefill_done", &Controller::on_prefill_done).def("on_decode_done", &Controller::on_decode_done)
       .def("on_migrate_done", &Controller::on_migrate_done).def("on_params_done", &Controller::on_params_done)
-      .def("on_relay_done", &Controller::on_relay_done).def("on_failure", &Controller::on_failure)
+      .def("on_relay_done", &Controller::on_relay_done).def("on_failure", &Controller::on_failure, py::arg("op_id"), py::arg("now"), py::arg("failed_replica") = -1)
       .def("step", &Controller::step).def("manual_scale", &Controller::manual_scale)
       .def_property_readonly("num_replicas", &Controller::num_replicas).def("metric", &Controller::metric)
       .def("state_name", &Controller::state_name).def_property_readonly("queue_size", &Controller::queue_size)

@@ -66,6 +66,7 @@ struct ControllerConfig {
   bool autoscale = true;
   double mock_load_ms = 0;
   double param_gb = 0;   // parameter bytes per replica in GB (0: unknown); only used for the transfer-rate metric
+  double quarantine_ms = 5000;  // a lost replica is not chosen for scale-up again before this much time has passed
 };
 
 class Controller {
@@ -107,6 +108,7 @@ class Controller {
   struct TokenOut { uint64_t request_id; int32_t token; bool finished; };
 
   void on_prefill_done(uint64_t op_id, const std::vector<TokenOut>& toks, double now) {
+    if (late_answer(op_id)) return;
     Op op = take_op(op_id);
     Rep& rep = reps_[op.replica];
     rep.busy = false;
@@ -139,8 +141,7 @@ class Controller {
       return;
     }
     shrink_blocks(op.replica, rb);
-    if (rep.colocated || num_in_state(RState::Decode) + num_in_state(RState::AusDecode) +
-                                 num_in_state(RState::MutatingToDecode) + num_in_state(RState::LoadingDecode) == 0) {
+    if (rep.colocated || no_decode_side()) {
       rep.decode_batches.push_back(std::move(rb));  // no decode side: decode where the KV already is
     } else {
       rep.pending_migration.push_back(std::move(rb));
@@ -148,6 +149,7 @@ class Controller {
   }
 
   void on_decode_done(uint64_t op_id, const std::vector<TokenOut>& toks, double now) {
+    if (late_answer(op_id)) return;
     Op op = take_op(op_id);
     Rep& rep = reps_[op.replica];
     rep.busy = false;
@@ -174,6 +176,7 @@ class Controller {
 
   void on_migrate_done(uint64_t op_id, double now) {
     (void)now;
+    if (late_answer(op_id)) return;
     Op op = take_op(op_id);
     Rep& src = reps_[op.replica];
     Rep& dst = reps_[op.peer];
@@ -200,6 +203,7 @@ class Controller {
 
   // A parameter transfer / load finished on `replica` (its op may cover several destinations).
   void on_params_done(uint64_t op_id, double now) {
+    if (late_answer(op_id)) return;
     Op op = take_op(op_id);
     if (op.started >= 0 && !op.targets.empty()) {
       // first-class scale-out metrics: how long the parameter transfer took and what each destination received
@@ -234,6 +238,7 @@ class Controller {
   // Relay RPC answered: the new instance handed over `batch_id` at transformer layer `next_layer`
   // (has_batch = false: nothing was left to hand over).
   void on_relay_done(uint64_t op_id, bool has_batch, uint64_t batch_id, int next_layer, double now) {
+    if (late_answer(op_id)) return;
     Op op = take_op(op_id);
     const int neu = op.replica, old = op.peer;
     Rep& nrep = reps_[neu];
@@ -269,21 +274,24 @@ class Controller {
     maybe_finish_refractory(neu, now);
   }
 
-  // An RPC of `op_id` failed: the replica is lost (fail-stop workers, src/util/cuda_utils.h:15-22).
-  void on_failure(uint64_t op_id, double now) {
-    if (!ops_.count(op_id)) return;
-    Op op = take_op(op_id);
+  // An RPC of `op_id` failed: a replica is lost (fail-stop workers, src/util/cuda_utils.h:15-22).  `failed_replica`
+  // names the participant whose call failed when the caller knows it (a migration or a broadcast has several);
+  // without it the replica the operation was issued to is taken.
+  void on_failure(uint64_t op_id, double now, int failed_replica = -1) {
+    if (late_answer(op_id)) return;
+    auto it = ops_.find(op_id);
+    if (it == ops_.end()) return;
     counters_["blitz_request_failure"] += 1;
-    lose_replica(op.replica, now, &op);
+    const int issued_to = it->second.replica;
+    lose_replica(failed_replica >= 0 && failed_replica < num_replicas() ? failed_replica : issued_to, now);
+    if (ops_.count(op_id)) lose_replica(issued_to, now);  // the named replica was no participant after all
   }
 
   // Failure detector verdict (missed heartbeats): the replica is gone even if no operation was in flight on it.
-  // Requests it held are failed or re-queued exactly as after a failed RPC; operations still in flight on it fail
-  // on their own later and find the replica already inactive.
   bool on_replica_unhealthy(int replica, double now) {
     if (replica < 0 || replica >= num_replicas() || reps_[replica].m.state == RState::Inactive) return false;
     counters_["blitz_replica_lost"] += 1;
-    lose_replica(replica, now, nullptr);
+    lose_replica(replica, now);
     return true;
   }
 
@@ -366,6 +374,7 @@ class Controller {
   struct Rep {
     ReplicaMetric m;
     bool colocated = false;
+    double lost_at = -1e18;   // when the replica was last declared lost
     bool busy = false;        // an inference RPC is in flight
     bool migrating = false;   // this source has a migration in flight
     bool relay_wait = false;  // OldPrefill parked in the relay queue
@@ -384,6 +393,10 @@ class Controller {
     ResidentBatch batch;
     std::vector<int> sources, targets;
     double started = -1;   // parameter transfers: when the operation was issued
+  };
+  struct Cancelled {
+    uint64_t batch_id = 0;
+    std::vector<int> clear_on;   // surviving replicas that may still build state for the batch
   };
   struct Relayed {
     ResidentBatch batch;
@@ -676,7 +689,15 @@ class Controller {
     if (rep.migrating || rep.pending_migration.empty()) return;
     ResidentBatch& b = rep.pending_migration.front();
     const int dst = pick_decode_target(b.blocks);
-    if (dst < 0) return;
+    if (dst < 0) {
+      // no decode side is left (it was lost after this batch was queued for it): decode where the KV already is,
+      // as a prefill that completes in that situation does
+      if (no_decode_side() && (rep.m.state == RState::Prefill || rep.m.state == RState::ShuttingPrefill)) {
+        rep.decode_batches.push_back(std::move(b));
+        rep.pending_migration.pop_front();
+      }
+      return;
+    }
     acquire_target(dst, b.blocks);
     rep.migrating = true;
     Action a = make_simple(ActionType::Migrate, src, b.id);
@@ -734,7 +755,37 @@ class Controller {
       if (is_prefill_side(r.m.state)) { v.num_prefill += 1; v.prefill_used_blocks += r.m.used_blocks; }
       if (is_decode_side(r.m.state)) { v.num_decode += 1; v.decode_used_blocks += r.m.used_blocks; }
     }
-    if (v.num_prefill == 0 || v.num_decode == 0) return;  // colocated deployments do not autoscale roles
+    if (v.num_prefill == 0 || v.num_decode == 0) {
+      bool any_colocated = false;
+      for (auto& r : reps_) any_colocated = any_colocated || r.colocated;
+      if (any_colocated) return;  // colocated deployments do not autoscale roles
+      // a disaggregated deployment lost every replica of one role (failures): restore it before anything else
+      if (v.num_decode == 0 && !scale_up(false, now)) {
+        // nothing to load into: turn the least loaded of two or more prefill replicas into the decode side
+        int pick = -1, n_prefill = 0;
+        for (int r = 0; r < num_replicas(); ++r) {
+          if (reps_[r].m.state != RState::Prefill || reps_[r].partner >= 0) continue;
+          ++n_prefill;
+          if (pick < 0 || reps_[r].m.used_blocks < reps_[pick].m.used_blocks) pick = r;
+        }
+        if (n_prefill >= 2) set_state(pick, RState::MutatingToDecode);
+      }
+      if (v.num_prefill == 0 && !scale_up(true, now)) {
+        // nothing to load into either: the least loaded decode replica takes the prefill role; if it was the only
+        // one it keeps its resident batches and serves both phases until a replica can be added
+        int pick = -1;
+        for (int r = 0; r < num_replicas(); ++r) {
+          if (reps_[r].m.state != RState::Decode) continue;
+          if (pick < 0 || reps_[r].m.used_blocks < reps_[pick].m.used_blocks) pick = r;
+        }
+        if (pick >= 0) {
+          set_state(pick, RState::ShuttingNull);
+          reps_[pick].m.shutting_since = -1;
+          set_state(pick, RState::Prefill);
+        }
+      }
+      return;
+    }
     v.waiting_prefill_tokens = queue_.waiting_prefill_tokens();
     ScaleTarget t = plan_scale(cfg_.planner, v);
     last_target_ = t;
@@ -772,6 +823,12 @@ class Controller {
     if (dd < 0 && now - down_since_d_ >= patience) scale_down(false, now);
   }
 
+  bool quarantined(int r, double now) const { return (now - reps_[r].lost_at) * 1e3 < cfg_.quarantine_ms; }
+  bool no_decode_side() const {
+    return num_in_state(RState::Decode) + num_in_state(RState::AusDecode) + num_in_state(RState::MutatingToDecode) +
+               num_in_state(RState::LoadingDecode) == 0;
+  }
+
   // `group`: inactive replicas chosen so far in this planner turn; they start together (one multicast).
   bool scale_up(bool prefill, double now, std::vector<std::pair<int, bool>>* group = nullptr) {
     // 1. revive a replica that is shutting down
@@ -783,7 +840,7 @@ class Controller {
       if (reps_[r].m.state == RState::ShuttingNull) { scale_up_one(r, prefill, now); return true; }
     // 3. bring up an inactive replica
     for (int r = 0; r < num_replicas(); ++r) {
-      if (reps_[r].m.state != RState::Inactive) continue;
+      if (reps_[r].m.state != RState::Inactive || quarantined(r, now)) continue;
       if (!group) return scale_up_one(r, prefill, now);
       bool taken = false;
       for (auto& pr : *group) taken = taken || pr.first == r;
@@ -976,35 +1033,151 @@ class Controller {
     }
   }
 
-  void lose_replica(int r, double now, Op* op) {
-    (void)now;
+  // Replica `r` is gone.  Everything that involved it is settled here, at once: operations in flight on it or
+  // towards it are cancelled (their answers, if they still come, are ignored), prompts it had not answered go back
+  // to the head of the queue, requests whose KV lived on it or was on its way to or from it fail, and the surviving
+  // side of every such operation gets its pages and locks back.  `quarantine` = false resets a healthy replica whose
+  // parameter transfer was aborted because another participant was lost.
+  void lose_replica(int r, double now, bool quarantine = true) {
     Rep& rep = reps_[r];
-    auto fail_batch = [&](const ResidentBatch& b) {
-      for (uint64_t id : b.request_ids) {
+    if (quarantine) rep.lost_at = now;
+    auto fail_ids = [&](const std::vector<uint64_t>& ids) {
+      for (uint64_t id : ids) {
+        if (!requests_.count(id)) continue;
         Action a;
         a.type = ActionType::Fail; a.request_id = id; a.final = true;
         out_.push_back(a);
         requests_.erase(id);
       }
     };
-    if (op && (op->kind == ActionType::Prefill || op->kind == ActionType::ZagPrefill)) {
-      // nothing was delivered yet: the requests go back to the head of the queue
+    std::vector<uint64_t> requeued;  // a live-prefill batch is known both by its operation and by its replica
+    auto requeue_ids = [&](const std::vector<uint64_t>& ids) {
       std::vector<RequestEntry> es;
-      for (uint64_t id : op->batch.request_ids)
-        if (requests_.count(id)) es.push_back(requests_[id]);
-      queue_.requeue_front(es);
-    } else if (op) {
-      fail_batch(op->batch);
+      for (uint64_t id : ids) {
+        if (!requests_.count(id) || std::find(requeued.begin(), requeued.end(), id) != requeued.end()) continue;
+        es.push_back(requests_[id]);
+        requeued.push_back(id);
+      }
+      if (!es.empty()) queue_.requeue_front(es);
+    };
+    auto cancel = [&](uint64_t id, uint64_t batch_id, std::vector<int> survivors) {
+      Cancelled c;
+      c.batch_id = batch_id;
+      for (int s : survivors)
+        if (s >= 0 && s != r) c.clear_on.push_back(s);
+      cancelled_[id] = c;
+    };
+    auto involves = [&](const Op& o) {
+      return o.replica == r || o.peer == r || std::find(o.sources.begin(), o.sources.end(), r) != o.sources.end() ||
+             std::find(o.targets.begin(), o.targets.end(), r) != o.targets.end();
+    };
+
+    // relayed batches with the lost replica as first half, second half or destination
+    for (auto it = relayed_.begin(); it != relayed_.end();) {
+      Relayed& x = it->second;
+      if (x.new_replica != r && x.old_replica != r && x.target != r) { ++it; continue; }
+      fail_ids(x.batch.request_ids);
+      for (auto oi = ops_.begin(); oi != ops_.end();) {
+        Op& o = oi->second;
+        const bool mine = (o.kind == ActionType::PrefillPP || o.kind == ActionType::MigratePartial) && o.batch.id == x.batch.id;
+        if (!mine) { ++oi; continue; }
+        if (o.kind == ActionType::PrefillPP) reps_[o.replica].busy = reps_[o.replica].relay_wait = false;
+        cancel(oi->first, x.batch.id, {o.replica, o.peer});
+        oi = ops_.erase(oi);
+      }
+      const bool new_holds = !((x.fst_started && x.fst_done) || (x.next_layer == 0 && x.fst_done && x.snd_started));
+      if (x.fst_started && !x.fst_done && reps_[x.new_replica].m.flying_partial > 0) reps_[x.new_replica].m.flying_partial -= 1;
+      if (new_holds && x.new_replica != r) {
+        release_blocks(x.new_replica, x.blocks);
+        out_.push_back(make_simple(ActionType::ClearCache, x.new_replica, x.batch.id));
+      }
+      if (!x.snd_done && x.old_replica != r) {
+        release_blocks(x.old_replica, x.blocks);
+        out_.push_back(make_simple(ActionType::ClearCache, x.old_replica, x.batch.id));
+      }
+      if (x.target >= 0 && x.target != r) {
+        finish_relayed_target(x);
+        out_.push_back(make_simple(ActionType::ClearCache, x.target, x.batch.id));
+      }
+      it = relayed_.erase(it);
     }
-    for (auto& b : rep.pending_migration) fail_batch(b);
-    for (auto& b : rep.decode_batches) if (!b.in_step) fail_batch(b);
+
+    // every other operation in flight that involves the lost replica
+    std::vector<uint64_t> ids;
+    for (auto& kv : ops_)
+      if (involves(kv.second)) ids.push_back(kv.first);
+    std::vector<int> aborted_loads;
+    for (uint64_t id : ids) {
+      auto it = ops_.find(id);
+      if (it == ops_.end()) continue;
+      Op o = std::move(it->second);
+      ops_.erase(it);
+      const int other = o.replica == r ? o.peer : o.replica;
+      switch (o.kind) {
+        case ActionType::Prefill:
+        case ActionType::ZagPrefill:
+          requeue_ids(o.batch.request_ids);  // nothing was delivered yet
+          cancel(id, o.batch.id, {});
+          break;
+        case ActionType::Decode:
+          cancel(id, o.batch.id, {});        // its batches are resident on the lost replica: failed below
+          break;
+        case ActionType::Migrate:
+          fail_ids(o.batch.request_ids);
+          release_blocks(other, o.batch.blocks);
+          if (o.replica == r) unlock_target(other);
+          else reps_[other].migrating = false;
+          out_.push_back(make_simple(ActionType::ClearCache, other, o.batch.id));
+          cancel(id, o.batch.id, {other});
+          break;
+        case ActionType::Relay:
+          if (o.peer != r) reps_[o.peer].busy = reps_[o.peer].relay_wait = false;
+          cancel(id, 0, {});
+          break;
+        case ActionType::PrefillPP:
+        case ActionType::MigratePartial:  // a relayed batch that is no longer tracked: nothing left to settle
+          if (o.kind == ActionType::PrefillPP && o.replica != r) reps_[o.replica].busy = reps_[o.replica].relay_wait = false;
+          cancel(id, o.batch.id, {o.replica, o.peer});
+          break;
+        default:  // a parameter transfer: without one of its participants nobody's copy completes
+          for (int s : o.sources) {
+            steer_.set_nvlink_busy(s, false);
+            reps_[s].m.marker.reset();
+          }
+          for (int d : o.targets)
+            if (d != r) aborted_loads.push_back(d);
+          cancel(id, 0, {});
+          break;
+      }
+    }
+
+    for (auto& b : rep.pending_migration) fail_ids(b.request_ids);
+    for (auto& b : rep.decode_batches) fail_ids(b.request_ids);
+    for (auto& b : rep.inflight_zag) requeue_ids(b.request_ids);
     rep.pending_migration.clear();
     rep.decode_batches.clear();
     rep.inflight_zag.clear();
     rep.busy = rep.migrating = rep.relay_wait = false;
+    rep.incoming = 0;
     rep.m.used_blocks = 0;
+    rep.m.flying_partial = 0;
     rep.m.model_loaded = false;
-    rep.partner = -1;
+    rep.m.shutting_since = -1;
+    rep.m.marker.reset();
+    if (rep.partner >= 0) {
+      Rep& other = reps_[rep.partner];
+      if (other.partner == r) {
+        other.partner = -1;
+        other.relay_wait = false;
+        if (other.m.state == RState::OldPrefill) {
+          other.busy = false;
+          for (auto& kv : ops_) other.busy = other.busy || (kv.second.replica == rep.partner &&
+                                                              (kv.second.kind == ActionType::Prefill || kv.second.kind == ActionType::Decode));
+          set_state(rep.partner, RState::Prefill);
+        }
+      }
+      rep.partner = -1;
+    }
     steer_.record_model_unloaded(r, now);
     steer_.set_nvlink_busy(r, false);
     if (rep.m.state != RState::Inactive) {
@@ -1013,6 +1186,23 @@ class Controller {
       rep.m.dst_busy = true;
       log_transition(r, old, RState::Inactive);
     }
+    for (int d : aborted_loads) {
+      lose_replica(d, now, false);
+      Action a = make_simple(ActionType::ResetStatus, d, 0);
+      a.dst_ranks = steer_.ranks_of_replica(d);
+      out_.push_back(a);
+    }
+  }
+
+  // Answer (or failure) of an operation that was cancelled when a replica was lost: what the surviving workers
+  // built for it in the meantime is dropped.
+  bool late_answer(uint64_t op_id) {
+    auto it = cancelled_.find(op_id);
+    if (it == cancelled_.end()) return false;
+    for (int s : it->second.clear_on)
+      if (reps_[s].m.state != RState::Inactive) out_.push_back(make_simple(ActionType::ClearCache, s, it->second.batch_id));
+    cancelled_.erase(it);
+    return true;
   }
 
   ControllerConfig cfg_;
@@ -1023,6 +1213,7 @@ class Controller {
   std::map<uint64_t, RequestEntry> requests_, finished_;
   std::map<uint64_t, Op> ops_;
   std::map<uint64_t, Relayed> relayed_;
+  std::map<uint64_t, Cancelled> cancelled_;
   std::vector<Action> out_;
   std::vector<std::string> log_;
   std::map<std::string, double> counters_, gauges_;

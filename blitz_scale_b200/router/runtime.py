@@ -22,6 +22,25 @@ from ..utils.tracing import child_traceparent, new_traceparent
 from .stub import CURRENT_TRACE, WorkerStub, encode_prefill_case
 
 log = logging.getLogger("blitz.router")
+
+
+class RankFailure(Exception):
+    """An RPC to `rank` failed while carrying out an action."""
+
+    def __init__(self, rank: int, cause: BaseException):
+        super().__init__(f"rank {rank}: {type(cause).__name__}: {cause}")
+        self.rank = rank
+
+
+def _is_unreachable(e: BaseException) -> bool:
+    code = getattr(e, "code", None)
+    try:
+        import grpc
+        return callable(code) and code() in (grpc.StatusCode.UNAVAILABLE, grpc.StatusCode.DEADLINE_EXCEEDED)
+    except Exception:  # noqa: BLE001
+        return False
+
+
 A = core.ActionType
 
 
@@ -156,6 +175,22 @@ class RouterRuntime:
         self._tasks.add(t)
         t.add_done_callback(self._tasks.discard)
 
+    async def _all(self, ranks, calls) -> list:
+        """Await one call per rank; if any fails, raise `RankFailure` naming the rank to blame.  A migration or a
+        broadcast spans several replicas and a healthy participant's call can fail merely because its peer went
+        away (a bounded wait that ran out), so a rank that cannot be reached at all is blamed before one that
+        answered with an error."""
+        res = await asyncio.gather(*calls, return_exceptions=True)
+        bad = [(r, e) for r, e in zip(ranks, res) if isinstance(e, BaseException)]
+        if not bad:
+            return res
+        for r, e in bad:
+            if isinstance(e, asyncio.CancelledError):
+                raise e
+        unreachable = [(r, e) for r, e in bad if _is_unreachable(e)]
+        r, e = (unreachable or bad)[0]
+        raise RankFailure(r, e) from e
+
     def _ranks(self, replica: int) -> List[int]:
         return [replica * self.tp + i for i in range(self.tp)]
 
@@ -195,9 +230,10 @@ class RouterRuntime:
         except asyncio.CancelledError:
             raise
         except Exception as e:  # noqa: BLE001  an RPC failed: the replica is gone
-            log.error("RPC for %s on replica %d failed: %s", a.type.name, a.replica, e)
+            blamed = e.rank // self.tp if isinstance(e, RankFailure) else a.replica
+            log.error("RPC for %s on replica %d failed (replica %d is taken as lost): %s", a.type.name, a.replica, blamed, e)
             if a.op_id:
-                self.ctl.on_failure(a.op_id, self.now())
+                self.ctl.on_failure(a.op_id, self.now(), blamed)
         self.wake.set()
 
     # ------------------------------------------------------------------ handlers
@@ -224,7 +260,7 @@ class RouterRuntime:
                 pp.tfm_layer = a.num_layer
             case = encode_prefill_case(pb.PREFILL_CASE_NAIVE_PP, pb.PREFILL_CASE_IMMIGRATE)
             calls = [self.stubs[r].prefill_v2(batch, case, pp, a.dst_ranks) for r in ranks]
-        res = (await asyncio.gather(*calls))[0]
+        res = (await self._all(ranks, calls))[0]
         if a.type == A.ZagPrefill and not res.generations and res.HasField("pp_info"):
             # taken over by a relay: the relay completion reports the hand-over to the core
             which = res.pp_info.WhichOneof("start_layer")
@@ -249,7 +285,7 @@ class RouterRuntime:
                 t.ids.extend(ft.get(rid, 0) for rid in cb.request_ids)
             lasts.append(t)
         ranks = self._ranks(a.replica)
-        res = (await asyncio.gather(*[self.stubs[r].decode_v2(batches, lasts) for r in ranks]))[0]
+        res = (await self._all(ranks, [self.stubs[r].decode_v2(batches, lasts) for r in ranks]))[0]
         for bid in a.batch_ids:
             self.cached.pop((a.replica, bid), None)
         if res.HasField("batch"):
@@ -262,14 +298,14 @@ class RouterRuntime:
         src, dst = list(a.src_ranks), list(a.dst_ranks)
         calls = [self.stubs[r].migrate(batch, src, dst, partial, a.num_layer) for r in src] + \
                 [self.stubs[r].immigrate(batch, src, dst, partial, a.num_layer) for r in dst]
-        res = await asyncio.gather(*calls)
+        res = await self._all(src + dst, calls)
         self.cached.pop((a.replica, a.batch_id), None)
         self.cached[(a.peer, a.batch_id)] = res[-1].batch
         self.ctl.on_migrate_done(a.op_id, self.now())
 
     async def _do_relay(self, a) -> None:
         new_ranks = self._ranks(a.replica)
-        res = (await asyncio.gather(*[self.stubs[r].relay(a.src_ranks[0], a.final) for r in new_ranks]))[0]
+        res = (await self._all(new_ranks, [self.stubs[r].relay(a.src_ranks[0], a.final) for r in new_ranks]))[0]
         has = res.HasField("batch_id")
         next_layer = 0
         if has:
@@ -284,15 +320,15 @@ class RouterRuntime:
     async def _do_params(self, a) -> None:
         if a.mock:
             await asyncio.sleep(self.cfg.mock_load_ms * 1e-3)
-            await asyncio.gather(*[self.stubs[r].set_status_ready() for r in a.dst_ranks])
+            await self._all(list(a.dst_ranks), [self.stubs[r].set_status_ready() for r in a.dst_ranks])
         elif a.type == A.LoadParams:
-            await asyncio.gather(*[self.stubs[r].load_params(a.load_case, self.cfg.model_name, self.model_path)
-                                   for r in a.dst_ranks])
+            await self._all(list(a.dst_ranks), [self.stubs[r].load_params(a.load_case, self.cfg.model_name, self.model_path)
+                                                for r in a.dst_ranks])
         else:
             kind = {A.NvlBroadcast: "nvl", A.TanzBroadcast: "tanz", A.RdmaBroadcast: "rdma"}[a.type]
             # every participant receives the same request and derives its role (src/service/service.cc:1341-1347)
             ranks = list(a.src_ranks) + list(a.dst_ranks)
-            await asyncio.gather(*[self.stubs[r].broadcast(kind, a.src_ranks, a.dst_ranks) for r in ranks])
+            await self._all(ranks, [self.stubs[r].broadcast(kind, a.src_ranks, a.dst_ranks) for r in ranks])
         self.ctl.on_params_done(a.op_id, self.now())
 
     async def _do_simple(self, a) -> None:

@@ -366,6 +366,8 @@ def main(argv=None) -> None:
     ap.add_argument("--log-level", default="INFO")
     ap.add_argument("--health-interval-ms", type=float, default=0.0, help="ping every active replica this often (0 = off)")
     ap.add_argument("--health-misses", type=int, default=2, help="consecutive missed pings that declare a replica lost")
+    ap.add_argument("--quarantine-ms", type=float, default=5000.0,
+                    help="a replica declared lost is not chosen for scale-up again before this much time has passed")
     ap.add_argument("--statistic-csv", default="", help="write prefill/decode token deltas every 500 ms to this file")
     a = ap.parse_args(argv)
     logging.basicConfig(level=a.log_level, format="%(asctime)s %(name)s %(message)s")
@@ -382,6 +384,7 @@ def main(argv=None) -> None:
         decode_upper=a.decode_upper_bound, migration_lower=a.migration_lower_bound,
         migration_upper=a.migration_upper_bound, min_prefill=a.min_prefill_num, max_prefill=a.max_prefill_num,
         min_decode=a.min_decode_num, max_decode=a.max_decode_num, scale_down_threshold_ms=a.scale_down_threshold_millis)
+    cfg.quarantine_ms = a.quarantine_ms
     layers = get_config(a.model_name).layers
     try:
         from ..runtime import core as _core

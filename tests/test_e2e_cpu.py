@@ -305,3 +305,46 @@ def test_heartbeat_failure_detector_marks_idle_replica_lost():
             s.set()
         await asyncio.wait(tasks, timeout=5)
     asyncio.run(go())
+
+
+def test_migration_to_dead_decode_replica_blames_the_destination():
+    """The only decode worker's server is shut down (host-side failure).  The next request's KV migration fails on
+    the destination's RPC: that replica is declared lost, the prefill replica stays in service, takes over both
+    phases, and later requests complete."""
+    async def go():
+        ports = _free_ports(2)
+        stops, tasks = [], []
+        states = ["Prefill", "Decode"]
+        backends = [StubBackend(r, 2, ready=True) for r in range(2)]
+        for r, b in enumerate(backends):
+            ready, stop = asyncio.Event(), asyncio.Event()
+            tasks.append(asyncio.create_task(serve(b, "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            await ready.wait()
+            stops.append(stop)
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * 2}, 1, "impl_blitz,impl_nvl",
+                                             max_blocks_per_replica=4000)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2)
+        lt = asyncio.create_task(rt.run())
+
+        async def run_one(n_new):
+            lr = rt.submit(list(range(40)), n_new)
+            evs = []
+            while True:
+                ev = await asyncio.wait_for(lr.queue.get(), timeout=20)
+                evs.append(ev)
+                if ev[0] == "error" or ev[2]:
+                    return evs
+        assert len(await run_one(4)) == 4                       # healthy pair: prefill on 0, decode on 1
+        stops[1].set()
+        await asyncio.wait([tasks[1]], timeout=5)
+        evs = await run_one(4)                                  # prefill answers, then the migration finds nobody
+        assert evs[0][0] == "token" and evs[-1][0] == "error"
+        assert rt.ctl.state_name(1) == "Inactive" and rt.ctl.state_name(0) == "Prefill"
+        evs = await run_one(5)                                  # the survivor now serves both phases
+        assert [e[0] for e in evs] == ["token"] * 5 and evs[-1][2]
+        assert rt.ctl.total_used_blocks() == 0
+        await rt.stop()
+        lt.cancel()
+        stops[0].set()
+        await asyncio.wait(tasks, timeout=5)
+    asyncio.run(go())

@@ -377,6 +377,93 @@ def test_simultaneous_scale_ups_share_one_multicast():
     assert ctl.state_name(2) == "NewPrefill" and ctl.state_name(3) == "NewPrefill" and ctl.state_name(0) == "OldPrefill"
 
 
+def _prefill_one(ctl, rid, t=0.0, new_tokens=8):
+    """Submit one request and carry it through prefill on whichever replica takes it; returns that replica."""
+    ctl.submit(E(rid, 100, new_tokens, t))
+    pf = [a for a in ctl.step(t) if a.type == core.ActionType.Prefill]
+    assert len(pf) == 1
+    ctl.on_prefill_done(pf[0].op_id, [core.TokenOut(rid, 7, False)], t + 0.01)
+    return pf[0].replica
+
+
+def test_lost_migration_destination_is_blamed_not_the_source():
+    """A migration spans two replicas: when its destination dies the batch fails, the source gets its pages back and
+    stays in service, and the late answer of the cancelled operation is ignored."""
+    cfg = _cfg(["Prefill", "Decode", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+    ctl = core.Controller(cfg)
+    src = _prefill_one(ctl, 1)
+    mig = [a for a in ctl.step(0.02) if a.type == core.ActionType.Migrate]
+    assert len(mig) == 1 and mig[0].replica == src
+    dst = mig[0].peer
+    assert ctl.metric(src).used_blocks > 0 and ctl.metric(dst).used_blocks > 0
+    ctl.on_failure(mig[0].op_id, 0.03, dst)                   # the destination's RPC was the one that failed
+    assert ctl.state_name(dst) == "Inactive" and ctl.state_name(src) == "Prefill"
+    acts = ctl.step(0.03)
+    assert [a.request_id for a in acts if a.type == core.ActionType.Fail] == [1]
+    assert any(a.type == core.ActionType.ClearCache and a.replica == src for a in acts)
+    assert ctl.total_used_blocks() == 0 and ctl.inflight_ops() == 0
+    ctl.on_migrate_done(mig[0].op_id, 0.05)                   # the source's RPC still answers: ignored, cache cleared again
+    assert any(a.type == core.ActionType.ClearCache and a.replica == src for a in ctl.step(0.05))
+    assert ctl.idle()
+    # the survivors keep serving: the next request migrates to the other decode replica
+    src = _prefill_one(ctl, 2, 0.1)
+    mig = [a for a in ctl.step(0.12) if a.type == core.ActionType.Migrate]
+    assert len(mig) == 1 and mig[0].peer not in (dst, src)
+    # the failure detector's verdict while a migration is in flight settles it the same way
+    ctl.on_replica_unhealthy(mig[0].peer, 0.13)
+    assert [a.request_id for a in ctl.step(0.13) if a.type == core.ActionType.Fail] == [2]
+    assert ctl.total_used_blocks() == 0 and ctl.inflight_ops() == 0
+
+
+def test_lost_role_is_restored_and_lost_replica_is_quarantined():
+    # the only decode replica dies: the spare becomes the decode side and the queued migration goes there
+    cfg = _cfg(["Prefill", "Decode", "Inactive"], "impl_blitz,impl_nvl", quarantine_ms=1000.0)
+    ctl = core.Controller(cfg)
+    assert _prefill_one(ctl, 1) == 0
+    ctl.on_replica_unhealthy(1, 0.02)
+    acts = ctl.step(0.05)
+    loads = [a for a in acts if a.type in (core.ActionType.NvlBroadcast, core.ActionType.RdmaBroadcast)]
+    assert len(loads) == 1 and loads[0].dst_ranks == [2] and loads[0].src_ranks == [0]   # never the lost replica
+    assert ctl.state_name(2) == "LoadingDecode" and ctl.state_name(1) == "Inactive"
+    ctl.on_params_done(loads[0].op_id, 0.1)
+    assert ctl.state_name(2) == "Decode"
+    mig = [a for a in ctl.step(0.11) if a.type == core.ActionType.Migrate]
+    assert len(mig) == 1 and (mig[0].replica, mig[0].peer) == (0, 2)    # request 1 waited for the new decode side
+    # with no spare at all the surviving replica serves both phases instead of waiting for ever
+    cfg = _cfg(["Prefill", "Decode"], "impl_blitz,impl_nvl", quarantine_ms=1000.0)
+    ctl = core.Controller(cfg)
+    ctl.on_replica_unhealthy(0, 0.0)
+    ctl.submit(E(5, 64, 3, 0.0))
+    acts = ctl.step(0.02)
+    assert ctl.state_name(1) == "Prefill" and ctl.state_name(0) == "Inactive"
+    pf = [a for a in acts + ctl.step(0.03) if a.type == core.ActionType.Prefill]
+    assert len(pf) == 1 and pf[0].replica == 1
+    ctl.on_prefill_done(pf[0].op_id, [core.TokenOut(5, 1, False)], 0.05)
+    dec = [a for a in ctl.step(0.06) if a.type == core.ActionType.Decode]
+    assert len(dec) == 1 and dec[0].replica == 1
+    # after the quarantine the lost replica may be tried again
+    assert not [a for a in ctl.step(0.5) if a.type == core.ActionType.NvlBroadcast]
+    again = [a for a in ctl.step(1.2) if a.type in (core.ActionType.NvlBroadcast, core.ActionType.RdmaBroadcast)]
+    assert len(again) == 1 and again[0].dst_ranks == [0]
+
+
+def test_lost_participant_aborts_a_shared_parameter_transfer():
+    cfg = _cfg(["Prefill", "Decode"] + ["Inactive"] * 2, "impl_blitz,impl_nvl,manually_scale")
+    ctl = core.Controller(cfg)
+    assert ctl.manual_scale(2, "Prefill", 0.0) and ctl.manual_scale(3, "Prefill", 0.0)
+    bc = [a for a in ctl.step(0.0) if a.type == core.ActionType.TanzBroadcast]
+    assert len(bc) == 1 and bc[0].dst_ranks == [2, 3]
+    ctl.on_failure(bc[0].op_id, 0.01, 3)
+    acts = ctl.step(0.01)
+    assert ctl.state_name(2) == "Inactive" and ctl.state_name(3) == "Inactive"
+    assert [a.dst_ranks for a in acts if a.type == core.ActionType.ResetStatus] == [[2]]   # the healthy one starts over
+    assert ctl.metric(0).marker == "" and ctl.metric(1).marker == "" and ctl.inflight_ops() == 0
+    ctl.on_params_done(bc[0].op_id, 0.02)                     # late answer of the aborted transfer
+    assert ctl.state_name(2) == "Inactive"
+    assert ctl.manual_scale(2, "Prefill", 0.03)               # the healthy replica can be scaled again at once
+    assert [a.dst_ranks for a in ctl.step(0.03) if a.type == core.ActionType.NvlBroadcast] == [[2]]
+
+
 def test_calibrated_autoscaling_study_orders_the_policies():
     """Virtual-time replay with the measured B200 cost model: faster parameter delivery -> lower p99 TTFT."""
     import os
