@@ -5,7 +5,7 @@ step times are plugged in.
 
     python bench/sim_study.py [--model llama3_8b|mistral_24b] [--horizon-ms 100] [--json out.json]
 
-Calibration (B200, bf16; see BASELINE.md section 3 and profiles/):
+Calibration (B200, bf16; numbers measured with bench.py, bench/comm_bench.py and bench/cluster_bench.py):
   llama3_8b    prefill 1024 tokens in ~17 ms; decode step 4.2 / 5.1 / 6.3 / 9.5 ms at batch 16 / 64 / 128 / 256;
                16.06 GB per replica; striped multicast 630 GB/s into every destination; pinned host 55 GB/s;
                KV push 690 GB/s = 5.3 M tokens/s.

@@ -9,6 +9,8 @@
 //           bounded spin, read the unit, and the single consumer that owns the flag resets it;
 //        b. split-K tickets: every contributor stores its partial, takes a ticket (acq_rel); the last one sums the
 //           partials in index order and resets the ticket.
+//        c. one-kernel all-reduce: blocks of the same index on all ranks rendezvous through per-block counters in two
+//           alternating parities; slots are reused every second call without any other synchronisation.
 //      ThreadSanitizer checks that the data accesses are ordered by those atomics.
 #include <atomic>
 #include <chrono>
@@ -131,7 +133,7 @@ static void flag_protocol() {
           for (int w = k; w < kWords; w += 97)
             if (buf[static_cast<size_t>(u) * kWords + w] != static_cast<uint32_t>(r * 1000003 + u * 131 + w)) failed = true;
         }
-        // readers meet; reader 0 owns the flags: it re-arms them, then releases the producer into the next round
+        // readers meet; reader 0 owns the flags: it re-arms them, then releases the producer into the next pass
         readers_done.fetch_add(1, std::memory_order_acq_rel);
         while (readers_done.load(std::memory_order_acquire) < kReaders * r) std::this_thread::yield();
         if (k == 0) {
@@ -185,12 +187,74 @@ static void ticket_protocol() {
   }
 }
 
+// ---- 3c: one-kernel all-reduce over peer memory, two parities -----------------------------------------------
+// Rank r, block b (one thread each here) of call c: store its chunk of the local vector into slot [parity][r] of
+// every rank, release-add 1 to counter [parity][r][b] on every rank, acquire-wait for counters [parity][s][b] of all
+// sources on its own rank, sum the slots in rank order, re-arm the counters it consumed.  Calls alternate between
+// two parities; a rank starts call c + 1 only when all its blocks have finished call c (stream order).  The claim
+// under test: that alone orders a peer's next write into a slot after this rank's last read of it.
+static void allreduce_protocol() {
+  constexpr int kTp = 4, kBlocks = 4, kChunk = 64, kCalls = 200;
+  constexpr int kN = kBlocks * kChunk;
+  struct Rank {
+    std::vector<float> slots;                       // [parity][src][n]
+    std::vector<std::atomic<uint32_t>> flags;       // [parity][src][block]
+    std::vector<float> out;
+    std::atomic<int> blocks_done{0};
+    Rank() : slots(2 * kTp * kN), flags(2 * kTp * kBlocks), out(kN) { for (auto& f : flags) f.store(0); }
+  };
+  std::vector<Rank> ranks(kTp);
+  std::atomic<bool> failed{false};
+  auto contribution = [](int call, int rank, int i) { return static_cast<float>((call % 17) * 64 + rank * 8 + (i % 5)); };
+  std::vector<std::thread> threads;
+  for (int r = 0; r < kTp; ++r)
+    for (int b = 0; b < kBlocks; ++b)
+      threads.emplace_back([&, r, b] {
+        Rank& me = ranks[r];
+        for (int c = 0; c < kCalls; ++c) {
+          const int par = c & 1;
+          for (int d = 0; d < kTp; ++d)
+            for (int i = b * kChunk; i < (b + 1) * kChunk; ++i)
+              ranks[d].slots[(static_cast<size_t>(par) * kTp + r) * kN + i] = contribution(c, r, i);
+          for (int d = 0; d < kTp; ++d)
+            ranks[d].flags[(static_cast<size_t>(par) * kTp + r) * kBlocks + b].fetch_add(1, std::memory_order_release);
+          for (int s = 0; s < kTp; ++s) {
+            auto& f = me.flags[(static_cast<size_t>(par) * kTp + s) * kBlocks + b];
+            const auto t0 = std::chrono::steady_clock::now();
+            while (f.load(std::memory_order_acquire) < 1) {
+              if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(30)) { failed = true; return; }
+              std::this_thread::yield();
+            }
+          }
+          for (int i = b * kChunk; i < (b + 1) * kChunk; ++i) {
+            float acc = 0.f, want = 0.f;
+            for (int s = 0; s < kTp; ++s) {
+              acc += me.slots[(static_cast<size_t>(par) * kTp + s) * kN + i];
+              want += contribution(c, s, i);
+            }
+            me.out[i] = acc;
+            if (acc != want) failed = true;
+          }
+          for (int s = 0; s < kTp; ++s)
+            me.flags[(static_cast<size_t>(par) * kTp + s) * kBlocks + b].store(0, std::memory_order_relaxed);
+          // end of the kernel on this rank: the next call starts when every block of this one has finished
+          me.blocks_done.fetch_add(1, std::memory_order_acq_rel);
+          while (me.blocks_done.load(std::memory_order_acquire) < kBlocks * (c + 1)) std::this_thread::yield();
+        }
+      });
+  for (auto& t : threads) t.join();
+  CHECK(!failed.load());
+  for (auto& rk : ranks)
+    for (auto& f : rk.flags) CHECK(f.load() == 0);
+}
+
 int main(int argc, char** argv) {
   const std::string what = argc > 1 ? argv[1] : "all";
   if (what == "all" || what == "pool") pool_fuzz();
   if (what == "all" || what == "sim") controller_sim();
   if (what == "all" || what == "flags") flag_protocol();
   if (what == "all" || what == "tickets") ticket_protocol();
+  if (what == "all" || what == "allreduce") allreduce_protocol();
   std::printf("core_stress %s: OK\n", what.c_str());
   return 0;
 }
