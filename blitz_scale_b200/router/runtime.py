@@ -56,7 +56,8 @@ class LiveRequest:
 
 class RouterRuntime:
     def __init__(self, cfg: "core.ControllerConfig", worker_urls: List[str], model_layers: int = 32,
-                 model_path: str = "", stat_csv: str = "", health_interval_s: float = 0.0, health_misses: int = 2):
+                 model_path: str = "", stat_csv: str = "", health_interval_s: float = 0.0, health_misses: int = 2,
+                 rpc_timeout_s: float = 300.0):
         self.cfg = cfg
         # failure detector: every `health_interval_s` each active replica's ranks are pinged with the Health RPC;
         # `health_misses` consecutive misses (error or no answer within the interval) declare the replica lost.
@@ -69,7 +70,9 @@ class RouterRuntime:
             self.stat_csv.write("time_s,prefill_tokens,decode_tokens\n")
         self._stat_last = (0.0, 0, 0)
         self.ctl = core.Controller(cfg)
-        self.stubs = [WorkerStub(u) for u in worker_urls]
+        # deadline of every worker RPC: a reply that never comes fails the operation (and the replica that owed it)
+        # instead of leaving it in flight for ever; generous, a cold load of a large model from disk must fit
+        self.stubs = [WorkerStub(u, rpc_timeout_s) for u in worker_urls]
         self.tp = cfg.tp
         self.layers = model_layers
         self.model_path = model_path

@@ -366,6 +366,8 @@ def main(argv=None) -> None:
     ap.add_argument("--log-level", default="INFO")
     ap.add_argument("--health-interval-ms", type=float, default=0.0, help="ping every active replica this often (0 = off)")
     ap.add_argument("--health-misses", type=int, default=2, help="consecutive missed pings that declare a replica lost")
+    ap.add_argument("--rpc-timeout-ms", type=float, default=300000.0,
+                    help="deadline of every worker RPC; a reply that never comes then counts as a failed replica (0 = none)")
     ap.add_argument("--quarantine-ms", type=float, default=5000.0,
                     help="a replica declared lost is not chosen for scale-up again before this much time has passed")
     ap.add_argument("--statistic-csv", default="", help="write prefill/decode token deltas every 500 ms to this file")
@@ -394,7 +396,8 @@ def main(argv=None) -> None:
     async def amain():
         # the gRPC channels of the runtime belong to the event loop that creates them: build it inside the loop
         rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv,
-                           health_interval_s=a.health_interval_ms * 1e-3, health_misses=a.health_misses)
+                           health_interval_s=a.health_interval_ms * 1e-3, health_misses=a.health_misses,
+                           rpc_timeout_s=a.rpc_timeout_ms * 1e-3)
         await serve_router(rt, a.hostname, a.port, model_name=a.model_name, max_input_length=a.max_input_length,
                            max_total_tokens=a.max_total_tokens, tokenizer_path=a.tokenizer_path,
                            tokenizer_workers=a.validation_workers)

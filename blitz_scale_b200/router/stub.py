@@ -23,8 +23,11 @@ def encode_prefill_case(*cases: int) -> int:
 
 
 class WorkerStub:
-    def __init__(self, url: str):
+    def __init__(self, url: str, default_timeout: Optional[float] = None):
+        """`default_timeout` (seconds) is the deadline of every call that does not pass its own: a worker that never
+        answers then surfaces as DEADLINE_EXCEEDED instead of an operation that stays in flight for ever."""
         self.url = url
+        self.default_timeout = default_timeout if default_timeout and default_timeout > 0 else None
         self.channel = grpc.aio.insecure_channel(url, options=[("grpc.max_receive_message_length", 256 << 20),
                                                                ("grpc.max_send_message_length", 256 << 20)])
         self._m = {}
@@ -37,7 +40,8 @@ class WorkerStub:
         if metadata is None:
             # trace context of the operation this call belongs to (set by the router runtime per dispatched op)
             metadata = grpc_metadata(CURRENT_TRACE.get())
-        return await self._m[rpc](request, timeout=timeout, metadata=metadata)
+        return await self._m[rpc](request, timeout=timeout if timeout is not None else self.default_timeout,
+                                  metadata=metadata)
 
     async def close(self):
         await self.channel.close()

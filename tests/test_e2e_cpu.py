@@ -348,3 +348,50 @@ def test_migration_to_dead_decode_replica_blames_the_destination():
         stops[0].set()
         await asyncio.wait(tasks, timeout=5)
     asyncio.run(go())
+
+
+def test_dropped_immigrate_reply_fails_the_operation_not_the_router():
+    """A decode worker accepts the Immigrate call and never answers (host-side fault: its handler blocks).  The RPC
+    deadline turns that into a failed operation: the silent replica is declared lost, its batch fails, and the next
+    request migrates to the other decode replica."""
+    import threading
+    release = threading.Event()
+
+    async def go():
+        ports = _free_ports(3)
+        stop, tasks = asyncio.Event(), []
+        states = ["Prefill", "Decode", "Decode"]
+        backends = [StubBackend(r, 3, ready=True) for r in range(3)]
+        backends[1].immigrate = lambda *a, **k: release.wait(30)          # reply withheld
+        for r, b in enumerate(backends):
+            ready = asyncio.Event()
+            tasks.append(asyncio.create_task(serve(b, "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            await ready.wait()
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * 3}, 1, "impl_blitz,impl_nvl",
+                                             max_blocks_per_replica=4000, autoscale=False)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, rpc_timeout_s=0.5)
+        lt = asyncio.create_task(rt.run())
+
+        async def run_one(n_new):
+            lr = rt.submit(list(range(40)), n_new)
+            evs = []
+            while True:
+                ev = await asyncio.wait_for(lr.queue.get(), timeout=20)
+                evs.append(ev)
+                if ev[0] == "error" or ev[2]:
+                    return evs
+        evs = await run_one(4)
+        assert evs[0][0] == "token" and evs[-1][0] == "error"
+        assert rt.ctl.state_name(1) == "Inactive" and rt.ctl.state_name(0) == "Prefill"
+        evs = await run_one(4)
+        assert [e[0] for e in evs] == ["token"] * 4 and rt.ctl.state_name(2) == "Decode"
+        assert rt.ctl.total_used_blocks() == 0 and rt.ctl.inflight_ops() == 0
+        release.set()
+        await rt.stop()
+        lt.cancel()
+        stop.set()
+        await asyncio.wait(tasks, timeout=5)
+    try:
+        asyncio.run(go())
+    finally:
+        release.set()
