@@ -157,16 +157,12 @@ def run_router(a, world, states, cfg_model, backend):
         async def one(i, t_arr):
             await asyncio.sleep(max(0.0, t_arr - (rt.now() - t_start)))
             t0 = rt.now()
-            lr = rt.submit(prompts[i], a.new_tokens)
-            times = []
-            while True:
-                ev = await asyncio.wait_for(lr.queue.get(), timeout=300)
-                if ev[0] == "error":
-                    records.append({"i": i, "ok": False})
-                    return
-                times.append(rt.now())
-                if ev[2]:
-                    break
+            # whole response at once (what POST /generate does): the token times are the router's delivery times
+            lr = rt.submit(prompts[i], a.new_tokens, stream=False)
+            if await asyncio.wait_for(lr.done, timeout=300):
+                records.append({"i": i, "ok": False})
+                return
+            times = list(lr.times)
             tbt = [b - c for b, c in zip(times[1:], times[:-1])]
             records.append({"i": i, "ok": True, "burst": t_arr >= a.base_s, "ttft": times[0] - t0, "tbt": tbt,
                             "tokens": len(times), "done": times[-1]})

@@ -138,6 +138,27 @@ void bind_router(py::module_& m) {
       .def("on_migrate_done", &Controller::on_migrate_done).def("on_params_done", &Controller::on_params_done)
       .def("on_relay_done", &Controller::on_relay_done).def("on_failure", &Controller::on_failure, py::arg("op_id"), py::arg("now"), py::arg("failed_replica") = -1)
       .def("step", &Controller::step).def("manual_scale", &Controller::manual_scale)
+      .def("set_compact_deliveries", &Controller::set_compact_deliveries)
+      .def("take_deliveries", [](Controller& c) {
+        std::vector<std::tuple<uint64_t, int32_t, bool>> out;
+        for (auto& d : c.take_deliveries()) out.emplace_back(d.request_id, d.token, d.final);
+        return out; })
+      // completions given as three parallel lists (request ids, tokens, finished flags): cheaper to build than one
+      // TokenOut object per token
+      .def("on_prefill_done_lists", [](Controller& c, uint64_t op, const std::vector<uint64_t>& ids, const std::vector<int32_t>& toks,
+                                       const std::vector<bool>& fins, double now) {
+        if (ids.size() != toks.size() || ids.size() != fins.size()) throw std::invalid_argument("lists differ in length");
+        std::vector<Controller::TokenOut> t;
+        t.reserve(ids.size());
+        for (size_t i = 0; i < ids.size(); ++i) t.push_back({ids[i], toks[i], fins[i]});
+        c.on_prefill_done(op, t, now); })
+      .def("on_decode_done_lists", [](Controller& c, uint64_t op, const std::vector<uint64_t>& ids, const std::vector<int32_t>& toks,
+                                      const std::vector<bool>& fins, double now) {
+        if (ids.size() != toks.size() || ids.size() != fins.size()) throw std::invalid_argument("lists differ in length");
+        std::vector<Controller::TokenOut> t;
+        t.reserve(ids.size());
+        for (size_t i = 0; i < ids.size(); ++i) t.push_back({ids[i], toks[i], fins[i]});
+        c.on_decode_done(op, t, now); })
       .def_property_readonly("num_replicas", &Controller::num_replicas).def("metric", &Controller::metric)
       .def("state_name", &Controller::state_name).def_property_readonly("queue_size", &Controller::queue_size)
       .def_property_readonly("waiting_prefill_tokens", &Controller::waiting_prefill_tokens)

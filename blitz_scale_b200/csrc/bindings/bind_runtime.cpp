@@ -71,6 +71,9 @@ void bind_runtime(py::module_& m) {
       .def("append_tokens", &Batch::append_tokens, py::arg("tokens"), py::arg("count_cached") = true)
       .def("filter", &Batch::filter).def("unfinished_ids", &Batch::unfinished_ids)
       .def("extend", &Batch::extend).def("clear", &Batch::clear)
+      .def("request_ids", &Batch::request_ids).def("prompt_lens", &Batch::prompt_lens).def("emit_info", &Batch::emit_info)
+      .def("encode_generations", [](const Batch& b, const std::vector<int32_t>& toks) { return py::bytes(b.encode_generations(toks)); })
+      .def("none_generated", &Batch::none_generated).def("prompt_page_ids", &Batch::prompt_page_ids)
       .def("fill_prefill", [](const Batch& b, py::array_t<int32_t, py::array::c_style> h, const MetaLayout& L) {
         if (h.size() < L.total) throw std::invalid_argument("staging array too small");
         return b.fill_prefill(h.mutable_data(), L); })

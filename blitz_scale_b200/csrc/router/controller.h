@@ -344,6 +344,11 @@ class Controller {
     return it == requests_.end() ? nullptr : &it->second;
   }
   std::vector<std::string> drain_log() { std::vector<std::string> l; l.swap(log_); return l; }
+  // Token deliveries are by far the most frequent output.  A shell that serves many tokens per second switches them
+  // from one `Action` each to a compact list that it drains after every completion it reports.
+  struct Delivery { uint64_t request_id; int32_t token; bool final; };
+  void set_compact_deliveries(bool on) { compact_deliveries_ = on; }
+  std::vector<Delivery> take_deliveries() { std::vector<Delivery> d; d.swap(deliveries_); return d; }
   std::string system_metrics_line() const {
     std::ostringstream s;
     s << "System Metrics: prefill_tokens: " << stats_prefill_tokens_ << ", decode_tokens: " << stats_decode_tokens_;
@@ -482,9 +487,13 @@ class Controller {
       e.generated += 1;
       e.t_last_token = now;
       const bool fin = t.finished || e.generated >= e.max_new_tokens || !e.client_alive;
-      Action a;
-      a.type = ActionType::Deliver; a.request_id = t.request_id; a.token = t.token; a.final = fin;
-      out_.push_back(a);
+      if (compact_deliveries_) {
+        deliveries_.push_back({t.request_id, t.token, fin});
+      } else {
+        Action a;
+        a.type = ActionType::Deliver; a.request_id = t.request_id; a.token = t.token; a.final = fin;
+        out_.push_back(a);
+      }
       if (fin) {
         b.request_ids.erase(std::remove(b.request_ids.begin(), b.request_ids.end(), t.request_id), b.request_ids.end());
         counters_["blitz_request_success"] += 1;
@@ -1215,6 +1224,8 @@ class Controller {
   std::map<uint64_t, Relayed> relayed_;
   std::map<uint64_t, Cancelled> cancelled_;
   std::vector<Action> out_;
+  std::vector<Delivery> deliveries_;
+  bool compact_deliveries_ = false;
   std::vector<std::string> log_;
   std::map<std::string, double> counters_, gauges_;
   uint64_t next_op_ = 0;

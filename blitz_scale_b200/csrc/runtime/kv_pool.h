@@ -16,6 +16,7 @@
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
+#include <tuple>
 #include <vector>
 
 namespace blitz {
@@ -199,6 +200,76 @@ class Batch {
     for (auto& s : seqs_)
       if (s.finish == kFinishNone) ids.push_back(s.spec.id);
     return ids;
+  }
+  // Compact per-request views for the serving loop (the per-step paths must not copy prompts or token histories).
+  std::vector<uint64_t> request_ids() const {
+    std::vector<uint64_t> ids;
+    ids.reserve(seqs_.size());
+    for (auto& s : seqs_) ids.push_back(s.spec.id);
+    return ids;
+  }
+  std::vector<int> prompt_lens() const {
+    std::vector<int> n;
+    n.reserve(seqs_.size());
+    for (auto& s : seqs_) n.push_back(static_cast<int>(s.spec.prompt.size()));
+    return n;
+  }
+  // (request id, finish code or -1, tokens generated so far) of every request, in batch order.
+  std::vector<std::tuple<uint64_t, int, int>> emit_info() const {
+    std::vector<std::tuple<uint64_t, int, int>> out;
+    out.reserve(seqs_.size());
+    for (auto& s : seqs_) out.emplace_back(s.spec.id, static_cast<int>(s.finish), static_cast<int>(s.generated.size()));
+    return out;
+  }
+  // Wire bytes of one `Generation` message per request (field 1 of the prefill / decode responses of the
+  // generate.v2 contract), carrying this step's token: request_id, tokens{ids, logprobs = 0, texts = "<id>",
+  // is_special = false} and, for requests that finished with this token, generated_text{text, generated_tokens,
+  // finish_reason}.  Building these messages one by one in the scripting layer costs more than the decode step's
+  // launch overhead at large batch; the service parses the bytes back in one call.
+  std::string encode_generations(const std::vector<int32_t>& tokens) const {
+    if (tokens.size() != seqs_.size()) throw std::invalid_argument("encode_generations: one token per request");
+    auto put_varint = [](std::string& o, uint64_t v) {
+      while (v >= 0x80) { o.push_back(static_cast<char>((v & 0x7f) | 0x80)); v >>= 7; }
+      o.push_back(static_cast<char>(v));
+    };
+    std::string out, gen, sub;
+    out.reserve(seqs_.size() * 32);
+    for (size_t i = 0; i < seqs_.size(); ++i) {
+      const SeqState& s = seqs_[i];
+      const std::string text = "<" + std::to_string(tokens[i]) + ">";
+      gen.clear();
+      gen.push_back(0x08); put_varint(gen, s.spec.id);
+      sub.clear();
+      sub.push_back(0x08); put_varint(sub, static_cast<uint32_t>(tokens[i]));
+      sub.push_back(0x15); sub.append(4, '\0');
+      sub.push_back(0x1a); put_varint(sub, text.size()); sub += text;
+      sub.push_back(0x20); sub.push_back(0);
+      gen.push_back(0x1a); put_varint(gen, sub.size()); gen += sub;
+      if (s.finish != kFinishNone) {
+        sub.clear();
+        sub.push_back(0x0a); put_varint(sub, text.size()); sub += text;
+        sub.push_back(0x10); put_varint(sub, s.generated.size());
+        sub.push_back(0x18); put_varint(sub, static_cast<uint64_t>(s.finish));
+        gen.push_back(0x22); put_varint(gen, sub.size()); gen += sub;
+      }
+      out.push_back(0x0a); put_varint(out, gen.size()); out += gen;
+    }
+    return out;
+  }
+  bool none_generated() const {
+    for (auto& s : seqs_)
+      if (!s.generated.empty()) return false;
+    return true;
+  }
+  // Pages that hold the prompts' KV, request after request (what a migration ships).
+  std::vector<int32_t> prompt_page_ids() const {
+    const int ps = pool_->page_size();
+    std::vector<int32_t> out;
+    for (auto& s : seqs_) {
+      const size_t used = (s.spec.prompt.size() + ps - 1) / ps;
+      out.insert(out.end(), s.pages.begin(), s.pages.begin() + static_cast<long>(std::min(used, s.pages.size())));
+    }
+    return out;
   }
   // Move the requests of `other` to the end of this batch (page ownership moves too).
   void extend(Batch& other) {

@@ -52,6 +52,12 @@ class LiveRequest:
     t_submit: float = 0.0
     tokens: List[int] = field(default_factory=list)
     texts: List[str] = field(default_factory=list)
+    times: List[float] = field(default_factory=list)   # router clock at the delivery of each token
+    # stream = True: every token is also put on `queue` as ("token", id, final) / ("error", text), waking the consumer
+    # once per token.  stream = False: tokens only accumulate in `tokens` / `times` and `done` resolves at the end
+    # (None, or the error text): one wake-up per request instead of one per token.
+    stream: bool = True
+    done: Optional[asyncio.Future] = None
 
 
 class RouterRuntime:
@@ -70,6 +76,7 @@ class RouterRuntime:
             self.stat_csv.write("time_s,prefill_tokens,decode_tokens\n")
         self._stat_last = (0.0, 0, 0)
         self.ctl = core.Controller(cfg)
+        self.ctl.set_compact_deliveries(True)       # tokens come back as (request, token, final) tuples, not Actions
         # deadline of every worker RPC: a reply that never comes fails the operation (and the replica that owed it)
         # instead of leaving it in flight for ever; generous, a cold load of a large model from disk must fit
         self.stubs = [WorkerStub(u, rpc_timeout_s) for u in worker_urls]
@@ -93,7 +100,7 @@ class RouterRuntime:
         return time.monotonic() - self.t0
 
     def submit(self, input_tokens: List[int], max_new_tokens: int, *, inputs: str = "", parameters=None,
-               ignore_eos: bool = True) -> LiveRequest:
+               ignore_eos: bool = True, stream: bool = True) -> LiveRequest:
         rid = self._next_id
         self._next_id += 1
         r = pb.Request(id=rid, inputs=inputs, prefill_logprobs=False, top_n_tokens=0)
@@ -102,7 +109,7 @@ class RouterRuntime:
         r.stopping_parameters.ignore_eos_token = ignore_eos
         if parameters is not None:
             r.parameters.CopyFrom(parameters)
-        lr = LiveRequest(rid, r, t_submit=self.now())
+        lr = LiveRequest(rid, r, t_submit=self.now(), stream=stream, done=asyncio.get_running_loop().create_future())
         self.requests[rid] = lr
         self.ctl.submit(core.RequestEntry(rid, len(input_tokens), max_new_tokens, lr.t_submit))
         self.wake.set()
@@ -144,6 +151,7 @@ class RouterRuntime:
                     self.transitions.append((now, line))
             for a in actions:
                 self._dispatch(a)
+            self._deliver(now)
             if self.stat_csv is not None and now - self._stat_last[0] >= 0.5:
                 p_tok, d_tok = self.ctl.token_counts()
                 self.stat_csv.write(f"{now:.3f},{p_tok - self._stat_last[1]},{d_tok - self._stat_last[2]}\n")
@@ -207,17 +215,16 @@ class RouterRuntime:
 
     def _dispatch(self, a) -> None:
         t = a.type
-        if t == A.Deliver or t == A.Fail:
-            lr = self.requests.get(a.request_id)
+        if t == A.Fail:
+            lr = self.requests.pop(a.request_id, None)
             if lr is not None:
-                if t == A.Fail:
+                if lr.stream:
                     lr.queue.put_nowait(("error", "replica lost"))
-                    self.requests.pop(a.request_id, None)
-                else:
-                    lr.tokens.append(a.token)
-                    lr.queue.put_nowait(("token", a.token, a.final))
-                    if a.final:
-                        self.requests.pop(a.request_id, None)
+                if not lr.done.done():
+                    lr.done.set_result("replica lost")
+            return
+        if t == A.Deliver:     # only when compact deliveries are off
+            self._deliver_one(a.request_id, a.token, a.final, self.now())
             return
         handler = {A.Prefill: self._do_prefill, A.ZagPrefill: self._do_prefill, A.PrefillPP: self._do_prefill,
                    A.Decode: self._do_decode, A.Migrate: self._do_migrate, A.MigratePartial: self._do_migrate,
@@ -225,6 +232,24 @@ class RouterRuntime:
                    A.RdmaBroadcast: self._do_params, A.LoadParams: self._do_params, A.ResetStatus: self._do_simple,
                    A.SetStatusReady: self._do_simple, A.ClearCache: self._do_simple}[t]
         self._spawn(self._guard(a, handler))
+
+    def _deliver_one(self, rid: int, token: int, final: bool, now: float) -> None:
+        lr = self.requests.get(rid)
+        if lr is None:
+            return
+        lr.tokens.append(token)
+        lr.times.append(now)
+        if lr.stream:
+            lr.queue.put_nowait(("token", token, final))
+        if final:
+            del self.requests[rid]
+            if not lr.done.done():
+                lr.done.set_result(None)
+
+    def _deliver(self, now: float) -> None:
+        """Hand the tokens the core has released since the last call to their requests."""
+        for rid, token, final in self.ctl.take_deliveries():
+            self._deliver_one(rid, token, final, now)
 
     async def _guard(self, a, handler) -> None:
         try:
@@ -241,12 +266,10 @@ class RouterRuntime:
 
     # ------------------------------------------------------------------ handlers
     @staticmethod
-    def _tokens_out(generations) -> list:
-        out = []
-        for g in generations:
-            fin = g.HasField("generated_text")
-            out.append(core.TokenOut(g.request_id, int(g.tokens.ids[0]) if g.tokens.ids else -1, fin))
-        return out
+    def _tokens_out(generations) -> tuple:
+        """(request ids, tokens, finished flags) of a response's generations, as parallel lists."""
+        return ([g.request_id for g in generations], [g.tokens.ids[0] if g.tokens.ids else -1 for g in generations],
+                [g.HasField("generated_text") for g in generations])
 
     async def _do_prefill(self, a) -> None:
         batch = self._batch_proto(a)
@@ -271,9 +294,11 @@ class RouterRuntime:
             return
         if res.HasField("batch"):
             self.cached[(a.replica, a.batch_id)] = res.batch
-        toks = self._tokens_out(res.generations)
-        self.first_tokens[a.batch_id] = {g.request_id: int(g.tokens.ids[0]) for g in res.generations if g.tokens.ids}
-        self.ctl.on_prefill_done(a.op_id, toks, self.now())
+        ids, toks, fins = self._tokens_out(res.generations)
+        self.first_tokens[a.batch_id] = {i: t for i, t in zip(ids, toks) if t >= 0}
+        now = self.now()
+        self.ctl.on_prefill_done_lists(a.op_id, ids, toks, fins, now)
+        self._deliver(now)
 
     async def _do_decode(self, a) -> None:
         batches, lasts = [], []
@@ -293,7 +318,9 @@ class RouterRuntime:
             self.cached.pop((a.replica, bid), None)
         if res.HasField("batch"):
             self.cached[(a.replica, res.batch.id)] = res.batch
-        self.ctl.on_decode_done(a.op_id, self._tokens_out(res.generations), self.now())
+        now = self.now()
+        self.ctl.on_decode_done_lists(a.op_id, *self._tokens_out(res.generations), now)
+        self._deliver(now)          # straight away: the next step of the loop may be a tick away
 
     async def _do_migrate(self, a) -> None:
         batch = self._batch_proto(a)

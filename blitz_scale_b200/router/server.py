@@ -166,37 +166,23 @@ class RouterApp:
         err = core.validate_request(g, self.limits)
         return toks, g, err
 
-    async def _run(self, toks, g):
-        t_start = time.monotonic()
-        lr = self.rt.submit(toks, g.max_new_tokens)
-        out, t_first, t_first_dec, t_prev, tbt = [], None, None, None, []
-        while True:
-            ev = await lr.queue.get()
-            now = time.monotonic()
-            if ev[0] == "error":
-                raise web.HTTPServiceUnavailable(text=json.dumps({"error": ev[1], "error_type": "generation"}),
-                                                 content_type="application/json")
-            _, tok, final = ev
-            if t_first is None:
-                t_first = now
-            else:
-                if t_first_dec is None:
-                    t_first_dec = now
-                else:
-                    tbt.append(now - t_prev)
-            t_prev = now
-            out.append(tok)
-            yield tok, final, None
-            if final:
-                break
+    def _finish(self, lr, toks, g):
+        """Timing headers and metrics of a finished request, from the router-clock time of each token delivery."""
+        times, out = lr.times, lr.tokens
+        t_start = lr.t_submit
+        total = (times[-1] if times else self.rt.now()) - t_start
+        t_first = times[0] if times else t_start
+        t_first_dec = times[1] if len(times) > 1 else t_first
+        # the interval between the prefill token and the first decode token contains the KV migration: it is reported
+        # on its own and is not a time-between-tokens sample
+        tbt = [b - a for a, b in zip(times[1:], times[2:])]
         e = self.rt.ctl.finished().get(lr.id)
         queue_s = (e.t_batched - e.t_arrival) if e is not None and e.t_batched >= 0 else 0.0
-        total = time.monotonic() - t_start
         stats = {
             "x-compute-type": "gpu+optimized", "x-total-time": int(total * 1e3), "x-validation-time": 0,
             "x-queue-time": int(queue_s * 1e3), "x-inference-time": int((total - queue_s) * 1e3),
             "x-first-token-time": int((t_first - t_start) * 1e3),
-            "x-first-decode-token-time": int(((t_first_dec or t_first) - t_start) * 1e3),
+            "x-first-decode-token-time": int((t_first_dec - t_start) * 1e3),
             "x-time-per-token": int(total * 1e3 / max(1, len(out))),
             "x-max-time-between-tokens": int(max(tbt, default=0.0) * 1e3),
             "x-avg-time-between-tokens": int((sum(tbt) / len(tbt) if tbt else 0.0) * 1e3),
@@ -212,7 +198,33 @@ class RouterApp:
         m.observe("blitz_request_generated_tokens", len(out))
         m.observe("blitz_request_input_length", len(toks))
         m.observe("blitz_request_max_new_tokens", g.max_new_tokens)
-        yield None, True, (out, stats)
+        return list(out), stats
+
+    @staticmethod
+    def _unavailable(text):
+        return web.HTTPServiceUnavailable(text=json.dumps({"error": text, "error_type": "generation"}),
+                                          content_type="application/json")
+
+    async def _collect(self, toks, g):
+        """Whole response at once: the handler sleeps until the last token instead of waking for every token."""
+        lr = self.rt.submit(toks, g.max_new_tokens, stream=False)
+        err = await lr.done
+        if err:
+            raise self._unavailable(err)
+        return self._finish(lr, toks, g)
+
+    async def _run(self, toks, g):
+        """Token by token (server-sent events); the last item carries (tokens, timing headers)."""
+        lr = self.rt.submit(toks, g.max_new_tokens)
+        while True:
+            ev = await lr.queue.get()
+            if ev[0] == "error":
+                raise self._unavailable(ev[1])
+            _, tok, final = ev
+            yield tok, final, None
+            if final:
+                break
+        yield None, True, self._finish(lr, toks, g)
 
     # ------------------------------------------------------------------ handlers
     async def generate(self, req: web.Request) -> web.Response:
@@ -227,11 +239,7 @@ class RouterApp:
         if self.sem.locked():
             return web.json_response({"error": "Model is overloaded", "error_type": "overloaded"}, status=429)
         async with self.sem:
-            result = None
-            async for tok, final, done in self._run(toks, g):
-                if done is not None:
-                    result = done
-            out, stats = result
+            out, stats = await self._collect(toks, g)
         details = None
         if (body.get("parameters") or {}).get("details"):
             details = {"finish_reason": "length", "generated_tokens": len(out),

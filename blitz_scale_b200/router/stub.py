@@ -37,6 +37,9 @@ class WorkerStub:
                                                     response_deserializer=getattr(pb, res).FromString)
 
     async def call(self, rpc: str, request, timeout: Optional[float] = None, metadata=None):
+        if not request.IsInitialized():
+            # the transport would swallow the encoding error and send an empty message instead
+            raise ValueError(f"{rpc}: request is missing required fields: {request.FindInitializationErrors()}")
         if metadata is None:
             # trace context of the operation this call belongs to (set by the router runtime per dispatched op)
             metadata = grpc_metadata(CURRENT_TRACE.get())

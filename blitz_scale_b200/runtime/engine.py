@@ -130,7 +130,7 @@ class Engine:
         if T > self.max_batch_tokens:
             raise ValueError(f"prefill of {T} tokens exceeds max_batch_tokens={self.max_batch_tokens}")
         self._h2d(self.layout.page_indices + P)
-        lens = [len(s.spec.prompt) for s in batch.seqs]
+        lens = batch.prompt_lens()
         m = self._views(T, batch.size, P, True, lens)
         with nvtx_range("prefill"):
             toks = self.runner.forward(m)

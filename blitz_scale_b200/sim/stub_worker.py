@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 
 from ..pb.schema import pb
 from ..runtime import core
-from ..worker.service import Backend, make_generation
+from ..worker.service import Backend
 
 
 def stub_token(seed: int, request_id: int, position: int, vocab: int = 32000) -> int:
@@ -65,14 +65,10 @@ class StubBackend(Backend):
         return pb.CachedBatch(id=b.id, request_ids=ids, size=len(ids), max_tokens=b.max_tokens())
 
     def _emit(self, b, new_tokens: List[int]):
-        gens = []
-        for s, t in zip(b.seqs, new_tokens):
-            fin = None if s.finish < 0 else s.finish
-            gens.append(make_generation(s.spec.id, t, f"<{t}>", fin, len(s.generated)))
-        return gens
+        return b.encode_generations(new_tokens)
 
     def _step(self, b, prefill: bool):
-        toks = [stub_token(self.seed, s.spec.id, s.total_len()) for s in b.seqs]
+        toks = [stub_token(self.seed, rid, pl + n) for (rid, _, n), pl in zip(b.emit_info(), b.prompt_lens())]
         if prefill:
             b.mark_prefilled()
         b.append_tokens(toks, not prefill)
@@ -166,7 +162,7 @@ class StubBackend(Backend):
             for i, cb in enumerate(batches):
                 ids = list(last_iter_tokens[i].ids) if i < len(last_iter_tokens) else []
                 bi = self.batches[cb.id]
-                if ids and len(ids) == bi.size and all(len(s.generated) == 0 for s in bi.seqs):
+                if ids and len(ids) == bi.size and bi.none_generated():
                     bi.append_tokens(ids, False)
             first = self.batches[batches[0].id]
             for cb in batches[1:]:
@@ -225,7 +221,7 @@ class StubBackend(Backend):
                 b.decode = True
                 self.batches[batch.id] = b
             self.counters["immigrate"] += 1
-            return pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+            return pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
 
     # ------------------------------------------------------------------ parameters
     def _arrive(self, total_s: float):
@@ -295,11 +291,14 @@ def main(argv=None) -> None:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--load-seconds", type=float, default=0.2)
+    ap.add_argument("--decode-step-ms", type=float, default=2.0, help="simulated duration of one decode step")
+    ap.add_argument("--prefill-tokens-per-s", type=float, default=2e5, help="simulated prefill rate")
     a = ap.parse_args(argv)
     ready = True
     if a.config:
         ready = json.load(open(a.config))["init_states"][a.rank] != "Inactive"
-    backend = StubBackend(a.rank, a.world, seed=a.seed, layers=a.layers, ready=ready, load_s=a.load_seconds)
+    backend = StubBackend(a.rank, a.world, seed=a.seed, layers=a.layers, ready=ready, load_s=a.load_seconds,
+                          decode_step_s=a.decode_step_ms * 1e-3, prefill_tokens_per_s=a.prefill_tokens_per_s)
 
     async def run():
         stop = asyncio.Event()

@@ -34,7 +34,7 @@ from ..parallel.agreement import LoadAgreement
 from ..pb.schema import pb
 from ..runtime import core
 from ..runtime.engine import Engine
-from .service import Backend, make_generation
+from .service import Backend
 
 CTL_SLOT_WORDS = 16384  # page ids one transfer slot can publish
 log = logging.getLogger("blitz.worker")
@@ -114,8 +114,9 @@ class GpuBackend(Backend):
         return pb.CachedBatch(id=b.id, request_ids=ids, size=len(ids), max_tokens=b.max_tokens()) if ids else None
 
     def _emit(self, b, toks):
-        return [make_generation(s.spec.id, t, f"<{t}>", None if s.finish < 0 else s.finish, len(s.generated))
-                for s, t in zip(b.seqs, toks)]
+        # wire bytes built natively: touching `b.seqs` here would copy every prompt and token history per step, and
+        # building the messages one by one costs ~4 us each
+        return b.encode_generations(toks)
 
     def _finish_step(self, b, toks):
         gens = self._emit(b, toks)
@@ -150,7 +151,7 @@ class GpuBackend(Backend):
         eng = self.engine
         T, P = b.fill_prefill(eng.host_np, eng.layout)
         eng._h2d(eng.layout.page_indices + P)
-        m = eng._views(T, b.size, P, True, [len(s.spec.prompt) for s in b.seqs])
+        m = eng._views(T, b.size, P, True, b.prompt_lens())
         if start_layer > 0:
             slot = b.id % 4
             self.fabric.wait_flag(symm.MAILBOX_FLAG0 + slot, int(b.id) + 1, budget_ms=5000)
@@ -173,7 +174,7 @@ class GpuBackend(Backend):
             for i, cb in enumerate(batches):
                 ids = list(last_iter_tokens[i].ids) if i < len(last_iter_tokens) else []
                 bi = self.batches[cb.id]
-                if ids and len(ids) == bi.size and all(len(s.generated) == 0 for s in bi.seqs):
+                if ids and len(ids) == bi.size and bi.none_generated():
                     bi.append_tokens(ids, False)
             b = self.batches[batches[0].id]
             for cb in batches[1:]:
@@ -242,7 +243,7 @@ class GpuBackend(Backend):
                     task["meta"] = (T, P, dev_copy)
                 T, P, dev_copy = task["meta"]
                 eng.dev[:dev_copy.numel()].copy_(dev_copy)
-                m = eng._views(T, b.size, P, True, [len(s.spec.prompt) for s in b.seqs])
+                m = eng._views(T, b.size, P, True, b.prompt_lens())
                 saved = eng.runner.res
                 eng.runner.res = self.zag_slots[task["slot"]]
                 try:
@@ -298,7 +299,7 @@ class GpuBackend(Backend):
             # layers [0, k) of this batch's KV stay here until MigratePartial(FIRST) moves them
             b.mark_prefilled()
             self.batches[b.id] = b
-            cb = pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+            cb = pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
             task["future"].set_result(([], cb, pp))
             return r.batch_id, r.seq_num
 
@@ -325,12 +326,11 @@ class GpuBackend(Backend):
             lo, hi = self._layer_range(partial, num_layer)
             half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
             log.info("batch %d immigrate start%s layers [%d,%d) <~- rank %s", batch.id, half, lo, hi, list(src))
-            cb = pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+            cb = pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
             want = None
             if hi > lo and self.fabric is not None:
                 # publish the destination page ids of the prompt pages
-                ps = self.engine.page_size
-                ids = [p for s in b.seqs for p in s.pages[:(len(s.spec.prompt) + ps - 1) // ps]]
+                ids = b.prompt_page_ids()
                 want = list(self._kv_want(slot, lo, hi))
         if want is not None:
             # ... then wait for the layers to land, without holding the lock: decode steps of other batches go on
@@ -369,8 +369,7 @@ class GpuBackend(Backend):
             slot = batch.id % symm.KV_SLOTS
             half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
             log.info("batch %d migrate start%s layers [%d,%d) -~> rank %d", batch.id, half, lo, hi, peer)
-            ps = self.engine.page_size
-            src_ids = [p for s in b.seqs for p in s.pages[:(len(s.spec.prompt) + ps - 1) // ps]]
+            src_ids = b.prompt_page_ids()
         # the push itself runs outside the lock, on the transfer stream: this batch is parked until it has migrated,
         # and prefills of other batches continue meanwhile
         if hi > lo:
@@ -397,7 +396,7 @@ class GpuBackend(Backend):
                 self.side.synchronize()
             ops.check_status()
         with self.lock:
-            cb = pb.CachedBatch(id=b.id, request_ids=[s.spec.id for s in b.seqs], size=b.size, max_tokens=b.max_tokens())
+            cb = pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
             log.info("batch %d migrate done%s", batch.id, half)
             self.batches.pop(batch.id, None)
             b.clear()

@@ -122,7 +122,7 @@ class TextGenerationService:
         except Exception as e:  # noqa: BLE001
             return await self._abort(ctx, e)
         dt = time.perf_counter_ns() - t0
-        r = pb.PrefillV2Response(generations=gens, forward_ns=dt, decode_ns=0, total_ns=dt)
+        r = _response(pb.PrefillV2Response, gens, forward_ns=dt, decode_ns=0, total_ns=dt)
         if cb is not None:
             r.batch.CopyFrom(cb)
         if pp is not None:
@@ -142,7 +142,7 @@ class TextGenerationService:
         except Exception as e:  # noqa: BLE001
             return await self._abort(ctx, e)
         dt = time.perf_counter_ns() - t0
-        r = pb.PrefillV2Response(generations=gens, forward_ns=dt, decode_ns=0, total_ns=dt)
+        r = _response(pb.PrefillV2Response, gens, forward_ns=dt, decode_ns=0, total_ns=dt)
         if cb is not None:
             r.batch.CopyFrom(cb)
         if pp is not None:
@@ -155,7 +155,7 @@ class TextGenerationService:
             gens, cb = await self._call(self.b.decode, list(req.batches), list(req.last_iter_tokens))
         except Exception as e:  # noqa: BLE001
             return await self._abort(ctx, e)
-        r = pb.DecodeV2Response(generations=gens, total_ns=time.perf_counter_ns() - t0)
+        r = _response(pb.DecodeV2Response, gens, total_ns=time.perf_counter_ns() - t0)
         if cb is not None:
             r.batch.CopyFrom(cb)
         return r
@@ -266,6 +266,17 @@ async def serve(backend: Backend, host: str, port: int, urls=None, ready_event: 
             await server.wait_for_termination()
     finally:
         await server.stop(grace=1.0)
+
+
+def _response(cls, gens, **fields):
+    """Response of class `cls` whose `generations` (field 1 in both response types) come either as a list of
+    messages or as the wire bytes a backend encoded natively (`Batch.encode_generations`)."""
+    if isinstance(gens, (bytes, bytearray)):
+        r = cls.FromString(bytes(gens))
+        for k, v in fields.items():
+            setattr(r, k, v)
+        return r
+    return cls(generations=gens, **fields)
 
 
 def make_generation(request_id: int, token: int, text: str = "", finished: Optional[int] = None, n_generated: int = 0):

@@ -311,3 +311,31 @@ def test_oracle_kv_cache_matches_recomputation_and_tp_shards_sum_to_full():
         again = o.generate([p + t[:3]], 2)[0]
         assert again == t[3:5]
     assert o.generate(prompts, 5) == toks                      # deterministic
+
+
+def test_native_generation_encoding_equals_the_message_built_one():
+    from blitz_scale_b200.pb.schema import pb
+    from blitz_scale_b200.worker.service import _response, make_generation
+    pool = core.PagePool(64, 16)
+    b = core.Batch(3, pool)
+    specs = [core.SeqSpec(2 ** 40 + 5, [1, 2, 3], 1), core.SeqSpec(7, [4] * 20, 5), core.SeqSpec(300, [9], 2)]
+    assert b.add_prompts(specs)
+    b.mark_prefilled()
+    toks = [0, 131071, 127]
+    b.append_tokens(toks, False)                       # the first request reaches max_new_tokens = 1 and finishes
+    info = b.emit_info()
+    assert [i[0] for i in info] == [2 ** 40 + 5, 7, 300] and [i[1] for i in info] == [0, -1, -1] and [i[2] for i in info] == [1, 1, 1]
+    want = pb.DecodeV2Response(generations=[make_generation(rid, t, f"<{t}>", None if fin < 0 else fin, n)
+                                            for (rid, fin, n), t in zip(info, toks)])
+    raw = b.encode_generations(toks)
+    assert raw == want.SerializePartialToString()
+    got = _response(pb.DecodeV2Response, raw, total_ns=5)
+    assert got.total_ns == 5 and got.generations == want.generations and got.IsInitialized()
+    assert got.generations[0].generated_text.finish_reason == 0 and not got.generations[1].HasField("generated_text")
+    pre = _response(pb.PrefillV2Response, raw, forward_ns=1, decode_ns=0, total_ns=1)
+    assert [g.tokens.ids[0] for g in pre.generations] == toks and [g.tokens.texts[0] for g in pre.generations] == ["<0>", "<131071>", "<127>"]
+    assert b.request_ids() == [2 ** 40 + 5, 7, 300] and b.prompt_lens() == [3, 20, 1] and not b.none_generated()
+    assert b.prompt_page_ids() == [s.pages[0] for s in b.seqs[:1]] + list(b.seqs[1].pages[:2]) + [b.seqs[2].pages[0]]
+    with pytest.raises(Exception):
+        b.encode_generations([1])
+    b.clear()
