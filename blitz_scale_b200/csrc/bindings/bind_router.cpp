@@ -123,7 +123,7 @@ void bind_router(py::module_& m) {
       .def_readwrite("planner_interval_ms", &ControllerConfig::planner_interval_ms)
       .def_readwrite("model_layers", &ControllerConfig::model_layers).def_readwrite("model_name", &ControllerConfig::model_name)
       .def_readwrite("planner", &ControllerConfig::planner).def_readwrite("features", &ControllerConfig::features)
-      .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("quarantine_ms", &ControllerConfig::quarantine_ms).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
+      .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("quarantine_ms", &ControllerConfig::quarantine_ms).def_readwrite("max_incoming_migrations", &ControllerConfig::max_incoming_migrations).def_readwrite("kv_transfer_slots", &ControllerConfig::kv_transfer_slots).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
   py::class_<Controller::TokenOut>(m, "TokenOut")
       .def(py::init([](uint64_t id, int32_t tok, bool fin) { return Controller::TokenOut{id, tok, fin}; }));
   py::class_<ReplicaMetric>(m, "ReplicaMetric")

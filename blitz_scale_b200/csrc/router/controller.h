@@ -66,6 +66,12 @@ struct ControllerConfig {
   bool autoscale = true;
   double mock_load_ms = 0;
   double param_gb = 0;   // parameter bytes per replica in GB (0: unknown); only used for the transfer-rate metric
+  // Migrations that may be in flight towards one decode replica at a time.  1 is the reference's behaviour (a mutex
+  // per destination, router_v2/src/replica/disaggregation.rs try_lock scan); more lets the RPC latency of one
+  // migration overlap the transfer of another.  Concurrent migrations never share a transfer slot of the worker
+  // (slot = batch id mod `kv_transfer_slots`).
+  int max_incoming_migrations = 1;
+  int kv_transfer_slots = 8;
   double quarantine_ms = 5000;  // a lost replica is not chosen for scale-up again before this much time has passed
 };
 
@@ -184,7 +190,7 @@ class Controller {
     if (op.kind == ActionType::Migrate) {
       src.migrating = false;
       release_blocks(op.replica, op.batch.blocks);
-      unlock_target(op.peer);
+      unlock_target(op.peer, op.batch.id);
       dst.decode_batches.push_back(std::move(op.batch));
       return;
     }
@@ -195,7 +201,7 @@ class Controller {
     if (op.partial == 1) { r.fst_done = true; reps_[r.new_replica].m.flying_partial -= 1; }
     if (op.partial == 2) r.snd_done = true;
     if (r.fst_done && r.snd_done) {
-      unlock_target(op.peer);
+      unlock_target(op.peer, r.batch.id);
       dst.decode_batches.push_back(r.batch);
       relayed_.erase(it);
     }
@@ -260,10 +266,10 @@ class Controller {
     nrep.busy = !nrep.inflight_zag.empty();
     Relayed r;
     r.batch = rb; r.new_replica = neu; r.old_replica = old; r.next_layer = std::max(0, next_layer); r.blocks = rb.blocks;
-    r.target = pick_decode_target(rb.blocks);
+    r.target = pick_decode_target(rb.blocks, rb.id);
     // both replicas hold KV pages of this batch until their half has migrated
     reps_[old].m.used_blocks += rb.blocks;
-    if (r.target >= 0) acquire_target(r.target, rb.blocks);
+    if (r.target >= 0) acquire_target(r.target, rb.blocks, rb.id);
     Action a = make_simple(ActionType::PrefillPP, old, rb.id);
     a.op_id = new_op(ActionType::PrefillPP, old, neu, rb);
     a.peer = neu; a.num_layer = r.next_layer; a.request_ids = rb.request_ids; a.max_tokens = rb.max_tokens;
@@ -391,6 +397,7 @@ class Controller {
     double zag_started = 0;
     int partner = -1;         // OldPrefill <-> NewPrefill pairing
     int incoming = 0;         // migrations in flight towards this replica
+    std::vector<uint64_t> incoming_batches;  // their batch ids (for the transfer-slot rule)
   };
   struct Op {
     ActionType kind;
@@ -441,7 +448,7 @@ class Controller {
       throw std::logic_error(std::string("illegal transition ") + rstate_name(old) + " => " + rstate_name(s));
     reps_[r].m.state = s;
     // dst_mutex invariant: a replica holds its own mutex whenever it is not a decode target
-    if (s == RState::Decode) reps_[r].m.dst_busy = false;
+    if (s == RState::Decode) reps_[r].m.dst_busy = target_full(reps_[r]);
     else if (old == RState::Decode) reps_[r].m.dst_busy = true;
     log_transition(r, old, s);
   }
@@ -507,31 +514,40 @@ class Controller {
       if (it->id == batch_id) { rep.inflight_zag.erase(it); break; }
     rep.busy = !rep.inflight_zag.empty();
   }
-  int pick_decode_target(uint32_t need_blocks) const {
+  int pick_decode_target(uint32_t need_blocks, uint64_t batch_id) const {
     int best = -1;
     uint32_t best_used = UINT32_MAX;
+    const uint64_t slots = static_cast<uint64_t>(std::max(1, cfg_.kv_transfer_slots));
     for (int d = 0; d < num_replicas(); ++d) {
       const Rep& r = reps_[d];
       if (r.m.state != RState::Decode || r.m.dst_busy) continue;
+      bool slot_taken = false;
+      for (uint64_t other : r.incoming_batches) slot_taken = slot_taken || (other % slots == batch_id % slots);
+      if (slot_taken) continue;
       if (r.m.used_blocks + need_blocks > cfg_.max_blocks_per_replica) continue;
       if (!features_.has("decode_load_balance")) return d;  // first fit, like the reference's try_lock scan
       if (r.m.used_blocks < best_used) { best = d; best_used = r.m.used_blocks; }
     }
     return best;
   }
-  void acquire_target(int d, uint32_t blocks) {
+  bool target_full(const Rep& r) const { return r.incoming >= std::max(1, cfg_.max_incoming_migrations); }
+  void acquire_target(int d, uint32_t blocks, uint64_t batch_id) {
     reps_[d].incoming += 1;
-    reps_[d].m.dst_busy = true;
+    reps_[d].incoming_batches.push_back(batch_id);
+    reps_[d].m.dst_busy = reps_[d].m.state != RState::Decode || target_full(reps_[d]);
     reps_[d].m.used_blocks += blocks;
   }
-  void unlock_target(int d) {
-    reps_[d].incoming = std::max(0, reps_[d].incoming - 1);
-    reps_[d].m.dst_busy = reps_[d].m.state != RState::Decode || reps_[d].incoming > 0;
+  void unlock_target(int d, uint64_t batch_id) {
+    Rep& r = reps_[d];
+    r.incoming = std::max(0, r.incoming - 1);
+    auto it = std::find(r.incoming_batches.begin(), r.incoming_batches.end(), batch_id);
+    if (it != r.incoming_batches.end()) r.incoming_batches.erase(it);
+    r.m.dst_busy = r.m.state != RState::Decode || target_full(r);
   }
   void finish_relayed_target(Relayed& r) {
     if (r.target >= 0) {
       release_blocks(r.target, r.blocks);
-      unlock_target(r.target);
+      unlock_target(r.target, r.batch.id);
     }
   }
 
@@ -643,7 +659,8 @@ class Controller {
       return false;
     }
     if (nrep.inflight_zag.empty()) return false;
-    if (pick_decode_target(nrep.inflight_zag.front().blocks) < 0 && num_in_state(RState::Decode) > 0) return false;
+    if (pick_decode_target(nrep.inflight_zag.front().blocks, nrep.inflight_zag.front().id) < 0 && num_in_state(RState::Decode) > 0)
+      return false;
     orep.busy = true;
     orep.relay_wait = true;
     Action a = make_simple(ActionType::Relay, neu, 0);
@@ -697,7 +714,7 @@ class Controller {
     Rep& rep = reps_[src];
     if (rep.migrating || rep.pending_migration.empty()) return;
     ResidentBatch& b = rep.pending_migration.front();
-    const int dst = pick_decode_target(b.blocks);
+    const int dst = pick_decode_target(b.blocks, b.id);
     if (dst < 0) {
       // no decode side is left (it was lost after this batch was queued for it): decode where the KV already is,
       // as a prefill that completes in that situation does
@@ -707,7 +724,7 @@ class Controller {
       }
       return;
     }
-    acquire_target(dst, b.blocks);
+    acquire_target(dst, b.blocks, b.id);
     rep.migrating = true;
     Action a = make_simple(ActionType::Migrate, src, b.id);
     a.peer = dst; a.request_ids = b.request_ids; a.max_tokens = b.max_tokens;
@@ -722,9 +739,9 @@ class Controller {
     for (auto& kv : relayed_) {
       Relayed& r = kv.second;
       if (r.target < 0) {
-        r.target = pick_decode_target(r.blocks);
+        r.target = pick_decode_target(r.blocks, r.batch.id);
         if (r.target < 0) continue;
-        acquire_target(r.target, r.blocks);
+        acquire_target(r.target, r.blocks, r.batch.id);
       }
       auto emit = [&](int part, int from) {
         Action a = make_simple(ActionType::MigratePartial, from, r.batch.id);
@@ -1134,7 +1151,7 @@ class Controller {
         case ActionType::Migrate:
           fail_ids(o.batch.request_ids);
           release_blocks(other, o.batch.blocks);
-          if (o.replica == r) unlock_target(other);
+          if (o.replica == r) unlock_target(other, o.batch.id);
           else reps_[other].migrating = false;
           out_.push_back(make_simple(ActionType::ClearCache, other, o.batch.id));
           cancel(id, o.batch.id, {other});
@@ -1168,6 +1185,7 @@ class Controller {
     rep.inflight_zag.clear();
     rep.busy = rep.migrating = rep.relay_wait = false;
     rep.incoming = 0;
+    rep.incoming_batches.clear();
     rep.m.used_blocks = 0;
     rep.m.flying_partial = 0;
     rep.m.model_loaded = false;

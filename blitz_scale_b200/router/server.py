@@ -376,6 +376,8 @@ def main(argv=None) -> None:
     ap.add_argument("--health-misses", type=int, default=2, help="consecutive missed pings that declare a replica lost")
     ap.add_argument("--rpc-timeout-ms", type=float, default=300000.0,
                     help="deadline of every worker RPC; a reply that never comes then counts as a failed replica (0 = none)")
+    ap.add_argument("--max-incoming-migrations", type=int, default=1,
+                    help="KV migrations in flight towards one decode replica at a time (1 = one at a time, as the reference)")
     ap.add_argument("--quarantine-ms", type=float, default=5000.0,
                     help="a replica declared lost is not chosen for scale-up again before this much time has passed")
     ap.add_argument("--statistic-csv", default="", help="write prefill/decode token deltas every 500 ms to this file")
@@ -395,6 +397,7 @@ def main(argv=None) -> None:
         migration_upper=a.migration_upper_bound, min_prefill=a.min_prefill_num, max_prefill=a.max_prefill_num,
         min_decode=a.min_decode_num, max_decode=a.max_decode_num, scale_down_threshold_ms=a.scale_down_threshold_millis)
     cfg.quarantine_ms = a.quarantine_ms
+    cfg.max_incoming_migrations = max(1, a.max_incoming_migrations)
     layers = get_config(a.model_name).layers
     try:
         from ..runtime import core as _core

@@ -464,6 +464,33 @@ def test_lost_participant_aborts_a_shared_parameter_transfer():
     assert [a.dst_ranks for a in ctl.step(0.03) if a.type == core.ActionType.NvlBroadcast] == [[2]]
 
 
+def test_concurrent_incoming_migrations_respect_limit_and_transfer_slots():
+    def start(max_in, slots):
+        cfg = _cfg(["Prefill", "Prefill", "Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False,
+                   max_incoming_migrations=max_in, kv_transfer_slots=slots)
+        ctl = core.Controller(cfg)
+        for i in range(3):
+            ctl.submit(E(i, 6000, 8))            # one request per batch (prefill token budget 8192)
+        pf = [a for a in ctl.step(0.0) if a.type == core.ActionType.Prefill]
+        assert sorted(a.replica for a in pf) == [0, 1, 2]
+        for a in pf:
+            ctl.on_prefill_done(a.op_id, [core.TokenOut(a.request_ids[0], 1, False)], 0.01)
+        return ctl, [a for a in ctl.step(0.02) if a.type == core.ActionType.Migrate]
+    ctl, mig = start(1, 8)
+    assert len(mig) == 1 and ctl.metric(3).dst_busy          # one at a time (the reference's destination mutex)
+    ctl.on_migrate_done(mig[0].op_id, 0.03)
+    assert len([a for a in ctl.step(0.04) if a.type == core.ActionType.Migrate]) == 1
+    ctl, mig = start(2, 8)
+    assert len(mig) == 2 and ctl.metric(3).dst_busy          # two in flight, the third waits
+    assert not [a for a in ctl.step(0.03) if a.type == core.ActionType.Migrate]
+    ctl.on_migrate_done(mig[0].op_id, 0.04)
+    assert len([a for a in ctl.step(0.05) if a.type == core.ActionType.Migrate]) == 1
+    ctl, mig = start(3, 1)
+    assert len(mig) == 1                                     # a single transfer slot: never two at once, whatever the limit
+    ctl, mig = start(3, 8)
+    assert len(mig) == 3 and len({a.batch_id % 8 for a in mig}) == 3
+
+
 def test_calibrated_autoscaling_study_orders_the_policies():
     """Virtual-time replay with the measured B200 cost model: faster parameter delivery -> lower p99 TTFT."""
     import os

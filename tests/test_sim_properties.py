@@ -17,15 +17,17 @@ FEATURES = ["impl_blitz,impl_nvl", "impl_blitz,impl_nvl,impl_live", "impl_blitz,
 @settings(max_examples=int(os.environ.get("BLITZ_PROPERTY_EXAMPLES", "25")), deadline=None)
 @given(feat=st.sampled_from(FEATURES), seed=st.integers(0, 10 ** 6), n_inactive=st.integers(0, 4),
        burst=st.floats(4.0, 60.0), cv=st.sampled_from([1.0, 2.0, 4.0]), kill=st.booleans(), kill_replica=st.integers(0, 2), kill_at=st.sampled_from([0.5, 1.2, 2.0, 3.5]),
-       prefill_rate=st.sampled_from([8000.0, 30000.0, 120000.0]), tp=st.sampled_from([1, 2]))
+       prefill_rate=st.sampled_from([8000.0, 30000.0, 120000.0]), tp=st.sampled_from([1, 2]),
+       max_incoming=st.sampled_from([1, 2, 4]))
 def test_requests_and_blocks_are_conserved(feat, seed, n_inactive, burst, cv, kill, kill_replica, kill_at, prefill_rate,
-                                           tp):
+                                           tp, max_incoming):
     states = ["Prefill", "Decode"] + ["Inactive"] * n_inactive
     cfg = core.ControllerConfig()
     cfg.num_ranks, cfg.tp = len(states) * tp, tp
     cfg.init_states = sum([[s] * tp for s in states], [])
     cfg.features = feat
     cfg.max_blocks_per_replica = 3000
+    cfg.max_incoming_migrations = max_incoming
     p = cfg.planner
     p.tokens_prefilled_per_sec, p.tokens_transferred_per_sec = int(prefill_rate * 0.2), 500000
     p.max_prefill, p.max_decode = len(states) - 1, len(states) - 1
