@@ -52,6 +52,7 @@ def main():
     ap.add_argument("--pages", type=int, default=4096)
     ap.add_argument("--model-path", default="")
     ap.add_argument("--multimem", action="store_true")
+    ap.add_argument("--precapture", action="store_true", help="capture every decode graph at start-up instead of on first use")
     ap.add_argument("--autoscale", action="store_true", help="let the planner decide when and how far to scale (no manual trigger)")
     ap.add_argument("--prefill-rate", type=float, default=60000.0, help="autoscale: prefill tokens/s one replica sustains")
     ap.add_argument("--horizon-ms", type=float, default=100.0, help="autoscale: queue the planner tolerates, as time")
@@ -69,7 +70,8 @@ def main():
     cfg_model = get_config(a.model)
     states = ["Prefill", "Decode"] + ["Inactive"] * (world - 2)
     backend = GpuBackend(rank, world, a.model, tp=1, num_pages=a.pages, page_size=64, max_batch=256, max_batch_tokens=8192,
-                         ready=states[rank] != "Inactive", seed=0, use_multimem=a.multimem, model_path=a.model_path)
+                         ready=states[rank] != "Inactive", seed=0, use_multimem=a.multimem, model_path=a.model_path,
+                         precapture=a.precapture)
     if states[rank] == "Inactive":
         if a.mode == "sllm" and not a.model_path:
             # best case of the host-cache baseline: the weights already sit in pinned host memory on this machine

@@ -173,6 +173,31 @@ class Engine:
         self._graphs[(Bp, splits)] = g
         return g
 
+    def precapture(self, max_batch: Optional[int] = None, contexts: Sequence[int] = (64, 1024, 4096, 16384)) -> int:
+        """Capture the decode graphs of every batch bucket up to `max_batch` (default: the engine's) and of the
+        split-KV choices that contexts of the given lengths select, so that no request pays for a capture later.
+        The captures run on padded rows only (an empty batch): graph topology and buffer addresses do not depend
+        on the parameters' values, so this also works on a replica whose parameters have not arrived.  With tp > 1
+        every rank of the replica must call it (the captures contain the collectives).  Returns the number captured."""
+        if not self.use_graphs:
+            return 0
+        limit = min(max_batch or self.max_batch, self.max_batch)
+        empty = core.Batch((1 << 62), self.pool)
+        n = 0
+        for Bp in _BUCKETS:
+            if Bp > limit:
+                break
+            for ctx in contexts:
+                splits = self.choose_splits(Bp, ctx)
+                if (Bp, splits) in self._graphs:
+                    continue
+                P = empty.fill_decode(self.host_np, self.layout, Bp)      # Bp padded rows: no page, no cache write
+                self._h2d(self.layout.page_indices + P)
+                self._capture(Bp, splits)
+                n += 1
+        torch.cuda.current_stream().synchronize()
+        return n
+
     def decode_launch_count(self) -> int:
         """Kernels of this library launched by one decode step at tp = 1 (for the bench's launch accounting)."""
         per_layer = 8  # rms_norm, qkv gemm, rope_kv_store, attention, o gemm, rms_norm, gate_up gemm, down gemm

@@ -44,7 +44,7 @@ class GpuBackend(Backend):
     def __init__(self, rank: int, world: int, model: str, *, tp: int = 1, num_pages: int = 2048, page_size: int = 64,
                  max_batch: int = 256, max_batch_tokens: int = 8192, ready: bool = True, use_fabric: bool = True,
                  tp_group=None, model_path: str = "", seed: int = 0, use_multimem: bool = False, copy_ctas: int = 128,
-                 fused_tp: bool = True):
+                 fused_tp: bool = True, precapture: bool = False):
         self.rank, self.world, self.tp = rank, world, tp
         self.cfg = get_config(model)
         self.model, self.model_path = model, model_path
@@ -71,6 +71,12 @@ class GpuBackend(Backend):
                              max_batch_tokens=max_batch_tokens, tp=tp, tp_rank=rank % tp, dtype=dt, comm=comm,
                              seg_buffer=seg_buf, kv_buffer=kv_buf, ready=ready, seed=seed, fused_tp=fused_tp)
         self.units = [(n, o, b) for n, o, b in self.engine.seg.layout.units]
+        if precapture:
+            # every decode graph is captured now, whether or not the parameters are here yet, so that neither a
+            # running replica nor one that has just been scaled out stops to capture when a new batch size shows up
+            t0 = time.perf_counter()
+            n = self.engine.precapture()
+            log.info("captured %d decode graphs in %.2f s", n, time.perf_counter() - t0)
         self.batches: Dict[int, "core.Batch"] = {}
         self.param_expected = 0      # cumulative flag value that means "all stripes of the current transfer landed"
         self.host_mirror: Optional[torch.Tensor] = None
