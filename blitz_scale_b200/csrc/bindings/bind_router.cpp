@@ -1,6 +1,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 #include "router/controller.h"
+#include "util/pbwire.h"
 namespace py = pybind11;
 using namespace blitz;
 
@@ -124,6 +125,10 @@ void bind_router(py::module_& m) {
       .def_readwrite("model_layers", &ControllerConfig::model_layers).def_readwrite("model_name", &ControllerConfig::model_name)
       .def_readwrite("planner", &ControllerConfig::planner).def_readwrite("features", &ControllerConfig::features)
       .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("quarantine_ms", &ControllerConfig::quarantine_ms).def_readwrite("max_incoming_migrations", &ControllerConfig::max_incoming_migrations).def_readwrite("kv_transfer_slots", &ControllerConfig::kv_transfer_slots).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
+  m.def("parse_generations", [](py::bytes raw) {
+    auto g = pbwire::parse_generations(static_cast<std::string>(raw));
+    return py::make_tuple(g.request_ids, g.tokens, g.finished); },
+    "(request ids, first token ids, finished flags) of the `generations` of a serialized prefill / decode response");
   py::class_<Controller::TokenOut>(m, "TokenOut")
       .def(py::init([](uint64_t id, int32_t tok, bool fin) { return Controller::TokenOut{id, tok, fin}; }));
   py::class_<ReplicaMetric>(m, "ReplicaMetric")
@@ -138,6 +143,19 @@ void bind_router(py::module_& m) {
       .def("on_migrate_done", &Controller::on_migrate_done).def("on_params_done", &Controller::on_params_done)
       .def("on_relay_done", &Controller::on_relay_done).def("on_failure", &Controller::on_failure, py::arg("op_id"), py::arg("now"), py::arg("failed_replica") = -1)
       .def("step", &Controller::step).def("manual_scale", &Controller::manual_scale)
+      // completion straight from the wire bytes of the worker's response: the generations are read natively
+      .def("on_prefill_done_wire", [](Controller& c, uint64_t op, py::bytes raw, double now) {
+        auto g = pbwire::parse_generations(static_cast<std::string>(raw));
+        std::vector<Controller::TokenOut> t;
+        t.reserve(g.request_ids.size());
+        for (size_t i = 0; i < g.request_ids.size(); ++i) t.push_back({g.request_ids[i], g.tokens[i], g.finished[i]});
+        c.on_prefill_done(op, t, now); })
+      .def("on_decode_done_wire", [](Controller& c, uint64_t op, py::bytes raw, double now) {
+        auto g = pbwire::parse_generations(static_cast<std::string>(raw));
+        std::vector<Controller::TokenOut> t;
+        t.reserve(g.request_ids.size());
+        for (size_t i = 0; i < g.request_ids.size(); ++i) t.push_back({g.request_ids[i], g.tokens[i], g.finished[i]});
+        c.on_decode_done(op, t, now); })
       .def("set_compact_deliveries", &Controller::set_compact_deliveries)
       .def("take_deliveries", [](Controller& c) {
         std::vector<std::tuple<uint64_t, int32_t, bool>> out;

@@ -265,12 +265,6 @@ class RouterRuntime:
         self.wake.set()
 
     # ------------------------------------------------------------------ handlers
-    @staticmethod
-    def _tokens_out(generations) -> tuple:
-        """(request ids, tokens, finished flags) of a response's generations, as parallel lists."""
-        return ([g.request_id for g in generations], [g.tokens.ids[0] if g.tokens.ids else -1 for g in generations],
-                [g.HasField("generated_text") for g in generations])
-
     async def _do_prefill(self, a) -> None:
         batch = self._batch_proto(a)
         ranks = self._ranks(a.replica)
@@ -294,7 +288,7 @@ class RouterRuntime:
             return
         if res.HasField("batch"):
             self.cached[(a.replica, a.batch_id)] = res.batch
-        ids, toks, fins = self._tokens_out(res.generations)
+        ids, toks, fins = core.parse_generations(res.raw)
         self.first_tokens[a.batch_id] = {i: t for i, t in zip(ids, toks) if t >= 0}
         now = self.now()
         self.ctl.on_prefill_done_lists(a.op_id, ids, toks, fins, now)
@@ -319,7 +313,7 @@ class RouterRuntime:
         if res.HasField("batch"):
             self.cached[(a.replica, res.batch.id)] = res.batch
         now = self.now()
-        self.ctl.on_decode_done_lists(a.op_id, *self._tokens_out(res.generations), now)
+        self.ctl.on_decode_done_wire(a.op_id, res.raw, now)
         self._deliver(now)          # straight away: the next step of the loop may be a tick away
 
     async def _do_migrate(self, a) -> None:

@@ -22,6 +22,25 @@ def encode_prefill_case(*cases: int) -> int:
     return v
 
 
+class WireResponse:
+    """A parsed response that also keeps its wire bytes (the router core reads the generations from them natively
+    instead of walking the message object token by token).  Attribute access goes to the message."""
+    __slots__ = ("msg", "raw")
+
+    def __init__(self, msg, raw: bytes):
+        self.msg, self.raw = msg, raw
+
+    def __getattr__(self, name):
+        return getattr(self.msg, name)
+
+
+_KEEP_WIRE = ("PrefillV2", "ZagPrefill", "DecodeV2")
+
+
+def _wire_deserializer(cls):
+    return lambda data: WireResponse(cls.FromString(data), data)
+
+
 class WorkerStub:
     def __init__(self, url: str, default_timeout: Optional[float] = None):
         """`default_timeout` (seconds) is the deadline of every call that does not pass its own: a worker that never
@@ -32,9 +51,10 @@ class WorkerStub:
                                                                ("grpc.max_send_message_length", 256 << 20)])
         self._m = {}
         for rpc, (req, res) in RPCS.items():
+            des = _wire_deserializer(getattr(pb, res)) if rpc in _KEEP_WIRE else getattr(pb, res).FromString
             self._m[rpc] = self.channel.unary_unary(method_path(rpc),
                                                     request_serializer=getattr(pb, req).SerializeToString,
-                                                    response_deserializer=getattr(pb, res).FromString)
+                                                    response_deserializer=des)
 
     async def call(self, rpc: str, request, timeout: Optional[float] = None, metadata=None):
         if not request.IsInitialized():

@@ -339,3 +339,39 @@ def test_native_generation_encoding_equals_the_message_built_one():
     with pytest.raises(Exception):
         b.encode_generations([1])
     b.clear()
+
+
+def test_native_generation_reader_agrees_with_the_protobuf_library():
+    from blitz_scale_b200.pb.schema import pb
+    from blitz_scale_b200.worker.service import make_generation
+    rng = random.Random(1)
+    for trial in range(50):
+        gens = []
+        for _ in range(rng.randint(0, 40)):
+            tok = rng.choice([0, 1, 127, 128, 300, 131071, 2 ** 31 - 1])
+            fin = rng.choice([None, 0, 1, 2])
+            g = make_generation(rng.choice([0, 5, 2 ** 33, 2 ** 63 + 1]), tok, f"<{tok}>", fin, rng.randint(0, 9))
+            if rng.random() < 0.3:                         # fields the reader must skip
+                g.prefill_tokens.ids.extend([1, 2, 3])
+                g.prefill_tokens.logprobs.extend([0.5, 0.25, 0.0])
+            if rng.random() < 0.2:
+                g.tokens.ids.append(9)                     # only the first token id counts
+                g.tokens.logprobs.append(0.0)
+                g.tokens.texts.append("x")
+                g.tokens.is_special.append(True)
+            gens.append(g)
+        r = pb.DecodeV2Response(generations=gens, total_ns=rng.randint(0, 2 ** 40))
+        if gens and rng.random() < 0.5:
+            r.batch.CopyFrom(pb.CachedBatch(id=3, request_ids=[1, 2], size=2, max_tokens=128))
+        ids, toks, fins = core.parse_generations(r.SerializeToString())
+        assert ids == [g.request_id for g in gens]
+        assert toks == [g.tokens.ids[0] for g in gens]
+        assert fins == [g.HasField("generated_text") for g in gens]
+    # a prefill response carries the same field 1, plus fields the decode response does not have
+    p = pb.PrefillV2Response(generations=[make_generation(4, 77)], forward_ns=1, decode_ns=2, total_ns=3)
+    p.pp_info.tfm_layer = 5
+    assert core.parse_generations(p.SerializeToString()) == ([4], [77], [False])
+    assert core.parse_generations(b"") == ([], [], [])
+    for bad in (b"\x0a\x05\x08", b"\x0a\xff\xff\xff\xff\xff\xff\xff\xff\xff\xff\xff", b"\x0b\x00", b"\x0a\x03\x1a\x05\x08"):
+        with pytest.raises(Exception):
+            core.parse_generations(bad)                    # truncated or malformed input is refused, never read past
