@@ -102,14 +102,17 @@ def commands(inst: dict, d: Path) -> dict:
     return {"workers": workers, "router": router, "client": client}
 
 
-def wait_for(path: Path, needle: str, count: int, timeout: float, also_glob: str = "") -> bool:
+def wait_for(path: Path, needle: str, count: int, timeout: float, also_glob: str = "", procs=()) -> bool:
     """Wait until `needle` occurs `count` times in `path` plus the files matching `also_glob` (workers started with
-    --log-dir write one file per rank instead of their stdout)."""
+    --log-dir write one file per rank instead of their stdout).  Gives up at once when one of `procs` has exited:
+    a worker that could not bind its port will never print the line."""
     t0 = time.time()
     while time.time() - t0 < timeout:
         files = [path] + (sorted(path.parent.glob(also_glob)) if also_glob else [])
         if sum(f.read_text(errors="ignore").count(needle) for f in files if f.exists()) >= count:
             return True
+        if any(p.poll() is not None for p in procs):
+            return False
         time.sleep(0.2)
     return False
 
@@ -130,12 +133,12 @@ def run_instance(inst: dict, d: Path, dry: bool) -> dict:
             procs.append(subprocess.Popen(shlex.split(c), stdout=wl, stderr=subprocess.STDOUT, env=env, start_new_session=True))
         n = int(inst["global"].get("num_gpus", 2))
         if not wait_for(d / "workers.log", "Start gRPC server", n, float(inst["global"].get("boot_timeout", 600)),
-                        also_glob="worker-logs/*.log"):
-            raise RuntimeError("workers did not start")
+                        also_glob="worker-logs/*.log", procs=procs):
+            raise RuntimeError("workers did not start (see workers.log)")
         rl = open(d / "router.log", "w")
         logs.append(rl)
         procs.append(subprocess.Popen(shlex.split(cmds["router"]), stdout=rl, stderr=subprocess.STDOUT, env=env, start_new_session=True))
-        if not wait_for(d / "router.log", "Router listening", 1, 60):
+        if not wait_for(d / "router.log", "Router listening", 1, 60, procs=procs[-1:]):
             raise RuntimeError("router did not start")
         # scripted manual scaling: [[global.manual_scale]] at_s = 20, replica = 2, state = "Prefill"  (needs the
         # manually_scale feature; entries with the same at_s reach the router before its next step and therefore

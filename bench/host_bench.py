@@ -11,7 +11,8 @@ Measures, on the machine it runs on:
     model when it is installed);
   * loader: throughput of the native multi-threaded segment-file reader (page cache warm);
   * RPC: round-trip latency of worker RPCs over loopback gRPC against a stub worker (what the transport adds to a
-    decode step), and router-level requests/s through the HTTP API with stub workers.
+    decode step), router-level requests/s with stub workers, and the same through the HTTP API (`POST /generate`) with
+    the router started from its command line.
 """
 import argparse
 import asyncio
@@ -255,14 +256,70 @@ def bench_rpc(quick: bool) -> dict:
             p.wait(timeout=10)
 
 
+def bench_http(quick: bool) -> dict:
+    """The user-facing path: POST /generate against the router started from its command line (own process), two
+    stub workers (own processes, zero simulated compute), a client with many requests in flight."""
+    import subprocess
+
+    import aiohttp
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    wports, rport = [_free_port() for _ in range(2)], _free_port()
+    with tempfile.TemporaryDirectory() as d:
+        json.dump({"init_states": ["Prefill", "Decode"], "machines": [0, 0]}, open(os.path.join(d, "cluster.json"), "w"))
+        procs = [subprocess.Popen([sys.executable, "-m", "blitz_scale_b200.sim.stub_worker", "--rank", str(r), "--world", "2",
+                                   "--port", str(wports[r]), "--decode-step-ms", "0", "--prefill-tokens-per-s", "1e12"],
+                                  cwd=root, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL) for r in range(2)]
+        procs.append(subprocess.Popen(
+            [sys.executable, "-m", "blitz_scale_b200.router.server", "--port", str(rport), "--client-config",
+             json.dumps([f"127.0.0.1:{p}" for p in wports]), "--deployment-config-path", os.path.join(d, "cluster.json"),
+             "--features", "impl_blitz,impl_nvl,manually_scale", "--model-name", "tiny", "--max-blocks-per-replica", "2000000",
+             "--log-level", "WARNING"], cwd=root, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL))
+
+        async def go():
+            url = f"http://127.0.0.1:{rport}/generate"
+            out = {}
+            async with aiohttp.ClientSession(connector=aiohttp.TCPConnector(limit=0)) as sess:
+                for _ in range(300):
+                    try:
+                        async with sess.get(f"http://127.0.0.1:{rport}/health") as r:
+                            if r.status == 200:
+                                break
+                    except Exception:  # noqa: BLE001
+                        pass
+                    await asyncio.sleep(0.1)
+
+                async def one(n_tok):
+                    body = {"input_tokens": list(range(64)), "parameters": {"max_new_tokens": n_tok}}
+                    async with sess.post(url, json=body) as r:
+                        await r.json()
+                        return r.status == 200
+                assert all(await asyncio.gather(*[one(4) for _ in range(16)]))
+                n_req = 200 if quick else 1500
+                for label, n_tok in (("8_tokens", 8), ("64_tokens", 64)):
+                    t0 = time.perf_counter()
+                    oks = await asyncio.gather(*[one(n_tok) for _ in range(n_req)])
+                    dt = time.perf_counter() - t0
+                    assert all(oks)
+                    out[f"http_generate_{label}_requests_per_s"] = round(n_req / dt, 1)
+                    out[f"http_generate_{label}_tokens_per_s"] = round(n_req * n_tok / dt, 1)
+            return out
+        try:
+            return asyncio.run(go())
+        finally:
+            for p in procs:
+                p.terminate()
+            for p in procs:
+                p.wait(timeout=10)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--only", default="", help="comma list of: controller,queue,tokenizer,loader,rpc")
+    ap.add_argument("--only", default="", help="comma list of: controller,queue,tokenizer,loader,rpc,http")
     a = ap.parse_args()
     parts = {"controller": bench_controller, "queue": bench_queue, "tokenizer": bench_tokenizer, "loader": bench_loader,
-             "rpc": bench_rpc}
+             "rpc": bench_rpc, "http": bench_http}
     want = [p for p in a.only.split(",") if p] or list(parts)
     res = {"bench": "host", "cpus": os.cpu_count()}
     for name in want:

@@ -186,6 +186,6 @@ void bind_router(py::module_& m) {
       .def("inflight_ops", &Controller::inflight_ops).def("total_used_blocks", &Controller::total_used_blocks)
       .def("request", [](const Controller& c, uint64_t id) -> py::object {
         const RequestEntry* e = c.request(id); if (!e) return py::none(); return py::cast(*e); })
-      .def("finished", &Controller::finished).def("last_target", &Controller::last_target)
+      .def("finished", &Controller::finished).def("pop_finished", &Controller::pop_finished).def("last_target", &Controller::last_target)
       .def("has_feature", [](const Controller& c, const std::string& f) { return c.features().has(f); });
 }

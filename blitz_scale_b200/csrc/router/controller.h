@@ -12,6 +12,7 @@
 #include <algorithm>
 #include <deque>
 #include <map>
+#include <optional>
 #include <sstream>
 #include <string>
 #include <vector>
@@ -1256,6 +1257,14 @@ class Controller {
 
  public:
   const std::map<uint64_t, RequestEntry>& finished() const { return finished_; }
+  // Take the record of a finished request out of the core (a long-running shell must, or the map grows for ever).
+  std::optional<RequestEntry> pop_finished(uint64_t id) {
+    auto it = finished_.find(id);
+    if (it == finished_.end()) return std::nullopt;
+    RequestEntry e = std::move(it->second);
+    finished_.erase(it);
+    return e;
+  }
   const std::map<std::string, double>& gauges() const { return gauges_; }
   Steersman& steersman() { return steer_; }
 };

@@ -58,6 +58,7 @@ class LiveRequest:
     # (None, or the error text): one wake-up per request instead of one per token.
     stream: bool = True
     done: Optional[asyncio.Future] = None
+    entry: object = None               # the core's record of the request (queue and token times), set when it finishes
 
 
 class RouterRuntime:
@@ -243,6 +244,7 @@ class RouterRuntime:
             lr.queue.put_nowait(("token", token, final))
         if final:
             del self.requests[rid]
+            lr.entry = self.ctl.pop_finished(rid)     # out of the core: its map of finished requests stays empty
             if not lr.done.done():
                 lr.done.set_result(None)
 

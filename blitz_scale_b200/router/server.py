@@ -176,7 +176,7 @@ class RouterApp:
         # the interval between the prefill token and the first decode token contains the KV migration: it is reported
         # on its own and is not a time-between-tokens sample
         tbt = [b - a for a, b in zip(times[1:], times[2:])]
-        e = self.rt.ctl.finished().get(lr.id)
+        e = lr.entry
         queue_s = (e.t_batched - e.t_arrival) if e is not None and e.t_batched >= 0 else 0.0
         stats = {
             "x-compute-type": "gpu+optimized", "x-total-time": int(total * 1e3), "x-validation-time": 0,

@@ -31,6 +31,27 @@ def _free_ports(n):
     return ports
 
 
+def _free_port_run(n):
+    """First port of a run of n consecutive free ports."""
+    for _ in range(200):
+        base = _free_ports(1)[0]
+        if base + n >= 65536:
+            continue
+        socks = []
+        try:
+            for i in range(n):
+                s = socket.socket()
+                socks.append(s)
+                s.bind(("127.0.0.1", base + i))
+            return base
+        except OSError:
+            continue
+        finally:
+            for s in socks:
+                s.close()
+    raise RuntimeError("no run of free ports found")
+
+
 def test_proto_contract_roundtrip():
     assert len(RPCS) == 25
     for rpc, (req, res) in RPCS.items():
@@ -249,13 +270,19 @@ def test_experiment_runs_processes_end_to_end(tmp_path):
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     tpl = open(os.path.join(root, "bench/templates/cpu_plumbing.toml")).read()
-    p0, p1, p2 = _free_ports(3)
+    p0, p2 = _free_port_run(3), _free_ports(1)[0]            # the workers listen on p0, p0 + 1, p0 + 2
     tpl = tpl.replace("worker_port = 50151", f"worker_port = {p0}").replace("port = 3100", f"port = {p2}")
     tpl = tpl.replace("duration = 50", "duration = 4").replace("num_requests = 200", "num_requests = 16")
     (tmp_path / "t.toml").write_text(tpl)
-    res = subprocess.run([sys.executable, os.path.join(root, "bench/experiment.py"), "--template", str(tmp_path / "t.toml"),
-                          "--out", str(tmp_path / "out"), "--force"], capture_output=True, text=True, timeout=240)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    run = subprocess.Popen([sys.executable, os.path.join(root, "bench/experiment.py"), "--template", str(tmp_path / "t.toml"),
+                            "--out", str(tmp_path / "out"), "--force"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        out, _ = run.communicate(timeout=240)
+    except subprocess.TimeoutExpired:
+        run.terminate()                                     # SIGTERM: the runner stops the processes it started
+        out, _ = run.communicate(timeout=60)
+        raise AssertionError("experiment runner timed out:\n" + out[-3000:])
+    assert run.returncode == 0, out[-4000:]
     d = next(p for p in (tmp_path / "out").iterdir() if p.is_dir())
     recs = [json.loads(l) for l in open(d / "client.jsonl")]
     assert len(recs) >= 8 and all(r.get("status") == "ok" for r in recs), recs[:2]
