@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import asyncio
+import bisect
 from concurrent.futures import ThreadPoolExecutor
 import json
 import logging
@@ -73,16 +74,24 @@ class Metrics:
     """Prometheus exposition with the reference's metric names (router_v2/src/server.rs:811-857)."""
     BUCKETS = [0.005, 0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10, 30]
 
+    SIZE_BUCKETS = [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192, 16384]
+    _SIZES = ("blitz_request_generated_tokens", "blitz_request_input_length", "blitz_request_max_new_tokens",
+              "blitz_batch_next_size")
+
     def __init__(self):
         self.counters = {"blitz_request_count": 0, "blitz_request_success": 0, "blitz_request_failure": 0}
-        self.hist = {n: [] for n in ("blitz_request_duration", "blitz_request_validation_duration",
-                                     "blitz_request_queue_duration", "blitz_request_inference_duration",
-                                     "blitz_request_mean_time_per_token_duration", "blitz_request_generated_tokens",
-                                     "blitz_request_input_length", "blitz_request_max_new_tokens",
-                                     "blitz_batch_next_size")}
+        names = ("blitz_request_duration", "blitz_request_validation_duration", "blitz_request_queue_duration",
+                 "blitz_request_inference_duration", "blitz_request_mean_time_per_token_duration") + self._SIZES
+        # fixed-size state per histogram: [bucket upper bounds, count per bucket (last = overflow), sum, count]
+        self.hist = {n: [self.SIZE_BUCKETS if n in self._SIZES else self.BUCKETS, None, 0.0, 0] for n in names}
+        for h in self.hist.values():
+            h[1] = [0] * (len(h[0]) + 1)
 
     def observe(self, name: str, v: float) -> None:
-        self.hist[name].append(v)
+        h = self.hist[name]
+        h[1][bisect.bisect_left(h[0], v)] += 1
+        h[2] += v
+        h[3] += 1
 
     def render(self, rt: RouterRuntime) -> str:
         out = []
@@ -96,13 +105,15 @@ class Metrics:
         gauges["blitz_queue_size"] = ctl.queue_size
         for k, v in sorted(gauges.items()):
             out += [f"# TYPE {k} gauge", f"{k} {v}"]
-        for name, xs in sorted(self.hist.items()):
+        for name, (bounds, counts, total, n) in sorted(self.hist.items()):
             out.append(f"# TYPE {name} histogram")
-            for b in self.BUCKETS:
-                out.append(f'{name}_bucket{{le="{b}"}} {sum(1 for x in xs if x <= b)}')
-            out.append(f'{name}_bucket{{le="+Inf"}} {len(xs)}')
-            out.append(f"{name}_sum {sum(xs)}")
-            out.append(f"{name}_count {len(xs)}")
+            acc = 0
+            for b, c in zip(bounds, counts):
+                acc += c
+                out.append(f'{name}_bucket{{le="{b}"}} {acc}')
+            out.append(f'{name}_bucket{{le="+Inf"}} {n}')
+            out.append(f"{name}_sum {total}")
+            out.append(f"{name}_count {n}")
         return "\n".join(out) + "\n"
 
 

@@ -133,6 +133,10 @@ def test_config1_cpu_plumbing_scale_out_and_determinism():
     assert any("Replica<1> LoadingPrefill => Prefill" in l for l in transitions)
     assert backends[1].counters["prefill"] > 0, "the scaled-out instance must serve requests"
     assert "blitz_request_count 80" in metrics and "blitz_request_duration_count 80" in metrics
+    # histograms are cumulative and end at the count; sizes have buckets of their own
+    assert 'blitz_request_duration_bucket{le="+Inf"} 80' in metrics and 'blitz_request_input_length_bucket{le="16384"} 80' in metrics
+    cum = [int(l.rsplit(" ", 1)[1]) for l in metrics.splitlines() if l.startswith("blitz_request_generated_tokens_bucket")]
+    assert cum == sorted(cum) and cum[-1] == 80 and cum[0] < 80
     assert info["replicas"] == ["Prefill", "Prefill"]
     assert used == 0 and pages == [0, 0]
     s = request_sim.summarize(recs)
