@@ -291,7 +291,8 @@ class RouterRuntime:
         if res.HasField("batch"):
             self.cached[(a.replica, a.batch_id)] = res.batch
         ids, toks, fins = core.parse_generations(res.raw)
-        self.first_tokens[a.batch_id] = {i: t for i, t in zip(ids, toks) if t >= 0}
+        if res.HasField("batch"):      # somebody will decode this batch: its first tokens travel with the first step
+            self.first_tokens[a.batch_id] = {i: t for i, t in zip(ids, toks) if t >= 0}
         now = self.now()
         self.ctl.on_prefill_done_lists(a.op_id, ids, toks, fins, now)
         self._deliver(now)
@@ -360,6 +361,8 @@ class RouterRuntime:
     async def _do_simple(self, a) -> None:
         if a.type == A.ClearCache:
             self.cached.pop((a.replica, a.batch_id), None)
+            if not any(k[1] == a.batch_id for k in self.cached):
+                self.first_tokens.pop(a.batch_id, None)
             await asyncio.gather(*[self.stubs[r].clear_cache(a.batch_id) for r in self._ranks(a.replica)])
         elif a.type == A.ResetStatus:
             await asyncio.gather(*[self.stubs[r].reset_status() for r in a.dst_ranks])

@@ -426,3 +426,31 @@ def test_dropped_immigrate_reply_fails_the_operation_not_the_router():
         asyncio.run(go())
     finally:
         release.set()
+
+
+def test_nothing_is_left_behind_after_many_requests():
+    """Soak: after a few hundred requests of mixed lengths (some finish with their first token) every map of the
+    router runtime and of the core is empty again and the workers hold no batch and no page."""
+    async def go():
+        rt, backends, port, stop, tasks = await _cluster(3, ["Prefill", "Decode", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+        for b in backends:
+            b.decode_step_s, b.prefill_rate = 0.0, 1e12
+
+        async def one(i):
+            lr = rt.submit(list(range(8 + i % 50)), 1 + (i * 7) % 12, stream=bool(i % 2))
+            assert (await asyncio.wait_for(lr.done, timeout=60)) is None
+            assert len(lr.tokens) == 1 + (i * 7) % 12 and lr.entry is not None
+            if lr.stream:
+                assert lr.queue.qsize() == len(lr.tokens)
+        for wave in range(3):
+            await asyncio.gather(*[one(wave * 100 + i) for i in range(100)])
+        for _ in range(100):                                   # trailing ClearCache actions
+            if rt.ctl.idle() and not rt.cached and all(not b.batches for b in backends):
+                break
+            await asyncio.sleep(0.05)
+        state = (len(rt.requests), len(rt.cached), len(rt.first_tokens), len(rt.ctl.finished()), rt.ctl.inflight_ops(),
+                 rt.ctl.total_used_blocks(), rt.ctl.idle(), [len(b.batches) for b in backends],
+                 [b.pool.used_pages for b in backends])
+        await _shutdown(stop, tasks)
+        return state
+    assert asyncio.run(go()) == (0, 0, 0, 0, 0, 0, True, [0, 0, 0], [0, 0, 0])
