@@ -124,7 +124,7 @@ void bind_router(py::module_& m) {
       .def_readwrite("planner_interval_ms", &ControllerConfig::planner_interval_ms)
       .def_readwrite("model_layers", &ControllerConfig::model_layers).def_readwrite("model_name", &ControllerConfig::model_name)
       .def_readwrite("planner", &ControllerConfig::planner).def_readwrite("features", &ControllerConfig::features)
-      .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("quarantine_ms", &ControllerConfig::quarantine_ms).def_readwrite("max_incoming_migrations", &ControllerConfig::max_incoming_migrations).def_readwrite("kv_transfer_slots", &ControllerConfig::kv_transfer_slots).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
+      .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("quarantine_ms", &ControllerConfig::quarantine_ms).def_readwrite("kv_mb_per_token", &ControllerConfig::kv_mb_per_token).def_readwrite("max_incoming_migrations", &ControllerConfig::max_incoming_migrations).def_readwrite("kv_transfer_slots", &ControllerConfig::kv_transfer_slots).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
   m.def("parse_generations", [](py::bytes raw) {
     auto g = pbwire::parse_generations(static_cast<std::string>(raw));
     return py::make_tuple(g.request_ids, g.tokens, g.finished); },
@@ -156,6 +156,7 @@ void bind_router(py::module_& m) {
         t.reserve(g.request_ids.size());
         for (size_t i = 0; i < g.request_ids.size(); ++i) t.push_back({g.request_ids[i], g.tokens[i], g.finished[i]});
         c.on_decode_done(op, t, now); })
+      .def("take_flows", &Controller::take_flows).def("waiting_migration_tokens", &Controller::waiting_migration_tokens)
       .def("set_compact_deliveries", &Controller::set_compact_deliveries)
       .def("take_deliveries", [](Controller& c) {
         std::vector<std::tuple<uint64_t, int32_t, bool>> out;

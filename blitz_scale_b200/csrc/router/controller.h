@@ -15,6 +15,7 @@
 #include <optional>
 #include <sstream>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "queue.h"
@@ -67,6 +68,7 @@ struct ControllerConfig {
   bool autoscale = true;
   double mock_load_ms = 0;
   double param_gb = 0;   // parameter bytes per replica in GB (0: unknown); only used for the transfer-rate metric
+  double kv_mb_per_token = 0;  // KV bytes of one token over all layers of a replica, in MB (0: unknown); flow report only
   // Migrations that may be in flight towards one decode replica at a time.  1 is the reference's behaviour (a mutex
   // per destination, router_v2/src/replica/disaggregation.rs try_lock scan); more lets the RPC latency of one
   // migration overlap the transfer of another.  Concurrent migrations never share a transfer slot of the worker
@@ -188,7 +190,13 @@ class Controller {
     Rep& src = reps_[op.replica];
     Rep& dst = reps_[op.peer];
     counters_[op.kind == ActionType::Migrate ? "blitz_kv_cache_times" : "blitz_partial_kv_cache_times"] += 1;
+    auto count_flow = [&](double fraction) {
+      const double kv_mb = cfg_.kv_mb_per_token * op.batch.prompt_tokens * fraction;
+      src.m.flow_out_mb += kv_mb;
+      dst.m.flow_in_mb += kv_mb;
+    };
     if (op.kind == ActionType::Migrate) {
+      count_flow(1.0);
       src.migrating = false;
       release_blocks(op.replica, op.batch.blocks);
       unlock_target(op.peer, op.batch.id);
@@ -198,6 +206,8 @@ class Controller {
     auto it = relayed_.find(op.batch.id);
     if (it == relayed_.end()) return;
     Relayed& r = it->second;
+    const double first = static_cast<double>(r.next_layer) / std::max<uint32_t>(1, cfg_.model_layers);
+    count_flow(op.partial == 1 ? first : 1.0 - first);   // layers [0, k) from the new instance, [k, L) from the old one
     release_blocks(op.replica, r.blocks);
     if (op.partial == 1) { r.fst_done = true; reps_[r.new_replica].m.flying_partial -= 1; }
     if (op.partial == 2) r.snd_done = true;
@@ -224,9 +234,12 @@ class Controller {
     for (int s : op.sources) {
       steer_.set_nvlink_busy(s, false);
       reps_[s].m.marker.reset();
+      // every source streams its stripe of the parameters to all targets
+      reps_[s].m.flow_out_mb += cfg_.param_gb * 1e3 * static_cast<double>(op.targets.size()) / static_cast<double>(op.sources.size());
     }
     for (int d : op.targets) {
       Rep& rep = reps_[d];
+      if (!op.sources.empty()) rep.m.flow_in_mb += cfg_.param_gb * 1e3;
       rep.m.model_loaded = true;
       steer_.record_model_loaded(d);
       steer_.touch_host_cache(steer_.machine_of(d * cfg_.tp), now);
@@ -356,6 +369,25 @@ class Controller {
   struct Delivery { uint64_t request_id; int32_t token; bool final; };
   void set_compact_deliveries(bool on) { compact_deliveries_ = on; }
   std::vector<Delivery> take_deliveries() { std::vector<Delivery> d; d.swap(deliveries_); return d; }
+  // Network flow since the last call, per replica that moved anything: (replica, MB in, MB out).  Parameters count
+  // with `param_gb`, migrated KV with `kv_mb_per_token` x the batch's prompt tokens (the periodic report of
+  // router_v2/src/replica/disaggregation.rs:244-298).
+  std::vector<std::tuple<int, double, double>> take_flows() {
+    std::vector<std::tuple<int, double, double>> out;
+    for (int r = 0; r < num_replicas(); ++r) {
+      ReplicaMetric& m = reps_[r].m;
+      if (m.flow_in_mb + m.flow_out_mb > 0) out.emplace_back(r, m.flow_in_mb, m.flow_out_mb);
+      m.flow_in_mb = m.flow_out_mb = 0;
+    }
+    return out;
+  }
+  // Prompt tokens of batches that have been prefilled and wait for their migration to a decode replica.
+  uint64_t waiting_migration_tokens() const {
+    uint64_t t = 0;
+    for (auto& r : reps_)
+      for (auto& b : r.pending_migration) t += b.prompt_tokens;
+    return t;
+  }
   std::string system_metrics_line() const {
     std::ostringstream s;
     s << "System Metrics: prefill_tokens: " << stats_prefill_tokens_ << ", decode_tokens: " << stats_decode_tokens_;

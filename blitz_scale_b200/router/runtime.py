@@ -88,6 +88,7 @@ class RouterRuntime:
         self.cached: Dict[tuple, object] = {}        # (replica, batch_id) -> pb.CachedBatch
         self.first_tokens: Dict[int, Dict[int, int]] = {}  # batch_id -> {request_id: first token} until first decode
         self.wake = asyncio.Event()
+        self._loop_turns = 0
         self.stopped = False
         self.t0 = time.monotonic()
         self.root_trace = new_traceparent()
@@ -145,6 +146,7 @@ class RouterRuntime:
             self._spawn(self._health_loop())
         while not self.stopped:
             now = self.now()
+            self._loop_turns += 1
             actions = self.ctl.step(now)
             for line in self.ctl.drain_log():
                 log.info(line)
@@ -160,6 +162,13 @@ class RouterRuntime:
             if now - last_metrics >= 1.0:
                 last_metrics = now
                 log.info(self.ctl.system_metrics_line())
+                log.info("Waiting migration token num: %d", self.ctl.waiting_migration_tokens())
+                for rep, mb_in, mb_out in self.ctl.take_flows():
+                    log.info("Replica[%d]: Flow in: %dMB, Flow out: %dMB", rep, round(mb_in), round(mb_out))
+                # the loop that plans and dispatches must keep turning (the reference asserts the same once a second)
+                if self._loop_turns == 0 and now > 2.0:
+                    log.error("Control loop stuck!")
+                self._loop_turns = 0
                 if log.isEnabledFor(logging.DEBUG):
                     for r in range(self.ctl.num_replicas):
                         m = self.ctl.metric(r)

@@ -413,6 +413,7 @@ def main(argv=None) -> None:
     try:
         from ..runtime import core as _core
         cfg.param_gb = _core.build_segment_layout(a.model_name, a.tensor_parallel_size, 2).total_bytes * a.tensor_parallel_size / 1e9
+        cfg.kv_mb_per_token = get_config(a.model_name).kv_bytes_per_token(1, 2) / 1e6
     except Exception:  # noqa: BLE001 - only feeds a metric
         pass
     async def amain():

@@ -20,6 +20,7 @@ from ..models.config import get_config
 
 _TRANS = re.compile(r"Replica<(\d+)> (\w+) => (\w+)")
 _METRIC = re.compile(r"System Metrics: prefill_tokens: (\d+), decode_tokens: (\d+)")
+_FLOW = re.compile(r"Replica\[(\d+)\]: Flow in: (\d+)MB, Flow out: (\d+)MB")
 _SIGNAL = re.compile(r"Control signal: P([+-]\d+) D([+-]\d+)")
 _STAMP = re.compile(r"^\[?\s*(\d+\.\d+)\]?")
 
@@ -45,7 +46,7 @@ def line_time(ln: str):
 
 def parse_router_log(lines: Iterable[str]) -> dict:
     """Times are relative to the first stamped line when the log carries wall-clock stamps."""
-    out = {"transitions": [], "signals": [], "metrics": [], "unloads": [], "client_start": None}
+    out = {"transitions": [], "signals": [], "metrics": [], "unloads": [], "flows": [], "client_start": None}
     t0 = None
     for ln in lines:
         t = line_time(ln)
@@ -61,6 +62,9 @@ def parse_router_log(lines: Iterable[str]) -> dict:
         me = _METRIC.search(ln)
         if me:
             out["metrics"].append((t, int(me.group(1)), int(me.group(2))))
+        fl = _FLOW.search(ln)
+        if fl:
+            out["flows"].append((t, int(fl.group(1)), int(fl.group(2)), int(fl.group(3))))   # (t, replica, MB in, MB out)
         if ">>= unload" in ln:
             out["unloads"].append(t)
         if "Client start" in ln and out["client_start"] is None:

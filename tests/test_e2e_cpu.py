@@ -253,10 +253,11 @@ def test_log_analysis_and_sizing():
     from blitz_scale_b200.utils import analysis
     log = ["[0.000000] Replica<0> boot => Prefill", "[1.5] Replica<2> Inactive => LoadingPrefill",
            "[1.9] Replica<2> LoadingPrefill => Prefill", "[2.0] Control signal: P+1 D+0 | x",
-           "[3.0] System Metrics: prefill_tokens: 100, decode_tokens: 7", "[4.0] Replica<2> >>= unload", "Client start"]
+           "[3.0] System Metrics: prefill_tokens: 100, decode_tokens: 7", "[4.0] Replica<2> >>= unload", "Client start",
+           "[4.5] Replica[2]: Flow in: 16061MB, Flow out: 0MB"]
     p = analysis.parse_router_log(log)
     assert p["transitions"][1] == (1.5, 2, "Inactive", "LoadingPrefill") and p["signals"] == [(2.0, 1, 0)]
-    assert p["metrics"] == [(3.0, 100, 7)] and p["unloads"] == [4.0]
+    assert p["metrics"] == [(3.0, 100, 7)] and p["unloads"] == [4.0] and p["flows"] == [(4.5, 2, 16061, 0)]
     assert analysis.scale_out_latencies(p["transitions"]) == [(2, pytest.approx(0.4))]
     tl = analysis.replica_timeline(p["transitions"], 5.0)
     assert tl[2] == [(1.5, 1.9, "LoadingPrefill"), (1.9, 5.0, "Prefill")]

@@ -491,6 +491,24 @@ def test_concurrent_incoming_migrations_respect_limit_and_transfer_slots():
     assert len(mig) == 3 and len({a.batch_id % 8 for a in mig}) == 3
 
 
+def test_network_flow_accounting():
+    cfg = _cfg(["Prefill", "Decode", "Inactive"], "impl_blitz,impl_nvl,manually_scale", param_gb=16.0, kv_mb_per_token=0.125)
+    ctl = core.Controller(cfg)
+    assert ctl.manual_scale(2, "Decode", 0.0)
+    bc = [a for a in ctl.step(0.0) if a.type == core.ActionType.NvlBroadcast][0]
+    ctl.on_params_done(bc.op_id, 0.03)
+    assert ctl.take_flows() == [(1, 0.0, 16000.0), (2, 16000.0, 0.0)]       # decode replica 1 was the source
+    assert ctl.take_flows() == []                                             # reported once
+    ctl.submit(E(1, 1000, 4))
+    pf = [a for a in ctl.step(0.1) if a.type == core.ActionType.Prefill][0]
+    ctl.on_prefill_done(pf.op_id, [core.TokenOut(1, 5, False)], 0.12)
+    assert ctl.waiting_migration_tokens() == 1000
+    mig = [a for a in ctl.step(0.13) if a.type == core.ActionType.Migrate][0]
+    assert ctl.waiting_migration_tokens() == 0
+    ctl.on_migrate_done(mig.op_id, 0.14)
+    assert ctl.take_flows() == [(0, 0.0, 125.0), (mig.peer, 125.0, 0.0)]
+
+
 def test_calibrated_autoscaling_study_orders_the_policies():
     """Virtual-time replay with the measured B200 cost model: faster parameter delivery -> lower p99 TTFT."""
     import os
