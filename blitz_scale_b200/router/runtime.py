@@ -64,8 +64,10 @@ class LiveRequest:
 class RouterRuntime:
     def __init__(self, cfg: "core.ControllerConfig", worker_urls: List[str], model_layers: int = 32,
                  model_path: str = "", stat_csv: str = "", health_interval_s: float = 0.0, health_misses: int = 2,
-                 rpc_timeout_s: float = 300.0):
+                 rpc_timeout_s: float = 300.0, exporter=None):
         self.cfg = cfg
+        # optional span sink (`utils.otlp.SpanExporter`): one span per dispatched operation and one per request
+        self.exporter = exporter
         # failure detector: every `health_interval_s` each active replica's ranks are pinged with the Health RPC;
         # `health_misses` consecutive misses (error or no answer within the interval) declare the replica lost.
         # The reference has no detector (its Health is a stub and a failed RPC panics the replica task).
@@ -254,6 +256,11 @@ class RouterRuntime:
         if final:
             del self.requests[rid]
             lr.entry = self.ctl.pop_finished(rid)     # out of the core: its map of finished requests stays empty
+            if self.exporter is not None:
+                end = time.time()
+                self.exporter.span("generate", child_traceparent(self.root_trace), end - (now - lr.t_submit), end,
+                                   request_id=rid, input_tokens=len(lr.proto.input_tokens), generated_tokens=len(lr.tokens),
+                                   first_token_s=lr.times[0] - lr.t_submit, parent_span_id=self.root_trace.split("-")[2])
             if not lr.done.done():
                 lr.done.set_result(None)
 
@@ -263,16 +270,22 @@ class RouterRuntime:
             self._deliver_one(rid, token, final, now)
 
     async def _guard(self, a, handler) -> None:
+        tp = child_traceparent(self.root_trace)       # one span per dispatched operation
+        t0, ok = time.time(), True
         try:
-            CURRENT_TRACE.set(child_traceparent(self.root_trace))     # one span per dispatched operation
+            CURRENT_TRACE.set(tp)
             await handler(a)
         except asyncio.CancelledError:
             raise
         except Exception as e:  # noqa: BLE001  an RPC failed: the replica is gone
+            ok = False
             blamed = e.rank // self.tp if isinstance(e, RankFailure) else a.replica
             log.error("RPC for %s on replica %d failed (replica %d is taken as lost): %s", a.type.name, a.replica, blamed, e)
             if a.op_id:
                 self.ctl.on_failure(a.op_id, self.now(), blamed)
+        if self.exporter is not None:
+            self.exporter.span(a.type.name, tp, t0, time.time(), replica=a.replica, peer=a.peer, batch_id=int(a.batch_id),
+                               requests=len(a.request_ids), ok=ok, parent_span_id=self.root_trace.split("-")[2])
         self.wake.set()
 
     # ------------------------------------------------------------------ handlers

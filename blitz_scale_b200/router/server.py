@@ -19,6 +19,8 @@ import bisect
 from concurrent.futures import ThreadPoolExecutor
 import json
 import logging
+import os
+import signal
 import time
 import zlib
 from typing import List, Optional
@@ -81,7 +83,8 @@ class Metrics:
     def __init__(self):
         self.counters = {"blitz_request_count": 0, "blitz_request_success": 0, "blitz_request_failure": 0}
         names = ("blitz_request_duration", "blitz_request_validation_duration", "blitz_request_queue_duration",
-                 "blitz_request_inference_duration", "blitz_request_mean_time_per_token_duration") + self._SIZES
+                 "blitz_request_inference_duration", "blitz_request_mean_time_per_token_duration",
+                 "blitz_request_skipped_tokens") + self._SIZES
         # fixed-size state per histogram: [bucket upper bounds, count per bucket (last = overflow), sum, count]
         self.hist = {n: [self.SIZE_BUCKETS if n in self._SIZES else self.BUCKETS, None, 0.0, 0] for n in names}
         for h in self.hist.values():
@@ -120,12 +123,16 @@ class Metrics:
 class RouterApp:
     def __init__(self, rt: RouterRuntime, *, model_name: str = "llama3_8b", max_input_length: int = 4095,
                  max_total_tokens: int = 4096, max_concurrent: int = 4096, vocab: int = 32000,
-                 tokenizer_path: str = "", tokenizer_workers: int = 2):
+                 tokenizer_path: str = "", tokenizer_workers: int = 2, max_best_of: int = 2, max_stop_sequences: int = 4,
+                 max_top_n_tokens: int = 5, cors_allow_origin: Optional[List[str]] = None):
         self.rt = rt
         self.tok = NativeTokenizer(tokenizer_path) if tokenizer_path else WordHashTokenizer(vocab)
         self.tok_pool = ThreadPoolExecutor(max_workers=max(1, tokenizer_workers), thread_name_prefix="tokenizer")
         self.limits = core.ValidationLimits()
         self.limits.max_input_length, self.limits.max_total_tokens = max_input_length, max_total_tokens
+        self.limits.max_best_of, self.limits.max_stop_sequences = max_best_of, max_stop_sequences
+        self.limits.max_top_n_tokens = max_top_n_tokens
+        self.cors = list(cors_allow_origin or [])
         self.model_name = model_name
         try:
             from ..models.config import get_config
@@ -136,7 +143,7 @@ class RouterApp:
             self.tok = WordHashTokenizer(min(vocab, self.model_vocab))
         self.sem = asyncio.Semaphore(max_concurrent)
         self.metrics = Metrics()
-        self.app = web.Application(client_max_size=64 << 20)
+        self.app = web.Application(client_max_size=64 << 20, middlewares=[self._cors_middleware] if self.cors else [])
         r = self.app.router
         for path in ("/", "/generate", "/invocations"):
             r.add_post(path, self.generate)
@@ -147,6 +154,22 @@ class RouterApp:
         r.add_get("/metrics", self.prom)
         r.add_get("/docs", self.docs)
         r.add_post("/modify_cluster_state", self.modify_cluster_state)
+
+    @web.middleware
+    async def _cors_middleware(self, req: web.Request, handler):
+        """Cross-origin access for the origins given with --cors-allow-origin ("*" allows any)."""
+        origin = req.headers.get("Origin", "")
+        allowed = origin and ("*" in self.cors or origin in self.cors)
+        if req.method == "OPTIONS" and allowed:
+            resp = web.Response(status=204)
+        else:
+            resp = await handler(req)
+        if allowed:
+            resp.headers["Access-Control-Allow-Origin"] = "*" if "*" in self.cors else origin
+            resp.headers["Access-Control-Allow-Methods"] = "GET, POST, OPTIONS"
+            resp.headers["Access-Control-Allow-Headers"] = req.headers.get("Access-Control-Request-Headers", "Content-Type")
+            resp.headers["Vary"] = "Origin"
+        return resp
 
     # ------------------------------------------------------------------ request parsing
     async def _parse(self, body: dict):
@@ -209,6 +232,7 @@ class RouterApp:
         m.observe("blitz_request_generated_tokens", len(out))
         m.observe("blitz_request_input_length", len(toks))
         m.observe("blitz_request_max_new_tokens", g.max_new_tokens)
+        m.observe("blitz_request_skipped_tokens", 0.0)     # no speculation: a token is never skipped
         return list(out), stats
 
     @staticmethod
@@ -349,8 +373,9 @@ async def serve_router(rt: RouterRuntime, host: str, port: int, stop: Optional[a
         await runner.cleanup()
 
 
-def main(argv=None) -> None:
-    """CLI of the router binary (the subset of router_v2/src/main.rs:40-155 that applies to one NVSwitch box)."""
+def build_parser() -> argparse.ArgumentParser:
+    """Flags of the router binary (router_v2/src/main.rs:40-155; what does not apply to one NVSwitch box is accepted
+    and ignored).  Every flag can also be given through the environment, as FLAG_NAME in upper case."""
     ap = argparse.ArgumentParser("blitz-router")
     ap.add_argument("--hostname", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=3000)
@@ -382,7 +407,7 @@ def main(argv=None) -> None:
         ap.add_argument("--" + n, type=int, default=8)
     ap.add_argument("--scale-down-threshold-millis", type=float, default=333)
     ap.add_argument("--mock-load-millis", type=float, default=0)
-    ap.add_argument("--log-level", default="INFO")
+    ap.add_argument("--log-level", default=None, help="default: the LOG_LEVEL environment variable, else INFO")
     ap.add_argument("--health-interval-ms", type=float, default=0.0, help="ping every active replica this often (0 = off)")
     ap.add_argument("--health-misses", type=int, default=2, help="consecutive missed pings that declare a replica lost")
     ap.add_argument("--rpc-timeout-ms", type=float, default=300000.0,
@@ -391,9 +416,46 @@ def main(argv=None) -> None:
                     help="KV migrations in flight towards one decode replica at a time (1 = one at a time, as the reference)")
     ap.add_argument("--quarantine-ms", type=float, default=5000.0,
                     help="a replica declared lost is not chosen for scale-up again before this much time has passed")
-    ap.add_argument("--statistic-csv", default="", help="write prefill/decode token deltas every 500 ms to this file")
-    a = ap.parse_args(argv)
-    logging.basicConfig(level=a.log_level, format="%(asctime)s %(name)s %(message)s")
+    ap.add_argument("--statistic-csv", "--statistic-path", dest="statistic_csv", default="",
+                    help="write prefill/decode token deltas every 500 ms to this file")
+    ap.add_argument("--json-output", action="store_true", help="log lines as JSON objects")
+    ap.add_argument("--log-path", default="", help="write the log to this file (through a background writer) instead of stderr")
+    ap.add_argument("--otlp-endpoint", default="", help="OTLP/HTTP collector, e.g. http://127.0.0.1:4318: spans of every "
+                    "dispatched operation and request are exported there as service blitz.router")
+    ap.add_argument("--otlp-service-name", default="blitz.router")
+    ap.add_argument("--cors-allow-origin", action="append", default=[], help="origin allowed for cross-origin requests (repeatable, * = any)")
+    ap.add_argument("--max-concurrent-requests", type=int, default=4096)
+    ap.add_argument("--max-best-of", type=int, default=2)
+    ap.add_argument("--max-stop-sequences", type=int, default=4)
+    ap.add_argument("--max-top-n-tokens", type=int, default=5)
+    # accepted so that the reference's launch scripts run unchanged; what they configure is either derived from the
+    # model registry here (layers, parameter size), fixed by the one-box deployment, or has no counterpart
+    for name, kw in (("--num-hidden-layers", dict(type=int)), ("--parameter-size", dict(type=float)),
+                     ("--num-gpus-per-node", dict(type=int)), ("--mock-transfer-millis", dict(type=float)),
+                     ("--waiting-served-ratio", dict(type=float)), ("--max-waiting-tokens", dict(type=int)),
+                     ("--max-batch-total-tokens", dict(type=int)), ("--tokenizer-name", {}), ("--revision", {}),
+                     ("--deployment", {}), ("--use-tokenizer", dict(action="store_true"))):
+        ap.add_argument(name, help="accepted for command-line compatibility", **({"default": None} | kw if "action" not in kw else kw))
+    # every flag can also be given through the environment (FLAG_NAME in upper case), as with the reference's CLI
+    for act in ap._actions:
+        env = os.environ.get(act.dest.upper())
+        # HOSTNAME is set by most shells and containers to the machine's name: not a request to listen there
+        if env is None or not act.option_strings or act.dest in ("help", "hostname"):
+            continue
+        if isinstance(act, argparse._StoreTrueAction):
+            act.default = env.lower() not in ("", "0", "false", "no")
+        elif isinstance(act, argparse._AppendAction):
+            act.default = [x for x in env.split(",") if x]
+        else:
+            act.default = act.type(env) if act.type else env
+            act.required = False
+    return ap
+
+
+def main(argv=None) -> None:
+    a = build_parser().parse_args(argv)
+    from ..utils.otlp import SpanExporter, init_logging
+    log_listener = init_logging(a.log_level, a.json_output, a.log_path)
     from ..models.config import get_config
     cluster = json.load(open(a.deployment_config_path))
     urls = json.loads(a.client_config) if a.client_config.strip().startswith("[") else json.load(open(a.client_config))
@@ -418,14 +480,30 @@ def main(argv=None) -> None:
         pass
     async def amain():
         # the gRPC channels of the runtime belong to the event loop that creates them: build it inside the loop
+        exporter = SpanExporter(a.otlp_endpoint, a.otlp_service_name) if a.otlp_endpoint else None
+        if exporter is not None:
+            exporter.start()
         rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv,
                            health_interval_s=a.health_interval_ms * 1e-3, health_misses=a.health_misses,
-                           rpc_timeout_s=a.rpc_timeout_ms * 1e-3)
-        await serve_router(rt, a.hostname, a.port, model_name=a.model_name, max_input_length=a.max_input_length,
-                           max_total_tokens=a.max_total_tokens, tokenizer_path=a.tokenizer_path,
-                           tokenizer_workers=a.validation_workers)
+                           rpc_timeout_s=a.rpc_timeout_ms * 1e-3, exporter=exporter)
+        stop = asyncio.Event()
+        for sig in (signal.SIGINT, signal.SIGTERM):
+            asyncio.get_running_loop().add_signal_handler(sig, stop.set)
+        try:
+            await serve_router(rt, a.hostname, a.port, stop=stop, model_name=a.model_name, max_input_length=a.max_input_length,
+                               max_total_tokens=a.max_total_tokens, tokenizer_path=a.tokenizer_path,
+                               tokenizer_workers=a.validation_workers, max_concurrent=a.max_concurrent_requests,
+                               max_best_of=a.max_best_of, max_stop_sequences=a.max_stop_sequences,
+                               max_top_n_tokens=a.max_top_n_tokens, cors_allow_origin=a.cors_allow_origin)
+        finally:
+            if exporter is not None:
+                await exporter.stop()           # flushes what is buffered
 
-    asyncio.run(amain())
+    try:
+        asyncio.run(amain())
+    finally:
+        if log_listener is not None:
+            log_listener.stop()
 
 
 if __name__ == "__main__":

@@ -30,8 +30,11 @@ _ISO = re.compile(r"^\[?(\d{4}-\d{2}-\d{2})[T ](\d{2}):(\d{2}):(\d{2})(?:[.,](\d
 
 def line_time(ln: str):
     """Seconds from a log line's stamp: `[  12.345]` / `12.345 ...` (seconds) or `2024-01-01 10:00:00,123` (the
-    `logging` default; returned as seconds since midnight of the line's own date plus the day number * 86400)."""
+    `logging` default; also the "timestamp" field of a JSON log line; returned as seconds since midnight of the line's own date plus the day number * 86400)."""
     ln = ln.strip()
+    if ln.startswith("{"):               # a JSON log line: its "timestamp" field is an ISO stamp
+        m = re.search(r'"timestamp"\s*:\s*"([^"]+)"', ln)
+        return line_time(m.group(1)) if m else None
     m = _STAMP.match(ln)
     if m and not _ISO.match(ln):
         return float(m.group(1))

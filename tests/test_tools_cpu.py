@@ -2,6 +2,7 @@
 import asyncio
 import io
 import json
+import os
 import socket
 
 import pytest
@@ -187,3 +188,140 @@ def test_tp_load_agreement():
     a[1].publish(L + 2)
     assert a[0].agreed_state() == (True, L, True)
     assert 0 not in pads[0] and F0 not in pads[0]          # nothing leaks to other replicas' pads
+
+
+def test_otlp_span_export_logging_and_cors(tmp_path):
+    """Spans of dispatched operations and requests reach an OTLP/HTTP collector (a local stand-in) in the JSON
+    mapping; the log set-up writes JSON lines through the background file writer; CORS headers follow the allow list."""
+    import asyncio
+    import json
+    import logging
+    import socket
+
+    from aiohttp import web
+
+    from blitz_scale_b200.router.runtime import RouterRuntime
+    from blitz_scale_b200.router.server import RouterApp, controller_config_from_cluster
+    from blitz_scale_b200.sim.stub_worker import StubBackend
+    from blitz_scale_b200.utils import analysis
+    from blitz_scale_b200.utils.otlp import SpanExporter, init_logging, span_record
+    from blitz_scale_b200.worker.service import serve
+
+    rec = span_record("x", "00-" + "ab" * 16 + "-" + "cd" * 8 + "-01", 10, 20, {"n": 3, "f": 0.5, "s": "t", "b": True}, "ee" * 8, ok=False)
+    assert rec["traceId"] == "ab" * 16 and rec["spanId"] == "cd" * 8 and rec["parentSpanId"] == "ee" * 8
+    assert rec["startTimeUnixNano"] == "10" and rec["status"]["code"] == 2
+    assert {a["key"]: list(a["value"])[0] for a in rec["attributes"]} == {"n": "intValue", "f": "doubleValue", "s": "stringValue", "b": "boolValue"}
+
+    def free_port():
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        p = s.getsockname()[1]
+        s.close()
+        return p
+
+    async def go():
+        got = []
+
+        async def collect(req):
+            got.append(await req.json())
+            return web.json_response({})
+        capp = web.Application()
+        capp.router.add_post("/v1/traces", collect)
+        crun = web.AppRunner(capp, access_log=None)
+        await crun.setup()
+        cport = free_port()
+        await web.TCPSite(crun, "127.0.0.1", cport).start()
+
+        ports = [free_port(), free_port()]
+        stop, tasks = asyncio.Event(), []
+        for r in range(2):
+            ready = asyncio.Event()
+            tasks.append(asyncio.create_task(serve(StubBackend(r, 2, ready=True), "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            await ready.wait()
+        exp = SpanExporter(f"http://127.0.0.1:{cport}", "blitz.router", interval_s=0.1)
+        exp.start()
+        cfg = controller_config_from_cluster({"init_states": ["Prefill", "Decode"], "machines": [0, 0]}, 1, "impl_blitz,impl_nvl",
+                                             max_blocks_per_replica=4000, autoscale=False)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, exporter=exp)
+        lt = asyncio.create_task(rt.run())
+        lr = rt.submit(list(range(20)), 3, stream=False)
+        assert (await asyncio.wait_for(lr.done, 20)) is None
+        # CORS on the HTTP app
+        app = RouterApp(rt, model_name="tiny", cors_allow_origin=["http://ui.example"])
+        arun = web.AppRunner(app.app, access_log=None)
+        await arun.setup()
+        aport = free_port()
+        await web.TCPSite(arun, "127.0.0.1", aport).start()
+        import aiohttp
+        async with aiohttp.ClientSession() as s:
+            async with s.get(f"http://127.0.0.1:{aport}/info", headers={"Origin": "http://ui.example"}) as r:
+                assert r.status == 200 and r.headers["Access-Control-Allow-Origin"] == "http://ui.example"
+            async with s.get(f"http://127.0.0.1:{aport}/info", headers={"Origin": "http://other.example"}) as r:
+                assert r.status == 200 and "Access-Control-Allow-Origin" not in r.headers
+            async with s.options(f"http://127.0.0.1:{aport}/generate", headers={"Origin": "http://ui.example",
+                                                                                "Access-Control-Request-Headers": "content-type"}) as r:
+                assert r.status == 204 and r.headers["Access-Control-Allow-Headers"] == "content-type"
+            async with s.get(f"http://127.0.0.1:{aport}/metrics") as r:
+                assert "blitz_request_skipped_tokens_count" in await r.text()
+        await exp.stop()                                        # flushes
+        await rt.stop()
+        lt.cancel()
+        stop.set()
+        await asyncio.wait(tasks, timeout=5)
+        await arun.cleanup()
+        await crun.cleanup()
+        # the collector is gone now: export fails quietly and counts the loss
+        exp2 = SpanExporter(f"http://127.0.0.1:{cport}", interval_s=0.1)
+        exp2.span("late", "", 1.0, 2.0)
+        assert await exp2.flush() == 0 and exp2.dropped == 1
+        if exp2._session is not None:
+            await exp2._session.close()
+        return got, exp
+    got, exp = asyncio.run(go())
+    spans = [s for g in got for rs in g["resourceSpans"] for ss in rs["scopeSpans"] for s in ss["spans"]]
+    assert got[0]["resourceSpans"][0]["resource"]["attributes"][0]["value"]["stringValue"] == "blitz.router"
+    names = [s["name"] for s in spans]
+    assert {"Prefill", "Migrate", "Decode", "generate"} <= set(names) and exp.exported == len(spans) and exp.dropped == 0
+    assert len({s["traceId"] for s in spans}) == 1 and len({s["spanId"] for s in spans}) == len(spans)
+    gen = [s for s in spans if s["name"] == "generate"][0]
+    attrs = {a["key"]: a["value"] for a in gen["attributes"]}
+    assert attrs["generated_tokens"] == {"intValue": "3"} and attrs["input_tokens"] == {"intValue": "20"}
+    assert int(gen["endTimeUnixNano"]) > int(gen["startTimeUnixNano"])
+
+    # logging: JSON lines through the background file writer, level from LOG_LEVEL
+    saved = logging.getLogger().handlers[:], logging.getLogger().level
+    try:
+        os.environ["LOG_LEVEL"] = "warning"
+        listener = init_logging(None, True, str(tmp_path / "router.log"))
+        logging.getLogger("blitz.router").info("dropped by the filter")
+        logging.getLogger("blitz.router").warning("Replica<%d> Inactive => LoadingPrefill", 2)
+        listener.stop()
+        lines = [json.loads(l) for l in open(tmp_path / "router.log")]
+        assert len(lines) == 1 and lines[0]["level"] == "WARNING" and lines[0]["target"] == "blitz.router"
+        assert lines[0]["message"] == "Replica<2> Inactive => LoadingPrefill" and lines[0]["filename"].endswith(".py")
+        p = analysis.parse_router_log(open(tmp_path / "router.log"))
+        assert p["transitions"][0][1:] == (2, "Inactive", "LoadingPrefill") and p["transitions"][0][0] is not None
+    finally:
+        os.environ.pop("LOG_LEVEL", None)
+        root = logging.getLogger()
+        for h in root.handlers[:]:
+            root.removeHandler(h)
+        for h in saved[0]:
+            root.addHandler(h)
+        root.setLevel(saved[1])
+
+
+def test_router_flags_from_the_environment(monkeypatch):
+    from blitz_scale_b200.router.server import build_parser
+    monkeypatch.setenv("CLIENT_CONFIG", '["127.0.0.1:1"]')
+    monkeypatch.setenv("DEPLOYMENT_CONFIG_PATH", "/tmp/cluster.json")
+    monkeypatch.setenv("MAX_BEST_OF", "3")
+    monkeypatch.setenv("JSON_OUTPUT", "true")
+    monkeypatch.setenv("CORS_ALLOW_ORIGIN", "http://a,http://b")
+    monkeypatch.setenv("HOSTNAME", "some-container-name")
+    a = build_parser().parse_args(["--max-stop-sequences", "7", "--num-hidden-layers", "32", "--parameter-size", "16.0"])
+    assert a.client_config == '["127.0.0.1:1"]' and a.deployment_config_path == "/tmp/cluster.json"   # required ones too
+    assert a.max_best_of == 3 and a.json_output is True and a.cors_allow_origin == ["http://a", "http://b"]
+    assert a.max_stop_sequences == 7 and a.hostname == "127.0.0.1"          # the command line wins; HOSTNAME is ignored
+    monkeypatch.setenv("MAX_BEST_OF", "9")
+    assert build_parser().parse_args(["--max-best-of", "4"]).max_best_of == 4
