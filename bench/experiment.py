@@ -7,7 +7,8 @@ runner.py:124-790): a *template* lists models, datasets, feature sets and router
 `config-stubs.json`, starts workers (GPU workers under torch.distributed.run, or GPU-less stub workers),
 the router and the trace client, waits, tears down, summarises (`summary.json`) and appends its path to
 `checkpoint.txt` so `--checkpoint` skips finished instances.  `--dry-run` only writes the configs and the
-command lines.
+command lines.  `<out>/provenance/` records the commit, the uncommitted diff and small untracked files of the
+source tree the run used; the exit status is non-zero when an instance failed (see `<out>/error.log`).
 
     python bench/experiment.py --template bench/templates/cpu_plumbing.toml --out runs/ [--dry-run] [--force]
 """
@@ -18,6 +19,7 @@ import itertools
 import json
 import os
 import shlex
+import shutil
 import signal
 import subprocess
 import sys
@@ -192,6 +194,32 @@ def _terminate(signum, frame):
     raise KeyboardInterrupt      # run the `finally` blocks: the worker / router process groups must not outlive us
 
 
+def record_provenance(dest: Path, max_file_bytes: int = 1 << 20) -> None:
+    """What exactly ran: commit, branch and status, the uncommitted diff, and copies of small untracked files, so
+    that a result directory can be traced back to its source (the reference's harness archives the same,
+    scripts/batch/runner.py:60-121).  Best effort: outside a git checkout it only notes that."""
+    dest.mkdir(parents=True, exist_ok=True)
+
+    def git(*args):
+        r = subprocess.run(["git", "-C", str(ROOT), *args], capture_output=True, text=True, timeout=60)
+        if r.returncode != 0:
+            raise RuntimeError(r.stderr.strip() or "git failed")
+        return r.stdout
+    try:
+        info = "commit " + git("rev-parse", "HEAD").strip() + "\nbranch " + git("rev-parse", "--abbrev-ref", "HEAD").strip()
+        info += "\n\n" + git("status", "--short")
+        (dest / "git-info.txt").write_text(info)
+        (dest / "git-diff.patch").write_text(git("diff", "HEAD"))
+        for rel in git("ls-files", "--others", "--exclude-standard").splitlines():
+            src = ROOT / rel
+            if src.is_file() and src.stat().st_size <= max_file_bytes:
+                tgt = dest / "untracked" / rel
+                tgt.parent.mkdir(parents=True, exist_ok=True)
+                shutil.copy2(src, tgt)
+    except Exception as e:  # noqa: BLE001
+        (dest / "git-info.txt").write_text(f"no source provenance: {e}\n")
+
+
 def main():
     signal.signal(signal.SIGTERM, _terminate)
     ap = argparse.ArgumentParser()
@@ -208,6 +236,8 @@ def main():
     if a.force and ck.exists():
         ck.unlink()
     done = set(ck.read_text().split()) if ck.exists() else set()
+    if not a.dry_run:
+        record_provenance(out / "provenance")
     results = []
     for inst in expand(tpl):
         d = out / inst["tag"]
@@ -223,6 +253,8 @@ def main():
                 f.write(f"{inst['tag']}: {e}\n")
             results.append({"tag": inst["tag"], "error": str(e)})
     print(json.dumps(results, indent=1))
+    if any("error" in r for r in results):
+        sys.exit(1)
 
 
 if __name__ == "__main__":

@@ -294,6 +294,8 @@ def test_experiment_runs_processes_end_to_end(tmp_path):
     summary = json.load(open(d / "summary.json"))
     assert "slo" in summary
     assert "attached to a different loop" not in open(d / "router.log").read()
+    prov = tmp_path / "out" / "provenance"
+    assert (prov / "git-info.txt").exists()
 
 
 def test_heartbeat_failure_detector_marks_idle_replica_lost():
