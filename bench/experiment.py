@@ -187,6 +187,11 @@ def run_instance(inst: dict, d: Path, dry: bool) -> dict:
     summary = {"tag": inst["tag"], "slo": analysis.slo_table(recs), "scale_out": analysis.scale_out_latencies(log["transitions"]),
                "transitions": len(log["transitions"])}
     (d / "summary.json").write_text(json.dumps(summary, indent=1))
+    try:      # figures of the run (TTFT / TBT against the SLO lines, replica states, token rates)
+        from blitz_scale_b200.utils import plots
+        (d / "report.html").write_text(plots.report(open(d / "router.log", errors="ignore"), recs, inst["tag"]))
+    except Exception as e:  # noqa: BLE001 - a figure must not fail a finished run
+        print(f"report for {inst['tag']} not written: {e}", flush=True)
     return summary
 
 

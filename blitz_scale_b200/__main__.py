@@ -8,6 +8,8 @@
     repl          interactive gRPC client / load-latency / broadcast benchmark          -> utils.worker_client
     logs          log debuggers (merge, grep, zigzag, usage, migrations)                -> utils.logtools
     trace         trace-file tools (slice, scale, concat, stats, compare)               -> sim.trace_tools
+    report        figures of a run (TTFT / TBT vs SLO, replica states, token rates) as HTML -> utils.plots
+    chrome-trace  router log (+ client.jsonl) as a Chrome / Perfetto trace                  -> utils.tracing
     build         compile the kernel library and the native core                        -> build
 """
 import importlib
@@ -18,6 +20,7 @@ COMMANDS = {
     "router": "blitz_scale_b200.router.server", "client": "blitz_scale_b200.sim.request_sim",
     "convert": "blitz_scale_b200.models.convert", "repl": "blitz_scale_b200.utils.worker_client",
     "logs": "blitz_scale_b200.utils.logtools", "trace": "blitz_scale_b200.sim.trace_tools",
+    "report": "blitz_scale_b200.utils.plots", "chrome-trace": "blitz_scale_b200.utils.tracing",
     "build": "blitz_scale_b200.build",
 }
 

@@ -1,6 +1,8 @@
 """Hugging Face Llama-family checkpoint (.safetensors) -> weight-segment files, one per TP rank.
 
     python -m blitz_scale_b200.models.convert --src /path/to/hf_model --model llama3_8b --out /data/llama3_8b --tp 2
+    python -m blitz_scale_b200.models.convert --src /path/to/hf_model --list                      # tensor names, dtypes, shapes
+    python -m blitz_scale_b200.models.convert --src ... --model ... --out ... --tp 2 --verify     # re-read and compare
 
 What it does, like the reference's converter (scripts/util/make_dangertensors.py:9-30, 33-208): fixed tensor
 order, every 2-D projection transposed to ``[in, out]``, gate and up fused, shards cut by head / intermediate
@@ -132,15 +134,67 @@ def convert(src, model: str, out_dir, tp: int = 1, dtype=torch.bfloat16) -> List
     return paths
 
 
+def list_checkpoint(src) -> List[Tuple[str, str, Tuple[int, ...]]]:
+    """(name, dtype, shape) of every tensor of a checkpoint (the reference's read_safetensors helper)."""
+    r = CheckpointReader(src)
+    out = []
+    for n in sorted(r.names()):
+        info = r.files[r.where[n]].info(n)
+        out.append((n, info.dtype, tuple(info.shape)))
+    return out
+
+
+def verify(src, model: str, out_dir, tp: int = 1, dtype=torch.bfloat16) -> List[str]:
+    """Re-read the segment files under `out_dir` and compare every tensor of every TP rank with what the source
+    checkpoint says it should be (the reference's check_dangertensors helper).  Returns the list of problems."""
+    cfg = get_config(model)
+    full = hf_to_segment(CheckpointReader(src), cfg, dtype)
+    problems = []
+    d = Path(out_dir) / (f"tp{tp}" if tp > 1 else "")
+    for r in range(tp):
+        want = full if tp == 1 else shard_from_full(full, tp, r, device="cpu")
+        try:
+            path = WeightSegment.check_sidecar(d, cfg, tp, r, dtype)
+        except Exception as e:  # noqa: BLE001
+            problems.append(f"rank {r}: {e}")
+            continue
+        got = WeightSegment(cfg, tp, r, dtype)
+        n = got.layout.total_bytes
+        if path.stat().st_size != n:
+            problems.append(f"rank {r}: file has {path.stat().st_size} bytes, layout needs {n}")
+            continue
+        core.load_file_to_host(str(path), got.buffer.data_ptr(), n)
+        for name in want.names():
+            if not torch.equal(got[name], want[name]):
+                diff = (got[name].float() - want[name].float()).abs().max().item()
+                problems.append(f"rank {r}: {name} differs (max abs {diff:g})")
+    return problems
+
+
 def main(argv: Optional[Iterable[str]] = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--src", required=True, help="directory of .safetensors shards, or one file")
-    ap.add_argument("--model", required=True, help="registry name (llama3_8b, llama2_7b, mistral_24b, ...)")
-    ap.add_argument("--out", required=True)
+    ap.add_argument("--model", default="", help="registry name (llama3_8b, llama2_7b, mistral_24b, ...)")
+    ap.add_argument("--out", default="")
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--list", action="store_true", help="only list the tensors of the source checkpoint")
+    ap.add_argument("--verify", action="store_true", help="do not write: compare the segment files under --out with the source")
     a = ap.parse_args(argv)
-    for p in convert(a.src, a.model, a.out, a.tp, torch.bfloat16 if a.dtype == "bf16" else torch.float16):
+    if a.list:
+        for n, dt, shape in list_checkpoint(a.src):
+            print(f"{n}\t{dt}\t{list(shape)}")
+        return 0
+    if not a.model or not a.out:
+        ap.error("--model and --out are required")
+    dt = torch.bfloat16 if a.dtype == "bf16" else torch.float16
+    if a.verify:
+        problems = verify(a.src, a.model, a.out, a.tp, dt)
+        for p in problems:
+            print(p)
+        print("ok" if not problems else f"{len(problems)} problem(s)")
+        return 1 if problems else 0
+    for p in convert(a.src, a.model, a.out, a.tp, dt):
         print(p)
     return 0
 

@@ -112,6 +112,20 @@ def test_safetensors_reader_and_hf_conversion(tmp_path):
         WeightSegment.check_sidecar(p.parent, cfg, 2, r, torch.bfloat16)
     assert convert.main(["--src", str(tmp_path), "--model", "tiny", "--out", str(tmp_path / "cli")]) == 0
     assert (tmp_path / "cli" / "segment.0.bin").stat().st_size == seg.layout.total_bytes
+    # list and verify modes
+    listed = convert.list_checkpoint(tmp_path)
+    assert ("lm_head.weight", "BF16", (cfg.vocab, cfg.hidden)) in listed and len(listed) == 3 + 9 * cfg.layers
+    assert convert.main(["--src", str(tmp_path), "--list"]) == 0
+    assert convert.verify(tmp_path, "tiny", tmp_path / "out", tp=2) == []
+    assert convert.main(["--src", str(tmp_path), "--model", "tiny", "--out", str(tmp_path / "out"), "--tp", "2", "--verify"]) == 0
+    with open(paths[1], "r+b") as f:                       # flip one byte inside rank 1's first layer
+        f.seek(WeightSegment(cfg, 2, 1, device="meta").layout.unit("layer.0")[0] + 64)
+        b = f.read(1)
+        f.seek(-1, 1)
+        f.write(bytes([b[0] ^ 0x40]))
+    bad = convert.verify(tmp_path, "tiny", tmp_path / "out", tp=2)
+    assert len(bad) == 1 and bad[0].startswith("rank 1: layers.0.")
+    assert convert.main(["--src", str(tmp_path), "--model", "tiny", "--out", str(tmp_path / "out"), "--tp", "2", "--verify"]) == 1
     # a truncated file is rejected, not mis-read
     raw = (tmp_path / "model-00002-of-00002.safetensors").read_bytes()
     (tmp_path / "bad.safetensors").write_bytes(raw[:len(raw) // 2])

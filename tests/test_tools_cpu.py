@@ -325,3 +325,24 @@ def test_router_flags_from_the_environment(monkeypatch):
     assert a.max_stop_sequences == 7 and a.hostname == "127.0.0.1"          # the command line wins; HOSTNAME is ignored
     monkeypatch.setenv("MAX_BEST_OF", "9")
     assert build_parser().parse_args(["--max-best-of", "4"]).max_best_of == 4
+
+
+def test_run_report_figures(tmp_path):
+    from blitz_scale_b200.utils import plots
+    log = ["[0.000] Replica<0> boot => Prefill", "[0.000] Replica<1> boot => Decode",
+           "[1.500] Replica<2> Inactive => LoadingPrefill", "[1.530] Replica<2> LoadingPrefill => Prefill",
+           "[1.0] System Metrics: prefill_tokens: 0, decode_tokens: 0", "[2.0] System Metrics: prefill_tokens: 9000, decode_tokens: 700",
+           "[3.0] System Metrics: prefill_tokens: 30000, decode_tokens: 2100", "[3.2] Replica<2> Prefill => ShuttingPrefill"]
+    recs = [{"status": "ok", "s_time": 0.1 * i, "first_token_time": 40.0 + (500.0 if i == 7 else 0.0), "input_length": 200,
+             "max_time_between_tokens": 12.0 + (120.0 if i == 3 else 0.0)} for i in range(20)] + [{"status": "error", "s_time": 1.0}]
+    doc = plots.report(log, recs, "tiny <run>")
+    assert doc.count("<svg") == 4 and "tiny &lt;run&gt;" in doc
+    assert doc.count('fill="#d6453d" fill-opacity') == 2          # one TTFT violation, one TBT violation
+    assert "replica 2 in 30.0 ms" in doc and "replica 2: LoadingPrefill" in doc and "prefill" in doc
+    import xml.dom.minidom
+    for part in doc.split("<svg")[1:]:
+        xml.dom.minidom.parseString("<svg" + part.split("</svg>")[0] + "</svg>")      # every panel is well-formed
+    (tmp_path / "router.log").write_text("\n".join(log))
+    assert plots.main(["--router-log", str(tmp_path / "router.log"), "-o", str(tmp_path / "r.html")]) == 0
+    assert (tmp_path / "r.html").read_text().count("<svg") == 2   # without client records: states and token rates
+    assert plots._ticks(0.0, 10.0, 5) == [0.0, 2.0, 4.0, 6.0, 8.0, 10.0]
