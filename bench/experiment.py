@@ -181,6 +181,8 @@ def run_instance(inst: dict, d: Path, dry: bool) -> dict:
                 os.killpg(p.pid, signal.SIGKILL)
         for f in logs:
             f.close()
+        if not inst["global"].get("stub_workers", False):
+            wait_gpus_released(int(inst["global"].get("num_gpus", 2)))
     from blitz_scale_b200.utils import analysis
     recs = analysis.load_jsonl(str(d / "client.jsonl"))
     log = analysis.parse_router_log(open(d / "router.log", errors="ignore"))
@@ -197,6 +199,34 @@ def run_instance(inst: dict, d: Path, dry: bool) -> dict:
 
 def _terminate(signum, frame):
     raise KeyboardInterrupt      # run the `finally` blocks: the worker / router process groups must not outlive us
+
+
+def wait_gpus_released(num_gpus: int, timeout: float = 60.0, query=None) -> bool:
+    """After tearing a GPU instance down, wait until no compute process is left on the first `num_gpus` devices, so
+    that the next instance finds its memory free (the reference's runner polls the same before it goes on,
+    scripts/batch/runner.py:563-790).  Read-only NVML queries; `query(i)` -> number of compute processes on device
+    i can be injected for tests.  True when the devices are free (or cannot be inspected)."""
+    if query is None:
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+        except Exception:  # noqa: BLE001 - no driver here: nothing to wait for
+            return True
+
+        def query(i):
+            return len(pynvml.nvmlDeviceGetComputeRunningProcesses(pynvml.nvmlDeviceGetHandleByIndex(i)))
+    t0 = time.time()
+    while True:
+        try:
+            busy = [i for i in range(num_gpus) if query(i) > 0]
+        except Exception:  # noqa: BLE001
+            return True
+        if not busy:
+            return True
+        if time.time() - t0 > timeout:
+            print(f"GPUs {busy} still hold compute processes after {timeout:.0f} s", flush=True)
+            return False
+        time.sleep(0.5)
 
 
 def record_provenance(dest: Path, max_file_bytes: int = 1 << 20) -> None:

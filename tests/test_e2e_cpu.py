@@ -247,6 +247,16 @@ def test_experiment_runner_expansion_and_dry_run(tmp_path):
     cmds = json.load(open(d / "commands.json"))
     assert len(cmds["workers"]) == 3 and "request_sim" in cmds["client"] and "--features" in cmds["router"]
     assert json.load(open(d / "config-server.json"))["init_states"] == ["Prefill", "Decode", "Inactive"]
+    # waiting for the GPUs of a finished instance: a fake device query that frees up on the third poll
+    polls = []
+
+    def fake(i):
+        polls.append(i)
+        return 1 if len(polls) <= 4 and i == 1 else 0
+    assert experiment.wait_gpus_released(2, timeout=10.0, query=fake) and len(polls) >= 6
+    assert not experiment.wait_gpus_released(1, timeout=0.2, query=lambda i: 3)
+    experiment.record_provenance(tmp_path / "prov")
+    assert (tmp_path / "prov" / "git-info.txt").read_text()
 
 
 def test_log_analysis_and_sizing():
