@@ -256,6 +256,59 @@ def bench_rpc(quick: bool) -> dict:
             p.wait(timeout=10)
 
 
+def bench_decode_steps(quick: bool) -> dict:
+    """What the router's round trip costs a decode replica, and what several steps per call give back: stub workers
+    whose decode step sleeps 5 ms (a stand-in for the GPU time of one step), 64 requests decoding together."""
+    import subprocess
+    from blitz_scale_b200.router.runtime import RouterRuntime
+    from blitz_scale_b200.router.server import controller_config_from_cluster
+    from blitz_scale_b200.router.stub import WorkerStub
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ports = [_free_port() for _ in range(2)]
+    step_ms = 5.0
+    procs = [subprocess.Popen([sys.executable, "-m", "blitz_scale_b200.sim.stub_worker", "--rank", str(r), "--world", "2",
+                               "--port", str(ports[r]), "--decode-step-ms", str(step_ms), "--prefill-tokens-per-s", "1e12"],
+                              cwd=root, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL) for r in range(2)]
+
+    async def go():
+        for p in ports:
+            probe = WorkerStub(f"127.0.0.1:{p}")
+            for _ in range(200):
+                try:
+                    await probe.health(timeout=0.5)
+                    break
+                except Exception:  # noqa: BLE001
+                    await asyncio.sleep(0.1)
+            await probe.close()
+        out = {"simulated_step_ms": step_ms, "batch": 64}
+        n_tok = 48 if quick else 160
+        for k in (1, 2, 4, 8):
+            cfg = controller_config_from_cluster({"init_states": ["Prefill", "Decode"], "machines": [0, 0]}, 1,
+                                                 "impl_blitz,impl_nvl", max_blocks_per_replica=200000, autoscale=False)
+            rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, decode_steps=k)
+            lt = asyncio.create_task(rt.run())
+            lrs = [rt.submit(list(range(64)), n_tok, stream=False) for _ in range(64)]
+            for lr in lrs:
+                assert (await asyncio.wait_for(lr.done, timeout=300)) is None
+            # steady state: from the moment all 64 decode together to the last token
+            t_a = max(lr.times[1] for lr in lrs)
+            t_b = max(lr.times[-1] for lr in lrs)
+            toks = sum(sum(1 for t in lr.times if t > t_a) for lr in lrs)
+            out[f"ms_per_step_{k}_steps_per_call"] = round((t_b - t_a) * 1e3 / max(1, toks / 64), 3)
+            out[f"tokens_per_s_{k}_steps_per_call"] = round(toks / max(1e-9, t_b - t_a), 1)
+            await rt.stop()
+            lt.cancel()
+            await asyncio.sleep(0.2)
+        return out
+    try:
+        return asyncio.run(go())
+    finally:
+        for p in procs:
+            p.terminate()
+        for p in procs:
+            p.wait(timeout=10)
+
+
 def bench_http(quick: bool) -> dict:
     """The user-facing path: POST /generate against the router started from its command line (own process), two
     stub workers (own processes, zero simulated compute), a client with many requests in flight."""
@@ -316,10 +369,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--only", default="", help="comma list of: controller,queue,tokenizer,loader,rpc,http")
+    ap.add_argument("--only", default="", help="comma list of: controller,queue,tokenizer,loader,rpc,decode_steps,http")
     a = ap.parse_args()
     parts = {"controller": bench_controller, "queue": bench_queue, "tokenizer": bench_tokenizer, "loader": bench_loader,
-             "rpc": bench_rpc, "http": bench_http}
+             "rpc": bench_rpc, "decode_steps": bench_decode_steps, "http": bench_http}
     want = [p for p in a.only.split(",") if p] or list(parts)
     res = {"bench": "host", "cpus": os.cpu_count()}
     for name in want:

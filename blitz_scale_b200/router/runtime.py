@@ -64,8 +64,12 @@ class LiveRequest:
 class RouterRuntime:
     def __init__(self, cfg: "core.ControllerConfig", worker_urls: List[str], model_layers: int = 32,
                  model_path: str = "", stat_csv: str = "", health_interval_s: float = 0.0, health_misses: int = 2,
-                 rpc_timeout_s: float = 300.0, exporter=None):
+                 rpc_timeout_s: float = 300.0, exporter=None, decode_steps: int = 1):
         self.cfg = cfg
+        # decode steps a worker runs per DecodeV2 call.  1: every token makes the round trip through the router (the
+        # reference's behaviour).  k > 1: the round trip is paid once per k steps; tokens then arrive k at a time, and
+        # a batch that migrates in joins the running one up to k steps later.
+        self.decode_steps = max(1, int(decode_steps))
         # optional span sink (`utils.otlp.SpanExporter`): one span per dispatched operation and one per request
         self.exporter = exporter
         # failure detector: every `health_interval_s` each active replica's ranks are pinged with the Health RPC;
@@ -332,7 +336,7 @@ class RouterRuntime:
                 t.ids.extend(ft.get(rid, 0) for rid in cb.request_ids)
             lasts.append(t)
         ranks = self._ranks(a.replica)
-        res = (await self._all(ranks, [self.stubs[r].decode_v2(batches, lasts) for r in ranks]))[0]
+        res = (await self._all(ranks, [self.stubs[r].decode_v2(batches, lasts, self.decode_steps) for r in ranks]))[0]
         for bid in a.batch_ids:
             self.cached.pop((a.replica, bid), None)
         if res.HasField("batch"):

@@ -412,6 +412,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--health-misses", type=int, default=2, help="consecutive missed pings that declare a replica lost")
     ap.add_argument("--rpc-timeout-ms", type=float, default=300000.0,
                     help="deadline of every worker RPC; a reply that never comes then counts as a failed replica (0 = none)")
+    ap.add_argument("--decode-steps-per-call", type=int, default=1,
+                    help="decode steps a worker runs per DecodeV2 call (1 = one round trip per token, as the reference)")
     ap.add_argument("--max-incoming-migrations", type=int, default=1,
                     help="KV migrations in flight towards one decode replica at a time (1 = one at a time, as the reference)")
     ap.add_argument("--quarantine-ms", type=float, default=5000.0,
@@ -485,7 +487,7 @@ def main(argv=None) -> None:
             exporter.start()
         rt = RouterRuntime(cfg, urls, model_layers=layers, model_path=a.model_path, stat_csv=a.statistic_csv,
                            health_interval_s=a.health_interval_ms * 1e-3, health_misses=a.health_misses,
-                           rpc_timeout_s=a.rpc_timeout_ms * 1e-3, exporter=exporter)
+                           rpc_timeout_s=a.rpc_timeout_ms * 1e-3, exporter=exporter, decode_steps=a.decode_steps_per_call)
         stop = asyncio.Event()
         for sig in (signal.SIGINT, signal.SIGTERM):
             asyncio.get_running_loop().add_signal_handler(sig, stop.set)

@@ -104,8 +104,14 @@ class WorkerStub:
             r.pp_info.CopyFrom(pp_info)
         return await self.call("ZagPrefill", r)
 
-    async def decode_v2(self, batches, last_iter_tokens):
-        return await self.call("DecodeV2", pb.DecodeV2Request(batches=list(batches), last_iter_tokens=list(last_iter_tokens)))
+    async def decode_v2(self, batches, last_iter_tokens, steps: int = 1):
+        """`steps` > 1: the worker runs up to that many decode steps in this call (asked for in the call's metadata;
+        the request message of the contract stays as it is) and returns every step's generations in order."""
+        req = pb.DecodeV2Request(batches=list(batches), last_iter_tokens=list(last_iter_tokens))
+        if steps <= 1:
+            return await self.call("DecodeV2", req)
+        md = tuple(grpc_metadata(CURRENT_TRACE.get()) or ()) + (("x-decode-steps", str(int(steps))),)
+        return await self.call("DecodeV2", req, metadata=md)
 
     async def relay(self, rank: int, relax_not_head: bool):
         return await self.call("Relay", pb.RelayRequest(rank=rank, relax_not_head=relax_not_head))

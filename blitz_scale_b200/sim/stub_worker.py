@@ -155,7 +155,16 @@ class StubBackend(Backend):
                 ev.set()
             return r.batch_id, r.seq_num
 
-    def decode(self, batches, last_iter_tokens):
+    def decode(self, batches, last_iter_tokens, steps: int = 1):
+        gens, cb = self._decode_once(batches, last_iter_tokens)
+        for _ in range(1, max(1, steps)):
+            if cb is None:
+                break
+            more, cb = self._decode_once([cb], [])
+            gens += more
+        return gens, cb
+
+    def _decode_once(self, batches, last_iter_tokens):
         with self.lock:
             # tokens produced by prefill elsewhere travel with a migrated batch and are appended before the
             # first decode step here (src/service/service.cc:657-679); then all batches merge into the first

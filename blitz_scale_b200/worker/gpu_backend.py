@@ -175,7 +175,10 @@ class GpuBackend(Backend):
         b.decode = True
         return out
 
-    def decode(self, batches, last_iter_tokens):
+    def decode(self, batches, last_iter_tokens, steps: int = 1):
+        """One decode step of the merged batches; with `steps` > 1 up to that many steps back to back (the generations
+        of all steps come back in step order), which takes the router's round trip out of the time between steps.
+        The lock is released between steps so that other calls (a prefill here, the set-up of a migration) get in."""
         with self.lock:
             for i, cb in enumerate(batches):
                 ids = list(last_iter_tokens[i].ids) if i < len(last_iter_tokens) else []
@@ -187,7 +190,16 @@ class GpuBackend(Backend):
                 b.extend(self.batches.pop(cb.id))
             toks = self.engine.decode(b)
             gens, cb = self._finish_step(b, toks)
-            return gens, cb
+        for _ in range(1, max(1, steps)):
+            if cb is None:
+                break
+            with self.lock:
+                if self.batches.get(b.id) is not b:       # cleared or migrated away in between
+                    break
+                toks = self.engine.decode(b)
+                more, cb = self._finish_step(b, toks)
+            gens += more
+        return gens, cb
 
     def clear_cache(self, batch_id):
         with self.lock:

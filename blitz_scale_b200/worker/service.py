@@ -152,7 +152,15 @@ class TextGenerationService:
     async def DecodeV2(self, req, ctx):
         t0 = time.perf_counter_ns()
         try:
-            gens, cb = await self._call(self.b.decode, list(req.batches), list(req.last_iter_tokens))
+            # "x-decode-steps: k" in the call's metadata asks for up to k steps in this one call
+            steps = 1
+            for k, v in (ctx.invocation_metadata() or ()):
+                if k == "x-decode-steps":
+                    steps = max(1, min(64, int(v)))
+            if steps > 1:
+                gens, cb = await self._call(self.b.decode, list(req.batches), list(req.last_iter_tokens), steps)
+            else:
+                gens, cb = await self._call(self.b.decode, list(req.batches), list(req.last_iter_tokens))
         except Exception as e:  # noqa: BLE001
             return await self._abort(ctx, e)
         r = _response(pb.DecodeV2Response, gens, total_ns=time.perf_counter_ns() - t0)

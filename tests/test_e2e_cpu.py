@@ -467,3 +467,39 @@ def test_nothing_is_left_behind_after_many_requests():
         await _shutdown(stop, tasks)
         return state
     assert asyncio.run(go()) == (0, 0, 0, 0, 0, 0, True, [0, 0, 0], [0, 0, 0])
+
+
+def test_several_decode_steps_per_call_give_the_same_tokens():
+    """With k decode steps per DecodeV2 call the token streams are those of one step per call; tokens arrive up to k
+    at a time, requests still stop at their own length, and nothing is left behind."""
+    async def run(k):
+        ports = _free_ports(2)
+        stop, tasks = asyncio.Event(), []
+        backends = [StubBackend(r, 2, ready=True, seed=5) for r in range(2)]
+        for r, b in enumerate(backends):
+            ready = asyncio.Event()
+            tasks.append(asyncio.create_task(serve(b, "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            await ready.wait()
+        cfg = controller_config_from_cluster({"init_states": ["Prefill", "Decode"], "machines": [0, 0]}, 1, "impl_blitz,impl_nvl",
+                                             max_blocks_per_replica=4000, autoscale=False)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, decode_steps=k)
+        lt = asyncio.create_task(rt.run())
+        lrs = [rt.submit(list(range(10 + i)), 3 + 2 * i, stream=False) for i in range(6)]     # lengths 3, 5, ..., 13
+        for lr in lrs:
+            assert (await asyncio.wait_for(lr.done, 30)) is None
+        for _ in range(100):
+            if rt.ctl.idle() and not rt.cached and all(not b.batches for b in backends):
+                break
+            await asyncio.sleep(0.05)
+        left = (len(rt.cached), rt.ctl.total_used_blocks(), [len(b.batches) for b in backends], [b.pool.used_pages for b in backends])
+        await rt.stop()
+        lt.cancel()
+        stop.set()
+        await asyncio.wait(tasks, timeout=5)
+        return [list(lr.tokens) for lr in lrs], [list(lr.times) for lr in lrs], left
+    one, _, left1 = asyncio.run(run(1))
+    four, times4, left4 = asyncio.run(run(4))
+    assert [len(t) for t in one] == [3, 5, 7, 9, 11, 13] and four == one
+    assert left1 == left4 == (0, 0, [0, 0], [0, 0])
+    bursts = max(sum(1 for a, b in zip(ts, ts[1:]) if a == b) for ts in times4)
+    assert bursts >= 6                                   # the longest request got most of its tokens in groups
