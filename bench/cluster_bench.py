@@ -56,6 +56,8 @@ def main():
     ap.add_argument("--autoscale", action="store_true", help="let the planner decide when and how far to scale (no manual trigger)")
     ap.add_argument("--prefill-rate", type=float, default=60000.0, help="autoscale: prefill tokens/s one replica sustains")
     ap.add_argument("--horizon-ms", type=float, default=100.0, help="autoscale: queue the planner tolerates, as time")
+    ap.add_argument("--decode-steps", type=int, default=1, help="decode steps per DecodeV2 call")
+    ap.add_argument("--max-incoming-migrations", type=int, default=1, help="KV migrations in flight per decode replica")
     ap.add_argument("--port", type=int, default=50600)
     ap.add_argument("--json", default="")
     a = ap.parse_args()
@@ -139,6 +141,7 @@ def run_router(a, world, states, cfg_model, backend):
     cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
                                          max_blocks_per_replica=a.pages - 64, block_size=64, max_prefill_tokens=8192,
                                          model_layers=cfg_model.layers, **extra)
+    cfg.max_incoming_migrations = max(1, a.max_incoming_migrations)
     g = torch.Generator().manual_seed(5)
     n_base, n_burst = int(a.base_rate * a.base_s), int(a.burst_rate * a.burst_s)
     arrivals = [i / a.base_rate for i in range(n_base)] + [a.base_s + i / a.burst_rate for i in range(n_burst)]
@@ -146,7 +149,7 @@ def run_router(a, world, states, cfg_model, backend):
 
     async def go():
         rt = RouterRuntime(cfg, [f"127.0.0.1:{a.port + r}" for r in range(world)], model_layers=cfg_model.layers,
-                           model_path=a.model_path)
+                           model_path=a.model_path, decode_steps=a.decode_steps)
         loop_task = asyncio.create_task(rt.run())
         # warm both serving replicas (graph capture, first-use work) outside the measurement
         warm = rt.submit(prompts[0], 4)
@@ -204,7 +207,8 @@ def run_router(a, world, states, cfg_model, backend):
     out = {"bench": "cluster_scale_out", "model": a.model, "mode": a.mode + ("+autoscale" if getattr(a, "autoscale", False) else ""),
            "gpus": world, "requests": len(records),
            "failed": len(records) - len(ok), "prompt_len": a.prompt_len, "new_tokens": a.new_tokens,
-           "base_rate": a.base_rate, "burst_rate": a.burst_rate,
+           "base_rate": a.base_rate, "burst_rate": a.burst_rate, "decode_steps_per_call": a.decode_steps,
+           "max_incoming_migrations": a.max_incoming_migrations, "precapture": bool(a.precapture),
            "scale_out_latency_ms": {str(r): round(v * 1e3, 2) for r, v in sorted(scale["serving"].items())},
            "fully_loaded_ms": {str(r): round(v * 1e3, 2) for r, v in sorted(scale["loaded"].items())},
            "param_gb_per_replica": round(seg_bytes / 1e9, 3),
