@@ -101,9 +101,12 @@ class SpanExporter:
             await self.flush()
             raise
         finally:
-            if self._session is not None:
-                await self._session.close()
-                self._session = None
+            await self.close()
+
+    async def close(self) -> None:
+        if self._session is not None:
+            await self._session.close()
+            self._session = None
 
     def start(self) -> None:
         self._task = asyncio.get_running_loop().create_task(self.run())
@@ -116,6 +119,7 @@ class SpanExporter:
             except asyncio.CancelledError:
                 pass
             self._task = None
+        await self.close()
 
 
 # ---------------------------------------------------------------------------------------------- logging

@@ -274,8 +274,7 @@ def test_otlp_span_export_logging_and_cors(tmp_path):
         exp2 = SpanExporter(f"http://127.0.0.1:{cport}", interval_s=0.1)
         exp2.span("late", "", 1.0, 2.0)
         assert await exp2.flush() == 0 and exp2.dropped == 1
-        if exp2._session is not None:
-            await exp2._session.close()
+        await exp2.close()
         return got, exp
     got, exp = asyncio.run(go())
     spans = [s for g in got for rs in g["resourceSpans"] for ss in rs["scopeSpans"] for s in ss["spans"]]
