@@ -307,6 +307,13 @@ class Controller {
     if (ops_.count(op_id)) lose_replica(issued_to, now);  // the named replica was no participant after all
   }
 
+  // A shell with a failure detector reports whether a replica that is out of service answers again; the planner
+  // loads into a lost replica only once it does (and its quarantine has passed).
+  void set_reachable(int replica, bool ok) {
+    if (replica >= 0 && replica < num_replicas()) reps_[replica].reachable = ok;
+  }
+  bool reachable(int replica) const { return replica >= 0 && replica < num_replicas() && reps_[replica].reachable; }
+
   // Failure detector verdict (missed heartbeats): the replica is gone even if no operation was in flight on it.
   bool on_replica_unhealthy(int replica, double now) {
     if (replica < 0 || replica >= num_replicas() || reps_[replica].m.state == RState::Inactive) return false;
@@ -419,6 +426,7 @@ class Controller {
     ReplicaMetric m;
     bool colocated = false;
     double lost_at = -1e18;   // when the replica was last declared lost
+    bool reachable = true;    // failure detector's view (a shell without a detector leaves it true)
     bool busy = false;        // an inference RPC is in flight
     bool migrating = false;   // this source has a migration in flight
     bool relay_wait = false;  // OldPrefill parked in the relay queue
@@ -882,7 +890,9 @@ class Controller {
     if (dd < 0 && now - down_since_d_ >= patience) scale_down(false, now);
   }
 
-  bool quarantined(int r, double now) const { return (now - reps_[r].lost_at) * 1e3 < cfg_.quarantine_ms; }
+  bool quarantined(int r, double now) const {
+    return !reps_[r].reachable || (now - reps_[r].lost_at) * 1e3 < cfg_.quarantine_ms;
+  }
   bool no_decode_side() const {
     return num_in_state(RState::Decode) + num_in_state(RState::AusDecode) + num_in_state(RState::MutatingToDecode) +
                num_in_state(RState::LoadingDecode) == 0;

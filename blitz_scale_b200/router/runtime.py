@@ -133,6 +133,16 @@ class RouterRuntime:
             for rep in range(self.ctl.num_replicas):
                 if self.ctl.state_name(rep) == "Inactive":
                     self._missed.pop(rep, None)
+                    if not self.ctl.reachable(rep):
+                        # a lost replica is pinged until it answers again (a restarted worker); only then may the
+                        # planner load into it
+                        try:
+                            await asyncio.wait_for(asyncio.gather(*[self.stubs[r].health(timeout=self.health_interval_s)
+                                                                    for r in self._ranks(rep)]), timeout=self.health_interval_s)
+                            log.info("replica %d answers again", rep)
+                            self.ctl.set_reachable(rep, True)
+                        except Exception:  # noqa: BLE001
+                            pass
                     continue
                 try:
                     await asyncio.wait_for(asyncio.gather(*[self.stubs[r].health(timeout=self.health_interval_s)
@@ -143,6 +153,7 @@ class RouterRuntime:
                     if self._missed[rep] >= self.health_misses:
                         log.error("replica %d missed %d heartbeats: declared lost", rep, self._missed[rep])
                         self.ctl.on_replica_unhealthy(rep, self.now())
+                        self.ctl.set_reachable(rep, False)
                         self._missed[rep] = 0
                         self.wake.set()
 
@@ -287,6 +298,8 @@ class RouterRuntime:
             log.error("RPC for %s on replica %d failed (replica %d is taken as lost): %s", a.type.name, a.replica, blamed, e)
             if a.op_id:
                 self.ctl.on_failure(a.op_id, self.now(), blamed)
+                if self.health_interval_s > 0 and isinstance(e, RankFailure) and self.ctl.state_name(blamed) == "Inactive":
+                    self.ctl.set_reachable(blamed, False)       # the detector will say when it answers again
         if self.exporter is not None:
             self.exporter.span(a.type.name, tp, t0, time.time(), replica=a.replica, peer=a.peer, batch_id=int(a.batch_id),
                                requests=len(a.request_ids), ok=ok, parent_span_id=self.root_trace.split("-")[2])

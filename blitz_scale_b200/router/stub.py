@@ -47,8 +47,13 @@ class WorkerStub:
         answers then surfaces as DEADLINE_EXCEEDED instead of an operation that stays in flight for ever."""
         self.url = url
         self.default_timeout = default_timeout if default_timeout and default_timeout > 0 else None
+        # short reconnect back-off: a worker that was restarted is reachable again within a second, while calls to
+        # one that is away still fail at once (no wait-for-ready), which is what the failure handling relies on
         self.channel = grpc.aio.insecure_channel(url, options=[("grpc.max_receive_message_length", 256 << 20),
-                                                               ("grpc.max_send_message_length", 256 << 20)])
+                                                               ("grpc.max_send_message_length", 256 << 20),
+                                                               ("grpc.initial_reconnect_backoff_ms", 100),
+                                                               ("grpc.min_reconnect_backoff_ms", 100),
+                                                               ("grpc.max_reconnect_backoff_ms", 1000)])
         self._m = {}
         for rpc, (req, res) in RPCS.items():
             des = _wire_deserializer(getattr(pb, res)) if rpc in _KEEP_WIRE else getattr(pb, res).FromString

@@ -503,3 +503,59 @@ def test_several_decode_steps_per_call_give_the_same_tokens():
     assert left1 == left4 == (0, 0, [0, 0], [0, 0])
     bursts = max(sum(1 for a, b in zip(ts, ts[1:]) if a == b) for ts in times4)
     assert bursts >= 6                                   # the longest request got most of its tokens in groups
+
+
+def test_restarted_stub_worker_is_readmitted():
+    """A worker goes away, is declared lost by the heartbeat detector, comes back on the same port (a restart) and is
+    scaled in again: the router's channel reconnects and the replica serves."""
+    async def go():
+        ports = _free_ports(3)
+        stops, tasks = [], []
+        states = ["Prefill", "Decode", "Prefill"]
+
+        async def start(r, ready_flag):
+            ready, stop = asyncio.Event(), asyncio.Event()
+            t = asyncio.create_task(serve(StubBackend(r, 3, ready=ready_flag, load_s=0.05), "127.0.0.1", ports[r],
+                                          stop_event=stop, ready_event=ready))
+            await ready.wait()
+            return stop, t
+        for r in range(3):
+            s, t = await start(r, True)
+            stops.append(s)
+            tasks.append(t)
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * 3}, 1, "impl_blitz,impl_nvl,manually_scale",
+                                             max_blocks_per_replica=4000)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, health_interval_s=0.1, health_misses=2)
+        lt = asyncio.create_task(rt.run())
+        stops[2].set()
+        await asyncio.wait([tasks[2]], timeout=5)
+        for _ in range(80):
+            await asyncio.sleep(0.1)
+            if rt.ctl.state_name(2) == "Inactive":
+                break
+        assert rt.ctl.state_name(2) == "Inactive" and not rt.ctl.reachable(2)
+        stops[2], tasks[2] = await start(2, False)               # the restarted worker: same port, no parameters yet
+        for _ in range(100):                                     # the detector keeps pinging; the channel reconnects (<= 1 s)
+            if rt.ctl.reachable(2):
+                break
+            await asyncio.sleep(0.1)
+        assert rt.ctl.reachable(2)
+        assert rt.ctl.manual_scale(2, "Prefill", rt.now())
+        rt.wake.set()
+        for _ in range(80):
+            await asyncio.sleep(0.1)
+            if rt.ctl.state_name(2) == "Prefill":
+                break
+        assert rt.ctl.state_name(2) == "Prefill"
+        served = set()
+        for i in range(8):                                       # both prefill replicas take work again
+            lr = rt.submit(list(range(30)), 2, stream=False)
+            assert (await asyncio.wait_for(lr.done, 20)) is None
+        served = {l.split(">")[0][-1] for _, l in rt.transitions}
+        await rt.stop()
+        lt.cancel()
+        for s in stops:
+            s.set()
+        await asyncio.wait(tasks, timeout=5)
+        return served
+    assert "2" in asyncio.run(go())

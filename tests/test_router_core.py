@@ -441,8 +441,11 @@ def test_lost_role_is_restored_and_lost_replica_is_quarantined():
     ctl.on_prefill_done(pf[0].op_id, [core.TokenOut(5, 1, False)], 0.05)
     dec = [a for a in ctl.step(0.06) if a.type == core.ActionType.Decode]
     assert len(dec) == 1 and dec[0].replica == 1
-    # after the quarantine the lost replica may be tried again
+    # after the quarantine the lost replica may be tried again, unless a failure detector says it is still away
     assert not [a for a in ctl.step(0.5) if a.type == core.ActionType.NvlBroadcast]
+    ctl.set_reachable(0, False)
+    assert not [a for a in ctl.step(1.1) if a.type in (core.ActionType.NvlBroadcast, core.ActionType.RdmaBroadcast)]
+    ctl.set_reachable(0, True)
     again = [a for a in ctl.step(1.2) if a.type in (core.ActionType.NvlBroadcast, core.ActionType.RdmaBroadcast)]
     assert len(again) == 1 and again[0].dst_ranks == [0]
 
