@@ -154,6 +154,7 @@ class RouterRuntime:
                         log.error("replica %d missed %d heartbeats: declared lost", rep, self._missed[rep])
                         self.ctl.on_replica_unhealthy(rep, self.now())
                         self.ctl.set_reachable(rep, False)
+                        self._purge_replica(rep)
                         self._missed[rep] = 0
                         self.wake.set()
 
@@ -260,6 +261,19 @@ class RouterRuntime:
                    A.SetStatusReady: self._do_simple, A.ClearCache: self._do_simple}[t]
         self._spawn(self._guard(a, handler))
 
+    def _purge_replica(self, rep: int) -> None:
+        """Forget what the runtime remembers about batches on a replica that was lost."""
+        for k in [k for k in self.cached if k[0] == rep]:
+            del self.cached[k]
+        held = {k[1] for k in self.cached}
+        for b in [b for b in self.first_tokens if b not in held]:
+            del self.first_tokens[b]
+
+    def _remember(self, replica: int, batch) -> None:
+        """Keep a worker's handle of a resident batch, unless the replica was lost while the call was in flight."""
+        if self.ctl.state_name(replica) != "Inactive":
+            self.cached[(replica, batch.id)] = batch
+
     def _deliver_one(self, rid: int, token: int, final: bool, now: float) -> None:
         lr = self.requests.get(rid)
         if lr is None:
@@ -298,6 +312,9 @@ class RouterRuntime:
             log.error("RPC for %s on replica %d failed (replica %d is taken as lost): %s", a.type.name, a.replica, blamed, e)
             if a.op_id:
                 self.ctl.on_failure(a.op_id, self.now(), blamed)
+                for rep in range(self.ctl.num_replicas):
+                    if self.ctl.state_name(rep) == "Inactive":
+                        self._purge_replica(rep)
                 if self.health_interval_s > 0 and isinstance(e, RankFailure) and self.ctl.state_name(blamed) == "Inactive":
                     self.ctl.set_reachable(blamed, False)       # the detector will say when it answers again
         if self.exporter is not None:
@@ -328,9 +345,9 @@ class RouterRuntime:
             self._zag_pp[a.batch_id] = res.pp_info.tfm_layer if which == "tfm_layer" else 0
             return
         if res.HasField("batch"):
-            self.cached[(a.replica, a.batch_id)] = res.batch
+            self._remember(a.replica, res.batch)
         ids, toks, fins = core.parse_generations(res.raw)
-        if res.HasField("batch"):      # somebody will decode this batch: its first tokens travel with the first step
+        if (a.replica, a.batch_id) in self.cached:      # somebody will decode this batch: its first tokens travel with the first step
             self.first_tokens[a.batch_id] = {i: t for i, t in zip(ids, toks) if t >= 0}
         now = self.now()
         self.ctl.on_prefill_done_lists(a.op_id, ids, toks, fins, now)
@@ -353,7 +370,7 @@ class RouterRuntime:
         for bid in a.batch_ids:
             self.cached.pop((a.replica, bid), None)
         if res.HasField("batch"):
-            self.cached[(a.replica, res.batch.id)] = res.batch
+            self._remember(a.replica, res.batch)
         now = self.now()
         self.ctl.on_decode_done_wire(a.op_id, res.raw, now)
         self._deliver(now)          # straight away: the next step of the loop may be a tick away
@@ -366,7 +383,7 @@ class RouterRuntime:
                 [self.stubs[r].immigrate(batch, src, dst, partial, a.num_layer) for r in dst]
         res = await self._all(src + dst, calls)
         self.cached.pop((a.replica, a.batch_id), None)
-        self.cached[(a.peer, a.batch_id)] = res[-1].batch
+        self._remember(a.peer, res[-1].batch)
         self.ctl.on_migrate_done(a.op_id, self.now())
 
     async def _do_relay(self, a) -> None:

@@ -559,3 +559,79 @@ def test_restarted_stub_worker_is_readmitted():
         await asyncio.wait(tasks, timeout=5)
         return served
     assert "2" in asyncio.run(go())
+
+
+def test_chaos_workers_fail_and_return_while_requests_flow():
+    """Workers are stopped and restarted at random while requests flow (host-side failures only).  Every request
+    either completes with exactly its tokens or fails with an error, nothing hangs, and once things are quiet the
+    runtime, the core and the surviving workers hold nothing."""
+    import random
+    rng = random.Random(int(os.environ.get("BLITZ_CHAOS_SEED", "7")))
+
+    async def go():
+        n = 4
+        ports = _free_ports(n)
+        states = ["Prefill", "Decode", "Prefill", "Decode"]
+        backends, stops, tasks = [None] * n, [None] * n, [None] * n
+
+        async def start(r, ready_flag):
+            ready, stop = asyncio.Event(), asyncio.Event()
+            backends[r] = StubBackend(r, n, ready=ready_flag, load_s=0.02, decode_step_s=0.001)
+            tasks[r] = asyncio.create_task(serve(backends[r], "127.0.0.1", ports[r], stop_event=stop, ready_event=ready))
+            stops[r] = stop
+            await ready.wait()
+        for r in range(n):
+            await start(r, True)
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n}, 1, "impl_blitz,impl_nvl",
+                                             max_blocks_per_replica=4000, tokens_prefilled_per_sec=2000, min_prefill=1,
+                                             min_decode=1, max_prefill=3, max_decode=3)
+        cfg.quarantine_ms = 200.0
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, health_interval_s=0.05, health_misses=2,
+                           rpc_timeout_s=2.0)
+        lt = asyncio.create_task(rt.run())
+        results = []
+
+        async def client(i):
+            await asyncio.sleep(rng.random() * 3.0)
+            want = 1 + i % 9
+            lr = rt.submit(list(range(5 + i % 40)), want, stream=False)
+            err = await asyncio.wait_for(lr.done, timeout=60)
+            results.append((err, len(lr.tokens), want))
+
+        async def chaos():
+            down = None
+            for _ in range(6):
+                await asyncio.sleep(0.4)
+                if down is None:
+                    down = rng.choice([1, 2, 3])
+                    stops[down].set()
+                    await asyncio.wait([tasks[down]], timeout=5)
+                else:
+                    await start(down, False)
+                    down = None
+            if down is not None:
+                await start(down, False)
+        await asyncio.gather(chaos(), *[client(i) for i in range(120)])
+        for _ in range(200):
+            if rt.ctl.idle() and not rt.requests:
+                break
+            await asyncio.sleep(0.05)
+        await asyncio.sleep(0.3)
+        alive = [r for r in range(n) if rt.ctl.state_name(r) != "Inactive"]
+        left = {"requests": len(rt.requests), "cached": len(rt.cached), "first_tokens": len(rt.first_tokens),
+                "finished": len(rt.ctl.finished()), "ops": rt.ctl.inflight_ops(), "blocks": rt.ctl.total_used_blocks(),
+                "idle": rt.ctl.idle(), "worker_batches": [len(backends[r].batches) for r in alive],
+                "worker_pages": [backends[r].pool.used_pages for r in alive]}
+        await rt.stop()
+        lt.cancel()
+        for s in stops:
+            s.set()
+        await asyncio.wait([t for t in tasks if t is not None], timeout=5)
+        return results, left, alive
+    results, left, alive = asyncio.run(go())
+    assert len(results) == 120
+    done = [r for r in results if r[0] is None]
+    assert all(got == want for _, got, want in done) and len(done) >= 60
+    assert all(err == "replica lost" for err, _, _ in results if err is not None)
+    assert left == {"requests": 0, "cached": 0, "first_tokens": 0, "finished": 0, "ops": 0, "blocks": 0, "idle": True,
+                    "worker_batches": [0] * len(alive), "worker_pages": [0] * len(alive)}, left
