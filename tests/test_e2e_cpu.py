@@ -582,7 +582,8 @@ def test_chaos_workers_fail_and_return_while_requests_flow():
             await ready.wait()
         for r in range(n):
             await start(r, True)
-        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n}, 1, "impl_blitz,impl_nvl",
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n}, 1,
+                                             os.environ.get("BLITZ_CHAOS_FEATURES", "impl_blitz,impl_nvl"),
                                              max_blocks_per_replica=4000, tokens_prefilled_per_sec=2000, min_prefill=1,
                                              min_decode=1, max_prefill=3, max_decode=3)
         cfg.quarantine_ms = 200.0
