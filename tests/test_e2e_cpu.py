@@ -636,3 +636,57 @@ def test_chaos_workers_fail_and_return_while_requests_flow():
     assert all(err == "replica lost" for err, _, _ in results if err is not None)
     assert left == {"requests": 0, "cached": 0, "first_tokens": 0, "finished": 0, "ops": 0, "blocks": 0, "idle": True,
                     "worker_batches": [0] * len(alive), "worker_pages": [0] * len(alive)}, left
+
+
+def test_new_replica_dies_while_serving_during_its_load():
+    """Live scaling: the new prefill replica serves while its parameters stream in, then its worker goes away in the
+    middle.  Prompts it held go back to the queue and finish elsewhere, relayed batches fail cleanly, the helper
+    replica returns to ordinary prefill, nothing hangs."""
+    async def go():
+        n = 3
+        ports = _free_ports(n)
+        states = ["Prefill", "Decode", "Inactive"]
+        backends, stops, tasks = [], [], []
+        for r in range(n):
+            ready, stop = asyncio.Event(), asyncio.Event()
+            b = StubBackend(r, n, ready=states[r] != "Inactive", load_s=1.5, decode_step_s=0.001, prefill_tokens_per_s=20000)
+            backends.append(b)
+            tasks.append(asyncio.create_task(serve(b, "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            stops.append(stop)
+            await ready.wait()
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n}, 1,
+                                             "impl_blitz,impl_nvl,impl_live,manually_scale", max_blocks_per_replica=4000)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, rpc_timeout_s=3.0)
+        lt = asyncio.create_task(rt.run())
+        results = []
+
+        async def client(i):
+            await asyncio.sleep(0.02 * i)
+            lr = rt.submit(list(range(200 + i)), 3, stream=False)
+            err = await asyncio.wait_for(lr.done, timeout=60)
+            results.append((err, len(lr.tokens)))
+        cl = [asyncio.create_task(client(i)) for i in range(60)]
+        await asyncio.sleep(0.1)
+        assert rt.ctl.manual_scale(2, "Prefill", rt.now())
+        rt.wake.set()
+        await asyncio.sleep(0.4)
+        seen_new = rt.ctl.state_name(2)
+        stops[2].set()                                           # the new replica's worker goes away mid-load
+        await asyncio.gather(*cl)
+        for _ in range(100):
+            if rt.ctl.idle() and not rt.requests:
+                break
+            await asyncio.sleep(0.05)
+        final = ([rt.ctl.state_name(r) for r in range(n)], rt.ctl.idle(), rt.ctl.total_used_blocks(), len(rt.cached),
+                 [len(backends[r].batches) for r in (0, 1)], [backends[r].pool.used_pages for r in (0, 1)])
+        await rt.stop()
+        lt.cancel()
+        for s in stops:
+            s.set()
+        await asyncio.wait(tasks, timeout=5)
+        return results, seen_new, final
+    results, seen_new, final = asyncio.run(go())
+    assert seen_new == "NewPrefill"
+    assert len(results) == 60 and all((err is None and k == 3) or err == "replica lost" for err, k in results)
+    assert sum(1 for err, _ in results if err is None) >= 40
+    assert final == (["Prefill", "Decode", "Inactive"], True, 0, 0, [0, 0], [0, 0]), final
