@@ -102,7 +102,8 @@ void bind_router(py::module_& m) {
       .value("Relay", ActionType::Relay).value("NvlBroadcast", ActionType::NvlBroadcast).value("TanzBroadcast", ActionType::TanzBroadcast)
       .value("RdmaBroadcast", ActionType::RdmaBroadcast).value("LoadParams", ActionType::LoadParams)
       .value("ResetStatus", ActionType::ResetStatus).value("SetStatusReady", ActionType::SetStatusReady)
-      .value("ClearCache", ActionType::ClearCache).value("Deliver", ActionType::Deliver).value("Fail", ActionType::Fail);
+      .value("ClearCache", ActionType::ClearCache).value("Deliver", ActionType::Deliver).value("Fail", ActionType::Fail)
+      .value("FilterBatch", ActionType::FilterBatch);
   py::class_<Action>(m, "Action").def_readonly("type", &Action::type).def_readonly("op_id", &Action::op_id)
       .def_readonly("replica", &Action::replica).def_readonly("peer", &Action::peer).def_readonly("batch_id", &Action::batch_id)
       .def_readonly("batch_ids", &Action::batch_ids).def_readonly("request_ids", &Action::request_ids)
@@ -141,7 +142,7 @@ void bind_router(py::module_& m) {
       .def("submit", &Controller::submit).def("client_gone", &Controller::client_gone)
       .def("on_prefill_done", &Controller::on_prefill_done).def("on_decode_done", &Controller::on_decode_done)
       .def("on_migrate_done", &Controller::on_migrate_done).def("on_params_done", &Controller::on_params_done)
-      .def("on_relay_done", &Controller::on_relay_done).def("on_failure", &Controller::on_failure, py::arg("op_id"), py::arg("now"), py::arg("failed_replica") = -1)
+      .def("on_relay_done", &Controller::on_relay_done).def("on_filter_done", &Controller::on_filter_done).def("on_failure", &Controller::on_failure, py::arg("op_id"), py::arg("now"), py::arg("failed_replica") = -1)
       .def("step", &Controller::step).def("manual_scale", &Controller::manual_scale)
       // completion straight from the wire bytes of the worker's response: the generations are read natively
       .def("on_prefill_done_wire", [](Controller& c, uint64_t op, py::bytes raw, double now) {

@@ -27,6 +27,7 @@ enum class ActionType : int {
   Prefill = 0, ZagPrefill, PrefillPP, Decode, Migrate, MigratePartial, Relay,
   NvlBroadcast, TanzBroadcast, RdmaBroadcast, LoadParams, ResetStatus, SetStatusReady, ClearCache,
   Deliver, Fail,
+  FilterBatch,   // drop requests whose client went away from a resident batch (request_ids = the ones to keep)
 };
 
 struct Action {
@@ -108,10 +109,19 @@ class Controller {
     queue_.append(e);
     counters_["blitz_request_count"] += 1;
   }
-  void client_gone(uint64_t id) {
+  // The client of `id` went away.  A request that still waits in the queue is forgotten at once (returns true; the
+  // queue drops its entry when it reaches it); one that is being served ends with its next token and, if the
+  // worker would go on with it, is filtered out of its batch.
+  bool client_gone(uint64_t id) {
     queue_.mark_client_gone(id);
     auto it = requests_.find(id);
-    if (it != requests_.end()) it->second.client_alive = false;
+    if (it == requests_.end()) return false;
+    if (it->second.t_batched < 0) {
+      requests_.erase(it);
+      return true;
+    }
+    it->second.client_alive = false;
+    return false;
   }
 
   struct TokenOut { uint64_t request_id; int32_t token; bool finished; };
@@ -173,14 +183,31 @@ class Controller {
     rep.decode_batches.erase(rep.decode_batches.begin(), rep.decode_batches.begin() + consumed);
     merged.in_step = false;
     stats_decode_tokens_ += toks.size();
-    deliver_tokens(merged, toks, now, false);
+    const bool dropped_alive = deliver_tokens(merged, toks, now, false);
     if (merged.request_ids.empty()) {
       release_blocks(op.replica, merged.blocks);
       out_.push_back(make_simple(ActionType::ClearCache, op.replica, merged.id));
     } else {
       shrink_blocks(op.replica, merged);
+      if (dropped_alive) {
+        // the worker would go on decoding for a client that is gone: take those requests out of its batch before
+        // the next step (router_v2/src/replica/mod.rs:37-100 filters after every step)
+        Action a = make_simple(ActionType::FilterBatch, op.replica, merged.id);
+        a.request_ids = merged.request_ids;
+        a.op_id = new_op(ActionType::FilterBatch, op.replica, -1, merged);
+        out_.push_back(a);
+        rep.busy = true;
+        counters_["blitz_filtered_batches"] += 1;
+      }
       rep.decode_batches.insert(rep.decode_batches.begin(), std::move(merged));
     }
+  }
+
+  void on_filter_done(uint64_t op_id, double now) {
+    (void)now;
+    if (late_answer(op_id)) return;
+    Op op = take_op(op_id);
+    reps_[op.replica].busy = false;
   }
 
   void on_migrate_done(uint64_t op_id, double now) {
@@ -521,7 +548,9 @@ class Controller {
     a.blocks += b.blocks;
     a.max_tokens += b.max_tokens;
   }
-  void deliver_tokens(ResidentBatch& b, const std::vector<TokenOut>& toks, double now, bool prefill) {
+  // Returns true when a request was finished here although the worker still runs it (its client went away).
+  bool deliver_tokens(ResidentBatch& b, const std::vector<TokenOut>& toks, double now, bool prefill) {
+    bool dropped_alive = false;
     for (const TokenOut& t : toks) {
       auto it = requests_.find(t.request_id);
       if (it == requests_.end()) continue;
@@ -535,6 +564,7 @@ class Controller {
       e.generated += 1;
       e.t_last_token = now;
       const bool fin = t.finished || e.generated >= e.max_new_tokens || !e.client_alive;
+      if (fin && !t.finished && e.generated < e.max_new_tokens) dropped_alive = true;
       if (compact_deliveries_) {
         deliveries_.push_back({t.request_id, t.token, fin});
       } else {
@@ -549,6 +579,7 @@ class Controller {
         requests_.erase(it);
       }
     }
+    return dropped_alive;
   }
   void erase_inflight_zag(Rep& rep, uint64_t batch_id) {
     for (auto it = rep.inflight_zag.begin(); it != rep.inflight_zag.end(); ++it)
@@ -1124,6 +1155,7 @@ class Controller {
       std::vector<RequestEntry> es;
       for (uint64_t id : ids) {
         if (!requests_.count(id) || std::find(requeued.begin(), requeued.end(), id) != requeued.end()) continue;
+        requests_[id].t_batched = -1;   // waiting again: a client that leaves now is forgotten at once
         es.push_back(requests_[id]);
         requeued.push_back(id);
       }
@@ -1189,6 +1221,7 @@ class Controller {
           cancel(id, o.batch.id, {});
           break;
         case ActionType::Decode:
+        case ActionType::FilterBatch:
           cancel(id, o.batch.id, {});        // its batches are resident on the lost replica: failed below
           break;
         case ActionType::Migrate:

@@ -200,6 +200,7 @@ class ClusterSim {
         push(now + d + cm_.rpc_overhead_s, a);
         break;
       }
+      case ActionType::FilterBatch: push(now + cm_.rpc_overhead_s, a); break;
       case ActionType::Deliver: rep.delivered_tokens += 1; break;
       case ActionType::Fail: rep.failed += 1; break;
       default: break;
@@ -236,6 +237,7 @@ class ClusterSim {
       case ActionType::TanzBroadcast:
       case ActionType::RdmaBroadcast:
       case ActionType::LoadParams: ctl_.on_params_done(ev.op_id, ev.t); break;
+      case ActionType::FilterBatch: ctl_.on_filter_done(ev.op_id, ev.t); break;
       default: break;
     }
   }

@@ -124,7 +124,12 @@ class RouterRuntime:
         return lr
 
     def client_gone(self, rid: int) -> None:
-        self.ctl.client_gone(rid)
+        """The consumer of request `rid` went away: stop spending work on it."""
+        if self.ctl.client_gone(rid):                 # still queued: nothing will ever be delivered for it
+            lr = self.requests.pop(rid, None)
+            if lr is not None and not lr.done.done():
+                lr.done.set_result("client gone")
+        self.wake.set()
 
     # ------------------------------------------------------------------ main loop
     async def _health_loop(self) -> None:
@@ -258,7 +263,7 @@ class RouterRuntime:
                    A.Decode: self._do_decode, A.Migrate: self._do_migrate, A.MigratePartial: self._do_migrate,
                    A.Relay: self._do_relay, A.NvlBroadcast: self._do_params, A.TanzBroadcast: self._do_params,
                    A.RdmaBroadcast: self._do_params, A.LoadParams: self._do_params, A.ResetStatus: self._do_simple,
-                   A.SetStatusReady: self._do_simple, A.ClearCache: self._do_simple}[t]
+                   A.SetStatusReady: self._do_simple, A.ClearCache: self._do_simple, A.FilterBatch: self._do_filter}[t]
         self._spawn(self._guard(a, handler))
 
     def _purge_replica(self, rep: int) -> None:
@@ -374,6 +379,14 @@ class RouterRuntime:
         now = self.now()
         self.ctl.on_decode_done_wire(a.op_id, res.raw, now)
         self._deliver(now)          # straight away: the next step of the loop may be a tick away
+
+    async def _do_filter(self, a) -> None:
+        """Drop the requests whose client went away from a worker's resident batch (`a.request_ids` stay)."""
+        ranks = self._ranks(a.replica)
+        res = (await self._all(ranks, [self.stubs[r].filter_batch(a.batch_id, list(a.request_ids)) for r in ranks]))[0]
+        if res.HasField("batch"):
+            self._remember(a.replica, res.batch)
+        self.ctl.on_filter_done(a.op_id, self.now())
 
     async def _do_migrate(self, a) -> None:
         batch = self._batch_proto(a)

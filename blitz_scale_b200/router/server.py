@@ -243,7 +243,11 @@ class RouterApp:
     async def _collect(self, toks, g):
         """Whole response at once: the handler sleeps until the last token instead of waking for every token."""
         lr = self.rt.submit(toks, g.max_new_tokens, stream=False)
-        err = await lr.done
+        try:
+            err = await lr.done
+        except asyncio.CancelledError:        # the client closed the connection: stop generating for it
+            self.rt.client_gone(lr.id)
+            raise
         if err:
             raise self._unavailable(err)
         return self._finish(lr, toks, g)
@@ -251,14 +255,19 @@ class RouterApp:
     async def _run(self, toks, g):
         """Token by token (server-sent events); the last item carries (tokens, timing headers)."""
         lr = self.rt.submit(toks, g.max_new_tokens)
-        while True:
-            ev = await lr.queue.get()
-            if ev[0] == "error":
-                raise self._unavailable(ev[1])
-            _, tok, final = ev
-            yield tok, final, None
-            if final:
-                break
+        try:
+            while True:
+                ev = await lr.queue.get()
+                if ev[0] == "error":
+                    raise self._unavailable(ev[1])
+                _, tok, final = ev
+                yield tok, final, None
+                if final:
+                    break
+        except (asyncio.CancelledError, GeneratorExit, ConnectionResetError):
+            if not lr.done.done():
+                self.rt.client_gone(lr.id)    # the consumer left before the last token: stop generating for it
+            raise
         yield None, True, self._finish(lr, toks, g)
 
     # ------------------------------------------------------------------ handlers
@@ -290,8 +299,9 @@ class RouterApp:
         resp = web.StreamResponse(headers={"Content-Type": "text/event-stream", "Cache-Control": "no-cache"})
         await resp.prepare(req)
         n = 0
+        agen = self._run(toks, g)
         try:
-            async for tok, final, done in self._run(toks, g):
+            async for tok, final, done in agen:
                 if done is not None:
                     out, _ = done
                     continue
@@ -301,9 +311,11 @@ class RouterApp:
                 if final:
                     ev["details"] = {"finish_reason": "length", "generated_tokens": n}
                 await resp.write(f"data:{json.dumps(ev)}\n\n".encode())
+            await resp.write_eof()
         except (ConnectionResetError, asyncio.CancelledError):
-            pass  # client went away; the queue entry is dropped by the core when it is still waiting
-        await resp.write_eof()
+            pass  # the client went away
+        finally:
+            await agen.aclose()      # an unfinished stream tells the core that its client is gone
         return resp
 
     async def info(self, req):
@@ -356,7 +368,9 @@ def controller_config_from_cluster(cluster: dict, tp: int, features: str, **over
 
 async def serve_router(rt: RouterRuntime, host: str, port: int, stop: Optional[asyncio.Event] = None, **kw) -> None:
     app = RouterApp(rt, **kw)
-    runner = web.AppRunner(app.app, access_log=None)
+    # a handler is cancelled when its client closes the connection: that is how a collected `/generate` learns
+    # that nobody waits for the answer any more
+    runner = web.AppRunner(app.app, access_log=None, handler_cancellation=True)
     await runner.setup()
     site = web.TCPSite(runner, host, port)
     await site.start()

@@ -690,3 +690,44 @@ def test_new_replica_dies_while_serving_during_its_load():
     assert len(results) == 60 and all((err is None and k == 3) or err == "replica lost" for err, k in results)
     assert sum(1 for err, _ in results if err is None) >= 40
     assert final == (["Prefill", "Decode", "Inactive"], True, 0, 0, [0, 0], [0, 0]), final
+
+
+def test_client_disconnect_stops_generation_for_that_request():
+    """A client closes its connection in the middle of a long generation (and another one while still queued): the
+    router tells the worker to drop the request, the others go on, and nothing is left behind."""
+    import aiohttp
+
+    async def go():
+        rt, backends, port, stop, tasks = await _cluster(2, ["Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+        for b in backends:
+            b.decode_step_s = 0.01
+        url = f"http://127.0.0.1:{port}"
+        async with aiohttp.ClientSession() as s:
+            async def full(n):
+                async with s.post(url + "/generate", json={"input_tokens": list(range(30)), "parameters": {"max_new_tokens": n}}) as r:
+                    return r.status, r.headers.get("x-generated-tokens")
+            keep = asyncio.create_task(full(60))
+            gone = asyncio.create_task(full(2000))               # 20 s of decoding if nobody stops it
+            await asyncio.sleep(0.3)
+            gone.cancel()                                        # closes that connection
+            streamed = 0
+            async with s.post(url + "/generate_stream", json={"input_tokens": list(range(30)), "parameters": {"max_new_tokens": 2000}}) as r:
+                async for line in r.content:
+                    if line.startswith(b"data:"):
+                        streamed += 1
+                        if streamed == 3:
+                            break                                # leave in the middle of the stream
+            status, n = await asyncio.wait_for(keep, timeout=30)
+        assert status == 200 and n == "60"
+        for _ in range(100):
+            if rt.ctl.idle() and not rt.requests and all(not b.batches for b in backends):
+                break
+            await asyncio.sleep(0.05)
+        state = (len(rt.requests), rt.ctl.idle(), rt.ctl.total_used_blocks(), [len(b.batches) for b in backends],
+                 [b.pool.used_pages for b in backends], dict(rt.ctl.counters()).get("blitz_filtered_batches", 0),
+                 backends[1].counters["decode"])
+        await _shutdown(stop, tasks)
+        return state
+    state = asyncio.run(go())
+    assert state[:5] == (0, True, 0, [0, 0], [0, 0]), state
+    assert state[5] >= 1 and state[6] < 400                      # filtered; nowhere near the 2000 steps asked for

@@ -525,3 +525,37 @@ def test_calibrated_autoscaling_study_orders_the_policies():
     assert mc["scale_outs"] >= 2 and mc["scale_out_latency_ms"] < host["scale_out_latency_ms"] < disk["scale_out_latency_ms"]
     assert mc["ttft_ms_p99"] < host["ttft_ms_p99"] < disk["ttft_ms_p99"]
     assert mc["ttft_violation_rate"] <= host["ttft_violation_rate"] <= disk["ttft_violation_rate"]
+
+
+def test_client_gone_is_forgotten_in_the_queue_and_filtered_out_of_a_running_batch():
+    cfg = _cfg(["Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+    ctl = core.Controller(cfg)
+    ctl.set_compact_deliveries(True)
+    for i in range(3):
+        ctl.submit(E(i, 100, 50))
+    ctl.submit(E(9, 9000, 5))                               # does not fit the first prefill batch: stays queued
+    pf = [a for a in ctl.step(0.0) if a.type == core.ActionType.Prefill][0]
+    assert sorted(pf.request_ids) == [0, 1, 2]
+    assert ctl.client_gone(9) is True and ctl.queue_size in (0, 1)      # forgotten at once
+    ctl.on_prefill_done(pf.op_id, [core.TokenOut(i, 7, False) for i in range(3)], 0.01)
+    mig = [a for a in ctl.step(0.02) if a.type == core.ActionType.Migrate][0]
+    ctl.on_migrate_done(mig.op_id, 0.03)
+    dec = [a for a in ctl.step(0.04) if a.type == core.ActionType.Decode][0]
+    assert ctl.client_gone(1) is False                      # being served: ends with its next token
+    ctl.on_decode_done(dec.op_id, [core.TokenOut(i, 8, False) for i in range(3)], 0.05)
+    assert (1, 8, True) in ctl.take_deliveries()
+    acts = ctl.step(0.06)
+    flt = [a for a in acts if a.type == core.ActionType.FilterBatch]
+    assert len(flt) == 1 and sorted(flt[0].request_ids) == [0, 2] and flt[0].replica == 1
+    assert not [a for a in acts if a.type == core.ActionType.Decode]          # no step before the batch is filtered
+    ctl.on_filter_done(flt[0].op_id, 0.07)
+    dec = [a for a in ctl.step(0.08) if a.type == core.ActionType.Decode]
+    assert len(dec) == 1
+    # everybody leaves: the batch is cleared instead of filtered
+    ctl.client_gone(0), ctl.client_gone(2)
+    ctl.on_decode_done(dec[0].op_id, [core.TokenOut(0, 8, False), core.TokenOut(2, 8, False)], 0.09)
+    acts = ctl.step(0.1)
+    assert [a.type for a in acts if a.type in (core.ActionType.FilterBatch, core.ActionType.ClearCache)] == [core.ActionType.ClearCache]
+    for _ in range(3):
+        ctl.step(0.2)
+    assert ctl.idle() and ctl.total_used_blocks() == 0 and ctl.inflight_ops() == 0
