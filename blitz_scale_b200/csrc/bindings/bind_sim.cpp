@@ -40,12 +40,13 @@ void bind_sim(py::module_& m) {
       .def_readonly("output_len", &SimRequestResult::output_len);
   py::class_<SimReport>(m, "SimReport").def_readonly("requests", &SimReport::requests).def_readonly("log", &SimReport::log)
       .def_readonly("submitted", &SimReport::submitted).def_readonly("completed", &SimReport::completed)
-      .def_readonly("failed", &SimReport::failed).def_readonly("delivered_tokens", &SimReport::delivered_tokens)
+      .def_readonly("failed", &SimReport::failed).def_readonly("gone_in_queue", &SimReport::gone_in_queue)
+      .def_readonly("gone_in_service", &SimReport::gone_in_service).def_readonly("delivered_tokens", &SimReport::delivered_tokens)
       .def_readonly("end_time", &SimReport::end_time).def_readonly("leftover_blocks", &SimReport::leftover_blocks)
       .def_readonly("prefill_replicas", &SimReport::prefill_replicas).def_readonly("decode_replicas", &SimReport::decode_replicas)
       .def_readonly("scale_up_latency", &SimReport::scale_up_latency);
   py::class_<ClusterSim>(m, "ClusterSim").def(py::init<const ControllerConfig&, const CostModel&>())
       .def("run", &ClusterSim::run, py::arg("trace"), py::arg("tick_s") = 0.001, py::arg("drain_s") = 120.0,
-           py::arg("kill_replica") = -1, py::arg("kill_at") = -1.0)
+           py::arg("kill_replica") = -1, py::arg("kill_at") = -1.0, py::arg("gone_every") = 0)
       .def("controller", &ClusterSim::controller, py::return_value_policy::reference_internal);
 }

@@ -1155,6 +1155,10 @@ class Controller {
       std::vector<RequestEntry> es;
       for (uint64_t id : ids) {
         if (!requests_.count(id) || std::find(requeued.begin(), requeued.end(), id) != requeued.end()) continue;
+        if (!requests_[id].client_alive) {   // nobody waits for it any more: end it here instead of queueing it again
+          fail_ids({id});
+          continue;
+        }
         requests_[id].t_batched = -1;   // waiting again: a client that leaves now is forgotten at once
         es.push_back(requests_[id]);
         requeued.push_back(id);

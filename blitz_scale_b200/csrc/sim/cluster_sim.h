@@ -38,6 +38,7 @@ struct SimReport {
   std::vector<SimRequestResult> requests;
   std::vector<std::string> log;
   uint64_t submitted = 0, completed = 0, failed = 0, delivered_tokens = 0;
+  uint64_t gone_in_queue = 0, gone_in_service = 0;  // clients that left before / after their request was batched
   double end_time = 0;
   uint64_t leftover_blocks = 0;
   std::vector<std::pair<double, int>> prefill_replicas, decode_replicas;  // (time, count) samples
@@ -56,11 +57,14 @@ class ClusterSim {
  public:
   ClusterSim(const ControllerConfig& cc, const CostModel& cm) : ctl_(cc), cm_(cm), cc_(cc) {}
 
+  // `gone_every` = n > 0: the client of every n-th request leaves a little after it arrived (in the queue, during
+  // prefill or in the middle of decoding, depending on the load).
   SimReport run(const std::vector<TraceItem>& trace, double tick_s = 0.001, double drain_s = 120.0,
-                int kill_replica = -1, double kill_at = -1) {
+                int kill_replica = -1, double kill_at = -1, int gone_every = 0) {
     SimReport rep;
     size_t next = 0;
     double now = 0;
+    std::multimap<double, uint64_t> leaving;
     const double t_last = trace.empty() ? 0 : trace.back().t;
     std::map<int, double> load_started;
     while (true) {
@@ -73,7 +77,15 @@ class ClusterSim {
         e.t_arrival = trace[next].t;
         ctl_.submit(e);
         rep.submitted += 1;
+        if (gone_every > 0 && next % static_cast<size_t>(gone_every) == 0)
+          leaving.emplace(trace[next].t + 0.02 + 0.045 * static_cast<double>(next % 11), next);
         ++next;
+      }
+      while (!leaving.empty() && leaving.begin()->first <= now) {
+        const uint64_t id = leaving.begin()->second;
+        leaving.erase(leaving.begin());
+        if (ctl_.client_gone(id)) rep.gone_in_queue += 1;
+        else if (ctl_.request(id)) rep.gone_in_service += 1;
       }
       // completions due
       while (!events_.empty() && events_.top().t <= now) {
@@ -92,7 +104,7 @@ class ClusterSim {
         rep.log.push_back("[" + std::to_string(now) + "] " + l);
         note_transition(l, now, load_started, rep);
       }
-      if (next >= trace.size() && events_.empty() && ctl_.idle()) break;
+      if (next >= trace.size() && events_.empty() && ctl_.idle() && leaving.empty()) break;
       if (now > t_last + drain_s) break;
       // advance: next tick, or jump to the next arrival / completion when idle
       double tn = now + tick_s;

@@ -18,9 +18,9 @@ FEATURES = ["impl_blitz,impl_nvl", "impl_blitz,impl_nvl,impl_live", "impl_blitz,
 @given(feat=st.sampled_from(FEATURES), seed=st.integers(0, 10 ** 6), n_inactive=st.integers(0, 4),
        burst=st.floats(4.0, 60.0), cv=st.sampled_from([1.0, 2.0, 4.0]), kill=st.booleans(), kill_replica=st.integers(0, 2), kill_at=st.sampled_from([0.5, 1.2, 2.0, 3.5]),
        prefill_rate=st.sampled_from([8000.0, 30000.0, 120000.0]), tp=st.sampled_from([1, 2]),
-       max_incoming=st.sampled_from([1, 2, 4]))
+       max_incoming=st.sampled_from([1, 2, 4]), gone_every=st.sampled_from([0, 0, 3, 7]))
 def test_requests_and_blocks_are_conserved(feat, seed, n_inactive, burst, cv, kill, kill_replica, kill_at, prefill_rate,
-                                           tp, max_incoming):
+                                           tp, max_incoming, gone_every):
     states = ["Prefill", "Decode"] + ["Inactive"] * n_inactive
     cfg = core.ControllerConfig()
     cfg.num_ranks, cfg.tp = len(states) * tp, tp
@@ -42,12 +42,16 @@ def test_requests_and_blocks_are_conserved(feat, seed, n_inactive, burst, cv, ki
     trace = core.generate_trace(spec)
     sim = core.ClusterSim(cfg, cm)
     kill_replica = min(kill_replica, len(states) - 1)
-    rep = sim.run(trace, 0.001, 120.0, kill_replica if kill else -1, kill_at if kill else -1.0)
+    rep = sim.run(trace, 0.001, 120.0, kill_replica if kill else -1, kill_at if kill else -1.0, gone_every)
     assert rep.submitted == len(trace)
-    assert rep.completed + rep.failed == len(trace), (rep.completed, rep.failed, len(trace))
+    # a client that leaves while its request waits is forgotten; one that leaves later gets a shortened answer
+    assert rep.completed + rep.failed + rep.gone_in_queue == len(trace), (rep.completed, rep.failed, rep.gone_in_queue, len(trace))
     assert rep.leftover_blocks == 0
+    want = sum(x.output_len for x in trace)
     if not kill:
         assert rep.failed == 0
-        assert rep.delivered_tokens == sum(x.output_len for x in trace)
+        assert rep.delivered_tokens == want if gone_every == 0 else rep.delivered_tokens <= want
+    if gone_every == 0:
+        assert rep.gone_in_queue == rep.gone_in_service == 0
     for r in rep.requests:
         assert r.ttft >= 0 and r.t_done >= r.t_arrival
