@@ -563,7 +563,10 @@ class Controller {
       }
       e.generated += 1;
       e.t_last_token = now;
-      const bool fin = t.finished || e.generated >= e.max_new_tokens || !e.client_alive;
+      // a client that left ends its request at a decode step, where the worker's batch can be filtered before the
+      // next step; ending it at the prefill token would leave the batch that is about to migrate out of step with
+      // the worker's copy of it
+      const bool fin = t.finished || e.generated >= e.max_new_tokens || (!prefill && !e.client_alive);
       if (fin && !t.finished && e.generated < e.max_new_tokens) dropped_alive = true;
       if (compact_deliveries_) {
         deliveries_.push_back({t.request_id, t.token, fin});
