@@ -731,3 +731,46 @@ def test_client_disconnect_stops_generation_for_that_request():
     state = asyncio.run(go())
     assert state[:5] == (0, True, 0, [0, 0], [0, 0]), state
     assert state[5] >= 1 and state[6] < 400                      # filtered; nowhere near the 2000 steps asked for
+
+
+def test_tensor_parallel_replicas_over_grpc_and_loss_of_one_shard():
+    """Replicas of two ranks each: every action goes to both ranks of a replica; when one shard's worker goes away the
+    whole replica is lost (the failing rank maps to its replica), and the survivor takes over both phases."""
+    async def go():
+        n, tp = 4, 2
+        ports = _free_ports(n)
+        states = ["Prefill", "Prefill", "Decode", "Decode"]          # per rank: replica 0 = ranks 0-1, replica 1 = ranks 2-3
+        backends, stops, tasks = [], [], []
+        for r in range(n):
+            ready, stop = asyncio.Event(), asyncio.Event()
+            backends.append(StubBackend(r, n, ready=True, seed=3))
+            tasks.append(asyncio.create_task(serve(backends[r], "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            stops.append(stop)
+            await ready.wait()
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n}, tp, "impl_blitz,impl_nvl",
+                                             max_blocks_per_replica=4000)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2)
+        assert rt.ctl.num_replicas == 2
+        lt = asyncio.create_task(rt.run())
+
+        async def one(k):
+            lr = rt.submit(list(range(25)), k, stream=False)
+            return await asyncio.wait_for(lr.done, 30), list(lr.tokens)
+        err, toks = await one(5)
+        assert err is None and len(toks) == 5
+        counts = [dict(b.counters) for b in backends]
+        assert counts[0]["prefill"] == counts[1]["prefill"] == 1 and counts[2]["decode"] == counts[3]["decode"] >= 4
+        assert counts[0]["migrate"] == counts[1]["migrate"] == 1 and counts[2]["immigrate"] == counts[3]["immigrate"] == 1
+        stops[3].set()                                            # one shard of the decode replica goes away
+        await asyncio.wait([tasks[3]], timeout=5)
+        err, _ = await one(5)
+        assert err == "replica lost" and rt.ctl.state_name(1) == "Inactive" and rt.ctl.state_name(0) == "Prefill"
+        err, toks2 = await one(5)                                 # replica 0 now serves both phases, on both of its ranks
+        assert err is None and len(toks2) == 5
+        assert backends[0].counters["decode"] == backends[1].counters["decode"] >= 4
+        await rt.stop()
+        lt.cancel()
+        for s in stops:
+            s.set()
+        await asyncio.wait(tasks, timeout=5)
+    asyncio.run(go())
