@@ -1296,6 +1296,16 @@ class Controller {
       rep.m.dst_busy = true;
       log_transition(r, old, RState::Inactive);
     }
+    if (quarantine && cfg_.tp > 1) {
+      // the replica is lost as a whole, but some of its shards may still run: they drop what they hold, so that
+      // nothing stale is left if the replica is brought back (calls to the shard that is gone simply fail)
+      Action c = make_simple(ActionType::ClearCache, r, 0);
+      c.final = true;   // every batch
+      out_.push_back(c);
+      Action z = make_simple(ActionType::ResetStatus, r, 0);
+      z.dst_ranks = steer_.ranks_of_replica(r);
+      out_.push_back(z);
+    }
     for (int d : aborted_loads) {
       lose_replica(d, now, false);
       Action a = make_simple(ActionType::ResetStatus, d, 0);

@@ -428,6 +428,21 @@ class RouterRuntime:
         self.ctl.on_params_done(a.op_id, self.now())
 
     async def _do_simple(self, a) -> None:
+        if self.ctl.state_name(a.replica) == "Inactive" and a.type in (A.ClearCache, A.ResetStatus):
+            # housekeeping on a replica that is out of service (lost, or just unloaded): some of its ranks may be
+            # gone, which is no reason to declare anything else lost
+            if a.type == A.ClearCache and a.final:
+                self._purge_replica(a.replica)
+                calls = [self.stubs[r].clear_cache(None) for r in self._ranks(a.replica)]
+            elif a.type == A.ClearCache:
+                self.cached.pop((a.replica, a.batch_id), None)
+                calls = [self.stubs[r].clear_cache(a.batch_id) for r in self._ranks(a.replica)]
+            else:
+                calls = [self.stubs[r].reset_status() for r in a.dst_ranks]
+            for res in await asyncio.gather(*calls, return_exceptions=True):
+                if isinstance(res, Exception):
+                    log.debug("%s on inactive replica %d: %s", a.type.name, a.replica, res)
+            return
         if a.type == A.ClearCache:
             self.cached.pop((a.replica, a.batch_id), None)
             if not any(k[1] == a.batch_id for k in self.cached):
