@@ -94,6 +94,23 @@ static void controller_sim() {
     CHECK(rep.submitted == trace.size() && rep.completed + rep.failed == rep.submitted);
     CHECK(rep.leftover_blocks == 0);
   }
+  for (int tp : {1, 2}) {
+    // failures of every replica in turn, clients that leave, several migrations in flight, tensor-parallel replicas
+    ControllerConfig c2 = cc;
+    c2.tp = tp;
+    c2.num_ranks = 6 * tp;
+    c2.init_states.clear();
+    for (const char* st : {"Prefill", "Decode", "Prefill", "Inactive", "Inactive", "Inactive"})
+      for (int k = 0; k < tp; ++k) c2.init_states.push_back(st);
+    c2.max_incoming_migrations = 3;
+    c2.quarantine_ms = 300;
+    for (int victim = 0; victim < 3; ++victim) {
+      ClusterSim sim(c2, cm);
+      const SimReport rep = sim.run(trace, 0.001, 120.0, victim, 4.0 + victim, /*gone_every=*/4);
+      CHECK(rep.submitted == trace.size() && rep.completed + rep.failed + rep.gone_in_queue == rep.submitted);
+      CHECK(rep.leftover_blocks == 0);
+    }
+  }
 }
 
 // ---- 3a: unit copy with per-unit flags -------------------------------------------------------------------
