@@ -54,8 +54,10 @@ void bind_router(py::module_& m) {
     auto x = rstate_from_name(a), y = rstate_from_name(b);
     if (!x || !y) throw std::invalid_argument("unknown state");
     return transition_allowed(*x, *y); });
-  m.def("replica_state_names", [] { std::vector<std::string> v;
-    for (int i = 0; i <= static_cast<int>(RState::TanzCasting); ++i) v.push_back(rstate_name(static_cast<RState>(i))); return v; });
+  m.def("replica_state_names", [] {
+    std::vector<std::string> v;
+    for (int i = 0; i <= static_cast<int>(RState::TanzCasting); ++i) v.push_back(rstate_name(static_cast<RState>(i)));
+    return v; });
 
   py::class_<PlannerConfig>(m, "PlannerConfig").def(py::init<>())
       .def_readwrite("prefill_lower", &PlannerConfig::prefill_lower).def_readwrite("prefill_upper", &PlannerConfig::prefill_upper)

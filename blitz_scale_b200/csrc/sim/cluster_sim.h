@@ -46,7 +46,7 @@ struct SimReport {
 };
 
 struct SimEv {
-  double t; uint64_t seq; uint64_t op_id; ActionType type; int replica;
+  double t = 0; uint64_t seq = 0; uint64_t op_id = 0; ActionType type = ActionType::Deliver; int replica = -1;
   std::vector<uint64_t> request_ids;
   bool has_batch = false; uint64_t batch_id = 0; int next_layer = 0;
   uint64_t batch_key = 0;  // batch the action was about
