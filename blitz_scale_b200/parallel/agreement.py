@@ -12,7 +12,7 @@ Unit numbering follows the weight segment: unit 0 = embedding, units 1..L = laye
 """
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
+from typing import Sequence, Tuple
 
 
 class LoadAgreement:

@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from .. import ops
+from .. import ops  # noqa: F401  (loads the kernel library: its absence must show when the engine is imported)
 from ..models.config import ModelConfig, get_config
 from ..models.llama import LlamaRunner, StepMeta, TPComm
 from ..models.weights import WeightSegment

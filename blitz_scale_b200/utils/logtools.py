@@ -15,7 +15,6 @@ from __future__ import annotations
 import argparse
 import heapq
 import re
-import sys
 from datetime import datetime
 from typing import Dict, Iterable, Iterator, List, Optional, Tuple
 

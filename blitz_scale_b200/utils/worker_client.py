@@ -19,7 +19,7 @@ import json
 import shlex
 import sys
 import time
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Sequence
 
 from ..pb.schema import pb
 from ..router.stub import WorkerStub
