@@ -10,9 +10,10 @@
 // binding (Rust `tokenizers` behind a C ABI: create_tokenizer_from_file / encode / decode / num_ids / get_id,
 // src/tokenizer/): the same five operations are exported with C linkage by the core module.
 //
-// The scanner treats every non-ASCII character as a letter; for scripts where Unicode classes matter (digits or
-// punctuation outside ASCII) the split can differ from the regex engine's, which changes token boundaries but never
-// loses bytes: decode(encode(s)) == s always holds for byte-level models.
+// The scanner classifies characters with Unicode tables (letters L*, numbers N*, White_Space; generated into
+// unicode_tables.h) and evaluates the word pattern as a first-match alternation, so token boundaries are those of
+// the regular-expression engine the format's own library uses; two patterns are known: GPT-2's (ByteLevel) and the
+// cl100k family's (Llama-3, Qwen-2).  decode(encode(s)) == s always holds for byte-level models.
 #pragma once
 #include <cstdint>
 #include <cstdio>
@@ -29,6 +30,7 @@
 #include <vector>
 
 #include "../util/minijson.h"
+#include "unicode_tables.h"
 
 namespace blitz {
 
@@ -73,9 +75,12 @@ class Tokenizer {
       }
     // byte-level if the pre-tokenizer or decoder says so; otherwise SentencePiece conventions
     t.byte_level_ = mentions(root.find("pre_tokenizer"), "ByteLevel") || mentions(root.find("decoder"), "ByteLevel");
-    t.max_digits_ = text.find("\\\\p{N}{1,3}") != std::string::npos || text.find("\\p{N}{1,3}") != std::string::npos
-                        ? 3
-                        : std::numeric_limits<int>::max();
+    // the word pattern: ByteLevel's own (GPT-2) unless a Split pre-tokenizer carries the cl100k-family expression
+    auto has = [&](const char* needle) { return text.find(needle) != std::string::npos; };
+    t.cl100k_ = has("?\\\\p{L}+|\\\\p{N}") || has("?\\p{L}+|\\p{N}");
+    if (has("\\\\p{N}{1,3}") || has("\\p{N}{1,3}")) t.max_digits_ = 3;
+    else if (t.cl100k_ && (has("|\\\\p{N}|") || has("|\\p{N}|"))) t.max_digits_ = 1;
+    else t.max_digits_ = std::numeric_limits<int>::max();
     if (const json::Value* add = root.find("added_tokens"))
       for (const json::Value& a : add->arr) {
         const std::string& content = a.at("content").str;
@@ -178,6 +183,7 @@ class Tokenizer {
   bool byte_level_ = true, byte_fallback_ = false;
   int32_t unk_id_ = -1;
   int max_digits_ = std::numeric_limits<int>::max();
+  bool cl100k_ = false;   // word pattern of the cl100k family instead of GPT-2's
   std::string byte_to_str_[256];
   std::unordered_map<uint32_t, uint8_t> cp_to_byte_;
   mutable std::unique_ptr<std::mutex> cache_mu_ = std::make_unique<std::mutex>();
@@ -241,41 +247,122 @@ class Tokenizer {
     }
   }
 
-  static bool is_letter(unsigned char c) { return (c >= 'a' && c <= 'z') || (c >= 'A' && c <= 'Z') || c >= 0x80; }
-  static bool is_digit(unsigned char c) { return c >= '0' && c <= '9'; }
-  static bool is_space(unsigned char c) { return c == ' ' || c == '\t' || c == '\n' || c == '\r' || c == '\v' || c == '\f'; }
+  // ---- word scanner -------------------------------------------------------------------------------------------
+  // One decoded character of the text: code point and byte length (malformed bytes count as one-byte characters of
+  // class "other", so nothing is ever lost).
+  struct Ch { uint32_t cp; uint32_t len; };
+  static Ch char_at(std::string_view s, size_t i) {
+    const unsigned char c = static_cast<unsigned char>(s[i]);
+    size_t n = utf8_len(c);
+    if (n == 1 || i + n > s.size()) return {c < 0x80 ? c : 0xFFFDu, 1};
+    uint32_t cp = c & (0xFFu >> (n + 1));
+    for (size_t k = 1; k < n; ++k) {
+      const unsigned char cc = static_cast<unsigned char>(s[i + k]);
+      if ((cc & 0xC0) != 0x80) return {0xFFFDu, 1};
+      cp = (cp << 6) | (cc & 0x3F);
+    }
+    return {cp, static_cast<uint32_t>(n)};
+  }
+  enum Cls { kL, kN, kS, kO };   // letter, number, white space, anything else
+  static Cls cls(uint32_t cp) {
+    if (unicode::is_letter(cp)) return kL;
+    if (unicode::is_number(cp)) return kN;
+    if (unicode::is_space(cp)) return kS;
+    return kO;
+  }
+  static bool is_crlf(uint32_t cp) { return cp == '\r' || cp == '\n'; }
 
-  // GPT-2 style word boundaries; returns the end of the word starting at i.
+  // End of the contraction that starts at i ('s 't 're 've 'm 'll 'd, tried in this order), or i if there is none.
+  static size_t contraction_end(std::string_view s, size_t i, bool ignore_case) {
+    if (s[i] != '\'' || i + 1 >= s.size()) return i;
+    static const char* kContr[] = {"s", "t", "re", "ve", "m", "ll", "d"};
+    for (const char* c : kContr) {
+      const size_t l = std::char_traits<char>::length(c);
+      if (i + 1 + l > s.size()) continue;
+      bool ok = true;
+      for (size_t k = 0; k < l && ok; ++k) {
+        char x = s[i + 1 + k];
+        if (ignore_case && x >= 'A' && x <= 'Z') x = static_cast<char>(x - 'A' + 'a');
+        ok = x == c[k];
+      }
+      if (ok) return i + 1 + l;
+    }
+    return i;
+  }
+  // End of the maximal run of characters of class `want` starting at i (at most `limit` characters).
+  static size_t run_end(std::string_view s, size_t i, Cls want, int limit = std::numeric_limits<int>::max()) {
+    int k = 0;
+    while (i < s.size() && k < limit) {
+      const Ch c = char_at(s, i);
+      if (cls(c.cp) != want) break;
+      i += c.len;
+      ++k;
+    }
+    return i;
+  }
+  // White space starting at i, as the tail of both patterns matches it: `\s+(?!\S)` (the run without its last
+  // character when something follows it, so that the last blank can prefix the next word), else `\s+`.
+  static size_t space_end(std::string_view s, size_t i) {
+    size_t j = i, last = i, count = 0;
+    while (j < s.size()) {
+      const Ch c = char_at(s, j);
+      if (cls(c.cp) != kS) break;
+      last = j;
+      j += c.len;
+      ++count;
+    }
+    if (j < s.size() && count > 1) return last;
+    return j;
+  }
+
+  // End of the word that starts at i.  Two patterns are implemented as first-match alternations, exactly as a
+  // regular-expression engine evaluates them:
+  //   GPT-2 (ByteLevel's own):  's|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+
+  //   cl100k family (Llama-3, Qwen-2; a Split pre-tokenizer in tokenizer.json):
+  //     (?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,k}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+
   size_t next_word(std::string_view s, size_t i) const {
     const size_t n = s.size();
-    if (s[i] == '\'' && i + 1 < n) {
-      static const char* kContr[] = {"'s", "'t", "'re", "'ve", "'m", "'ll", "'d"};
-      for (const char* c : kContr) {
-        const size_t l = std::char_traits<char>::length(c);
-        if (s.compare(i, l, c) == 0) return i + l;
+    const size_t ce = contraction_end(s, i, cl100k_);
+    if (ce != i) return ce;
+    const Ch c0 = char_at(s, i);
+    const Cls k0 = cls(c0.cp);
+    const size_t i1 = i + c0.len;
+    const bool has1 = i1 < n;
+    const Ch c1 = has1 ? char_at(s, i1) : Ch{0, 0};
+    const Cls k1 = has1 ? cls(c1.cp) : kO;
+    if (cl100k_) {
+      // [^\r\n\p{L}\p{N}]?\p{L}+
+      if (k0 != kL && k0 != kN && !is_crlf(c0.cp) && has1 && k1 == kL) return run_end(s, i1, kL);
+      if (k0 == kL) return run_end(s, i, kL);
+      // \p{N}{1,k}
+      if (k0 == kN) return run_end(s, i, kN, max_digits_);
+      // ` ?[^\s\p{L}\p{N}]+[\r\n]*`
+      size_t j = i;
+      if (c0.cp == ' ' && has1 && k1 == kO) j = i1;
+      if (j < n && cls(char_at(s, j).cp) == kO) {
+        j = run_end(s, j, kO);
+        while (j < n && is_crlf(static_cast<unsigned char>(s[j]))) ++j;
+        return j;
       }
+      // \s*[\r\n]+ : through the last line break of the white-space run, if it has one
+      size_t e = i, last_break_end = i;
+      while (e < n) {
+        const Ch c = char_at(s, e);
+        if (cls(c.cp) != kS) break;
+        e += c.len;
+        if (is_crlf(c.cp)) last_break_end = e;
+      }
+      if (last_break_end != i) return last_break_end;
+      return space_end(s, i);
     }
+    // GPT-2: an optional blank, then a run of one class
     size_t j = i;
-    if (s[j] == ' ' && j + 1 < n && !is_space(s[j + 1])) ++j;  // optional leading space
-    const unsigned char c = s[j];
-    if (is_letter(c)) {
-      while (j < n && is_letter(s[j])) ++j;
-      return j;
-    }
-    if (is_digit(c)) {
-      int d = 0;
-      while (j < n && is_digit(s[j]) && d < max_digits_) { ++j; ++d; }
-      return j;
-    }
-    if (!is_space(c)) {
-      while (j < n && !is_space(s[j]) && !is_letter(s[j]) && !is_digit(s[j])) ++j;
-      return j;
-    }
-    // white space: a run, leaving its last blank to prefix the next word when one follows
-    j = i;
-    while (j < n && is_space(s[j])) ++j;
-    if (j < n && j - i > 1 && s[j - 1] == ' ') --j;
-    return j;
+    Cls k = k0;
+    if (c0.cp == ' ' && has1 && k1 != kS) { j = i1; k = k1; }
+    if (k == kL) return run_end(s, j, kL);
+    if (k == kN) return run_end(s, j, kN, max_digits_);
+    if (k == kO) return run_end(s, j, kO);
+    return space_end(s, i);
   }
 
   void bpe(std::vector<std::string>& sym) const {

@@ -200,3 +200,50 @@ def test_router_http_with_native_tokenizer(trained):
     ids = [tk["id"] for tk in body["details"]["tokens"]]
     assert len(ids) == 5 and body["generated_text"] == t.decode(ids, True)
     assert [tk["text"] for tk in body["details"]["tokens"]] == [t.decode([i], False) for i in ids]
+
+
+LLAMA3_PATTERN = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+"
+                  r"|\s+(?!\S)|\s+")
+QWEN2_PATTERN = LLAMA3_PATTERN.replace(r"\p{N}{1,3}", r"\p{N}")
+HARD = ["word—word ² ³ ١٢٣ 12345 x1y22z333", "tab\there\r\nnext  line\n\n  indented", "I'M HE'LL we'Ve 'quoted' don't",
+        "naïve café — ünïcödé ✓ 日本語 한국어 😀😀", "a b c 　d  e", "price: $1,234.56 (approx.)!!!\n",
+        "foo_bar-baz/qux.py:42", "  a", "x \n\n y\r\n\r\n  z  "]
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "llama3", "qwen2"])
+def test_word_patterns_match_the_reference_library_on_random_text(kind, tmp_path):
+    """Token ids equal those of the `tokenizers` library for GPT-2's word pattern and for the cl100k-family patterns of
+    Llama-3 and Qwen-2 (a Split pre-tokenizer in tokenizer.json), on hand-picked hard cases and on random strings
+    rich in Unicode white space, digits and punctuation."""
+    pytest.importorskip("tokenizers")
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    ref = Tokenizer(models.BPE())
+    if kind == "gpt2":
+        ref.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    else:
+        pat = LLAMA3_PATTERN if kind == "llama3" else QWEN2_PATTERN
+        ref.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pat), behavior="isolated", invert=False),
+                                                     pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    ref.decoder = decoders.ByteLevel()
+    ref.train_from_iterator(CORPUS + HARD * 4, trainers.BpeTrainer(vocab_size=900, special_tokens=["<|begin|>", "<|end|>"],
+                                                                   initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                                                                   show_progress=False))
+    ref.save(str(tmp_path / "tokenizer.json"))
+    nat = core.Tokenizer.from_file(str(tmp_path / "tokenizer.json"))
+    for s in HARD + PROBES:
+        assert nat.encode(s) == ref.encode(s).ids, (kind, s)
+        assert nat.decode(nat.encode(s), False) == s
+    if kind != "gpt2":
+        assert nat.encode("in 12345 days") != core.Tokenizer.from_file(str(tmp_path / "tokenizer.json")).encode("in 12 345 days")
+    pieces = st.sampled_from(list("abcXYZ019 '\t\n\r.,!?-_’é日本ñ²١—✓😀$") + ["'s", "'LL", "'Ve", " ", " ", "　",
+                                                                              "  ", "\r\n", "<|end|>", "12345", " the", "word"])
+
+    @settings(max_examples=400, deadline=None)
+    @given(st.lists(pieces, max_size=20).map("".join))
+    def agree(s):
+        ids = nat.encode(s)
+        assert ids == ref.encode(s).ids, (kind, s)
+        assert nat.decode(ids, False) == s
+    agree()
