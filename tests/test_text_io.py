@@ -247,3 +247,26 @@ def test_word_patterns_match_the_reference_library_on_random_text(kind, tmp_path
         assert ids == ref.encode(s).ids, (kind, s)
         assert nat.decode(ids, False) == s
     agree()
+
+
+def test_sentencepiece_style_matches_the_reference_library_on_random_text(tmp_path):
+    pytest.importorskip("tokenizers")
+    pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+    from tokenizers import Tokenizer, decoders, models, normalizers, trainers
+    ref = Tokenizer(models.BPE(unk_token="<unk>", byte_fallback=True, fuse_unk=True))
+    ref.normalizer = normalizers.Sequence([normalizers.Prepend("▁"), normalizers.Replace(" ", "▁")])
+    ref.decoder = decoders.Sequence([decoders.Replace("▁", " "), decoders.ByteFallback(), decoders.Fuse(), decoders.Strip(" ", 1, 0)])
+    ref.train_from_iterator(CORPUS, trainers.BpeTrainer(vocab_size=700, show_progress=False,
+                                                        special_tokens=["<unk>", "<s>", "</s>"] + [f"<0x{i:02X}>" for i in range(256)]))
+    ref.save(str(tmp_path / "tokenizer.json"))
+    nat = core.Tokenizer.from_file(str(tmp_path / "tokenizer.json"))
+    pieces = st.sampled_from(list("abcXYZ019 '\t\n.,!?-_é日ñ—😀") + [" ", "  ", "the", " quick", "<s>", "</s>", "▁"])
+
+    @settings(max_examples=400, deadline=None)
+    @given(st.lists(pieces, max_size=20).map("".join))
+    def agree(s):
+        ids = nat.encode(s)
+        assert ids == ref.encode(s).ids, s
+        assert nat.decode(ids, True) == ref.decode(ids, skip_special_tokens=True), s
+    agree()
