@@ -18,6 +18,7 @@ from __future__ import annotations
 import argparse
 import json
 import struct
+import warnings
 from pathlib import Path
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -27,8 +28,10 @@ from ..runtime import core
 from .config import ModelConfig, get_config
 from .weights import WeightSegment, shard_from_full
 
-_DT = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32}
-_ST = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32"}
+_DT = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F64": torch.float64, "I64": torch.int64,
+       "I32": torch.int32, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8, "BOOL": torch.bool,
+       "F8_E4M3": torch.float8_e4m3fn, "F8_E5M2": torch.float8_e5m2}
+_ST = {v: k for k, v in _DT.items()}
 
 
 class CheckpointReader:
@@ -55,8 +58,12 @@ class CheckpointReader:
         f = self.files[self.where[name]]
         info = f.info(name)
         view, _keep = f.view(name)
-        t = torch.frombuffer(view, dtype=_DT[info.dtype]) if info.nbytes else torch.empty(0, dtype=_DT[info.dtype])
-        return t.view(*info.shape)
+        if info.dtype not in _DT:
+            raise TypeError(f"{name}: element type {info.dtype} is not supported")
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)      # the mapping is read-only; so are its users
+            t = torch.frombuffer(view, dtype=_DT[info.dtype]) if info.nbytes else torch.empty(0, dtype=_DT[info.dtype])
+        return t.reshape(tuple(info.shape))     # also right for 0-dimensional (scalar) tensors
 
 
 def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata: Optional[Dict[str, str]] = None) -> None:
@@ -66,7 +73,7 @@ def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata: Optional
         header["__metadata__"] = metadata
     for name, t in tensors.items():
         t = t.contiguous().cpu()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _ST[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)

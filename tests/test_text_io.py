@@ -112,6 +112,20 @@ def test_safetensors_reader_and_hf_conversion(tmp_path):
         WeightSegment.check_sidecar(p.parent, cfg, 2, r, torch.bfloat16)
     assert convert.main(["--src", str(tmp_path), "--model", "tiny", "--out", str(tmp_path / "cli")]) == 0
     assert (tmp_path / "cli" / "segment.0.bin").stat().st_size == seg.layout.total_bytes
+    # scalars, integer and boolean tensors, empty tensors: both directions against the `safetensors` library
+    st_lib = pytest.importorskip("safetensors.torch")
+    odd = {"scalar": torch.tensor(2.5), "ids": torch.arange(6, dtype=torch.int64).view(2, 3), "mask": torch.tensor([True, False]),
+           "empty": torch.zeros(0, 4, dtype=torch.float16), "bytes": torch.arange(5, dtype=torch.uint8)}
+    st_lib.save_file(odd, str(tmp_path / "odd.safetensors"))
+    r = convert.CheckpointReader(tmp_path / "odd.safetensors")
+    for k, v in odd.items():
+        got = r.get(k)
+        assert got.dtype == v.dtype and got.shape == v.shape and torch.equal(got, v), k
+    convert.write_safetensors(tmp_path / "odd2.safetensors", odd)
+    back = st_lib.load_file(str(tmp_path / "odd2.safetensors"))
+    assert all(back[k].dtype == v.dtype and back[k].shape == v.shape and torch.equal(back[k], v) for k, v in odd.items())
+    (tmp_path / "odd.safetensors").unlink()
+    (tmp_path / "odd2.safetensors").unlink()
     # list and verify modes
     listed = convert.list_checkpoint(tmp_path)
     assert ("lm_head.weight", "BF16", (cfg.vocab, cfg.hidden)) in listed and len(listed) == 3 + 9 * cfg.layers
