@@ -265,6 +265,11 @@ class Tokenizer {
   }
   enum Cls { kL, kN, kS, kO };   // letter, number, white space, anything else
   static Cls cls(uint32_t cp) {
+    if (cp < 0x80) {   // the common case without the range tables
+      if ((cp | 0x20) >= 'a' && (cp | 0x20) <= 'z') return kL;
+      if (cp >= '0' && cp <= '9') return kN;
+      return (cp == ' ' || (cp >= 0x09 && cp <= 0x0D)) ? kS : kO;
+    }
     if (unicode::is_letter(cp)) return kL;
     if (unicode::is_number(cp)) return kN;
     if (unicode::is_space(cp)) return kS;
