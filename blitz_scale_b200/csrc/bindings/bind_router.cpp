@@ -30,7 +30,7 @@ void bind_router(py::module_& m) {
       .def("next_batch", &BatchQueue::next_batch, py::arg("min_size"), py::arg("prefill_token_budget"),
            py::arg("token_budget"), py::arg("block_budget") = std::nullopt);
 
-  py::class_<GenerateParams>(m, "GenerateParams").def(py::init<>())
+  py::class_<GenerateParams>(m, "GenerateParams", py::dynamic_attr()).def(py::init<>())
       .def_readwrite("input_len", &GenerateParams::input_len).def_readwrite("max_new_tokens", &GenerateParams::max_new_tokens)
       .def_readwrite("best_of", &GenerateParams::best_of).def_readwrite("do_sample", &GenerateParams::do_sample)
       .def_readwrite("temperature", &GenerateParams::temperature)

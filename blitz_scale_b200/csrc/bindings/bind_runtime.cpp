@@ -73,6 +73,9 @@ void bind_runtime(py::module_& m) {
       .def("extend", &Batch::extend).def("clear", &Batch::clear)
       .def("request_ids", &Batch::request_ids).def("prompt_lens", &Batch::prompt_lens).def("emit_info", &Batch::emit_info)
       .def("encode_generations", [](const Batch& b, const std::vector<int32_t>& toks) { return py::bytes(b.encode_generations(toks)); })
+      .def("sampling_rows", [](const Batch& b) {
+        auto r = b.sampling_rows();
+        return py::make_tuple(r.rows, r.temperature, r.top_k, r.top_p, r.seeds); })
       .def("none_generated", &Batch::none_generated).def("prompt_page_ids", &Batch::prompt_page_ids)
       .def("fill_prefill", [](const Batch& b, py::array_t<int32_t, py::array::c_style> h, const MetaLayout& L) {
         if (h.size() < L.total) throw std::invalid_argument("staging array too small");

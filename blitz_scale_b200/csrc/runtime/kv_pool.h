@@ -256,6 +256,29 @@ class Batch {
     }
     return out;
   }
+  // Rows of the batch that sample their next token instead of taking the arg-max, with their parameters; the seed
+  // of a row is mixed with the number of tokens it has generated so that every step draws a fresh, reproducible
+  // number.  Empty when the whole batch is greedy (the common case: one pass over the batch, no allocation).
+  struct SamplingRows {
+    std::vector<int64_t> rows;
+    std::vector<float> temperature, top_p;
+    std::vector<int32_t> top_k;
+    std::vector<int64_t> seeds;
+  };
+  SamplingRows sampling_rows() const {
+    SamplingRows out;
+    for (size_t i = 0; i < seqs_.size(); ++i) {
+      const SeqSpec& sp = seqs_[i].spec;
+      if (!sp.do_sample) continue;
+      out.rows.push_back(static_cast<int64_t>(i));
+      out.temperature.push_back(sp.temperature > 0.f ? sp.temperature : 1.f);
+      out.top_p.push_back(sp.top_p > 0.f && sp.top_p <= 1.f ? sp.top_p : 1.f);
+      out.top_k.push_back(sp.top_k > 0 ? sp.top_k : 0);
+      const uint64_t mixed = sp.seed * 0x9E3779B97F4A7C15ull + static_cast<uint64_t>(seqs_[i].generated.size()) + 1ull;
+      out.seeds.push_back(static_cast<int64_t>(mixed));
+    }
+    return out;
+  }
   bool none_generated() const {
     for (auto& s : seqs_)
       if (!s.generated.empty()) return false;

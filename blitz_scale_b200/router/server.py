@@ -27,6 +27,7 @@ from typing import List, Optional
 
 from aiohttp import web
 
+from ..pb.schema import pb
 from ..runtime import core
 from .runtime import RouterRuntime
 
@@ -198,6 +199,12 @@ class RouterApp:
             toks = toks[-int(p["truncate"]):]
         g.has_seed = p.get("seed") is not None
         err = core.validate_request(g, self.limits)
+        if not err and g.do_sample:
+            # carried to the worker in the request's NextTokenChooserParameters; greedy requests carry none
+            seed = int(p["seed"]) if g.has_seed else zlib.crc32(repr((toks[:16], time.time_ns())).encode())
+            g.chooser = pb.NextTokenChooserParameters(
+                temperature=g.temperature, top_k=g.top_k, top_p=g.top_p, typical_p=g.typical_p, do_sample=True,
+                seed=seed & 0xFFFFFFFFFFFFFFFF, repetition_penalty=g.repetition_penalty, watermark=False)
         return toks, g, err
 
     def _finish(self, lr, toks, g):
@@ -242,7 +249,7 @@ class RouterApp:
 
     async def _collect(self, toks, g):
         """Whole response at once: the handler sleeps until the last token instead of waking for every token."""
-        lr = self.rt.submit(toks, g.max_new_tokens, stream=False)
+        lr = self.rt.submit(toks, g.max_new_tokens, stream=False, parameters=getattr(g, "chooser", None))
         try:
             err = await lr.done
         except asyncio.CancelledError:        # the client closed the connection: stop generating for it
@@ -254,7 +261,7 @@ class RouterApp:
 
     async def _run(self, toks, g):
         """Token by token (server-sent events); the last item carries (tokens, timing headers)."""
-        lr = self.rt.submit(toks, g.max_new_tokens)
+        lr = self.rt.submit(toks, g.max_new_tokens, parameters=getattr(g, "chooser", None))
         try:
             while True:
                 ev = await lr.queue.get()

@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from .. import ops  # noqa: F401  (loads the kernel library: its absence must show when the engine is imported)
+from .. import ops
 from ..models.config import ModelConfig, get_config
 from ..models.llama import LlamaRunner, StepMeta, TPComm
 from ..models.weights import WeightSegment
@@ -134,6 +134,7 @@ class Engine:
         m = self._views(T, batch.size, P, True, lens)
         with nvtx_range("prefill"):
             toks = self.runner.forward(m)
+        toks = self._sample_rows(batch, batch.size, toks)
         out = self._tokens_to_host(toks, batch.size)
         batch.mark_prefilled()
         batch.append_tokens(out, False)
@@ -158,9 +159,35 @@ class Engine:
             toks = self.runner.tokens
         else:
             toks = self.runner.forward(self._views(Bp, Bp, self.num_pages, False, splits=splits))
+        toks = self._sample_rows(batch, B, toks)
         out = self._tokens_to_host(toks, B)
         batch.append_tokens(out, True)
         return out
+
+    def _sample_rows(self, batch: "core.Batch", B: int, toks: torch.Tensor) -> torch.Tensor:
+        """Rows whose request asked for sampling (`do_sample` with temperature / top-k / top-p / seed) draw their token
+        from this step's logits with the sampling kernel; all other rows keep the arg-max.  One extra small launch,
+        outside the CUDA graph, and only when such a row exists.  With tp > 1 every rank holds a vocabulary shard of
+        the logits, and sampling over shards is not built: those requests are served greedily."""
+        rows, temp, top_k, top_p, seeds = batch.sampling_rows()
+        if not rows:
+            return toks
+        if self.tp > 1:
+            if not getattr(self, "_warned_tp_sampling", False):
+                self._warned_tp_sampling = True
+                import logging
+                logging.getLogger("blitz.engine").warning("sampling parameters are ignored with tp > 1 (greedy decoding)")
+            return toks
+        dev = self.device
+        idx = torch.tensor(rows, dtype=torch.long, device=dev)
+        logits = self.runner.logits[:B].index_select(0, idx)
+        drawn = ops.sample(logits, torch.tensor(temp, dtype=torch.float32, device=dev),
+                           torch.tensor(top_k, dtype=torch.int32, device=dev),
+                           torch.tensor(top_p, dtype=torch.float32, device=dev),
+                           torch.tensor(seeds, dtype=torch.int64, device=dev), 0)
+        toks = toks[:B].clone()
+        toks[idx] = drawn.to(toks.dtype)
+        return toks
 
     def _capture(self, Bp: int, splits: int) -> torch.cuda.CUDAGraph:
         m = self._views(Bp, Bp, self.num_pages, False, splits=splits)

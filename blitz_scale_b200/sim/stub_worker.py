@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 
 from ..pb.schema import pb
 from ..runtime import core
-from ..worker.service import Backend
+from ..worker.service import Backend, seq_spec_from_request
 
 
 def stub_token(seed: int, request_id: int, position: int, vocab: int = 32000) -> int:
@@ -51,12 +51,7 @@ class StubBackend(Backend):
                 "ranks": {"rank": self.rank, "world": self.world}}
 
     def _specs(self, batch) -> List["core.SeqSpec"]:
-        out = []
-        for r in batch.requests:
-            toks = list(r.input_tokens) or [1] * max(1, len(r.inputs.split()))
-            out.append(core.SeqSpec(r.id, toks, r.stopping_parameters.max_new_tokens,
-                                    r.stopping_parameters.ignore_eos_token, -1))
-        return out
+        return [seq_spec_from_request(r, [1] * max(1, len(r.inputs.split()))) for r in batch.requests]
 
     def _cached(self, b) -> Optional[object]:
         ids = b.unfinished_ids()
@@ -69,6 +64,9 @@ class StubBackend(Backend):
 
     def _step(self, b, prefill: bool):
         toks = [stub_token(self.seed, rid, pl + n) for (rid, _, n), pl in zip(b.emit_info(), b.prompt_lens())]
+        rows, _temp, top_k, _top_p, seeds = b.sampling_rows()
+        for row, k, sd in zip(rows, top_k, seeds):      # stand-in for sampling: a function of the (mixed) seed, within top-k
+            toks[row] = (sd & 0x7FFFFFFF) % (k if k > 0 else self.vocab)
         if prefill:
             b.mark_prefilled()
         b.append_tokens(toks, not prefill)

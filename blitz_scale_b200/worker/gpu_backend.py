@@ -34,7 +34,7 @@ from ..parallel.agreement import LoadAgreement
 from ..pb.schema import pb
 from ..runtime import core
 from ..runtime.engine import Engine
-from .service import Backend
+from .service import Backend, seq_spec_from_request
 
 CTL_SLOT_WORDS = 16384  # page ids one transfer slot can publish
 log = logging.getLogger("blitz.worker")
@@ -112,8 +112,7 @@ class GpuBackend(Backend):
                 "ranks": {"rank": self.rank, "world": self.world, "tp": self.tp}}
 
     def _specs(self, batch) -> List["core.SeqSpec"]:
-        return [core.SeqSpec(r.id, list(r.input_tokens) or [1], r.stopping_parameters.max_new_tokens,
-                             r.stopping_parameters.ignore_eos_token, -1) for r in batch.requests]
+        return [seq_spec_from_request(r) for r in batch.requests]
 
     def _cached(self, b):
         ids = b.unfinished_ids()

@@ -276,6 +276,18 @@ async def serve(backend: Backend, host: str, port: int, urls=None, ready_event: 
         await server.stop(grace=1.0)
 
 
+def seq_spec_from_request(r, default_tokens=None) -> "core.SeqSpec":
+    """The engine's view of one `Request` of the contract: prompt ids, stopping rule and, when the request asks for
+    it (`parameters.do_sample`), the sampling parameters."""
+    from ..runtime import core
+    s = core.SeqSpec(r.id, list(r.input_tokens) or list(default_tokens or [1]), r.stopping_parameters.max_new_tokens,
+                     r.stopping_parameters.ignore_eos_token, -1)
+    if r.HasField("parameters") and r.parameters.do_sample:
+        p = r.parameters
+        s.do_sample, s.temperature, s.top_k, s.top_p, s.seed = True, float(p.temperature), int(p.top_k), float(p.top_p), int(p.seed)
+    return s
+
+
 def _response(cls, gens, **fields):
     """Response of class `cls` whose `generations` (field 1 in both response types) come either as a list of
     messages or as the wire bytes a backend encoded natively (`Batch.encode_generations`)."""

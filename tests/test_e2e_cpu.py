@@ -779,3 +779,35 @@ def test_tensor_parallel_replicas_over_grpc_and_loss_of_one_shard():
             s.set()
         await asyncio.wait(tasks, timeout=5)
     asyncio.run(go())
+
+
+def test_sampling_parameters_reach_the_worker():
+    """`do_sample` with temperature / top-k / seed travels from the HTTP request through the router into the worker's
+    sequence state: the same seed reproduces the same tokens, another seed gives others, top-k bounds the draw, and
+    greedy requests in the same batch are unaffected (the stub draws a function of the seed instead of sampling)."""
+    import aiohttp
+
+    async def go():
+        rt, backends, port, stop, tasks = await _cluster(2, ["Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+        url = f"http://127.0.0.1:{port}/generate"
+        async with aiohttp.ClientSession() as s:
+            async def gen(params):
+                body = {"input_tokens": list(range(12)), "parameters": dict({"max_new_tokens": 6, "details": True}, **params)}
+                async with s.post(url, json=body) as r:
+                    data = await r.json()
+                    assert r.status == 200, data
+                    return [t["id"] for t in data["details"]["tokens"]]
+            greedy, a1, a2, b, k = await asyncio.gather(
+                gen({}), gen({"do_sample": True, "temperature": 0.7, "seed": 11}), gen({"do_sample": True, "temperature": 0.7, "seed": 11}),
+                gen({"do_sample": True, "temperature": 0.7, "seed": 12}), gen({"do_sample": True, "top_k": 5, "seed": 3}))
+            greedy2 = await gen({})
+            async with s.post(url, json={"input_tokens": [1, 2], "parameters": {"do_sample": True, "temperature": -1.0}}) as r:
+                bad = r.status
+        await _shutdown(stop, tasks)
+        return greedy, greedy2, a1, a2, b, k, bad
+    greedy, greedy2, a1, a2, b, k, bad = asyncio.run(go())
+    assert len(greedy) == 6 and len(greedy2) == 6          # greedy requests next to sampled ones run as usual
+    assert a1 == a2 and a1 != b and a1 != greedy           # the seed decides
+    assert len(set(a1)) > 1                                # a fresh draw at every step
+    assert all(0 <= t < 5 for t in k)                      # top-k bounds the draw
+    assert bad == 422

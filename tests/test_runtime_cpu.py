@@ -375,3 +375,21 @@ def test_native_generation_reader_agrees_with_the_protobuf_library():
     for bad in (b"\x0a\x05\x08", b"\x0a\xff\xff\xff\xff\xff\xff\xff\xff\xff\xff\xff", b"\x0b\x00", b"\x0a\x03\x1a\x05\x08"):
         with pytest.raises(Exception):
             core.parse_generations(bad)                    # truncated or malformed input is refused, never read past
+
+
+def test_sampling_rows_of_a_batch():
+    pool = core.PagePool(16, 16)
+    b = core.Batch(1, pool)
+    specs = [core.SeqSpec(i, [1, 2, 3], 4) for i in range(4)]
+    specs[1].do_sample, specs[1].temperature, specs[1].top_k, specs[1].top_p, specs[1].seed = True, 0.5, 40, 0.9, 7
+    specs[3].do_sample, specs[3].temperature, specs[3].top_p, specs[3].seed = True, 0.0, 2.0, 2 ** 63 + 5   # out-of-range values
+    assert b.add_prompts(specs)
+    rows, temp, top_k, top_p, seeds = b.sampling_rows()
+    assert rows == [1, 3] and temp == [0.5, 1.0] and top_k == [40, 0] and top_p == pytest.approx([0.9, 1.0])
+    assert all(-2 ** 63 <= s < 2 ** 63 for s in seeds) and seeds[0] != seeds[1]
+    b.mark_prefilled()
+    b.append_tokens([5, 5, 5, 5], False)
+    assert b.sampling_rows()[4] != seeds                       # another draw at the next step
+    b.filter([0, 2])
+    assert b.sampling_rows() == ([], [], [], [], [])           # greedy batch: nothing to do
+    b.clear()
