@@ -11,6 +11,8 @@
 //           partials in index order and resets the ticket.
 //        c. one-kernel all-reduce: blocks of the same index on all ranks rendezvous through per-block counters in two
 //           alternating parities; slots are reused every second call without any other synchronisation.
+//        d. KV push of a partial migration: page ids and a tag published by the destination, two sources pushing
+//           disjoint layer ranges into the same transfer slot, per-layer arrival counters re-armed by the consumer.
 //      ThreadSanitizer checks that the data accesses are ordered by those atomics.
 #include <atomic>
 #include <chrono>
@@ -265,6 +267,62 @@ static void allreduce_protocol() {
     for (auto& f : rk.flags) CHECK(f.load() == 0);
 }
 
+// ---- 3d: KV push into a transfer slot, two sources (partial migration) ------------------------------------------
+// The destination publishes the page ids of the batch in its control slot, then release-stores the batch's tag.  Each
+// source acquire-waits for the tag, reads the page ids, stores the KV of ITS layers (the new instance layers [0, k),
+// the old instance layers [k, L)) into those pages and release-adds 1 to the per-layer arrival counter.  The
+// destination acquire-waits for every layer, uses the pages, re-arms the counters and moves on to the next batch in
+// the same slot.  Every wait is bounded.
+static void kv_push_protocol() {
+  constexpr int kLayers = 8, kPages = 6, kPageWords = 128, kBatches = 150, kPool = 64;
+  std::vector<uint32_t> pool(static_cast<size_t>(kLayers) * kPool * kPageWords);   // [layer][page][word]
+  std::vector<int> page_ids(kPages);
+  std::atomic<uint32_t> tag{0};
+  std::vector<std::atomic<uint32_t>> arrived(kLayers);
+  for (auto& a : arrived) a.store(0);
+  std::atomic<bool> failed{false};
+  auto wait_until = [&](auto pred) {
+    const auto t0 = std::chrono::steady_clock::now();
+    while (!pred()) {
+      if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(30)) return false;
+      std::this_thread::yield();
+    }
+    return true;
+  };
+  auto split_of = [](int batch) { return 1 + batch % (kLayers - 1); };   // k: first layer of the old instance's half
+  auto word = [](int batch, int layer, int page, int w) { return static_cast<uint32_t>(batch * 7919 + layer * 131 + page * 17 + w); };
+  auto source = [&](bool first_half) {
+    for (int b = 1; b <= kBatches; ++b) {
+      if (!wait_until([&] { return tag.load(std::memory_order_acquire) == static_cast<uint32_t>(b); })) { failed = true; return; }
+      const int k = split_of(b);
+      for (int l = first_half ? 0 : k; l < (first_half ? k : kLayers); ++l) {
+        for (int p = 0; p < kPages; ++p)
+          for (int w = 0; w < kPageWords; ++w)
+            pool[(static_cast<size_t>(l) * kPool + page_ids[p]) * kPageWords + w] = word(b, l, p, w);
+        arrived[l].fetch_add(1, std::memory_order_release);
+      }
+    }
+  };
+  std::thread newer(source, true), older(source, false);
+  std::mt19937 rng(3);
+  for (int b = 1; b <= kBatches; ++b) {
+    for (int p = 0; p < kPages; ++p) page_ids[p] = (static_cast<int>(rng() % 9) * kPages + p) % kPool;   // distinct pages
+    tag.store(static_cast<uint32_t>(b), std::memory_order_release);
+    for (int l = 0; l < kLayers; ++l)
+      if (!wait_until([&] { return arrived[l].load(std::memory_order_acquire) >= 1; })) failed = true;
+    if (failed) break;
+    for (int l = 0; l < kLayers; ++l)
+      for (int p = 0; p < kPages; ++p)
+        for (int w = 0; w < kPageWords; w += 31)
+          if (pool[(static_cast<size_t>(l) * kPool + page_ids[p]) * kPageWords + w] != word(b, l, p, w)) failed = true;
+    for (auto& a : arrived) a.store(0, std::memory_order_relaxed);   // consumed: re-arm before the next tag is published
+  }
+  if (failed) tag.store(0xFFFFFFFFu, std::memory_order_release);
+  newer.join();
+  older.join();
+  CHECK(!failed.load());
+}
+
 int main(int argc, char** argv) {
   const std::string what = argc > 1 ? argv[1] : "all";
   if (what == "all" || what == "pool") pool_fuzz();
@@ -272,6 +330,7 @@ int main(int argc, char** argv) {
   if (what == "all" || what == "flags") flag_protocol();
   if (what == "all" || what == "tickets") ticket_protocol();
   if (what == "all" || what == "allreduce") allreduce_protocol();
+  if (what == "all" || what == "kvpush") kv_push_protocol();
   std::printf("core_stress %s: OK\n", what.c_str());
   return 0;
 }

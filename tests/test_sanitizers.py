@@ -1,7 +1,7 @@
 """Host code under AddressSanitizer + UndefinedBehaviorSanitizer and under ThreadSanitizer (CPU only).
 
 Builds tests/native/core_stress.cpp twice and runs it: the page pool and the controller-in-simulator under
-ASan/UBSan, the flag, ticket and all-reduce rendezvous protocols (CPU-thread emulation of what the kernels do) under TSan.
+ASan/UBSan, the flag, ticket, all-reduce rendezvous and two-source KV-push protocols (CPU-thread emulation of what the kernels do) under TSan.
 """
 import os
 import shutil
@@ -36,7 +36,7 @@ def test_core_under_asan_ubsan(tmp_path):
 @pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
 def test_protocols_under_tsan(tmp_path):
     exe = _build(tmp_path, "cs_tsan", ["-fsanitize=thread"])
-    for part in ("flags", "tickets", "allreduce"):
+    for part in ("flags", "tickets", "allreduce", "kvpush"):
         r = subprocess.run([exe, part], capture_output=True, text=True, timeout=600,
                            env=dict(os.environ, TSAN_OPTIONS="halt_on_error=1"))
         assert r.returncode == 0 and "OK" in r.stdout and "WARNING: ThreadSanitizer" not in r.stderr, \
