@@ -12,7 +12,7 @@
 //        c. one-kernel all-reduce: blocks of the same index on all ranks rendezvous through per-block counters in two
 //           alternating parities; slots are reused every second call without any other synchronisation.
 //        d. KV push of a partial migration: page ids and a tag published by the destination, two sources pushing
-//           disjoint layer ranges into the same transfer slot, per-layer arrival counters re-armed by the consumer.
+//           disjoint layer ranges into the same transfer slot, growing per-layer arrival counters.
 //      ThreadSanitizer checks that the data accesses are ordered by those atomics.
 #include <atomic>
 #include <chrono>
@@ -271,8 +271,9 @@ static void allreduce_protocol() {
 // The destination publishes the page ids of the batch in its control slot, then release-stores the batch's tag.  Each
 // source acquire-waits for the tag, reads the page ids, stores the KV of ITS layers (the new instance layers [0, k),
 // the old instance layers [k, L)) into those pages and release-adds 1 to the per-layer arrival counter.  The
-// destination acquire-waits for every layer, uses the pages, re-arms the counters and moves on to the next batch in
-// the same slot.  Every wait is bounded.
+// destination acquire-waits until every layer's counter has reached the value it expects for this batch (the counters
+// only grow; the destination keeps the expected values), uses the pages and moves on to the next batch in the same
+// slot.  Every wait is bounded.
 static void kv_push_protocol() {
   constexpr int kLayers = 8, kPages = 6, kPageWords = 128, kBatches = 150, kPool = 64;
   std::vector<uint32_t> pool(static_cast<size_t>(kLayers) * kPool * kPageWords);   // [layer][page][word]
@@ -309,13 +310,12 @@ static void kv_push_protocol() {
     for (int p = 0; p < kPages; ++p) page_ids[p] = (static_cast<int>(rng() % 9) * kPages + p) % kPool;   // distinct pages
     tag.store(static_cast<uint32_t>(b), std::memory_order_release);
     for (int l = 0; l < kLayers; ++l)
-      if (!wait_until([&] { return arrived[l].load(std::memory_order_acquire) >= 1; })) failed = true;
+      if (!wait_until([&] { return arrived[l].load(std::memory_order_acquire) >= static_cast<uint32_t>(b); })) failed = true;
     if (failed) break;
     for (int l = 0; l < kLayers; ++l)
       for (int p = 0; p < kPages; ++p)
         for (int w = 0; w < kPageWords; w += 31)
           if (pool[(static_cast<size_t>(l) * kPool + page_ids[p]) * kPageWords + w] != word(b, l, p, w)) failed = true;
-    for (auto& a : arrived) a.store(0, std::memory_order_relaxed);   // consumed: re-arm before the next tag is published
   }
   if (failed) tag.store(0xFFFFFFFFu, std::memory_order_release);
   newer.join();
