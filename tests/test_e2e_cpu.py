@@ -413,7 +413,7 @@ def test_dropped_immigrate_reply_fails_the_operation_not_the_router():
             await ready.wait()
         cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * 3}, 1, "impl_blitz,impl_nvl",
                                              max_blocks_per_replica=4000, autoscale=False)
-        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, rpc_timeout_s=0.5)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2, rpc_timeout_s=1.0)
         lt = asyncio.create_task(rt.run())
 
         async def run_one(n_new):
