@@ -163,6 +163,7 @@ class Controller {
     if (rep.colocated || no_decode_side()) {
       rep.decode_batches.push_back(std::move(rb));  // no decode side: decode where the KV already is
     } else {
+      rb.ready_at = now;
       rep.pending_migration.push_back(std::move(rb));
     }
   }
@@ -362,7 +363,17 @@ class Controller {
     }
     expire_parked(now);
     for (int r = 0; r < num_replicas(); ++r) drive_replica(r, now);
-    for (int r = 0; r < num_replicas(); ++r) drive_migration(r, now);
+    {
+      // Batches leave for the decode side oldest first, whichever replica prefilled them.  (Scanning the replicas in
+      // index order would hand a free destination to replica 0 whenever it has something waiting and starve the
+      // others under load; the reference's per-replica watchers race for the destination's lock instead.)
+      std::vector<std::pair<double, int>> order;
+      for (int r = 0; r < num_replicas(); ++r)
+        if (!reps_[r].pending_migration.empty() && !reps_[r].migrating)
+          order.emplace_back(reps_[r].pending_migration.front().ready_at, r);
+      std::sort(order.begin(), order.end());
+      for (auto& o : order) drive_migration(o.second, now);
+    }
     drive_relayed(now);
     std::vector<Action> o;
     o.swap(out_);
@@ -448,6 +459,7 @@ class Controller {
     std::vector<uint64_t> request_ids;
     uint32_t max_tokens = 0, prompt_tokens = 0, blocks = 0;
     bool in_step = false;
+    double ready_at = 0;   // when its prefill finished (order of service in the migration queue)
   };
   struct Rep {
     ReplicaMetric m;

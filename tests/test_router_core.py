@@ -559,3 +559,36 @@ def test_client_gone_is_forgotten_in_the_queue_and_filtered_out_of_a_running_bat
     for _ in range(3):
         ctl.step(0.2)
     assert ctl.idle() and ctl.total_used_blocks() == 0 and ctl.inflight_ops() == 0
+
+
+def test_migrations_are_served_oldest_first_across_replicas():
+    """With one destination and several prefill replicas holding finished batches, the free destination goes to the
+    batch that has waited longest, not to the replica with the lowest index."""
+    cfg = _cfg(["Prefill", "Prefill", "Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+    ctl = core.Controller(cfg)
+    for i in range(3):
+        ctl.submit(E(i, 6000, 8))
+    pf = {a.replica: a for a in ctl.step(0.0) if a.type == core.ActionType.Prefill}
+    assert sorted(pf) == [0, 1, 2]
+    # replica 2 finishes first, then 1, then 0
+    for t, r in ((0.010, 2), (0.011, 1), (0.012, 0)):
+        ctl.on_prefill_done(pf[r].op_id, [core.TokenOut(pf[r].request_ids[0], 1, False)], t)
+    order = []
+    t = 0.02
+    for _ in range(3):
+        mig = [a for a in ctl.step(t) if a.type == core.ActionType.Migrate]
+        assert len(mig) == 1
+        order.append(mig[0].replica)
+        ctl.on_migrate_done(mig[0].op_id, t + 0.005)
+        t += 0.01
+    assert order == [2, 1, 0]
+    # under sustained load the tail of the prefill-to-first-decode gap stays close to its median (no starved replica)
+    cfg = _cfg(["Prefill"] * 4 + ["Decode"], "impl_blitz,impl_nvl", autoscale=False, blocks=300000)
+    cm = core.CostModel()
+    cm.kv_tokens_per_s, cm.migrate_overhead_s, cm.rpc_overhead_s = 250000.0, 0.004, 0.003
+    trace = _trace([(0, 180.0)], 6.0, seed=3, cv=2.0, inp=(900, 1100), out=(16, 32))
+    sim = core.ClusterSim(cfg, cm)
+    rep = sim.run(trace)
+    _check_conservation(rep, trace)
+    gaps = sorted(e.t_first_decode_token - e.t_first_token for e in sim.controller().finished().values() if e.t_first_decode_token > 0)
+    assert gaps[int(0.99 * len(gaps))] < 3.0 * gaps[len(gaps) // 2]
