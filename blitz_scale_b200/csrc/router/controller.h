@@ -612,7 +612,10 @@ class Controller {
       for (uint64_t other : r.incoming_batches) slot_taken = slot_taken || (other % slots == batch_id % slots);
       if (slot_taken) continue;
       if (r.m.used_blocks + need_blocks > cfg_.max_blocks_per_replica) continue;
-      if (!features_.has("decode_load_balance")) return d;  // first fit, like the reference's try_lock scan
+      // The reference takes the first decode replica whose lock is free (a try_lock scan from index 0; its
+      // `decode_load_balance` feature is declared but unimplemented), which piles every request on the first one
+      // while the others idle.  Here the least loaded one is taken; `decode_first_fit` restores the scan.
+      if (features_.has("decode_first_fit")) return d;
       if (r.m.used_blocks < best_used) { best = d; best_used = r.m.used_blocks; }
     }
     return best;

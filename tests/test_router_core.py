@@ -592,3 +592,17 @@ def test_migrations_are_served_oldest_first_across_replicas():
     _check_conservation(rep, trace)
     gaps = sorted(e.t_first_decode_token - e.t_first_token for e in sim.controller().finished().values() if e.t_first_decode_token > 0)
     assert gaps[int(0.99 * len(gaps))] < 3.0 * gaps[len(gaps) // 2]
+
+
+def test_decode_placement_prefers_the_least_loaded_replica():
+    def tbt_p99(features):
+        cfg = _cfg(["Prefill"] * 3 + ["Decode"] * 3, features, autoscale=False, blocks=30000)
+        cm = core.CostModel()
+        cm.decode_step_per_seq_s = 4e-5
+        trace = _trace([(0, 150.0)], 4.0, seed=3, cv=2.0, inp=(400, 600), out=(100, 300))
+        rep = core.ClusterSim(cfg, cm).run(trace)
+        _check_conservation(rep, trace)
+        xs = sorted(r.avg_tbt for r in rep.requests)
+        return xs[int(0.99 * len(xs))]
+    balanced, first_fit = tbt_p99("impl_blitz,impl_nvl"), tbt_p99("impl_blitz,impl_nvl,decode_first_fit")
+    assert balanced < 0.6 * first_fit          # the reference's first-fit scan piles everything on one decode replica
