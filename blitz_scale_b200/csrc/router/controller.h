@@ -695,7 +695,7 @@ class Controller {
     if (rep.busy || queue_.empty()) return false;
     if (rep.m.used_blocks > cfg_.max_blocks_per_replica) return false;
     const uint32_t free_blocks = cfg_.max_blocks_per_replica - rep.m.used_blocks;
-    auto nb = queue_.next_batch(std::nullopt, cfg_.max_prefill_tokens, cfg_.max_total_tokens, free_blocks);
+    auto nb = queue_.next_batch(std::nullopt, prefill_share(), cfg_.max_total_tokens, free_blocks);
     if (!nb) return false;
     ResidentBatch rb;
     rb.id = nb->batch.id; rb.request_ids = nb->batch.request_ids; rb.max_tokens = nb->batch.max_tokens;
@@ -708,6 +708,22 @@ class Controller {
     a.request_ids = rb.request_ids; a.max_tokens = rb.max_tokens;
     out_.push_back(a);
     return true;
+  }
+
+  // Prefill token budget of the batch an idle prefill replica takes now.  By default, as in the reference, whichever
+  // replica asks first takes everything that fits its budget.  With the feature `prefill_share_idle` the waiting
+  // prompt tokens are shared among the prefill replicas that are idle at this moment (a lone idle replica still takes
+  // a full batch).  In the simulator this lowers the median TTFT at low load (106 -> 77 ms) but leaves no idle
+  // replica for the arrivals that follow a burst (p99 170 -> 192 ms) and is neutral under load, so it is opt-in.
+  uint32_t prefill_share() const {
+    if (!features_.has("prefill_share_idle")) return cfg_.max_prefill_tokens;
+    uint32_t idle = 0;
+    for (auto& r : reps_)
+      if (r.m.state == RState::Prefill && !r.busy && r.decode_batches.empty()) ++idle;
+    if (idle <= 1) return cfg_.max_prefill_tokens;
+    const uint64_t waiting = queue_.waiting_prefill_tokens();
+    const uint32_t share = static_cast<uint32_t>((waiting + idle - 1) / idle);
+    return std::min(cfg_.max_prefill_tokens, std::max(share, queue_.front_input_len()));
   }
 
   void try_zag_prefill(int r, double now) {

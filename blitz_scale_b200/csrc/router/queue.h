@@ -115,6 +115,8 @@ class BatchQueue {
     }
   }
   uint64_t dropped() const { return dropped_; }
+  // Prompt length of the entry at the head of the queue (0 when empty).
+  uint32_t front_input_len() const { return entries_.empty() ? 0u : entries_.front().input_len; }
 
  private:
   uint32_t block_, speculate_;
@@ -187,7 +189,7 @@ class FeatureSet {
         {"fast", {}}, {"live", {}},
         {"cache_replace", {}}, {"cache_all_hit", {}}, {"cache_all_miss", {}},
         {"manually_scale", {}}, {"motiv", {}}, {"mock_transfer", {}}, {"optimize_op_loading", {}},
-        {"optimize_network_interference", {}}, {"decode_load_balance", {}}, {"decode_first_fit", {}}, {"statistic", {}}, {"ngrok", {}},
+        {"optimize_network_interference", {}}, {"decode_load_balance", {}}, {"decode_first_fit", {}}, {"prefill_share_idle", {}}, {"statistic", {}}, {"ngrok", {}},
         {"eval_all", {"impl_blitz", "impl_fast_pro", "impl_live_pro"}},
         {"eval_net", {"impl_blitz", "impl_fast_pro", "impl_live_pro", "optimize_network_interference"}},
         {"eval_fast", {"impl_blitz", "impl_fast_pro"}},
