@@ -74,6 +74,10 @@ struct ControllerConfig {
   // per destination, router_v2/src/replica/disaggregation.rs try_lock scan); more lets the RPC latency of one
   // migration overlap the transfer of another.  Concurrent migrations never share a transfer slot of the worker
   // (slot = batch id mod `kv_transfer_slots`).
+  // Sequences one worker step can carry (the workers' --max-batch-size).  No prefill batch is larger, and a decode
+  // replica is not given a batch that would take its resident sequences beyond it (the batch waits for room, like one
+  // that waits for free KV blocks).  0 = no limit.
+  uint32_t max_batch_seqs = 256;
   int max_incoming_migrations = 1;
   int kv_transfer_slots = 8;
   double quarantine_ms = 5000;  // a lost replica is not chosen for scale-up again before this much time has passed
@@ -308,10 +312,10 @@ class Controller {
     nrep.busy = !nrep.inflight_zag.empty();
     Relayed r;
     r.batch = rb; r.new_replica = neu; r.old_replica = old; r.next_layer = std::max(0, next_layer); r.blocks = rb.blocks;
-    r.target = pick_decode_target(rb.blocks, rb.id);
+    r.target = pick_decode_target(rb.blocks, rb.id, rb.request_ids.size());
     // both replicas hold KV pages of this batch until their half has migrated
     reps_[old].m.used_blocks += rb.blocks;
-    if (r.target >= 0) acquire_target(r.target, rb.blocks, rb.id);
+    if (r.target >= 0) acquire_target(r.target, rb.blocks, rb.id, rb.request_ids.size());
     Action a = make_simple(ActionType::PrefillPP, old, rb.id);
     a.op_id = new_op(ActionType::PrefillPP, old, neu, rb);
     a.peer = neu; a.num_layer = r.next_layer; a.request_ids = rb.request_ids; a.max_tokens = rb.max_tokens;
@@ -478,6 +482,7 @@ class Controller {
     int partner = -1;         // OldPrefill <-> NewPrefill pairing
     int incoming = 0;         // migrations in flight towards this replica
     std::vector<uint64_t> incoming_batches;  // their batch ids (for the transfer-slot rule)
+    uint32_t incoming_seqs = 0;              // sequences of those batches
   };
   struct Op {
     ActionType kind;
@@ -601,13 +606,19 @@ class Controller {
       if (it->id == batch_id) { rep.inflight_zag.erase(it); break; }
     rep.busy = !rep.inflight_zag.empty();
   }
-  int pick_decode_target(uint32_t need_blocks, uint64_t batch_id) const {
+  static uint32_t resident_seqs(const Rep& r) {
+    size_t n = r.incoming_seqs;
+    for (auto& b : r.decode_batches) n += b.request_ids.size();
+    return static_cast<uint32_t>(n);
+  }
+  int pick_decode_target(uint32_t need_blocks, uint64_t batch_id, size_t nseqs = 0) const {
     int best = -1;
     uint32_t best_used = UINT32_MAX;
     const uint64_t slots = static_cast<uint64_t>(std::max(1, cfg_.kv_transfer_slots));
     for (int d = 0; d < num_replicas(); ++d) {
       const Rep& r = reps_[d];
       if (r.m.state != RState::Decode || r.m.dst_busy) continue;
+      if (cfg_.max_batch_seqs > 0 && resident_seqs(r) > 0 && resident_seqs(r) + nseqs > cfg_.max_batch_seqs) continue;
       bool slot_taken = false;
       for (uint64_t other : r.incoming_batches) slot_taken = slot_taken || (other % slots == batch_id % slots);
       if (slot_taken) continue;
@@ -621,9 +632,11 @@ class Controller {
     return best;
   }
   bool target_full(const Rep& r) const { return r.incoming >= std::max(1, cfg_.max_incoming_migrations); }
-  void acquire_target(int d, uint32_t blocks, uint64_t batch_id) {
+  void acquire_target(int d, uint32_t blocks, uint64_t batch_id, size_t nseqs = 0) {
     reps_[d].incoming += 1;
     reps_[d].incoming_batches.push_back(batch_id);
+    reps_[d].incoming_seqs += static_cast<uint32_t>(nseqs);
+    incoming_seqs_of_[batch_id] = static_cast<uint32_t>(nseqs);
     reps_[d].m.dst_busy = reps_[d].m.state != RState::Decode || target_full(reps_[d]);
     reps_[d].m.used_blocks += blocks;
   }
@@ -632,6 +645,11 @@ class Controller {
     r.incoming = std::max(0, r.incoming - 1);
     auto it = std::find(r.incoming_batches.begin(), r.incoming_batches.end(), batch_id);
     if (it != r.incoming_batches.end()) r.incoming_batches.erase(it);
+    auto sq = incoming_seqs_of_.find(batch_id);
+    if (sq != incoming_seqs_of_.end()) {
+      r.incoming_seqs = r.incoming_seqs >= sq->second ? r.incoming_seqs - sq->second : 0;
+      incoming_seqs_of_.erase(sq);
+    }
     r.m.dst_busy = r.m.state != RState::Decode || target_full(r);
   }
   void finish_relayed_target(Relayed& r) {
@@ -695,7 +713,7 @@ class Controller {
     if (rep.busy || queue_.empty()) return false;
     if (rep.m.used_blocks > cfg_.max_blocks_per_replica) return false;
     const uint32_t free_blocks = cfg_.max_blocks_per_replica - rep.m.used_blocks;
-    auto nb = queue_.next_batch(std::nullopt, prefill_share(), cfg_.max_total_tokens, free_blocks);
+    auto nb = queue_.next_batch(std::nullopt, prefill_share(), cfg_.max_total_tokens, free_blocks, cfg_.max_batch_seqs);
     if (!nb) return false;
     ResidentBatch rb;
     rb.id = nb->batch.id; rb.request_ids = nb->batch.request_ids; rb.max_tokens = nb->batch.max_tokens;
@@ -736,7 +754,7 @@ class Controller {
     if (rep.inflight_zag.size() >= limit || queue_.empty()) return;
     if (rep.m.used_blocks > cfg_.max_blocks_per_replica) return;
     auto nb = queue_.next_batch(std::nullopt, cfg_.max_prefill_tokens, cfg_.max_total_tokens,
-                                cfg_.max_blocks_per_replica - rep.m.used_blocks);
+                                cfg_.max_blocks_per_replica - rep.m.used_blocks, cfg_.max_batch_seqs);
     if (!nb) return;
     ResidentBatch rb;
     rb.id = nb->batch.id; rb.request_ids = nb->batch.request_ids; rb.max_tokens = nb->batch.max_tokens;
@@ -820,7 +838,7 @@ class Controller {
     Rep& rep = reps_[src];
     if (rep.migrating || rep.pending_migration.empty()) return;
     ResidentBatch& b = rep.pending_migration.front();
-    const int dst = pick_decode_target(b.blocks, b.id);
+    const int dst = pick_decode_target(b.blocks, b.id, b.request_ids.size());
     if (dst < 0) {
       // no decode side is left (it was lost after this batch was queued for it): decode where the KV already is,
       // as a prefill that completes in that situation does
@@ -830,7 +848,7 @@ class Controller {
       }
       return;
     }
-    acquire_target(dst, b.blocks, b.id);
+    acquire_target(dst, b.blocks, b.id, b.request_ids.size());
     rep.migrating = true;
     Action a = make_simple(ActionType::Migrate, src, b.id);
     a.peer = dst; a.request_ids = b.request_ids; a.max_tokens = b.max_tokens;
@@ -845,9 +863,9 @@ class Controller {
     for (auto& kv : relayed_) {
       Relayed& r = kv.second;
       if (r.target < 0) {
-        r.target = pick_decode_target(r.blocks, r.batch.id);
+        r.target = pick_decode_target(r.blocks, r.batch.id, r.batch.request_ids.size());
         if (r.target < 0) continue;
-        acquire_target(r.target, r.blocks, r.batch.id);
+        acquire_target(r.target, r.blocks, r.batch.id, r.batch.request_ids.size());
       }
       auto emit = [&](int part, int from) {
         Action a = make_simple(ActionType::MigratePartial, from, r.batch.id);
@@ -1234,6 +1252,7 @@ class Controller {
         release_blocks(x.old_replica, x.blocks);
         out_.push_back(make_simple(ActionType::ClearCache, x.old_replica, x.batch.id));
       }
+      if (x.target == r) incoming_seqs_of_.erase(x.batch.id);
       if (x.target >= 0 && x.target != r) {
         finish_relayed_target(x);
         out_.push_back(make_simple(ActionType::ClearCache, x.target, x.batch.id));
@@ -1267,6 +1286,7 @@ class Controller {
           release_blocks(other, o.batch.blocks);
           if (o.replica == r) unlock_target(other, o.batch.id);
           else reps_[other].migrating = false;
+          incoming_seqs_of_.erase(o.batch.id);
           out_.push_back(make_simple(ActionType::ClearCache, other, o.batch.id));
           cancel(id, o.batch.id, {other});
           break;
@@ -1300,6 +1320,7 @@ class Controller {
     rep.busy = rep.migrating = rep.relay_wait = false;
     rep.incoming = 0;
     rep.incoming_batches.clear();
+    rep.incoming_seqs = 0;
     rep.m.used_blocks = 0;
     rep.m.flying_partial = 0;
     rep.m.model_loaded = false;
@@ -1365,6 +1386,7 @@ class Controller {
   std::map<uint64_t, Op> ops_;
   std::map<uint64_t, Relayed> relayed_;
   std::map<uint64_t, Cancelled> cancelled_;
+  std::map<uint64_t, uint32_t> incoming_seqs_of_;   // batch on its way to a decode replica -> its sequences
   std::vector<Action> out_;
   std::vector<Delivery> deliveries_;
   bool compact_deliveries_ = false;

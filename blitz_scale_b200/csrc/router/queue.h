@@ -64,8 +64,10 @@ class BatchQueue {
     std::vector<RequestEntry> entries;
   };
 
+  // `max_size` (0 = no limit) caps the number of requests in the batch: a worker's step handles a bounded number of
+  // sequences whatever their lengths.
   std::optional<Next> next_batch(std::optional<size_t> min_size, uint32_t prefill_token_budget, uint32_t token_budget,
-                                 std::optional<uint32_t> block_budget) {
+                                 std::optional<uint32_t> block_budget, size_t max_size = 0) {
     if (entries_.empty()) return std::nullopt;
     if (min_size && entries_.size() < *min_size) return std::nullopt;
     Next out;
@@ -84,7 +86,8 @@ class BatchQueue {
       const bool over_blocks = block_budget && (max_req + max_tokens > *block_budget * block_);
       const bool over_prefill = prefill_tokens + e.input_len > prefill_token_budget;
       const bool over_total = max_req + speculate_ > token_budget;
-      if (over_blocks || over_prefill || over_total) {
+      const bool over_size = max_size > 0 && out.entries.size() >= max_size;
+      if (over_blocks || over_prefill || over_total || over_size) {
         entries_.push_front(e);
         break;
       }

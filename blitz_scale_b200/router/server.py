@@ -433,6 +433,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--health-misses", type=int, default=2, help="consecutive missed pings that declare a replica lost")
     ap.add_argument("--rpc-timeout-ms", type=float, default=300000.0,
                     help="deadline of every worker RPC; a reply that never comes then counts as a failed replica (0 = none)")
+    ap.add_argument("--max-batch-size", type=int, default=256,
+                    help="sequences one worker step can carry; must equal the workers' --max-batch-size (0 = no limit)")
     ap.add_argument("--decode-steps-per-call", type=int, default=1,
                     help="decode steps a worker runs per DecodeV2 call (1 = one round trip per token, as the reference)")
     ap.add_argument("--max-incoming-migrations", type=int, default=1,
@@ -493,6 +495,7 @@ def main(argv=None) -> None:
         migration_upper=a.migration_upper_bound, min_prefill=a.min_prefill_num, max_prefill=a.max_prefill_num,
         min_decode=a.min_decode_num, max_decode=a.max_decode_num, scale_down_threshold_ms=a.scale_down_threshold_millis)
     cfg.quarantine_ms = a.quarantine_ms
+    cfg.max_batch_seqs = max(0, a.max_batch_size)
     cfg.max_incoming_migrations = max(1, a.max_incoming_migrations)
     layers = get_config(a.model_name).layers
     try:

@@ -126,6 +126,8 @@ class Engine:
         """Run the prompt of every request in `batch`, cache its K/V and return the first token of each."""
         if not self.status.fully_loaded():
             raise RuntimeError("model parameters are not loaded")
+        if batch.size > self.max_batch:
+            raise ValueError(f"prefill batch of {batch.size} sequences exceeds max_batch={self.max_batch}")
         T, P = batch.fill_prefill(self.host_np, self.layout)
         if T > self.max_batch_tokens:
             raise ValueError(f"prefill of {T} tokens exceeds max_batch_tokens={self.max_batch_tokens}")
@@ -145,6 +147,8 @@ class Engine:
     def decode(self, batch: "core.Batch") -> List[int]:
         """One decode step for every request in `batch` (already extended if several were merged)."""
         B = batch.size
+        if B > self.max_batch:
+            raise ValueError(f"decode batch of {B} sequences exceeds max_batch={self.max_batch}")
         Bp = _bucket(B) if self.use_graphs else B
         Bp = min(Bp, self.max_batch)
         splits = self.choose_splits(Bp, batch.max_seq_len())

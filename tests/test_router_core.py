@@ -606,3 +606,41 @@ def test_decode_placement_prefers_the_least_loaded_replica():
         return xs[int(0.99 * len(xs))]
     balanced, first_fit = tbt_p99("impl_blitz,impl_nvl"), tbt_p99("impl_blitz,impl_nvl,decode_first_fit")
     assert balanced < 0.6 * first_fit          # the reference's first-fit scan piles everything on one decode replica
+
+
+def test_sequence_cap_of_a_worker_step():
+    # the queue never forms a batch with more requests than one worker step carries
+    q = core.BatchQueue(64)
+    for i in range(10):
+        q.append(E(i, 8, 4))
+    nb = q.next_batch(None, 8192, 16000, None, 4)
+    assert nb.batch.request_ids == [0, 1, 2, 3] and len(q) == 6
+    assert len(q.next_batch(None, 8192, 16000).batch.request_ids) == 6          # no cap: everything that fits the budgets
+    # a decode replica is not handed more sequences than it can step; the batch waits and goes elsewhere or later
+    cfg = _cfg(["Prefill", "Prefill", "Decode", "Decode"], "impl_blitz,impl_nvl,decode_first_fit", autoscale=False, max_batch_seqs=4)
+    ctl = core.Controller(cfg)
+    for i in range(8):
+        ctl.submit(E(i, 8, 50))
+    pf = [a for a in ctl.step(0.0) if a.type == core.ActionType.Prefill]
+    assert [len(a.request_ids) for a in pf] == [4, 4]                          # capped prefill batches
+    for a in pf:
+        ctl.on_prefill_done(a.op_id, [core.TokenOut(i, 1, False) for i in a.request_ids], 0.01)
+    first = [a for a in ctl.step(0.02) if a.type == core.ActionType.Migrate]
+    assert len(first) == 2 and sorted(a.peer for a in first) == [2, 3]         # first fit would have sent both to replica 2
+    for a in first:
+        ctl.on_migrate_done(a.op_id, 0.03)
+    # a third batch finds both decode replicas full and waits
+    for i in range(8, 10):
+        ctl.submit(E(i, 8, 50))
+    acts = ctl.step(0.04)
+    pf = [a for a in acts if a.type == core.ActionType.Prefill]
+    ctl.on_prefill_done(pf[0].op_id, [core.TokenOut(i, 1, False) for i in pf[0].request_ids], 0.05)
+    assert not [a for a in ctl.step(0.06) if a.type == core.ActionType.Migrate]
+    assert ctl.waiting_migration_tokens() == 16
+    # when a request of a decode replica finishes, room opens up
+    dec = [a for a in ctl.step(0.07) + acts if a.type == core.ActionType.Decode]
+    d2 = [a for a in dec if a.replica == 2][0]
+    ids = list(d2.request_ids)
+    ctl.on_decode_done(d2.op_id, [core.TokenOut(ids[0], 2, True), core.TokenOut(ids[1], 2, True)] + [core.TokenOut(i, 2, False) for i in ids[2:]], 0.08)
+    mig = [a for a in ctl.step(0.09) if a.type == core.ActionType.Migrate]
+    assert len(mig) == 1 and mig[0].peer == 2

@@ -29,6 +29,7 @@ def test_requests_and_blocks_are_conserved(feat, seed, n_inactive, burst, cv, ki
     cfg.features = feat
     cfg.max_blocks_per_replica = 3000
     cfg.max_incoming_migrations = max_incoming
+    cfg.max_batch_seqs = [0, 6, 256][seed % 3]          # a worker step's sequence cap, sometimes tight
     p = cfg.planner
     p.tokens_prefilled_per_sec, p.tokens_transferred_per_sec = int(prefill_rate * 0.2), 500000
     p.max_prefill, p.max_decode = len(states) - 1, len(states) - 1
