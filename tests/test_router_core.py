@@ -596,7 +596,7 @@ def test_migrations_are_served_oldest_first_across_replicas():
 
 def test_decode_placement_prefers_the_least_loaded_replica():
     def tbt_p99(features):
-        cfg = _cfg(["Prefill"] * 3 + ["Decode"] * 3, features, autoscale=False, blocks=30000)
+        cfg = _cfg(["Prefill"] * 3 + ["Decode"] * 3, features, autoscale=False, blocks=30000, max_batch_seqs=0)
         cm = core.CostModel()
         cm.decode_step_per_seq_s = 4e-5
         trace = _trace([(0, 150.0)], 4.0, seed=3, cv=2.0, inp=(400, 600), out=(100, 300))
