@@ -938,6 +938,19 @@ class Controller {
     }
     v.waiting_prefill_tokens = queue_.waiting_prefill_tokens();
     ScaleTarget t = plan_scale(cfg_.planner, v);
+    // The reference sizes the decode side by KV memory only.  A decode replica is also full when it holds as many
+    // sequences as a worker step carries: when the decode side is nearly full in that sense (or prefilled batches
+    // already wait for room), ask for one more decode replica, and never shrink it then.
+    if (cfg_.max_batch_seqs > 0 && v.num_decode > 0) {
+      uint64_t seqs = 0, waiting = 0;
+      for (auto& r : reps_) {
+        if (is_decode_side(r.m.state)) seqs += resident_seqs(r);
+        for (auto& b : r.pending_migration) waiting += b.request_ids.size();
+      }
+      const double util = static_cast<double>(seqs + waiting) / (static_cast<double>(v.num_decode) * cfg_.max_batch_seqs);
+      if (util > cfg_.planner.decode_upper && v.num_decode < cfg_.planner.max_decode) t.d_decode = std::max(t.d_decode, 1);
+      else if (util > cfg_.planner.decode_lower) t.d_decode = std::max(t.d_decode, 0);
+    }
     last_target_ = t;
     gauges_["blitz_prefill_replica"] = v.num_prefill;
     gauges_["blitz_decode_replica"] = v.num_decode;

@@ -644,3 +644,13 @@ def test_sequence_cap_of_a_worker_step():
     ctl.on_decode_done(d2.op_id, [core.TokenOut(ids[0], 2, True), core.TokenOut(ids[1], 2, True)] + [core.TokenOut(i, 2, False) for i in ids[2:]], 0.08)
     mig = [a for a in ctl.step(0.09) if a.type == core.ActionType.Migrate]
     assert len(mig) == 1 and mig[0].peer == 2
+
+
+def test_planner_adds_a_decode_replica_when_the_sequence_cap_is_reached():
+    """Many short requests fill a decode replica's step long before its KV memory: the planner scales the decode side on
+    that signal too, and everything completes."""
+    cfg = _cfg(["Prefill", "Decode"] + ["Inactive"] * 3, "impl_blitz,impl_nvl", blocks=30000, max_batch_seqs=64, max_p=2, max_d=3)
+    trace = _trace([(0, 120.0)], 5.0, seed=3, inp=(32, 128), out=(100, 200))
+    rep = core.ClusterSim(cfg, core.CostModel()).run(trace)
+    _check_conservation(rep, trace)
+    assert sum(1 for l in rep.log if l.endswith("=> LoadingDecode")) >= 1
