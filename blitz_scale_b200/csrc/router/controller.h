@@ -713,7 +713,14 @@ class Controller {
     if (rep.busy || queue_.empty()) return false;
     if (rep.m.used_blocks > cfg_.max_blocks_per_replica) return false;
     const uint32_t free_blocks = cfg_.max_blocks_per_replica - rep.m.used_blocks;
-    auto nb = queue_.next_batch(std::nullopt, prefill_share(), cfg_.max_total_tokens, free_blocks, cfg_.max_batch_seqs);
+    size_t max_size = cfg_.max_batch_seqs;
+    if (max_size > 0 && (rep.colocated || no_decode_side())) {
+      // what it prefills stays here for decoding: leave room for it in this replica's decode step
+      const uint32_t held = resident_seqs(rep);
+      if (held >= max_size) return false;
+      max_size -= held;
+    }
+    auto nb = queue_.next_batch(std::nullopt, prefill_share(), cfg_.max_total_tokens, free_blocks, max_size);
     if (!nb) return false;
     ResidentBatch rb;
     rb.id = nb->batch.id; rb.request_ids = nb->batch.request_ids; rb.max_tokens = nb->batch.max_tokens;

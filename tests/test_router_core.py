@@ -654,3 +654,31 @@ def test_planner_adds_a_decode_replica_when_the_sequence_cap_is_reached():
     rep = core.ClusterSim(cfg, core.CostModel()).run(trace)
     _check_conservation(rep, trace)
     assert sum(1 for l in rep.log if l.endswith("=> LoadingDecode")) >= 1
+
+
+def test_colocated_replica_never_exceeds_its_step_size():
+    cfg = _cfg(["Normal"], "impl_blitz,impl_nvl", autoscale=False, max_batch_seqs=8)
+    trace = _trace([(0, 200.0)], 2.0, seed=1, inp=(16, 64), out=(30, 60))
+    sim = core.ClusterSim(cfg, core.CostModel())
+    rep = sim.run(trace)
+    _check_conservation(rep, trace)
+    # driving the core by hand: what the replica holds never exceeds the cap, and new prompts come in as others finish
+    ctl = core.Controller(cfg)
+    for i in range(30):
+        ctl.submit(E(i, 16, 10))
+    held, t, peak, prefills = set(), 0.0, 0, 0
+    for _ in range(300):
+        t += 0.001
+        for a in ctl.step(t):
+            if a.type == core.ActionType.Deliver and a.final:
+                held.discard(a.request_id)
+            elif a.type == core.ActionType.Prefill:
+                held |= set(a.request_ids)
+                prefills += 1
+                assert len(held) <= 8
+                ctl.on_prefill_done(a.op_id, [core.TokenOut(i, 1, False) for i in a.request_ids], t)
+            elif a.type == core.ActionType.Decode:
+                assert len(a.request_ids) <= 8
+                ctl.on_decode_done(a.op_id, [core.TokenOut(i, 2, False) for i in a.request_ids], t)
+        peak = max(peak, len(held))
+    assert peak == 8 and prefills >= 4 and ctl.idle() and not held
