@@ -140,7 +140,7 @@ def run_router(a, world, states, cfg_model, backend):
                      tokens_transferred_per_sec=5000000, max_prefill=world - 1, max_decode=1, min_prefill=1, min_decode=1)
     cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
                                          max_blocks_per_replica=a.pages - 64, block_size=64, max_prefill_tokens=8192,
-                                         model_layers=cfg_model.layers, **extra)
+                                         model_layers=cfg_model.layers, max_batch_seqs=256, **extra)
     cfg.max_incoming_migrations = max(1, a.max_incoming_migrations)
     g = torch.Generator().manual_seed(5)
     n_base, n_burst = int(a.base_rate * a.base_s), int(a.burst_rate * a.burst_s)

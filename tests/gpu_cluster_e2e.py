@@ -114,7 +114,7 @@ def run_router(case, world, states, base_port) -> int:
              "live": "impl_blitz,impl_nvl,impl_live,manually_scale"}[case]
     cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
                                          max_blocks_per_replica=200, block_size=16, max_prefill_tokens=1024,
-                                         model_layers=2, zigzag_req_limit=2, zigzag_req_floor=2)
+                                         model_layers=2, zigzag_req_limit=2, zigzag_req_floor=2, max_batch_seqs=16)
 
     async def go():
         rt = RouterRuntime(cfg, [f"127.0.0.1:{base_port + r}" for r in range(world)], model_layers=2)
