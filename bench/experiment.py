@@ -89,7 +89,7 @@ def commands(inst: dict, d: Path) -> dict:
               "migration-lower-bound", "migration-upper-bound", "min-prefill-num", "max-prefill-num", "min-decode-num",
               "max-decode-num", "scale-down-threshold-millis", "mock-load-millis", "max-input-length", "max-total-tokens",
               "decode-steps-per-call", "max-incoming-migrations", "health-interval-ms", "health-misses", "rpc-timeout-ms",
-              "quarantine-ms", "planner-horizon-ms", "otlp-endpoint"):
+              "quarantine-ms", "planner-horizon-ms", "otlp-endpoint", "max-batch-size"):
         kk = k.replace("-", "_")
         if kk in r:
             router_args["--" + k] = r[kk]
