@@ -411,7 +411,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-input-length", type=int, default=4095)
     ap.add_argument("--max-total-tokens", type=int, default=4096)
     ap.add_argument("--max-batch-prefill-tokens", type=int, default=8192)
-    ap.add_argument("--max-blocks-per-replica", type=int, default=30000)
+    ap.add_argument("--max-blocks-per-replica", type=int, default=4000,
+                    help="KV pages the router lets one replica hold; keep it a little below the workers' --num-total-blocks "
+                         "(default 4096) or a worker runs out of pages")
     ap.add_argument("--planner-horizon-ms", type=float, default=1000.0,
                     help="how much queued prefill work per replica the planner tolerates before it adds one, as time: the "
                          "capacity it plans with is tokens-prefilled-per-sec x horizon.  1000 = the per-second rule of the "
