@@ -159,6 +159,8 @@ void bind_router(py::module_& m) {
         t.reserve(g.request_ids.size());
         for (size_t i = 0; i < g.request_ids.size(); ++i) t.push_back({g.request_ids[i], g.tokens[i], g.finished[i]});
         c.on_decode_done(op, t, now); })
+      .def("limit_blocks_per_replica", &Controller::limit_blocks_per_replica)
+      .def_property_readonly("max_blocks_per_replica", &Controller::max_blocks_per_replica)
       .def("set_reachable", &Controller::set_reachable).def("reachable", &Controller::reachable)
       .def("take_flows", &Controller::take_flows).def("waiting_migration_tokens", &Controller::waiting_migration_tokens)
       .def("set_compact_deliveries", &Controller::set_compact_deliveries)

@@ -339,6 +339,15 @@ class Controller {
     if (ops_.count(op_id)) lose_replica(issued_to, now);  // the named replica was no participant after all
   }
 
+  // The workers' answer to Warmup (how many KV tokens a rank can hold) bounds what the router lets a replica hold.
+  void limit_blocks_per_replica(uint32_t blocks) {
+    if (blocks > 0 && blocks < cfg_.max_blocks_per_replica) {
+      cfg_.max_blocks_per_replica = blocks;
+      cfg_.planner.max_blocks_per_replica = blocks;
+    }
+  }
+  uint32_t max_blocks_per_replica() const { return cfg_.max_blocks_per_replica; }
+
   // A shell with a failure detector reports whether a replica that is out of service answers again; the planner
   // loads into a lost replica only once it does (and its quarantine has passed).
   void set_reachable(int replica, bool ok) {

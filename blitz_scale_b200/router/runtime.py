@@ -163,7 +163,26 @@ class RouterRuntime:
                         self._missed[rep] = 0
                         self.wake.set()
 
+    async def _warmup(self) -> None:
+        """Ask every worker how many KV tokens it can hold (the Warmup call of the contract; the reference's router
+        does the same at start, router_v2/src/replica/disaggregation.rs:679) and never plan for more pages per replica
+        than the smallest answer, less a little headroom.  Workers that do not answer are left to the failure handling."""
+        async def ask(r):
+            try:
+                return (await self.stubs[r].warmup()).max_supported_total_tokens
+            except Exception:  # noqa: BLE001
+                return 0
+        tokens = [t for t in await asyncio.gather(*[ask(r) for r in range(len(self.stubs))]) if t > 0]
+        if tokens:
+            blocks = min(tokens) // max(1, self.cfg.block_size)
+            before = self.ctl.max_blocks_per_replica
+            self.ctl.limit_blocks_per_replica(max(1, blocks - max(1, blocks // 64)))
+            if self.ctl.max_blocks_per_replica != before:
+                log.warning("workers hold %d KV pages: the limit per replica is lowered from %d to %d", blocks, before,
+                            self.ctl.max_blocks_per_replica)
+
     async def run(self) -> None:
+        await self._warmup()
         last_metrics = 0.0
         if self.health_interval_s > 0:
             self._spawn(self._health_loop())

@@ -811,3 +811,27 @@ def test_sampling_parameters_reach_the_worker():
     assert len(set(a1)) > 1                                # a fresh draw at every step
     assert all(0 <= t < 5 for t in k)                      # top-k bounds the draw
     assert bad == 422
+
+
+def test_router_learns_the_workers_kv_capacity_at_start():
+    async def go():
+        ports = _free_ports(2)
+        stop, tasks = asyncio.Event(), []
+        for r in range(2):
+            ready = asyncio.Event()
+            b = StubBackend(r, 2, ready=True, num_pages=512 if r == 0 else 300, page_size=64)
+            tasks.append(asyncio.create_task(serve(b, "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            await ready.wait()
+        cfg = controller_config_from_cluster({"init_states": ["Prefill", "Decode"], "machines": [0, 0]}, 1, "impl_blitz,impl_nvl",
+                                             max_blocks_per_replica=30000, block_size=64)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2)
+        lt = asyncio.create_task(rt.run())
+        lr = rt.submit(list(range(20)), 3, stream=False)
+        assert (await asyncio.wait_for(lr.done, 20)) is None
+        limit = rt.ctl.max_blocks_per_replica
+        await rt.stop()
+        lt.cancel()
+        stop.set()
+        await asyncio.wait(tasks, timeout=5)
+        return limit
+    assert asyncio.run(go()) == 300 - 300 // 64          # the smaller pool, less headroom; not the configured 30000
