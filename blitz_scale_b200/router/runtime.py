@@ -132,36 +132,41 @@ class RouterRuntime:
         self.wake.set()
 
     # ------------------------------------------------------------------ main loop
+    async def _ping(self, rep: int) -> bool:
+        """True when every rank of the replica answers Health within one interval."""
+        try:
+            await asyncio.wait_for(asyncio.gather(*[self.stubs[r].health(timeout=self.health_interval_s)
+                                                    for r in self._ranks(rep)]), timeout=self.health_interval_s)
+            return True
+        except Exception:  # noqa: BLE001 - any failure to answer counts as a miss
+            return False
+
     async def _health_loop(self) -> None:
         while not self.stopped:
             await asyncio.sleep(self.health_interval_s)
-            for rep in range(self.ctl.num_replicas):
+            # replicas in service, and lost ones that may have come back (a restarted worker); all pinged at once, so
+            # one that is away does not delay the verdict on the others
+            reps = [rep for rep in range(self.ctl.num_replicas)
+                    if self.ctl.state_name(rep) != "Inactive" or not self.ctl.reachable(rep)]
+            answers = await asyncio.gather(*[self._ping(rep) for rep in reps])
+            for rep, ok in zip(reps, answers):
                 if self.ctl.state_name(rep) == "Inactive":
                     self._missed.pop(rep, None)
-                    if not self.ctl.reachable(rep):
-                        # a lost replica is pinged until it answers again (a restarted worker); only then may the
-                        # planner load into it
-                        try:
-                            await asyncio.wait_for(asyncio.gather(*[self.stubs[r].health(timeout=self.health_interval_s)
-                                                                    for r in self._ranks(rep)]), timeout=self.health_interval_s)
-                            log.info("replica %d answers again", rep)
-                            self.ctl.set_reachable(rep, True)
-                        except Exception:  # noqa: BLE001
-                            pass
+                    if ok and not self.ctl.reachable(rep):
+                        log.info("replica %d answers again", rep)
+                        self.ctl.set_reachable(rep, True)     # only now may the planner load into it
                     continue
-                try:
-                    await asyncio.wait_for(asyncio.gather(*[self.stubs[r].health(timeout=self.health_interval_s)
-                                                            for r in self._ranks(rep)]), timeout=self.health_interval_s)
+                if ok:
                     self._missed[rep] = 0
-                except Exception:  # noqa: BLE001 - any failure to answer counts as a miss
-                    self._missed[rep] = self._missed.get(rep, 0) + 1
-                    if self._missed[rep] >= self.health_misses:
-                        log.error("replica %d missed %d heartbeats: declared lost", rep, self._missed[rep])
-                        self.ctl.on_replica_unhealthy(rep, self.now())
-                        self.ctl.set_reachable(rep, False)
-                        self._purge_replica(rep)
-                        self._missed[rep] = 0
-                        self.wake.set()
+                    continue
+                self._missed[rep] = self._missed.get(rep, 0) + 1
+                if self._missed[rep] >= self.health_misses:
+                    log.error("replica %d missed %d heartbeats: declared lost", rep, self._missed[rep])
+                    self.ctl.on_replica_unhealthy(rep, self.now())
+                    self.ctl.set_reachable(rep, False)
+                    self._purge_replica(rep)
+                    self._missed[rep] = 0
+                    self.wake.set()
 
     async def _warmup(self) -> None:
         """Ask every worker how many KV tokens it can hold (the Warmup call of the contract; the reference's router
