@@ -331,8 +331,14 @@ class RouterApp:
                                   "replicas": [self.rt.ctl.state_name(i) for i in range(self.rt.ctl.num_replicas)]})
 
     async def health(self, req):
+        """Healthy when every replica in service answers (replicas that are out of service, parked or lost, do not
+        count against the router) and at least one prefill-capable and one decode-capable replica exist."""
+        ctl = self.rt.ctl
+        serving = [r for r in range(ctl.num_replicas) if ctl.state_name(r) != "Inactive"]
+        if not serving:
+            return web.json_response({"error": "unhealthy: no replica in service", "error_type": "healthcheck"}, status=503)
         try:
-            await asyncio.gather(*[s.health() for s in self.rt.stubs])
+            await asyncio.gather(*[self.rt.stubs[k].health() for r in serving for k in self.rt._ranks(r)])
             return web.Response(text="ok")
         except Exception as e:  # noqa: BLE001
             return web.json_response({"error": f"unhealthy: {e}", "error_type": "healthcheck"}, status=503)
