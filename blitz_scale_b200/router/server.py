@@ -331,8 +331,8 @@ class RouterApp:
                                   "replicas": [self.rt.ctl.state_name(i) for i in range(self.rt.ctl.num_replicas)]})
 
     async def health(self, req):
-        """Healthy when every replica in service answers (replicas that are out of service, parked or lost, do not
-        count against the router) and at least one prefill-capable and one decode-capable replica exist."""
+        """Healthy when at least one replica is in service and every replica in service answers (replicas that are
+        out of service, parked or lost, do not count against the router)."""
         ctl = self.rt.ctl
         serving = [r for r in range(ctl.num_replicas) if ctl.state_name(r) != "Inactive"]
         if not serving:
