@@ -105,10 +105,14 @@ def slo_table(records: Iterable[dict]) -> dict:
     pct = lambda xs, q: sorted(xs)[min(len(xs) - 1, int(q * len(xs)))] if xs else 0.0
     ttft = [r["first_token_time"] for r in ok]
     tbt = [r["max_time_between_tokens"] for r in ok]
+    # prefill token -> first decode token: contains the KV migration, reported apart from the time between tokens
+    gap = [r["first_decode_token_time"] - r["first_token_time"] for r in ok
+           if r.get("first_decode_token_time", 0) > r.get("first_token_time", 0)]
     return {
         "requests": len(ok),
         "ttft_ms": {"p50": pct(ttft, .5), "p90": pct(ttft, .9), "p99": pct(ttft, .99)},
         "max_tbt_ms": {"p50": pct(tbt, .5), "p90": pct(tbt, .9), "p99": pct(tbt, .99)},
+        "first_decode_gap_ms": {"p50": pct(gap, .5), "p90": pct(gap, .9), "p99": pct(gap, .99)},
         "ttft_violation_rate": sum(1 for r in ok if r["first_token_time"] > max(300.0, 0.375 * r["input_length"])) / n,
         "tbt_violation_rate": sum(1 for x in tbt if x > 100.0) / n,
     }

@@ -172,7 +172,8 @@ def report(router_log: Iterable[str], client_records: Optional[List[dict]] = Non
              f"<h2>{html.escape(title)}</h2>"]
     if recs:
         s = slo_table(recs)
-        parts.append("<p>" + ", ".join(f"{k}: {v:.4g}" if isinstance(v, float) else f"{k}: {v}" for k, v in s.items()) + "</p>")
+        parts.append("<p>" + ", ".join(f"{html.escape(str(k))}: {v:.4g}" if isinstance(v, float) else f"{html.escape(str(k))}: {html.escape(str(v))}"
+                                       for k, v in s.items()) + "</p>")
         parts += [ttft_panel(recs), "<br>", tbt_panel(recs), "<br>"]
     so = scale_out_latencies(tr)
     if so:
