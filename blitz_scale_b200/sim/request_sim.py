@@ -106,7 +106,10 @@ def summarize(records: list) -> dict:
     tbt = [r["max_time_between_tokens"] for r in ok]
     # TTFT SLO of the reference's plots: violated if TTFT > max(300 ms, 0.375 ms * input_len) (scripts/batch/plot.py:116-119)
     viol = sum(1 for r in ok if r["first_token_time"] > max(300.0, 0.375 * r["input_length"]))
+    gap = [r["first_decode_token_time"] - r["first_token_time"] for r in ok
+           if r.get("first_decode_token_time", 0) > r.get("first_token_time", 0)]
     return {"requests": len(records), "ok": len(ok), "ttft_p50_ms": pct(ttft, .5), "ttft_p99_ms": pct(ttft, .99),
+            "first_decode_gap_p50_ms": pct(gap, .5), "first_decode_gap_p99_ms": pct(gap, .99),
             "max_tbt_p50_ms": pct(tbt, .5), "max_tbt_p99_ms": pct(tbt, .99),
             "ttft_slo_violation_rate": viol / max(1, len(ok)),
             "tbt_slo_violation_rate": sum(1 for x in tbt if x > 100.0) / max(1, len(ok)),
