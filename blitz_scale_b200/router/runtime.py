@@ -13,6 +13,7 @@ from __future__ import annotations
 import asyncio
 import logging
 import time
+from collections import deque
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -100,7 +101,7 @@ class RouterRuntime:
         self.root_trace = new_traceparent()
         self._next_id = 0
         self._tasks: set = set()
-        self.transitions: List[tuple] = []
+        self.transitions: "deque[tuple]" = deque(maxlen=50000)   # (router time, log line) of recent state transitions
         self._zag_pp: Dict[int, int] = {}            # batch_id -> layer at which a relayed batch was handed over
 
     # ------------------------------------------------------------------ submission
