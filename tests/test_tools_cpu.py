@@ -345,3 +345,17 @@ def test_run_report_figures(tmp_path):
     assert plots.main(["--router-log", str(tmp_path / "router.log"), "-o", str(tmp_path / "r.html")]) == 0
     assert (tmp_path / "r.html").read_text().count("<svg") == 2   # without client records: states and token rates
     assert plots._ticks(0.0, 10.0, 5) == [0.0, 2.0, 4.0, 6.0, 8.0, 10.0]
+
+
+def test_package_command_dispatcher():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = lambda *a: subprocess.run([sys.executable, "-m", "blitz_scale_b200", *a], cwd=root, capture_output=True, text=True, timeout=120)
+    r = run("--help")
+    assert r.returncode == 0 and "stub-worker" in r.stdout and "report" in r.stdout
+    assert run("no-such-command").returncode == 2
+    r = run("trace", "--help")
+    assert r.returncode == 0 and "usage" in r.stdout.lower()
+    r = run("report", "--help")
+    assert r.returncode == 0 and "--router-log" in r.stdout
