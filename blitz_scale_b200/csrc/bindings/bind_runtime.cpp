@@ -77,6 +77,7 @@ void bind_runtime(py::module_& m) {
         auto r = b.sampling_rows();
         return py::make_tuple(r.rows, r.temperature, r.top_k, r.top_p, r.seeds); })
       .def("none_generated", &Batch::none_generated).def("prompt_page_ids", &Batch::prompt_page_ids)
+      .def("prompt_page_ids_for", &Batch::prompt_page_ids_for)
       .def("fill_prefill", [](const Batch& b, py::array_t<int32_t, py::array::c_style> h, const MetaLayout& L) {
         if (h.size() < L.total) throw std::invalid_argument("staging array too small");
         return b.fill_prefill(h.mutable_data(), L); })

@@ -101,6 +101,7 @@ struct KvPushParams {
   uint32_t* dst_flags;   // one per layer (indexed by absolute layer), bumped by 1 per push
   uint32_t* tickets;     // one per layer in [layer_begin, layer_end), zero on entry
   int ctas_per_layer;
+  const int32_t* dst_count;  // optional: number of page ids the destination published; must equal n_pages
   int* status;
 };
 
@@ -109,6 +110,12 @@ __global__ void __launch_bounds__(256) kv_push_kernel(const KvPushParams p) {
   __shared__ uint32_t s_last;
   const int layer = p.layer_begin + blockIdx.y;
   const int64_t vec_per_page = p.page_bytes >> 4;
+  // the two ends built their page lists independently: if they disagree on the count, page i of one side does not
+  // face page i of the other, so nothing is copied and the layer is not flagged (the receiver's wait reports it)
+  if (p.dst_count != nullptr && *reinterpret_cast<const volatile int32_t*>(p.dst_count) != p.n_pages) {
+    if (p.status && threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadIndex);
+    return;
+  }
   const int64_t total = vec_per_page * p.n_pages;
   constexpr int kUnroll = 4;
   const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x * kUnroll;
@@ -123,7 +130,9 @@ __global__ void __launch_bounds__(256) kv_push_kernel(const KvPushParams p) {
         const int pg = static_cast<int>(i / vec_per_page);
         const int64_t within = i % vec_per_page;
         const int sp = p.src_pages[pg], dp = p.dst_pages[pg];
-        if (sp < 0 || sp >= p.src_max_pages || dp < 0 || dp >= p.dst_max_pages) {
+        if (sp == -1 || dp == -1) {
+          // a request one side no longer holds: its entries stay in both lists so that the others keep their places
+        } else if (sp < 0 || sp >= p.src_max_pages || dp < 0 || dp >= p.dst_max_pages) {
           if (p.status) atomicCAS(p.status, 0, kStatusBadIndex);
         } else {
           v[k] = ptx::ld_nc_na_v4(p.src_base + layer * p.src_layer_stride + sp * p.page_bytes + (within << 4));
@@ -151,6 +160,21 @@ __global__ void __launch_bounds__(256) kv_push_kernel(const KvPushParams p) {
 __global__ void flag_wait_kernel(const uint32_t* flag, uint32_t want, uint64_t budget_ns, int* status) {
   if (!ptx::bounded_flag_wait_ge(flag, want, budget_ns)) {
     if (status) atomicCAS(status, 0, kStatusTimeoutFlag);
+  }
+}
+// Wait for an exact value: a transfer tag that a stale, larger tag of an earlier transfer must not satisfy.
+__global__ void flag_wait_eq_kernel(const uint32_t* flag, uint32_t want, uint64_t budget_ns, int* status) {
+  if (ptx::ld_acquire_sys(flag) == want) return;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t it = 0;
+  while (ptx::ld_acquire_sys(flag) != want) {
+    if ((++it & 15u) == 0) {
+      if (ptx::globaltimer_ns() - t0 > budget_ns) {
+        if (status) atomicCAS(status, 0, kStatusTimeoutFlag);
+        return;
+      }
+      __nanosleep(64);
+    }
   }
 }
 __global__ void flag_set_kernel(uint32_t* flag, uint32_t value, int add) {
@@ -202,11 +226,13 @@ int blitz_peer_copy_units(const void* src_base, void* const* dst_bases, uint32_t
 // Push pages src_pages[i] -> dst_pages[i] (device int32 arrays) of layers [layer_begin, layer_end) from the
 // local pool at src_base into the peer pool at dst_base.  page_bytes = K plane + V plane of one page of one
 // layer.  dst_flags (peer pointer, may be null): one counter per layer, +1 when the layer's pages landed.
-// tickets: (layer_end - layer_begin) zeroed uint32 of local scratch.
+// tickets: (layer_end - layer_begin) zeroed uint32 of local scratch.  dst_count (may be null): address of the
+// number of ids the destination published; when it differs from n_pages the push copies nothing and reports
+// kStatusBadIndex.
 int blitz_kv_push(const void* src_base, void* dst_base, const int32_t* src_pages, const int32_t* dst_pages,
                   int n_pages, int layer_begin, int layer_end, int64_t page_bytes, int64_t src_layer_stride,
                   int64_t dst_layer_stride, int src_max_pages, int dst_max_pages, uint32_t* dst_flags,
-                  uint32_t* tickets, int ctas_per_layer, int* status, cudaStream_t stream) {
+                  uint32_t* tickets, int ctas_per_layer, const int32_t* dst_count, int* status, cudaStream_t stream) {
   if (n_pages <= 0 || layer_end <= layer_begin) return 0;
   if (page_bytes & 15) return -1;
   KvPushParams p;
@@ -216,7 +242,7 @@ int blitz_kv_push(const void* src_base, void* dst_base, const int32_t* src_pages
   p.layer_begin = layer_begin; p.layer_end = layer_end; p.page_bytes = page_bytes;
   p.src_layer_stride = src_layer_stride; p.dst_layer_stride = dst_layer_stride;
   p.src_max_pages = src_max_pages; p.dst_max_pages = dst_max_pages;
-  p.dst_flags = dst_flags; p.tickets = tickets; p.status = status;
+  p.dst_flags = dst_flags; p.tickets = tickets; p.status = status; p.dst_count = dst_count;
   if (ctas_per_layer <= 0) {
     const int64_t work = (page_bytes >> 4) * n_pages;  // vectors per layer
     int64_t c = (work + 256 * 4 * 4 - 1) / (256 * 4 * 4);
@@ -230,6 +256,10 @@ int blitz_kv_push(const void* src_base, void* dst_base, const int32_t* src_pages
 
 int blitz_flag_wait(const uint32_t* flag, uint32_t want, uint64_t budget_ns, int* status, cudaStream_t stream) {
   flag_wait_kernel<<<1, 1, 0, stream>>>(flag, want, budget_ns, status);
+  return (int)cudaGetLastError();
+}
+int blitz_flag_wait_eq(const uint32_t* flag, uint32_t want, uint64_t budget_ns, int* status, cudaStream_t stream) {
+  flag_wait_eq_kernel<<<1, 1, 0, stream>>>(flag, want, budget_ns, status);
   return (int)cudaGetLastError();
 }
 int blitz_flag_set(uint32_t* flag, uint32_t value, int add, cudaStream_t stream) {

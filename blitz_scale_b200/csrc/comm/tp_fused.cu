@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const RsReduceParam
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int s = 0; s < p.tp; ++s) {
       float f[8];
-      unpack8<T>(ld_nc16(stage + ((static_cast<int64_t>(s) * nvec + i) * p.rows_per_rank + row) * 8), f);
+      // staging is written by peers while this kernel runs: coherent L2 loads after the acquire, never the read-only path
+      unpack8<T>(__ldcg(reinterpret_cast<const uint4*>(stage + ((static_cast<int64_t>(s) * nvec + i) * p.rows_per_rank + row) * 8)), f);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] += f[j];
     }
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(256) oneshot_reduce_kernel(const OneShotParams
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int s = 0; s < p.tp; ++s) {
       float f[8];
-      unpack8<T>(ld_nc16(mine + static_cast<int64_t>(s) * p.n + i * 8), f);
+      unpack8<T>(__ldcg(reinterpret_cast<const uint4*>(mine + static_cast<int64_t>(s) * p.n + i * 8)), f);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] += f[j];
     }

@@ -20,6 +20,8 @@
  *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with that
  *     device current) and raises the kernel's shared-memory limit.  Make that first call outside any stream
  *     capture; later calls do no set-up work.
+ *     Host threads may make that first call concurrently: the set-up runs once per device under a lock.
+ *   - A process may use devices 0..63 with this entry point; on a higher device ordinal it returns -1.
  *   - No cudaMalloc, cudaFree, or allocating library routine is called, on any call.
  *
  * Arguments are those of blitz_attn_decode without the workspace pointer:

@@ -363,12 +363,9 @@ __global__ void attn_merge_tc_kernel(const float* __restrict__ part_o, const flo
 template <typename T, int HD>
 static int launch_tc(const CUtensorMap& tm, const DecodeTcParams& p, int batch, cudaStream_t stream) {
   auto kern = attn_decode_tc_kernel<T, HD>;
-  static bool attr = false;
-  if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<HD>::kSmemBytes);
-    if (e != cudaSuccess) return (int)e;
-    attr = true;
-  }
+  static PerDeviceOnce once;
+  cudaError_t e = once.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<HD>::kSmemBytes); });
+  if (e != cudaSuccess) return (int)e;
   const int items = batch * p.kv_heads * p.num_splits;
   const int sms = device_sm_count();
   return (int)launch_pdl(kern, dim3(items < sms ? items : sms), dim3(kTcThreads), TcCfg<HD>::kSmemBytes, stream, tm, p);
@@ -445,16 +442,18 @@ namespace blitz {
 // name, is what the kernels receive.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[BLITZ_ATTN_NOALLOC_SCRATCH_BYTES];
 
-constexpr int kNoallocMaxDevices = 64;
-static void* g_noalloc_ptr[kNoallocMaxDevices] = {};
-static bool g_noalloc_ready[kNoallocMaxDevices] = {};
+constexpr int kNoallocMaxDevices = kMaxDevicesPerProcess;
+// Device address of the scratch on each device: written once under the set-up lock and published with release
+// order, so a host thread that sees a non-null value also sees a fully set-up device.
+static std::atomic<void*> g_noalloc_ptr[kNoallocMaxDevices];
+static PerDeviceOnce g_noalloc_once;
 
 // Per-device set-up with that device current: resolve the scratch address, raise the shared-memory limits.
-static int noalloc_setup(int dev) {
+static cudaError_t noalloc_setup(int dev) {
   void* ptr = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-  if (e != cudaSuccess) return (int)e;
-  if (ptr == nullptr) return (int)cudaErrorInvalidSymbol;
+  if (e != cudaSuccess) return e;
+  if (ptr == nullptr) return cudaErrorInvalidSymbol;
   e = cudaFuncSetAttribute(attn_decode_tc_kernel<__nv_bfloat16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::kSmemBytes);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(attn_decode_tc_kernel<__nv_bfloat16, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64>::kSmemBytes);
@@ -462,10 +461,9 @@ static int noalloc_setup(int dev) {
     e = cudaFuncSetAttribute(attn_decode_tc_kernel<__half, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::kSmemBytes);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(attn_decode_tc_kernel<__half, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64>::kSmemBytes);
-  if (e != cudaSuccess) return (int)e;
-  g_noalloc_ptr[dev] = ptr;
-  g_noalloc_ready[dev] = true;
-  return 0;
+  if (e != cudaSuccess) return e;
+  g_noalloc_ptr[dev].store(ptr, std::memory_order_release);
+  return cudaSuccess;
 }
 
 // Tensor map of one KV layer built on the stack (the cached builder keeps a host-side table; this path keeps nothing).
@@ -508,17 +506,17 @@ extern "C" int blitz_attn_decode_noalloc(const void* q, int64_t q_stride, const 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kNoallocMaxDevices) return -1;
-  if (!g_noalloc_ready[dev]) {
-    const int rc = noalloc_setup(dev);
-    if (rc != 0) return rc;
-  }
+  e = g_noalloc_once.run([&] { return noalloc_setup(dev); });
+  if (e != cudaSuccess) return (int)e;
+  void* const scratch = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) return (int)cudaErrorInvalidSymbol;
   const int bt = page_size < kTcChunk ? page_size : kTcChunk;
   CUtensorMap tm;
   if (!noalloc_tmap(&tm, kv_layer, head_dim, kv_heads, max_pages, page_size, bt)) return -2;
   DecodeTcParams p;
   p.q = q; p.q_stride = q_stride; p.indices = indices; p.indptr = indptr; p.last_page_len = last_page_len;
   p.out = out; p.out_stride = out_stride;
-  p.part_o = reinterpret_cast<float*>(g_noalloc_ptr[dev]);
+  p.part_o = reinterpret_cast<float*>(scratch);
   p.part_lse = p.part_o + (int64_t)batch * q_heads * num_splits * head_dim;
   p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size;
   p.max_pages = max_pages; p.num_splits = num_splits; p.box_tokens = bt;

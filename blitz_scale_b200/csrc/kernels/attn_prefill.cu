@@ -17,6 +17,7 @@
 //
 // Replaces FlashInfer's BatchPrefillWithRaggedKVCacheWrapper call and its host
 // Plan() (src/kernel/attention_prefill.cu:11-45, src/kernel/flashinfer_types.cu:24-49).
+#include "launch.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
 #include "common.cuh"
@@ -300,22 +301,20 @@ int blitz_attn_prefill(const void* qkv, void* out, int64_t out_stride, const int
   p.out = out; p.out_stride = out_stride; p.indptr = indptr_dev; p.batch = batch;
   p.q_heads = q_heads; p.kv_heads = kv_heads; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
   dim3 grid(total_q_tiles, q_heads);
-  static bool attr_bf16 = false, attr_f16 = false;
+  static PerDeviceOnce once_bf16, once_f16;
   if (dtype == 1) {
-    if (!attr_bf16) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<__nv_bfloat16>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
-      if (e != cudaSuccess) return (int)e;
-      attr_bf16 = true;
-    }
+    cudaError_t e = once_bf16.run([] {
+      return cudaFuncSetAttribute(attn_prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kPfSmemBytes);
+    });
+    if (e != cudaSuccess) return (int)e;
     attn_prefill_kernel<__nv_bfloat16><<<grid, kPfThreads, kPfSmemBytes, stream>>>(tm, p);
   } else {
-    if (!attr_f16) {
-      cudaError_t e =
-          cudaFuncSetAttribute(attn_prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
-      if (e != cudaSuccess) return (int)e;
-      attr_f16 = true;
-    }
+    cudaError_t e = once_f16.run([] {
+      return cudaFuncSetAttribute(attn_prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kPfSmemBytes);
+    });
+    if (e != cudaSuccess) return (int)e;
     attn_prefill_kernel<__half><<<grid, kPfThreads, kPfSmemBytes, stream>>>(tm, p);
   }
   return (int)cudaGetLastError();

@@ -452,20 +452,25 @@ template <typename T, int EPI>
 static cudaError_t launch_dec(const CUtensorMap& tx, const CUtensorMap& tw, DecGemmParams& p, int split_hint, int sms,
                               cudaStream_t stream) {
   auto kern = gemm_decode_kernel<T, EPI>;
-  static bool attr_set = false;
+  // per device: the shared-memory attribute; the cluster occupancy is the same on every GPU of a box (the first
+  // device to get here fills the table under the set-up lock)
+  static PerDeviceOnce once;
   static int max_clusters[2][kDecMaxSplit + 1];
   static int occ_env = -1;
-  if (!attr_set) {
+  cudaError_t e0 = once.run([&] {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DecCfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    for (int s = 2; s <= kDecMaxSplit; ++s) {
-      max_clusters[0][s] = max_active_clusters(kern, dim3(kDecThreads), DecCfg::kSmemBytes, s);
-      max_clusters[1][s] = max_active_clusters(kern, dim3(kDecThreads), DecCfg::kSmemBytesHalf, s);
+    if (occ_env < 0) {
+      for (int s = 2; s <= kDecMaxSplit; ++s) {
+        max_clusters[0][s] = max_active_clusters(kern, dim3(kDecThreads), DecCfg::kSmemBytes, s);
+        max_clusters[1][s] = max_active_clusters(kern, dim3(kDecThreads), DecCfg::kSmemBytesHalf, s);
+      }
+      const char* env = std::getenv("BLITZ_DECODE_OCC");
+      occ_env = env ? std::atoi(env) : 0;
     }
-    const char* env = std::getenv("BLITZ_DECODE_OCC");
-    occ_env = env ? std::atoi(env) : 0;
-    attr_set = true;
-  }
+    return cudaSuccess;
+  });
+  if (e0 != cudaSuccess) return e0;
   const int halves = EPI == 2 ? 2 : 1;
   const int stage_bytes = DecCfg::x_stage_bytes(p.npad) + halves * kDecTile * kDecBK * 2;
   // One CTA per SM.  BLITZ_DECODE_OCC=2 runs two CTAs per SM on half the shared memory each (so that one CTA's

@@ -11,7 +11,9 @@
 // CUDA graph.
 #pragma once
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstdlib>
+#include <mutex>
 #include <utility>
 
 namespace blitz {
@@ -24,6 +26,31 @@ inline int& pdl_flag() {
   }
   return v;
 }
+
+// Set-up that must run once per device and kernel (function attributes are per device; a process may drive
+// several GPUs, and several host threads may make the first call at the same time).  `setup` runs with the
+// calling thread's current device; devices beyond kMaxDevicesPerProcess are refused.
+constexpr int kMaxDevicesPerProcess = 64;
+struct PerDeviceOnce {
+  std::atomic<int> done[kMaxDevicesPerProcess];
+  std::mutex mu;
+  PerDeviceOnce() {
+    for (auto& d : done) d.store(0, std::memory_order_relaxed);
+  }
+  template <typename F>
+  cudaError_t run(F&& setup) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevicesPerProcess) return cudaErrorInvalidDevice;
+    if (done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+    std::lock_guard<std::mutex> g(mu);
+    if (done[dev].load(std::memory_order_relaxed)) return cudaSuccess;
+    e = setup();
+    if (e == cudaSuccess) done[dev].store(1, std::memory_order_release);
+    return e;
+  }
+};
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -125,13 +126,17 @@ inline bool get_tmap_3d(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t
   return true;
 }
 
+// Number of SMs of the calling thread's current device (cached per device).
 inline int device_sm_count() {
-  static int n = 0;
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const bool cacheable = dev >= 0 && dev < 64;
+  int n = cacheable ? cache[dev].load(std::memory_order_relaxed) : 0;
   if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     if (n <= 0) n = 148;
+    if (cacheable) cache[dev].store(n, std::memory_order_relaxed);
   }
   return n;
 }

@@ -294,6 +294,24 @@ class Batch {
     }
     return out;
   }
+  // The same for the requests `ids` with prompt lengths `lens`, in that order: both ends of a migration build
+  // their page lists from the requests named in the RPC, so that entry i of one side always faces entry i of the
+  // other.  A request that is not (or no longer) in this batch still takes its ceil(len / page) entries, filled
+  // with -1, which the push kernel skips: the two lists have the same length whatever each side has filtered.
+  std::vector<int32_t> prompt_page_ids_for(const std::vector<uint64_t>& ids, const std::vector<int>& lens) const {
+    if (ids.size() != lens.size()) throw std::invalid_argument("prompt_page_ids_for: one length per request");
+    const int ps = pool_->page_size();
+    std::vector<int32_t> out;
+    for (size_t i = 0; i < ids.size(); ++i) {
+      const SeqState* found = nullptr;
+      for (auto& s : seqs_)
+        if (s.spec.id == ids[i]) { found = &s; break; }
+      const size_t used = (static_cast<size_t>(std::max(0, lens[i])) + ps - 1) / ps;
+      for (size_t k = 0; k < used; ++k)
+        out.push_back(found && k < found->pages.size() ? found->pages[k] : -1);
+    }
+    return out;
+  }
   // Move the requests of `other` to the end of this batch (page ownership moves too).
   void extend(Batch& other) {
     if (other.pool_ != pool_) throw std::invalid_argument("extend: different pools");
@@ -340,6 +358,16 @@ class Batch {
     for (int b = 0; b < B; ++b) {
       const auto& s = seqs_[b];
       const int n = s.total_len() - 1;  // position of the fed token
+      if (s.finish != kFinishNone || n < 0 || n / ps >= static_cast<int>(s.pages.size())) {
+        // a finished request, an empty one, or one without a page for the next position: the row is carried as
+        // padding (no page, no cache write) instead of indexing past its page list; its token is meaningless
+        h[L.ids + b] = 0;
+        h[L.pos + b] = 0;
+        h[L.slot + b] = -1;
+        h[L.page_indptr + b + 1] = np;
+        h[L.last_page_len + b] = 0;
+        continue;
+      }
       h[L.ids + b] = s.generated.empty() ? s.spec.prompt.back() : s.generated.back();
       h[L.pos + b] = n;
       h[L.slot + b] = s.pages[n / ps] * ps + n % ps;

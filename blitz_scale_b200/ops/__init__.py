@@ -59,6 +59,8 @@ def check_status(device=None, reset: bool = True) -> int:
             w.zero_()
             for _, tickets in _gemm_ws.values():  # an aborted split-K GEMM may leave tickets behind
                 tickets.zero_()
+            for _, flags in _pair_ws.values():
+                flags.zero_()
         names = {1: "TMA producer wait timed out", 2: "MMA wait timed out", 3: "epilogue wait timed out",
                  4: "flag wait timed out", 5: "index out of range", 6: "size beyond the supported maximum"}
         raise RuntimeError(f"kernel status {code}: {names.get(code, 'unknown')}")
@@ -70,8 +72,11 @@ _EPI = {"store": 0, "add": 1, "silu_mul": 2}
 
 
 _gemm_ws = {}
+_pair_ws = {}
 GEMM_TICKETS = 4096
+PAIR_FLAGS = 65536
 DECODE_GEMM_MAX_M = 128
+PAIR_GEMM_MAX_M = 256
 
 
 def gemm_workspace(device=None):
@@ -85,9 +90,22 @@ def gemm_workspace(device=None):
     return _gemm_ws[key]
 
 
+def pair_gemm_workspace(device=None):
+    """Per-device scratch of the paired-SM GEMM: (fp32 partials as bytes, zeroed uint32 counters, eight per tile)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.type, dev.index)
+    if key not in _pair_ws:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        n = int(lib().blitz_gemm_pair_workspace_bytes(sms))
+        _pair_ws[key] = (torch.empty(n, dtype=torch.uint8, device=dev),
+                         torch.zeros(PAIR_FLAGS, dtype=torch.int32, device=dev))
+    return _pair_ws[key]
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, residual=None,
          epilogue: str = "store", b_layout: str = "kn", bn: int = 0, split_k: int = 0, static_b: bool = False,
-         decode_path: Optional[bool] = None, decode_split: int = 0) -> torch.Tensor:
+         decode_path: Optional[bool] = None, decode_split: int = 0, pair_path: Optional[bool] = None,
+         pair_bnf: int = 0, pair_upp: int = 0, pair_nacc: int = 0) -> torch.Tensor:
     """``out = a @ b`` on tcgen05 with a fused epilogue.
 
     a: [M, K].  b: [K, N] when ``b_layout == 'kn'`` (weights stored in,out) or [N, K] for ``'nk'``.
@@ -100,6 +118,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     ``decode_path`` forces (True) or forbids (False) that choice and ``decode_split`` caps its cluster size.  ``static_b=True`` promises that ``b`` is not written by kernels still
     running in this stream (model weights), so the decode kernel may start streaming it before its
     predecessor has finished.
+
+    129..256 rows with 'kn' weights go to the paired-SM kernel (two CTAs issue one 256-row
+    ``tcgen05.mma.cta_group::2``, stream-K over CTA pairs); ``pair_path`` forces (True) or forbids (False) it for
+    any M, ``pair_bnf`` / ``pair_nacc`` / ``pair_upp`` override its tile width, tiles per pair and units per pair.
     """
     assert a.is_cuda and a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     M, K = a.shape
@@ -124,6 +146,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     if decode_path is not None:
         assert not decode_path or lib().blitz_gemm_decode_supported(M, N, K, 0 if b_layout == "kn" else 1, epi)
         use_dec = decode_path
+    pair_ok = bool(lib().blitz_gemm_pair_supported(M, N, K, 0 if b_layout == "kn" else 1, epi))
+    use_pair = (not use_dec and DECODE_GEMM_MAX_M < M <= PAIR_GEMM_MAX_M and bn == 0 and split_k == 0 and pair_ok)
+    if pair_path is not None:
+        assert not pair_path or pair_ok
+        use_pair = pair_path
+    if use_pair:
+        pws, pflags = pair_gemm_workspace(a.device)
+        rc = lib().blitz_gemm_pair(_p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), _p(residual), M, N,
+                                   K, epi, N if epi == 2 else 0, _dt(a), int(static_b), pair_bnf, pair_nacc, pair_upp,
+                                   _p(pws), pws.numel(), _p(pflags), pflags.numel(), _p(status_word(a.device)),
+                                   _stream())
+        _check(rc, "blitz_gemm_pair")
+        return out
     if use_dec:
         rc = lib().blitz_gemm_decode(_p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), _p(residual), M, N,
                                      K, epi, N if epi == 2 else 0, _dt(a), int(static_b), decode_split,

@@ -58,6 +58,10 @@ def _declare(L: ctypes.CDLL) -> None:
     sig("blitz_gemm_workspace_bytes", [c_i], c_i64)
     sig("blitz_gemm_decode", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_p])
     sig("blitz_gemm_decode_supported", [c_i, c_i, c_i, c_i, c_i], c_i)
+    sig("blitz_gemm_pair", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p,
+                            c_i64, c_p, c_i, c_p, c_p])
+    sig("blitz_gemm_pair_supported", [c_i, c_i, c_i, c_i, c_i], c_i)
+    sig("blitz_gemm_pair_workspace_bytes", [c_i], c_i64)
     sig("blitz_set_pdl", [c_i], None)
     sig("blitz_get_pdl", [], c_i)
     sig("blitz_gemm_tile_n", [c_i, c_i, c_i, c_i], c_i)
@@ -86,6 +90,8 @@ def _declare(L: ctypes.CDLL) -> None:
     pp = ctypes.POINTER(c_p)
     pi64 = ctypes.POINTER(c_i64)
     sig("blitz_peer_copy_units", [c_p, pp, pp, c_i, c_p, pi64, pi64, c_i, c_i, c_i, c_i, c_p, c_i, c_p])
-    sig("blitz_kv_push", [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i64, c_i64, c_i64, c_i, c_i, c_p, c_p, c_i, c_p, c_p])
+    sig("blitz_kv_push", [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i64, c_i64, c_i64, c_i, c_i, c_p, c_p, c_i, c_p, c_p,
+                          c_p])
     sig("blitz_flag_wait", [c_p, ctypes.c_uint32, c_u64, c_p, c_p])
+    sig("blitz_flag_wait_eq", [c_p, ctypes.c_uint32, c_u64, c_p, c_p])
     sig("blitz_flag_set", [c_p, ctypes.c_uint32, c_i, c_p])

@@ -13,6 +13,7 @@ Flag pad layout (uint32 counters, all zero at boot):
     [128, 128 + 16)               activation mailbox slots                    (value = sequence tag)
     [256, 256 + KV_SLOTS*LAYERS)  KV push: per (transfer slot, layer)         (+1 per push)
     [AGREE_FLAG0, +16)            loaded-unit counts published by the TP shards of the replica (plain stores)
+    [KV_DONE_FLAG0, +KV_SLOTS)    KV push: per transfer slot, +1 after the last layer of a push
 """
 from __future__ import annotations
 
@@ -32,7 +33,8 @@ KV_FLAG0 = 256
 KV_SLOTS = 8
 MAX_LAYERS = 128
 AGREE_FLAG0 = KV_FLAG0 + KV_SLOTS * MAX_LAYERS    # loaded-unit count of every TP shard of this replica (<= 16)
-FLAG_WORDS = AGREE_FLAG0 + 16
+KV_DONE_FLAG0 = AGREE_FLAG0 + 16                  # per transfer slot: +1 when a whole push (all its layers) has landed
+FLAG_WORDS = KV_DONE_FLAG0 + KV_SLOTS
 
 
 def _stream() -> ctypes.c_void_p:
@@ -113,6 +115,12 @@ class PeerFabric:
                                         ctypes.c_void_p(status_word(self.device).data_ptr()), _stream()),
                "blitz_flag_wait")
 
+    def wait_flag_eq(self, ptr: int, want: int, budget_ms: float = 1000.0) -> None:
+        """Bounded device-side wait until the word at `ptr` (any rank's memory) equals `want` exactly."""
+        _check(_L.lib().blitz_flag_wait_eq(ctypes.c_void_p(ptr), want, int(budget_ms * 1e6),
+                                           ctypes.c_void_p(status_word(self.device).data_ptr()), _stream()),
+               "blitz_flag_wait_eq")
+
     def set_flag(self, rank: int, index: int, value: int, add: bool = False) -> None:
         ptr = self.flags.ptrs[rank] + index * 4
         _check(_L.lib().blitz_flag_set(ctypes.c_void_p(ptr), value, int(add), _stream()), "blitz_flag_set")
@@ -144,19 +152,29 @@ class PeerFabric:
     # ------------------------------------------------------------------ KV push
     def kv_push(self, dst_rank: int, src_pages: torch.Tensor, dst_pages: torch.Tensor, layer_begin: int,
                 layer_end: int, page_bytes: int, src_layer_stride: int, dst_layer_stride: int, src_max_pages: int,
-                dst_max_pages: int, flag_slot: Optional[int] = None, ctas_per_layer: int = 0) -> None:
-        """Store prompt pages of layers [layer_begin, layer_end) into `dst_rank`'s pool using its page ids."""
-        assert src_pages.dtype == torch.int32 and dst_pages.dtype == torch.int32
+                dst_max_pages: int, flag_slot: Optional[int] = None, ctas_per_layer: int = 0,
+                dst_pages_ptr: int = 0, dst_count_ptr: int = 0, n_pages: Optional[int] = None) -> None:
+        """Store prompt pages of layers [layer_begin, layer_end) into `dst_rank`'s pool using its page ids.
+
+        ``dst_pages`` is a local int32 tensor, or None with ``dst_pages_ptr`` the address (possibly in the peer's
+        memory) of the ids the destination published; ``dst_count_ptr`` then names the count it published, which
+        the kernel compares with the number of source pages.  With a ``flag_slot`` the slot's completion counter
+        on the destination is bumped after the push (stream order: after every layer has been stored)."""
+        assert src_pages.dtype == torch.int32 and (dst_pages is None or dst_pages.dtype == torch.int32)
         nl = layer_end - layer_begin
         tick = self.tickets[1024:1024 + nl]
         tick.zero_()
         flags = 0
         if flag_slot is not None:
             flags = self.flags.ptrs[dst_rank] + (KV_FLAG0 + flag_slot * MAX_LAYERS) * 4
+        dptr = dst_pages.data_ptr() if dst_pages is not None else dst_pages_ptr
+        n = src_pages.numel() if n_pages is None else n_pages
         rc = _L.lib().blitz_kv_push(ctypes.c_void_p(self.kv.ptrs[self.rank]), ctypes.c_void_p(self.kv.ptrs[dst_rank]),
-                                    ctypes.c_void_p(src_pages.data_ptr()), ctypes.c_void_p(dst_pages.data_ptr()),
-                                    src_pages.numel(), layer_begin, layer_end, page_bytes, src_layer_stride,
+                                    ctypes.c_void_p(src_pages.data_ptr()), ctypes.c_void_p(dptr),
+                                    n, layer_begin, layer_end, page_bytes, src_layer_stride,
                                     dst_layer_stride, src_max_pages, dst_max_pages, ctypes.c_void_p(flags),
-                                    ctypes.c_void_p(tick.data_ptr()), ctas_per_layer,
+                                    ctypes.c_void_p(tick.data_ptr()), ctas_per_layer, ctypes.c_void_p(dst_count_ptr),
                                     ctypes.c_void_p(status_word(self.device).data_ptr()), _stream())
         _check(rc, "blitz_kv_push")
+        if flag_slot is not None:
+            self.set_flag(dst_rank, KV_DONE_FLAG0 + flag_slot, 1, add=True)

@@ -145,7 +145,11 @@ class Engine:
 
     @torch.no_grad()
     def decode(self, batch: "core.Batch") -> List[int]:
-        """One decode step for every request in `batch` (already extended if several were merged)."""
+        """One decode step for every request in `batch` (already extended if several were merged).  Requests that
+        have already finished stay in their rows as padding (no cache write; their returned token is meaningless and
+        is not recorded): callers normally filter them out between steps."""
+        if not self.status.fully_loaded():
+            raise RuntimeError("model parameters are not loaded")
         B = batch.size
         if B > self.max_batch:
             raise ValueError(f"decode batch of {B} sequences exceeds max_batch={self.max_batch}")

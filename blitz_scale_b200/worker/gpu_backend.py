@@ -64,7 +64,7 @@ class GpuBackend(Backend):
             self.fabric = symm.PeerFabric(symm.FabricSizes(weight_bytes=probe.layout.total_bytes, kv_bytes=kv_bytes,
                                                            mailbox_slots=4, mailbox_slot_bytes=self.slot_bytes))
             seg_buf, kv_buf = self.fabric.weights.local, self.fabric.kv.local
-            self.ctl = symm.SymmRegion(symm.KV_SLOTS * CTL_SLOT_WORDS * 4 + symm.KV_SLOTS * 4)
+            self.ctl = symm.SymmRegion(symm.KV_SLOTS * CTL_SLOT_WORDS * 4 + symm.KV_SLOTS * 4)  # id lists, then tags
             self.ctl.local.zero_()
         comm = TPComm(tp_group) if tp > 1 else None
         self.engine = Engine(self.cfg, num_pages=num_pages, page_size=page_size, max_batch=max_batch,
@@ -90,7 +90,10 @@ class GpuBackend(Backend):
         # transfers (parameter copies, KV push / arrival waits, relays) run on their own high-priority stream so that
         # they overlap the serving kernels of the default stream instead of queueing between decode steps
         self.side = torch.cuda.Stream(device=self.device, priority=-1)
-        self.xfer_lock = threading.Lock()      # one transfer at a time uses the side stream, the ticket words and a KV slot
+        self.xfer_lock = threading.Lock()      # one transfer at a time uses the side stream and the ticket words
+        self._poll_stream = torch.cuda.Stream(device=self.device)
+        self._kv_slot_busy = [False] * symm.KV_SLOTS   # incoming KV transfers: slot reserved until the push has completed
+        self._kv_done_want = [0] * symm.KV_SLOTS       # pushes started per slot = value its completion counter will reach
         # TP shards of a replica act on the minimum of their loaded-unit counts
         self.agree: Optional[LoadAgreement] = None
         if tp > 1 and self.fabric is not None:
@@ -329,9 +332,33 @@ class GpuBackend(Backend):
             return min(num_layer, L), L
         return 0, L
 
+    # Handshake of one transfer (all layers, or one half of a relayed batch).  Control region of every GPU:
+    # KV_SLOTS slots of CTL_SLOT_WORDS words (word 0 = number of page ids, then the ids) followed by one tag word per
+    # slot.  The destination reserves slot `batch id mod KV_SLOTS` (a second transfer that maps to the same slot waits
+    # until the first has completed), writes count and ids, then publishes the transfer's tag: a value unique to
+    # (batch, half), matched exactly by the source, so a tag left by any other transfer can never satisfy the wait.
+    # The source pushes every layer and then, in stream order, bumps the slot's completion counter on the
+    # destination; only then does the destination clear the tag and free the slot, so no CTA of the push can still
+    # be reading the id list when the next transfer overwrites it.  Both page lists follow the requests of the RPC,
+    # in its order, with -1 entries for requests one side no longer holds (see Batch::prompt_page_ids_for).
+    @staticmethod
+    def _kv_tag(batch_id: int, partial: int) -> int:
+        return (((int(batch_id) + 1) & 0x0FFFFFFF) << 2) | (int(partial) & 3)
+
+    def _rpc_page_list(self, b, batch) -> List[int]:
+        specs = self._specs(batch)
+        ids = b.prompt_page_ids_for([sp.id for sp in specs], [len(sp.prompt) for sp in specs])
+        if len(ids) + 1 > CTL_SLOT_WORDS:
+            raise RuntimeError(f"batch {batch.id}: {len(ids)} KV pages exceed the {CTL_SLOT_WORDS - 1} a transfer slot holds")
+        return ids
+
     def immigrate(self, batch, src, dst, partial=0, num_layer=0):
+        lo, hi = self._layer_range(partial, num_layer)
+        half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
+        slot = batch.id % symm.KV_SLOTS
+        keep = [r.id for r in batch.requests]
+        reserved = False
         with self.lock:
-            slot = batch.id % symm.KV_SLOTS
             b = self.batches.get(batch.id)
             if b is None:
                 b = self.engine.new_batch(batch.id, self._specs(batch))
@@ -340,35 +367,51 @@ class GpuBackend(Backend):
                 b.mark_prefilled()
                 b.decode = True
                 self.batches[batch.id] = b
-            lo, hi = self._layer_range(partial, num_layer)
-            half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
+            elif partial == pb.PARTIAL_CASE_SECOND:
+                # the second half names the requests that are still alive after the prefill; the ones that ended at
+                # their first token were part of the first half only and leave the batch (and their pages) here
+                b.filter([i for i in b.request_ids() if i in set(keep)])
             log.info("batch %d immigrate start%s layers [%d,%d) <~- rank %s", batch.id, half, lo, hi, list(src))
-            cb = pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
-            want = None
+            ids = None
             if hi > lo and self.fabric is not None:
-                # publish the destination page ids of the prompt pages
-                ids = b.prompt_page_ids()
-                want = list(self._kv_want(slot, lo, hi))
-        if want is not None:
-            # ... then wait for the layers to land, without holding the lock: decode steps of other batches go on
-            with self.xfer_lock, torch.cuda.stream(self.side):
-                words = self.ctl.local.view(torch.int32)
-                words[slot * CTL_SLOT_WORDS:slot * CTL_SLOT_WORDS + len(ids)].copy_(
-                    torch.tensor(ids, dtype=torch.int32), non_blocking=False)
+                ids = self._rpc_page_list(b, batch) or None
+            if ids is not None:
+                deadline = time.monotonic() + 30.0
+                while self._kv_slot_busy[slot]:
+                    if not self.zag_cv.wait(max(0.0, deadline - time.monotonic())) and time.monotonic() >= deadline:
+                        raise RuntimeError(f"batch {batch.id}: transfer slot {slot} stayed busy")
+                self._kv_slot_busy[slot] = reserved = True
+                self._kv_done_want[slot] += 1
+                done_want = self._kv_done_want[slot]
+        try:
+            if ids is not None:
                 tag_index = symm.KV_SLOTS * CTL_SLOT_WORDS + slot
-                self._ctl_set(self.rank, tag_index, int(batch.id) + 1)
-                self.fabric.wait_flag(symm.KV_FLAG0 + slot * symm.MAX_LAYERS + hi - 1, want[hi - 1], budget_ms=10000)
-                self.side.synchronize()
-            ops.check_status()
+                with self.xfer_lock, torch.cuda.stream(self.side):
+                    words = self.ctl.local.view(torch.int32)
+                    words[slot * CTL_SLOT_WORDS:slot * CTL_SLOT_WORDS + 1 + len(ids)].copy_(
+                        torch.tensor([len(ids)] + ids, dtype=torch.int32), non_blocking=False)
+                    self._ctl_set(self.rank, tag_index, self._kv_tag(batch.id, partial))
+                    self.side.synchronize()
+                # the layers land without this GPU doing anything: poll the completion counter from the host, with no
+                # stream or lock held, so that decode steps and other transfers go on meanwhile
+                deadline = time.monotonic() + 10.0
+                with torch.cuda.stream(self._poll_stream):
+                    while self.fabric.read_flags(symm.KV_DONE_FLAG0 + slot, 1)[0] < done_want:
+                        if time.monotonic() > deadline:
+                            raise RuntimeError(f"batch {batch.id}: KV push did not complete{half}")
+                        time.sleep(0.0001)
+                    self.ctl.local.view(torch.int32)[tag_index:tag_index + 1].zero_()
+                    self._poll_stream.synchronize()
+                ops.check_status()
+        finally:
+            if reserved:
+                with self.lock:
+                    self._kv_slot_busy[slot] = False
+                    self.zag_cv.notify_all()
+        with self.lock:
+            cb = pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
         log.info("batch %d immigrate done%s", batch.id, half)
         return cb
-
-    def _kv_want(self, slot, lo, hi):
-        if not hasattr(self, "_kv_layer_count"):
-            self._kv_layer_count = [[0] * symm.MAX_LAYERS for _ in range(symm.KV_SLOTS)]
-        for l in range(lo, hi):
-            self._kv_layer_count[slot][l] += 1
-        return self._kv_layer_count[slot]
 
     def _ctl_set(self, rank, word_index, value):
         import ctypes
@@ -386,30 +429,19 @@ class GpuBackend(Backend):
             slot = batch.id % symm.KV_SLOTS
             half = {pb.PARTIAL_CASE_FIRST: " first half", pb.PARTIAL_CASE_SECOND: " second half"}.get(partial, "")
             log.info("batch %d migrate start%s layers [%d,%d) -~> rank %d", batch.id, half, lo, hi, peer)
-            src_ids = b.prompt_page_ids()
+            src_ids = self._rpc_page_list(b, batch)
         # the push itself runs outside the lock, on the transfer stream: this batch is parked until it has migrated,
         # and prefills of other batches continue meanwhile
-        if hi > lo:
+        if hi > lo and src_ids:
             with self.xfer_lock, torch.cuda.stream(self.side):
-                import ctypes
                 src_pages = torch.tensor(src_ids, dtype=torch.int32, device=self.device)
-                # wait until the destination has published its page ids for this batch
+                # wait until the destination has published its page ids for exactly this transfer
                 tag_ptr = self.ctl.ptrs[peer] + (symm.KV_SLOTS * CTL_SLOT_WORDS + slot) * 4
-                symm._check(symm._L.lib().blitz_flag_wait(ctypes.c_void_p(tag_ptr), int(batch.id) + 1, int(10e9),
-                                                          ctypes.c_void_p(ops.status_word().data_ptr()), symm._stream()),
-                            "blitz_flag_wait")
-                dst_pages_ptr = self.ctl.ptrs[peer] + slot * CTL_SLOT_WORDS * 4
-                nl = hi - lo
-                tick = self.fabric.tickets[1024:1024 + nl]
-                tick.zero_()
-                flags = self.fabric.flags.ptrs[peer] + (symm.KV_FLAG0 + slot * symm.MAX_LAYERS) * 4
-                rc = symm._L.lib().blitz_kv_push(
-                    ctypes.c_void_p(self.fabric.kv.ptrs[self.rank]), ctypes.c_void_p(self.fabric.kv.ptrs[peer]),
-                    ctypes.c_void_p(src_pages.data_ptr()), ctypes.c_void_p(dst_pages_ptr), len(src_ids), lo, hi,
-                    self.page_bytes, self.kv_layer_stride, self.kv_layer_stride, self.engine.num_pages,
-                    self.engine.num_pages, ctypes.c_void_p(flags), ctypes.c_void_p(tick.data_ptr()), 0,
-                    ctypes.c_void_p(ops.status_word().data_ptr()), symm._stream())
-                symm._check(rc, "blitz_kv_push")
+                self.fabric.wait_flag_eq(tag_ptr, self._kv_tag(batch.id, partial), budget_ms=10000)
+                count_ptr = self.ctl.ptrs[peer] + slot * CTL_SLOT_WORDS * 4
+                self.fabric.kv_push(peer, src_pages, None, lo, hi, self.page_bytes, self.kv_layer_stride,
+                                    self.kv_layer_stride, self.engine.num_pages, self.engine.num_pages,
+                                    flag_slot=slot, dst_pages_ptr=count_ptr + 4, dst_count_ptr=count_ptr)
                 self.side.synchronize()
             ops.check_status()
         with self.lock:

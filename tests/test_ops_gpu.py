@@ -112,6 +112,49 @@ def test_gemm_decode_path(ops, M, N, K):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M", [129, 200, 256, 640])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1088, 520), (6144, 1024)])
+def test_gemm_pair_path(ops, M, N, K):
+    """Paired-SM GEMM (one 256-row tcgen05.mma over two CTAs, stream-K over CTA pairs): every tile width and every
+    cut of the unit range gives the right result, and the same one on every run (partials are summed in pair order)."""
+    torch.manual_seed(17)
+    a = torch.randn(M, K, device="cuda", dtype=DT)
+    b = torch.randn(K, N, device="cuda", dtype=DT) * K ** -0.5
+    r = torch.randn(M, N, device="cuda", dtype=DT)
+    ref = a.float() @ b.float()
+    gu = torch.randn(K, 2 * N, device="cuda", dtype=DT) * K ** -0.5
+    acc = a.float() @ gu.float()
+    ref2 = torch.nn.functional.silu(acc[:, :N]) * acc[:, N:]
+    nkb = (K + 63) // 64
+    for bnf, nacc in ((0, 0), (128, 1), (128, 2), (256, 1), (256, 2)):
+        for upp in (0, nkb, max(1, nkb // 2), (nkb + 2) // 3 + 1, 3 * nkb + 1, -2, -3, -4):
+            kw = dict(pair_path=True, pair_bnf=bnf, pair_nacc=nacc, pair_upp=upp)
+            out = ops.gemm(a, b, **kw)
+            assert rel_err(out, ref) < 1e-2, (bnf, nacc, upp, rel_err(out, ref))
+            assert torch.equal(out, ops.gemm(a, b, static_b=True, **kw)), "must be deterministic"
+            r2 = r.clone()
+            ops.gemm(a, b, out=r2, residual=r2, epilogue="add", **kw)
+            assert rel_err(r2, ref + r.float()) < 1e-2, (bnf, nacc, upp)
+            out2 = ops.gemm(a, gu, epilogue="silu_mul", **kw)
+            assert rel_err(out2, ref2) < 1e-2, (bnf, nacc, upp)
+    ops.check_status()
+
+
+def test_gemm_pair_fp16_and_pdl_chain(ops):
+    torch.manual_seed(18)
+    a = torch.randn(192, 768, device="cuda", dtype=torch.float16)
+    w1 = torch.randn(768, 1536, device="cuda", dtype=torch.float16) / 28
+    w2 = torch.randn(1536, 768, device="cuda", dtype=torch.float16) / 39
+    torch.cuda.synchronize()
+    # back-to-back dependent launches share the partial scratch: the second waits for the first before it writes
+    h = ops.gemm(a, w1, pair_path=True, static_b=True, pair_upp=5)
+    y = ops.gemm(h, w2, pair_path=True, static_b=True, pair_upp=7)
+    ref_h = (a.float() @ w1.float()).to(torch.float16)
+    assert rel_err(h, a.float() @ w1.float()) < 5e-3
+    assert rel_err(y, ref_h.float() @ w2.float()) < 5e-3
+    ops.check_status()
+
+
 def test_gemm_decode_fp16_and_pdl_chain(ops):
     torch.manual_seed(14)
     a = torch.randn(48, 768, device="cuda", dtype=torch.float16)

@@ -341,6 +341,40 @@ def test_native_generation_encoding_equals_the_message_built_one():
     b.clear()
 
 
+def test_migration_page_lists_stay_aligned_when_one_side_has_filtered():
+    """Both ends of a KV migration list pages per request of the RPC, in its order; a request one side no longer holds
+    keeps its entries as -1, so entry i always faces entry i (a relayed batch whose request ended at its first token)."""
+    from blitz_scale_b200.runtime import core
+    src_pool, dst_pool = core.PagePool(64, 16), core.PagePool(64, 16)
+    specs = [core.SeqSpec(11, [1] * 40, 1), core.SeqSpec(12, [2] * 16, 8), core.SeqSpec(13, [3] * 5, 8)]
+    src, dst = core.Batch(9, src_pool), core.Batch(9, dst_pool)
+    assert src.add_prompts(specs) and dst.add_prompts(list(reversed(specs)))      # the destination allocated in another order
+    ids, lens = [11, 12, 13], [40, 16, 5]
+    a, b = src.prompt_page_ids_for(ids, lens), dst.prompt_page_ids_for(ids, lens)
+    assert len(a) == len(b) == 3 + 1 + 1 and -1 not in a and -1 not in b
+    by_req = {s.spec.id: list(s.pages) for s in dst.seqs}
+    assert b == by_req[11][:3] + by_req[12][:1] + by_req[13][:1]
+    # request 11 finished at its first token on the source: its batch was filtered, the destination still holds all
+    src.mark_prefilled()
+    src.append_tokens([5, 6, 7], False)
+    src.filter(src.unfinished_ids())
+    a2 = src.prompt_page_ids_for(ids, lens)
+    assert a2[:3] == [-1, -1, -1] and a2[3:] == a[3:] and len(a2) == len(b)
+    # the second half names the survivors only: both sides list exactly those
+    assert len(src.prompt_page_ids_for([12, 13], [16, 5])) == len(dst.prompt_page_ids_for([12, 13], [16, 5])) == 2
+    with pytest.raises(Exception):
+        src.prompt_page_ids_for([12], [16, 5])
+    # a finished request left in a decode batch is carried as a padded row instead of indexing past its pages
+    d = core.Batch(1, dst_pool)
+    assert d.add_prompts([core.SeqSpec(1, [1] * 16, 1), core.SeqSpec(2, [1] * 3, 4)])
+    d.mark_prefilled()
+    d.append_tokens([9, 9], False)
+    L = core.MetaLayout.make(64, 8, 64)
+    h = np.zeros(L.total, dtype=np.int32)
+    P = d.fill_decode(h, L, 4)
+    assert h[L.slot + 0] == -1 and h[L.last_page_len + 0] == 0 and h[L.slot + 1] >= 0 and P == 1
+
+
 def test_native_generation_reader_agrees_with_the_protobuf_library():
     from blitz_scale_b200.pb.schema import pb
     from blitz_scale_b200.worker.service import make_generation
