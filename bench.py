@@ -17,6 +17,13 @@ Two numbers are reported:
              sampled tokens device->host, updates the page tables on the host.
 Per step each replica touches all weights (~15 GB) and its KV working set (batch x ctx x 128 KB),
 far beyond the 126 MB L2, so no explicit flush is needed between iterations.
+
+`vs_baseline`: the reference publishes no numbers and cannot be built here, so the anchor is a stand-in
+measured in the same run, before the product's own numbers and on the same GPUs: the reference's decode
+iteration on cuBLAS GEMMs and a library paged decode attention (`baseline/decode_step.py`), same model
+shape, batch, context, CUDA-graph timing and end-to-end definition.  `--impl baseline` prints that arm
+alone; `--no-baseline` skips it (vs_baseline is then null).  With --tp > 1 the stand-in is the NCCL
+all-reduce runner (`--no-fused-tp`), which this script does not run by itself.
 """
 from __future__ import annotations
 
@@ -94,6 +101,7 @@ def main():
                     "peer-memory all-reduce instead of the reduce-scatter / all-gather pipeline")
     ap.add_argument("--no-fused-tp", action="store_true", help="tp > 1: NCCL all-reduce layers (the baseline) instead of the "
                     "fused peer-memory kernels")
+    ap.add_argument("--no-baseline", action="store_true", help="do not run the stand-in baseline arm first")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -114,6 +122,52 @@ def main():
     from blitz_scale_b200 import ops
 
     B, ctx, ps = args.batch, args.ctx, args.page_size
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(*vals):
+        if world == 1:
+            return list(vals)
+        t = torch.tensor(list(vals), device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(x) for x in t]
+
+    # ---------------- stand-in baseline arm (library kernels only), same GPUs, before the product's own run
+    base = None
+    if args.impl == "baseline" or (not args.no_baseline and args.tp <= 1):
+        r, err = None, ""
+        try:
+            from baseline import decode_step
+            r = decode_step.run(args.model, B, ctx, args.steps, args.warmup, torch.device("cuda", local),
+                                seed=rank, barrier=barrier)
+        except Exception as e:  # noqa: BLE001  (the product's number must not depend on the stand-in)
+            err = f"{type(e).__name__}: {e}"[:300]
+        # every rank takes part in the reduction whether or not its own arm worked
+        dev_b, e2e_b, failed = max_over_ranks(r["dev_s"] if r else 0.0, r["e2e_s"] if r else 0.0, 0.0 if r else 1.0)
+        if r is not None and failed == 0.0:
+            tokens_b = world * B * args.steps
+            base = {"value": tokens_b / dev_b, "ms_per_step": dev_b / args.steps * 1e3,
+                    "e2e_value": tokens_b / e2e_b, "e2e_ms_per_step": e2e_b / args.steps * 1e3,
+                    "gemm": "cuBLAS (torch.matmul / addmm)", "attention": r["attention"], "kv_block": r["page"],
+                    "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": r["d2h_bytes_per_step"]}
+        else:
+            base = {"error": err or "the arm failed on another rank"}
+    if args.impl == "baseline":
+        if rank == 0:
+            ok = base is not None and "value" in base
+            print(json.dumps({"impl": "baseline", "metric": "decode_tokens_per_s", "value": base["value"] if ok else None,
+                              "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                              "ms_per_step": base["ms_per_step"] if ok else None, "higher_is_better": True,
+                              "scaling": "weak", "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+                              "config": {"model": args.model, "global_batch": world * B, "seq_len": ctx,
+                                         "parallelism": f"dp{world}"}, "detail": base}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
     total_steps = args.warmup + args.steps + 8
     pages_per_seq = (ctx + total_steps + ps) // ps + 1
     tp = max(1, args.tp)
@@ -149,11 +203,6 @@ def main():
             batch.extend(nb)
     ops.check_status()
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     # ---------------- e2e: real decode steps through the public engine API
     for _ in range(args.warmup):
         eng.decode(batch)
@@ -188,17 +237,16 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     ops.check_status()
 
-    if world > 1:
-        t = torch.tensor([dev_s, e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_s, e2e_s = float(t[0]), float(t[1])
+    dev_s, e2e_s = max_over_ranks(dev_s, e2e_s)
     if rank == 0:
         replicas = world // tp
         tokens = replicas * B * args.steps
+        have_base = base is not None and "value" in base
         out = {
             "metric": "decode_tokens_per_s", "value": tokens / dev_s, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (tokens / dev_s) / base["value"] if have_base else None, "dtype": "bf16",
             "data": "synthetic token ids, random-init weights",
             "config": {"model": args.model, "global_batch": replicas * B, "seq_len": ctx,
                        "parallelism": f"dp{replicas}" + (f"xtp{tp}" + ("" if eng.fused is not None else "-nccl") if tp > 1 else ""),
@@ -206,7 +254,10 @@ def main():
                        "timing": "CUDA events around K graph replays, max over ranks"},
             "clocks": clocks,
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "ms_per_step": e2e_s / args.steps * 1e3,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "vs_baseline": (tokens / e2e_s) / base["e2e_value"] if have_base else None},
+            "baseline": ({**base, "what": "stand-in for the reference (not buildable here): its decode iteration on "
+                          "library kernels, measured in this run on the same GPUs"} if base is not None else None),
             "gpu_launches": eng.decode_launch_count() * args.steps,
         }
         print(json.dumps(out))

@@ -40,7 +40,7 @@ namespace blitz {
 
 constexpr int kTcThreads = 160;
 constexpr int kTcChunk = 64;
-constexpr int kTcStages = 4;
+constexpr int kTcStages = 6;
 constexpr int kTcSlabBytes = kTcChunk * 128;
 
 struct DecodeTcParams {
@@ -54,6 +54,7 @@ struct DecodeTcParams {
   float* part_o;
   float* part_lse;
   int batch, q_heads, kv_heads, group, page_size, max_pages, num_splits, box_tokens;
+  int tail_box_tokens;  // box height of the second tensor map, used for the last (partly filled) chunk of a sequence
   float scale_log2;
   int* status;
 };
@@ -118,7 +119,8 @@ __device__ __forceinline__ DecItem dec_item(const DecodeTcParams& p, int item) {
 
 template <typename T, int HD>
 __global__ void __launch_bounds__(kTcThreads)
-attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcParams p) {
+attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_tail,
+                      const DecodeTcParams p) {
   using Cfg = TcCfg<HD>;
   constexpr int SL = Cfg::kSlabs;
   extern __shared__ uint8_t smem_raw[];
@@ -146,6 +148,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcPa
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::tma_prefetch_desc(&tmap);
+    ptx::tma_prefetch_desc(&tmap_tail);
   }
   ptx::fence_proxy_async_smem();
   __syncthreads();
@@ -155,47 +158,84 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcPa
   ptx::griddep_wait();
 
   if (warp == 4) {
-    // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      const int bt = p.box_tokens;
-      const uint32_t box_bytes = static_cast<uint32_t>(bt) * 128u;
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-        const DecItem it = dec_item(p, item);
-        for (int c = it.c_beg; c < it.c_end; ++c) {
+    // ------------------------------------------------------------ producer (whole warp; lane 0 issues)
+    // A TMA box can only be issued once its page id is known, and a page id read from global memory right before
+    // the issue costs one memory latency per chunk, which by itself caps the stream near 50 GB/s per SM.  So the
+    // warp reads page ids 32 at a time (one coalesced load, lane l keeps entry l of the window), hands them out by
+    // shuffle, and requests the next item's page-table window and lengths while the current item streams.
+    const int ps = p.page_size;
+    auto load_window = [&](const DecItem& it, int first_page) -> int {
+      const int npages = p.indptr[it.b + 1] - it.pg_beg;
+      return (first_page + lane < npages) ? p.indices[it.pg_beg + first_page + lane] : 0;
+    };
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int item = blockIdx.x;
+    DecItem it = item < num_items ? dec_item(p, item) : DecItem{};
+    int win_base = item < num_items ? (it.c_beg * kTcChunk) / ps : 0;
+    int win = item < num_items ? load_window(it, win_base) : 0;
+    while (item < num_items && ok) {
+      // next item's metadata and first window: in flight while this item streams
+      const int next = item + gridDim.x;
+      DecItem nit = next < num_items ? dec_item(p, next) : DecItem{};
+      const int nwin_base = next < num_items ? (nit.c_beg * kTcChunk) / ps : 0;
+      const int nwin = next < num_items ? load_window(nit, nwin_base) : 0;
+      for (int c = it.c_beg; c < it.c_end && ok; ++c) {
+        const int tok0 = c * kTcChunk;
+        const int ntok = min(kTcChunk, it.seq_len - tok0);
+        // a full chunk comes in boxes of box_tokens rows; the last chunk of a sequence only as far as it is
+        // filled, in the smaller boxes of the second map (a 64-token page with 18 live tokens costs 32 rows)
+        const bool tail = ntok < kTcChunk;
+        const int bt = tail ? p.tail_box_tokens : p.box_tokens;
+        const CUtensorMap* tm = tail ? &tmap_tail : &tmap;
+        const uint32_t box_bytes = static_cast<uint32_t>(bt) * 128u;
+        const int pieces = (ntok + bt - 1) / bt;
+        const int last_page = (tok0 + ntok - 1) / ps;
+        if (last_page >= win_base + 32) {  // sequences of more than 32 pages: move the window
+          win_base = tok0 / ps;
+          win = load_window(it, win_base);
+        }
+        int good = 1;
+        if (lane == 0) {
           if (!ptx::bounded_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             if (p.status) atomicCAS(p.status, 0, kStatusTimeoutProducer);
-            ok = false;
-            break;
+            good = 0;
+          } else {
+            ptx::mbar_expect_tx(&full_bar[stage], static_cast<uint32_t>(pieces) * 2u * SL * box_bytes);
           }
-          const int tok0 = c * kTcChunk;
-          const int ntok = min(kTcChunk, it.seq_len - tok0);
-          const int pieces = (ntok + bt - 1) / bt;
-          ptx::mbar_expect_tx(&full_bar[stage], static_cast<uint32_t>(pieces) * 2u * SL * box_bytes);
-          uint8_t* sb = smem + stage * Cfg::kStageBytes;
-          for (int i = 0; i < pieces; ++i) {
-            const int t = tok0 + i * bt;
-            int page = p.indices[it.pg_beg + t / p.page_size];
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) {
+          ok = false;
+          break;
+        }
+        uint8_t* sb = smem + stage * Cfg::kStageBytes;
+        for (int i = 0; i < pieces; ++i) {
+          const int t = tok0 + i * bt;
+          int page = __shfl_sync(0xffffffffu, win, (t / ps - win_base) & 31);
+          if (lane == 0) {
             if (page < 0 || page >= p.max_pages) {
               if (p.status) atomicCAS(p.status, 0, kStatusBadIndex);
               page = 0;
             }
-            const int z = page * 2 * p.page_size + (t % p.page_size);
+            const int z = page * 2 * ps + (t % ps);
 #pragma unroll
             for (int s = 0; s < SL; ++s) {
-              ptx::tma_load_3d(sb + s * kTcSlabBytes + i * box_bytes, &tmap, &full_bar[stage], s * 64, it.h, z);
-              ptx::tma_load_3d(sb + (SL + s) * kTcSlabBytes + i * box_bytes, &tmap, &full_bar[stage], s * 64, it.h,
-                               z + p.page_size);
+              ptx::tma_load_3d(sb + s * kTcSlabBytes + i * box_bytes, tm, &full_bar[stage], s * 64, it.h, z);
+              ptx::tma_load_3d(sb + (SL + s) * kTcSlabBytes + i * box_bytes, tm, &full_bar[stage], s * 64, it.h, z + ps);
             }
           }
-          if (++stage == kTcStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+        }
+        if (++stage == kTcStages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
+      item = next;
+      it = nit;
+      win_base = nwin_base;
+      win = nwin;
     }
   } else {
     // ------------------------------------------------------------ consumers (128 threads, named barrier 1)
@@ -205,18 +245,29 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcPa
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;  // after a timeout this warp stops waiting but keeps meeting the others at the barriers
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-      const DecItem it = dec_item(p, item);
+    // The consumers stop consuming between two items (merge, then the next item's lengths and query rows), and a
+    // pause longer than the pipeline can absorb empties the memory pipe, which then costs a full latency to refill.
+    // So the next item's descriptor and Q fragments are requested while the current item is being processed.
+    auto load_q = [&](const DecItem& d, uint32_t (&a0)[HD / 16], uint32_t (&a2)[HD / 16]) {
       // Q as A fragments (rows >= G are zero padding; rows 8..15 are never populated since G <= 8)
-      uint32_t qa0[HD / 16], qa2[HD / 16];
-      {
-        const T* qrow = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(it.b) * p.q_stride +
-                        static_cast<int64_t>(it.h * G + g) * HD;
+      const T* qrow = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(d.b) * p.q_stride +
+                      static_cast<int64_t>(d.h * G + g) * HD;
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          qa0[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4) : 0u;
-          qa2[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8) : 0u;
-        }
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        a0[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4) : 0u;
+        a2[ks] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8) : 0u;
+      }
+    };
+    DecItem it = blockIdx.x < num_items ? dec_item(p, blockIdx.x) : DecItem{};
+    uint32_t qa0[HD / 16], qa2[HD / 16];
+    if (blockIdx.x < num_items) load_q(it, qa0, qa2);
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const int next = item + gridDim.x;
+      DecItem nit = DecItem{};
+      uint32_t nqa0[HD / 16], nqa2[HD / 16];
+      if (next < num_items) {
+        nit = dec_item(p, next);
+        load_q(nit, nqa0, nqa2);
       }
       float o[HD / 8][4];
 #pragma unroll
@@ -330,6 +381,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeTcPa
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // merge buffers are reused by the next item
+      it = nit;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        qa0[ks] = nqa0[ks];
+        qa2[ks] = nqa2[ks];
+      }
     }
   }
 }
@@ -361,14 +418,16 @@ __global__ void attn_merge_tc_kernel(const float* __restrict__ part_o, const flo
 }
 
 template <typename T, int HD>
-static int launch_tc(const CUtensorMap& tm, const DecodeTcParams& p, int batch, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& tm, const CUtensorMap& tm_tail, const DecodeTcParams& p, int batch,
+                     cudaStream_t stream) {
   auto kern = attn_decode_tc_kernel<T, HD>;
   static PerDeviceOnce once;
   cudaError_t e = once.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<HD>::kSmemBytes); });
   if (e != cudaSuccess) return (int)e;
   const int items = batch * p.kv_heads * p.num_splits;
   const int sms = device_sm_count();
-  return (int)launch_pdl(kern, dim3(items < sms ? items : sms), dim3(kTcThreads), TcCfg<HD>::kSmemBytes, stream, tm, p);
+  return (int)launch_pdl(kern, dim3(items < sms ? items : sms), dim3(kTcThreads), TcCfg<HD>::kSmemBytes, stream, tm,
+                         tm_tail, p);
 }
 
 }  // namespace blitz
@@ -397,9 +456,13 @@ int blitz_attn_decode(const void* q, int64_t q_stride, const void* kv_layer, con
   if (page_size < 8 || (page_size & (page_size - 1)) != 0) return -1;
   if (num_splits > 1 && workspace == nullptr) return -1;
   const int bt = page_size < kTcChunk ? page_size : kTcChunk;
-  CUtensorMap tm;
+  const int bt_tail = bt < 16 ? bt : 16;
+  CUtensorMap tm, tm_tail;
   if (!get_tmap_3d(&tm, kv_layer, (uint64_t)head_dim, (uint64_t)kv_heads, (uint64_t)max_pages * 2 * page_size,
                    (uint64_t)head_dim * 2, (uint64_t)kv_heads * head_dim * 2, 64, 1, (uint32_t)bt))
+    return -2;
+  if (!get_tmap_3d(&tm_tail, kv_layer, (uint64_t)head_dim, (uint64_t)kv_heads, (uint64_t)max_pages * 2 * page_size,
+                   (uint64_t)head_dim * 2, (uint64_t)kv_heads * head_dim * 2, 64, 1, (uint32_t)bt_tail))
     return -2;
   DecodeTcParams p;
   p.q = q; p.q_stride = q_stride; p.indices = indices; p.indptr = indptr; p.last_page_len = last_page_len;
@@ -407,13 +470,15 @@ int blitz_attn_decode(const void* q, int64_t q_stride, const void* kv_layer, con
   p.part_o = reinterpret_cast<float*>(workspace);
   p.part_lse = p.part_o ? p.part_o + (int64_t)batch * q_heads * num_splits * head_dim : nullptr;
   p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size; p.max_pages = max_pages;
-  p.num_splits = num_splits; p.box_tokens = bt; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
+  p.num_splits = num_splits; p.box_tokens = bt; p.tail_box_tokens = bt_tail;
+  p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
   int rc;
   if (dtype == 1)
-    rc = head_dim == 128 ? launch_tc<__nv_bfloat16, 128>(tm, p, batch, stream)
-                         : launch_tc<__nv_bfloat16, 64>(tm, p, batch, stream);
+    rc = head_dim == 128 ? launch_tc<__nv_bfloat16, 128>(tm, tm_tail, p, batch, stream)
+                         : launch_tc<__nv_bfloat16, 64>(tm, tm_tail, p, batch, stream);
   else
-    rc = head_dim == 128 ? launch_tc<__half, 128>(tm, p, batch, stream) : launch_tc<__half, 64>(tm, p, batch, stream);
+    rc = head_dim == 128 ? launch_tc<__half, 128>(tm, tm_tail, p, batch, stream)
+                         : launch_tc<__half, 64>(tm, tm_tail, p, batch, stream);
   if (rc != 0) return rc;
   if (num_splits > 1) {
     dim3 grid(batch, q_heads);
@@ -481,9 +546,10 @@ static bool noalloc_tmap(CUtensorMap* out, const void* kv_layer, int head_dim, i
 }
 
 template <typename T, int HD>
-static int noalloc_launch(const CUtensorMap& tm, const DecodeTcParams& p, int sms, cudaStream_t stream) {
+static int noalloc_launch(const CUtensorMap& tm, const CUtensorMap& tm_tail, const DecodeTcParams& p, int sms,
+                          cudaStream_t stream) {
   const int items = p.batch * p.kv_heads * p.num_splits;
-  attn_decode_tc_kernel<T, HD><<<items < sms ? items : sms, kTcThreads, TcCfg<HD>::kSmemBytes, stream>>>(tm, p);
+  attn_decode_tc_kernel<T, HD><<<items < sms ? items : sms, kTcThreads, TcCfg<HD>::kSmemBytes, stream>>>(tm, tm_tail, p);
   return (int)cudaGetLastError();
 }
 
@@ -511,24 +577,28 @@ extern "C" int blitz_attn_decode_noalloc(const void* q, int64_t q_stride, const 
   void* const scratch = g_noalloc_ptr[dev].load(std::memory_order_acquire);
   if (scratch == nullptr) return (int)cudaErrorInvalidSymbol;
   const int bt = page_size < kTcChunk ? page_size : kTcChunk;
-  CUtensorMap tm;
+  const int bt_tail = bt < 16 ? bt : 16;
+  CUtensorMap tm, tm_tail;
   if (!noalloc_tmap(&tm, kv_layer, head_dim, kv_heads, max_pages, page_size, bt)) return -2;
+  if (!noalloc_tmap(&tm_tail, kv_layer, head_dim, kv_heads, max_pages, page_size, bt_tail)) return -2;
   DecodeTcParams p;
   p.q = q; p.q_stride = q_stride; p.indices = indices; p.indptr = indptr; p.last_page_len = last_page_len;
   p.out = out; p.out_stride = out_stride;
   p.part_o = reinterpret_cast<float*>(scratch);
   p.part_lse = p.part_o + (int64_t)batch * q_heads * num_splits * head_dim;
   p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size;
-  p.max_pages = max_pages; p.num_splits = num_splits; p.box_tokens = bt;
+  p.max_pages = max_pages; p.num_splits = num_splits; p.box_tokens = bt; p.tail_box_tokens = bt_tail;
   p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
   int rc;
   if (dtype == 1)
-    rc = head_dim == 128 ? noalloc_launch<__nv_bfloat16, 128>(tm, p, sms, stream) : noalloc_launch<__nv_bfloat16, 64>(tm, p, sms, stream);
+    rc = head_dim == 128 ? noalloc_launch<__nv_bfloat16, 128>(tm, tm_tail, p, sms, stream)
+                         : noalloc_launch<__nv_bfloat16, 64>(tm, tm_tail, p, sms, stream);
   else
-    rc = head_dim == 128 ? noalloc_launch<__half, 128>(tm, p, sms, stream) : noalloc_launch<__half, 64>(tm, p, sms, stream);
+    rc = head_dim == 128 ? noalloc_launch<__half, 128>(tm, tm_tail, p, sms, stream)
+                         : noalloc_launch<__half, 64>(tm, tm_tail, p, sms, stream);
   if (rc != 0 || num_splits == 1) return rc;
   dim3 grid(batch, q_heads);
   if (dtype == 1)

@@ -532,4 +532,10 @@ class GpuBackend(Backend):
             self.engine.set_status_ready()
 
     def close(self):
+        """Stop the live-execution thread and wait for it: a thread that is still inside a native call when the
+        interpreter shuts down takes the process down with it."""
         self._stop = True
+        with self.lock:
+            self.zag_cv.notify_all()
+        if self.zag_thread.is_alive() and threading.current_thread() is not self.zag_thread:
+            self.zag_thread.join(timeout=5.0)
