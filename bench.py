@@ -165,7 +165,8 @@ def main():
                               "config": {"model": args.model, "global_batch": world * B, "seq_len": ctx,
                                          "parallelism": f"dp{world}"}, "detail": base}))
         if world > 1:
-            dist.destroy_process_group()
+            from blitz_scale_b200.parallel.teardown import shutdown
+            shutdown([])
         return 0
 
     total_steps = args.warmup + args.steps + 8
@@ -263,9 +264,9 @@ def main():
         print(json.dumps(out))
     if world > 1:
         sys.stdout.flush()
-        if tp > 1:
-            os._exit(0)      # symmetric-memory teardown with live graphs can block for minutes
-        dist.destroy_process_group()
+        from blitz_scale_b200.parallel.teardown import shutdown
+        del graph
+        shutdown([eng])      # graphs, then symmetric regions, then process groups, with barriers in between
     return 0
 
 

@@ -125,7 +125,9 @@ def main():
             json.dump(result, open(a.json, "w"), indent=1)
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0 if int(flag) else 1)
+    from blitz_scale_b200.parallel.teardown import shutdown
+    shutdown([backend])      # graphs, then symmetric regions, then process groups, with barriers in between
+    sys.exit(0 if int(flag) else 1)
 
 
 def run_router(a, world, states, cfg_model, backend):

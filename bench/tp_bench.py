@@ -134,7 +134,8 @@ def main():
         json.dump(out, open(a.json, "w"), indent=1)
     dist.barrier()
     sys.stdout.flush()
-    os._exit(0)      # skip symmetric-memory / NCCL teardown, which can block for minutes with live graphs
+    from blitz_scale_b200.parallel.teardown import shutdown
+    shutdown([fused])      # graphs (local to the timing helpers, already gone), symmetric regions, process groups
 
 
 if __name__ == "__main__":

@@ -68,6 +68,14 @@ class SymmRegion:
     def barrier(self) -> None:
         self.handle.barrier()
 
+    def close_regions(self) -> None:
+        """Drop the mapping (local tensor and rendezvous handle).  Call on every rank, between two barriers, after
+        everything that names this region's pointers (kernels, captured graphs) is gone."""
+        self.handle = None
+        self.local = None
+        self.ptrs = []
+        self.mc_ptr = 0
+
 
 @dataclass
 class FabricSizes:
@@ -96,6 +104,10 @@ class PeerFabric:
         self.tickets = torch.zeros(4096, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         self.flags.barrier()
+
+    def close_regions(self) -> None:
+        for r in (self.weights, self.kv, self.mailbox, self.flags):
+            r.close_regions()
 
     # ------------------------------------------------------------------ flags
     def flag_view(self) -> torch.Tensor:

@@ -67,6 +67,9 @@ class FusedTP:
         self.device = self.region.local.device
         self.budget_ns = int(2e9)
 
+    def close_regions(self) -> None:
+        self.region.close_regions()
+
     # ------------------------------------------------------------------ views / pointers
     def xg(self, which: int, rows: int) -> torch.Tensor:
         off = self.o_xg[which]

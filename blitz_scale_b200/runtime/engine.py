@@ -233,6 +233,16 @@ class Engine:
         torch.cuda.current_stream().synchronize()
         return n
 
+    def release_graphs(self) -> None:
+        """Drop every captured decode graph (first step of an orderly exit: the graphs hold kernel arguments that
+        name peer memory and, with the NCCL runner, collectives of its communicator)."""
+        self._graphs.clear()
+
+    def close_regions(self) -> None:
+        """Drop the symmetric regions this engine owns (the fused tensor-parallel state); see parallel/teardown.py."""
+        if self.fused is not None:
+            self.fused.close_regions()
+
     def decode_launch_count(self) -> int:
         """Kernels of this library launched by one decode step at tp = 1 (for the bench's launch accounting)."""
         per_layer = 8  # rms_norm, qkv gemm, rope_kv_store, attention, o gemm, rms_norm, gate_up gemm, down gemm

@@ -531,6 +531,16 @@ class GpuBackend(Backend):
         with self.lock:
             self.engine.set_status_ready()
 
+    def release_graphs(self) -> None:
+        self.engine.release_graphs()
+
+    def close_regions(self) -> None:
+        """Symmetric regions of this worker: engine (fused TP), fabric, control words.  See parallel/teardown.py."""
+        self.engine.close_regions()
+        if self.fabric is not None:
+            self.fabric.close_regions()
+            self.ctl.close_regions()
+
     def close(self):
         """Stop the live-execution thread and wait for it: a thread that is still inside a native call when the
         interpreter shuts down takes the process down with it."""

@@ -110,7 +110,8 @@ def main(argv=None) -> int:
     sys.stdout.flush()
     sys.stderr.flush()
     if world > 1:
-        os._exit(0)      # tearing down NCCL / symmetric memory with live CUDA graphs can block for minutes
+        from ..parallel.teardown import shutdown
+        shutdown([backend])      # graphs, then symmetric regions, then process groups, with barriers in between
     return 0
 
 

@@ -98,7 +98,9 @@ def main():
         print(f"cluster {case}: OK on {world} GPUs", flush=True)
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0 if good else 1)   # skip NCCL / symmetric-memory teardown (it can block for minutes)
+    from blitz_scale_b200.parallel.teardown import shutdown
+    shutdown([backend])          # graphs, then symmetric regions, then process groups, with barriers in between
+    sys.exit(0 if good else 1)
 
 
 def run_router(case, world, states, base_port) -> int:

@@ -23,6 +23,7 @@ def main():
     layers, pages, page_bytes = 4, 64, 2 * 16 * 2 * 128 * 2
     fab = symm.PeerFabric(symm.FabricSizes(weight_bytes=wbytes, kv_bytes=layers * pages * page_bytes,
                                            mailbox_slots=4, mailbox_slot_bytes=1 << 20))
+    owners = [fab]          # what holds CUDA graphs or symmetric regions: handed to the orderly exit at the end
     use_mm = case.endswith("_multimem")
     if use_mm and not fab.weights.mc_ptr:
         if rank == 0:
@@ -143,6 +144,7 @@ def main():
         kvshape = (cfg.layers, max_pages, 2, page, cfg.kv_heads // tp, cfg.head_dim)
         comm = TPComm(dist.group.WORLD)
         fused = FusedTP(dist.group.WORLD, cfg.hidden, 1024)
+        owners.append(fused)
         r_fused = LlamaRunnerTP(seg, torch.zeros(kvshape, dtype=torch.bfloat16, device="cuda"), 1024, 16, comm, fused)
         r_nccl = LlamaRunner(seg, torch.zeros(kvshape, dtype=torch.bfloat16, device="cuda"), 1024, 16, comm=comm)
         mb = MetaBuilder(1024, 16, max_pages, page)
@@ -209,6 +211,7 @@ def main():
             eng = Engine("tiny_gpu", num_pages=64, page_size=16, max_batch=8, max_batch_tokens=1024, tp=world, tp_rank=rank,
                          comm=comm, seed=4, fused_tp=fused_tp, oneshot_max_rows=oneshot)   # 0: always the row-sharded pipeline
             assert (eng.fused is not None) == fused_tp
+            owners.append(eng)
             g = torch.Generator().manual_seed(9)
             specs = [core.SeqSpec(i, torch.randint(0, 4096, (n,), generator=g).tolist(), 8) for i, n in enumerate((33, 7, 120))]
             b = eng.new_batch(1, specs)
@@ -243,11 +246,14 @@ def main():
     dist.barrier()
     if rank == 0:
         print(f"{case}: OK on {world} ranks", flush=True)
-    # leave without tearing down NCCL / symmetric memory: destroying a process group while captured graphs and
-    # peer mappings still reference it can block for minutes, and nothing here needs an orderly teardown
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0)
+    # orderly exit: graphs, then symmetric regions, then process groups, with barriers in between
+    from blitz_scale_b200.parallel.teardown import shutdown
+    took = shutdown(owners)
+    if rank == 0:
+        print(f"{case}: teardown {took:.2f} s", flush=True)
+    return 0
 
 
 if __name__ == "__main__":
