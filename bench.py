@@ -86,6 +86,61 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(self.rows)}
 
 
+def measure_tp_replica(args, world, rank, barrier, owners):
+    """One replica spanning all `world` GPUs (tensor parallel), decode step timed on the device for the fused
+    peer-memory runner and for the NCCL all-reduce runner: a number in the record that depends on NVLink."""
+    import torch
+    import torch.distributed as dist
+    from blitz_scale_b200.models.llama import TPComm
+    from blitz_scale_b200.runtime import core
+    from blitz_scale_b200.runtime.engine import Engine, _BUCKETS
+    from blitz_scale_b200 import ops
+    B, ctx, ps = args.batch, args.ctx, args.page_size
+    steps, warmup = args.steps, args.warmup
+    comm = TPComm(dist.group.WORLD)
+    out = {"tp": world, "model": args.model, "batch": B, "seq_len": ctx}
+    for name, fused in (("fused", True), ("nccl", False)):
+        eng = Engine(args.model, num_pages=B * ((ctx + warmup + steps + 16 + ps) // ps + 1) + 8, page_size=ps,
+                     max_batch=max(B, 8), max_batch_tokens=8192, seed=0, tp=world, tp_rank=rank, comm=comm,
+                     fused_tp=fused, oneshot_max_rows=args.oneshot_max_rows)
+        owners.append(eng)
+        g = torch.Generator().manual_seed(77)          # every rank of the replica sees the same prompts
+        per, batch, bid = max(1, 8192 // ctx), None, 0
+        for s0 in range(0, B, per):
+            n = min(per, B - s0)
+            nb = eng.new_batch(bid, [core.SeqSpec(s0 + i, torch.randint(0, eng.cfg.vocab, (ctx,), generator=g).tolist(),
+                                                  warmup + steps + 12) for i in range(n)])
+            bid += 1
+            eng.prefill(nb)
+            if batch is None:
+                batch = nb
+            else:
+                batch.extend(nb)
+        for _ in range(warmup):
+            eng.decode(batch)
+        Bp = min(b for b in _BUCKETS if b >= B)
+        splits = eng.choose_splits(Bp, batch.max_seq_len())
+        graph = eng._graphs.get((Bp, splits)) or eng._capture(Bp, splits)
+        for _ in range(warmup):
+            graph.replay()
+        barrier()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(steps):
+            graph.replay()
+        k1.record()
+        barrier()
+        t = torch.tensor([k0.elapsed_time(k1) * 1e-3], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ops.check_status()
+        out[f"{name}_ms_per_step"] = float(t[0]) / steps * 1e3
+        out[f"{name}_tokens_per_s"] = B * steps / float(t[0])
+        del graph, batch
+        eng.release_graphs()
+    out["fused_vs_nccl"] = out["nccl_ms_per_step"] / out["fused_ms_per_step"]
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -102,6 +157,8 @@ def main():
     ap.add_argument("--no-fused-tp", action="store_true", help="tp > 1: NCCL all-reduce layers (the baseline) instead of the "
                     "fused peer-memory kernels")
     ap.add_argument("--no-baseline", action="store_true", help="do not run the stand-in baseline arm first")
+    ap.add_argument("--no-extra-tp", action="store_true", help="N > 1: do not add the tensor-parallel record "
+                    "(one replica over all N GPUs, fused peer-memory runner against the NCCL runner)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -239,6 +296,16 @@ def main():
     ops.check_status()
 
     dev_s, e2e_s = max_over_ranks(dev_s, e2e_s)
+    owners = [eng]
+    extra = None
+    if world > 1 and tp == 1 and not args.no_extra_tp and world in (2, 4, 8):
+        del graph, batch
+        eng.release_graphs()
+        try:
+            extra = {"tp": measure_tp_replica(args, world, rank, barrier, owners)}
+        except Exception as e:  # noqa: BLE001  (the headline line must not depend on the extra record)
+            extra = {"tp": {"error": f"{type(e).__name__}: {e}"[:300]}}
+        graph = None
     if rank == 0:
         replicas = world // tp
         tokens = replicas * B * args.steps
@@ -261,12 +328,14 @@ def main():
                           "library kernels, measured in this run on the same GPUs"} if base is not None else None),
             "gpu_launches": eng.decode_launch_count() * args.steps,
         }
+        if extra is not None:
+            out["extra"] = extra
         print(json.dumps(out))
     if world > 1:
         sys.stdout.flush()
         from blitz_scale_b200.parallel.teardown import shutdown
-        del graph
-        shutdown([eng])      # graphs, then symmetric regions, then process groups, with barriers in between
+        graph = None
+        shutdown(owners)     # graphs, then symmetric regions, then process groups, with barriers in between
     return 0
 
 

@@ -199,6 +199,10 @@ class RouterApp:
             toks = toks[-int(p["truncate"]):]
         g.has_seed = p.get("seed") is not None
         err = core.validate_request(g, self.limits)
+        if not err and g.best_of > 1:
+            # candidates would have to be ranked by sequence log-probability, which the workers do not return
+            # (Generation.logprobs is always 0, as in the reference's workers): refuse instead of ignoring the field
+            err = "`best_of` > 1 is not supported: the workers return no log-probabilities to rank candidates by"
         if not err and g.do_sample:
             # carried to the worker in the request's NextTokenChooserParameters; greedy requests carry none
             seed = int(p["seed"]) if g.has_seed else zlib.crc32(repr((toks[:16], time.time_ns())).encode())

@@ -803,6 +803,9 @@ def test_sampling_parameters_reach_the_worker():
             greedy2 = await gen({})
             async with s.post(url, json={"input_tokens": [1, 2], "parameters": {"do_sample": True, "temperature": -1.0}}) as r:
                 bad = r.status
+            # best_of > 1 is refused, not silently ignored
+            async with s.post(url, json={"input_tokens": [1, 2], "parameters": {"do_sample": True, "best_of": 2}}) as r:
+                assert r.status == 422 and "best_of" in (await r.text())
         await _shutdown(stop, tasks)
         return greedy, greedy2, a1, a2, b, k, bad
     greedy, greedy2, a1, a2, b, k, bad = asyncio.run(go())
