@@ -64,6 +64,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--hidden", type=int, default=8192)
+    ap.add_argument("--small-only", action="store_true", help="only the decode-size all-reduce + add + norm comparison")
     a = ap.parse_args()
     rank, tp = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -72,7 +73,7 @@ def main():
     flops_peak, src = peaks()
     fused = FusedTP(dist.group.WORLD, H, 4096)
     out = []
-    for M in (16, 256, 4096):
+    for M in ((16, 256, 4096) if not a.small_only else ()):
         torch.manual_seed(rank)
         x = torch.randn(M, H // tp, device="cuda", dtype=torch.bfloat16)             # row-parallel input (K sharded)
         w_row = torch.randn(H // tp, H, device="cuda", dtype=torch.bfloat16) * H ** -0.5
@@ -129,6 +130,53 @@ def main():
                        stage_us_gemm_rs_reduce_norm_ag_gemm=stages)
             out.append(row)
             print(json.dumps(row), flush=True)
+    # Decode-size all-reduce + residual add + RMSNorm: the switch-reduced one-kernel form, the one-shot push form
+    # followed by the add+norm kernel, and NCCL all-reduce followed by the add+norm kernel.  Eight dependent
+    # rounds per graph replay, so the time per round includes the launch gap a layer loop sees.
+    for Hs in (4096, 8192):
+        f2 = fused if Hs == H else FusedTP(dist.group.WORLD, Hs, 1024)
+        for M in (16, 256, 1024):
+            nw = torch.ones(Hs, device="cuda", dtype=torch.bfloat16)
+            xin = torch.randn(M, Hs, device="cuda", dtype=torch.bfloat16)
+            resid = torch.zeros(M, Hs, device="cuda", dtype=torch.bfloat16)
+            tmp = torch.empty(M, Hs, device="cuda", dtype=torch.bfloat16)
+            normed = torch.empty(M, Hs, device="cuda", dtype=torch.bfloat16)
+            rounds = 8
+
+            def run_switch():
+                for _ in range(rounds):
+                    f2.next_partial(M).copy_(xin)
+                    f2.ar_add_norm(M, nw, 1e-5)
+
+            def run_oneshot():
+                for _ in range(rounds):
+                    tmp.copy_(xin)
+                    f2.allreduce_oneshot(tmp, tmp)
+                    ops.add_rms_norm(tmp, resid, nw, 1e-5, out=normed)
+
+            def run_nccl2():
+                for _ in range(rounds):
+                    tmp.copy_(xin)
+                    dist.all_reduce(tmp)
+                    ops.add_rms_norm(tmp, resid, nw, 1e-5, out=normed)
+
+            def run_copy():
+                for _ in range(rounds):
+                    tmp.copy_(xin)
+
+            row = dict(kind="ar_add_norm", tp=tp, M=M, H=Hs, has_switch=bool(f2.has_mc))
+            t_c = graph_time(run_copy) / rounds
+            f2.reset_allreduce_parity()
+            if f2.has_mc:
+                f2.res(M).zero_()
+                row["switch_us"] = (graph_time(run_switch) / rounds - t_c) * 1e6
+            f2.reset_allreduce_parity()
+            row["oneshot_us"] = (graph_time(run_oneshot) / rounds - t_c) * 1e6
+            row["nccl_us"] = (graph_time(run_nccl2) / rounds - t_c) * 1e6
+            ops.check_status()
+            if rank == 0:
+                out.append(row)
+                print(json.dumps(row), flush=True)
     if rank == 0 and a.json:
         os.makedirs(os.path.dirname(os.path.abspath(a.json)), exist_ok=True)
         json.dump(out, open(a.json, "w"), indent=1)

@@ -248,6 +248,179 @@ __global__ void __launch_bounds__(256) allreduce_fused_kernel(const OneShotParam
   if (threadIdx.x < p.tp) p.flags[p.my_rank][threadIdx.x * kArBlocks + blockIdx.x] = 0;  // consumed: re-arm
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// All-reduce + residual add + RMSNorm in one kernel through the switch (NVLS), for steps of a few hundred rows.
+//
+// Every rank's partial result x[M][H] lies in its own copy of a symmetric buffer.  Rows are dealt out evenly: rank r
+// finalises rows [r * rpr, (r + 1) * rpr).  For each of its rows a block
+//   1. pulls the sum over all ranks with multimem.ld_reduce (the switch adds the tp copies, fp32 accumulation),
+//   2. adds its own copy of the residual row, computes the row's RMS statistic,
+//   3. writes the new residual row and the normalised row into EVERY rank's copies with multimem.st.
+// Per GPU that is one partial out and two rows in per element, whatever tp is (a push-to-everyone all-reduce moves
+// tp - 1 copies), and the add + norm launches disappear.  Rendezvous: a "partial is ready" counter per (rank,
+// source) before step 1 and an "I have written my rows" counter per (rank, source) after step 3, which the last
+// block of the kernel waits for, so that whatever runs next in the stream sees all rows; the waits are bounded.
+// Calls alternate between two counter sets (parity): a rank cannot run two calls ahead of a peer because every
+// call ends with the all-ranks wait, so a counter is always consumed and re-armed before its next use.
+// This is the AllReduce of src/layer/attn.h:217-233 / src/layer/glu.h:138-154 fused with src/kernel/add.cu and
+// src/kernel/norm.cu:24-39.
+struct ArNormParams {
+  const void* x_mc;        // multicast address of the partial-result buffer (all ranks' copies)
+  const void* res_local;   // this rank's copy of the residual stream [M][H] (null: no residual, e.g. after the embedding)
+  void* res_mc;            // multicast address of the residual stream (written)
+  void* xn_mc;             // multicast address of the normalised activations (written)
+  const void* norm_w;      // [H]
+  uint32_t* flags[kMaxTp]; // flags[d]: rank d's counters of this parity: ready[kMaxTp] | done[kMaxTp] | ticket
+  int tp, my_rank, rows, rows_per_rank, hidden;
+  float eps;
+  uint64_t budget_ns;
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ uint4 mm_ld_reduce8(const void* p);
+template <>
+__device__ __forceinline__ uint4 mm_ld_reduce8<__nv_bfloat16>(const void* p) { return ptx::multimem_ld_reduce_bf16x8(p); }
+template <>
+__device__ __forceinline__ uint4 mm_ld_reduce8<__half>(const void* p) { return ptx::multimem_ld_reduce_f16x8(p); }
+
+constexpr int kArNormVecs = 4;  // 16-byte vectors per thread: hidden <= 256 threads x 4 x 8 = 8192
+
+template <typename T>
+__global__ void __launch_bounds__(256) ar_add_norm_mm_kernel(const ArNormParams p) {
+  __shared__ float red[33];
+  __shared__ int s_ok;
+  uint32_t* mine = p.flags[p.my_rank];
+  // tell every rank that this rank's partial is complete (it was written by earlier kernels of this stream)
+  if (blockIdx.x == 0 && threadIdx.x < p.tp) {
+    ptx::fence_acq_rel_sys();
+    ptx::red_add_release_sys(p.flags[threadIdx.x] + p.my_rank, 1u);
+  }
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int s = 0; s < p.tp; ++s)
+      if (!ptx::bounded_flag_wait_ge(mine + s, 1u, p.budget_ns)) ok = 0;
+    if (!ok && p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
+    s_ok = ok;
+  }
+  __syncthreads();
+  const int row = p.my_rank * p.rows_per_rank + blockIdx.x;
+  if (s_ok && blockIdx.x < p.rows_per_rank && row < p.rows) {
+    const int H = p.hidden, nvec = H >> 3;
+    const int64_t roff = static_cast<int64_t>(row) * H;
+    const T* xm = reinterpret_cast<const T*>(p.x_mc) + roff;
+    const T* rl = p.res_local ? reinterpret_cast<const T*>(p.res_local) + roff : nullptr;
+    float v[kArNormVecs][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kArNormVecs; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < nvec) {
+        unpack8<T>(mm_ld_reduce8<T>(xm + i * 8), v[k]);
+        if (rl) {
+          float f[8];
+          unpack8<T>(*reinterpret_cast<const uint4*>(rl + i * 8), f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[k][j] += f[j];
+        }
+        // the residual stream is kept in 16 bits: normalise what is stored
+        const uint4 packed = pack8<T>(v[k]);
+        ptx::multimem_st_v4(reinterpret_cast<T*>(p.res_mc) + roff + i * 8, packed);
+        unpack8<T>(packed, v[k]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float scale = rsqrtf(ss / static_cast<float>(H) + p.eps);
+    const T* w = reinterpret_cast<const T*>(p.norm_w);
+#pragma unroll
+    for (int k = 0; k < kArNormVecs; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < nvec) {
+        float g[8];
+        unpack8<T>(__ldg(reinterpret_cast<const uint4*>(w) + i), g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[k][j] = v[k][j] * scale * g[j];
+        ptx::multimem_st_v4(reinterpret_cast<T*>(p.xn_mc) + roff + i * 8, pack8<T>(v[k]));
+      }
+    }
+  }
+  // the last block of this rank: tell every rank that this rank's rows are written, wait for everybody's, re-arm
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t t = ptx::atom_add_acq_rel_gpu(mine + 2 * kMaxTp, 1u);
+    s_ok = (t == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    if (threadIdx.x < p.tp) {
+      ptx::fence_acq_rel_sys();
+      ptx::red_add_release_sys(p.flags[threadIdx.x] + kMaxTp + p.my_rank, 1u);
+      if (!ptx::bounded_flag_wait_ge(mine + kMaxTp + threadIdx.x, 1u, p.budget_ns)) {
+        if (p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < p.tp) {
+      mine[threadIdx.x] = 0;
+      mine[kMaxTp + threadIdx.x] = 0;
+    }
+    if (threadIdx.x == 0) mine[2 * kMaxTp] = 0;
+    __threadfence_system();
+  }
+}
+
+// Small all-gather over peer memory: every rank stores its n bytes into slot [my_rank] of every rank's receive
+// area and bumps a counter there; after the (bounded) wait for all tp counters the area holds everybody's piece.
+// One block; for (value, index) pairs of a sharded arg-max and the logit rows of sampled requests.
+struct PeerGatherParams {
+  const void* x;
+  void* slots[kMaxTp];      // slots[d]: rank d's receive area [tp][n bytes]
+  uint32_t* flags[kMaxTp];  // flags[d] + src, zero between calls of one parity
+  int tp, my_rank;
+  int64_t nbytes;           // multiple of 16
+  uint64_t budget_ns;
+  int* status;
+};
+__global__ void __launch_bounds__(256) peer_allgather_kernel(const PeerGatherParams p) {
+  const int64_t nvec = p.nbytes >> 4;
+  const uint4* x = reinterpret_cast<const uint4*>(p.x);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 v = x[i];
+    for (int d = 0; d < p.tp; ++d)
+      ptx::st_na_v4(reinterpret_cast<uint8_t*>(p.slots[d]) + static_cast<int64_t>(p.my_rank) * p.nbytes + (i << 4), v);
+  }
+  __threadfence_system();
+  __syncthreads();
+  uint32_t* mine = p.flags[p.my_rank];
+  if (threadIdx.x < p.tp) {
+    ptx::fence_acq_rel_sys();
+    ptx::red_add_release_sys(p.flags[threadIdx.x] + p.my_rank, 1u);
+  }
+  // the last block waits for every source's blocks and re-arms the counters
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    const uint32_t t = ptx::atom_add_acq_rel_gpu(mine + kMaxTp, 1u);
+    s_last = (t == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < p.tp) {
+      if (!ptx::bounded_flag_wait_ge(mine + threadIdx.x, gridDim.x, p.budget_ns)) {
+        if (p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < p.tp) mine[threadIdx.x] = 0;
+    if (threadIdx.x == 0) mine[kMaxTp] = 0;
+    __threadfence_system();
+  }
+}
+
 }  // namespace blitz
 
 extern "C" {
@@ -270,6 +443,46 @@ int blitz_allreduce_fused(const void* x, void* const* slots, uint32_t* const* fl
   if (blocks > kArBlocks) blocks = kArBlocks;
   if (dtype == 1) allreduce_fused_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(p);
   else allreduce_fused_kernel<__half><<<blocks, 256, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+
+// All-reduce + residual add + RMSNorm through the switch (see ar_add_norm_mm_kernel).  x_mc / res_mc / xn_mc:
+// multicast addresses of the symmetric buffers; res_local: this rank's residual copy or null; flags[d]: rank d's
+// counter block of this call's parity (2 * kMaxTp + 1 words, zero at start).  rows_per_rank = ceil(rows / tp).
+int blitz_ar_add_norm_mm(const void* x_mc, const void* res_local, void* res_mc, void* xn_mc, const void* norm_w,
+                         uint32_t* const* flags, int tp, int my_rank, int rows, int hidden, float eps,
+                         uint64_t budget_ns, int* status, int dtype, cudaStream_t stream) {
+  using namespace blitz;
+  if (rows <= 0) return 0;
+  if (tp < 1 || tp > kMaxTp || (hidden & 7) || hidden > 256 * kArNormVecs * 8 || !x_mc || !res_mc || !xn_mc) return -1;
+  ArNormParams p;
+  p.x_mc = x_mc; p.res_local = res_local; p.res_mc = res_mc; p.xn_mc = xn_mc; p.norm_w = norm_w;
+  for (int d = 0; d < kMaxTp; ++d) p.flags[d] = d < tp ? flags[d] : nullptr;
+  p.tp = tp; p.my_rank = my_rank; p.rows = rows; p.rows_per_rank = (rows + tp - 1) / tp; p.hidden = hidden;
+  p.eps = eps; p.budget_ns = budget_ns; p.status = status;
+  // every rank launches the same grid (the counters count ranks, not blocks), even where its last rows are padding
+  if (dtype == 1) ar_add_norm_mm_kernel<__nv_bfloat16><<<p.rows_per_rank, 256, 0, stream>>>(p);
+  else ar_add_norm_mm_kernel<__half><<<p.rows_per_rank, 256, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// All-gather of nbytes (multiple of 16) per rank into every rank's receive area (see peer_allgather_kernel).
+// flags[d]: rank d's kMaxTp + 1 counters of this call's parity, zero at start.
+int blitz_peer_allgather(const void* x, void* const* slots, uint32_t* const* flags, int tp, int my_rank, int64_t nbytes,
+                         uint64_t budget_ns, int* status, cudaStream_t stream) {
+  using namespace blitz;
+  if (nbytes <= 0) return 0;
+  if (tp < 1 || tp > kMaxTp || (nbytes & 15)) return -1;
+  PeerGatherParams p;
+  p.x = x; p.tp = tp; p.my_rank = my_rank; p.nbytes = nbytes; p.budget_ns = budget_ns; p.status = status;
+  for (int d = 0; d < kMaxTp; ++d) {
+    p.slots[d] = d < tp ? slots[d] : nullptr;
+    p.flags[d] = d < tp ? flags[d] : nullptr;
+  }
+  int blocks = (int)(((nbytes >> 4) + 255) / 256);
+  if (blocks > 32) blocks = 32;
+  peer_allgather_kernel<<<blocks, 256, 0, stream>>>(p);
   return (int)cudaGetLastError();
 }
 

@@ -433,6 +433,15 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_ptr) {
   return v;
 }
 
+__device__ __forceinline__ uint4 multimem_ld_reduce_f16x8(const void* mc_ptr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_ptr)
+               : "memory");
+  return v;
+}
+
 }  // namespace ptx
 
 }  // namespace blitz

@@ -73,6 +73,8 @@ def _declare(L: ctypes.CDLL) -> None:
     sig("blitz_flags_zero", [c_p, c_i, c_p])
     sig("blitz_allreduce_oneshot", [c_p, pp_, pp_, c_p, c_i, c_i, c_i64, c_u64, c_p, c_i, c_p])
     sig("blitz_allreduce_fused", [c_p, pp_, pp_, c_p, c_i, c_i, c_i64, c_u64, c_p, c_i, c_p])
+    sig("blitz_ar_add_norm_mm", [c_p, c_p, c_p, c_p, c_p, pp_, c_i, c_i, c_i, c_i, c_f, c_u64, c_p, c_i, c_p])
+    sig("blitz_peer_allgather", [c_p, pp_, pp_, c_i, c_i, c_i64, c_u64, c_p, c_p])
     sig("blitz_embedding", [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_i, c_p])
     sig("blitz_rms_norm", [c_p, c_p, c_p, c_i, c_i, c_f, c_i, c_p])
     sig("blitz_add_rms_norm", [c_p, c_p, c_p, c_p, c_i, c_i, c_f, c_i, c_p])

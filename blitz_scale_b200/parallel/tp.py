@@ -41,7 +41,8 @@ _EPI = {"store": 0, "add": 1, "silu_mul": 2, "push": 3}
 class FusedTP:
     FLAG_WORDS = 128  # rs0: 0..15, rs1: 16..31, ag0: 32..39, ag1: 40..47, one-shot all-reduce: 48..56 and 64..72
 
-    def __init__(self, group, hidden: int, max_rows: int, dtype=torch.bfloat16, device=None):
+    def __init__(self, group, hidden: int, max_rows: int, dtype=torch.bfloat16, device=None, contexts: int = 1,
+                 gather_bytes: int = 1 << 20):
         import torch.distributed as dist
         self.group = group
         self.tp = dist.get_world_size(group)
@@ -58,7 +59,21 @@ class FusedTP:
         self._ar_parity = 0
         self.fused_allreduce = True                           # one-kernel all-reduce (per-block rendezvous)
         self.o_cflags = self.o_flags + self.FLAG_WORDS * 4    # per-block counters of it: [parity 2][tp 8][64 blocks]
-        total = self.o_cflags + 2 * 8 * 64 * 4
+        # switch-reduced path (all-reduce + add + RMSNorm in one kernel): partial results [parity 2], and `contexts`
+        # copies of the replicated residual stream and of the normalised activations (one per interleaved task)
+        self.contexts = contexts
+        self.o_in = [self.o_cflags + 2 * 8 * 64 * 4, 0]
+        self.o_in[1] = self.o_in[0] + self.buf_bytes
+        self.o_res = self.o_in[1] + self.buf_bytes
+        self.o_xn = self.o_res + contexts * self.buf_bytes
+        self.o_nflags = self.o_xn + contexts * self.buf_bytes  # [parity 2][32 words]: ready[8] | done[8] | ticket
+        self.gather_bytes = gather_bytes                       # per rank and call of the small all-gather
+        self.o_gather = self.o_nflags + 2 * 32 * 4             # [parity 2][tp][gather_bytes]
+        self.o_gflags = self.o_gather + 2 * self.tp * gather_bytes  # [parity 2][16 words]
+        total = self.o_gflags + 2 * 16 * 4
+        self._in_parity = 0
+        self._g_parity = 0
+        self.ctx = 0
         self.region = SymmRegion(total, group, device)
         self.region.local[self.o_flags:].zero_()
         torch.cuda.synchronize()
@@ -66,6 +81,8 @@ class FusedTP:
         self.ptrs = self.region.ptrs
         self.device = self.region.local.device
         self.budget_ns = int(2e9)
+        # the switch-reduced kernels need the region's multicast address (NVLS); without it the push kernels serve
+        self.has_mc = bool(self.region.mc_ptr) and hidden <= 8192
 
     def close_regions(self) -> None:
         self.region.close_regions()
@@ -152,6 +169,70 @@ class FusedTP:
     def reset_allreduce_parity(self) -> None:
         """Call at the same point of the program on every rank (the runner does it at the start of a forward)."""
         self._ar_parity = 0
+        self._in_parity = 0
+        self._g_parity = 0
+
+    # ------------------------------------------------------------------ switch-reduced path
+    def use_context(self, i: int) -> None:
+        """Select which copy of (residual stream, normalised activations) the next calls work on; interleaved
+        live-execution tasks each keep their own.  Every rank of the group must select the same one."""
+        assert 0 <= i < self.contexts
+        self.ctx = i
+
+    def next_partial(self, rows: int) -> torch.Tensor:
+        """Buffer for the next row-parallel GEMM's partial result (alternates between two, like the counters)."""
+        off = self.o_in[self._in_parity]
+        return self.region.local[off:off + rows * self.hidden * self.elem].view(self.dtype).view(rows, self.hidden)
+
+    def res(self, rows: int) -> torch.Tensor:
+        off = self.o_res + self.ctx * self.buf_bytes
+        return self.region.local[off:off + rows * self.hidden * self.elem].view(self.dtype).view(rows, self.hidden)
+
+    def xn(self, rows: int) -> torch.Tensor:
+        off = self.o_xn + self.ctx * self.buf_bytes
+        return self.region.local[off:off + rows * self.hidden * self.elem].view(self.dtype).view(rows, self.hidden)
+
+    def ar_add_norm(self, rows: int, norm_w: torch.Tensor, eps: float, add_residual: bool = True) -> None:
+        """residual (+)= sum over ranks of the partial written to `next_partial`; normalised rows = RMSNorm(residual) * w.
+        One kernel: the switch sums the partials (multimem.ld_reduce), every rank finalises its share of the rows and
+        writes them into every rank's copies (multimem.st).  Both results are valid on every rank afterwards."""
+        assert self.has_mc and rows <= self.max_rows
+        par = self._in_parity
+        self._in_parity ^= 1
+        mc = self.region.mc_ptr
+        fl = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + self.o_nflags + par * 32 * 4 for r in range(self.tp)])
+        res_off = self.o_res + self.ctx * self.buf_bytes
+        rc = _L.lib().blitz_ar_add_norm_mm(
+            ctypes.c_void_p(mc + self.o_in[par]),
+            ctypes.c_void_p(self.ptrs[self.rank] + res_off if add_residual else 0),
+            ctypes.c_void_p(mc + res_off), ctypes.c_void_p(mc + self.o_xn + self.ctx * self.buf_bytes), _p(norm_w), fl,
+            self.tp, self.rank, rows, self.hidden, eps, self.budget_ns, _p(status_word(self.device)),
+            1 if self.dtype == torch.bfloat16 else 0, _stream())
+        _check(rc, "blitz_ar_add_norm_mm")
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        """[tp, *t.shape] with every rank's `t`, exchanged by peer stores (no collective library): for the (value,
+        index) pairs of the sharded arg-max and the logit rows of sampled requests."""
+        t = t.contiguous()
+        nbytes = (t.numel() * t.element_size() + 15) // 16 * 16
+        assert nbytes <= self.gather_bytes, "piece too large for the small all-gather"
+        par = self._g_parity
+        self._g_parity ^= 1
+        base = self.o_gather + par * self.tp * self.gather_bytes
+        src = t
+        if t.numel() * t.element_size() != nbytes:          # pad to whole 16-byte vectors
+            src = torch.zeros(nbytes, dtype=torch.uint8, device=t.device)
+            src[:t.numel() * t.element_size()].copy_(t.view(torch.uint8).view(-1))
+        slots = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + base for r in range(self.tp)])
+        fl = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + self.o_gflags + par * 16 * 4 for r in range(self.tp)])
+        rc = _L.lib().blitz_peer_allgather(_p(src), slots, fl, self.tp, self.rank, nbytes, self.budget_ns,
+                                           _p(status_word(self.device)), _stream())
+        _check(rc, "blitz_peer_allgather")
+        # the slots of this parity are rewritten two calls later: hand out a copy
+        out = torch.empty((self.tp,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        raw = self.region.local[base:base + self.tp * nbytes].view(self.tp, nbytes)      # the kernel packs slots by nbytes
+        out.view(self.tp, -1).view(torch.uint8).copy_(raw[:, :t.numel() * t.element_size()])
+        return out
 
     def allreduce_oneshot(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out = sum over ranks of x (out may be x).  Every rank stores its contribution into every rank's slot and
@@ -178,8 +259,7 @@ class FusedTP:
 
 
 class _PeerAllReduce:
-    """The collective interface of `TPComm` with the sum done by the one-shot peer-memory kernels; the tiny
-    (value, index) all-gather of the sharded argmax stays on the library."""
+    """The collective interface of `TPComm` on the peer-memory kernels: one-shot all-reduce and small all-gather."""
 
     def __init__(self, comm: TPComm, fused: FusedTP):
         self.comm, self.fused = comm, fused
@@ -189,7 +269,7 @@ class _PeerAllReduce:
         return self.fused.allreduce_oneshot(t, t)
 
     def all_gather(self, t: torch.Tensor) -> torch.Tensor:
-        return self.comm.all_gather(t)
+        return self.fused.all_gather(t)
 
 
 class LlamaRunnerTP(LlamaRunner):
@@ -204,6 +284,7 @@ class LlamaRunnerTP(LlamaRunner):
         self.oneshot_max_rows = oneshot_max_rows
         self._nccl_comm = comm
         self._peer_comm = _PeerAllReduce(comm, fused)
+        self.use_switch = True
         self.res_shard = torch.empty(fused.max_rows // fused.tp, self.cfg.hidden, dtype=seg.dtype, device=self.res.device)
         self._pad_ids = torch.zeros(fused.max_rows, dtype=torch.int32, device=self.res.device)
 
@@ -215,10 +296,22 @@ class LlamaRunnerTP(LlamaRunner):
     def _small(self, m: StepMeta) -> bool:
         return m.num_tokens <= self.oneshot_max_rows
 
+    def _switch(self, m: StepMeta) -> bool:
+        """Steps of a few hundred rows on a fabric with in-switch reduction: all-reduce, residual add and RMSNorm are
+        one kernel (`FusedTP.ar_add_norm`), the residual stream and the normalised rows live in symmetric memory."""
+        return self._small(m) and self.fused.has_mc and self.use_switch
+
     def embed(self, m: StepMeta) -> None:
         self.fused.reset_allreduce_parity()
+        self.comm = self._peer_comm
+        if self._switch(m):
+            T, f = m.num_tokens, self.fused
+            vs = self.cfg.vocab // self.tp
+            ops.embedding(m.ids[:T], self.seg["embed"], f.next_partial(T), vocab_start=self.seg.tp_rank * vs,
+                          zero_missing=True)
+            f.ar_add_norm(T, self._w(0, "input_ln"), self.cfg.rms_eps, add_residual=False)
+            return
         if self._small(m):
-            self.comm = self._peer_comm
             return LlamaRunner.embed(self, m)
         self.comm = self._nccl_comm
         T = m.num_tokens
@@ -236,6 +329,22 @@ class LlamaRunnerTP(LlamaRunner):
         self._first = True
 
     def attention_block(self, l: int, m: StepMeta) -> None:
+        if self._switch(m):
+            T, c, f = m.num_tokens, self.cfg, self.fused
+            ops.gemm(f.xn(T), self._w(l, "qkv"), static_b=True, out=self.qkv[:T])
+            ops.rope_kv_store(self.qkv[:T], m.pos[:T], m.slot[:T], self.kv[l], q_heads=self.qh, kv_heads=self.kvh,
+                              head_dim=self.hd, page_size=self.page_size, rope_theta=c.rope_theta)
+            if m.is_prefill:
+                ops.attn_prefill(self.qkv[:T], m.tok_indptr, m.seq_lens_host, q_heads=self.qh, kv_heads=self.kvh,
+                                 head_dim=self.hd, out=self.attn[:T])
+            else:
+                ops.attn_decode(self.qkv[:T], self.kv[l], m.page_indices, m.page_indptr, m.last_page_len,
+                                q_heads=self.qh, kv_heads=self.kvh, head_dim=self.hd, page_size=self.page_size,
+                                num_splits=m.num_splits, workspace=self._workspace(m.batch, m.num_splits),
+                                out=self.attn[:T])
+            ops.gemm(self.attn[:T], self._w(l, "o"), static_b=True, out=f.next_partial(T))
+            f.ar_add_norm(T, self._w(l, "post_ln"), c.rms_eps)
+            return
         if self._small(m):
             return LlamaRunner.attention_block(self, l, m)
         T, c, f = m.num_tokens, self.cfg, self.fused
@@ -257,6 +366,13 @@ class LlamaRunnerTP(LlamaRunner):
         f.reduce_norm(0, exp, rpr, self.res_shard, self._w(l, "post_ln"), 1, c.rms_eps)
 
     def ffn_block(self, l: int, m: StepMeta) -> None:
+        if self._switch(m):
+            T, c, f = m.num_tokens, self.cfg, self.fused
+            ops.gemm(f.xn(T), self._w(l, "gate_up"), static_b=True, out=self.act[:T], epilogue="silu_mul")
+            ops.gemm(self.act[:T], self._w(l, "down"), static_b=True, out=f.next_partial(T))
+            nw = self._w(l + 1, "input_ln") if l + 1 < c.layers else self.seg["final_norm"]
+            f.ar_add_norm(T, nw, c.rms_eps)       # the normalised rows are the next layer's (or the head's) input
+            return
         if self._small(m):
             return LlamaRunner.ffn_block(self, l, m)
         c, f = self.cfg, self.fused
@@ -267,6 +383,16 @@ class LlamaRunnerTP(LlamaRunner):
         f.reduce_norm(1, exp, rpr, self.res_shard, nw, 0, c.rms_eps)
 
     def head(self, m: StepMeta) -> torch.Tensor:
+        if self._switch(m):
+            B, T, c, f = m.batch, m.num_tokens, self.cfg, self.fused
+            xn = f.xn(T)                           # already normalised with the final norm's weight
+            if m.is_prefill:
+                ops.gather_last(xn, m.tok_indptr, out=self.last[:B])
+                src = self.last[:B]
+            else:
+                src = xn[:B]
+            ops.gemm(src, self.seg["lm_head"], static_b=True, out=self.logits[:B])
+            return self._pick_tokens(B)
         if self._small(m):
             return LlamaRunner.head(self, m)
         B, T, c, f = m.batch, m.num_tokens, self.cfg, self.fused
@@ -279,10 +405,14 @@ class LlamaRunnerTP(LlamaRunner):
         else:
             src = xn[:B]
         ops.gemm(src, self.seg["lm_head"], static_b=True, out=self.logits[:B])
-        vs = c.vocab // self.tp
+        return self._pick_tokens(B)
+
+    def _pick_tokens(self, B: int) -> torch.Tensor:
+        """Arg-max over the vocabulary shards: every rank's (value, index) candidates travel by peer stores."""
+        vs = self.cfg.vocab // self.tp
         ops.argmax(self.logits[:B], out=self.tokens[:B], out_val=self.maxval[:B], idx_offset=self.seg.tp_rank * vs)
-        vals = self.comm.all_gather(self.maxval[:B])
-        idxs = self.comm.all_gather(self.tokens[:B])
-        best = vals.argmax(0, keepdim=True)
-        self.tokens[:B].copy_(idxs.gather(0, best)[0])
+        pair = torch.stack([self.maxval[:B], self.tokens[:B].view(torch.float32)], dim=1)      # [B, 2] x 4 bytes
+        both = self.fused.all_gather(pair)                                                     # [tp, B, 2]
+        best = both[:, :, 0].argmax(0, keepdim=True)
+        self.tokens[:B].copy_(both[:, :, 1].view(torch.int32).gather(0, best)[0])
         return self.tokens[:B]

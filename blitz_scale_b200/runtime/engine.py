@@ -38,7 +38,8 @@ class Engine:
                  max_batch_tokens: int = 8192, tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16,
                  device: Optional[torch.device] = None, comm: Optional[TPComm] = None, use_graphs: bool = True,
                  seg_buffer: Optional[torch.Tensor] = None, kv_buffer: Optional[torch.Tensor] = None,
-                 ready: bool = True, seed: int = 0, fused_tp: bool = True, oneshot_max_rows: int = 1024):
+                 ready: bool = True, seed: int = 0, fused_tp: bool = True, oneshot_max_rows: int = 1024,
+                 tp_contexts: int = 1, use_switch: bool = True):
         self.cfg = get_config(model) if isinstance(model, str) else model
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.dtype, self.tp, self.tp_rank = dtype, tp, tp_rank
@@ -58,9 +59,11 @@ class Engine:
             # tensor-parallel layers through the fused peer-memory kernels (GEMM -> reduce-scatter push, reduce + norm +
             # all-gather push, flag-gated GEMM); the NCCL all-reduce runner is the baseline (`fused_tp=False`)
             from ..parallel.tp import FusedTP, LlamaRunnerTP
-            self.fused = FusedTP(comm.group, c.hidden, max(max_batch_tokens, max_batch), dtype=dtype)
+            self.fused = FusedTP(comm.group, c.hidden, max(max_batch_tokens, max_batch), dtype=dtype,
+                                 contexts=tp_contexts)
             self.runner = LlamaRunnerTP(self.seg, self.kv, max(max_batch_tokens, max_batch), max_batch, comm, self.fused,
                                         oneshot_max_rows=oneshot_max_rows)
+            self.runner.use_switch = use_switch
         else:
             self.runner = LlamaRunner(self.seg, self.kv, max_tokens=max(max_batch_tokens, max_batch), max_batch=max_batch,
                                       comm=comm)
@@ -176,19 +179,17 @@ class Engine:
         """Rows whose request asked for sampling (`do_sample` with temperature / top-k / top-p / seed) draw their token
         from this step's logits with the sampling kernel; all other rows keep the arg-max.  One extra small launch,
         outside the CUDA graph, and only when such a row exists.  With tp > 1 every rank holds a vocabulary shard of
-        the logits, and sampling over shards is not built: those requests are served greedily."""
+        the logits; the shards of the sampled rows are gathered first (the reference serves greedily only)."""
         rows, temp, top_k, top_p, seeds = batch.sampling_rows()
         if not rows:
-            return toks
-        if self.tp > 1:
-            if not getattr(self, "_warned_tp_sampling", False):
-                self._warned_tp_sampling = True
-                import logging
-                logging.getLogger("blitz.engine").warning("sampling parameters are ignored with tp > 1 (greedy decoding)")
             return toks
         dev = self.device
         idx = torch.tensor(rows, dtype=torch.long, device=dev)
         logits = self.runner.logits[:B].index_select(0, idx)
+        if self.tp > 1:
+            # every rank holds a vocabulary shard of the rows: gather the shards of the (few) sampled rows, so that
+            # every rank draws from the same full distribution with the same seed and gets the same token
+            logits = self._gather_vocab_shards(logits)
         drawn = ops.sample(logits, torch.tensor(temp, dtype=torch.float32, device=dev),
                            torch.tensor(top_k, dtype=torch.int32, device=dev),
                            torch.tensor(top_p, dtype=torch.float32, device=dev),
@@ -196,6 +197,20 @@ class Engine:
         toks = toks[:B].clone()
         toks[idx] = drawn.to(toks.dtype)
         return toks
+
+    def _gather_vocab_shards(self, shard_rows: torch.Tensor) -> torch.Tensor:
+        """[n, vocab / tp] on every rank -> [n, vocab] on every rank, through the peer-memory all-gather of the fused
+        runner (a few rows per call, bounded by its slot size) or the collective library of the comparison runner."""
+        n, vs = shard_rows.shape
+        if self.fused is None:
+            full = self.runner.comm.all_gather(shard_rows)                       # [tp, n, vs]
+            return full.permute(1, 0, 2).reshape(n, self.tp * vs).contiguous()
+        per_call = max(1, self.fused.gather_bytes // (vs * shard_rows.element_size()))
+        parts = []
+        for r0 in range(0, n, per_call):
+            g = self.fused.all_gather(shard_rows[r0:r0 + per_call])             # [tp, k, vs]
+            parts.append(g.permute(1, 0, 2).reshape(g.shape[1], self.tp * vs))
+        return torch.cat(parts, 0).contiguous()
 
     def _capture(self, Bp: int, splits: int) -> torch.cuda.CUDAGraph:
         m = self._views(Bp, Bp, self.num_pages, False, splits=splits)

@@ -206,35 +206,49 @@ def main():
         from blitz_scale_b200.runtime.engine import Engine
         comm = TPComm(dist.group.WORLD)
         outs, logits = [], []
-        # the row-sharded fused pipeline, the one-shot peer-memory all-reduce mode, and the NCCL runner (reference)
-        for fused_tp, oneshot in ((True, 0), (True, 1024), (False, 0)):
+        # the row-sharded fused pipeline, the switch-reduced one-kernel mode (where the fabric has NVLS), the one-shot
+        # peer-memory all-reduce mode, and the NCCL runner (reference, last)
+        sampled = []
+        for fused_tp, oneshot, switch in ((True, 0, False), (True, 1024, True), (True, 1024, False), (False, 0, False)):
             eng = Engine("tiny_gpu", num_pages=64, page_size=16, max_batch=8, max_batch_tokens=1024, tp=world, tp_rank=rank,
-                         comm=comm, seed=4, fused_tp=fused_tp, oneshot_max_rows=oneshot)   # 0: always the row-sharded pipeline
+                         comm=comm, seed=4, fused_tp=fused_tp, oneshot_max_rows=oneshot, use_switch=switch)
             assert (eng.fused is not None) == fused_tp
             owners.append(eng)
             g = torch.Generator().manual_seed(9)
             specs = [core.SeqSpec(i, torch.randint(0, 4096, (n,), generator=g).tolist(), 8) for i, n in enumerate((33, 7, 120))]
             b = eng.new_batch(1, specs)
             seqs = [[t] for t in eng.prefill(b)]
-            parts = comm.all_gather(eng.runner.logits[:3].contiguous())
-            logits.append(torch.cat([parts[i] for i in range(world)], dim=1).float())
-            for _ in range(6):
-                for s_, t in zip(seqs, eng.decode(b)):
-                    s_.append(t)
-            torch.cuda.synchronize()
-            ops.check_status()
+            logits.append(eng.runner.logits[:3].float().clone())
+            for _ in range(5):
+                for sq, t in zip(seqs, eng.decode(b)):
+                    sq.append(t)
             outs.append(seqs)
-            b.clear()
+            # sampling over vocabulary shards: the same seeds give the same tokens on every rank
+            sp = []
+            for i, n in enumerate((20, 9)):
+                q = core.SeqSpec(100 + i, torch.randint(0, 4096, (n,), generator=g).tolist(), 4)
+                q.do_sample, q.temperature, q.top_k, q.top_p, q.seed = True, 0.8, 50, 0.95, 1234 + i
+                sp.append(q)
+            b2 = eng.new_batch(2, sp)
+            drawn = [eng.prefill(b2)] + [eng.decode(b2) for _ in range(3)]
+            sampled.append(drawn)
+            ops.check_status()
         # same function, different rounding (bf16 partials summed in fp32 vs a bf16 all-reduce): the prefill logits
         # agree closely, and where the first tokens differ the two candidates are a near-tie
-        for k in (0, 1):
-            err = float((logits[k] - logits[2]).norm() / logits[2].norm())
+        ref_i = len(logits) - 1
+        for k in range(ref_i):
+            err = float((logits[k] - logits[ref_i]).norm() / logits[ref_i].norm())
             assert err < 3e-2, (k, err)
             for bi in range(3):
-                t0, t1 = outs[k][bi][0], outs[2][bi][0]
+                t0, t1 = outs[k][bi][0], outs[ref_i][bi][0]
                 if t0 != t1:
-                    r = logits[2][bi]
+                    r = logits[ref_i][bi]
                     assert float(r.max() - r[t0]) < 0.05 * float(r.abs().max()), (k, bi, t0, t1)
+        # every rank drew the same sampled tokens, in every mode
+        st = torch.tensor(sampled, device="cuda")
+        sref = st.clone()
+        dist.broadcast(sref, 0)
+        assert torch.equal(st, sref) and int(st.min()) >= 0 and int(st.max()) < 4096
         # every rank sampled the same tokens
         t = torch.tensor(outs[0], device="cuda")
         ref = t.clone()
