@@ -58,6 +58,14 @@ def main():
     ap.add_argument("--horizon-ms", type=float, default=100.0, help="autoscale: queue the planner tolerates, as time")
     ap.add_argument("--decode-steps", type=int, default=1, help="decode steps per DecodeV2 call")
     ap.add_argument("--max-incoming-migrations", type=int, default=1, help="KV migrations in flight per decode replica")
+    ap.add_argument("--scale-down-ms", type=float, default=0.0,
+                    help="autoscale: how long demand must stay below capacity before a replica is released (0 = the default)")
+    ap.add_argument("--max-decode", type=int, default=1, help="autoscale: decode replicas the planner may use")
+    ap.add_argument("--trace", default="fixed", choices=["fixed", "gamma"],
+                    help="fixed: evenly spaced requests of --prompt-len / --new-tokens; gamma: Gamma inter-arrivals (CV 4) whose "
+                         "rate steps from --base-rate to --burst-rate at --base-s, lognormal prompt lengths (median "
+                         "--prompt-len, at most 4096) and output lengths (median --new-tokens, at most 1024)")
+    ap.add_argument("--trace-sigma", type=float, default=0.8, help="gamma trace: sigma of the two lognormal length laws")
     ap.add_argument("--port", type=int, default=50600)
     ap.add_argument("--json", default="")
     a = ap.parse_args()
@@ -114,6 +122,18 @@ def main():
             traceback.print_exc()
     flag = torch.tensor([1 if result else 0])
     dist.broadcast(flag, 0, group=host_group)
+    logs = [None] * world
+    dist.all_gather_object(logs, backend.transfer_log, group=host_group)
+    if rank == 0 and result:
+        src = [e for l in logs for e in (l or []) if e["role"] == "source"]
+        dst = [e for l in logs for e in (l or []) if e["role"] == "destination"]
+        result["param_transfer"] = {
+            "device_ms_max_over_sources": round(max((e["device_ms"] for e in src), default=0.0), 3),
+            "gbs_into_each_destination": round(sum(e["bytes"] / max(1, len(e["dests"])) for e in src) / 1e9 /
+                                               max(1e-9, max((e["device_ms"] for e in src), default=0.0) * 1e-3), 1) if src else 0.0,
+            "sources": sorted({e["rank"] for e in src}), "destinations": sorted({e["rank"] for e in dst}),
+            "destination_host_ms": {str(e["rank"]): round(e["host_ms"], 2) for e in dst},
+            "timing": "CUDA events around the copy kernels on every source GPU (first store to last flag), max over sources"}
     holder["loop"].call_soon_threadsafe(holder["stop"].set)
     th.join(10)
     backend.close()
@@ -139,15 +159,35 @@ def run_router(a, world, states, cfg_model, backend):
     if getattr(a, "autoscale", False):
         feats = feats.replace(",manually_scale", "")
         extra = dict(tokens_prefilled_per_sec=max(1, int(a.prefill_rate * a.horizon_ms * 1e-3)),
-                     tokens_transferred_per_sec=5000000, max_prefill=world - 1, max_decode=1, min_prefill=1, min_decode=1)
+                     tokens_transferred_per_sec=5000000, max_prefill=world - 1, max_decode=max(1, a.max_decode), min_prefill=1,
+                     min_decode=1)
+        if a.scale_down_ms > 0:
+            # a CV-4 arrival process has long gaps inside a burst: the patience has to cover them, or replicas are
+            # released and reloaded between two clusters of arrivals
+            extra["scale_down_threshold_ms"] = a.scale_down_ms
     cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
                                          max_blocks_per_replica=a.pages - 64, block_size=64, max_prefill_tokens=8192,
                                          model_layers=cfg_model.layers, max_batch_seqs=256, **extra)
     cfg.max_incoming_migrations = max(1, a.max_incoming_migrations)
     g = torch.Generator().manual_seed(5)
-    n_base, n_burst = int(a.base_rate * a.base_s), int(a.burst_rate * a.burst_s)
-    arrivals = [i / a.base_rate for i in range(n_base)] + [a.base_s + i / a.burst_rate for i in range(n_burst)]
-    prompts = [torch.randint(0, cfg_model.vocab, (a.prompt_len,), generator=g).tolist() for _ in arrivals]
+    if a.trace == "gamma":
+        # the bursty synthetic trace of the second benchmark configuration, from the native generator (seeded)
+        from blitz_scale_b200.runtime import core
+        spec = core.TraceSpec()
+        spec.phases = [core.RatePhase(0.0, a.base_rate), core.RatePhase(a.base_s, a.burst_rate)]
+        spec.cv, spec.duration, spec.seed = 4.0, a.base_s + a.burst_s, 0
+        spec.input.kind, spec.input.a, spec.input.b, spec.input.max_len, spec.input.min_len = \
+            core.LengthDist.Kind.LogNormal, float(a.prompt_len), a.trace_sigma, 4096, 8
+        spec.output.kind, spec.output.a, spec.output.b, spec.output.max_len, spec.output.min_len = \
+            core.LengthDist.Kind.LogNormal, float(a.new_tokens), a.trace_sigma, 1024, 2
+        items = core.generate_trace(spec)
+        arrivals = [it.t for it in items]
+        in_lens, out_lens = [int(it.input_len) for it in items], [int(it.output_len) for it in items]
+    else:
+        n_base, n_burst = int(a.base_rate * a.base_s), int(a.burst_rate * a.burst_s)
+        arrivals = [i / a.base_rate for i in range(n_base)] + [a.base_s + i / a.burst_rate for i in range(n_burst)]
+        in_lens, out_lens = [a.prompt_len] * len(arrivals), [a.new_tokens] * len(arrivals)
+    prompts = [torch.randint(0, cfg_model.vocab, (n,), generator=g).tolist() for n in in_lens]
 
     async def go():
         rt = RouterRuntime(cfg, [f"127.0.0.1:{a.port + r}" for r in range(world)], model_layers=cfg_model.layers,
@@ -165,7 +205,7 @@ def run_router(a, world, states, cfg_model, backend):
             await asyncio.sleep(max(0.0, t_arr - (rt.now() - t_start)))
             t0 = rt.now()
             # whole response at once (what POST /generate does): the token times are the router's delivery times
-            lr = rt.submit(prompts[i], a.new_tokens, stream=False)
+            lr = rt.submit(prompts[i], out_lens[i], stream=False)
             if await asyncio.wait_for(lr.done, timeout=300):
                 records.append({"i": i, "ok": False})
                 return
@@ -207,7 +247,9 @@ def run_router(a, world, states, cfg_model, backend):
     first_gap = [r["tbt"][0] for r in burst if r["tbt"]]
     seg_bytes = backend.engine.seg.layout.total_bytes
     out = {"bench": "cluster_scale_out", "model": a.model, "mode": a.mode + ("+autoscale" if getattr(a, "autoscale", False) else ""),
-           "gpus": world, "requests": len(records),
+           "gpus": world, "requests": len(records), "trace": a.trace,
+           "input_len_p50_max": [sorted(in_lens)[len(in_lens) // 2], max(in_lens)],
+           "output_len_p50_max": [sorted(out_lens)[len(out_lens) // 2], max(out_lens)],
            "failed": len(records) - len(ok), "prompt_len": a.prompt_len, "new_tokens": a.new_tokens,
            "base_rate": a.base_rate, "burst_rate": a.burst_rate, "decode_steps_per_call": a.decode_steps,
            "max_incoming_migrations": a.max_incoming_migrations, "precapture": bool(a.precapture),

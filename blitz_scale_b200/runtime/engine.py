@@ -218,7 +218,10 @@ class Engine:
         self.runner.forward(m)
         torch.cuda.current_stream().synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        # thread-local capture: transfer and RPC threads of a worker keep making CUDA calls (small copies, flag reads)
+        # on their own streams while this thread captures; under the default global mode those calls invalidate
+        # the capture ("operation not permitted when stream is capturing")
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             self.runner.forward(m)
         self._graphs[(Bp, splits)] = g
         return g

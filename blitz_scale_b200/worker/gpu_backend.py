@@ -83,6 +83,7 @@ class GpuBackend(Backend):
         # live execution
         L = self.cfg.layers
         self.zag = core.ZigzagScheduler(L, 4)
+        self._zag_layers_seen = 0
         self.zag_tasks: Dict[int, dict] = {}
         self.zag_slots = torch.empty(4, max_batch_tokens, self.cfg.hidden, dtype=dt, device=self.device)
         self.zag_cv = threading.Condition(self.lock)
@@ -103,6 +104,7 @@ class GpuBackend(Backend):
         self.zag_thread = threading.Thread(target=self._zag_loop, daemon=True)
         self.zag_thread.start()
         self.transfer_thread: Optional[threading.Thread] = None
+        self.transfer_log: List[dict] = []     # one entry per parameter transfer this GPU took part in
         torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ helpers
@@ -241,51 +243,66 @@ class GpuBackend(Backend):
     def _zag_loop(self) -> None:
         torch.cuda.set_device(self.device)
         while not self._stop:
-            with self.lock:
-                st = self.engine.status
-                if self.agree is not None and not st.fully_loaded():
-                    self.zag.set_loaded(*self.agree.agreed_state())
+            try:
+                self._zag_turn()
+            except Exception:  # noqa: BLE001  (this thread serves every later live-execution task: it must survive)
+                log.exception("live-execution step failed")
+                with self.lock:
+                    for t in list(self.zag_tasks.values()):
+                        if not t["future"].done():
+                            t["future"].set_exception(RuntimeError("live-execution step failed"))
+                time.sleep(0.01)
+
+    def _zag_turn(self) -> None:
+        with self.lock:
+            st = self.engine.status
+            if self.agree is not None and not st.fully_loaded():
+                loaded = self.agree.agreed_state()
+            else:
+                loaded = (st.embed_ready, st.layers_ready, st.head_ready)
+            if loaded[1] < self._zag_layers_seen:
+                self.zag.reset()        # a replica that was emptied and is being loaded again starts from no layers
+            self.zag.set_loaded(*loaded)
+            self._zag_layers_seen = loaded[1]
+            d = self.zag.next()
+            if d.step in (core.ZagStep.Idle, core.ZagStep.Blocked):
+                # nothing to run: sleep until a task or a parameter unit arrives (both notify the condition); the
+                # short timeout only bounds the wait while layers are still landing
+                self.zag_cv.wait(0.0005 if d.step == core.ZagStep.Blocked else 0.05)
+                return
+            task = self.zag_tasks[d.batch_id]
+            eng, b = self.engine, task["batch"]
+            if task["meta"] is None:
+                T, P = b.fill_prefill(eng.host_np, eng.layout)
+                eng._h2d(eng.layout.page_indices + P)
+                # the staging arrays are shared: keep a private device copy of this task's inputs
+                dev_copy = eng.dev[:eng.layout.page_indices + P].clone()
+                task["meta"] = (T, P, dev_copy)
+            T, P, dev_copy = task["meta"]
+            eng.dev[:dev_copy.numel()].copy_(dev_copy)
+            m = eng._views(T, b.size, P, True, b.prompt_lens())
+            saved = eng.runner.res
+            eng.runner.res = self.zag_slots[task["slot"]]
+            try:
+                if d.step == core.ZagStep.Embed:
+                    log.debug("zag embed batch=%d", d.batch_id)
+                    eng.runner.embed(m)
+                elif d.step == core.ZagStep.Layer:
+                    log.debug("zag layer batch=%d layer=%d", d.batch_id, d.layer)
+                    eng.runner.run_layer(d.layer, m)
                 else:
-                    self.zag.set_loaded(st.embed_ready, st.layers_ready, st.head_ready)
-                d = self.zag.next()
-                if d.step in (core.ZagStep.Idle, core.ZagStep.Blocked):
-                    # nothing to run: sleep until a task or a parameter unit arrives (both notify the condition); the
-                    # short timeout only bounds the wait while layers are still landing
-                    self.zag_cv.wait(0.0005 if d.step == core.ZagStep.Blocked else 0.05)
-                    continue
-                task = self.zag_tasks[d.batch_id]
-                eng, b = self.engine, task["batch"]
-                if task["meta"] is None:
-                    T, P = b.fill_prefill(eng.host_np, eng.layout)
-                    eng._h2d(eng.layout.page_indices + P)
-                    # the staging arrays are shared: keep a private device copy of this task's inputs
-                    dev_copy = eng.dev[:eng.layout.page_indices + P].clone()
-                    task["meta"] = (T, P, dev_copy)
-                T, P, dev_copy = task["meta"]
-                eng.dev[:dev_copy.numel()].copy_(dev_copy)
-                m = eng._views(T, b.size, P, True, b.prompt_lens())
-                saved = eng.runner.res
-                eng.runner.res = self.zag_slots[task["slot"]]
-                try:
-                    if d.step == core.ZagStep.Embed:
-                        log.debug("zag embed batch=%d", d.batch_id)
-                        eng.runner.embed(m)
-                    elif d.step == core.ZagStep.Layer:
-                        log.debug("zag layer batch=%d layer=%d", d.batch_id, d.layer)
-                        eng.runner.run_layer(d.layer, m)
-                    else:
-                        log.debug("zag head batch=%d", d.batch_id)
-                        toks = eng._tokens_to_host(eng.runner.head(m), b.size)
-                    torch.cuda.current_stream().synchronize()
-                finally:
-                    eng.runner.res = saved
-                done = self.zag.complete(d)
-                if done:
-                    b.mark_prefilled()
-                    b.append_tokens(toks, False)
-                    b.decode = True
-                    gens, cb = self._finish_step(b, toks)
-                    self.zag_tasks.pop(d.batch_id)["future"].set_result((gens, cb, None))
+                    log.debug("zag head batch=%d", d.batch_id)
+                    toks = eng._tokens_to_host(eng.runner.head(m), b.size)
+                torch.cuda.current_stream().synchronize()
+            finally:
+                eng.runner.res = saved
+            done = self.zag.complete(d)
+            if done:
+                b.mark_prefilled()
+                b.append_tokens(toks, False)
+                b.decode = True
+                gens, cb = self._finish_step(b, toks)
+                self.zag_tasks.pop(d.batch_id)["future"].set_result((gens, cb, None))
 
     def relay(self, rank, relax_not_head):
         with self.lock:
@@ -467,11 +484,18 @@ class GpuBackend(Backend):
             # same bytes: with tp > 1 the shards differ between ranks and the copy stays on peer stores)
             mm = self.use_multimem and self.tp == 1 and len(dests) >= 2 and bool(self.fabric.weights.mc_ptr)
             with self.xfer_lock:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 with torch.cuda.stream(self.side):
+                    e0.record()
                     self.fabric.copy_units(self.fabric.weights, dests, offs, lens, symm.PARAM_FLAG0,
                                            stripe=sources.index(self.rank), n_stripes=len(sources), use_multimem=mm,
                                            num_ctas=self.copy_ctas)
+                    e1.record()
                 self.side.synchronize()
+                # device time of this source's share (first store to last flag), for reports beside the router's clock
+                self.transfer_log.append({"role": "source", "rank": self.rank, "device_ms": e0.elapsed_time(e1),
+                                          "bytes": sum(lens) // len(sources) * len(dests), "dests": list(dests),
+                                          "sources": list(sources), "multimem": bool(mm)})
         elif self.rank in dests:
             self._receive_params(len(sources))
 
@@ -501,6 +525,8 @@ class GpuBackend(Backend):
                 if time.monotonic() - t0 > timeout_s:
                     raise RuntimeError(f"parameter transfer stalled at unit {nxt}")
                 time.sleep(0.0002)
+        self.transfer_log.append({"role": "destination", "rank": self.rank, "host_ms": (time.monotonic() - t0) * 1e3,
+                                  "units": n_units, "stripes": n_stripes})
 
     def send_params(self, dst):
         self.broadcast("p2p", [self.rank], [dst])
