@@ -224,16 +224,18 @@ def run_router(a, world, states, cfg_model, backend):
             rt.wake.set()
         await asyncio.gather(*tasks)
         t_end = rt.now()
-        scale, loaded = {}, {}
+        scale, loaded, decided = {}, {}, {}
         for t, line in rt.transitions:
             for r in range(2, world):
                 if f"Replica<{r}>" not in line or t < t_trigger:
                     continue
+                if r not in decided and f"Replica<{r}> Inactive =>" in line:
+                    decided[r] = t - t_trigger            # the planner's (or the manual) decision: the replica leaves Inactive
                 if r not in scale and line.rstrip().endswith(("=> Prefill", "=> NewPrefill")):
                     scale[r] = t - t_trigger              # first moment the replica takes work
                 if r not in loaded and line.rstrip().endswith("=> Prefill"):
                     loaded[r] = t - t_trigger             # all parameters resident, ordinary prefill replica
-        scale = {"serving": scale, "loaded": loaded}
+        scale = {"serving": scale, "loaded": loaded, "decided": decided}
         await rt.stop()
         loop_task.cancel()
         return records, scale, t_start, t_end, [l for _, l in rt.transitions if "boot" not in l]
@@ -255,6 +257,13 @@ def run_router(a, world, states, cfg_model, backend):
            "max_incoming_migrations": a.max_incoming_migrations, "precapture": bool(a.precapture),
            "scale_out_latency_ms": {str(r): round(v * 1e3, 2) for r, v in sorted(scale["serving"].items())},
            "fully_loaded_ms": {str(r): round(v * 1e3, 2) for r, v in sorted(scale["loaded"].items())},
+           # with --autoscale the clock starts when the burst begins, so the figures above contain the time the planner
+           # needed to see the burst; these two split it off
+           "decision_ms": {str(r): round(v * 1e3, 2) for r, v in sorted(scale["decided"].items())},
+           "serving_after_decision_ms": {str(r): round((v - scale["decided"].get(r, 0.0)) * 1e3, 2)
+                                         for r, v in sorted(scale["serving"].items())},
+           "loaded_after_decision_ms": {str(r): round((v - scale["decided"].get(r, 0.0)) * 1e3, 2)
+                                        for r, v in sorted(scale["loaded"].items())},
            "param_gb_per_replica": round(seg_bytes / 1e9, 3),
            "effective_gbs_per_replica": {str(r): round(seg_bytes / v / 1e9, 1) for r, v in sorted(scale["loaded"].items()) if v > 0},
            "ttft_ms_p50": round(pct([r["ttft"] for r in burst], 0.5) * 1e3, 2),

@@ -136,7 +136,32 @@ class ZigzagScheduler {
     r.next_layer = t.embedded ? t.next_layer : -1;
     return r;
   }
+  // The same hand-over for a task named by its sequence number: what the other tensor-parallel shards of a replica
+  // do once the leading shard has chosen (their queues may momentarily hold a different set of tasks, so "head" or
+  // "second" would not name the same task everywhere).
+  std::optional<ZagRelay> relay_task(uint32_t seq_num) {
+    for (auto it = tasks_.begin(); it != tasks_.end(); ++it) {
+      if (it->seq_num != seq_num) continue;
+      ZagRelay r;
+      r.batch_id = it->batch_id; r.seq_num = it->seq_num; r.slot = it->slot; r.num_tokens = it->num_tokens;
+      r.next_layer = it->embedded ? it->next_layer : -1;
+      tasks_.erase(it);
+      return r;
+    }
+    return std::nullopt;
+  }
   void release_slot(int slot) { free_slots_.push_back(slot); }
+  // batch id of the queued task with this sequence number (nullopt while its request has not arrived here)
+  std::optional<uint64_t> batch_of(uint32_t seq_num) const {
+    for (const ZagTask& t : tasks_)
+      if (t.seq_num == seq_num) return t.batch_id;
+    return std::nullopt;
+  }
+  std::optional<uint32_t> seq_of(uint64_t batch_id) const {
+    for (const ZagTask& t : tasks_)
+      if (t.batch_id == batch_id) return t.seq_num;
+    return std::nullopt;
+  }
 
   bool embed_ready() const { return embed_ready_; }
   int layers_ready() const { return layers_ready_; }
@@ -154,9 +179,9 @@ inline void bind_zigzag(pybind11::module_& m) {
   namespace py = pybind11;
   py::enum_<ZagStep>(m, "ZagStep").value("Idle", ZagStep::Idle).value("Blocked", ZagStep::Blocked)
       .value("Embed", ZagStep::Embed).value("Layer", ZagStep::Layer).value("Head", ZagStep::Head);
-  py::class_<ZagDecision>(m, "ZagDecision").def_readonly("step", &ZagDecision::step)
-      .def_readonly("batch_id", &ZagDecision::batch_id).def_readonly("layer", &ZagDecision::layer)
-      .def_readonly("slot", &ZagDecision::slot);
+  py::class_<ZagDecision>(m, "ZagDecision").def(py::init<>()).def_readwrite("step", &ZagDecision::step)
+      .def_readwrite("batch_id", &ZagDecision::batch_id).def_readwrite("layer", &ZagDecision::layer)
+      .def_readwrite("slot", &ZagDecision::slot);
   py::class_<ZagRelay>(m, "ZagRelay").def_readonly("batch_id", &ZagRelay::batch_id)
       .def_readonly("seq_num", &ZagRelay::seq_num).def_readonly("next_layer", &ZagRelay::next_layer)
       .def_readonly("slot", &ZagRelay::slot).def_readonly("num_tokens", &ZagRelay::num_tokens);
@@ -165,6 +190,8 @@ inline void bind_zigzag(pybind11::module_& m) {
       .def("pending", &ZigzagScheduler::pending).def("free_slots", &ZigzagScheduler::free_slots)
       .def("add_task", &ZigzagScheduler::add_task).def("next", &ZigzagScheduler::next)
       .def("complete", &ZigzagScheduler::complete).def("relay", &ZigzagScheduler::relay)
+      .def("relay_task", &ZigzagScheduler::relay_task).def("batch_of", &ZigzagScheduler::batch_of)
+      .def("seq_of", &ZigzagScheduler::seq_of)
       .def("release_slot", &ZigzagScheduler::release_slot)
       .def_property_readonly("layers_ready", &ZigzagScheduler::layers_ready);
 }

@@ -14,6 +14,7 @@ Flag pad layout (uint32 counters, all zero at boot):
     [256, 256 + KV_SLOTS*LAYERS)  KV push: per (transfer slot, layer)         (+1 per push)
     [AGREE_FLAG0, +16)            loaded-unit counts published by the TP shards of the replica (plain stores)
     [KV_DONE_FLAG0, +KV_SLOTS)    KV push: per transfer slot, +1 after the last layer of a push
+    [ZAG_LOG_FLAG0, +ZAG_LOG)     live execution at tp > 1: ring of step decisions the leading shard publishes
 """
 from __future__ import annotations
 
@@ -34,7 +35,9 @@ KV_SLOTS = 8
 MAX_LAYERS = 128
 AGREE_FLAG0 = KV_FLAG0 + KV_SLOTS * MAX_LAYERS    # loaded-unit count of every TP shard of this replica (<= 16)
 KV_DONE_FLAG0 = AGREE_FLAG0 + 16                  # per transfer slot: +1 when a whole push (all its layers) has landed
-FLAG_WORDS = KV_DONE_FLAG0 + KV_SLOTS
+ZAG_LOG_FLAG0 = KV_DONE_FLAG0 + KV_SLOTS           # ring of decisions of the leading TP shard (see parallel/agreement.py)
+ZAG_LOG = 16
+FLAG_WORDS = ZAG_LOG_FLAG0 + ZAG_LOG
 
 
 def _stream() -> ctypes.c_void_p:

@@ -39,6 +39,7 @@ _EPI = {"store": 0, "add": 1, "silu_mul": 2, "push": 3}
 
 
 class FusedTP:
+    LANES = 2
     FLAG_WORDS = 128  # rs0: 0..15, rs1: 16..31, ag0: 32..39, ag1: 40..47, one-shot all-reduce: 48..56 and 64..72
 
     def __init__(self, group, hidden: int, max_rows: int, dtype=torch.bfloat16, device=None, contexts: int = 1,
@@ -59,20 +60,25 @@ class FusedTP:
         self._ar_parity = 0
         self.fused_allreduce = True                           # one-kernel all-reduce (per-block rendezvous)
         self.o_cflags = self.o_flags + self.FLAG_WORDS * 4    # per-block counters of it: [parity 2][tp 8][64 blocks]
-        # switch-reduced path (all-reduce + add + RMSNorm in one kernel): partial results [parity 2], and `contexts`
-        # copies of the replicated residual stream and of the normalised activations (one per interleaved task)
+        # switch-reduced path (all-reduce + add + RMSNorm in one kernel): partial results [lane][parity], and `contexts`
+        # copies of the replicated residual stream and of the normalised activations (one per interleaved task).
+        # A lane is an independent sequence of calls with its own partial buffers, counters and parity: lane 0 is the
+        # ordinary forward pass (parity restarts with every pass, which is what a captured graph bakes in), lane 1 is
+        # live execution, whose steps of several tasks interleave and whose parity therefore just keeps alternating.
         self.contexts = contexts
-        self.o_in = [self.o_cflags + 2 * 8 * 64 * 4, 0]
-        self.o_in[1] = self.o_in[0] + self.buf_bytes
-        self.o_res = self.o_in[1] + self.buf_bytes
+        L2 = 2 * self.LANES
+        o = self.o_cflags + 2 * 8 * 64 * 4
+        self.o_in = [o + i * self.buf_bytes for i in range(L2)]            # index lane * 2 + parity
+        self.o_res = o + L2 * self.buf_bytes
         self.o_xn = self.o_res + contexts * self.buf_bytes
-        self.o_nflags = self.o_xn + contexts * self.buf_bytes  # [parity 2][32 words]: ready[8] | done[8] | ticket
+        self.o_nflags = self.o_xn + contexts * self.buf_bytes  # [lane][parity][32 words]: ready[8] | done[8] | ticket
         self.gather_bytes = gather_bytes                       # per rank and call of the small all-gather
-        self.o_gather = self.o_nflags + 2 * 32 * 4             # [parity 2][tp][gather_bytes]
-        self.o_gflags = self.o_gather + 2 * self.tp * gather_bytes  # [parity 2][16 words]
-        total = self.o_gflags + 2 * 16 * 4
-        self._in_parity = 0
-        self._g_parity = 0
+        self.o_gather = self.o_nflags + L2 * 32 * 4            # [lane][parity][tp][gather_bytes]
+        self.o_gflags = self.o_gather + L2 * self.tp * gather_bytes  # [lane][parity][16 words]
+        total = self.o_gflags + L2 * 16 * 4
+        self._in_parity = [0] * self.LANES
+        self._g_parity = [0] * self.LANES
+        self.lane = 0
         self.ctx = 0
         self.region = SymmRegion(total, group, device)
         self.region.local[self.o_flags:].zero_()
@@ -168,9 +174,10 @@ class FusedTP:
 
     def reset_allreduce_parity(self) -> None:
         """Call at the same point of the program on every rank (the runner does it at the start of a forward)."""
-        self._ar_parity = 0
-        self._in_parity = 0
-        self._g_parity = 0
+        if self.lane == 0:
+            self._ar_parity = 0
+            self._in_parity[0] = 0
+            self._g_parity[0] = 0
 
     # ------------------------------------------------------------------ switch-reduced path
     def use_context(self, i: int) -> None:
@@ -179,9 +186,15 @@ class FusedTP:
         assert 0 <= i < self.contexts
         self.ctx = i
 
+    def use_lane(self, i: int) -> None:
+        """Select the call sequence (partial buffers, counters, parity) the next calls belong to.  Every rank of the
+        group must make the same calls in the same order within a lane; the lanes are independent of each other."""
+        assert 0 <= i < self.LANES
+        self.lane = i
+
     def next_partial(self, rows: int) -> torch.Tensor:
         """Buffer for the next row-parallel GEMM's partial result (alternates between two, like the counters)."""
-        off = self.o_in[self._in_parity]
+        off = self.o_in[self.lane * 2 + self._in_parity[self.lane]]
         return self.region.local[off:off + rows * self.hidden * self.elem].view(self.dtype).view(rows, self.hidden)
 
     def res(self, rows: int) -> torch.Tensor:
@@ -197,8 +210,8 @@ class FusedTP:
         One kernel: the switch sums the partials (multimem.ld_reduce), every rank finalises its share of the rows and
         writes them into every rank's copies (multimem.st).  Both results are valid on every rank afterwards."""
         assert self.has_mc and rows <= self.max_rows
-        par = self._in_parity
-        self._in_parity ^= 1
+        par = self.lane * 2 + self._in_parity[self.lane]
+        self._in_parity[self.lane] ^= 1
         mc = self.region.mc_ptr
         fl = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + self.o_nflags + par * 32 * 4 for r in range(self.tp)])
         res_off = self.o_res + self.ctx * self.buf_bytes
@@ -216,8 +229,8 @@ class FusedTP:
         t = t.contiguous()
         nbytes = (t.numel() * t.element_size() + 15) // 16 * 16
         assert nbytes <= self.gather_bytes, "piece too large for the small all-gather"
-        par = self._g_parity
-        self._g_parity ^= 1
+        par = self.lane * 2 + self._g_parity[self.lane]
+        self._g_parity[self.lane] ^= 1
         base = self.o_gather + par * self.tp * self.gather_bytes
         src = t
         if t.numel() * t.element_size() != nbytes:          # pad to whole 16-byte vectors
@@ -285,6 +298,7 @@ class LlamaRunnerTP(LlamaRunner):
         self._nccl_comm = comm
         self._peer_comm = _PeerAllReduce(comm, fused)
         self.use_switch = True
+        self.force_switch = False     # live execution: every step takes the switch-reduced path, whatever its size
         self.res_shard = torch.empty(fused.max_rows // fused.tp, self.cfg.hidden, dtype=seg.dtype, device=self.res.device)
         self._pad_ids = torch.zeros(fused.max_rows, dtype=torch.int32, device=self.res.device)
 
@@ -299,7 +313,18 @@ class LlamaRunnerTP(LlamaRunner):
     def _switch(self, m: StepMeta) -> bool:
         """Steps of a few hundred rows on a fabric with in-switch reduction: all-reduce, residual add and RMSNorm are
         one kernel (`FusedTP.ar_add_norm`), the residual stream and the normalised rows live in symmetric memory."""
-        return self._small(m) and self.fused.has_mc and self.use_switch
+        return (self._small(m) or self.force_switch) and self.fused.has_mc and self.use_switch
+
+    def load_residual(self, T: int, src: torch.Tensor, layer: int) -> None:
+        """Continue a batch whose first `layer` layers ran elsewhere: `src` [T, hidden] is the residual stream after
+        them (every shard holds all rows on the switch-reduced path).  The normalised rows that layer `layer` reads are
+        rebuilt from it here."""
+        f, c = self.fused, self.cfg
+        f.reset_allreduce_parity()
+        self.comm = self._peer_comm
+        f.res(T).copy_(src[:T])
+        nw = self._w(layer, "input_ln") if layer < c.layers else self.seg["final_norm"]
+        ops.rms_norm(f.res(T), nw, c.rms_eps, out=f.xn(T))
 
     def embed(self, m: StepMeta) -> None:
         self.fused.reset_allreduce_parity()

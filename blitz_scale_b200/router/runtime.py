@@ -426,7 +426,10 @@ class RouterRuntime:
 
     async def _do_relay(self, a) -> None:
         new_ranks = self._ranks(a.replica)
-        res = (await self._all(new_ranks, [self.stubs[r].relay(a.src_ranks[0], a.final) for r in new_ranks]))[0]
+        # shard i of the new replica hands its copy of the activations to shard i of the old one
+        old = list(a.src_ranks)
+        res = (await self._all(new_ranks, [self.stubs[r].relay(old[i % len(old)], a.final)
+                                           for i, r in enumerate(new_ranks)]))[0]
         has = res.HasField("batch_id")
         next_layer = 0
         if has:

@@ -30,7 +30,7 @@ from ..models.config import get_config
 from ..models.llama import TPComm
 from ..models.weights import WeightSegment
 from ..parallel import symm
-from ..parallel.agreement import LoadAgreement
+from ..parallel.agreement import LoadAgreement, StepLog
 from ..pb.schema import pb
 from ..runtime import core
 from ..runtime.engine import Engine
@@ -69,7 +69,8 @@ class GpuBackend(Backend):
         comm = TPComm(tp_group) if tp > 1 else None
         self.engine = Engine(self.cfg, num_pages=num_pages, page_size=page_size, max_batch=max_batch,
                              max_batch_tokens=max_batch_tokens, tp=tp, tp_rank=rank % tp, dtype=dt, comm=comm,
-                             seg_buffer=seg_buf, kv_buffer=kv_buf, ready=ready, seed=seed, fused_tp=fused_tp)
+                             seg_buffer=seg_buf, kv_buffer=kv_buf, ready=ready, seed=seed, fused_tp=fused_tp,
+                             tp_contexts=5 if tp > 1 else 1)     # context 0 + one per live-execution slot
         self.units = [(n, o, b) for n, o, b in self.engine.seg.layout.units]
         if precapture:
             # every decode graph is captured now, whether or not the parameters are here yet, so that neither a
@@ -97,10 +98,14 @@ class GpuBackend(Backend):
         self._kv_done_want = [0] * symm.KV_SLOTS       # pushes started per slot = value its completion counter will reach
         # TP shards of a replica act on the minimum of their loaded-unit counts
         self.agree: Optional[LoadAgreement] = None
+        self.steplog: Optional[StepLog] = None          # order of live-execution steps, decided by the first shard
+        self._agreed_full = False
+        self._relay_waiters: List[tuple] = []           # relay calls waiting for the leading shard's choice
         if tp > 1 and self.fabric is not None:
             first = rank - rank % tp
             self.agree = LoadAgreement(self.fabric, list(range(first, first + tp)), rank, symm.AGREE_FLAG0, L)
             self.agree.publish(L + 2 if ready else 0)
+            self.steplog = StepLog(self.fabric, list(range(first, first + tp)), rank, symm.ZAG_LOG_FLAG0, symm.ZAG_LOG)
         self.zag_thread = threading.Thread(target=self._zag_loop, daemon=True)
         self.zag_thread.start()
         self.transfer_thread: Optional[threading.Thread] = None
@@ -166,11 +171,23 @@ class GpuBackend(Backend):
             slot = b.id % 4
             self.fabric.wait_flag(symm.MAILBOX_FLAG0 + slot, int(b.id) + 1, budget_ms=5000)
             src = self.fabric.mailbox.local[slot * self.slot_bytes:(slot + 1) * self.slot_bytes]
-            eng.runner.res[:T].copy_(src.view(torch.bfloat16).view(-1, self.cfg.hidden)[:T])
+            rows = src.view(torch.bfloat16).view(-1, self.cfg.hidden)
+            if eng.fused is not None:
+                # tensor parallel: every shard received all rows from its counterpart; the rest of the pass keeps the
+                # residual stream replicated (switch-reduced path), whatever the number of rows
+                if not eng.fused.has_mc:
+                    raise RuntimeError("continuing a relayed batch with tp > 1 needs in-switch reduction")
+                eng.runner.load_residual(T, rows, start_layer)
+            else:
+                eng.runner.res[:T].copy_(rows[:T])
             # the slot is consumed: re-arm its flag (stream-ordered after the copy) so that a later batch with a
             # smaller id cannot pass the wait on a stale value
             self.fabric.set_flag(self.rank, symm.MAILBOX_FLAG0 + slot, 0, add=False)
-            toks = eng.runner.forward(m, lo=start_layer, with_embed=False)
+            eng.runner.force_switch = eng.fused is not None
+            try:
+                toks = eng.runner.forward(m, lo=start_layer, with_embed=False)
+            finally:
+                eng.runner.force_switch = False
         else:
             toks = eng.runner.forward(m)
         out = eng._tokens_to_host(toks, b.size)
@@ -223,10 +240,12 @@ class GpuBackend(Backend):
 
     # ------------------------------------------------------------------ live execution (ZigZag)
     def zag_prefill(self, batch, forward_case, pp_info, zag_layers, zag_seq):
-        if self.engine.fused is not None:
-            # the fused TP runner keeps the residual stream sharded by rows inside its own buffers; interleaving several
-            # live-execution tasks layer by layer needs per-task copies of that state, which only the all-reduce runner has
-            raise RuntimeError("live execution with tp > 1 needs workers started with --no-fused-tp")
+        if self.engine.fused is not None and not self.engine.fused.has_mc:
+            # tensor-parallel live execution keeps one residual stream per task in symmetric memory and updates it
+            # through the switch-reduced kernel, which needs the fabric's multicast address
+            raise RuntimeError("live execution with tp > 1 needs in-switch reduction (or workers started with --no-fused-tp)")
+        if self.tp > 1 and self.steplog is None:
+            raise RuntimeError("live execution with tp > 1 needs the peer fabric")
         fut: Future = Future()
         with self.lock:
             b = self.engine.new_batch(batch.id, self._specs(batch))
@@ -236,7 +255,7 @@ class GpuBackend(Backend):
             if slot < 0:
                 b.clear()
                 raise RuntimeError("no activation slot free")
-            self.zag_tasks[batch.id] = {"batch": b, "future": fut, "slot": slot, "meta": None}
+            self.zag_tasks[batch.id] = {"batch": b, "future": fut, "slot": slot, "meta": None, "seq": int(zag_seq)}
             self.zag_cv.notify_all()
         return fut.result(timeout=120)
 
@@ -253,92 +272,187 @@ class GpuBackend(Backend):
                             t["future"].set_exception(RuntimeError("live-execution step failed"))
                 time.sleep(0.01)
 
+    def _zag_loaded(self):
+        """(embedding, layers, head) this replica may use now: what every tensor-parallel shard holds."""
+        st = self.engine.status
+        if self.agree is not None and not self._agreed_full:
+            loaded = self.agree.agreed_state()
+            self._agreed_full = loaded[2] and loaded[1] >= self.cfg.layers
+            return loaded
+        return st.embed_ready, st.layers_ready, st.head_ready
+
     def _zag_turn(self) -> None:
         with self.lock:
-            st = self.engine.status
-            if self.agree is not None and not st.fully_loaded():
-                loaded = self.agree.agreed_state()
+            if self.steplog is not None and not self.steplog.leader:
+                d = self._zag_follow()
+                if d is None:
+                    return
             else:
-                loaded = (st.embed_ready, st.layers_ready, st.head_ready)
-            if loaded[1] < self._zag_layers_seen:
-                self.zag.reset()        # a replica that was emptied and is being loaded again starts from no layers
-            self.zag.set_loaded(*loaded)
-            self._zag_layers_seen = loaded[1]
-            d = self.zag.next()
-            if d.step in (core.ZagStep.Idle, core.ZagStep.Blocked):
-                # nothing to run: sleep until a task or a parameter unit arrives (both notify the condition); the
-                # short timeout only bounds the wait while layers are still landing
-                self.zag_cv.wait(0.0005 if d.step == core.ZagStep.Blocked else 0.05)
-                return
-            task = self.zag_tasks[d.batch_id]
-            eng, b = self.engine, task["batch"]
-            if task["meta"] is None:
-                T, P = b.fill_prefill(eng.host_np, eng.layout)
-                eng._h2d(eng.layout.page_indices + P)
-                # the staging arrays are shared: keep a private device copy of this task's inputs
-                dev_copy = eng.dev[:eng.layout.page_indices + P].clone()
-                task["meta"] = (T, P, dev_copy)
-            T, P, dev_copy = task["meta"]
-            eng.dev[:dev_copy.numel()].copy_(dev_copy)
-            m = eng._views(T, b.size, P, True, b.prompt_lens())
-            saved = eng.runner.res
+                loaded = self._zag_loaded()
+                if loaded[1] < self._zag_layers_seen:
+                    self.zag.reset()    # a replica that was emptied and is being loaded again starts from no layers
+                self.zag.set_loaded(*loaded)
+                self._zag_layers_seen = loaded[1]
+                d = self.zag.next()
+                if d.step in (core.ZagStep.Idle, core.ZagStep.Blocked):
+                    # nothing to run: sleep until a task or a parameter unit arrives (both notify the condition); the
+                    # short timeout only bounds the wait while layers are still landing
+                    self.zag_cv.wait(0.0005 if d.step == core.ZagStep.Blocked else 0.05)
+                    return
+                if self.steplog is not None:
+                    self.steplog.publish(StepLog.STEP, int(d.step), max(0, d.layer), d.slot, self.zag.seq_of(d.batch_id))
+            self._zag_run(d)
+
+    def _zag_follow(self):
+        """A shard other than the leading one: the next entry of the leader's log, as a decision to run here.  Returns
+        None after having waited a little when there is nothing to do yet (no entry, or an entry about a request or a
+        relay call that has not reached this shard)."""
+        e = self.steplog.peek()
+        if e is None:
+            self.zag_cv.wait(0.0003 if (self.zag.pending() or self._relay_waiters) else 0.02)
+            return None
+        if e["kind"] == StepLog.RELAY_NONE:
+            if not self._relay_waiters:
+                self.zag_cv.wait(0.0003)
+                return None
+            self.steplog.consume()
+            self._relay_waiters.pop(0)[1].set_result(None)
+            return None
+        seq = self._zag_seq_full(e["seq_num"])
+        if seq is None:
+            self.zag_cv.wait(0.0003)      # the request itself is still on its way here
+            return None
+        if e["kind"] == StepLog.RELAY:
+            if not self._relay_waiters:
+                self.zag_cv.wait(0.0003)
+                return None
+            self.steplog.consume()
+            rank, fut = self._relay_waiters.pop(0)
+            r = self.zag.relay_task(seq)
+            assert r is not None and r.next_layer == e["layer"] - 1, "shards disagree about a relayed task"
+            fut.set_result(self._relay_task(r, rank, e["slot"]))
+            return None
+        self.steplog.consume()
+        d = core.ZagDecision()
+        d.step, d.batch_id, d.slot = core.ZagStep(e["step"]), self.zag.batch_of(seq), e["slot"]
+        d.layer = e["layer"] if d.step == core.ZagStep.Layer else -1
+        return d
+
+    def _zag_seq_full(self, low8: int):
+        """Sequence number of the queued task whose low 8 bits are `low8` (at most a handful are in flight)."""
+        for t in self.zag_tasks.values():
+            if (t["seq"] & 0xFF) == low8:
+                return t["seq"]
+        return None
+
+    def _zag_run(self, d) -> None:
+        """Run one step (embedding, one layer, or the head) of one live-execution task.  Lock held."""
+        task = self.zag_tasks[d.batch_id]
+        eng, b = self.engine, task["batch"]
+        if task["meta"] is None:
+            T, P = b.fill_prefill(eng.host_np, eng.layout)
+            eng._h2d(eng.layout.page_indices + P)
+            # the staging arrays are shared: keep a private device copy of this task's inputs
+            dev_copy = eng.dev[:eng.layout.page_indices + P].clone()
+            task["meta"] = (T, P, dev_copy)
+        T, P, dev_copy = task["meta"]
+        eng.dev[:dev_copy.numel()].copy_(dev_copy)
+        m = eng._views(T, b.size, P, True, b.prompt_lens())
+        saved = eng.runner.res
+        fused = eng.fused
+        if fused is not None:
+            # tensor parallel: the residual stream and the normalised rows of each task live in a context of the
+            # symmetric region (context 0 belongs to ordinary passes); live steps form their own call sequence
+            fused.use_lane(1)
+            fused.use_context(1 + d.slot)
+            eng.runner.force_switch = True
+        else:
             eng.runner.res = self.zag_slots[task["slot"]]
-            try:
-                if d.step == core.ZagStep.Embed:
-                    log.debug("zag embed batch=%d", d.batch_id)
-                    eng.runner.embed(m)
-                elif d.step == core.ZagStep.Layer:
-                    log.debug("zag layer batch=%d layer=%d", d.batch_id, d.layer)
-                    eng.runner.run_layer(d.layer, m)
-                else:
-                    log.debug("zag head batch=%d", d.batch_id)
-                    toks = eng._tokens_to_host(eng.runner.head(m), b.size)
-                torch.cuda.current_stream().synchronize()
-            finally:
-                eng.runner.res = saved
-            done = self.zag.complete(d)
-            if done:
-                b.mark_prefilled()
-                b.append_tokens(toks, False)
-                b.decode = True
-                gens, cb = self._finish_step(b, toks)
-                self.zag_tasks.pop(d.batch_id)["future"].set_result((gens, cb, None))
+        try:
+            if d.step == core.ZagStep.Embed:
+                log.debug("zag embed batch=%d", d.batch_id)
+                eng.runner.embed(m)
+            elif d.step == core.ZagStep.Layer:
+                log.debug("zag layer batch=%d layer=%d", d.batch_id, d.layer)
+                eng.runner.run_layer(d.layer, m)
+            else:
+                log.debug("zag head batch=%d", d.batch_id)
+                toks = eng._tokens_to_host(eng.runner.head(m), b.size)
+            torch.cuda.current_stream().synchronize()
+        finally:
+            eng.runner.res = saved
+            if fused is not None:
+                fused.use_lane(0)
+                fused.use_context(0)
+                eng.runner.force_switch = False
+        done = self.zag.complete(d)
+        if done:
+            b.mark_prefilled()
+            b.append_tokens(toks, False)
+            b.decode = True
+            gens, cb = self._finish_step(b, toks)
+            self.zag_tasks.pop(d.batch_id)["future"].set_result((gens, cb, None))
 
     def relay(self, rank, relax_not_head):
+        if self.steplog is not None and not self.steplog.leader:
+            # the leading shard chooses the task and the layer; this shard's live-execution thread acts when it reads
+            # that choice in the log
+            fut: Future = Future()
+            with self.lock:
+                self._relay_waiters.append((rank, fut))
+                self.zag_cv.notify_all()
+            return fut.result(timeout=60)
         with self.lock:
             r = self.zag.relay(bool(relax_not_head))
+            if self.steplog is not None:
+                if r is None:
+                    self.steplog.publish(StepLog.RELAY_NONE)
+                else:
+                    self.steplog.publish(StepLog.RELAY, 0, r.next_layer + 1, r.slot, r.seq_num)
             if r is None:
                 return None
-            task = self.zag_tasks.pop(r.batch_id)
-            b = task["batch"]
-            k = max(0, r.next_layer)
-            log.info("zag relay batch=%d layer=%d +>+> rank %d", r.batch_id, k, rank)
-            if k > 0:
-                # ship the residual stream [T, hidden] into the old instance's mailbox slot and flag it
-                T = r.num_tokens
-                nbytes = T * self.cfg.hidden * 2
-                nbytes = (nbytes + 15) // 16 * 16
-                slot = r.batch_id % 4
-                with self.xfer_lock, torch.cuda.stream(self.side):
-                    stage = self.fabric.mailbox.local[slot * self.slot_bytes:slot * self.slot_bytes + nbytes]
-                    stage.copy_(self.zag_slots[task["slot"]].view(torch.uint8).view(-1)[:nbytes])
-                    self.fabric.copy_units(self.fabric.mailbox, [rank], [slot * self.slot_bytes], [nbytes],
-                                           symm.MAILBOX_FLAG0 + slot, num_ctas=16)
-                    # the flag is a counter; publish the batch tag on top so the reader can wait for ">= id + 1"
-                    self.fabric.set_flag(rank, symm.MAILBOX_FLAG0 + slot, int(r.batch_id) + 1, add=False)
-                    self.side.synchronize()
-            self.zag.release_slot(task["slot"])
-            pp = pb.PipeParaInfo()
-            if r.next_layer <= 0:
-                pp.embedding_layer = 1
+            return self._relay_task(r, rank, r.slot)
+
+    def _relay_task(self, r, rank, ctx_slot):
+        """Hand a task over to the old instance's shard `rank`: ship its residual stream, release its slot, answer its
+        ZagPrefill call with the layer to resume from.  Lock held."""
+        task = self.zag_tasks.pop(r.batch_id)
+        b = task["batch"]
+        k = max(0, r.next_layer)
+        log.info("zag relay batch=%d layer=%d +>+> rank %d", r.batch_id, k, rank)
+        if k > 0:
+            # ship the residual stream [T, hidden] into the old instance's mailbox slot and flag it
+            T = r.num_tokens
+            nbytes = T * self.cfg.hidden * 2
+            nbytes = (nbytes + 15) // 16 * 16
+            slot = r.batch_id % 4
+            fused = self.engine.fused
+            if fused is not None:
+                fused.use_context(1 + ctx_slot)
+                resid = fused.res(T)
+                fused.use_context(0)
             else:
-                pp.tfm_layer = k
-            # layers [0, k) of this batch's KV stay here until MigratePartial(FIRST) moves them
-            b.mark_prefilled()
-            self.batches[b.id] = b
-            cb = pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
-            task["future"].set_result(([], cb, pp))
-            return r.batch_id, r.seq_num
+                resid = self.zag_slots[task["slot"]]
+            with self.xfer_lock, torch.cuda.stream(self.side):
+                stage = self.fabric.mailbox.local[slot * self.slot_bytes:slot * self.slot_bytes + nbytes]
+                stage.copy_(resid.view(torch.uint8).view(-1)[:nbytes])
+                self.fabric.copy_units(self.fabric.mailbox, [rank], [slot * self.slot_bytes], [nbytes],
+                                       symm.MAILBOX_FLAG0 + slot, num_ctas=16)
+                # the flag is a counter; publish the batch tag on top so the reader can wait for ">= id + 1"
+                self.fabric.set_flag(rank, symm.MAILBOX_FLAG0 + slot, int(r.batch_id) + 1, add=False)
+                self.side.synchronize()
+        self.zag.release_slot(task["slot"])
+        pp = pb.PipeParaInfo()
+        if r.next_layer <= 0:
+            pp.embedding_layer = 1
+        else:
+            pp.tfm_layer = k
+        # layers [0, k) of this batch's KV stay here until MigratePartial(FIRST) moves them
+        b.mark_prefilled()
+        self.batches[b.id] = b
+        cb = pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
+        task["future"].set_result(([], cb, pp))
+        return r.batch_id, r.seq_num
 
     # ------------------------------------------------------------------ KV migration
     def _layer_range(self, partial, num_layer):
@@ -506,6 +620,7 @@ class GpuBackend(Backend):
             self.engine.status.reset()
             if self.agree is not None:
                 self.agree.publish(0)
+                self._agreed_full = False
             base = self.param_expected
             self.param_expected += n_stripes
         want, n_units, nxt = base + n_stripes, len(self.units), 0

@@ -43,3 +43,17 @@ def test_peer_kernels(case):
     n = min(_ngpu(), 4) if case.startswith("multicast") else 2
     out = _run(case, n)
     assert "OK" in out or "SKIP" in out
+
+
+def test_live_execution_on_tensor_parallel_replicas():
+    """Layer-interleaved prefill while parameters arrive at tp = 2: the shards agree on loaded layers and follow the
+    leading shard's step order; with 4 GPUs the head task is also handed over to an old tp = 2 replica."""
+    if _ngpu() < 2:
+        pytest.skip("needs >= 2 GPUs")
+    n = 4 if _ngpu() >= 4 else 2
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29537", os.path.join(HERE, "gpu_live_tp.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "OK" in res.stdout or "SKIP" in res.stdout

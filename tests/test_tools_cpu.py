@@ -190,6 +190,70 @@ def test_tp_load_agreement():
     assert 0 not in pads[0] and F0 not in pads[0]          # nothing leaks to other replicas' pads
 
 
+def test_tp_step_log_orders_live_execution_steps():
+    """The leading shard's decisions reach the other shard in order, one word each, through a ring that is reused; the
+    follower's scheduler applies them by task sequence number although its queue filled in a different order."""
+    from blitz_scale_b200.parallel.agreement import StepLog
+    from blitz_scale_b200.runtime import core
+
+    class FakeFabric:
+        def __init__(self, rank, pads):
+            self.rank, self.pads = rank, pads
+        def set_flag(self, rank, index, value, add=False):
+            self.pads[rank][index] = value
+        def read_flags(self, start, count):
+            return [self.pads[self.rank].get(start + i, 0) for i in range(count)]
+
+    pads = {r: {} for r in range(2)}
+    lead = StepLog(FakeFabric(0, pads), [0, 1], 0, 500, 16)
+    fol = StepLog(FakeFabric(1, pads), [0, 1], 1, 500, 16)
+    assert lead.leader and not fol.leader and fol.peek() is None
+    L = 3
+    zl, zf = core.ZigzagScheduler(L, 4), core.ZigzagScheduler(L, 4)
+    zl.add_task(70, 1, 10)
+    zl.add_task(71, 2, 20)
+    zl.set_loaded(True, 1, False)
+    applied = []
+    fol_tasks_added = False
+    for turn in range(60):
+        if turn == 3:
+            zl.set_loaded(True, 2, False)
+        if turn == 6:
+            zl.set_loaded(True, L, True)
+        d = zl.next()
+        if d.step in (core.ZagStep.Idle, core.ZagStep.Blocked):
+            if turn > 6:
+                break
+            continue
+        lead.publish(StepLog.STEP, int(d.step), max(0, d.layer), d.slot, zl.seq_of(d.batch_id))
+        zl.complete(d)
+        if turn == 1 and not fol_tasks_added:
+            # the follower hears about the requests late, and in one go
+            zf.add_task(70, 1, 10)
+            zf.add_task(71, 2, 20)
+            fol_tasks_added = True
+        while fol_tasks_added:
+            e = fol.peek()
+            if e is None:
+                break
+            fol.consume()
+            fd = core.ZagDecision()
+            fd.step, fd.batch_id, fd.slot = core.ZagStep(e["step"]), zf.batch_of(e["seq_num"]), e["slot"]
+            fd.layer = e["layer"] if fd.step == core.ZagStep.Layer else -1
+            zf.complete(fd)
+            applied.append((int(fd.step), fd.batch_id, fd.layer))
+    assert zl.pending() == 0 and zf.pending() == 0
+    assert len(applied) == 2 * (L + 2) and lead.pos == fol.pos == len(applied)
+    # a hand-over names the task by sequence number
+    zf.add_task(80, 5, 7)
+    zf.add_task(81, 6, 9)
+    lead.publish(StepLog.RELAY, 0, 0, 2, 6)
+    e = fol.peek()
+    assert e["kind"] == StepLog.RELAY and e["seq_num"] == 6 and e["layer"] == 0
+    r = zf.relay_task(e["seq_num"])
+    assert r.batch_id == 81 and r.next_layer == -1 and zf.pending() == 1 and zf.relay_task(99) is None
+
+
 def test_otlp_span_export_logging_and_cors(tmp_path):
     """Spans of dispatched operations and requests reach an OTLP/HTTP collector (a local stand-in) in the JSON
     mapping; the log set-up writes JSON lines through the background file writer; CORS headers follow the allow list."""
