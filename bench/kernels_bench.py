@@ -133,11 +133,31 @@ def bench_prefill_attn(cases, out):
                    frac_of_gemm_peak=fl / t / flops_peak, peaks=src)
         out.append(row)
         print(json.dumps(row), flush=True)
+        # the same attention through the paged pool (two ping-ponged query tiles per CTA, keys and values read from
+        # 64-token pages), with and without the exponentials shared between the special-function unit and the FMA pipe
+        ps = 64
+        npg = n // ps
+        pool = torch.randn(B * npg, 2, ps, kvh, hd, device="cuda", dtype=torch.bfloat16)
+        ids = torch.randperm(B * npg, device="cuda").to(torch.int32)
+        pindptr = (torch.arange(B + 1, device="cuda") * npg).to(torch.int32)
+        last = torch.full((B,), ps, dtype=torch.int32, device="cuda")
+        work = ops.prefill_work_list([n] * B, [n] * B, "cuda")
+        for poly, ptmem in ((False, False), (False, True), (True, True)):
+            t = timeit(lambda i: ops.attn_prefill_paged(qkv, pool, indptr, ids, pindptr, last, [n] * B, q_heads=qh,
+                                                         kv_heads=kvh, head_dim=hd, page_size=ps, out=o, work=work,
+                                                         poly_exp=poly, p_in_tmem=ptmem))
+            ops.check_status()
+            row = dict(kind="attn_prefill_paged", B=B, n=n, q_heads=qh, kv_heads=kvh, poly_exp=poly, p_in_tmem=ptmem,
+                       us=t * 1e6,
+                       tflops=fl / t / 1e12, frac_of_gemm_peak=fl / t / flops_peak, peaks=src)
+            out.append(row)
+            print(json.dumps(row), flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--only", default="", help="run only one group: gemm, decode_attn, prefill_attn")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     out = []
@@ -148,11 +168,14 @@ def main():
         shapes += [(M, 6144, 4096, "store"), (M, 4096, 4096, "add"), (M, 14336, 4096, "silu_mul"),
                    (M, 4096, 14336, "add")]
     shapes += [(256, 128256, 4096, "store"), (8192, 8192, 8192, "store")]
-    bench_gemm(shapes, out)
+    if args.only in ("", "gemm"):
+        bench_gemm(shapes, out)
     cases = [(64, 1024, 32, 8, 128, 64, 1), (256, 1024, 32, 8, 128, 64, 1), (256, 1024, 32, 8, 128, 16, 1),
              (8, 8192, 32, 8, 128, 64, 8), (1, 16384, 32, 8, 128, 64, 32)]
-    bench_decode_attn(cases[:2] if args.quick else cases, out)
-    bench_prefill_attn([(4, 2048, 32, 8)] if args.quick else [(8, 512, 32, 8), (4, 2048, 32, 8), (1, 8192, 32, 8)], out)
+    if args.only in ("", "decode_attn"):
+        bench_decode_attn(cases[:2] if args.quick else cases, out)
+    if args.only in ("", "prefill_attn"):
+        bench_prefill_attn([(4, 2048, 32, 8)] if args.quick else [(8, 512, 32, 8), (4, 2048, 32, 8), (1, 8192, 32, 8)], out)
     if args.json:
         os.makedirs(os.path.dirname(os.path.abspath(args.json)), exist_ok=True)
         json.dump(out, open(args.json, "w"), indent=1)

@@ -45,6 +45,7 @@ inline const std::map<std::string, ModelShape>& model_registry() {
              mk("tiny", 32000, 256, 2, 4, 2, 688),
              mk("tiny_gpu", 4096, 512, 2, 4, 2, 1408, 5e5),
              mk("tiny_gpu_deep", 4096, 512, 8, 4, 2, 1408, 5e5),
+             mk("tiny_gpu_wide", 4096, 1024, 2, 8, 4, 2816, 5e5),
              mk("opt_125m", 50272, 768, 12, 12, 12, 3072),
              mk("opt_1.3b", 50272, 2048, 24, 32, 32, 8192),
              mk("opt_6.7b", 50272, 4096, 32, 32, 32, 16384),

@@ -56,6 +56,7 @@ REGISTRY: Dict[str, ModelConfig] = {c.name: c for c in [
     # smallest shape the tcgen05 attention (head_dim 128) accepts; used by GPU tests and smoke()
     _c("tiny_gpu", 4096, 512, 2, 4, 2, 1408, theta=5e5),
     _c("tiny_gpu_deep", 4096, 512, 8, 4, 2, 1408, theta=5e5),
+    _c("tiny_gpu_wide", 4096, 1024, 2, 8, 4, 2816, theta=5e5),
     _c("opt_125m", 50272, 768, 12, 12, 12, 3072),
     _c("opt_1.3b", 50272, 2048, 24, 32, 32, 8192),
     _c("opt_6.7b", 50272, 4096, 32, 32, 32, 16384),

@@ -10,6 +10,10 @@ rank 0 also runs the router runtime in-process and replays a small trace through
             replica (byte-exact weights -> same tokens), then used for prefill.
   live      the new replica serves while loading (ZigZag): batches are relayed to the old prefill replica
             through the activation mailbox; tokens again match.
+  pd_tp2    (4 GPUs) the pd case with two tensor-parallel replicas of two shards each: every RPC goes to both shards of
+            a replica, KV pages move shard to shard (rank i of the prefill replica pushes into rank i of the decode
+            replica); the expected tokens come from the prefill replica's own engine, run by its two shards together
+            before serving starts.
 """
 import asyncio
 import os
@@ -23,10 +27,23 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def reference_tokens(prompts, new_tokens):
+def make_requests():
+    g = torch.Generator().manual_seed(11)
+    n_req = 12
+    lens = [int(x) for x in torch.randint(20, 300, (n_req,), generator=g)]
+    news = [int(x) for x in torch.randint(3, 9, (n_req,), generator=g)]
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in lens]
+    return prompts, news
+
+
+def reference_tokens(prompts, new_tokens, eng=None):
+    """Greedy tokens of every request, one request at a time: on a fresh single-GPU engine, or on `eng` (all shards of
+    a tensor-parallel engine call this together)."""
     from blitz_scale_b200.runtime import core
     from blitz_scale_b200.runtime.engine import Engine
-    eng = Engine("tiny_gpu", num_pages=256, page_size=16, max_batch=8, max_batch_tokens=2048, seed=0, use_graphs=False)
+    own = eng is None
+    if own:
+        eng = Engine("tiny_gpu", num_pages=256, page_size=16, max_batch=8, max_batch_tokens=2048, seed=0, use_graphs=False)
     out = []
     for i, (p, n) in enumerate(zip(prompts, new_tokens)):
         b = eng.new_batch(1000 + i, [core.SeqSpec(i, p, n)])
@@ -36,8 +53,9 @@ def reference_tokens(prompts, new_tokens):
             seq += eng.decode(b)
         b.clear()
         out.append(seq)
-    del eng
-    torch.cuda.empty_cache()
+    if own:
+        del eng
+        torch.cuda.empty_cache()
     return out
 
 
@@ -49,15 +67,30 @@ def main():
     host_group = dist.new_group(backend="gloo")     # host-side rendezvous that keeps no kernel spinning on the GPUs
     from blitz_scale_b200.worker.gpu_backend import GpuBackend
     from blitz_scale_b200.worker.service import serve
-    states = {"pd": ["Prefill", "Decode"], "scale": ["Prefill", "Decode", "Inactive"],
-              "live": ["Prefill", "Decode", "Inactive"]}[case][:world]
+    tp = 2 if case.endswith("_tp2") else 1
+    case = case[:-4] if tp == 2 else case
+    replica_states = {"pd": ["Prefill", "Decode"], "scale": ["Prefill", "Decode", "Inactive"],
+                      "live": ["Prefill", "Decode", "Inactive"]}[case][:world // tp]
+    states = [s for s in replica_states for _ in range(tp)]          # one entry per rank
+    tp_group = None
+    if tp > 1:
+        for r0 in range(0, world, tp):
+            g_ = dist.new_group(list(range(r0, r0 + tp)))
+            if r0 <= rank < r0 + tp:
+                tp_group = g_
     base_port = 50400 + (os.getpid() % 50) * 0
-    backend = GpuBackend(rank, world, "tiny_gpu", tp=1, num_pages=256, page_size=16, max_batch=16, max_batch_tokens=2048,
-                         ready=states[rank] != "Inactive", seed=0, copy_ctas=16)
+    backend = GpuBackend(rank, world, "tiny_gpu", tp=tp, tp_group=tp_group, num_pages=256, page_size=16, max_batch=16,
+                         max_batch_tokens=2048, ready=states[rank] != "Inactive", seed=0, copy_ctas=16)
     if states[rank] == "Inactive":
         backend.engine.seg.buffer.zero_()          # a fresh replica holds no parameters
     torch.cuda.synchronize()
     dist.barrier()
+    ref = None
+    if tp > 1 and rank < tp:
+        # the expected tokens of a sharded model come from the first replica's own engine, before it serves
+        ref = reference_tokens(*make_requests(), eng=backend.engine)
+        assert backend.engine.pool.used_pages == 0
+    dist.barrier(group=host_group)
 
     stop_holder = {}
     started = threading.Event()
@@ -82,7 +115,7 @@ def main():
     ok = 1
     if rank == 0:
         try:
-            ok = run_router(case, world, states, base_port)
+            ok = run_router(case, world, states, base_port, tp, ref)
         except Exception as e:  # noqa: BLE001
             import traceback
             traceback.print_exc()
@@ -95,7 +128,7 @@ def main():
     dist.barrier(group=host_group)
     good = int(flag) == 1
     if rank == 0 and good:
-        print(f"cluster {case}: OK on {world} GPUs", flush=True)
+        print(f"cluster {case}{'_tp2' if tp == 2 else ''}: OK on {world} GPUs", flush=True)
     sys.stdout.flush()
     sys.stderr.flush()
     from blitz_scale_b200.parallel.teardown import shutdown
@@ -103,18 +136,16 @@ def main():
     sys.exit(0 if good else 1)
 
 
-def run_router(case, world, states, base_port) -> int:
+def run_router(case, world, states, base_port, tp=1, ref=None) -> int:
     from blitz_scale_b200.router.runtime import RouterRuntime
     from blitz_scale_b200.router.server import controller_config_from_cluster
-    g = torch.Generator().manual_seed(11)
-    n_req = 12
-    lens = [int(x) for x in torch.randint(20, 300, (n_req,), generator=g)]
-    news = [int(x) for x in torch.randint(3, 9, (n_req,), generator=g)]
-    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in lens]
-    ref = reference_tokens(prompts, news)
+    prompts, news = make_requests()
+    n_req = len(prompts)
+    if ref is None:
+        ref = reference_tokens(prompts, news)
     feats = {"pd": "impl_blitz,impl_nvl,manually_scale", "scale": "impl_blitz,impl_nvl,manually_scale",
              "live": "impl_blitz,impl_nvl,impl_live,manually_scale"}[case]
-    cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
+    cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, tp, feats,
                                          max_blocks_per_replica=200, block_size=16, max_prefill_tokens=1024,
                                          model_layers=2, zigzag_req_limit=2, zigzag_req_floor=2, max_batch_seqs=16)
 

@@ -205,12 +205,13 @@ def main():
         from blitz_scale_b200.runtime import core
         from blitz_scale_b200.runtime.engine import Engine
         comm = TPComm(dist.group.WORLD)
+        model = "tiny_gpu" if world <= 2 else "tiny_gpu_wide"       # 4 KV heads: one per shard at tp = 4
         outs, logits = [], []
         # the row-sharded fused pipeline, the switch-reduced one-kernel mode (where the fabric has NVLS), the one-shot
         # peer-memory all-reduce mode, and the NCCL runner (reference, last)
         sampled = []
         for fused_tp, oneshot, switch in ((True, 0, False), (True, 1024, True), (True, 1024, False), (False, 0, False)):
-            eng = Engine("tiny_gpu", num_pages=64, page_size=16, max_batch=8, max_batch_tokens=1024, tp=world, tp_rank=rank,
+            eng = Engine(model, num_pages=64, page_size=16, max_batch=8, max_batch_tokens=1024, tp=world, tp_rank=rank,
                          comm=comm, seed=4, fused_tp=fused_tp, oneshot_max_rows=oneshot, use_switch=switch)
             assert (eng.fused is not None) == fused_tp
             owners.append(eng)

@@ -23,7 +23,7 @@ def _run(case, nproc, extra_env=None):
     return res.stdout
 
 
-@pytest.mark.parametrize("case,n", [("pd", 2), ("scale", 3), ("live", 3)])
+@pytest.mark.parametrize("case,n", [("pd", 2), ("scale", 3), ("live", 3), ("pd_tp2", 4)])
 def test_gpu_cluster_end_to_end(case, n):
     """GPU workers over gRPC + router runtime: PD with in-kernel KV push, scale-out by parameter multicast, live scaling."""
     if _ngpu() < n:
@@ -43,6 +43,13 @@ def test_peer_kernels(case):
     n = min(_ngpu(), 4) if case.startswith("multicast") else 2
     out = _run(case, n)
     assert "OK" in out or "SKIP" in out
+
+
+@pytest.mark.skipif(_ngpu() < 4, reason="needs >= 4 GPUs")
+def test_engine_tensor_parallel_4():
+    """The engine at tp = 4 (one KV head per shard): fused runners against the NCCL runner, sharded sampling."""
+    out = _run("engine_tp", 4)
+    assert "OK" in out
 
 
 def test_live_execution_on_tensor_parallel_replicas():

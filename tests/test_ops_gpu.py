@@ -343,6 +343,99 @@ def test_attn_decode_simt_matches_tc(ops):
     assert rc == 0 and rel_err(a, b) < 1e-2
 
 
+@pytest.mark.parametrize("qh,kvh,hd,ps,dt,cases", [
+    (8, 2, 128, 16, torch.bfloat16, [(300, 0), (128, 0), (1, 0), (77, 200), (513, 256)]),
+    (4, 4, 128, 64, torch.float16, [(256, 0), (257, 129), (40, 1000)]),
+    (6, 2, 64, 64, torch.bfloat16, [(700, 0), (130, 64), (5, 0)]),
+    (8, 1, 64, 8, torch.bfloat16, [(260, 24)]),
+])
+@pytest.mark.parametrize("poly,ptmem", [(False, False), (True, False), (False, True), (True, True)])
+def test_attn_prefill_paged(ops, qh, kvh, hd, ps, dt, cases, poly, ptmem):
+    """Chunk rows against prefix + chunk in the paged pool, two ping-ponged query tiles per CTA, against fp32 math.
+    (q_len, prefix) per sequence; pages are scattered over the pool; stale pool contents are finite garbage."""
+    torch.manual_seed(5)
+    T = sum(n for n, _ in cases)
+    qkv = torch.randn(T, (qh + 2 * kvh) * hd, device="cuda", dtype=dt)
+    need = sum((n + pre + ps - 1) // ps for n, pre in cases)
+    pool_pages = need + 7
+    pool = (torch.randn(pool_pages, 2, ps, kvh, hd, device="cuda") * 3).to(dt)      # garbage where nothing is stored
+    perm = torch.randperm(pool_pages).tolist()
+    tok_indptr, page_indptr, page_ids, last = [0], [0], [], []
+    full = []
+    o = 0
+    for n, pre in cases:
+        kv_len = n + pre
+        npg = (kv_len + ps - 1) // ps
+        mine = [perm.pop() for _ in range(npg)]
+        k = torch.randn(kv_len, kvh, hd, device="cuda", dtype=dt)
+        v = torch.randn(kv_len, kvh, hd, device="cuda", dtype=dt)
+        # the chunk's own keys and values are what its qkv rows carry
+        k[pre:] = qkv[o:o + n, qh * hd:(qh + kvh) * hd].view(n, kvh, hd)
+        v[pre:] = qkv[o:o + n, (qh + kvh) * hd:].view(n, kvh, hd)
+        for t in range(kv_len):
+            pool[mine[t // ps], 0, t % ps] = k[t]
+            pool[mine[t // ps], 1, t % ps] = v[t]
+        full.append((k, v))
+        page_ids += mine
+        tok_indptr.append(tok_indptr[-1] + n)
+        page_indptr.append(page_indptr[-1] + npg)
+        last.append(kv_len - (npg - 1) * ps)
+        o += n
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    q_lens = [n for n, _ in cases]
+    kv_lens = [n + pre for n, pre in cases]
+    work = ops.prefill_work_list(q_lens, kv_lens, "cuda")
+    out = ops.attn_prefill_paged(qkv, pool, dev(tok_indptr), dev(page_ids), dev(page_indptr), dev(last), q_lens,
+                                 q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps, work=work, poly_exp=poly,
+                                 p_in_tmem=ptmem)
+    out2 = ops.attn_prefill_paged(qkv, pool, dev(tok_indptr), dev(page_ids), dev(page_indptr), dev(last), q_lens,
+                                  q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps, poly_exp=poly, p_in_tmem=ptmem)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(out, out2)                  # the work list only changes the order
+    g = qh // kvh
+    o = 0
+    for (n, pre), (k, v) in zip(cases, full):
+        q = qkv[o:o + n, :qh * hd].view(n, qh, hd).float()
+        kk = k.float().repeat_interleave(g, 1)
+        vv = v.float().repeat_interleave(g, 1)
+        s_ = torch.einsum("thd,shd->hts", q, kk) * hd ** -0.5
+        mask = torch.arange(n + pre, device="cuda")[None, :] > (pre + torch.arange(n, device="cuda"))[:, None]
+        s_ = s_.masked_fill(mask[None], float("-inf"))
+        ref = torch.einsum("hts,shd->thd", s_.softmax(-1), vv).reshape(n, qh * hd)
+        assert rel_err(out[o:o + n], ref) < 1e-2, (n, pre, rel_err(out[o:o + n], ref))
+        o += n
+
+
+@pytest.mark.parametrize("ptmem", [False, True])
+def test_attn_prefill_paged_rescales_when_the_maximum_grows(ops, ptmem):
+    """Scores that grow steeply along the sequence force the in-place rescaling of the output rows in tensor memory."""
+    torch.manual_seed(6)
+    qh = kvh = 1
+    hd, ps, n = 128, 64, 512
+    qkv = torch.zeros(n, 3 * hd, device="cuda", dtype=torch.bfloat16)
+    q = torch.zeros(n, hd, device="cuda")
+    k = torch.zeros(n, hd, device="cuda")
+    q[:, 0] = 8.0
+    k[:, 0] = torch.arange(n, device="cuda") * 0.25          # score of key s = 2 s / sqrt(128) * ... grows by far more than 2^8 in all
+    v = torch.randn(n, hd, device="cuda")
+    qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:] = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    pool = torch.zeros(n // ps, 2, ps, 1, hd, device="cuda", dtype=torch.bfloat16)
+    pool[:, 0] = qkv[:, hd:2 * hd].view(n // ps, ps, 1, hd)
+    pool[:, 1] = qkv[:, 2 * hd:].view(n // ps, ps, 1, hd)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    out = ops.attn_prefill_paged(qkv, pool, dev([0, n]), dev(list(range(n // ps))), dev([0, n // ps]), dev([ps]), [n],
+                                 q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps, p_in_tmem=ptmem)
+    torch.cuda.synchronize()
+    ops.check_status()
+    qf, kf, vf = (qkv[:, i * hd:(i + 1) * hd].float() for i in range(3))
+    s_ = (qf @ kf.T) * hd ** -0.5
+    s_ = s_.masked_fill(torch.ones(n, n, device="cuda").triu(1).bool(), float("-inf"))
+    ref = s_.softmax(-1) @ vf
+    assert float((s_.max(-1).values[-1] - s_.max(-1).values[0]) * 1.4427) > 32     # far beyond one rescale threshold
+    assert rel_err(out, ref) < 1e-2, rel_err(out, ref)
+
+
 @pytest.mark.parametrize("qh,kvh,lens", [(4, 2, [128]), (4, 2, [5, 130, 257]), (8, 8, [300, 64, 1]), (32, 8, [700, 33])])
 def test_attn_prefill(ops, qh, kvh, lens):
     hd = 128
