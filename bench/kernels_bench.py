@@ -126,15 +126,9 @@ def bench_prefill_attn(cases, out):
         qkv = torch.randn(B * n, (qh + 2 * kvh) * hd, device="cuda", dtype=torch.bfloat16)
         indptr = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
         o = torch.empty(B * n, qh * hd, device="cuda", dtype=torch.bfloat16)
-        t = timeit(lambda i: ops.attn_prefill(qkv, indptr, [n] * B, q_heads=qh, kv_heads=kvh, head_dim=hd, out=o))
-        ops.check_status()
         fl = 4.0 * B * qh * hd * n * n / 2
-        row = dict(kind="attn_prefill", B=B, n=n, q_heads=qh, kv_heads=kvh, us=t * 1e6, tflops=fl / t / 1e12,
-                   frac_of_gemm_peak=fl / t / flops_peak, peaks=src)
-        out.append(row)
-        print(json.dumps(row), flush=True)
-        # the same attention through the paged pool (two ping-ponged query tiles per CTA, keys and values read from
-        # 64-token pages), with and without the exponentials shared between the special-function unit and the FMA pipe
+        # through the paged pool (two ping-ponged query tiles per CTA, keys and values read from 64-token pages): P in
+        # shared or tensor memory, with and without a share of the exponentials on the FMA pipe
         ps = 64
         npg = n // ps
         pool = torch.randn(B * npg, 2, ps, kvh, hd, device="cuda", dtype=torch.bfloat16)

@@ -2,7 +2,7 @@
 
     python bench/ncu_case.py gemm M N K [epilogue]       # 3 launches of the tcgen05 GEMM
     python bench/ncu_case.py attn_decode B CTX            # 3 launches of the paged decode attention
-    python bench/ncu_case.py attn_prefill B N             # 3 launches of the ragged prefill attention
+    python bench/ncu_case.py attn_prefill_paged B N       # 3 launches of the paged prefill attention (64-token pages)
 """
 import os
 import sys
@@ -35,12 +35,20 @@ def main():
         q = torch.randn(B, qh * hd, device="cuda", dtype=torch.bfloat16)
         for _ in range(3):
             ops.attn_decode(q, kv, idx, indptr, last, q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=page)
-    elif kind == "attn_prefill":
+    elif kind == "attn_prefill_paged":
         B, n = map(int, sys.argv[2:4])
-        qkv = torch.randn(B * n, (32 + 16) * 128, device="cuda", dtype=torch.bfloat16)
+        qh, kvh, hd, ps = 32, 8, 128, 64
+        qkv = torch.randn(B * n, (qh + 2 * kvh) * hd, device="cuda", dtype=torch.bfloat16)
         indptr = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
+        npg = n // ps
+        pool = torch.randn(B * npg, 2, ps, kvh, hd, device="cuda", dtype=torch.bfloat16)
+        ids = torch.randperm(B * npg, device="cuda").to(torch.int32)
+        pindptr = (torch.arange(B + 1, device="cuda") * npg).to(torch.int32)
+        last = torch.full((B,), ps, dtype=torch.int32, device="cuda")
+        work = ops.prefill_work_list([n] * B, [n] * B, "cuda")
         for _ in range(3):
-            ops.attn_prefill(qkv, indptr, [n] * B, q_heads=32, kv_heads=8, head_dim=128)
+            ops.attn_prefill_paged(qkv, pool, indptr, ids, pindptr, last, [n] * B, q_heads=qh, kv_heads=kvh, head_dim=hd,
+                                   page_size=ps, work=work)
     elif kind == "decode_step":
         # two eager decode steps of the full model (no CUDA graph), for a per-kernel launch list of one step:
         #   ncu --metrics gpu__time_duration.sum -k regex:"blitz|gemm|attn|rms|rope|argmax|embedding|sample" ...

@@ -81,6 +81,11 @@ void bind_runtime(py::module_& m) {
       .def("fill_prefill", [](const Batch& b, py::array_t<int32_t, py::array::c_style> h, const MetaLayout& L) {
         if (h.size() < L.total) throw std::invalid_argument("staging array too small");
         return b.fill_prefill(h.mutable_data(), L); })
+      .def("fill_prefill_chunk", [](const Batch& b, py::array_t<int32_t, py::array::c_style> h, const MetaLayout& L,
+                                    int64_t tok0, int max_tokens) {
+        if (h.size() < L.total) throw std::invalid_argument("staging array too small");
+        auto c = b.fill_prefill_chunk(h.mutable_data(), L, tok0, max_tokens);
+        return py::make_tuple(c.tokens, c.pages, c.rows, c.first_seq, c.q_lens, c.kv_lens, c.ended); })
       .def("fill_decode", [](const Batch& b, py::array_t<int32_t, py::array::c_style> h, const MetaLayout& L, int pad_to) {
         if (h.size() < L.total) throw std::invalid_argument("staging array too small");
         return b.fill_decode(h.mutable_data(), L, pad_to); });

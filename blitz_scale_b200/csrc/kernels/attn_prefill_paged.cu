@@ -14,6 +14,7 @@
 //                      fp32, P_t -> smem (16 bit, 128-byte swizzle)
 //   O_t += P_t V       tcgen05.mma accumulating in TMEM over all blocks
 //
+// A ninth warp issues the MMAs (one thread), a tenth the TMA loads.
 // While warpgroup 0 turns S_0 into P_0 the tensor core works on S_1 and on O_1, and the other way round: the
 // two tiles ping-pong, and every K and V block feeds two tiles from one load.  O stays in TMEM for the whole
 // walk: the running maximum a row's probabilities refer to only moves when the true maximum has grown by more
@@ -32,7 +33,7 @@
 
 namespace blitz {
 
-constexpr int kPpThreads = 288;  // warpgroup 0, warpgroup 1, control warp
+constexpr int kPpThreads = 320;  // warpgroup 0, warpgroup 1, MMA warp, load warp
 constexpr int kPpTile = 128;     // q rows per tile and kv tokens per block
 constexpr int kPpPBytes = kPpTile * kPpTile * 2;
 constexpr float kPpRescaleAt = 8.f;  // log2 units
@@ -48,7 +49,15 @@ struct PagedPrefillParams {
   int batch, q_heads, kv_heads, page_size, box_tokens, oob_row;
   float scale_log2;
   int* status;
+  long long* trace;  // profiling aid (null in production): clock stamps of CTA (0, 0), see blitz_attn_prefill_paged_set_trace
 };
+
+constexpr int kPpTraceIters = 32, kPpTraceSlots = 8;
+// role 0 / 1: first lane of warpgroup 0 / 1; role 2: the control warp's first lane
+__device__ __forceinline__ void pp_trace(const PagedPrefillParams& p, int role, int j, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && j < kPpTraceIters)
+    p.trace[(role * kPpTraceIters + j) * kPpTraceSlots + slot] = clock64();
+}
 
 // PTMEM: the probabilities stay in tensor memory (written over the first 64 columns of the scores they came from,
 // two 16-bit values per column) and the P V product takes its A operand from there; the 64 KB of shared memory the
@@ -161,59 +170,31 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   const uint32_t tmem_S = tmem_base;         // S_t at + 128 t
   const uint32_t tmem_O = tmem_base + 256;   // O_t at + HD t
 
-  if (warp == 8) {
-    // ------------------------------------------------------------ control warp: TMA + MMA issue
+  if (warp == 9) {
+    // ------------------------------------------------------------ load warp: Q, then K and V block by block
     // K or V block j -> one tile of 128 token rows: every lane fetches one box (a page, or 64 tokens of one)
-    auto load_kv = [&](uint8_t* dst, uint64_t* bar, int which, int j) {
+    const int bt = p.box_tokens;
+    const bool mine = lane < kPpTile / bt;
+    auto box_row = [&](int j) {  // this lane's first K row of block j (V: + page_size); past the pool = zeros
+      const int tok = j * kPpTile + lane * bt;
+      const int slot = tok / p.page_size;
+      if (!mine || slot >= npages) return p.oob_row;
+      return p.page_indices[pg0 + slot] * 2 * p.page_size + (tok & (p.page_size - 1));
+    };
+    auto load_kv = [&](uint8_t* dst, uint64_t* bar, int row) {
       if (lane == 0) ptx::mbar_expect_tx(bar, TB);
       __syncwarp();
-      const int bt = p.box_tokens;
-      if (lane < kPpTile / bt) {
-        const int tok = j * kPpTile + lane * bt;
-        const int slot = tok / p.page_size;
-        int row = p.oob_row;  // past the pool: the box arrives as zeros
-        if (slot < npages) row = (p.page_indices[pg0 + slot] * 2 + which) * p.page_size + (tok & (p.page_size - 1));
+      if (mine) {
 #pragma unroll
         for (int s = 0; s < C::kSlabs; ++s)
           ptx::tma_load_3d(dst + s * (TB / C::kSlabs) + lane * bt * 128, &tmap_kv, bar, s * 64, kv_head, row);
       }
     };
-    auto issue_S = [&](int t, int stage) {
-      const uint32_t a = ptx::smem_u32(sQ + t * TB), bb = ptx::smem_u32(sK + stage * TB);
-#pragma unroll
-      for (int k = 0; k < HD / 16; ++k) {
-        const uint32_t off = (k >> 2) * (TB / C::kSlabs) + (k & 3) * 32;
-        ptx::umma_f16_ss(tmem_S + t * 128, ptx::make_smem_desc(a + off, 16, 1024, ptx::kLayoutSw128),
-                         ptx::make_smem_desc(bb + off, 16, 1024, ptx::kLayoutSw128), kIdescS, k != 0 ? 1u : 0u);
-      }
-      ptx::umma_commit(&s_full[t]);
-    };
-    auto issue_PV = [&](int t, int stage, bool accumulate) {
-      const uint32_t a = ptx::smem_u32(sP + t * kPpPBytes), bb = ptx::smem_u32(sV + stage * TB);
-#pragma unroll
-      for (int k = 0; k < kPpTile / 16; ++k) {
-        // B = V: N-major, slabs of 64 head-dim columns; 16 tokens (K) advance 2 KB.
-        const uint64_t bdesc = ptx::make_smem_desc(bb + k * 2048, TB / C::kSlabs, 1024, ptx::kLayoutSw128);
-        if (PTMEM) {
-          // A = P in tensor memory: row = lane, 16 tokens = 8 columns
-          ptx::umma_f16_ts(tmem_O + t * HD, tmem_S + t * 128 + k * 8, bdesc, kIdescPV, (accumulate || k != 0) ? 1u : 0u);
-        } else {
-          // A = P in shared memory: K-major, two slabs of 64 tokens
-          const uint32_t aoff = (k >> 2) * (kPpPBytes / 2) + (k & 3) * 32;
-          ptx::umma_f16_ss(tmem_O + t * HD, ptx::make_smem_desc(a + aoff, 16, 1024, ptx::kLayoutSw128), bdesc, kIdescPV,
-                           (accumulate || k != 0) ? 1u : 0u);
-        }
-      }
-      ptx::umma_commit(&o_full[t]);
-    };
-    // waits are done by lane 0 and their outcome shared, so that the whole warp stays together for the loads
     auto wait = [&](uint64_t* bar, uint32_t parity) {
       int ok = 1;
       if (lane == 0) ok = ptx::bounded_mbar_wait(bar, parity, abort_flag) ? 1 : 0;
       return __shfl_sync(0xffffffffu, ok, 0) != 0;
     };
-
-    bool ok = true;
     if (lane == 0) {
       ptx::mbar_expect_tx(q_full, nt * TB);
       for (int t = 0; t < nt; ++t)
@@ -222,62 +203,89 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           ptx::tma_load_2d(sQ + t * TB + s * (TB / C::kSlabs), &tmap_q, q_full, head * HD + s * 64,
                            seq_start + q0 + t * kPpTile);
     }
-    load_kv(sK, &k_full[0], 0, 0);
-    load_kv(sV, &v_full[0], 1, 0);
-    if (nblk > 1) load_kv(sK + TB, &k_full[1], 0, 1);
-    if (NV == 2 && nblk > 1) load_kv(sV + TB, &v_full[1], 1, 1);
-    ok = wait(q_full, 0) && wait(&k_full[0], 0);
-    if (ok && lane == 0) {
-      ptx::tc_fence_after_sync();
-      for (int t = 0; t < nt; ++t)
-        if (nblk_t[t] > 0) issue_S(t, 0);
-      ptx::umma_commit(&k_empty[0]);
-    }
+    bool ok = true;
+    int row = box_row(0);
     for (int j = 0; j < nblk && ok; ++j) {
-      const int vs = j % NV;
-      // K of block j + 2 goes where block j's was, once the S products of block j (issued a block ago) are done
-      if (j + 2 < nblk) {
-        ok = wait(&k_empty[j & 1], (j >> 1) & 1);
-        if (!ok) break;
-        load_kv(sK + (j & 1) * TB, &k_full[j & 1], 0, j + 2);
-      }
-      if (NV == 2 && j >= 1 && j + 1 < nblk) {
-        ok = wait(&v_empty[(j + 1) & 1], ((j - 1) >> 1) & 1);
-        if (!ok) break;
-        load_kv(sV + ((j + 1) & 1) * TB, &v_full[(j + 1) & 1], 1, j + 1);
-      }
-      bool v_here = false, k_next = false;
-      for (int t = 0; t < nt && ok; ++t) {
-        if (j >= nblk_t[t]) continue;
-        ok = wait(&p_ready[t], j & 1);  // P_t of block j is in smem; S_t and (after a rescale) O_t are settled
-        if (ok && !v_here) {
-          ok = wait(&v_full[vs], (j / NV) & 1);
-          v_here = true;
+      const int row_next = j + 1 < nblk ? box_row(j + 1) : p.oob_row;  // looked up a block ahead of its use
+      // K of block j goes where block j - 2's was, once the S products of that block are done; V likewise
+      if (j >= 2) ok = wait(&k_empty[j & 1], ((j - 2) >> 1) & 1);
+      if (!ok) break;
+      load_kv(sK + (j & 1) * TB, &k_full[j & 1], row);
+      if (j >= NV) ok = wait(&v_empty[j % NV], ((j - NV) / NV) & 1);
+      if (!ok) break;
+      load_kv(sV + (j % NV) * TB, &v_full[j % NV], row == p.oob_row ? row : row + p.page_size);
+      row = row_next;
+    }
+    if (!ok && lane == 0 && p.status) atomicCAS(p.status, 0, kStatusTimeoutProducer);
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ MMA warp: one thread issues
+    if (lane == 0) {
+      auto issue_S = [&](int t, int stage) {
+        const uint32_t a = ptx::smem_u32(sQ + t * TB), bb = ptx::smem_u32(sK + stage * TB);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * (TB / C::kSlabs) + (k & 3) * 32;
+          ptx::umma_f16_ss(tmem_S + t * 128, ptx::make_smem_desc(a + off, 16, 1024, ptx::kLayoutSw128),
+                           ptx::make_smem_desc(bb + off, 16, 1024, ptx::kLayoutSw128), kIdescS, k != 0 ? 1u : 0u);
         }
-        if (!ok) break;
-        if (j + 1 < nblk_t[t] && !k_next) {
-          ok = wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
-          k_next = true;
+        ptx::umma_commit(&s_full[t]);
+      };
+      auto issue_PV = [&](int t, int stage, bool accumulate) {
+        const uint32_t a = ptx::smem_u32(sP + t * kPpPBytes), bb = ptx::smem_u32(sV + stage * TB);
+#pragma unroll
+        for (int k = 0; k < kPpTile / 16; ++k) {
+          // B = V: N-major, slabs of 64 head-dim columns; 16 tokens (K) advance 2 KB.
+          const uint64_t bdesc = ptx::make_smem_desc(bb + k * 2048, TB / C::kSlabs, 1024, ptx::kLayoutSw128);
+          if (PTMEM) {
+            // A = P in tensor memory: row = lane, 16 tokens = 8 columns
+            ptx::umma_f16_ts(tmem_O + t * HD, tmem_S + t * 128 + k * 8, bdesc, kIdescPV,
+                             (accumulate || k != 0) ? 1u : 0u);
+          } else {
+            // A = P in shared memory: K-major, two slabs of 64 tokens
+            const uint32_t aoff = (k >> 2) * (kPpPBytes / 2) + (k & 3) * 32;
+            ptx::umma_f16_ss(tmem_O + t * HD, ptx::make_smem_desc(a + aoff, 16, 1024, ptx::kLayoutSw128), bdesc,
+                             kIdescPV, (accumulate || k != 0) ? 1u : 0u);
+          }
+        }
+        ptx::umma_commit(&o_full[t]);
+      };
+      auto wait = [&](uint64_t* bar, uint32_t parity) { return ptx::bounded_mbar_wait(bar, parity, abort_flag); };
+      bool ok = wait(q_full, 0) && wait(&k_full[0], 0);
+      if (ok) {
+        ptx::tc_fence_after_sync();
+        for (int t = 0; t < nt; ++t)
+          if (nblk_t[t] > 0) issue_S(t, 0);
+        ptx::umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int vs = j % NV;
+        pp_trace(p, 2, j, 0);
+        bool v_here = false, k_next = false;
+        for (int t = 0; t < nt && ok; ++t) {
+          if (j >= nblk_t[t]) continue;
+          ok = wait(&p_ready[t], j & 1);  // P_t of block j is written; S_t and (after a rescale) O_t are settled
+          pp_trace(p, 2, j, 2 + 2 * t);
+          if (ok && !v_here) {
+            ok = wait(&v_full[vs], (j / NV) & 1);
+            v_here = true;
+          }
           if (!ok) break;
-        }
-        if (lane == 0) {
+          if (j + 1 < nblk_t[t] && !k_next) {
+            ok = wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
+            k_next = true;
+            if (!ok) break;
+          }
           ptx::tc_fence_after_sync();
           issue_PV(t, vs, j > 0);
           if (j + 1 < nblk_t[t]) issue_S(t, (j + 1) & 1);
+          pp_trace(p, 2, j, 3 + 2 * t);
         }
-      }
-      if (!ok) break;
-      if (lane == 0) {
+        if (!ok) break;
         if (k_next) ptx::umma_commit(&k_empty[(j + 1) & 1]);
         ptx::umma_commit(&v_empty[vs]);
       }
-      if (NV == 1 && j + 1 < nblk) {
-        ok = wait(&v_empty[0], j & 1);
-        if (!ok) break;
-        load_kv(sV, &v_full[0], 1, j + 1);
-      }
+      if (!ok && p.status) atomicCAS(p.status, 0, kStatusTimeoutMma);
     }
-    if (!ok && lane == 0 && p.status) atomicCAS(p.status, 0, kStatusTimeoutMma);
   } else {
     // ------------------------------------------------------------ softmax warpgroups (thread = query row)
     const int t = warp >> 2;
@@ -291,11 +299,14 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     float m_ref = 0.f, l = 0.f;
     bool ok = true;
     const int my_blocks = nblk_t[t];
+    const bool tracer = (warp & 3) == 0 && lane == 0;
     for (int j = 0; j < my_blocks; ++j) {
+      if (tracer) pp_trace(p, t, j, 0);
       if (!ptx::bounded_mbar_wait(&s_full[t], j & 1, abort_flag)) {
         ok = false;
         break;
       }
+      if (tracer) pp_trace(p, t, j, 1);
       ptx::tc_fence_after_sync();
       uint32_t v0[32], v1[32], v2[32], v3[32];  // the row's 128 scores (fp32 bits)
       ptx::tmem_ld_32x32(tS, v0);
@@ -303,6 +314,7 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       ptx::tmem_ld_32x32(tS + 64, v2);
       ptx::tmem_ld_32x32(tS + 96, v3);
       ptx::tmem_ld_wait();
+      if (tracer) pp_trace(p, t, j, 2);
       auto score = [&](int i) -> uint32_t& { return i < 32 ? v0[i] : i < 64 ? v1[i - 32] : i < 96 ? v2[i - 64] : v3[i - 96]; };
       const int kv0 = j * kPpTile;
       if (kv0 + kPpTile - 1 > prefix + q0 + t * kPpTile) {  // the block reaches past the tile's first row: mask
@@ -310,9 +322,20 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         for (int i = 0; i < kPpTile; ++i)
           if (kv0 + i > limit) score(i) = 0xff800000u;  // -inf
       }
-      float mx = -INFINITY;
+      // eight independent chains of three-input maxima: with two softmax warps per scheduler nothing else hides a
+      // serial one
+      float mxs[8];
 #pragma unroll
-      for (int i = 0; i < kPpTile; ++i) mx = fmaxf(mx, __uint_as_float(score(i)));
+      for (int i = 0; i < 8; ++i) mxs[i] = __uint_as_float(score(i));
+#pragma unroll
+      for (int i = 8; i < kPpTile - 8; i += 16)
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mxs[k] = ptx::fmax3(mxs[k], __uint_as_float(score(i + 2 * k)), __uint_as_float(score(i + 2 * k + 1)));
+#pragma unroll
+      for (int i = kPpTile - 8; i < kPpTile; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(score(i)));
+      float mx = fmaxf(ptx::fmax3(mxs[0], mxs[1], mxs[2]), ptx::fmax3(mxs[3], mxs[4], mxs[5]));
+      mx = ptx::fmax3(mx, mxs[6], mxs[7]);
       mx *= p.scale_log2;
       // the previous block's P V must have been read out of P's buffer (and into O) before either is touched
       if (j > 0 && !ptx::bounded_mbar_wait(&o_full[t], (j - 1) & 1, abort_flag)) {
@@ -340,8 +363,9 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           if (grow) m_ref = mx;
         }
       }
+      if (tracer) pp_trace(p, t, j, 3);
       // probabilities (16 bit) -> tensor memory over the scores, or shared memory in 128-byte swizzled rows; row sum
-      float rowsum = 0.f;
+      float rs[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = -m_ref;
       if (PTMEM) {
 #pragma unroll
@@ -354,11 +378,12 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             const float x1 = fmaf(__uint_as_float(score(c + 1)), p.scale_log2, neg_m);
             const float e0 = ptx::ex2_approx(x0);
             const float e1 = (POLY && (i & 1)) ? ptx::ex2_poly(x1) : ptx::ex2_approx(x1);
-            rowsum += e0 + e1;
+            rs[i & 3] += e0 + e1;
             pk[i] = pk2<T>(e0, e1);
           }
           ptx::tmem_st_32x32(tS + h * 32, pk);
         }
+        if (tracer) pp_trace(p, t, j, 4);
         ptx::tmem_st_wait();
       } else {
 #pragma unroll
@@ -368,7 +393,7 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           for (int i = 0; i < 8; ++i) {
             const float x = fmaf(__uint_as_float(score(c + i)), p.scale_log2, neg_m);
             e[i] = (POLY && (i & 3) == 3) ? ptx::ex2_poly(x) : ptx::ex2_approx(x);
-            rowsum += e[i];
+            rs[i & 3] += e[i];
           }
           const int chunk = c >> 3;  // 16-byte chunk along the token axis: 0..15
           const uint32_t off = (chunk >> 3) * (kPpPBytes / 2) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
@@ -377,9 +402,10 @@ attn_prefill_paged_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         }
         ptx::fence_proxy_async_smem();
       }
-      l += rowsum;
+      l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&p_ready[t]);
+      if (tracer) pp_trace(p, t, j, 5);
     }
     if (ok && my_blocks > 0) ok = ptx::bounded_mbar_wait(&o_full[t], (my_blocks - 1) & 1, abort_flag);
     if (!ok) {
@@ -431,8 +457,16 @@ static int launch_paged_prefill(const CUtensorMap& tq, const CUtensorMap& tkv, c
 
 }  // namespace blitz
 
+namespace blitz {
+static long long* g_pp_trace = nullptr;
+}
+
 extern "C" {
 using namespace blitz;
+
+// Profiling aid: while `buf` (3 roles x 32 iterations x 8 int64 clock stamps, device memory) is set, the CTA at grid
+// position (0, 0) of every following launch records when its warpgroups and its control warp pass each phase.
+void blitz_attn_prefill_paged_set_trace(long long* buf) { blitz::g_pp_trace = buf; }
 
 // qkv: [num_tokens, (q_heads + 2 kv_heads) * head_dim] of the current chunk, rotated in place; kv_layer: the
 // layer's pool [max_pages][2][page_size][kv_heads][head_dim], which already holds the chunk's keys and values;
@@ -461,7 +495,7 @@ int blitz_attn_prefill_paged(const void* qkv, const void* kv_layer, void* out, i
   p.page_indptr = page_indptr; p.last_page_len = last_page_len; p.work = work; p.batch = batch;
   p.q_heads = q_heads; p.kv_heads = kv_heads; p.page_size = page_size; p.box_tokens = bt;
   p.oob_row = max_pages * 2 * page_size;
-  p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
+  p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status; p.trace = g_pp_trace;
   dim3 grid(q_heads, total_pairs);
   const bool poly = (flags & 1) != 0, ptmem = (flags & 2) != 0;
 #define BLITZ_PP_LAUNCH(T, HD)                                                                            \

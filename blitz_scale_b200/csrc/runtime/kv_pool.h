@@ -348,6 +348,48 @@ class Batch {
     }
     return {t, np};
   }
+  // Prefill in chunks, for prompts that together exceed what one forward pass takes: the window [tok0, tok0 +
+  // max_tokens) over the prompts laid end to end.  Only the sequences the window touches get a row; a row's tokens
+  // are the part of its prompt inside the window (positions continue where the previous chunk stopped) while its
+  // page list covers everything up to the end of that part, i.e. the keys and values of earlier chunks too.
+  struct PrefillChunk {
+    int tokens = 0, pages = 0, rows = 0, first_seq = -1;
+    std::vector<int> q_lens, kv_lens;  // per row: tokens in this chunk, tokens cached after it
+    std::vector<int> ended;            // per row: 1 if the prompt ends in this chunk (its last row yields the first token)
+  };
+  PrefillChunk fill_prefill_chunk(int32_t* h, const MetaLayout& L, int64_t tok0, int max_tokens) const {
+    const int ps = pool_->page_size();
+    PrefillChunk c;
+    int64_t base = 0;
+    h[L.tok_indptr] = 0;
+    h[L.page_indptr] = 0;
+    for (size_t b = 0; b < seqs_.size(); ++b) {
+      const auto& s = seqs_[b];
+      const int64_t n = static_cast<int64_t>(s.spec.prompt.size());
+      const int64_t lo = std::max<int64_t>(tok0, base) - base, hi = std::min<int64_t>(tok0 + max_tokens, base + n) - base;
+      base += n;
+      if (hi <= lo) continue;
+      if (c.first_seq < 0) c.first_seq = static_cast<int>(b);
+      for (int64_t i = lo; i < hi; ++i) {
+        const int t = c.tokens + static_cast<int>(i - lo);
+        h[L.ids + t] = s.spec.prompt[i];
+        h[L.pos + t] = static_cast<int32_t>(i);
+        h[L.slot + t] = s.pages[i / ps] * ps + static_cast<int32_t>(i % ps);
+      }
+      c.tokens += static_cast<int>(hi - lo);
+      const int used = static_cast<int>((hi + ps - 1) / ps);
+      for (int i = 0; i < used; ++i) h[L.page_indices + c.pages + i] = s.pages[i];
+      c.pages += used;
+      h[L.tok_indptr + c.rows + 1] = c.tokens;
+      h[L.page_indptr + c.rows + 1] = c.pages;
+      h[L.last_page_len + c.rows] = static_cast<int32_t>(hi - static_cast<int64_t>(used - 1) * ps);
+      c.q_lens.push_back(static_cast<int>(hi - lo));
+      c.kv_lens.push_back(static_cast<int>(hi));
+      c.ended.push_back(hi == n ? 1 : 0);
+      c.rows += 1;
+    }
+    return c;
+  }
   // Decode: feed each request's last token at position total_len - 1; padded rows (b >= size) are
   // empty sequences whose cache write is skipped.  Returns the number of page entries.
   int fill_decode(int32_t* h, const MetaLayout& L, int pad_to) const {

@@ -39,7 +39,9 @@ class StepMeta:
     page_indptr: torch.Tensor    # [B + 1]
     last_page_len: torch.Tensor  # [B]
     tok_indptr: Optional[torch.Tensor] = None  # [B + 1] token offsets (prefill)
-    seq_lens_host: List[int] = field(default_factory=list)  # prompt lengths (prefill)
+    seq_lens_host: List[int] = field(default_factory=list)  # rows per sequence in this pass (prefill)
+    kv_lens_host: List[int] = field(default_factory=list)   # tokens cached per sequence after this pass (prefill)
+    prefill_work: Optional[torch.Tensor] = None             # CTA order of the prefill attention (heaviest first)
     is_prefill: bool = False
     batch: int = 0
     num_tokens: int = 0
@@ -122,8 +124,7 @@ class LlamaRunner:
         ops.rope_kv_store(self.qkv[:T], m.pos[:T], m.slot[:T], self.kv[l], q_heads=self.qh, kv_heads=self.kvh,
                           head_dim=self.hd, page_size=self.page_size, rope_theta=c.rope_theta)
         if m.is_prefill:
-            ops.attn_prefill(self.qkv[:T], m.tok_indptr, m.seq_lens_host, q_heads=self.qh, kv_heads=self.kvh,
-                             head_dim=self.hd, out=self.attn[:T])
+            self._prefill_attention(l, m)
         else:
             ops.attn_decode(self.qkv[:T], self.kv[l], m.page_indices, m.page_indptr, m.last_page_len,
                             q_heads=self.qh, kv_heads=self.kvh, head_dim=self.hd, page_size=self.page_size,
@@ -134,6 +135,26 @@ class LlamaRunner:
         else:
             ops.gemm(self.attn[:T], self._w(l, "o"), static_b=True, out=self.tmp[:T])
             self.comm.all_reduce_(self.tmp[:T])
+
+    def _prefill_attention(self, l: int, m: StepMeta) -> None:
+        """The pass's rows against everything the cache holds for their sequences (rope_kv_store has just added the
+        rows' own keys and values): earlier chunks of a long prompt are simply a longer page list."""
+        T = m.num_tokens
+        ops.attn_prefill_paged(self.qkv[:T], self.kv[l], m.tok_indptr, m.page_indices, m.page_indptr, m.last_page_len,
+                               m.seq_lens_host, q_heads=self.qh, kv_heads=self.kvh, head_dim=self.hd,
+                               page_size=self.page_size, out=self.attn[:T], work=m.prefill_work)
+
+    def last_rows(self, m: StepMeta) -> torch.Tensor:
+        """[batch, hidden]: the state `head` starts from, for the last row of every sequence of a prefill pass."""
+        ops.gather_last(self.res[:m.num_tokens], m.tok_indptr, out=self.last[:m.batch])
+        return self.last[:m.batch]
+
+    def head_from_rows(self, rows: torch.Tensor) -> torch.Tensor:
+        """First tokens from states collected with `last_rows` over several passes (a prompt prefetched in chunks)."""
+        B = rows.shape[0]
+        self.res[:B].copy_(rows)
+        return self.head(StepMeta(ids=None, pos=None, slot=None, page_indices=None, page_indptr=None, last_page_len=None,
+                                  is_prefill=False, batch=B, num_tokens=B))
 
     def ffn_block(self, l: int, m: StepMeta) -> None:
         T, c = m.num_tokens, self.cfg

@@ -318,18 +318,3 @@ def attn_prefill_paged(qkv: torch.Tensor, kv_layer: torch.Tensor, tok_indptr: to
                                           _p(status_word(qkv.device)), _dt(qkv),
                                           _stream()), "blitz_attn_prefill_paged")
     return out
-
-
-def attn_prefill(qkv: torch.Tensor, indptr_dev: torch.Tensor, seq_lens_host, *, q_heads: int, kv_heads: int,
-                 head_dim: int, out: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None) -> torch.Tensor:
-    """Causal attention of each prompt over itself. ``qkv`` must already be rotated (rope_kv_store)."""
-    T = qkv.shape[0]
-    if out is None:
-        out = torch.empty((T, q_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    tiles = sum((int(n) + 127) // 128 for n in seq_lens_host)
-    if sm_scale is None:
-        sm_scale = head_dim ** -0.5
-    _check(lib().blitz_attn_prefill(_p(qkv), _p(out), out.stride(0), _p(indptr_dev), len(seq_lens_host), T, tiles,
-                                    q_heads, kv_heads, head_dim, sm_scale, _p(status_word(qkv.device)), _dt(qkv),
-                                    _stream()), "blitz_attn_prefill")
-    return out

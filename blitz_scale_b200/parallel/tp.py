@@ -360,8 +360,7 @@ class LlamaRunnerTP(LlamaRunner):
             ops.rope_kv_store(self.qkv[:T], m.pos[:T], m.slot[:T], self.kv[l], q_heads=self.qh, kv_heads=self.kvh,
                               head_dim=self.hd, page_size=self.page_size, rope_theta=c.rope_theta)
             if m.is_prefill:
-                ops.attn_prefill(self.qkv[:T], m.tok_indptr, m.seq_lens_host, q_heads=self.qh, kv_heads=self.kvh,
-                                 head_dim=self.hd, out=self.attn[:T])
+                self._prefill_attention(l, m)
             else:
                 ops.attn_decode(self.qkv[:T], self.kv[l], m.page_indices, m.page_indptr, m.last_page_len,
                                 q_heads=self.qh, kv_heads=self.kvh, head_dim=self.hd, page_size=self.page_size,
@@ -379,8 +378,7 @@ class LlamaRunnerTP(LlamaRunner):
         ops.rope_kv_store(self.qkv[:T], m.pos[:T], m.slot[:T], self.kv[l], q_heads=self.qh, kv_heads=self.kvh,
                           head_dim=self.hd, page_size=self.page_size, rope_theta=c.rope_theta)
         if m.is_prefill:
-            ops.attn_prefill(self.qkv[:T], m.tok_indptr, m.seq_lens_host, q_heads=self.qh, kv_heads=self.kvh,
-                             head_dim=self.hd, out=self.attn[:T])
+            self._prefill_attention(l, m)
         else:
             ops.attn_decode(self.qkv[:T], self.kv[l], m.page_indices, m.page_indptr, m.last_page_len,
                             q_heads=self.qh, kv_heads=self.kvh, head_dim=self.hd, page_size=self.page_size,
@@ -431,6 +429,23 @@ class LlamaRunnerTP(LlamaRunner):
             src = xn[:B]
         ops.gemm(src, self.seg["lm_head"], static_b=True, out=self.logits[:B])
         return self._pick_tokens(B)
+
+    def last_rows(self, m: StepMeta) -> torch.Tensor:
+        if not self._switch(m):
+            raise NotImplementedError("a prompt prefetched in chunks runs on the switch-reduced path at tp > 1")
+        # already normalised with the final norm's weight (see ffn_block)
+        ops.gather_last(self.fused.xn(m.num_tokens), m.tok_indptr, out=self.last[:m.batch])
+        return self.last[:m.batch]
+
+    def head_from_rows(self, rows: torch.Tensor) -> torch.Tensor:
+        B = rows.shape[0]
+        self.fused.xn(B).copy_(rows)
+        saved, self.force_switch = self.force_switch, True
+        try:
+            return self.head(StepMeta(ids=None, pos=None, slot=None, page_indices=None, page_indptr=None,
+                                      last_page_len=None, is_prefill=False, batch=B, num_tokens=B))
+        finally:
+            self.force_switch = saved
 
     def _pick_tokens(self, B: int) -> torch.Tensor:
         """Arg-max over the vocabulary shards: every rank's (value, index) candidates travel by peer stores."""

@@ -86,9 +86,14 @@ class Engine:
         self.launches_per_decode_step = 0
 
     # ------------------------------------------------------------------ meta views
-    def _views(self, T: int, B: int, P: int, prefill: bool, seq_lens: Sequence[int] = (), splits: int = 1) -> StepMeta:
+    def _views(self, T: int, B: int, P: int, prefill: bool, seq_lens: Sequence[int] = (), splits: int = 1,
+               kv_lens: Sequence[int] = (), work: Optional[torch.Tensor] = None) -> StepMeta:
         L, d = self.layout, self.dev
-        return StepMeta(ids=d[L.ids:L.ids + T], pos=d[L.pos:L.pos + T], slot=d[L.slot:L.slot + T],
+        kv_lens = list(kv_lens) if kv_lens else list(seq_lens)
+        if prefill and work is None:
+            work = ops.prefill_work_list(seq_lens, kv_lens, self.device)
+        return StepMeta(kv_lens_host=kv_lens, prefill_work=work,
+                        ids=d[L.ids:L.ids + T], pos=d[L.pos:L.pos + T], slot=d[L.slot:L.slot + T],
                         page_indices=d[L.page_indices:L.page_indices + max(P, 1)],
                         page_indptr=d[L.page_indptr:L.page_indptr + B + 1],
                         last_page_len=d[L.last_page_len:L.last_page_len + B],
@@ -131,9 +136,15 @@ class Engine:
             raise RuntimeError("model parameters are not loaded")
         if batch.size > self.max_batch:
             raise ValueError(f"prefill batch of {batch.size} sequences exceeds max_batch={self.max_batch}")
+        if batch.num_prompt_tokens() > self.max_batch_tokens:
+            toks = self._prefill_in_chunks(batch)
+            toks = self._sample_rows(batch, batch.size, toks)
+            out = self._tokens_to_host(toks, batch.size)
+            batch.mark_prefilled()
+            batch.append_tokens(out, False)
+            batch.decode = True
+            return out
         T, P = batch.fill_prefill(self.host_np, self.layout)
-        if T > self.max_batch_tokens:
-            raise ValueError(f"prefill of {T} tokens exceeds max_batch_tokens={self.max_batch_tokens}")
         self._h2d(self.layout.page_indices + P)
         lens = batch.prompt_lens()
         m = self._views(T, batch.size, P, True, lens)
@@ -145,6 +156,40 @@ class Engine:
         batch.append_tokens(out, False)
         batch.decode = True
         return out
+
+    def _prefill_in_chunks(self, batch: "core.Batch") -> torch.Tensor:
+        """Prompts that together exceed `max_batch_tokens` (one prompt alone may): passes over windows of that many
+        tokens of the prompts laid end to end.  A window's rows attend to the cache, which holds what earlier windows
+        stored for the same sequence; the state of every sequence's last token is kept when its prompt ends, and the
+        head runs once over all of them.  The reference stops packing at the token budget and cannot split a prompt
+        (router_v2/src/queue.rs:279-286)."""
+        total, B = batch.num_prompt_tokens(), batch.size
+        runner = self.runner
+        forced = getattr(runner, "force_switch", None)
+        if forced is not None:
+            runner.force_switch = True          # tensor parallel: keep the residual stream replicated in every pass
+        try:
+            states = torch.empty(B, self.cfg.hidden, dtype=self.dtype, device=self.device)
+            tok0 = 0
+            while tok0 < total:
+                T, P, rows, s0, q_lens, kv_lens, ended = batch.fill_prefill_chunk(self.host_np, self.layout, tok0,
+                                                                                  self.max_batch_tokens)
+                self._h2d(self.layout.page_indices + P)
+                m = self._views(T, rows, P, True, q_lens, kv_lens=kv_lens)
+                with nvtx_range("prefill_chunk"):
+                    runner.forward(m, with_head=False)
+                    if any(ended):
+                        last = runner.last_rows(m)
+                        for r, e in enumerate(ended):
+                            if e:
+                                states[s0 + r].copy_(last[r])
+                # the staging arrays are reused by the next window
+                torch.cuda.current_stream().synchronize()
+                tok0 += T
+            return runner.head_from_rows(states)
+        finally:
+            if forced is not None:
+                runner.force_switch = forced
 
     @torch.no_grad()
     def decode(self, batch: "core.Batch") -> List[int]:

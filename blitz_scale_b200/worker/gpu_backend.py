@@ -357,7 +357,8 @@ class GpuBackend(Backend):
             task["meta"] = (T, P, dev_copy)
         T, P, dev_copy = task["meta"]
         eng.dev[:dev_copy.numel()].copy_(dev_copy)
-        m = eng._views(T, b.size, P, True, b.prompt_lens())
+        m = eng._views(T, b.size, P, True, b.prompt_lens(), work=task.get("work"))
+        task["work"] = m.prefill_work          # the attention's CTA order is the same for every step of the task
         saved = eng.runner.res
         fused = eng.fused
         if fused is not None:

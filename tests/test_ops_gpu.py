@@ -434,25 +434,3 @@ def test_attn_prefill_paged_rescales_when_the_maximum_grows(ops, ptmem):
     ref = s_.softmax(-1) @ vf
     assert float((s_.max(-1).values[-1] - s_.max(-1).values[0]) * 1.4427) > 32     # far beyond one rescale threshold
     assert rel_err(out, ref) < 1e-2, rel_err(out, ref)
-
-
-@pytest.mark.parametrize("qh,kvh,lens", [(4, 2, [128]), (4, 2, [5, 130, 257]), (8, 8, [300, 64, 1]), (32, 8, [700, 33])])
-def test_attn_prefill(ops, qh, kvh, lens):
-    hd = 128
-    torch.manual_seed(9)
-    T = sum(lens)
-    qkv = torch.randn(T, (qh + 2 * kvh) * hd, device="cuda", dtype=DT)
-    import itertools
-    indptr = torch.tensor([0] + list(itertools.accumulate(lens)), dtype=torch.int32, device="cuda")
-    out = ops.attn_prefill(qkv, indptr, lens, q_heads=qh, kv_heads=kvh, head_dim=hd)
-    g = qh // kvh
-    o = 0
-    for n in lens:
-        q = qkv[o:o + n, :qh * hd].view(n, qh, hd).float()
-        k = qkv[o:o + n, qh * hd:(qh + kvh) * hd].view(n, kvh, hd).float().repeat_interleave(g, 1)
-        v = qkv[o:o + n, (qh + kvh) * hd:].view(n, kvh, hd).float().repeat_interleave(g, 1)
-        s = torch.einsum("thd,shd->hts", q, k) * hd ** -0.5
-        s = s.masked_fill(torch.ones(n, n, device="cuda").triu(1).bool()[None], float("-inf"))
-        ref = torch.einsum("hts,shd->thd", s.softmax(-1), v).reshape(n, qh * hd)
-        assert rel_err(out[o:o + n], ref) < 1e-2, (n, rel_err(out[o:o + n], ref))
-        o += n

@@ -171,6 +171,48 @@ def test_batch_metadata_for_prefill_and_decode():
     assert pool.used_pages == 0
 
 
+def test_prefill_in_chunks_covers_every_token_once_with_growing_page_lists():
+    """Windows over the prompts laid end to end: the rows of all windows are exactly the prompts, positions continue
+    across windows, and a row's page list reaches to the end of what the window adds for its sequence."""
+    ps = 16
+    pool = core.PagePool(64, ps)
+    b = core.Batch(3, pool)
+    lens = [5, 70, 33, 1]
+    assert b.add_prompts([core.SeqSpec(i, list(range(1000 * i, 1000 * i + n)), 4) for i, n in enumerate(lens)])
+    pages = [list(s.pages) for s in b.seqs]
+    L = core.MetaLayout.make(32, 4, 64)
+    h = np.full(L.total, -7, dtype=np.int32)
+    seen = {i: [] for i in range(len(lens))}
+    tok0, windows, ended_at = 0, 0, {}
+    while tok0 < sum(lens):
+        T, P, rows, s0, q_lens, kv_lens, ended = b.fill_prefill_chunk(h, L, tok0, 32)
+        assert 0 < T <= 32 and rows == len(q_lens) == len(kv_lens) == len(ended) and sum(q_lens) == T
+        assert list(h[L.tok_indptr:L.tok_indptr + rows + 1]) == [0] + list(np.cumsum(q_lens))
+        off = pg = 0
+        for r in range(rows):
+            sq = s0 + r
+            n, kv = q_lens[r], kv_lens[r]
+            ids = list(h[L.ids + off:L.ids + off + n])
+            pos = list(h[L.pos + off:L.pos + off + n])
+            assert pos == list(range(kv - n, kv)) and ids == [1000 * sq + x for x in pos]
+            assert list(h[L.slot + off:L.slot + off + n]) == [pages[sq][x // ps] * ps + x % ps for x in pos]
+            used = (kv + ps - 1) // ps
+            assert list(h[L.page_indices + pg:L.page_indices + pg + used]) == pages[sq][:used]
+            assert h[L.page_indptr + r + 1] == pg + used and h[L.last_page_len + r] == kv - (used - 1) * ps
+            seen[sq] += pos
+            if ended[r]:
+                assert kv == lens[sq]
+                ended_at[sq] = windows
+            off += n
+            pg += used
+        assert P == pg
+        tok0 += T
+        windows += 1
+    assert windows == 4 and all(seen[i] == list(range(n)) for i, n in enumerate(lens))
+    assert ended_at == {0: 0, 1: 2, 2: 3, 3: 3}
+    b.clear()
+
+
 def test_batch_admission_is_all_or_nothing_and_eos_stops():
     pool = core.PagePool(4, 16)
     b = core.Batch(1, pool)
