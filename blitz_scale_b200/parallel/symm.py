@@ -57,6 +57,8 @@ class SymmRegion:
         self.rank = self.handle.rank
         self.world = self.handle.world_size
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        # the region may live on a sub-group (one tensor-parallel shard column): callers name ranks of the whole job
+        self.job_ranks: List[int] = list(dist.get_process_group_ranks(self.group))
         mc = 0
         try:
             if self.handle.has_multicast_support(dev.type, dev.index):
@@ -64,6 +66,10 @@ class SymmRegion:
         except Exception:
             mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.mc_ptr = mc
+
+    def ptr_of(self, job_rank: int) -> int:
+        """Address of `job_rank`'s copy (a rank of the whole job, which must belong to this region's group)."""
+        return self.ptrs[self.job_ranks.index(job_rank)]
 
     def peer_tensor(self, rank: int, dtype=torch.uint8) -> torch.Tensor:
         return self.handle.get_buffer(rank, (self.nbytes // torch.empty((), dtype=dtype).element_size(),), dtype)
@@ -92,17 +98,23 @@ class FabricSizes:
 class PeerFabric:
     """The per-GPU set of symmetric regions plus launch helpers for the peer-memory kernels."""
 
-    def __init__(self, sizes: FabricSizes, group=None, device: Optional[torch.device] = None):
+    def __init__(self, sizes: FabricSizes, group=None, device: Optional[torch.device] = None, weight_group=None):
+        """`weight_group`: the ranks that hold the same weight shard as this one (with tensor parallelism: the same
+        shard index in every replica).  Parameters only ever move within it, so the weight region and with it the
+        multicast address are made over that group alone: one `multimem.st` then reaches the replicas of this shard
+        and nothing else, and a scale-out costs the source one copy per shard whatever the number of new replicas
+        (the reference builds one broadcast chain per shard, src/service/service.cc:1339-1347)."""
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.group = group if group is not None else dist.group.WORLD
-        self.weights = SymmRegion(sizes.weight_bytes, self.group, self.device)
+        self.weights = SymmRegion(sizes.weight_bytes, weight_group if weight_group is not None else self.group,
+                                  self.device)
         self.kv = SymmRegion(sizes.kv_bytes, self.group, self.device)
         self.mailbox = SymmRegion(max(16, sizes.mailbox_slots * sizes.mailbox_slot_bytes), self.group, self.device)
         self.flags = SymmRegion(FLAG_WORDS * 4, self.group, self.device)
         self.flags.local.zero_()
         self.kv.local.zero_()
         self.sizes = sizes
-        self.rank, self.world = self.weights.rank, self.weights.world
+        self.rank, self.world = self.flags.rank, self.flags.world
         # local scratch: tickets for the "last CTA publishes" protocol
         self.tickets = torch.zeros(4096, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
@@ -154,12 +166,12 @@ class PeerFabric:
             k = u1 - u0
             offs = (ctypes.c_int64 * k)(*unit_offsets[u0:u1])
             lens = (ctypes.c_int64 * k)(*unit_nbytes[u0:u1])
-            bases = (ctypes.c_void_p * len(dst_ranks))(*[region.ptrs[r] for r in dst_ranks])
+            bases = (ctypes.c_void_p * len(dst_ranks))(*[region.ptr_of(r) for r in dst_ranks])
             flags = (ctypes.c_void_p * len(dst_ranks))(*[self.flags.ptrs[r] for r in dst_ranks])
             tick = self.tickets[:k]
             tick.zero_()
             mc = ctypes.c_void_p(region.mc_ptr if (use_multimem and region.mc_ptr) else 0)
-            rc = lib.blitz_peer_copy_units(ctypes.c_void_p(region.ptrs[self.rank]), bases, flags, len(dst_ranks), mc,
+            rc = lib.blitz_peer_copy_units(ctypes.c_void_p(region.ptrs[region.rank]), bases, flags, len(dst_ranks), mc,
                                            offs, lens, k, flag_index0 + u0, stripe, n_stripes,
                                            ctypes.c_void_p(tick.data_ptr()), num_ctas, _stream())
             _check(rc, "blitz_peer_copy_units")

@@ -60,9 +60,20 @@ class GpuBackend(Backend):
         self.slot_bytes = max_batch_tokens * self.cfg.hidden * 2
         self.fabric: Optional[symm.PeerFabric] = None
         seg_buf = kv_buf = None
+        self.multimem_min_dests = 2       # fewer destinations than this: plain peer stores are faster
         if use_fabric and world > 1:
+            column = None
+            if tp > 1:
+                import torch.distributed as dist
+                # one group per shard index (every rank creates all of them, in the same order): parameters of shard
+                # t only ever move between the ranks t, t + tp, t + 2 tp, ...
+                for t in range(tp):
+                    g_ = dist.new_group([r for r in range(world) if r % tp == t])
+                    if rank % tp == t:
+                        column = g_
             self.fabric = symm.PeerFabric(symm.FabricSizes(weight_bytes=probe.layout.total_bytes, kv_bytes=kv_bytes,
-                                                           mailbox_slots=4, mailbox_slot_bytes=self.slot_bytes))
+                                                           mailbox_slots=4, mailbox_slot_bytes=self.slot_bytes),
+                                          weight_group=column)
             seg_buf, kv_buf = self.fabric.weights.local, self.fabric.kv.local
             self.ctl = symm.SymmRegion(symm.KV_SLOTS * CTL_SLOT_WORDS * 4 + symm.KV_SLOTS * 4)  # id lists, then tags
             self.ctl.local.zero_()
@@ -595,9 +606,9 @@ class GpuBackend(Backend):
             lens = [(b + 15) // 16 * 16 for _, _, b in self.units]
             # one destination: plain peer stores are the fastest (92 % of the measured link rate); several: one
             # multimem store per 16 bytes keeps the source's egress at 1x whatever the fan-out
-            # (the multicast address covers every GPU of the box, so it is only usable when all of them hold the
-            # same bytes: with tp > 1 the shards differ between ranks and the copy stays on peer stores)
-            mm = self.use_multimem and self.tp == 1 and len(dests) >= 2 and bool(self.fabric.weights.mc_ptr)
+            # (the multicast address covers the GPUs that hold this shard, in every replica: the ones that are not
+            # destinations already hold the same bytes)
+            mm = self.use_multimem and len(dests) >= self.multimem_min_dests and bool(self.fabric.weights.mc_ptr)
             with self.xfer_lock:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 with torch.cuda.stream(self.side):

@@ -3,6 +3,9 @@
 Launched by test_multi_gpu.py through torch.distributed.run with 4 ranks (2 ranks: no hand-over part).  Ranks 0-1 are
 the two shards of a new replica, ranks 2-3 the shards of an old, fully loaded one; all hold the same weights.
 
+  0. (4 ranks) the new replica's weights are cleared and come back from the old replica: shard t of the old replica
+     stores into shard t of the new one through the multicast address of their shard column (the weight region of a
+     tensor-parallel worker spans only the ranks that hold the same shard).
   1. every replica prefills three prompts the ordinary way: the expected first tokens.
   2. the new replica forgets that it is loaded; a thread per shard then marks one unit after the other as arrived, the
      second shard later than the first, so that only the agreed minimum keeps a shard from running a layer its
@@ -63,6 +66,24 @@ def main():
         from blitz_scale_b200.parallel.teardown import shutdown
         shutdown([backend])
         return 0
+
+    if world == 4:
+        seg = backend.engine.seg.buffer
+        before = int(seg.view(torch.int32).sum(dtype=torch.int64))
+        assert backend.fabric.weights.world == world // tp and backend.fabric.weights.job_ranks == [rank % tp, rank % tp + tp]
+        if new_replica:
+            seg.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=host)
+        backend.use_multimem, backend.multimem_min_dests = True, 1
+        backend.broadcast("nvl", [2, 3], [0, 1])          # sources store, destinations wait for every unit
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert int(seg.view(torch.int32).sum(dtype=torch.int64)) == before, "shard differs after the transfer"
+        assert backend.engine.status.fully_loaded()
+        if not new_replica:
+            assert backend.transfer_log and backend.transfer_log[-1]["multimem"] == bool(backend.fabric.weights.mc_ptr)
+        dist.barrier(group=host)
 
     g = torch.Generator().manual_seed(21)
     prompts = [[torch.randint(0, 4096, (n,), generator=g).tolist() for n in lens] for lens in ((70, 33), (150,), (9, 40, 21))]
