@@ -12,7 +12,7 @@
 Timing: CUDA events on each rank's stream around the whole transfer (a destination's interval ends when its
 last readiness flag has been observed by a device-side wait), barrier + synchronize on both sides, the
 reported time is the max over ranks.  Link roofline: 900 GB/s nominal per direction per GPU; 770 GB/s measured
-peer copy on this pool.
+for a peer copy on B200 / NVSwitch.
 """
 from __future__ import annotations
 
