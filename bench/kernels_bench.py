@@ -124,25 +124,20 @@ def bench_prefill_attn(cases, out):
     for (B, n, qh, kvh) in cases:
         hd = 128
         qkv = torch.randn(B * n, (qh + 2 * kvh) * hd, device="cuda", dtype=torch.bfloat16)
-        indptr = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
         o = torch.empty(B * n, qh * hd, device="cuda", dtype=torch.bfloat16)
         fl = 4.0 * B * qh * hd * n * n / 2
-        # through the paged pool (two ping-ponged query tiles per CTA, keys and values read from 64-token pages): P in
-        # shared or tensor memory, with and without a share of the exponentials on the FMA pipe
+        # through the paged pool (persistent grid, two ping-ponged query tiles per work item, keys and values read from
+        # 64-token pages), with and without a share of the exponentials on the FMA pipe
         ps = 64
         npg = n // ps
         pool = torch.randn(B * npg, 2, ps, kvh, hd, device="cuda", dtype=torch.bfloat16)
         ids = torch.randperm(B * npg, device="cuda").to(torch.int32)
-        pindptr = (torch.arange(B + 1, device="cuda") * npg).to(torch.int32)
-        last = torch.full((B,), ps, dtype=torch.int32, device="cuda")
-        work = ops.prefill_work_list([n] * B, [n] * B, "cuda")
-        for poly, ptmem in ((False, False), (False, True), (True, True)):
-            t = timeit(lambda i: ops.attn_prefill_paged(qkv, pool, indptr, ids, pindptr, last, [n] * B, q_heads=qh,
-                                                         kv_heads=kvh, head_dim=hd, page_size=ps, out=o, work=work,
-                                                         poly_exp=poly, p_in_tmem=ptmem))
+        work = ops.prefill_work_list([n] * B, [n] * B, ps, "cuda")
+        for poly in (False, True):
+            t = timeit(lambda i: ops.attn_prefill_paged(qkv, pool, ids, work, q_heads=qh, kv_heads=kvh, head_dim=hd,
+                                                         page_size=ps, out=o, poly_exp=poly))
             ops.check_status()
-            row = dict(kind="attn_prefill_paged", B=B, n=n, q_heads=qh, kv_heads=kvh, poly_exp=poly, p_in_tmem=ptmem,
-                       us=t * 1e6,
+            row = dict(kind="attn_prefill_paged", B=B, n=n, q_heads=qh, kv_heads=kvh, poly_exp=poly, us=t * 1e6,
                        tflops=fl / t / 1e12, frac_of_gemm_peak=fl / t / flops_peak, peaks=src)
             out.append(row)
             print(json.dumps(row), flush=True)

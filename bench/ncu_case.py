@@ -39,16 +39,12 @@ def main():
         B, n = map(int, sys.argv[2:4])
         qh, kvh, hd, ps = 32, 8, 128, 64
         qkv = torch.randn(B * n, (qh + 2 * kvh) * hd, device="cuda", dtype=torch.bfloat16)
-        indptr = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
         npg = n // ps
         pool = torch.randn(B * npg, 2, ps, kvh, hd, device="cuda", dtype=torch.bfloat16)
         ids = torch.randperm(B * npg, device="cuda").to(torch.int32)
-        pindptr = (torch.arange(B + 1, device="cuda") * npg).to(torch.int32)
-        last = torch.full((B,), ps, dtype=torch.int32, device="cuda")
-        work = ops.prefill_work_list([n] * B, [n] * B, "cuda")
+        work = ops.prefill_work_list([n] * B, [n] * B, ps, "cuda")
         for _ in range(3):
-            ops.attn_prefill_paged(qkv, pool, indptr, ids, pindptr, last, [n] * B, q_heads=qh, kv_heads=kvh, head_dim=hd,
-                                   page_size=ps, work=work)
+            ops.attn_prefill_paged(qkv, pool, ids, work, q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps)
     elif kind == "decode_step":
         # two eager decode steps of the full model (no CUDA graph), for a per-kernel launch list of one step:
         #   ncu --metrics gpu__time_duration.sum -k regex:"blitz|gemm|attn|rms|rope|argmax|embedding|sample" ...

@@ -41,7 +41,7 @@ class StepMeta:
     tok_indptr: Optional[torch.Tensor] = None  # [B + 1] token offsets (prefill)
     seq_lens_host: List[int] = field(default_factory=list)  # rows per sequence in this pass (prefill)
     kv_lens_host: List[int] = field(default_factory=list)   # tokens cached per sequence after this pass (prefill)
-    prefill_work: Optional[torch.Tensor] = None             # CTA order of the prefill attention (heaviest first)
+    prefill_work: Optional[torch.Tensor] = None             # work records of the prefill attention (heaviest first)
     is_prefill: bool = False
     batch: int = 0
     num_tokens: int = 0
@@ -140,9 +140,11 @@ class LlamaRunner:
         """The pass's rows against everything the cache holds for their sequences (rope_kv_store has just added the
         rows' own keys and values): earlier chunks of a long prompt are simply a longer page list."""
         T = m.num_tokens
-        ops.attn_prefill_paged(self.qkv[:T], self.kv[l], m.tok_indptr, m.page_indices, m.page_indptr, m.last_page_len,
-                               m.seq_lens_host, q_heads=self.qh, kv_heads=self.kvh, head_dim=self.hd,
-                               page_size=self.page_size, out=self.attn[:T], work=m.prefill_work)
+        if m.prefill_work is None:      # a caller that built the step by hand
+            m.prefill_work = ops.prefill_work_list(m.seq_lens_host, m.kv_lens_host or m.seq_lens_host, self.page_size,
+                                                   self.qkv.device)
+        ops.attn_prefill_paged(self.qkv[:T], self.kv[l], m.page_indices, m.prefill_work, q_heads=self.qh,
+                               kv_heads=self.kvh, head_dim=self.hd, page_size=self.page_size, out=self.attn[:T])
 
     def last_rows(self, m: StepMeta) -> torch.Tensor:
         """[batch, hidden]: the state `head` starts from, for the last row of every sequence of a prefill pass."""

@@ -285,36 +285,40 @@ def attn_decode(q: torch.Tensor, kv_layer: torch.Tensor, indices: torch.Tensor, 
     return out
 
 
-def prefill_work_list(q_lens, kv_lens, device) -> torch.Tensor:
-    """Order in which `attn_prefill_paged` hands (sequence, 256-row pair of query tiles) to its CTAs: the pairs that
-    walk the most key blocks first, so that the short ones fill the tail of the grid."""
+def prefill_work_list(q_lens, kv_lens, page_size: int, device) -> torch.Tensor:
+    """Work records of `attn_prefill_paged`, one per (sequence, 256 rows of it): first row of the sequence in the
+    activation, its rows in this pass, index of its first page id, number of its pages, tokens cached for it (this
+    pass included), which 256-row pair.  Ordered by the number of key blocks the pair walks, heaviest first; the kernel
+    deals the list back and forth over its CTAs."""
     items = []
-    for b, (n, kv) in enumerate(zip(q_lens, kv_lens)):
-        for pair in range((int(n) + 255) // 256):
-            items.append((min(int(kv), int(kv) - int(n) + 256 * (pair + 1)), b, pair))
+    row0 = pg0 = 0
+    for n, kv in zip(q_lens, kv_lens):
+        n, kv = int(n), int(kv)
+        npages = (kv + page_size - 1) // page_size
+        for pair in range((n + 255) // 256):
+            items.append((min(kv, kv - n + 256 * (pair + 1)), row0, n, pg0, npages, kv, pair))
+        row0 += n
+        pg0 += npages
     items.sort(key=lambda x: -x[0])
-    return torch.tensor([(b << 12) | pair for _, b, pair in items], dtype=torch.int32).to(device, non_blocking=True)
+    rec = [[r0, n, p0, np_, kv, pair, 0, 0] for _, r0, n, p0, np_, kv, pair in items]
+    return torch.tensor(rec, dtype=torch.int32).reshape(-1, 8).to(device, non_blocking=True)
 
 
-def attn_prefill_paged(qkv: torch.Tensor, kv_layer: torch.Tensor, tok_indptr: torch.Tensor, page_indices: torch.Tensor,
-                       page_indptr: torch.Tensor, last_page_len: torch.Tensor, q_lens_host, *, q_heads: int,
-                       kv_heads: int, head_dim: int, page_size: int, out: Optional[torch.Tensor] = None,
-                       sm_scale: Optional[float] = None, work: Optional[torch.Tensor] = None,
-                       poly_exp: bool = False, p_in_tmem: bool = True) -> torch.Tensor:
-    """Causal attention of the chunk's rows over the paged cache (which already holds the chunk's own keys and values,
-    after whatever earlier chunks stored).  ``qkv`` rotated (rope_kv_store); the page table covers prefix + chunk."""
+def attn_prefill_paged(qkv: torch.Tensor, kv_layer: torch.Tensor, page_indices: torch.Tensor, work: torch.Tensor, *,
+                       q_heads: int, kv_heads: int, head_dim: int, page_size: int, out: Optional[torch.Tensor] = None,
+                       sm_scale: Optional[float] = None, poly_exp: bool = False) -> torch.Tensor:
+    """Causal attention of the pass's rows over the paged cache (which already holds the rows' own keys and values,
+    after whatever earlier passes stored).  ``qkv`` rotated (rope_kv_store); ``page_indices``: the sequences' page
+    ids back to back, covering prefix + rows; ``work`` from `prefill_work_list` for the same sequences."""
     T = qkv.shape[0]
     if out is None:
         out = torch.empty((T, q_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    pairs = sum((int(n) + 255) // 256 for n in q_lens_host)
     if sm_scale is None:
         sm_scale = head_dim ** -0.5
-    assert work is None or work.numel() == pairs
+    assert work.dtype == torch.int32 and work.dim() == 2 and work.shape[1] == 8 and work.is_contiguous()
     max_pages = kv_layer.shape[0]
-    _check(lib().blitz_attn_prefill_paged(_p(qkv), _p(kv_layer), _p(out), out.stride(0), _p(tok_indptr), _p(page_indices),
-                                          _p(page_indptr), _p(last_page_len), _p(work) if work is not None else None,
-                                          len(q_lens_host), T, pairs, q_heads, kv_heads, head_dim, page_size, max_pages,
-                                          sm_scale, (1 if poly_exp else 0) | (2 if p_in_tmem else 0),
-                                          _p(status_word(qkv.device)), _dt(qkv),
-                                          _stream()), "blitz_attn_prefill_paged")
+    _check(lib().blitz_attn_prefill_paged(_p(qkv), _p(kv_layer), _p(out), out.stride(0), _p(page_indices), _p(work),
+                                          work.shape[0], T, q_heads, kv_heads, head_dim, page_size, max_pages, sm_scale,
+                                          1 if poly_exp else 0, _p(status_word(qkv.device)), _dt(qkv), _stream()),
+           "blitz_attn_prefill_paged")
     return out

@@ -87,8 +87,8 @@ def _declare(L: ctypes.CDLL) -> None:
     sig("blitz_attn_decode_workspace_bytes", [c_i, c_i, c_i, c_i], c_i64)
     sig("blitz_attn_decode", [c_p, c_i64, c_p, c_p, c_p, c_p, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_f,
                               c_p, c_i, c_p])
-    sig("blitz_attn_prefill_paged", [c_p, c_p, c_p, c_i64, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i,
-                                     c_i, c_f, c_i, c_p, c_i, c_p])
+    sig("blitz_attn_prefill_paged", [c_p, c_p, c_p, c_i64, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_f, c_i, c_p,
+                                     c_i, c_p])
     # comm kernels
     pp = ctypes.POINTER(c_p)
     pi64 = ctypes.POINTER(c_i64)

@@ -91,7 +91,7 @@ class Engine:
         L, d = self.layout, self.dev
         kv_lens = list(kv_lens) if kv_lens else list(seq_lens)
         if prefill and work is None:
-            work = ops.prefill_work_list(seq_lens, kv_lens, self.device)
+            work = ops.prefill_work_list(seq_lens, kv_lens, self.page_size, self.device)
         return StepMeta(kv_lens_host=kv_lens, prefill_work=work,
                         ids=d[L.ids:L.ids + T], pos=d[L.pos:L.pos + T], slot=d[L.slot:L.slot + T],
                         page_indices=d[L.page_indices:L.page_indices + max(P, 1)],

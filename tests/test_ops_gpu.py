@@ -349,8 +349,8 @@ def test_attn_decode_simt_matches_tc(ops):
     (6, 2, 64, 64, torch.bfloat16, [(700, 0), (130, 64), (5, 0)]),
     (8, 1, 64, 8, torch.bfloat16, [(260, 24)]),
 ])
-@pytest.mark.parametrize("poly,ptmem", [(False, False), (True, False), (False, True), (True, True)])
-def test_attn_prefill_paged(ops, qh, kvh, hd, ps, dt, cases, poly, ptmem):
+@pytest.mark.parametrize("poly", [False, True])
+def test_attn_prefill_paged(ops, qh, kvh, hd, ps, dt, cases, poly):
     """Chunk rows against prefix + chunk in the paged pool, two ping-ponged query tiles per CTA, against fp32 math.
     (q_len, prefix) per sequence; pages are scattered over the pool; stale pool contents are finite garbage."""
     torch.manual_seed(5)
@@ -384,15 +384,16 @@ def test_attn_prefill_paged(ops, qh, kvh, hd, ps, dt, cases, poly, ptmem):
     dev = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
     q_lens = [n for n, _ in cases]
     kv_lens = [n + pre for n, pre in cases]
-    work = ops.prefill_work_list(q_lens, kv_lens, "cuda")
-    out = ops.attn_prefill_paged(qkv, pool, dev(tok_indptr), dev(page_ids), dev(page_indptr), dev(last), q_lens,
-                                 q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps, work=work, poly_exp=poly,
-                                 p_in_tmem=ptmem)
-    out2 = ops.attn_prefill_paged(qkv, pool, dev(tok_indptr), dev(page_ids), dev(page_indptr), dev(last), q_lens,
-                                  q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps, poly_exp=poly, p_in_tmem=ptmem)
+    work = ops.prefill_work_list(q_lens, kv_lens, ps, "cuda")
+    assert work.shape == (sum((n + 255) // 256 for n in q_lens), 8)
+    out = ops.attn_prefill_paged(qkv, pool, dev(page_ids), work, q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps,
+                                 poly_exp=poly)
+    # the order of the work list does not matter
+    out2 = ops.attn_prefill_paged(qkv, pool, dev(page_ids), work.flip(0).contiguous(), q_heads=qh, kv_heads=kvh,
+                                  head_dim=hd, page_size=ps, poly_exp=poly)
     torch.cuda.synchronize()
     ops.check_status()
-    assert torch.equal(out, out2)                  # the work list only changes the order
+    assert torch.equal(out, out2)
     g = qh // kvh
     o = 0
     for (n, pre), (k, v) in zip(cases, full):
@@ -407,8 +408,7 @@ def test_attn_prefill_paged(ops, qh, kvh, hd, ps, dt, cases, poly, ptmem):
         o += n
 
 
-@pytest.mark.parametrize("ptmem", [False, True])
-def test_attn_prefill_paged_rescales_when_the_maximum_grows(ops, ptmem):
+def test_attn_prefill_paged_rescales_when_the_maximum_grows(ops):
     """Scores that grow steeply along the sequence force the in-place rescaling of the output rows in tensor memory."""
     torch.manual_seed(6)
     qh = kvh = 1
@@ -424,8 +424,8 @@ def test_attn_prefill_paged_rescales_when_the_maximum_grows(ops, ptmem):
     pool[:, 0] = qkv[:, hd:2 * hd].view(n // ps, ps, 1, hd)
     pool[:, 1] = qkv[:, 2 * hd:].view(n // ps, ps, 1, hd)
     dev = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
-    out = ops.attn_prefill_paged(qkv, pool, dev([0, n]), dev(list(range(n // ps))), dev([0, n // ps]), dev([ps]), [n],
-                                 q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps, p_in_tmem=ptmem)
+    out = ops.attn_prefill_paged(qkv, pool, dev(list(range(n // ps))), ops.prefill_work_list([n], [n], ps, "cuda"),
+                                 q_heads=qh, kv_heads=kvh, head_dim=hd, page_size=ps)
     torch.cuda.synchronize()
     ops.check_status()
     qf, kf, vf = (qkv[:, i * hd:(i + 1) * hd].float() for i in range(3))
