@@ -311,6 +311,7 @@ __global__ void sample_kernel(const T* __restrict__ logits, int vocab, int64_t s
 // offset.  Cache layout of one layer: [page][K|V][token][kv_head][head_dim].
 // A negative slot skips the cache write (bounds: slot < max_pages * page_size
 // is checked; a bad slot sets *status and skips).
+constexpr int kRopeMaxHalf = 128;  // head_dim <= 256
 template <typename T>
 __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int32_t* __restrict__ pos,
                                      const int32_t* __restrict__ slot, T* __restrict__ kv_layer, int q_heads,
@@ -335,6 +336,14 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int32_t* __restr
   T* kdst = kv_layer + (static_cast<int64_t>(page) * 2) * plane + static_cast<int64_t>(off) * kv_heads * head_dim;
   T* vdst = kdst + plane;
 
+  // the angle of pair i depends on the token's position only: computed once per token (accurate sincosf: positions
+  // of thousands of radians) and shared by all heads through shared memory
+  __shared__ float s_cs[kRopeMaxHalf], s_sn[kRopeMaxHalf];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float inv_freq = exp2f(-(2.0f * static_cast<float>(i) / static_cast<float>(head_dim)) * log2_theta);
+    sincosf(p * inv_freq, &s_sn[i], &s_cs[i]);
+  }
+  __syncthreads();
   const int rot_items = (q_heads + kv_heads) * vec_per_half;
   for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
     const int head = it / vec_per_half;
@@ -345,10 +354,7 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int32_t* __restr
     unpack8<T>(*reinterpret_cast<uint4*>(hp + half + v * 8), b);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int i = v * 8 + j;
-      const float inv_freq = exp2f(-(2.0f * static_cast<float>(i) / static_cast<float>(head_dim)) * log2_theta);
-      float sn, cs;
-      sincosf(p * inv_freq, &sn, &cs);
+      const float cs = s_cs[v * 8 + j], sn = s_sn[v * 8 + j];
       const float x0 = a[j], x1 = b[j];
       a[j] = x0 * cs - x1 * sn;
       b[j] = x1 * cs + x0 * sn;
@@ -468,7 +474,7 @@ int blitz_rope_kv_store(void* qkv, const int32_t* pos, const int32_t* slot, void
                         int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, float rope_theta,
                         int* status, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (head_dim & 15) return -1;
+  if ((head_dim & 15) || head_dim > 2 * kRopeMaxHalf) return -1;
   const float log2_theta = log2f(rope_theta);
   cudaError_t blitz_last = cudaSuccess;
   BLITZ_DISPATCH_DTYPE(dtype, (blitz_last = launch_pdl(rope_kv_store_kernel<T>, dim3(num_tokens), dim3(256), 0, stream,
