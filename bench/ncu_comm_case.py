@@ -112,7 +112,7 @@ def main():
         H, tp = 8192, 2
         rpr = M // tp
         stage = torch.randn(tp * rpr * H, device=d0, dtype=bf)
-        flag_rs = torch.zeros(16, dtype=torch.int32, device=d0)
+        flag_rs = torch.zeros(64 * 8 + 8, dtype=torch.int32, device=d0)        # [block of 128 rows][source] + ticket
         res = torch.randn(rpr, H, device=d0, dtype=bf)
         nw = torch.ones(H, device=d0, dtype=bf)
         xg0 = torch.zeros(M, H, device=d0, dtype=bf)
@@ -121,11 +121,11 @@ def main():
         fa1 = torch.zeros(16, dtype=torch.int32, device=d1)
         xg = (ctypes.c_void_p * tp)(xg0.data_ptr(), xg1.data_ptr())
         fl = (ctypes.c_void_p * tp)(fa0.data_ptr(), fa1.data_ptr())
-        expect = 7
+        tiles_n = 7
         for _ in range(3):
-            flag_rs[:tp] = expect          # as if both sources had pushed all their tiles
-            rc = lib.blitz_rs_reduce_norm(vp(stage), vp(flag_rs), expect, vp(res), vp(nw), xg, fl, tp, 0, rpr, rpr, H, 1e-5,
-                                          int(10e6), vp(status), 1, stream)
+            flag_rs[:64 * 8] = tiles_n     # as if both sources had pushed all their tiles of every block
+            rc = lib.blitz_rs_reduce_norm(vp(stage), vp(flag_rs), tiles_n, vp(res), vp(nw), xg, fl, tp, 0, rpr, rpr, M, H,
+                                          1e-5, int(10e6), vp(status), 1, stream)
             assert rc == 0, rc
         torch.cuda.synchronize()
     elif kind == "allreduce":

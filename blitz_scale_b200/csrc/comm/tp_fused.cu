@@ -23,11 +23,14 @@
 namespace blitz {
 
 constexpr int kMaxTp = 8;
+constexpr int kRsBlocks = 64;  // 128-row blocks of one owner's rows: rows_per_rank <= 8192
 
 struct RsReduceParams {
   const void* stage;        // local staging: [tp][H/8][rows_per_rank][8] partials from every source rank
-  uint32_t* flag_rs;        // local: [tp] tiles landed per source (reset here)
-  uint32_t expect_tiles;    // tiles each source pushes into this rank per call
+  uint32_t* flag_rs;        // local: [kRsBlocks][kMaxTp] tiles landed per (block of 128 local rows, source), then a
+                            // ticket word (all reset here)
+  uint32_t tiles_n;         // tiles per block of 128 GEMM rows that every source pushes
+  int total_rows;           // rows of the GEMM whose partials arrive (all owners together)
   void* residual;           // local residual shard [rows_per_rank][H] (in/out); may be null (no residual)
   const void* norm_w;       // [H]
   void* xg[kMaxTp];         // gathered activations [M][H] on every rank (peer pointers, self included)
@@ -44,9 +47,16 @@ __global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const RsReduceParam
   __shared__ int s_ok;
   const int row = blockIdx.x;  // local row
   if (threadIdx.x == 0) {
+    // only the tiles that cover this row's block of 128 local rows are waited for: rows whose partials have all
+    // arrived are reduced, normalised and sent on while the sources still compute the later blocks.  A block's global
+    // rows may lie in more than one 128-row tile of the GEMM when rows_per_rank is not a multiple of 128.
+    const int lb = row >> 7;
+    const int g0 = p.my_rank * p.rows_per_rank + lb * 128;
+    const int g1 = min(p.total_rows, p.my_rank * p.rows_per_rank + min(p.rows_per_rank, (lb + 1) * 128)) - 1;
+    const uint32_t expect = p.tiles_n * static_cast<uint32_t>((g1 >> 7) - (g0 >> 7) + 1);
     int ok = 1;
     for (int s = 0; s < p.tp; ++s)
-      if (!ptx::bounded_flag_wait_ge(p.flag_rs + s, p.expect_tiles, p.budget_ns)) ok = 0;
+      if (!ptx::bounded_flag_wait_ge(p.flag_rs + lb * kMaxTp + s, expect, p.budget_ns)) ok = 0;
     if (!ok && p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
     s_ok = ok;
   }
@@ -108,10 +118,11 @@ __global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const RsReduceParam
   }
   // the last block to finish re-arms the reduce-scatter flags for the next call
   if (threadIdx.x == 0) {
-    const uint32_t t = ptx::atom_add_acq_rel_gpu(p.flag_rs + kMaxTp, 1u);
+    const uint32_t t = ptx::atom_add_acq_rel_gpu(p.flag_rs + kRsBlocks * kMaxTp, 1u);
     if (t == gridDim.x - 1) {
-      for (int s = 0; s < p.tp; ++s) p.flag_rs[s] = 0;
-      p.flag_rs[kMaxTp] = 0;
+      const int nb = (p.rows_per_rank + 127) >> 7;
+      for (int i = 0; i < nb * kMaxTp; ++i) p.flag_rs[i] = 0;
+      p.flag_rs[kRsBlocks * kMaxTp] = 0;
       __threadfence_system();
     }
   }
@@ -488,16 +499,18 @@ int blitz_peer_allgather(const void* x, void* const* slots, uint32_t* const* fla
 
 using namespace blitz;
 
-// stage: local [tp][hidden / 8][rows_per_rank][8] (the layout the GEMM push epilogue writes); flag_rs: local uint32[kMaxTp + 1] (zero at start; [kMaxTp] is a ticket);
+// stage: local [tp][hidden / 8][rows_per_rank][8] (the layout the GEMM push epilogue writes); flag_rs: local
+// uint32[64 blocks][8 sources] + a ticket word (zero at start); tiles_n: tiles per 128 GEMM rows each source pushes;
 // xg / flag_ag: tp peer pointers each.  rows_valid <= rows_per_rank local rows are processed.
-int blitz_rs_reduce_norm(const void* stage, uint32_t* flag_rs, uint32_t expect_tiles, void* residual,
+int blitz_rs_reduce_norm(const void* stage, uint32_t* flag_rs, uint32_t tiles_n, void* residual,
                          const void* norm_w, void* const* xg, uint32_t* const* flag_ag, int tp, int my_rank,
-                         int rows_per_rank, int rows_valid, int hidden, float eps, uint64_t budget_ns, int* status,
-                         int dtype, cudaStream_t stream) {
+                         int rows_per_rank, int rows_valid, int total_rows, int hidden, float eps, uint64_t budget_ns,
+                         int* status, int dtype, cudaStream_t stream) {
   if (rows_valid <= 0) return 0;
-  if (tp < 1 || tp > kMaxTp || (hidden & 7)) return -1;
+  if (tp < 1 || tp > kMaxTp || (hidden & 7) || rows_per_rank > kRsBlocks * 128) return -1;
   RsReduceParams p;
-  p.stage = stage; p.flag_rs = flag_rs; p.expect_tiles = expect_tiles; p.residual = residual; p.norm_w = norm_w;
+  p.stage = stage; p.flag_rs = flag_rs; p.tiles_n = tiles_n; p.total_rows = total_rows; p.residual = residual;
+  p.norm_w = norm_w;
   for (int d = 0; d < kMaxTp; ++d) {
     p.xg[d] = d < tp ? xg[d] : nullptr;
     p.flag_ag[d] = d < tp ? flag_ag[d] : nullptr;

@@ -63,7 +63,29 @@ struct GemmParams {
   const uint32_t* wait_flags;
   int n_wait;
   uint32_t wait_value;
+  int n_fast;  // tensor-parallel fusion: N runs fastest over the tiles, M blocks start at m_rot (see gemm_tile_blocks)
+  int m_rot;
 };
+
+// Tile number -> (M block, N block).  Normally M runs fastest.  When the rows of A arrive from other ranks
+// (n_wait > 0: counter s = rows that source s has delivered, wait_value rows each) N runs fastest and the M blocks
+// start at this rank's own rows and go on through the other sources' in rank order: every CTA first works on rows
+// that are here already, and waits (see the producer) only for the source whose rows it is about to load, so the
+// GEMM overlaps the arrival of the later sources' rows instead of starting after the last one.
+// (The push epilogue, GEMM -> reduce-scatter, keeps M fastest: an owner's block of rows is complete only when the
+// last source has produced it, and the kernel that reduces it is a later launch of the same stream, so a different
+// order buys no overlap and costs weight-tile reuse in L2: measured 252 against 233 us at M = 4096, K = 4096 per rank.)
+__device__ __forceinline__ void gemm_tile_blocks(const GemmParams& p, int tile, int& mb, int& nb) {
+  if (p.n_fast) {
+    const int lin = tile / p.tiles_n;
+    nb = tile - lin * p.tiles_n;
+    mb = lin + p.m_rot;
+    if (mb >= p.tiles_m) mb -= p.tiles_m;
+  } else {
+    mb = tile % p.tiles_m;
+    nb = tile / p.tiles_m;
+  }
+}
 
 template <int BN>
 struct GemmCfg {
@@ -163,15 +185,19 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&a
 }
 
 // After every epilogue thread has stored its rows of a tile: make them visible system-wide and tell each
-// owner rank that one more tile from this source has landed.
+// owner rank that one more tile from this source has landed in the 128-row block(s) of its rows the tile covers.
 __device__ __forceinline__ void push_signal(const GemmParams& p, int m0, int epi_tid) {
   __threadfence_system();
   asm volatile("bar.sync 2, 128;" ::: "memory");
   if (epi_tid == 0) {
+    // counters of an owner: [block of 128 of its rows][source]
     const int last_row = min(p.M, m0 + kBM) - 1;
     ptx::fence_acq_rel_sys();
-    for (int o = m0 / p.rows_per_rank; o <= last_row / p.rows_per_rank; ++o)
-      ptx::red_add_release_sys(p.push_flags[o] + p.tp_rank, 1u);
+    for (int o = m0 / p.rows_per_rank; o <= last_row / p.rows_per_rank; ++o) {
+      const int base = o * p.rows_per_rank;
+      const int lo = max(m0, base) - base, hi = min(last_row, base + p.rows_per_rank - 1) - base;
+      for (int lb = lo >> 7; lb <= (hi >> 7); ++lb) ptx::red_add_release_sys(p.push_flags[o] + lb * 8 + p.tp_rank, 1u);
+    }
   }
 }
 
@@ -240,20 +266,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       const uint32_t tx_bytes = static_cast<uint32_t>(p.a_box_rows) * kBK * 2 + Cfg::kBBytes;
       bool ok = true;
-      if (p.n_wait > 0) {
-        // rows of A arrive by peer stores (generic proxy); TMA reads them through the async proxy
-        for (int i = 0; i < p.n_wait && ok; ++i)
-          if (!ptx::bounded_flag_wait_ge(p.wait_flags + i, p.wait_value, ptx::kDefaultWaitNs)) ok = false;
-        if (!ok) {
-          *abort_flag = 1;
-          if (p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
-        }
-        ptx::fence_proxy_async_all();
-      }
+      uint32_t arrived = 0;  // sources whose rows are known to be here
       for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
         const int tile = w / p.split_k, split = w % p.split_k;
-        const int m0 = (tile % p.tiles_m) * kBM;
-        const int n0 = (tile / p.tiles_m) * kOutCols;
+        int mb, nb;
+        gemm_tile_blocks(p, tile, mb, nb);
+        const int m0 = mb * kBM;
+        const int n0 = nb * kOutCols;
+        if (p.n_wait > 0) {
+          // rows of A arrive by peer stores (generic proxy); TMA reads them through the async proxy: wait for the
+          // sources this M block takes rows from, then fence
+          const int s_lo = m0 / static_cast<int>(p.wait_value);
+          const int s_hi = min(p.n_wait - 1, (min(p.M, m0 + kBM) - 1) / static_cast<int>(p.wait_value));
+          bool fresh = false;
+          for (int sidx = s_lo; sidx <= s_hi && ok; ++sidx) {
+            if ((arrived >> sidx) & 1u) continue;
+            if (!ptx::bounded_flag_wait_ge(p.wait_flags + sidx, p.wait_value, ptx::kDefaultWaitNs)) ok = false;
+            arrived |= 1u << sidx;
+            fresh = true;
+          }
+          if (!ok) {
+            *abort_flag = 1;
+            if (p.status) atomicCAS(p.status, 0, kStatusTimeoutFlag);
+            break;
+          }
+          if (fresh) ptx::fence_proxy_async_all();
+        }
         const int kb_beg = split * p.kb_per_split;
         const int kb_end = min(num_kb, kb_beg + p.kb_per_split);
         for (int kb = kb_beg; kb < kb_end; ++kb) {
@@ -357,8 +395,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t acc_phase = 0;
     for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
       const int tile = w / p.split_k;
-      const int m0 = (tile % p.tiles_m) * kBM;
-      const int n0 = (tile / p.tiles_m) * kOutCols;
+      int mb, nb;
+      gemm_tile_blocks(p, tile, mb, nb);
+      const int m0 = mb * kBM;
+      const int n0 = nb * kOutCols;
       if (!ptx::bounded_mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
         if (p.status && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
         break;
@@ -567,11 +607,17 @@ static int gemm_impl(const void* A, int64_t lda, const void* B, int64_t ldb, voi
   p.tiles_m = (M + kBM - 1) / kBM;
   p.tiles_n = (N + out_cols - 1) / out_cols;
   p.status = status;
-  p.tp = 1; p.tp_rank = 0; p.rows_per_rank = M; p.wait_flags = nullptr; p.n_wait = 0; p.wait_value = 0;
+  p.tp = 1; p.tp_rank = 0; p.rows_per_rank = M; p.wait_flags = nullptr; p.n_wait = 0; p.wait_value = 0; p.m_rot = 0; p.n_fast = 0;
   for (int i = 0; i < 8; ++i) { p.push_base[i] = nullptr; p.push_flags[i] = nullptr; }
   if (tpa) {
     p.tp = tpa->tp; p.tp_rank = tpa->tp_rank; p.rows_per_rank = tpa->rows_per_rank > 0 ? tpa->rows_per_rank : M;
     p.wait_flags = tpa->wait_flags; p.n_wait = tpa->wait_flags ? tpa->n_wait : 0; p.wait_value = tpa->wait_value;
+    if (p.n_wait > 0) {
+      if (p.wait_value == 0 || p.n_wait > 32) return -1;
+      p.n_fast = 1;
+      p.m_rot = (int)(((int64_t)tpa->tp_rank * p.wait_value) / kBM) % ((M + kBM - 1) / kBM);
+    }
+
     for (int i = 0; i < 8 && i < tpa->tp; ++i) {
       p.push_base[i] = reinterpret_cast<uint8_t*>(tpa->push_base[i]);
       p.push_flags[i] = tpa->push_flags[i];

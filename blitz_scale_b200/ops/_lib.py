@@ -68,8 +68,8 @@ def _declare(L: ctypes.CDLL) -> None:
     sig("blitz_gemm_tp", [c_p, c_i64, c_p, c_i64, c_p, c_i64, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_i64,
                           c_p, c_i, c_p, c_p, c_p])
     pp_ = ctypes.POINTER(c_p)
-    sig("blitz_rs_reduce_norm", [c_p, c_p, ctypes.c_uint32, c_p, c_p, pp_, pp_, c_i, c_i, c_i, c_i, c_i, c_f, c_u64, c_p,
-                                 c_i, c_p])
+    sig("blitz_rs_reduce_norm", [c_p, c_p, ctypes.c_uint32, c_p, c_p, pp_, pp_, c_i, c_i, c_i, c_i, c_i, c_i, c_f, c_u64,
+                                 c_p, c_i, c_p])
     sig("blitz_flags_zero", [c_p, c_i, c_p])
     sig("blitz_allreduce_oneshot", [c_p, pp_, pp_, c_p, c_i, c_i, c_i64, c_u64, c_p, c_i, c_p])
     sig("blitz_allreduce_fused", [c_p, pp_, pp_, c_p, c_i, c_i, c_i64, c_u64, c_p, c_i, c_p])

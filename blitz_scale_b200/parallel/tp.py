@@ -75,7 +75,10 @@ class FusedTP:
         self.gather_bytes = gather_bytes                       # per rank and call of the small all-gather
         self.o_gather = self.o_nflags + L2 * 32 * 4            # [lane][parity][tp][gather_bytes]
         self.o_gflags = self.o_gather + L2 * self.tp * gather_bytes  # [lane][parity][16 words]
-        total = self.o_gflags + L2 * 16 * 4
+        # reduce-scatter arrival counters of the two staging areas: [64 blocks of 128 rows][8 sources] + a ticket word
+        self.RS_FLAG_WORDS = 64 * 8 + 8
+        self.o_rsflags = self.o_gflags + L2 * 16 * 4
+        total = self.o_rsflags + 2 * self.RS_FLAG_WORDS * 4
         self._in_parity = [0] * self.LANES
         self._g_parity = [0] * self.LANES
         self.lane = 0
@@ -101,6 +104,9 @@ class FusedTP:
     def _flag_ptr(self, rank: int, word: int) -> int:
         return self.ptrs[rank] + self.o_flags + word * 4
 
+    def _rs_flag_ptr(self, rank: int, which: int) -> int:
+        return self.ptrs[rank] + self.o_rsflags + which * self.RS_FLAG_WORDS * 4
+
     def _tp_struct(self) -> _GemmTp:
         s = _GemmTp()
         s.tp, s.tp_rank = self.tp, self.rank
@@ -120,7 +126,8 @@ class FusedTP:
     # ------------------------------------------------------------------ the three launches
     def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, which: int) -> int:
         """Partial result of a row-parallel GEMM pushed to the owners' staging area `which`.  a: [M, K_local] with
-        M a multiple of tp.  Returns the number of tiles every owner receives from each source."""
+        M a multiple of tp.  Returns the number of tiles per 128 rows that every source pushes (what `reduce_norm`
+        waits for, block of rows by block of rows)."""
         M = a.shape[0]
         assert M % self.tp == 0 and M <= self.max_rows
         rpr = M // self.tp
@@ -128,23 +135,22 @@ class FusedTP:
         s.rows_per_rank = rpr
         for r in range(self.tp):
             s.push_base[r] = self.ptrs[r] + self.o_stage[which]
-            s.push_flags[r] = self._flag_ptr(r, 16 * which)
+            s.push_flags[r] = self._rs_flag_ptr(r, which)
         self._gemm(a, w, None, 3, s)
         bn = int(_L.lib().blitz_gemm_tile_n(M, w.shape[1], 3, 0))
-        tiles_n = (w.shape[1] + bn - 1) // bn
-        lo, hi = self.rank * rpr, (self.rank + 1) * rpr - 1
-        return tiles_n * (hi // 128 - lo // 128 + 1)
+        return (w.shape[1] + bn - 1) // bn
 
-    def reduce_norm(self, which: int, expect_tiles: int, rows_per_rank: int, residual: Optional[torch.Tensor],
+    def reduce_norm(self, which: int, tiles_n: int, rows_per_rank: int, residual: Optional[torch.Tensor],
                     norm_w: torch.Tensor, which_x: int, eps: float) -> None:
         """Owner side: sum the partials of staging area `which` (+ residual shard, updated in place), RMSNorm, push the
-        normalised rows into gathered buffer `which_x` of every rank."""
+        normalised rows into gathered buffer `which_x` of every rank.  A row is processed as soon as the tiles of its
+        own block of 128 rows have arrived from every source (`tiles_n` each, from `gemm_rs`)."""
         xg = (ctypes.c_void_p * self.tp)(*[self.ptrs[r] + self.o_xg[which_x] for r in range(self.tp)])
         fl = (ctypes.c_void_p * self.tp)(*[self._flag_ptr(r, 32 + 8 * which_x) for r in range(self.tp)])
         rc = _L.lib().blitz_rs_reduce_norm(
-            ctypes.c_void_p(self.ptrs[self.rank] + self.o_stage[which]), ctypes.c_void_p(self._flag_ptr(self.rank, 16 * which)),
-            expect_tiles, _p(residual), _p(norm_w), xg, fl, self.tp, self.rank, rows_per_rank, rows_per_rank, self.hidden,
-            eps, self.budget_ns, _p(status_word(self.device)), 1 if self.dtype == torch.bfloat16 else 0, _stream())
+            ctypes.c_void_p(self.ptrs[self.rank] + self.o_stage[which]), ctypes.c_void_p(self._rs_flag_ptr(self.rank, which)),
+            tiles_n, _p(residual), _p(norm_w), xg, fl, self.tp, self.rank, rows_per_rank, rows_per_rank,
+            rows_per_rank * self.tp, self.hidden, eps, self.budget_ns, _p(status_word(self.device)), 1 if self.dtype == torch.bfloat16 else 0, _stream())
         _check(rc, "blitz_rs_reduce_norm")
 
     def ag_gemm(self, which_x: int, rows: int, w: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
