@@ -57,7 +57,13 @@ struct DecodeTcParams {
   int tail_box_tokens;  // box height of the second tensor map, used for the last (partly filled) chunk of a sequence
   float scale_log2;
   int* status;
+  long long* trace;  // profiling aid (null in production): clock stamps of CTA 0's first items, see blitz_attn_decode_set_trace
 };
+
+constexpr int kTcTraceItems = 16, kTcTraceSlots = 8;
+__device__ __forceinline__ void tc_trace(const DecodeTcParams& p, int n, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && n < kTcTraceItems) p.trace[n * kTcTraceSlots + slot] = clock64();
+}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -175,7 +181,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
     DecItem it = item < num_items ? dec_item(p, item) : DecItem{};
     int win_base = item < num_items ? (it.c_beg * kTcChunk) / ps : 0;
     int win = item < num_items ? load_window(it, win_base) : 0;
+    int n_done = 0;
     while (item < num_items && ok) {
+      if (lane == 0) tc_trace(p, n_done, 4);
       // next item's metadata and first window: in flight while this item streams
       const int next = item + gridDim.x;
       DecItem nit = next < num_items ? dec_item(p, next) : DecItem{};
@@ -232,6 +240,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
           phase ^= 1u;
         }
       }
+      if (lane == 0) tc_trace(p, n_done, 5);
+      ++n_done;
       item = next;
       it = nit;
       win_base = nwin_base;
@@ -261,7 +271,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
     DecItem it = blockIdx.x < num_items ? dec_item(p, blockIdx.x) : DecItem{};
     uint32_t qa0[HD / 16], qa2[HD / 16];
     if (blockIdx.x < num_items) load_q(it, qa0, qa2);
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+    int n_done = 0;
+    const bool tracer = warp == 0 && lane == 0;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++n_done) {
+      if (tracer) tc_trace(p, n_done, 0);
       const int next = item + gridDim.x;
       DecItem nit = DecItem{};
       uint32_t nqa0[HD / 16], nqa2[HD / 16];
@@ -278,6 +291,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
           if (p.status && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
           ok = false;
         }
+        if (tracer && c == it.c_beg) tc_trace(p, n_done, 1);
         const int nvalid = min(kTcChunk, it.seq_len - c * kTcChunk);
         if (ok && tokw < nvalid) {
           const uint32_t kbase = ptx::smem_u32(smem + stage * Cfg::kStageBytes);
@@ -338,6 +352,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
           phase ^= 1u;
         }
       }
+      if (tracer) tc_trace(p, n_done, 2);
       // per-warp partials -> shared memory (rows < 8 only), then the 4 warps combine them
       l += __shfl_xor_sync(0xffffffffu, l, 1);
       l += __shfl_xor_sync(0xffffffffu, l, 2);
@@ -381,6 +396,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // merge buffers are reused by the next item
+      if (tracer) tc_trace(p, n_done, 3);
       it = nit;
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks) {
@@ -432,7 +448,16 @@ static int launch_tc(const CUtensorMap& tm, const CUtensorMap& tm_tail, const De
 
 }  // namespace blitz
 
+namespace blitz {
+static long long* g_tc_trace = nullptr;
+}
+
 extern "C" {
+// Profiling aid: while `buf` (16 items x 8 int64 clock stamps, device memory) is set, CTA 0 of every following
+// blitz_attn_decode launch records, per work item, when its first consumer warp starts the item, gets its first chunk,
+// finishes its last chunk and finishes the merge (slots 0-3), and when the producer starts and ends issuing the item's
+// loads (slots 4-5).
+void blitz_attn_decode_set_trace(long long* buf) { blitz::g_tc_trace = buf; }
 using namespace blitz;
 
 // Bytes of fp32 scratch the split path needs: part_o then part_lse.
@@ -471,7 +496,7 @@ int blitz_attn_decode(const void* q, int64_t q_stride, const void* kv_layer, con
   p.part_lse = p.part_o ? p.part_o + (int64_t)batch * q_heads * num_splits * head_dim : nullptr;
   p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size; p.max_pages = max_pages;
   p.num_splits = num_splits; p.box_tokens = bt; p.tail_box_tokens = bt_tail;
-  p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
+  p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status; p.trace = g_tc_trace;
   int rc;
   if (dtype == 1)
     rc = head_dim == 128 ? launch_tc<__nv_bfloat16, 128>(tm, tm_tail, p, batch, stream)
@@ -588,7 +613,7 @@ extern "C" int blitz_attn_decode_noalloc(const void* q, int64_t q_stride, const 
   p.part_lse = p.part_o + (int64_t)batch * q_heads * num_splits * head_dim;
   p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = G; p.page_size = page_size;
   p.max_pages = max_pages; p.num_splits = num_splits; p.box_tokens = bt; p.tail_box_tokens = bt_tail;
-  p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
+  p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status; p.trace = nullptr;
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
