@@ -24,6 +24,7 @@ void bind_router(py::module_& m) {
   py::class_<BatchQueue>(m, "BatchQueue")
       .def(py::init<uint32_t, uint32_t, std::optional<uint32_t>>(), py::arg("block_size") = 64, py::arg("speculate") = 0,
            py::arg("window") = std::nullopt)
+      .def("set_split_long_prompts", &BatchQueue::set_split_long_prompts)
       .def("append", &BatchQueue::append).def("__len__", &BatchQueue::size)
       .def_property_readonly("waiting_prefill_tokens", &BatchQueue::waiting_prefill_tokens)
       .def("mark_client_gone", &BatchQueue::mark_client_gone).def_property_readonly("dropped", &BatchQueue::dropped)
@@ -127,7 +128,7 @@ void bind_router(py::module_& m) {
       .def_readwrite("planner_interval_ms", &ControllerConfig::planner_interval_ms)
       .def_readwrite("model_layers", &ControllerConfig::model_layers).def_readwrite("model_name", &ControllerConfig::model_name)
       .def_readwrite("planner", &ControllerConfig::planner).def_readwrite("features", &ControllerConfig::features)
-      .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("quarantine_ms", &ControllerConfig::quarantine_ms).def_readwrite("max_batch_seqs", &ControllerConfig::max_batch_seqs).def_readwrite("kv_mb_per_token", &ControllerConfig::kv_mb_per_token).def_readwrite("max_incoming_migrations", &ControllerConfig::max_incoming_migrations).def_readwrite("kv_transfer_slots", &ControllerConfig::kv_transfer_slots).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
+      .def_readwrite("param_gb", &ControllerConfig::param_gb).def_readwrite("quarantine_ms", &ControllerConfig::quarantine_ms).def_readwrite("max_batch_seqs", &ControllerConfig::max_batch_seqs).def_readwrite("chunked_prefill", &ControllerConfig::chunked_prefill).def_readwrite("kv_mb_per_token", &ControllerConfig::kv_mb_per_token).def_readwrite("max_incoming_migrations", &ControllerConfig::max_incoming_migrations).def_readwrite("kv_transfer_slots", &ControllerConfig::kv_transfer_slots).def_readwrite("autoscale", &ControllerConfig::autoscale).def_readwrite("mock_load_ms", &ControllerConfig::mock_load_ms);
   m.def("parse_generations", [](py::bytes raw) {
     auto g = pbwire::parse_generations(static_cast<std::string>(raw));
     return py::make_tuple(g.request_ids, g.tokens, g.finished); },

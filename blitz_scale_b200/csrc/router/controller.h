@@ -78,6 +78,7 @@ struct ControllerConfig {
   // replica is not given a batch that would take its resident sequences beyond it (the batch waits for room, like one
   // that waits for free KV blocks).  0 = no limit.
   uint32_t max_batch_seqs = 256;
+  bool chunked_prefill = true;  // workers prefill a prompt longer than max_prefill_tokens in chunks: admit it alone
   int max_incoming_migrations = 1;
   int kv_transfer_slots = 8;
   double quarantine_ms = 5000;  // a lost replica is not chosen for scale-up again before this much time has passed
@@ -89,6 +90,7 @@ class Controller {
       : cfg_(cfg), features_(FeatureSet::parse(cfg.features)), queue_(cfg.block_size),
         steer_(cfg.machines.empty() ? std::vector<int>(cfg.num_ranks, 0) : cfg.machines, cfg.tp) {
     if (cfg.num_ranks % cfg.tp) throw std::invalid_argument("num_ranks not divisible by tp");
+    queue_.set_split_long_prompts(cfg.chunked_prefill);
     const int R = cfg.num_ranks / cfg.tp;
     reps_.resize(R);
     for (int r = 0; r < R; ++r) {

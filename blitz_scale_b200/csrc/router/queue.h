@@ -84,7 +84,11 @@ class BatchQueue {
       if (window_) max_new = std::min(max_new, *window_ > e.input_len ? *window_ - e.input_len : 0u);
       const uint32_t max_req = (e.input_len + max_new + block_ - 1) / block_ * block_;
       const bool over_blocks = block_budget && (max_req + max_tokens > *block_budget * block_);
-      const bool over_prefill = prefill_tokens + e.input_len > prefill_token_budget;
+      // with `split_long_prompts` a prompt that alone exceeds the prefill budget gets a batch of its own, which the
+      // worker prefills in chunks; without it (the reference's rule) such a prompt is never admitted, and validation
+      // has to keep it out of the queue
+      const bool over_prefill = prefill_tokens + e.input_len > prefill_token_budget &&
+                                !(split_long_prompts_ && out.entries.empty());
       const bool over_total = max_req + speculate_ > token_budget;
       const bool over_size = max_size > 0 && out.entries.size() >= max_size;
       if (over_blocks || over_prefill || over_total || over_size) {
@@ -118,12 +122,14 @@ class BatchQueue {
     }
   }
   uint64_t dropped() const { return dropped_; }
+  void set_split_long_prompts(bool on) { split_long_prompts_ = on; }
   // Prompt length of the entry at the head of the queue (0 when empty).
   uint32_t front_input_len() const { return entries_.empty() ? 0u : entries_.front().input_len; }
 
  private:
   uint32_t block_, speculate_;
   std::optional<uint32_t> window_;
+  bool split_long_prompts_ = false;
   std::deque<RequestEntry> entries_;
   uint64_t waiting_prefill_tokens_ = 0;
   uint64_t next_batch_id_ = 0;

@@ -445,6 +445,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--health-misses", type=int, default=2, help="consecutive missed pings that declare a replica lost")
     ap.add_argument("--rpc-timeout-ms", type=float, default=300000.0,
                     help="deadline of every worker RPC; a reply that never comes then counts as a failed replica (0 = none)")
+    ap.add_argument("--no-chunked-prefill", action="store_true",
+                    help="never admit a prompt longer than --max-batch-prefill-tokens (by default it gets a batch of its own, "
+                         "which the worker prefills in chunks; raise --max-input-length / --max-total-tokens to let such "
+                         "prompts through validation)")
     ap.add_argument("--max-batch-size", type=int, default=256,
                     help="sequences one worker step can carry; must equal the workers' --max-batch-size (0 = no limit)")
     ap.add_argument("--decode-steps-per-call", type=int, default=1,
@@ -508,6 +512,7 @@ def main(argv=None) -> None:
         min_decode=a.min_decode_num, max_decode=a.max_decode_num, scale_down_threshold_ms=a.scale_down_threshold_millis)
     cfg.quarantine_ms = a.quarantine_ms
     cfg.max_batch_seqs = max(0, a.max_batch_size)
+    cfg.chunked_prefill = not a.no_chunked_prefill
     cfg.max_incoming_migrations = max(1, a.max_incoming_migrations)
     layers = get_config(a.model_name).layers
     try:

@@ -175,6 +175,8 @@ class GpuBackend(Backend):
     def _continue_relayed(self, b, start_layer: int) -> List[int]:
         """Old-instance half of a relayed batch: take the residual stream from the mailbox and run layers [k, L)."""
         eng = self.engine
+        if b.num_prompt_tokens() > eng.max_batch_tokens:
+            raise RuntimeError(f"a relayed batch takes at most {eng.max_batch_tokens} prompt tokens")
         T, P = b.fill_prefill(eng.host_np, eng.layout)
         eng._h2d(eng.layout.page_indices + P)
         m = eng._views(T, b.size, P, True, b.prompt_lens())
@@ -262,6 +264,10 @@ class GpuBackend(Backend):
             b = self.engine.new_batch(batch.id, self._specs(batch))
             if b is None:
                 raise RuntimeError("out of KV pages")
+            if b.num_prompt_tokens() > self.engine.max_batch_tokens:
+                # a layer-interleaved task keeps its whole residual stream in one activation slot
+                b.clear()
+                raise RuntimeError(f"live execution takes at most {self.engine.max_batch_tokens} prompt tokens per batch")
             slot = self.zag.add_task(batch.id, zag_seq, b.num_prompt_tokens())
             if slot < 0:
                 b.clear()

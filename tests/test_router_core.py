@@ -47,6 +47,12 @@ def test_queue_token_and_block_budgets():
     assert len(q) == 1
     # prefill budget: a 20-token prompt does not fit in 19
     assert q.next_batch(None, 19, 1000) is None
+    # ... unless long prompts may be split by the worker: then it gets a batch of its own (and only the first one does)
+    q.append(E(7, 20, 12))
+    q.set_split_long_prompts(True)
+    nb = q.next_batch(None, 19, 1000)
+    assert nb.batch.size == 1 and nb.batch.prompt_tokens == 20 and len(q) == 1
+    q.set_split_long_prompts(False)
     # a single request larger than the total-token budget is never admitted
     assert q.next_batch(None, 1000, 31) is None
     assert q.next_batch(None, 1000, 32).batch.size == 1
@@ -448,6 +454,20 @@ def test_lost_role_is_restored_and_lost_replica_is_quarantined():
     ctl.set_reachable(0, True)
     again = [a for a in ctl.step(1.2) if a.type in (core.ActionType.NvlBroadcast, core.ActionType.RdmaBroadcast)]
     assert len(again) == 1 and again[0].dst_ranks == [0]
+
+
+def test_prompt_longer_than_the_prefill_budget_gets_a_batch_of_its_own():
+    """Workers prefill long prompts in chunks, so the controller admits such a prompt alone instead of leaving it at the
+    head of the queue for ever; with chunked prefill switched off it is never admitted (the reference's rule)."""
+    for chunked, want in ((True, 1), (False, 0)):
+        cfg = _cfg(["Prefill", "Decode"], "impl_blitz,impl_nvl,manually_scale", max_prefill_tokens=64, chunked_prefill=chunked)
+        ctl = core.Controller(cfg)
+        ctl.submit(E(1, 300, 4, 0.0))
+        ctl.submit(E(2, 20, 4, 0.0))
+        pf = [a for a in ctl.step(0.01) + ctl.step(0.02) if a.type == core.ActionType.Prefill]
+        assert len(pf) == want
+        if want:
+            assert list(pf[0].request_ids) == [1]            # alone: the short request behind it waits for the next batch
 
 
 def test_lost_participant_aborts_a_shared_parameter_transfer():
