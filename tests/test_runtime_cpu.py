@@ -213,6 +213,26 @@ def test_prefill_in_chunks_covers_every_token_once_with_growing_page_lists():
     b.clear()
 
 
+def test_prefill_attention_work_list_covers_every_row_pair_heaviest_first():
+    """One record per (sequence, 256 rows of it): offsets follow the packed rows and page lists of the pass, pairs that
+    walk more key blocks come first, and a later chunk (prefix already cached) counts its prefix."""
+    from blitz_scale_b200 import ops
+    q_lens, kv_lens, ps = [300, 128, 1, 77, 513], [300, 128, 1, 277, 769], 16
+    w = ops.prefill_work_list(q_lens, kv_lens, ps, "cpu").tolist()
+    assert len(w) == sum((n + 255) // 256 for n in q_lens)
+    row0 = np.concatenate([[0], np.cumsum(q_lens)])
+    pg0 = np.concatenate([[0], np.cumsum([(kv + ps - 1) // ps for kv in kv_lens])])
+    seen = set()
+    weights = []
+    for r0, n, p0, npg, kv, pair, z0, z1 in w:
+        b = int(np.searchsorted(row0, r0, side="right")) - 1
+        assert (r0, n, p0, npg, kv) == (row0[b], q_lens[b], pg0[b], (kv_lens[b] + ps - 1) // ps, kv_lens[b]) and z0 == z1 == 0
+        assert 0 <= pair < (n + 255) // 256 and (b, pair) not in seen
+        seen.add((b, pair))
+        weights.append(min(kv, kv - n + 256 * (pair + 1)))
+    assert weights == sorted(weights, reverse=True) and weights[0] == 769
+
+
 def test_batch_admission_is_all_or_nothing_and_eos_stops():
     pool = core.PagePool(4, 16)
     b = core.Batch(1, pool)
