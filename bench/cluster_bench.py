@@ -26,7 +26,6 @@ import json
 import os
 import sys
 import threading
-import time
 
 import torch
 import torch.distributed as dist

@@ -19,7 +19,6 @@ import asyncio
 import os
 import sys
 import threading
-import time
 
 import torch
 import torch.distributed as dist
