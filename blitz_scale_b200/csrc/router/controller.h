@@ -139,6 +139,7 @@ class Controller {
     rep.busy = false;
     ResidentBatch rb = std::move(op.batch);
     stats_prefill_tokens_ += rb.prompt_tokens;
+    const size_t before = rb.request_ids.size();
     deliver_tokens(rb, toks, now, true);
     if (op.kind == ActionType::ZagPrefill) {
       erase_inflight_zag(rep, rb.id);
@@ -158,6 +159,37 @@ class Controller {
         }
       }
       reps_[op.replica].relay_wait = false;
+      return;
+    }
+    if (op.kind == ActionType::Prefill && op.peer >= 0) {
+      // pushed layer by layer while it ran: the KV is on the decode replica already and the prefill replica has let
+      // go of its copy
+      release_blocks(op.replica, rb.blocks);
+      counters_["blitz_kv_cache_times"] += 1;
+      counters_["blitz_progressive_kv_cache_times"] += 1;
+      const double kv_mb = cfg_.kv_mb_per_token * rb.prompt_tokens;
+      rep.m.flow_out_mb += kv_mb;
+      reps_[op.peer].m.flow_in_mb += kv_mb;
+      if (rb.request_ids.empty()) {
+        release_blocks(op.peer, rb.blocks);
+        unlock_target(op.peer, rb.id);
+        out_.push_back(make_simple(ActionType::ClearCache, op.peer, rb.id));
+        return;
+      }
+      shrink_blocks(op.peer, rb);
+      if (rb.request_ids.size() == before) {
+        unlock_target(op.peer, rb.id);
+        reps_[op.peer].decode_batches.push_back(std::move(rb));
+        return;
+      }
+      // some requests ended at their first token: the decode replica drops them from the batch it received before
+      // it decodes it (the batch stays locked to the replica, and out of its steps, until that is done)
+      Action f = make_simple(ActionType::FilterBatch, op.peer, rb.id);
+      f.request_ids = rb.request_ids;
+      f.op_id = new_op(ActionType::FilterBatch, op.peer, -1, rb);
+      ops_[f.op_id].partial = kAdoptAfterFilter;
+      out_.push_back(f);
+      counters_["blitz_filtered_batches"] += 1;
       return;
     }
     if (rb.request_ids.empty()) {
@@ -214,6 +246,11 @@ class Controller {
     (void)now;
     if (late_answer(op_id)) return;
     Op op = take_op(op_id);
+    if (op.partial == kAdoptAfterFilter) {   // a progressively migrated batch: now it may join the replica's steps
+      unlock_target(op.replica, op.batch.id);
+      reps_[op.replica].decode_batches.push_back(std::move(op.batch));
+      return;
+    }
     reps_[op.replica].busy = false;
   }
 
@@ -495,6 +532,7 @@ class Controller {
     std::vector<uint64_t> incoming_batches;  // their batch ids (for the transfer-slot rule)
     uint32_t incoming_seqs = 0;              // sequences of those batches
   };
+  static constexpr int kAdoptAfterFilter = 3;   // Op::partial of a FilterBatch that precedes a batch's first decode step
   struct Op {
     ActionType kind;
     int replica = -1, peer = -1, partial = 0;
@@ -739,8 +777,20 @@ class Controller {
     rep.m.used_blocks += rb.blocks;
     for (auto& e : nb->entries) requests_[e.id].t_batched = now;
     rep.busy = true;
+    // Layer-progressive migration (`PREFILL_CASE_MIGRATE_PROGRESSIVE`, proto/generate.proto:315-326; the reference
+    // declares the case and never issues it): the decode replica is chosen now and reserves its pages while the prefill
+    // runs, and the prefill replica pushes every layer's KV as soon as that layer has run.  Without a free decode
+    // replica at this moment the batch takes the ordinary path (prefill, then a migration of all layers).
+    int dst = -1;
+    if (features_.has("migrate_progressive") && !rep.colocated && !no_decode_side())
+      dst = pick_decode_target(rb.blocks, rb.id, rb.request_ids.size());
     Action a = make_simple(ActionType::Prefill, r, rb.id);
-    a.op_id = new_op(ActionType::Prefill, r, -1, rb);
+    if (dst >= 0) {
+      acquire_target(dst, rb.blocks, rb.id, rb.request_ids.size());
+      a.peer = dst;
+      a.src_ranks = steer_.ranks_of_replica(r); a.dst_ranks = steer_.ranks_of_replica(dst);
+    }
+    a.op_id = new_op(ActionType::Prefill, r, dst, rb);
     a.request_ids = rb.request_ids; a.max_tokens = rb.max_tokens;
     out_.push_back(a);
     return true;
@@ -1306,11 +1356,27 @@ class Controller {
         case ActionType::Prefill:
         case ActionType::ZagPrefill:
           requeue_ids(o.batch.request_ids);  // nothing was delivered yet
+          if (o.kind == ActionType::Prefill && o.peer >= 0) {
+            // a progressive migration: the surviving side gives back what it holds for the batch
+            release_blocks(other, o.batch.blocks);
+            if (o.replica == r) unlock_target(other, o.batch.id);
+            else reps_[other].busy = false;
+            incoming_seqs_of_.erase(o.batch.id);
+            out_.push_back(make_simple(ActionType::ClearCache, other, o.batch.id));
+            cancel(id, o.batch.id, {other});
+            break;
+          }
           cancel(id, o.batch.id, {});
           break;
         case ActionType::Decode:
         case ActionType::FilterBatch:
-          cancel(id, o.batch.id, {});        // its batches are resident on the lost replica: failed below
+          // its batches are resident on the lost replica: failed below (a batch that waits for its filter before it
+          // joins the replica's steps is known by the operation only)
+          if (o.partial == kAdoptAfterFilter) {
+            fail_ids(o.batch.request_ids);
+            incoming_seqs_of_.erase(o.batch.id);
+          }
+          cancel(id, o.batch.id, {});
           break;
         case ActionType::Migrate:
           fail_ids(o.batch.request_ids);

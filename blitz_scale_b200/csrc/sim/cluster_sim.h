@@ -144,7 +144,10 @@ class ClusterSim {
   void handle(const Action& a, double now, SimReport& rep, std::map<int, double>& load_started) {
     switch (a.type) {
       case ActionType::Prefill: {
-        const double d = cm_.rpc_overhead_s + cm_.prefill_overhead_s + tokens_of(a.request_ids) / cm_.prefill_tokens_per_s;
+        double d = cm_.rpc_overhead_s + cm_.prefill_overhead_s + tokens_of(a.request_ids) / cm_.prefill_tokens_per_s;
+        // layer-progressive migration: every layer's KV leaves while the next layers run; only the last layer's
+        // push comes after the pass
+        if (a.peer >= 0) d += tokens_of(a.request_ids) / cm_.kv_tokens_per_s / std::max(1, cm_.layers);
         push(now + d, a);
         break;
       }

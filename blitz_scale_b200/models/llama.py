@@ -197,10 +197,14 @@ class LlamaRunner:
         return self.tokens[:B]
 
     def forward(self, m: StepMeta, lo: int = 0, hi: Optional[int] = None, with_embed: bool = True,
-                with_head: bool = True) -> Optional[torch.Tensor]:
+                with_head: bool = True, after_layer=None) -> Optional[torch.Tensor]:
+        """`after_layer(l)` is called once layer l's kernels are in the stream (its K/V stores among them): the hook
+        of a layer-progressive KV migration."""
         hi = self.cfg.layers if hi is None else hi
         if with_embed:
             self.embed(m)
         for l in range(lo, hi):
             self.run_layer(l, m)
+            if after_layer is not None:
+                after_layer(l)
         return self.head(m) if with_head else None

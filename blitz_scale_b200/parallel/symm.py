@@ -180,13 +180,15 @@ class PeerFabric:
     def kv_push(self, dst_rank: int, src_pages: torch.Tensor, dst_pages: torch.Tensor, layer_begin: int,
                 layer_end: int, page_bytes: int, src_layer_stride: int, dst_layer_stride: int, src_max_pages: int,
                 dst_max_pages: int, flag_slot: Optional[int] = None, ctas_per_layer: int = 0,
-                dst_pages_ptr: int = 0, dst_count_ptr: int = 0, n_pages: Optional[int] = None) -> None:
+                dst_pages_ptr: int = 0, dst_count_ptr: int = 0, n_pages: Optional[int] = None,
+                done: bool = True) -> None:
         """Store prompt pages of layers [layer_begin, layer_end) into `dst_rank`'s pool using its page ids.
 
         ``dst_pages`` is a local int32 tensor, or None with ``dst_pages_ptr`` the address (possibly in the peer's
         memory) of the ids the destination published; ``dst_count_ptr`` then names the count it published, which
         the kernel compares with the number of source pages.  With a ``flag_slot`` the slot's completion counter
-        on the destination is bumped after the push (stream order: after every layer has been stored)."""
+        on the destination is bumped after the push (stream order: after every layer has been stored); a transfer
+        made of several calls passes ``done=False`` on all but its last one."""
         assert src_pages.dtype == torch.int32 and (dst_pages is None or dst_pages.dtype == torch.int32)
         nl = layer_end - layer_begin
         tick = self.tickets[1024:1024 + nl]
@@ -203,5 +205,5 @@ class PeerFabric:
                                     ctypes.c_void_p(tick.data_ptr()), ctas_per_layer, ctypes.c_void_p(dst_count_ptr),
                                     ctypes.c_void_p(status_word(self.device).data_ptr()), _stream())
         _check(rc, "blitz_kv_push")
-        if flag_slot is not None:
+        if flag_slot is not None and done:
             self.set_flag(dst_rank, KV_DONE_FLAG0 + flag_slot, 1, add=True)

@@ -356,7 +356,16 @@ class RouterRuntime:
     async def _do_prefill(self, a) -> None:
         batch = self._batch_proto(a)
         ranks = self._ranks(a.replica)
-        if a.type == A.Prefill:
+        holder = a.replica          # the replica that holds the batch's KV when the call returns
+        if a.type == A.Prefill and a.peer >= 0:
+            # layer-progressive migration: the decode replica reserves and publishes its pages while the prefill
+            # replica runs the pass and pushes each layer behind it; shard i pushes to shard i
+            src, dst = list(a.src_ranks), list(a.dst_ranks)
+            case = encode_prefill_case(pb.PREFILL_CASE_NORMAL, pb.PREFILL_CASE_MIGRATE_PROGRESSIVE)
+            calls = [self.stubs[r].prefill_v2(batch, case, None, dst) for r in src] + \
+                    [self.stubs[r].immigrate(batch, src, dst, 0, 0) for r in dst]
+            ranks, holder = src + dst, a.peer
+        elif a.type == A.Prefill:
             calls = [self.stubs[r].prefill_v2(batch, pb.PREFILL_CASE_NORMAL) for r in ranks]
         elif a.type == A.ZagPrefill:
             calls = [self.stubs[r].zag_prefill(batch, a.zag_seq, self.layers, pb.PREFILL_CASE_NAIVE_PP) for r in ranks]
@@ -368,16 +377,19 @@ class RouterRuntime:
                 pp.tfm_layer = a.num_layer
             case = encode_prefill_case(pb.PREFILL_CASE_NAIVE_PP, pb.PREFILL_CASE_IMMIGRATE)
             calls = [self.stubs[r].prefill_v2(batch, case, pp, a.dst_ranks) for r in ranks]
-        res = (await self._all(ranks, calls))[0]
+        answers = await self._all(ranks, calls)
+        res = answers[0]
         if a.type == A.ZagPrefill and not res.generations and res.HasField("pp_info"):
             # taken over by a relay: the relay completion reports the hand-over to the core
             which = res.pp_info.WhichOneof("start_layer")
             self._zag_pp[a.batch_id] = res.pp_info.tfm_layer if which == "tfm_layer" else 0
             return
-        if res.HasField("batch"):
+        if holder != a.replica:
+            self._remember(holder, answers[-1].batch)
+        elif res.HasField("batch"):
             self._remember(a.replica, res.batch)
         ids, toks, fins = core.parse_generations(res.raw)
-        if (a.replica, a.batch_id) in self.cached:      # somebody will decode this batch: its first tokens travel with the first step
+        if (holder, a.batch_id) in self.cached:      # somebody will decode this batch: its first tokens travel with the first step
             self.first_tokens[a.batch_id] = {i: t for i, t in zip(ids, toks) if t >= 0}
         now = self.now()
         self.ctl.on_prefill_done_lists(a.op_id, ids, toks, fins, now)

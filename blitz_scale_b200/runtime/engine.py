@@ -130,14 +130,17 @@ class Engine:
 
     # ------------------------------------------------------------------ steps
     @torch.no_grad()
-    def prefill(self, batch: "core.Batch") -> List[int]:
-        """Run the prompt of every request in `batch`, cache its K/V and return the first token of each."""
+    def prefill(self, batch: "core.Batch", after_layer=None) -> List[int]:
+        """Run the prompt of every request in `batch`, cache its K/V and return the first token of each.
+
+        `after_layer(l)` is called when every K/V row of layer l is in the stream that runs the pass (in a prefill of
+        several windows: during the last window), so that a caller can send the layer away while the next ones run."""
         if not self.status.fully_loaded():
             raise RuntimeError("model parameters are not loaded")
         if batch.size > self.max_batch:
             raise ValueError(f"prefill batch of {batch.size} sequences exceeds max_batch={self.max_batch}")
         if batch.num_prompt_tokens() > self.max_batch_tokens:
-            toks = self._prefill_in_chunks(batch)
+            toks = self._prefill_in_chunks(batch, after_layer)
             toks = self._sample_rows(batch, batch.size, toks)
             out = self._tokens_to_host(toks, batch.size)
             batch.mark_prefilled()
@@ -149,7 +152,7 @@ class Engine:
         lens = batch.prompt_lens()
         m = self._views(T, batch.size, P, True, lens)
         with nvtx_range("prefill"):
-            toks = self.runner.forward(m)
+            toks = self.runner.forward(m, after_layer=after_layer)
         toks = self._sample_rows(batch, batch.size, toks)
         out = self._tokens_to_host(toks, batch.size)
         batch.mark_prefilled()
@@ -157,7 +160,7 @@ class Engine:
         batch.decode = True
         return out
 
-    def _prefill_in_chunks(self, batch: "core.Batch") -> torch.Tensor:
+    def _prefill_in_chunks(self, batch: "core.Batch", after_layer=None) -> torch.Tensor:
         """Prompts that together exceed `max_batch_tokens` (one prompt alone may): passes over windows of that many
         tokens of the prompts laid end to end.  A window's rows attend to the cache, which holds what earlier windows
         stored for the same sequence; the state of every sequence's last token is kept when its prompt ends, and the
@@ -177,7 +180,7 @@ class Engine:
                 self._h2d(self.layout.page_indices + P)
                 m = self._views(T, rows, P, True, q_lens, kv_lens=kv_lens)
                 with nvtx_range("prefill_chunk"):
-                    runner.forward(m, with_head=False)
+                    runner.forward(m, with_head=False, after_layer=after_layer if tok0 + T >= total else None)
                     if any(ended):
                         last = runner.last_rows(m)
                         for r, e in enumerate(ended):

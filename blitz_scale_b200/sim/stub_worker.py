@@ -43,7 +43,7 @@ class StubBackend(Backend):
         self.zag_relayed: Dict[int, int] = {}
         self.transfer_done = threading.Event()
         self.transfer_done.set()
-        self.counters = {"prefill": 0, "decode": 0, "migrate": 0, "immigrate": 0}
+        self.counters = {"prefill": 0, "decode": 0, "migrate": 0, "immigrate": 0, "migrate_progressive": 0}
 
     # ------------------------------------------------------------------ helpers
     def info(self) -> dict:
@@ -92,11 +92,17 @@ class StubBackend(Backend):
             gens = self._emit(b, toks)
             b.filter(b.unfinished_ids())
             b.decode = True
+            self.counters["prefill"] += 1
+            if forward_case & pb.PREFILL_CASE_MIGRATE_PROGRESSIVE and pipe_peer:
+                # every layer's KV went to the decode replica as the layer ran: nothing of the batch stays here
+                self.counters["migrate_progressive"] += 1
+                self.batches.pop(b.id, None)
+                b.clear()
+                return gens, None, None
             if b.size:
                 self.batches[b.id] = b
             else:
                 self.batches.pop(b.id, None)
-            self.counters["prefill"] += 1
             return gens, self._cached(b) if b.size else None, None
 
     def zag_prefill(self, batch, forward_case, pp_info, zag_layers, zag_seq):

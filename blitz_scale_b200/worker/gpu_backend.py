@@ -166,11 +166,58 @@ class GpuBackend(Backend):
                 if pp_info is not None and pp_info.WhichOneof("start_layer") == "tfm_layer":
                     start = int(pp_info.tfm_layer)
                 toks = self._continue_relayed(b, start)
+            elif forward_case & pb.PREFILL_CASE_MIGRATE_PROGRESSIVE and pipe_peer:
+                if self.fabric is None:
+                    b.clear()
+                    raise RuntimeError("a layer-progressive migration needs the peer fabric")
+                try:
+                    toks = self._prefill_pushing(b, batch, list(pipe_peer))
+                    ops.check_status()
+                    gens, _ = self._finish_step(b, toks)
+                finally:
+                    # every layer has left for the decode replica (or the call failed): nothing of the batch stays
+                    self.batches.pop(b.id, None)
+                    b.clear()
+                return gens, None, None
             else:
                 toks = self.engine.prefill(b)
             ops.check_status()
             gens, cb = self._finish_step(b, toks)
             return gens, cb, None
+
+    def _prefill_pushing(self, b, batch, dst) -> List[int]:
+        """Prefill with a layer-progressive migration (`PREFILL_CASE_MIGRATE_PROGRESSIVE`, proto/generate.proto:315-326;
+        the reference declares the case and never runs it): layer l's pages are stored into the decode replica's pool
+        on the transfer stream as soon as layer l has run, so only the last layer's push is left when the pass ends.
+        The decode replica's `immigrate` runs at the same time and publishes its page ids under the transfer's tag,
+        as for a migration of all layers; shard i pushes to shard i."""
+        peer = dst[self.rank % self.tp]
+        slot = batch.id % symm.KV_SLOTS
+        src_ids = self._rpc_page_list(b, batch)
+        L = self.cfg.layers
+        main = torch.cuda.current_stream()
+        log.info("batch %d prefill, layers pushed as they run -~> rank %d", batch.id, peer)
+        with self.xfer_lock:
+            with torch.cuda.stream(self.side):
+                src_pages = torch.tensor(src_ids, dtype=torch.int32, device=self.device)
+                # the first push waits (on the transfer stream only) until the destination has published its page ids
+                tag_ptr = self.ctl.ptrs[peer] + (symm.KV_SLOTS * CTL_SLOT_WORDS + slot) * 4
+                self.fabric.wait_flag_eq(tag_ptr, self._kv_tag(batch.id, 0), budget_ms=10000)
+            count_ptr = self.ctl.ptrs[peer] + slot * CTL_SLOT_WORDS * 4
+
+            def after_layer(l: int) -> None:
+                ran = torch.cuda.Event()
+                ran.record(main)
+                self.side.wait_event(ran)
+                with torch.cuda.stream(self.side):
+                    self.fabric.kv_push(peer, src_pages, None, l, l + 1, self.page_bytes, self.kv_layer_stride,
+                                        self.kv_layer_stride, self.engine.num_pages, self.engine.num_pages,
+                                        flag_slot=slot, dst_pages_ptr=count_ptr + 4, dst_count_ptr=count_ptr,
+                                        done=(l == L - 1))
+            try:
+                return self.engine.prefill(b, after_layer=after_layer if src_ids else None)
+            finally:
+                self.side.synchronize()
 
     def _continue_relayed(self, b, start_layer: int) -> List[int]:
         """Old-instance half of a relayed batch: take the residual stream from the mailbox and run layers [k, L)."""

@@ -68,7 +68,8 @@ def main():
     from blitz_scale_b200.worker.service import serve
     tp = 2 if case.endswith("_tp2") else 1
     case = case[:-4] if tp == 2 else case
-    replica_states = {"pd": ["Prefill", "Decode"], "scale": ["Prefill", "Decode", "Inactive"],
+    replica_states = {"pd": ["Prefill", "Decode"], "pd_progressive": ["Prefill", "Decode"],
+                      "scale": ["Prefill", "Decode", "Inactive"],
                       "live": ["Prefill", "Decode", "Inactive"]}[case][:world // tp]
     states = [s for s in replica_states for _ in range(tp)]          # one entry per rank
     tp_group = None
@@ -143,6 +144,7 @@ def run_router(case, world, states, base_port, tp=1, ref=None) -> int:
     if ref is None:
         ref = reference_tokens(prompts, news)
     feats = {"pd": "impl_blitz,impl_nvl,manually_scale", "scale": "impl_blitz,impl_nvl,manually_scale",
+             "pd_progressive": "impl_blitz,impl_nvl,manually_scale,migrate_progressive",
              "live": "impl_blitz,impl_nvl,impl_live,manually_scale"}[case]
     cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, tp, feats,
                                          max_blocks_per_replica=200, block_size=16, max_prefill_tokens=1024,
@@ -181,11 +183,12 @@ def run_router(case, world, states, base_port, tp=1, ref=None) -> int:
             got += await asyncio.gather(*extra)
         trans = [l for _, l in rt.transitions]
         used = rt.ctl.total_used_blocks()
+        counters = dict(rt.ctl.counters())
         await rt.stop()
         loop_task.cancel()
-        return got, trans, used
+        return got, trans, used, counters
 
-    got, trans, used = asyncio.run(go())
+    got, trans, used, counters = asyncio.run(go())
     want = ref + (ref if len(got) > n_req else [])
     total = agree = 0
     for gtoks, w in zip(got, want):
@@ -195,6 +198,11 @@ def run_router(case, world, states, base_port, tp=1, ref=None) -> int:
     print(f"token agreement {agree}/{total}; transitions: {[t for t in trans if 'boot' not in t]}")
     assert agree >= 0.9 * total, (agree, total)
     assert used == 0
+    if case == "pd_progressive":
+        # batches whose KV left the prefill replica layer by layer while they ran
+        print(f"kv transfers {counters.get('blitz_kv_cache_times', 0):.0f}, of which layer-progressive "
+              f"{counters.get('blitz_progressive_kv_cache_times', 0):.0f}")
+        assert counters.get("blitz_progressive_kv_cache_times", 0) > 0
     if case == "scale":
         assert any("Replica<2> LoadingPrefill => Prefill" in t for t in trans)
     if case == "live":

@@ -469,6 +469,41 @@ def test_nothing_is_left_behind_after_many_requests():
     assert asyncio.run(go()) == (0, 0, 0, 0, 0, 0, True, [0, 0, 0], [0, 0, 0])
 
 
+def test_progressive_migration_over_grpc_gives_the_same_tokens_and_leaves_nothing_behind():
+    """`migrate_progressive`: the prefill call and the decode replica's immigrate run side by side, the batch decodes on
+    the decode replica without a Migrate round, requests that end at their first token are filtered out there, and the
+    tokens are the ones the ordinary path gives."""
+    async def go(features):
+        rt, backends, port, stop, tasks = await _cluster(3, ["Prefill", "Decode", "Decode"], features, autoscale=False)
+        for b in backends:
+            b.decode_step_s, b.prefill_rate = 0.0, 1e12
+
+        async def one(i):
+            lr = rt.submit(list(range(8 + i % 50)), 1 + (i * 7) % 12)
+            assert (await asyncio.wait_for(lr.done, timeout=60)) is None
+            return list(lr.tokens)
+        toks = []
+        for wave in range(2):
+            toks += await asyncio.gather(*[one(wave * 60 + i) for i in range(60)])
+        for _ in range(100):
+            if rt.ctl.idle() and not rt.cached and all(not b.batches for b in backends):
+                break
+            await asyncio.sleep(0.05)
+        state = (len(rt.requests), len(rt.cached), len(rt.first_tokens), rt.ctl.inflight_ops(), rt.ctl.total_used_blocks(),
+                 [len(b.batches) for b in backends], [b.pool.used_pages for b in backends])
+        counters = dict(rt.ctl.counters()), [dict(b.counters) for b in backends]
+        await _shutdown(stop, tasks)
+        return toks, state, counters
+    plain, state0, _ = asyncio.run(go("impl_blitz,impl_nvl"))
+    prog, state1, (ctl_counters, worker_counters) = asyncio.run(go("impl_blitz,impl_nvl,migrate_progressive"))
+    assert prog == plain
+    assert state0 == state1 == (0, 0, 0, 0, 0, [0, 0, 0], [0, 0, 0])
+    assert ctl_counters["blitz_progressive_kv_cache_times"] > 0
+    assert worker_counters[0]["migrate_progressive"] == ctl_counters["blitz_progressive_kv_cache_times"]
+    assert worker_counters[0]["migrate"] == ctl_counters["blitz_kv_cache_times"] - ctl_counters["blitz_progressive_kv_cache_times"]
+    assert ctl_counters.get("blitz_filtered_batches", 0) > 0      # some requests ask for one token only
+
+
 def test_several_decode_steps_per_call_give_the_same_tokens():
     """With k decode steps per DecodeV2 call the token streams are those of one step per call; tokens arrive up to k
     at a time, requests still stop at their own length, and nothing is left behind."""

@@ -702,3 +702,90 @@ def test_colocated_replica_never_exceeds_its_step_size():
                 ctl.on_decode_done(a.op_id, [core.TokenOut(i, 2, False) for i in a.request_ids], t)
         peak = max(peak, len(held))
     assert peak == 8 and prefills >= 4 and ctl.idle() and not held
+
+
+def test_progressive_migration_places_the_batch_at_prefill_dispatch():
+    """With `migrate_progressive` the decode replica is chosen and locked when the prefill is issued; when the prefill
+    answers, the batch is on the decode replica (no Migrate action), the prefill replica holds nothing, and requests
+    that ended at their first token are filtered out of the received batch before its first decode step."""
+    A = core.ActionType
+    cfg = _cfg(["Prefill", "Decode"], "impl_blitz,impl_nvl,migrate_progressive", autoscale=False)
+    ctl = core.Controller(cfg)
+    ctl.set_compact_deliveries(True)
+    for i in range(3):
+        ctl.submit(E(i, 100, 1 if i == 1 else 20))
+    pf = [a for a in ctl.step(0.0) if a.type == A.Prefill]
+    assert len(pf) == 1 and pf[0].replica == 0 and pf[0].peer == 1
+    assert list(pf[0].src_ranks) == [0] and list(pf[0].dst_ranks) == [1]
+    assert ctl.metric(0).used_blocks > 0 and ctl.metric(0).used_blocks == ctl.metric(1).used_blocks
+    # a second batch finds the only decode replica locked and takes the ordinary path (after the first has answered)
+    ctl.submit(E(7, 64, 4))
+    assert not [a for a in ctl.step(0.005) if a.type == A.Prefill]
+    ctl.on_prefill_done(pf[0].op_id, [core.TokenOut(0, 5, False), core.TokenOut(1, 5, True), core.TokenOut(2, 5, False)], 0.01)
+    assert ctl.metric(0).used_blocks == 0
+    acts = ctl.step(0.02)
+    assert not [a for a in acts if a.type == A.Migrate]
+    flt = [a for a in acts if a.type == A.FilterBatch]
+    assert len(flt) == 1 and flt[0].replica == 1 and sorted(flt[0].request_ids) == [0, 2]
+    assert not [a for a in acts if a.type == A.Decode]                 # not before the filter has been applied
+    nxt = [a for a in acts if a.type == A.Prefill]
+    assert len(nxt) == 1 and nxt[0].peer == -1                         # the decode replica is still locked by the first batch
+    ctl.on_filter_done(flt[0].op_id, 0.03)
+    dec = [a for a in ctl.step(0.04) if a.type == A.Decode]
+    assert len(dec) == 1 and dec[0].replica == 1 and sorted(dec[0].request_ids) == [0, 2]
+    assert ctl.counters()["blitz_progressive_kv_cache_times"] == 1
+    # nothing finished at the first token: the batch joins the decode replica as soon as the prefill answers
+    ctl.on_prefill_done(nxt[0].op_id, [core.TokenOut(7, 5, False)], 0.05)
+    ctl.on_decode_done(dec[0].op_id, [core.TokenOut(0, 6, False), core.TokenOut(2, 6, False)], 0.05)
+    acts = ctl.step(0.06)
+    mig = [a for a in acts if a.type == A.Migrate]
+    assert len(mig) == 1                                               # the ordinary path for the second batch
+    ctl.on_migrate_done(mig[0].op_id, 0.07)
+    ctl.submit(E(8, 64, 4))
+    pf = [a for a in ctl.step(0.08) if a.type == A.Prefill]
+    assert len(pf) == 1 and pf[0].peer == 1
+    ctl.on_prefill_done(pf[0].op_id, [core.TokenOut(8, 5, False)], 0.09)
+    assert not [a for a in ctl.step(0.1) if a.type in (A.FilterBatch, A.Migrate)]
+    assert ctl.metric(0).used_blocks == 0 and ctl.metric(1).used_blocks > 0
+
+
+@pytest.mark.parametrize("lost", ["source", "destination"])
+def test_progressive_migration_survives_the_loss_of_either_side(lost):
+    A = core.ActionType
+    cfg = _cfg(["Prefill", "Decode", "Prefill", "Decode"], "impl_blitz,impl_nvl,migrate_progressive", autoscale=False)
+    ctl = core.Controller(cfg)
+    ctl.submit(E(1, 100, 8))
+    pf = [a for a in ctl.step(0.0) if a.type == A.Prefill][0]
+    src, dst = pf.replica, pf.peer
+    assert dst >= 0
+    gone, kept = (src, dst) if lost == "source" else (dst, src)
+    ctl.on_failure(pf.op_id, 0.01, gone)
+    assert ctl.state_name(gone) == "Inactive" and ctl.state_name(kept) != "Inactive"
+    acts = ctl.step(0.01)
+    assert not [a for a in acts if a.type == A.Fail]                   # nothing was delivered: the prompt is served again
+    assert any(a.type == A.ClearCache and a.replica == kept for a in acts)
+    again = [a for a in acts if a.type == A.Prefill]
+    assert len(again) == 1 and again[0].replica not in (gone,) and again[0].peer != gone
+    assert ctl.metric(kept).used_blocks == (0 if kept not in (again[0].replica, again[0].peer) else ctl.metric(kept).used_blocks)
+    ctl.on_prefill_done(pf.op_id, [core.TokenOut(1, 5, False)], 0.02)   # the late answer of the cancelled call is ignored
+    ctl.on_prefill_done(again[0].op_id, [core.TokenOut(1, 5, False)], 0.03)
+    acts = ctl.step(0.04)
+    holder = again[0].peer if again[0].peer >= 0 else again[0].replica
+    if again[0].peer < 0:
+        mig = [a for a in acts if a.type == A.Migrate]
+        assert len(mig) == 1
+        ctl.on_migrate_done(mig[0].op_id, 0.05)
+        holder = mig[0].peer
+        acts = ctl.step(0.06)
+    dec = [a for a in acts if a.type == A.Decode]
+    assert len(dec) == 1 and dec[0].replica == holder
+
+
+def test_sim_progressive_migration_conserves_requests_and_pages():
+    cfg = _cfg(["Prefill", "Decode", "Prefill", "Decode"], "impl_blitz,impl_nvl,migrate_progressive", autoscale=False)
+    trace = _trace([(0, 6.0)], 40.0, n=240, seed=2, out=(1, 64))
+    sim = core.ClusterSim(cfg, core.CostModel())
+    rep = sim.run(trace)
+    _check_conservation(rep, trace)
+    c = sim.controller().counters()
+    assert c["blitz_progressive_kv_cache_times"] > 0 and c["blitz_kv_cache_times"] >= c["blitz_progressive_kv_cache_times"]

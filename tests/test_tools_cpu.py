@@ -276,12 +276,7 @@ def test_otlp_span_export_logging_and_cors(tmp_path):
     assert rec["startTimeUnixNano"] == "10" and rec["status"]["code"] == 2
     assert {a["key"]: list(a["value"])[0] for a in rec["attributes"]} == {"n": "intValue", "f": "doubleValue", "s": "stringValue", "b": "boolValue"}
 
-    def free_port():
-        s = socket.socket()
-        s.bind(("127.0.0.1", 0))
-        p = s.getsockname()[1]
-        s.close()
-        return p
+    cport, aport, *worker_ports = _free_ports(4)
 
     async def go():
         got = []
@@ -293,10 +288,9 @@ def test_otlp_span_export_logging_and_cors(tmp_path):
         capp.router.add_post("/v1/traces", collect)
         crun = web.AppRunner(capp, access_log=None)
         await crun.setup()
-        cport = free_port()
         await web.TCPSite(crun, "127.0.0.1", cport).start()
 
-        ports = [free_port(), free_port()]
+        ports = worker_ports
         stop, tasks = asyncio.Event(), []
         for r in range(2):
             ready = asyncio.Event()
@@ -314,7 +308,6 @@ def test_otlp_span_export_logging_and_cors(tmp_path):
         app = RouterApp(rt, model_name="tiny", cors_allow_origin=["http://ui.example"])
         arun = web.AppRunner(app.app, access_log=None)
         await arun.setup()
-        aport = free_port()
         await web.TCPSite(arun, "127.0.0.1", aport).start()
         import aiohttp
         async with aiohttp.ClientSession() as s:
