@@ -104,6 +104,7 @@ class GpuBackend(Backend):
         # they overlap the serving kernels of the default stream instead of queueing between decode steps
         self.side = torch.cuda.Stream(device=self.device, priority=-1)
         self.xfer_lock = threading.Lock()      # one transfer at a time uses the side stream and the ticket words
+        self.progressive_push_ctas = 16        # CTAs of one layer's push while the prefill pass goes on beside it
         self._poll_stream = torch.cuda.Stream(device=self.device)
         self._kv_slot_busy = [False] * symm.KV_SLOTS   # incoming KV transfers: slot reserved until the push has completed
         self._kv_done_want = [0] * symm.KV_SLOTS       # pushes started per slot = value its completion counter will reach
@@ -213,7 +214,7 @@ class GpuBackend(Backend):
                     self.fabric.kv_push(peer, src_pages, None, l, l + 1, self.page_bytes, self.kv_layer_stride,
                                         self.kv_layer_stride, self.engine.num_pages, self.engine.num_pages,
                                         flag_slot=slot, dst_pages_ptr=count_ptr + 4, dst_count_ptr=count_ptr,
-                                        done=(l == L - 1))
+                                        done=(l == L - 1), ctas_per_layer=self.progressive_push_ctas)
             try:
                 return self.engine.prefill(b, after_layer=after_layer if src_ids else None)
             finally:

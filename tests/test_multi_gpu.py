@@ -23,7 +23,7 @@ def _run(case, nproc, extra_env=None):
     return res.stdout
 
 
-@pytest.mark.parametrize("case,n", [("pd", 2), ("scale", 3), ("live", 3), ("pd_tp2", 4)])
+@pytest.mark.parametrize("case,n", [("pd", 2), ("pd_progressive", 2), ("scale", 3), ("live", 3), ("pd_tp2", 4)])
 def test_gpu_cluster_end_to_end(case, n):
     """GPU workers over gRPC + router runtime: PD with in-kernel KV push, scale-out by parameter multicast, live scaling."""
     if _ngpu() < n:
