@@ -394,6 +394,51 @@ def test_migration_to_dead_decode_replica_blames_the_destination():
     asyncio.run(go())
 
 
+def test_progressive_migration_to_dead_decode_replica_serves_the_prompt_again():
+    """As above with `migrate_progressive`: the decode replica is already part of the prefill call, so its loss is
+    noticed while the prompt has produced nothing; the prompt is queued again and the prefill replica, now alone,
+    serves it completely (no token is lost, nothing fails)."""
+    async def go():
+        ports = _free_ports(2)
+        stops, tasks = [], []
+        backends = [StubBackend(r, 2, ready=True) for r in range(2)]
+        for r, b in enumerate(backends):
+            ready, stop = asyncio.Event(), asyncio.Event()
+            tasks.append(asyncio.create_task(serve(b, "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
+            await ready.wait()
+            stops.append(stop)
+        cfg = controller_config_from_cluster({"init_states": ["Prefill", "Decode"], "machines": [0] * 2}, 1,
+                                             "impl_blitz,impl_nvl,migrate_progressive", max_blocks_per_replica=4000)
+        rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2)
+        lt = asyncio.create_task(rt.run())
+
+        async def run_one(n_new):
+            lr = rt.submit(list(range(40)), n_new)
+            evs = []
+            while True:
+                ev = await asyncio.wait_for(lr.queue.get(), timeout=20)
+                evs.append(ev)
+                if ev[0] == "error" or ev[2]:
+                    return evs
+        assert len(await run_one(4)) == 4
+        assert backends[0].counters["migrate_progressive"] == 1 and backends[0].counters["migrate"] == 0
+        stops[1].set()
+        await asyncio.wait([tasks[1]], timeout=5)
+        evs = await run_one(4)
+        assert [e[0] for e in evs] == ["token"] * 4 and evs[-1][2]
+        assert rt.ctl.state_name(1) == "Inactive" and rt.ctl.state_name(0) == "Prefill"
+        for _ in range(100):
+            if rt.ctl.idle() and not backends[0].batches:
+                break
+            await asyncio.sleep(0.02)
+        assert rt.ctl.total_used_blocks() == 0 and backends[0].pool.used_pages == 0
+        await rt.stop()
+        lt.cancel()
+        stops[0].set()
+        await asyncio.wait(tasks, timeout=5)
+    asyncio.run(go())
+
+
 def test_dropped_immigrate_reply_fails_the_operation_not_the_router():
     """A decode worker accepts the Immigrate call and never answers (host-side fault: its handler blocks).  The RPC
     deadline turns that into a failed operation: the silent replica is declared lost, its batch fails, and the next

@@ -12,7 +12,8 @@ from blitz_scale_b200.runtime import core  # noqa: E402
 FEATURES = ["impl_blitz,impl_nvl", "impl_blitz,impl_nvl,impl_live", "impl_blitz,impl_fast_pro,impl_live_pro",
             "impl_blitz,impl_nvl,impl_tanz", "impl_blitz,impl_nvl,mutate", "impl_sllm,cache_replace",
             "impl_sllm,cache_all_miss", "impl_blitz,impl_nvl,unidirect", "impl_blitz,impl_nvl,prefill_share_idle",
-            "impl_blitz,impl_nvl,impl_live,decode_first_fit"]
+            "impl_blitz,impl_nvl,impl_live,decode_first_fit", "impl_blitz,impl_nvl,migrate_progressive",
+            "impl_blitz,impl_fast_pro,impl_live_pro,migrate_progressive", "impl_blitz,impl_nvl,mutate,migrate_progressive"]
 
 
 @settings(max_examples=int(os.environ.get("BLITZ_PROPERTY_EXAMPLES", "25")), deadline=None)
