@@ -641,11 +641,13 @@ def test_restarted_stub_worker_is_readmitted():
     assert "2" in asyncio.run(go())
 
 
-def test_chaos_workers_fail_and_return_while_requests_flow():
+@pytest.mark.parametrize("features", ["impl_blitz,impl_nvl", "impl_blitz,impl_nvl,migrate_progressive"])
+def test_chaos_workers_fail_and_return_while_requests_flow(features):
     """Workers are stopped and restarted at random while requests flow (host-side failures only).  Every request
     either completes with exactly its tokens or fails with an error, nothing hangs, and once things are quiet the
     runtime, the core and the surviving workers hold nothing."""
     import random
+    features = os.environ.get("BLITZ_CHAOS_FEATURES", features)
     rng = random.Random(int(os.environ.get("BLITZ_CHAOS_SEED", "7")))
 
     async def go():
@@ -663,7 +665,7 @@ def test_chaos_workers_fail_and_return_while_requests_flow():
         for r in range(n):
             await start(r, True)
         cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n}, 1,
-                                             os.environ.get("BLITZ_CHAOS_FEATURES", "impl_blitz,impl_nvl"),
+                                             features,
                                              max_blocks_per_replica=4000, tokens_prefilled_per_sec=2000, min_prefill=1,
                                              min_decode=1, max_prefill=3, max_decode=3)
         cfg.quarantine_ms = 200.0
