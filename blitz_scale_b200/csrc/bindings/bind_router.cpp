@@ -114,7 +114,8 @@ void bind_router(py::module_& m) {
       .def_readonly("dst_ranks", &Action::dst_ranks).def_readonly("load_case", &Action::load_case)
       .def_readonly("partial", &Action::partial).def_readonly("num_layer", &Action::num_layer)
       .def_readonly("zag_seq", &Action::zag_seq).def_readonly("live", &Action::live).def_readonly("mock", &Action::mock)
-      .def_readonly("request_id", &Action::request_id).def_readonly("token", &Action::token).def_readonly("final", &Action::final);
+      .def_readonly("request_id", &Action::request_id).def_readonly("token", &Action::token).def_readonly("final", &Action::final)
+      .def_readonly("finish_reason", &Action::finish_reason);
   py::class_<ControllerConfig>(m, "ControllerConfig").def(py::init<>())
       .def_readwrite("num_ranks", &ControllerConfig::num_ranks).def_readwrite("tp", &ControllerConfig::tp)
       .def_readwrite("machines", &ControllerConfig::machines).def_readwrite("init_states", &ControllerConfig::init_states)
@@ -133,8 +134,15 @@ void bind_router(py::module_& m) {
     auto g = pbwire::parse_generations(static_cast<std::string>(raw));
     return py::make_tuple(g.request_ids, g.tokens, g.finished); },
     "(request ids, first token ids, finished flags) of the `generations` of a serialized prefill / decode response");
+  m.def("parse_generations_full", [](py::bytes raw) {
+    auto g = pbwire::parse_generations(static_cast<std::string>(raw));
+    std::vector<int> reasons(g.reasons.begin(), g.reasons.end());
+    return py::make_tuple(g.request_ids, g.tokens, g.finished, reasons); },
+    "as parse_generations, plus the finish reason of every generation (-1 while it is unfinished)");
   py::class_<Controller::TokenOut>(m, "TokenOut")
-      .def(py::init([](uint64_t id, int32_t tok, bool fin) { return Controller::TokenOut{id, tok, fin}; }));
+      .def(py::init([](uint64_t id, int32_t tok, bool fin, int reason) {
+             return Controller::TokenOut{id, tok, fin, static_cast<int8_t>(reason)}; }),
+           py::arg("request_id"), py::arg("token"), py::arg("finished"), py::arg("reason") = 0);
   py::class_<ReplicaMetric>(m, "ReplicaMetric")
       .def_property_readonly("state", [](const ReplicaMetric& r) { return std::string(rstate_name(r.state)); })
       .def_property_readonly("marker", [](const ReplicaMetric& r) { return r.marker ? std::string(rstate_name(*r.marker)) : std::string(); })
@@ -152,13 +160,15 @@ void bind_router(py::module_& m) {
         auto g = pbwire::parse_generations(static_cast<std::string>(raw));
         std::vector<Controller::TokenOut> t;
         t.reserve(g.request_ids.size());
-        for (size_t i = 0; i < g.request_ids.size(); ++i) t.push_back({g.request_ids[i], g.tokens[i], g.finished[i]});
+        for (size_t i = 0; i < g.request_ids.size(); ++i)
+          t.push_back({g.request_ids[i], g.tokens[i], g.finished[i], static_cast<int8_t>(std::max<int>(0, g.reasons[i]))});
         c.on_prefill_done(op, t, now); })
       .def("on_decode_done_wire", [](Controller& c, uint64_t op, py::bytes raw, double now) {
         auto g = pbwire::parse_generations(static_cast<std::string>(raw));
         std::vector<Controller::TokenOut> t;
         t.reserve(g.request_ids.size());
-        for (size_t i = 0; i < g.request_ids.size(); ++i) t.push_back({g.request_ids[i], g.tokens[i], g.finished[i]});
+        for (size_t i = 0; i < g.request_ids.size(); ++i)
+          t.push_back({g.request_ids[i], g.tokens[i], g.finished[i], static_cast<int8_t>(std::max<int>(0, g.reasons[i]))});
         c.on_decode_done(op, t, now); })
       .def("limit_blocks_per_replica", &Controller::limit_blocks_per_replica)
       .def_property_readonly("max_blocks_per_replica", &Controller::max_blocks_per_replica)
@@ -166,18 +176,24 @@ void bind_router(py::module_& m) {
       .def("take_flows", &Controller::take_flows).def("waiting_migration_tokens", &Controller::waiting_migration_tokens)
       .def("set_compact_deliveries", &Controller::set_compact_deliveries)
       .def("take_deliveries", [](Controller& c) {
-        std::vector<std::tuple<uint64_t, int32_t, bool>> out;
-        for (auto& d : c.take_deliveries()) out.emplace_back(d.request_id, d.token, d.final);
+        // (request id, token, final) with final = 0 while the request goes on, else 1 + finish reason
+        // (1 length, 2 EOS token, 3 stop sequence)
+        std::vector<std::tuple<uint64_t, int32_t, int>> out;
+        for (auto& d : c.take_deliveries()) out.emplace_back(d.request_id, d.token, d.final ? 1 + d.reason : 0);
         return out; })
       // completions given as three parallel lists (request ids, tokens, finished flags): cheaper to build than one
       // TokenOut object per token
       .def("on_prefill_done_lists", [](Controller& c, uint64_t op, const std::vector<uint64_t>& ids, const std::vector<int32_t>& toks,
-                                       const std::vector<bool>& fins, double now) {
-        if (ids.size() != toks.size() || ids.size() != fins.size()) throw std::invalid_argument("lists differ in length");
+                                       const std::vector<bool>& fins, double now, const std::vector<int>& reasons) {
+        if (ids.size() != toks.size() || ids.size() != fins.size() || (!reasons.empty() && reasons.size() != ids.size()))
+          throw std::invalid_argument("lists differ in length");
         std::vector<Controller::TokenOut> t;
         t.reserve(ids.size());
-        for (size_t i = 0; i < ids.size(); ++i) t.push_back({ids[i], toks[i], fins[i]});
-        c.on_prefill_done(op, t, now); })
+        for (size_t i = 0; i < ids.size(); ++i)
+          t.push_back({ids[i], toks[i], fins[i], static_cast<int8_t>(reasons.empty() ? 0 : std::max(0, reasons[i]))});
+        c.on_prefill_done(op, t, now); },
+        py::arg("op_id"), py::arg("request_ids"), py::arg("tokens"), py::arg("finished"), py::arg("now"),
+        py::arg("reasons") = std::vector<int>{})
       .def("on_decode_done_lists", [](Controller& c, uint64_t op, const std::vector<uint64_t>& ids, const std::vector<int32_t>& toks,
                                       const std::vector<bool>& fins, double now) {
         if (ids.size() != toks.size() || ids.size() != fins.size()) throw std::invalid_argument("lists differ in length");

@@ -50,6 +50,7 @@ struct Action {
   uint64_t request_id = 0;
   int32_t token = -1;
   bool final = false;
+  int finish_reason = 0;           // with `final`: 0 length, 1 EOS token, 2 stop sequence (proto FinishReason)
 };
 
 struct ControllerConfig {
@@ -130,7 +131,8 @@ class Controller {
     return false;
   }
 
-  struct TokenOut { uint64_t request_id; int32_t token; bool finished; };
+  // `reason`: why the worker finished the request (proto FinishReason: 0 length, 1 EOS token, 2 stop sequence)
+  struct TokenOut { uint64_t request_id; int32_t token; bool finished; int8_t reason = 0; };
 
   void on_prefill_done(uint64_t op_id, const std::vector<TokenOut>& toks, double now) {
     if (late_answer(op_id)) return;
@@ -463,7 +465,7 @@ class Controller {
   std::vector<std::string> drain_log() { std::vector<std::string> l; l.swap(log_); return l; }
   // Token deliveries are by far the most frequent output.  A shell that serves many tokens per second switches them
   // from one `Action` each to a compact list that it drains after every completion it reports.
-  struct Delivery { uint64_t request_id; int32_t token; bool final; };
+  struct Delivery { uint64_t request_id; int32_t token; bool final; int8_t reason = 0; };
   void set_compact_deliveries(bool on) { compact_deliveries_ = on; }
   std::vector<Delivery> take_deliveries() { std::vector<Delivery> d; d.swap(deliveries_); return d; }
   // Network flow since the last call, per replica that moved anything: (replica, MB in, MB out).  Parameters count
@@ -634,11 +636,14 @@ class Controller {
       // the worker's copy of it
       const bool fin = t.finished || e.generated >= e.max_new_tokens || (!prefill && !e.client_alive);
       if (fin && !t.finished && e.generated < e.max_new_tokens) dropped_alive = true;
+      // a request the router ends itself (token budget reached, client gone) is a length stop
+      const int8_t reason = t.finished ? t.reason : int8_t{0};
       if (compact_deliveries_) {
-        deliveries_.push_back({t.request_id, t.token, fin});
+        deliveries_.push_back({t.request_id, t.token, fin, reason});
       } else {
         Action a;
         a.type = ActionType::Deliver; a.request_id = t.request_id; a.token = t.token; a.final = fin;
+        a.finish_reason = reason;
         out_.push_back(a);
       }
       if (fin) {

@@ -52,6 +52,7 @@ struct Generations {
   std::vector<uint64_t> request_ids;
   std::vector<int32_t> tokens;   // -1 when a generation carries no token
   std::vector<bool> finished;
+  std::vector<int8_t> reasons;   // FinishReason of a finished generation (0 length, 1 EOS token, 2 stop sequence), else -1
 };
 
 inline Generations parse_generations(std::string_view response) {
@@ -64,6 +65,7 @@ inline Generations parse_generations(std::string_view response) {
     uint64_t rid = 0;
     int32_t tok = -1;
     bool fin = false;
+    int8_t reason = -1;
     while (!g.done()) {
       const uint64_t t = g.varint();
       const uint32_t field = static_cast<uint32_t>(t >> 3), wt = static_cast<uint32_t>(t & 7);
@@ -88,8 +90,15 @@ inline Generations parse_generations(std::string_view response) {
           }
         }
       } else if (field == 4 && wt == 2) {
-        g.sub();
+        Reader gt = g.sub();   // GeneratedText: text = 1, generated_tokens = 2, finish_reason = 3
         fin = true;
+        reason = 0;
+        while (!gt.done()) {
+          const uint64_t tt = gt.varint();
+          const uint32_t f2 = static_cast<uint32_t>(tt >> 3), w2 = static_cast<uint32_t>(tt & 7);
+          if (f2 == 3 && w2 == 0) reason = static_cast<int8_t>(gt.varint());
+          else gt.skip(w2);
+        }
       } else {
         g.skip(wt);
       }
@@ -97,6 +106,7 @@ inline Generations parse_generations(std::string_view response) {
     out.request_ids.push_back(rid);
     out.tokens.push_back(tok);
     out.finished.push_back(fin);
+    out.reasons.push_back(reason);
   }
   return out;
 }

@@ -41,13 +41,21 @@ class ModelConfig:
     rms_eps: float = 1e-5
     max_positions: int = 16384
     param_gb: float = 0.0  # size used for flow accounting by the router
+    eos_token: int = -1    # end-of-sequence id of the family's tokenizer (-1: none known); workers stop a request there
+                           # unless it sets ignore_eos_token
 
     def kv_bytes_per_token(self, tp: int = 1, elem: int = 2) -> int:
         return 2 * (self.kv_heads // tp) * self.head_dim * elem * self.layers
 
 
+# end-of-sequence ids of the published tokenizers: </s> = 2 (Llama-2, Mistral, OPT), <|end_of_text|> = 128001 (Llama-3),
+# <|endoftext|> = 151643 (Qwen-2.5); a chat-tuned checkpoint that ends turns with another id sets --eos-token-id
+_EOS = {"llama2": 2, "llama3": 128001, "mistral": 2, "qwen": 151643, "opt": 2, "tiny": 2}
+
+
 def _c(name, vocab, hidden, layers, qh, kvh, inter, theta=10000.0, hd=None, gb=0.0, eps=1e-5):
-    return ModelConfig(name, vocab, hidden, layers, qh, kvh, hd or hidden // qh, inter, theta, eps, 16384, gb)
+    return ModelConfig(name, vocab, hidden, layers, qh, kvh, hd or hidden // qh, inter, theta, eps, 16384, gb,
+                       _EOS.get(name.split("_")[0], -1))
 
 
 REGISTRY: Dict[str, ModelConfig] = {c.name: c for c in [

@@ -60,6 +60,16 @@ class LiveRequest:
     stream: bool = True
     done: Optional[asyncio.Future] = None
     entry: object = None               # the core's record of the request (queue and token times), set when it finishes
+    finish_reason: str = ""            # "length" | "eos_token" | "stop_sequence", set with the last token
+    # stop sequences (text): checked here, where the text of a request can be known, after every token.  `detok` turns
+    # token ids into text; `stop_window` = how many trailing tokens can contain the longest stop sequence.
+    stop: tuple = ()
+    detok: object = None
+    stop_window: int = 0
+    stopped: bool = False              # ended by a stop sequence; the worker's later tokens are dropped
+
+
+FINISH_REASONS = {1: "length", 2: "eos_token", 3: "stop_sequence"}   # the `final` code of a delivery
 
 
 class RouterRuntime:
@@ -109,16 +119,24 @@ class RouterRuntime:
         return time.monotonic() - self.t0
 
     def submit(self, input_tokens: List[int], max_new_tokens: int, *, inputs: str = "", parameters=None,
-               ignore_eos: bool = True, stream: bool = True) -> LiveRequest:
+               ignore_eos: bool = True, stream: bool = True, stop=(), detok=None) -> LiveRequest:
+        """Queue a request.  `ignore_eos` = False lets the worker end it at the model's end-of-sequence token.  `stop`:
+        texts that end the request when the generated text contains one (needs `detok`, ids -> text); the reference
+        carries both in the contract and applies neither (src/blitz/stopping.h:21 stops on length only)."""
         rid = self._next_id
         self._next_id += 1
         r = pb.Request(id=rid, inputs=inputs, prefill_logprobs=False, top_n_tokens=0)
         r.input_tokens.extend(input_tokens)
         r.stopping_parameters.max_new_tokens = max_new_tokens
         r.stopping_parameters.ignore_eos_token = ignore_eos
+        stop = tuple(s for s in stop if s)
+        if stop and detok is None:
+            raise ValueError("stop sequences need a detokenizer")
+        r.stopping_parameters.stop_sequences.extend(stop)
         if parameters is not None:
             r.parameters.CopyFrom(parameters)
-        lr = LiveRequest(rid, r, t_submit=self.now(), stream=stream, done=asyncio.get_running_loop().create_future())
+        lr = LiveRequest(rid, r, t_submit=self.now(), stream=stream, done=asyncio.get_running_loop().create_future(),
+                         stop=stop, detok=detok, stop_window=max((len(s.encode()) for s in stop), default=0) + 1)
         self.requests[rid] = lr
         self.ctl.submit(core.RequestEntry(rid, len(input_tokens), max_new_tokens, lr.t_submit))
         self.wake.set()
@@ -282,7 +300,7 @@ class RouterRuntime:
                     lr.done.set_result("replica lost")
             return
         if t == A.Deliver:     # only when compact deliveries are off
-            self._deliver_one(a.request_id, a.token, a.final, self.now())
+            self._deliver_one(a.request_id, a.token, 1 + a.finish_reason if a.final else 0, self.now())
             return
         handler = {A.Prefill: self._do_prefill, A.ZagPrefill: self._do_prefill, A.PrefillPP: self._do_prefill,
                    A.Decode: self._do_decode, A.Migrate: self._do_migrate, A.MigratePartial: self._do_migrate,
@@ -304,17 +322,36 @@ class RouterRuntime:
         if self.ctl.state_name(replica) != "Inactive":
             self.cached[(replica, batch.id)] = batch
 
-    def _deliver_one(self, rid: int, token: int, final: bool, now: float) -> None:
+    def _deliver_one(self, rid: int, token: int, final: int, now: float) -> None:
+        """`final`: 0 while the request goes on, else a key of FINISH_REASONS."""
         lr = self.requests.get(rid)
         if lr is None:
             return
+        final = int(final)
+        if lr.stopped:
+            # ended at a stop sequence: what the worker produced after it is dropped, and the core's record goes when
+            # the core ends the request (it filters it out of the worker's batch at the next step)
+            if final:
+                del self.requests[rid]
+                self.ctl.pop_finished(rid)
+            return
         lr.tokens.append(token)
         lr.times.append(now)
+        if not final and lr.stop and any(s in lr.detok(lr.tokens[-lr.stop_window:]) for s in lr.stop):
+            # every token is at least one byte of text, so the last `stop_window` tokens hold any stop sequence that
+            # this token completed; an earlier occurrence would have ended the request already
+            final, lr.stopped = 3, True
+            self.ctl.client_gone(rid)                 # nobody wants its next tokens
+            self.wake.set()
         if lr.stream:
             lr.queue.put_nowait(("token", token, final))
         if final:
-            del self.requests[rid]
-            lr.entry = self.ctl.pop_finished(rid)     # out of the core: its map of finished requests stays empty
+            lr.finish_reason = FINISH_REASONS.get(final, "length")
+            if lr.stopped:
+                lr.entry = self.ctl.request(rid)      # a copy: the core still holds the request for one more step
+            else:
+                del self.requests[rid]
+                lr.entry = self.ctl.pop_finished(rid)     # out of the core: its map of finished requests stays empty
             if self.exporter is not None:
                 end = time.time()
                 self.exporter.span("generate", child_traceparent(self.root_trace), end - (now - lr.t_submit), end,
@@ -388,11 +425,11 @@ class RouterRuntime:
             self._remember(holder, answers[-1].batch)
         elif res.HasField("batch"):
             self._remember(a.replica, res.batch)
-        ids, toks, fins = core.parse_generations(res.raw)
+        ids, toks, fins, reasons = core.parse_generations_full(res.raw)
         if (holder, a.batch_id) in self.cached:      # somebody will decode this batch: its first tokens travel with the first step
             self.first_tokens[a.batch_id] = {i: t for i, t in zip(ids, toks) if t >= 0}
         now = self.now()
-        self.ctl.on_prefill_done_lists(a.op_id, ids, toks, fins, now)
+        self.ctl.on_prefill_done_lists(a.op_id, ids, toks, fins, now, reasons)
         self._deliver(now)
 
     async def _do_decode(self, a) -> None:

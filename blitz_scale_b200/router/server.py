@@ -29,7 +29,7 @@ from aiohttp import web
 
 from ..pb.schema import pb
 from ..runtime import core
-from .runtime import RouterRuntime
+from .runtime import FINISH_REASONS, RouterRuntime
 
 log = logging.getLogger("blitz.router.http")
 
@@ -193,7 +193,10 @@ class RouterApp:
         g.typical_p = float(p.get("typical_p") or 1.0)
         g.top_k = int(p.get("top_k") or 0)
         g.top_n_tokens = int(p.get("top_n_tokens") or 0)
-        g.num_stop_sequences = len(p.get("stop") or [])
+        g.stop = [str(x) for x in (p.get("stop") or []) if str(x)]
+        g.num_stop_sequences = len(g.stop)
+        # the end-of-sequence token ends a request unless the request opts out (trace replays that fix output lengths do)
+        g.ignore_eos = bool(p.get("ignore_eos_token", False))
         if p.get("truncate"):
             g.truncate = int(p["truncate"])
             toks = toks[-int(p["truncate"]):]
@@ -244,7 +247,7 @@ class RouterApp:
         m.observe("blitz_request_input_length", len(toks))
         m.observe("blitz_request_max_new_tokens", g.max_new_tokens)
         m.observe("blitz_request_skipped_tokens", 0.0)     # no speculation: a token is never skipped
-        return list(out), stats
+        return list(out), stats, (lr.finish_reason or "length")
 
     @staticmethod
     def _unavailable(text):
@@ -253,7 +256,8 @@ class RouterApp:
 
     async def _collect(self, toks, g):
         """Whole response at once: the handler sleeps until the last token instead of waking for every token."""
-        lr = self.rt.submit(toks, g.max_new_tokens, stream=False, parameters=getattr(g, "chooser", None))
+        lr = self.rt.submit(toks, g.max_new_tokens, stream=False, parameters=getattr(g, "chooser", None),
+                            ignore_eos=g.ignore_eos, stop=g.stop, detok=self.tok.decode)
         try:
             err = await lr.done
         except asyncio.CancelledError:        # the client closed the connection: stop generating for it
@@ -265,7 +269,8 @@ class RouterApp:
 
     async def _run(self, toks, g):
         """Token by token (server-sent events); the last item carries (tokens, timing headers)."""
-        lr = self.rt.submit(toks, g.max_new_tokens, parameters=getattr(g, "chooser", None))
+        lr = self.rt.submit(toks, g.max_new_tokens, parameters=getattr(g, "chooser", None), ignore_eos=g.ignore_eos,
+                            stop=g.stop, detok=self.tok.decode)
         try:
             while True:
                 ev = await lr.queue.get()
@@ -294,10 +299,10 @@ class RouterApp:
         if self.sem.locked():
             return web.json_response({"error": "Model is overloaded", "error_type": "overloaded"}, status=429)
         async with self.sem:
-            out, stats = await self._collect(toks, g)
+            out, stats, reason = await self._collect(toks, g)
         details = None
         if (body.get("parameters") or {}).get("details"):
-            details = {"finish_reason": "length", "generated_tokens": len(out),
+            details = {"finish_reason": reason, "generated_tokens": len(out),
                        "tokens": [{"id": t, "text": self.tok.piece(t), "logprob": 0.0, "special": False} for t in out]}
         return web.json_response({"generated_text": self.tok.decode(out), "details": details},
                                  headers={k: str(v) for k, v in stats.items()})
@@ -314,13 +319,12 @@ class RouterApp:
         try:
             async for tok, final, done in agen:
                 if done is not None:
-                    out, _ = done
                     continue
                 n += 1
                 ev = {"token": {"id": tok, "text": self.tok.piece(tok), "logprob": 0.0, "special": False},
                       "generated_text": None, "details": None}
                 if final:
-                    ev["details"] = {"finish_reason": "length", "generated_tokens": n}
+                    ev["details"] = {"finish_reason": FINISH_REASONS.get(int(final), "length"), "generated_tokens": n}
                 await resp.write(f"data:{json.dumps(ev)}\n\n".encode())
             await resp.write_eof()
         except (ConnectionResetError, asyncio.CancelledError):

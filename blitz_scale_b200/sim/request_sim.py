@@ -48,7 +48,8 @@ def token_ids_for(item, vocab: int = 32000) -> List[int]:
 async def _one(session, endpoint: str, idx: int, item, t0: float, out: list, vocab: int, record_tokens: bool):
     s_time = time.monotonic() - t0
     body = {"input_tokens": token_ids_for(item, vocab),
-            "parameters": {"max_new_tokens": int(item.output_len), "details": record_tokens}}
+            # a replayed trace fixes every output length: the end-of-sequence token must not cut a request short
+            "parameters": {"max_new_tokens": int(item.output_len), "details": record_tokens, "ignore_eos_token": True}}
     rec = {"request_id": idx, "status": "error", "s_time": s_time, "input_length": int(item.input_len),
            "output_length": int(item.output_len)}
     try:

@@ -29,8 +29,10 @@ def stub_token(seed: int, request_id: int, position: int, vocab: int = 32000) ->
 class StubBackend(Backend):
     def __init__(self, rank: int = 0, world: int = 1, *, seed: int = 0, layers: int = 2, vocab: int = 32000,
                  num_pages: int = 4096, page_size: int = 64, ready: bool = True, prefill_tokens_per_s: float = 2e5,
-                 decode_step_s: float = 0.002, load_s: float = 0.2, peers: Optional[Dict[int, "StubBackend"]] = None):
+                 decode_step_s: float = 0.002, load_s: float = 0.2, peers: Optional[Dict[int, "StubBackend"]] = None,
+                 eos_token: int = -1):
         self.rank, self.world, self.seed, self.layers, self.vocab = rank, world, seed, layers, vocab
+        self.eos_token = eos_token
         self.pool = core.PagePool(num_pages, page_size)
         self.status = core.ModelStatus(layers)
         if ready:
@@ -51,7 +53,7 @@ class StubBackend(Backend):
                 "ranks": {"rank": self.rank, "world": self.world}}
 
     def _specs(self, batch) -> List["core.SeqSpec"]:
-        return [seq_spec_from_request(r, [1] * max(1, len(r.inputs.split()))) for r in batch.requests]
+        return [seq_spec_from_request(r, [1] * max(1, len(r.inputs.split())), self.eos_token) for r in batch.requests]
 
     def _cached(self, b) -> Optional[object]:
         ids = b.unfinished_ids()

@@ -44,9 +44,10 @@ class GpuBackend(Backend):
     def __init__(self, rank: int, world: int, model: str, *, tp: int = 1, num_pages: int = 2048, page_size: int = 64,
                  max_batch: int = 256, max_batch_tokens: int = 8192, ready: bool = True, use_fabric: bool = True,
                  tp_group=None, model_path: str = "", seed: int = 0, use_multimem: bool = False, copy_ctas: int = 128,
-                 fused_tp: bool = True, precapture: bool = False):
+                 fused_tp: bool = True, precapture: bool = False, eos_token: Optional[int] = None):
         self.rank, self.world, self.tp = rank, world, tp
         self.cfg = get_config(model)
+        self.eos_token = self.cfg.eos_token if eos_token is None else int(eos_token)
         self.model, self.model_path = model, model_path
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.lock = threading.RLock()
@@ -134,7 +135,7 @@ class GpuBackend(Backend):
                 "ranks": {"rank": self.rank, "world": self.world, "tp": self.tp}}
 
     def _specs(self, batch) -> List["core.SeqSpec"]:
-        return [seq_spec_from_request(r) for r in batch.requests]
+        return [seq_spec_from_request(r, eos_token=self.eos_token) for r in batch.requests]
 
     def _cached(self, b):
         ids = b.unfinished_ids()

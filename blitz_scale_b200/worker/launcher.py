@@ -50,6 +50,8 @@ def parse_args(argv=None):
                     "fused peer-memory kernels (needed for live execution with tp > 1)")
     ap.add_argument("--precapture-graphs", action="store_true", help="capture the decode CUDA graphs of every batch bucket "
                     "at start-up instead of on first use")
+    ap.add_argument("--eos-token-id", type=int, default=None, help="end-of-sequence token id (default: the model "
+                    "family's; -1: none).  A request stops there unless it sets ignore_eos_token")
     ap.add_argument("--no-numa-bind", action="store_true", help="do not pin host threads to the CPU cores next to the GPU")
     return ap.parse_args(argv)
 
@@ -93,7 +95,8 @@ def main(argv=None) -> int:
     backend = GpuBackend(rank, world, a.model_name, tp=tp, num_pages=a.num_total_blocks, page_size=a.page_size,
                          max_batch=a.max_batch_size, max_batch_tokens=a.max_batch_tokens,
                          ready=states[rank] != "Inactive", tp_group=tp_group, model_path=a.model_path,
-                         seed=0, use_multimem=a.multimem, fused_tp=not a.no_fused_tp, precapture=a.precapture_graphs)
+                         seed=0, use_multimem=a.multimem, fused_tp=not a.no_fused_tp, precapture=a.precapture_graphs,
+                         eos_token=a.eos_token_id)
     urls = [f"{a.host}:{a.port + r}" for r in range(world)]
 
     async def run():

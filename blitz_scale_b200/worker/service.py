@@ -276,12 +276,13 @@ async def serve(backend: Backend, host: str, port: int, urls=None, ready_event: 
         await server.stop(grace=1.0)
 
 
-def seq_spec_from_request(r, default_tokens=None) -> "core.SeqSpec":
-    """The engine's view of one `Request` of the contract: prompt ids, stopping rule and, when the request asks for
-    it (`parameters.do_sample`), the sampling parameters."""
+def seq_spec_from_request(r, default_tokens=None, eos_token: int = -1) -> "core.SeqSpec":
+    """The engine's view of one `Request` of the contract: prompt ids, stopping rule (token budget, and the model's
+    end-of-sequence id `eos_token` unless the request ignores it) and, when the request asks for it
+    (`parameters.do_sample`), the sampling parameters."""
     from ..runtime import core
     s = core.SeqSpec(r.id, list(r.input_tokens) or list(default_tokens or [1]), r.stopping_parameters.max_new_tokens,
-                     r.stopping_parameters.ignore_eos_token, -1)
+                     r.stopping_parameters.ignore_eos_token, int(eos_token))
     if r.HasField("parameters") and r.parameters.do_sample:
         p = r.parameters
         s.do_sample, s.temperature, s.top_k, s.top_p, s.seed = True, float(p.temperature), int(p.top_k), float(p.top_p), int(p.seed)

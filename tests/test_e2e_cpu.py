@@ -898,6 +898,74 @@ def test_sampling_parameters_reach_the_worker():
     assert bad == 422
 
 
+def test_end_of_sequence_token_and_stop_sequences_end_a_request():
+    """Stopping rules beyond the token budget, over HTTP: the worker ends a request at the model's end-of-sequence token
+    (finish_reason eos_token) unless the request sets ignore_eos_token; the router ends it when the generated text
+    contains a stop sequence (finish_reason stop_sequence), drops what the worker produced after it and has the request
+    filtered out of the worker's batch.  Other requests of the same batch are unaffected and nothing is left behind."""
+    import aiohttp
+    from blitz_scale_b200.sim.stub_worker import stub_token
+
+    async def go():
+        rt, backends, port, stop, tasks = await _cluster(2, ["Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+        url = f"http://127.0.0.1:{port}/generate"
+        async with aiohttp.ClientSession() as s:
+            async def gen(params, stream=False):
+                body = {"input_tokens": list(range(12)), "parameters": dict({"max_new_tokens": 8, "details": True}, **params)}
+                if not stream:
+                    async with s.post(url, json=body) as r:
+                        data = await r.json()
+                        assert r.status == 200, data
+                        return [t["id"] for t in data["details"]["tokens"]], data["details"]["finish_reason"]
+                toks, reason = [], None
+                async with s.post(url + "_stream", json=body) as r:
+                    assert r.status == 200
+                    async for line in r.content:
+                        if line.startswith(b"data:"):
+                            ev = json.loads(line[5:])
+                            toks.append(ev["token"]["id"])
+                            if ev["details"]:
+                                reason = ev["details"]["finish_reason"]
+                return toks, reason
+            def expected(rid):             # the stub's tokens are a function of (seed, request id, position)
+                return [stub_token(0, rid, 12 + n) for n in range(8)]
+            full = expected(rt._next_id)
+            assert await gen({}) == (full, "length")
+            # the worker's end-of-sequence id is the 4th token of the next request
+            nxt = expected(rt._next_id)
+            for b in backends:
+                b.eos_token = nxt[3]
+            cut = await gen({})
+            assert cut == (nxt[:4], "eos_token")
+            nxt = expected(rt._next_id)
+            for b in backends:
+                b.eos_token = nxt[3]
+            assert await gen({"ignore_eos_token": True}) == (nxt, "length")
+            for b in backends:
+                b.eos_token = -1
+            # a stop sequence that the 3rd token completes (two tokens long; streamed and not), next to a request
+            # that runs to its budget: the two are submitted together, so either may get the lower id
+            for stream in (False, True):
+                e0, e1 = expected(rt._next_id), expected(rt._next_id + 1)
+                stops = [f"<{e[1]}> <{e[2]}>" for e in (e0, e1)] + ["never"]
+                (st, why_st), (other, why_other) = await asyncio.gather(gen({"stop": stops}, stream=stream), gen({}))
+                assert (st, other) in ((e0[:3], e1), (e1[:3], e0)), (st, other, e0, e1)
+                assert (why_st, why_other) == ("stop_sequence", "length")
+            async with s.post(url, json={"input_tokens": [1], "parameters": {"stop": ["a", "b", "c", "d", "e"]}}) as r:
+                too_many = r.status
+        for _ in range(100):
+            if rt.ctl.idle() and not rt.requests and not rt.cached and all(not b.batches for b in backends):
+                break
+            await asyncio.sleep(0.05)
+        state = (len(rt.requests), len(rt.cached), len(rt.ctl.finished()), rt.ctl.total_used_blocks(),
+                 [len(b.batches) for b in backends], [b.pool.used_pages for b in backends])
+        await _shutdown(stop, tasks)
+        return too_many, state
+    too_many, state = asyncio.run(go())
+    assert too_many == 422
+    assert state == (0, 0, 0, 0, [0, 0], [0, 0])
+
+
 def test_router_learns_the_workers_kv_capacity_at_start():
     async def go():
         ports = _free_ports(2)

@@ -789,3 +789,28 @@ def test_sim_progressive_migration_conserves_requests_and_pages():
     _check_conservation(rep, trace)
     c = sim.controller().counters()
     assert c["blitz_progressive_kv_cache_times"] > 0 and c["blitz_kv_cache_times"] >= c["blitz_progressive_kv_cache_times"]
+
+
+def test_deliveries_carry_the_finish_reason():
+    """The last delivery of a request says why it ended: 1 token budget (also when the router ends it itself), 2 the
+    worker met the end-of-sequence token, 3 a stop sequence; 0 while it goes on."""
+    A = core.ActionType
+    cfg = _cfg(["Normal"], "impl_blitz,impl_nvl", autoscale=False)
+    ctl = core.Controller(cfg)
+    ctl.set_compact_deliveries(True)
+    ctl.submit(E(1, 50, 8))
+    ctl.submit(E(2, 50, 2))
+    ctl.submit(E(3, 50, 8))
+    pf = [a for a in ctl.step(0.0) if a.type == A.Prefill][0]
+    ctl.on_prefill_done(pf.op_id, [core.TokenOut(1, 5, True, 1), core.TokenOut(2, 5, False), core.TokenOut(3, 5, False)], 0.01)
+    assert ctl.take_deliveries() == [(1, 5, 2), (2, 5, 0), (3, 5, 0)]
+    dec = [a for a in ctl.step(0.02) if a.type == A.Decode][0]
+    ctl.on_decode_done(dec.op_id, [core.TokenOut(2, 6, False), core.TokenOut(3, 6, True, 2)], 0.03)
+    assert ctl.take_deliveries() == [(2, 6, 1), (3, 6, 3)]      # request 2 reached its budget in the router's count
+    # without compact deliveries the reason rides on the Deliver action
+    ctl = core.Controller(cfg)
+    ctl.submit(E(1, 50, 8))
+    pf = [a for a in ctl.step(0.0) if a.type == A.Prefill][0]
+    ctl.on_prefill_done(pf.op_id, [core.TokenOut(1, 5, True, 1)], 0.01)
+    d = [a for a in ctl.step(0.02) if a.type == A.Deliver]
+    assert len(d) == 1 and d[0].final and d[0].finish_reason == 1

@@ -244,8 +244,19 @@ def test_batch_admission_is_all_or_nothing_and_eos_stops():
     b.mark_prefilled()
     b.append_tokens([7], False)
     assert b.unfinished_ids() == [2]
+    assert core.parse_generations_full(b.encode_generations([7])) == ([2], [7], [False], [-1])
     b.append_tokens([42], True)
     assert b.unfinished_ids() == []
+    # the finish reason travels in the generation (proto FinishReason: 0 length, 1 EOS token) and the native reader
+    # hands it to the router core
+    assert core.parse_generations_full(b.encode_generations([42])) == ([2], [42], [True], [1])
+    b.clear()
+    s = core.SeqSpec(3, [1, 2, 3], 1)
+    assert b.add_prompts([s])
+    b.mark_prefilled()
+    b.append_tokens([9], False)
+    raw = b.encode_generations([9])
+    assert core.parse_generations_full(raw) == ([3], [9], [True], [0]) and core.parse_generations(raw) == ([3], [9], [True])
     b.clear()
 
 
