@@ -54,7 +54,13 @@ void bind_text(py::module_& m) {
       .def("encode", [](const Tokenizer& t, const std::string& s) {
              py::gil_scoped_release rel;
              return t.encode(s); })
-      .def("decode", [](const Tokenizer& t, const std::vector<int32_t>& ids, bool skip) { return py::str(t.decode(ids, skip)); },
+      // byte-level tokens can end in the middle of a character (a model may emit any id): such bytes become U+FFFD,
+      // as in the `tokenizers` library, instead of an exception
+      .def("decode", [](const Tokenizer& t, const std::vector<int32_t>& ids, bool skip) {
+             const std::string s = t.decode(ids, skip);
+             PyObject* u = PyUnicode_DecodeUTF8(s.data(), static_cast<Py_ssize_t>(s.size()), "replace");
+             if (!u) throw py::error_already_set();
+             return py::reinterpret_steal<py::str>(u); },
            py::arg("ids"), py::arg("skip_special_tokens") = true)
       .def("decode_bytes", [](const Tokenizer& t, const std::vector<int32_t>& ids, bool skip) { return py::bytes(t.decode(ids, skip)); },
            py::arg("ids"), py::arg("skip_special_tokens") = true)

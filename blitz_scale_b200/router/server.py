@@ -304,7 +304,10 @@ class RouterApp:
         if (body.get("parameters") or {}).get("details"):
             details = {"finish_reason": reason, "generated_tokens": len(out),
                        "tokens": [{"id": t, "text": self.tok.piece(t), "logprob": 0.0, "special": False} for t in out]}
-        return web.json_response({"generated_text": self.tok.decode(out), "details": details},
+        text = self.tok.decode(out)
+        if (body.get("parameters") or {}).get("return_full_text") and isinstance(body.get("inputs"), str):
+            text = body["inputs"] + text
+        return web.json_response({"generated_text": text, "details": details},
                                  headers={k: str(v) for k, v in stats.items()})
 
     async def generate_stream(self, req: web.Request) -> web.StreamResponse:

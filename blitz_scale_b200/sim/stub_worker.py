@@ -65,7 +65,7 @@ class StubBackend(Backend):
         return b.encode_generations(new_tokens)
 
     def _step(self, b, prefill: bool):
-        toks = [stub_token(self.seed, rid, pl + n) for (rid, _, n), pl in zip(b.emit_info(), b.prompt_lens())]
+        toks = [stub_token(self.seed, rid, pl + n, self.vocab) for (rid, _, n), pl in zip(b.emit_info(), b.prompt_lens())]
         rows, _temp, top_k, _top_p, seeds = b.sampling_rows()
         for row, k, sd in zip(rows, top_k, seeds):      # stand-in for sampling: a function of the (mixed) seed, within top-k
             toks[row] = (sd & 0x7FFFFFFF) % (k if k > 0 else self.vocab)

@@ -42,6 +42,17 @@ def test_byte_level_bpe_matches_reference_library(trained):
         assert t.decode(ids, False) == s
     assert t.decode(t.encode("<|begin|>hi<|end|>"), True) == "hi"
     assert t.get_id("<|end|>") == ref.token_to_id("<|end|>") and t.get_id("no such token") == -1
+    # ids that a model may emit in any order: bytes that form no character decode to U+FFFD, as in the library
+    import random
+    rng = random.Random(5)
+    lossy = 0
+    for _ in range(200):
+        ids = [rng.randrange(t.num_ids()) for _ in range(rng.randrange(1, 6))]
+        got = t.decode(ids, True)
+        assert got == ref.decode(ids, skip_special_tokens=True), ids
+        lossy += "\ufffd" in got
+    assert lossy > 0
+    assert t.decode_bytes(t.encode("é")[:1], True) in ("é".encode(), "é".encode()[:1])
 
 
 def test_tokenizer_c_abi(trained):
@@ -204,11 +215,38 @@ def test_router_http_with_native_tokenizer(trained):
                 hdr = dict(r.headers)
             async with s.post(f"http://127.0.0.1:{hport}/generate", json={"input_tokens": [10 ** 6], "parameters": {}}) as r:
                 assert r.status == 422 and "input_tokens" in (await r.json())["error"]
+            # a stop sequence in real text: the text that the third token of the next request adds ends the request
+            # there (the stub's tokens are a function of the request id and the position)
+            from blitz_scale_b200.sim.stub_worker import stub_token
+            import re
+            t = core.Tokenizer.from_file(path)
+            stopped = None
+            for extra in range(40):                      # a prompt whose (random) continuation contains a clean word
+                prompt = text + " a" * extra
+                n_in = len(t.encode(prompt))
+                exp = [stub_token(0, rt._next_id, n_in + n, ref.get_vocab_size()) for n in range(8)]
+                words = re.findall(r"[A-Za-z]{2,}", t.decode(exp, True))
+                cuts = [(next(k for k in range(1, 9) if w in t.decode(exp[:k], True)), w) for w in words]
+                cuts = [c for c in cuts if 2 <= c[0] < 8]
+                if not cuts:
+                    continue
+                cut, word = min(cuts)
+                async with s.post(f"http://127.0.0.1:{hport}/generate",
+                                  json={"inputs": prompt, "parameters": {"max_new_tokens": 8, "details": True, "stop": [word],
+                                                                         "return_full_text": True}}) as r:
+                    assert r.status == 200, await r.text()
+                    stopped = (await r.json(), exp[:cut], prompt + t.decode(exp[:cut], True))
+                break
         stop.set()
         await asyncio.wait(tasks, timeout=5)
-        return text, body, hdr
+        return text, body, hdr, stopped
 
-    text, body, hdr = asyncio.run(go())
+    text, body, hdr, stopped = asyncio.run(go())
+    assert stopped is not None
+    got, want_ids, want_text = stopped
+    assert [tk["id"] for tk in got["details"]["tokens"]] == want_ids and got["details"]["finish_reason"] == "stop_sequence"
+    assert got["generated_text"] == want_text
+    assert body["details"]["finish_reason"] == "length"
     t = core.Tokenizer.from_file(path)
     assert int(hdr["x-input-length"]) == len(t.encode(text)) == len(ref.encode(text).ids)
     ids = [tk["id"] for tk in body["details"]["tokens"]]
