@@ -146,11 +146,13 @@ class RouterApp:
         self.metrics = Metrics()
         self.app = web.Application(client_max_size=64 << 20, middlewares=[self._cors_middleware] if self.cors else [])
         r = self.app.router
-        for path in ("/", "/generate", "/invocations"):
-            r.add_post(path, self.generate)
+        r.add_post("/generate", self.generate)
+        for path in ("/", "/invocations"):
+            r.add_post(path, self.compat_generate)
         r.add_post("/generate_stream", self.generate_stream)
         r.add_get("/info", self.info)
         r.add_get("/health", self.health)
+        r.add_get("/", self.health)
         r.add_get("/ping", self.health)
         r.add_get("/metrics", self.prom)
         r.add_get("/docs", self.docs)
@@ -287,7 +289,18 @@ class RouterApp:
         yield None, True, self._finish(lr, toks, g)
 
     # ------------------------------------------------------------------ handlers
-    async def generate(self, req: web.Request) -> web.Response:
+    async def compat_generate(self, req: web.Request) -> web.StreamResponse:
+        """`/` and `/invocations`: `stream` in the body picks the event stream; otherwise the generation comes back
+        inside a one-element list (router_v2/src/server.rs:66-86)."""
+        try:
+            body = await req.json()
+        except Exception:  # noqa: BLE001
+            return web.json_response({"error": "invalid JSON", "error_type": "validation"}, status=422)
+        if isinstance(body, dict) and body.get("stream"):
+            return await self.generate_stream(req)
+        return await self.generate(req, wrap=True)
+
+    async def generate(self, req: web.Request, wrap: bool = False) -> web.Response:
         try:
             body = await req.json()
         except Exception:  # noqa: BLE001
@@ -307,7 +320,8 @@ class RouterApp:
         text = self.tok.decode(out)
         if (body.get("parameters") or {}).get("return_full_text") and isinstance(body.get("inputs"), str):
             text = body["inputs"] + text
-        return web.json_response({"generated_text": text, "details": details},
+        payload = {"generated_text": text, "details": details}
+        return web.json_response([payload] if wrap else payload,
                                  headers={k: str(v) for k, v in stats.items()})
 
     async def generate_stream(self, req: web.Request) -> web.StreamResponse:

@@ -953,6 +953,17 @@ def test_end_of_sequence_token_and_stop_sequences_end_a_request():
                 assert (why_st, why_other) == ("stop_sequence", "length")
             async with s.post(url, json={"input_tokens": [1], "parameters": {"stop": ["a", "b", "c", "d", "e"]}}) as r:
                 too_many = r.status
+            # the compatibility route: a one-element list, or the event stream when the body asks for it
+            root = f"http://127.0.0.1:{port}/"
+            want = expected(rt._next_id)[:3]
+            async with s.post(root, json={"input_tokens": list(range(12)), "parameters": {"max_new_tokens": 3, "details": True}}) as r:
+                data = await r.json()
+                assert r.status == 200 and isinstance(data, list) and len(data) == 1
+                assert [t["id"] for t in data[0]["details"]["tokens"]] == want and "x-first-token-time" in r.headers
+            async with s.post(root, json={"input_tokens": list(range(12)), "stream": True, "parameters": {"max_new_tokens": 3}}) as r:
+                assert r.status == 200 and r.headers["Content-Type"].startswith("text/event-stream")
+                events = [json.loads(l[5:]) async for l in r.content if l.startswith(b"data:")]
+                assert len(events) == 3 and events[-1]["details"]["finish_reason"] == "length"
         for _ in range(100):
             if rt.ctl.idle() and not rt.requests and not rt.cached and all(not b.batches for b in backends):
                 break
