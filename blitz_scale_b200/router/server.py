@@ -143,6 +143,8 @@ class RouterApp:
         if not tokenizer_path and self.model_vocab:
             self.tok = WordHashTokenizer(min(vocab, self.model_vocab))
         self.sem = asyncio.Semaphore(max_concurrent)
+        self.max_concurrent, self.tokenizer_workers = max_concurrent, max(1, tokenizer_workers)
+        self._worker_info = None          # dtype / device of the workers, asked once (the Info RPC of the contract)
         self.metrics = Metrics()
         self.app = web.Application(client_max_size=64 << 20, middlewares=[self._cors_middleware] if self.cors else [])
         r = self.app.router
@@ -351,9 +353,26 @@ class RouterApp:
         return resp
 
     async def info(self, req):
-        return web.json_response({"model_id": self.model_name, "max_input_length": self.limits.max_input_length,
-                                  "max_total_tokens": self.limits.max_total_tokens, "version": "0.1.0",
-                                  "replicas": [self.rt.ctl.state_name(i) for i in range(self.rt.ctl.num_replicas)]})
+        """Model and router parameters, with the fields of the reference's answer (router_v2/src/lib.rs:99-137; it
+        hard-codes the shard part, here the first worker that answers `Info` is asked once) plus the replica states."""
+        if self._worker_info is None:
+            for stub in self.rt.stubs:
+                try:
+                    wi = await stub.info()
+                    self._worker_info = (wi.dtype, wi.device_type)
+                    break
+                except Exception:  # noqa: BLE001 - that worker is away; the next one may answer
+                    continue
+        dtype, device = self._worker_info or ("unknown", "unknown")
+        cfg = self.rt.cfg
+        return web.json_response({
+            "model_id": self.model_name, "model_sha": None, "model_dtype": dtype, "model_device_type": device,
+            "model_pipeline_tag": "text-generation", "max_concurrent_requests": self.max_concurrent,
+            "max_best_of": self.limits.max_best_of, "max_stop_sequences": self.limits.max_stop_sequences,
+            "max_input_length": self.limits.max_input_length, "max_total_tokens": self.limits.max_total_tokens,
+            "max_batch_prefill_tokens": cfg.max_prefill_tokens, "max_batch_total_tokens": cfg.max_total_tokens,
+            "validation_workers": self.tokenizer_workers, "version": "0.1.0", "sha": None, "docker_label": None,
+            "replicas": [self.rt.ctl.state_name(i) for i in range(self.rt.ctl.num_replicas)]})
 
     async def health(self, req):
         """Healthy when at least one replica is in service and every replica in service answers (replicas that are

@@ -138,6 +138,9 @@ def test_config1_cpu_plumbing_scale_out_and_determinism():
     cum = [int(l.rsplit(" ", 1)[1]) for l in metrics.splitlines() if l.startswith("blitz_request_generated_tokens_bucket")]
     assert cum == sorted(cum) and cum[-1] == 80 and cum[0] < 80
     assert info["replicas"] == ["Prefill", "Prefill"]
+    # the reference's fields; dtype and device come from the workers' Info RPC
+    assert info["model_dtype"] == "float32" and info["model_device_type"] == "cpu" and info["max_stop_sequences"] == 4
+    assert info["max_batch_prefill_tokens"] > 0 and info["max_concurrent_requests"] > 0 and info["max_best_of"] >= 1
     assert used == 0 and pages == [0, 0]
     s = request_sim.summarize(recs)
     assert s["ok"] == 80 and s["output_tokens"] == sum(i.output_len for i in trace)
