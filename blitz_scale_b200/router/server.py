@@ -317,7 +317,9 @@ class RouterApp:
             out, stats, reason = await self._collect(toks, g)
         details = None
         if (body.get("parameters") or {}).get("details"):
-            details = {"finish_reason": reason, "generated_tokens": len(out),
+            chooser = getattr(g, "chooser", None)
+            details = {"finish_reason": reason, "generated_tokens": len(out), "prefill": [],
+                       "seed": int(chooser.seed) if chooser is not None else None,
                        "tokens": [{"id": t, "text": self.tok.piece(t), "logprob": 0.0, "special": False} for t in out]}
         text = self.tok.decode(out)
         if (body.get("parameters") or {}).get("return_full_text") and isinstance(body.get("inputs"), str):
@@ -505,6 +507,11 @@ def build_parser() -> argparse.ArgumentParser:
                     "dispatched operation and request are exported there as service blitz.router")
     ap.add_argument("--otlp-service-name", default="blitz.router")
     ap.add_argument("--cors-allow-origin", action="append", default=[], help="origin allowed for cross-origin requests (repeatable, * = any)")
+    # the reference can publish its port through an ngrok tunnel (router_v2/src/main.rs:83-89); there is no tunnel
+    # client here, so the flags are recognised and refused with a message instead of being unknown
+    ap.add_argument("--ngrok", action="store_true", help="not available: no tunnel client in this build")
+    ap.add_argument("--ngrok-authtoken", default="", help="not available (see --ngrok)")
+    ap.add_argument("--ngrok-edge", default="", help="not available (see --ngrok)")
     ap.add_argument("--max-concurrent-requests", type=int, default=4096)
     ap.add_argument("--max-best-of", type=int, default=2)
     ap.add_argument("--max-stop-sequences", type=int, default=4)
@@ -535,6 +542,8 @@ def build_parser() -> argparse.ArgumentParser:
 
 def main(argv=None) -> None:
     a = build_parser().parse_args(argv)
+    if a.ngrok or a.ngrok_authtoken or a.ngrok_edge:
+        raise SystemExit("--ngrok: no tunnel client in this build; publish the port with a reverse proxy instead")
     from ..utils.otlp import SpanExporter, init_logging
     log_listener = init_logging(a.log_level, a.json_output, a.log_path)
     from ..models.config import get_config
