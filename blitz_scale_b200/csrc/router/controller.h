@@ -1119,6 +1119,8 @@ class Controller {
     a.replica = targets.front().first;
     a.mock = features_.has("mock_transfer") || features_.has("motiv");
     a.type = multi ? ActionType::TanzBroadcast : (nvl ? ActionType::NvlBroadcast : ActionType::RdmaBroadcast);
+    if (a.type != ActionType::RdmaBroadcast) counters_["blitz_nvbroadcast_times"] += 1;
+    counters_["blitz_scale_up_times"] += static_cast<double>(targets.size());
     Op op;
     op.replica = a.replica;
     for (int s2 : sources) {
@@ -1199,6 +1201,8 @@ class Controller {
       const bool multi = features_.has("impl_tanz") && sources.size() > 1;
       const bool nvl = features_.has("impl_nvl");
       a.type = multi ? ActionType::TanzBroadcast : (nvl ? ActionType::NvlBroadcast : ActionType::RdmaBroadcast);
+      if (a.type != ActionType::RdmaBroadcast) counters_["blitz_nvbroadcast_times"] += 1;
+      counters_["blitz_scale_up_times"] += 1;
       if (!multi) sources.resize(1);
       for (int s : sources) {
         steer_.set_nvlink_busy(s, true);
@@ -1512,7 +1516,29 @@ class Controller {
     finished_.erase(it);
     return e;
   }
-  const std::map<std::string, double>& gauges() const { return gauges_; }
+  // Gauges of the planner's last turn plus the queue and replica gauges of the reference's metric list
+  // (router_v2/src/server.rs:1084-1134, declared there and mostly never updated), taken from the state as it is now.
+  const std::map<std::string, double>& gauges() {
+    uint64_t waiting_full = 0, waiting_partial = 0, shutting = 0, n_prefill = 0, n_decode = 0;
+    for (auto& r : reps_) {
+      waiting_full += r.pending_migration.size();
+      const RState st = r.m.state;
+      n_prefill += is_prefill_side(st) ? 1 : 0;
+      n_decode += is_decode_side(st) ? 1 : 0;
+      if (st == RState::ShuttingPrefill || st == RState::ShuttingDecode || st == RState::ShuttingNull) ++shutting;
+    }
+    for (auto& kv : relayed_) waiting_partial += (kv.second.fst_done ? 0 : 1) + (kv.second.snd_done ? 0 : 1);
+    gauges_["blitz_migration_queue_size"] = static_cast<double>(waiting_full);
+    gauges_["blitz_waiting_full_batches"] = static_cast<double>(waiting_full);
+    gauges_["blitz_relay_queue_size"] = static_cast<double>(relayed_.size());
+    gauges_["blitz_waiting_partial_batches"] = static_cast<double>(waiting_partial);
+    gauges_["blitz_used_blocks"] = static_cast<double>(total_used_blocks());
+    gauges_["blitz_shutting_replica"] = static_cast<double>(shutting);
+    gauges_["blitz_prefill_replica"] = static_cast<double>(n_prefill);
+    gauges_["blitz_decode_replica"] = static_cast<double>(n_decode);
+    gauges_["blitz_queue_size"] = static_cast<double>(queue_.size());
+    return gauges_;
+  }
   Steersman& steersman() { return steer_; }
 };
 

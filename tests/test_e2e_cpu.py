@@ -137,6 +137,13 @@ def test_config1_cpu_plumbing_scale_out_and_determinism():
     assert 'blitz_request_duration_bucket{le="+Inf"} 80' in metrics and 'blitz_request_input_length_bucket{le="16384"} 80' in metrics
     cum = [int(l.rsplit(" ", 1)[1]) for l in metrics.splitlines() if l.startswith("blitz_request_generated_tokens_bucket")]
     assert cum == sorted(cum) and cum[-1] == 80 and cum[0] < 80
+    # every metric name of the reference's list is exported (router_v2/src/server.rs:1084-1207)
+    for name in ("blitz_queue_size", "blitz_relay_queue_size", "blitz_migration_queue_size", "blitz_used_blocks",
+                 "blitz_scale_up_times", "blitz_nvbroadcast_times", "blitz_waiting_full_batches",
+                 "blitz_waiting_partial_batches", "blitz_shutting_replica", "blitz_prefill_replica", "blitz_decode_replica",
+                 "blitz_request_success", "blitz_request_validation_duration", "blitz_batch_next_size"):
+        assert f"\n{name}" in "\n" + metrics, name
+    assert "blitz_scale_up_times 1" in metrics and "blitz_nvbroadcast_times 1" in metrics and "blitz_used_blocks 0" in metrics
     assert info["replicas"] == ["Prefill", "Prefill"]
     # the reference's fields; dtype and device come from the workers' Info RPC
     assert info["model_dtype"] == "float32" and info["model_device_type"] == "cpu" and info["max_stop_sequences"] == 4
