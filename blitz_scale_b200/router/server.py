@@ -177,14 +177,32 @@ class RouterApp:
         return resp
 
     # ------------------------------------------------------------------ request parsing
-    async def _parse(self, body: dict):
-        p = body.get("parameters") or {}
+    async def _parse(self, body):
+        """(token ids, parameters, error text).  Anything in the body that has the wrong type or shape is a validation
+        error (HTTP 422), as a typed request structure makes it in the reference, never a server error."""
+        try:
+            return await self._parse_checked(body)
+        except (TypeError, ValueError, AttributeError, KeyError, OverflowError) as e:
+            return None, None, f"invalid request body: {e}"
+
+    async def _parse_checked(self, body):
+        if not isinstance(body, dict):
+            raise TypeError("a JSON object is expected")
+        p = body.get("parameters")
+        if p is not None and not isinstance(p, dict):
+            raise TypeError("`parameters` must be an object")
+        p = p or {}
         if "input_tokens" in body:
+            if not isinstance(body["input_tokens"], list) or not all(isinstance(t, int) and not isinstance(t, bool)
+                                                                     for t in body["input_tokens"]):
+                raise TypeError("`input_tokens` must be a list of integers")
             toks = [int(t) for t in body["input_tokens"]]
             if self.model_vocab and any(t < 0 or t >= self.model_vocab for t in toks):
                 # an id outside the embedding table would make the worker's lookup fail the whole batch
                 return toks, None, f"input_tokens must lie in [0, {self.model_vocab})"
         else:
+            if not isinstance(body.get("inputs", ""), str):
+                raise TypeError("`inputs` must be a string")
             toks = await asyncio.get_running_loop().run_in_executor(self.tok_pool, self.tok.encode, body.get("inputs", ""))
         g = core.GenerateParams()
         g.input_len = len(toks)
@@ -197,13 +215,18 @@ class RouterApp:
         g.typical_p = float(p.get("typical_p") or 1.0)
         g.top_k = int(p.get("top_k") or 0)
         g.top_n_tokens = int(p.get("top_n_tokens") or 0)
-        g.stop = [str(x) for x in (p.get("stop") or []) if str(x)]
+        if not isinstance(p.get("stop") or [], list) or not all(isinstance(x, str) for x in p.get("stop") or []):
+            raise TypeError("`stop` must be a list of strings")
+        g.stop = [x for x in (p.get("stop") or []) if x]
         g.num_stop_sequences = len(g.stop)
         # the end-of-sequence token ends a request unless the request opts out (trace replays that fix output lengths do)
         g.ignore_eos = bool(p.get("ignore_eos_token", False))
-        if p.get("truncate"):
+        if p.get("truncate") is not None:
+            if int(p["truncate"]) <= 0:
+                raise ValueError("`truncate` must be strictly positive")
             g.truncate = int(p["truncate"])
             toks = toks[-int(p["truncate"]):]
+            g.input_len = len(toks)
         g.has_seed = p.get("seed") is not None
         err = core.validate_request(g, self.limits)
         if not err and g.best_of > 1:
@@ -329,7 +352,10 @@ class RouterApp:
                                  headers={k: str(v) for k, v in stats.items()})
 
     async def generate_stream(self, req: web.Request) -> web.StreamResponse:
-        body = await req.json()
+        try:
+            body = await req.json()
+        except Exception:  # noqa: BLE001
+            return web.json_response({"error": "invalid JSON", "error_type": "validation"}, status=422)
         toks, g, err = await self._parse(body)
         if err:
             return web.json_response({"error": err, "error_type": "validation"}, status=422)

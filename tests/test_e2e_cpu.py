@@ -987,6 +987,37 @@ def test_end_of_sequence_token_and_stop_sequences_end_a_request():
     assert state == (0, 0, 0, 0, [0, 0], [0, 0])
 
 
+def test_malformed_request_bodies_are_validation_errors():
+    """Bodies with wrong types or shapes answer 422 on every generation route (a typed request structure does that in
+    the reference), never 5xx; well-formed edge cases still work."""
+    import aiohttp
+
+    async def go():
+        rt, backends, port, stop, tasks = await _cluster(2, ["Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+        url = f"http://127.0.0.1:{port}"
+        bad_bodies = [[1, 2, 3], "text", None, {"inputs": 123}, {"input_tokens": "abc"}, {"input_tokens": [1.5]},
+                      {"inputs": "a", "parameters": []}, {"inputs": "a", "parameters": {"max_new_tokens": "x"}},
+                      {"inputs": "a", "parameters": {"max_new_tokens": 0}}, {"inputs": "a", "parameters": {"stop": "word"}},
+                      {"inputs": "a", "parameters": {"stop": [1]}}, {"inputs": "a", "parameters": {"truncate": -1}},
+                      {"inputs": "a", "parameters": {"temperature": "hot", "do_sample": True}},
+                      {"inputs": "a", "parameters": {"seed": "s", "do_sample": True}}, {"inputs": ""}, {"input_tokens": []}]
+        out = []
+        async with aiohttp.ClientSession() as s:
+            for path in ("/generate", "/generate_stream", "/"):
+                for b in bad_bodies:
+                    async with s.post(url + path, json=b) as r:
+                        out.append((path, b, r.status))
+                async with s.post(url + path, data=b"{not json", headers={"Content-Type": "application/json"}) as r:
+                    out.append((path, "raw", r.status))
+            async with s.post(url + "/generate", json={"inputs": "a b c d e", "parameters": {"truncate": 2, "max_new_tokens": 2}}) as r:
+                ok = (r.status, r.headers.get("x-input-length"))
+        await _shutdown(stop, tasks)
+        return out, ok
+    out, ok = asyncio.run(go())
+    assert [o for o in out if o[2] != 422] == []
+    assert ok == (200, "2")
+
+
 def test_router_learns_the_workers_kv_capacity_at_start():
     async def go():
         ports = _free_ports(2)
