@@ -427,8 +427,15 @@ class RouterApp:
     async def modify_cluster_state(self, req):
         if not self.rt.ctl.has_feature("manually_scale"):
             return web.json_response({"error": "manually_scale is not enabled"}, status=403)
-        body = await req.json()
-        ok = self.rt.ctl.manual_scale(int(body["replica"]), str(body["state"]), self.rt.now())
+        try:
+            body = await req.json()
+            replica, state = body["replica"], body["state"]
+            if not isinstance(replica, int) or isinstance(replica, bool) or not isinstance(state, str):
+                raise TypeError("`replica` must be an integer and `state` a string")
+        except Exception as e:  # noqa: BLE001 - not JSON, not an object, or a field missing / of the wrong type
+            return web.json_response({"error": f"expected {{\"replica\": int, \"state\": str}}: {e}",
+                                      "error_type": "validation"}, status=422)
+        ok = self.rt.ctl.manual_scale(replica, state, self.rt.now())
         self.rt.wake.set()
         return web.json_response({"ok": bool(ok)}, status=200 if ok else 409)
 

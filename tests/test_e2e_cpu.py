@@ -993,7 +993,8 @@ def test_malformed_request_bodies_are_validation_errors():
     import aiohttp
 
     async def go():
-        rt, backends, port, stop, tasks = await _cluster(2, ["Prefill", "Decode"], "impl_blitz,impl_nvl", autoscale=False)
+        rt, backends, port, stop, tasks = await _cluster(2, ["Prefill", "Decode"], "impl_blitz,impl_nvl,manually_scale",
+                                                         autoscale=False)
         url = f"http://127.0.0.1:{port}"
         bad_bodies = [[1, 2, 3], "text", None, {"inputs": 123}, {"input_tokens": "abc"}, {"input_tokens": [1.5]},
                       {"inputs": "a", "parameters": []}, {"inputs": "a", "parameters": {"max_new_tokens": "x"}},
@@ -1009,6 +1010,11 @@ def test_malformed_request_bodies_are_validation_errors():
                         out.append((path, b, r.status))
                 async with s.post(url + path, data=b"{not json", headers={"Content-Type": "application/json"}) as r:
                     out.append((path, "raw", r.status))
+            for b in ({}, [], "x", {"replica": "a", "state": "Prefill"}, {"replica": 1}, {"state": "Decode"}, {"replica": 1.5, "state": "Decode"}):
+                async with s.post(url + "/modify_cluster_state", json=b) as r:
+                    out.append(("/modify_cluster_state", b, r.status))
+            async with s.post(url + "/modify_cluster_state", json={"replica": 7, "state": "Decode"}) as r:
+                assert r.status == 409                       # well-formed, but there is no such replica
             async with s.post(url + "/generate", json={"inputs": "a b c d e", "parameters": {"truncate": 2, "max_new_tokens": 2}}) as r:
                 ok = (r.status, r.headers.get("x-input-length"))
         await _shutdown(stop, tasks)
