@@ -234,7 +234,8 @@ class StubBackend(Backend):
                     raise RuntimeError("out of KV pages")
                 b.mark_prefilled()
                 b.decode = True
-                self.batches[batch.id] = b
+                if b.size:
+                    self.batches[batch.id] = b
             self.counters["immigrate"] += 1
             return pb.CachedBatch(id=b.id, request_ids=b.request_ids(), size=b.size, max_tokens=b.max_tokens())
 

@@ -564,7 +564,8 @@ class GpuBackend(Backend):
                     raise RuntimeError("out of KV pages")
                 b.mark_prefilled()
                 b.decode = True
-                self.batches[batch.id] = b
+                if b.size:
+                    self.batches[batch.id] = b
             elif partial == pb.PARTIAL_CASE_SECOND:
                 # the second half names the requests that are still alive after the prefill; the ones that ended at
                 # their first token were part of the first half only and leave the batch (and their pages) here

@@ -151,6 +151,8 @@ class TextGenerationService:
 
     async def DecodeV2(self, req, ctx):
         t0 = time.perf_counter_ns()
+        if not req.batches:
+            await ctx.abort(grpc.StatusCode.INVALID_ARGUMENT, "DecodeV2 needs at least one cached batch")
         try:
             # "x-decode-steps: k" in the call's metadata asks for up to k steps in this one call
             steps = 1
