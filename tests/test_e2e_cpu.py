@@ -955,7 +955,10 @@ def test_end_of_sequence_token_and_stop_sequences_end_a_request():
                 b.eos_token = -1
             # a stop sequence that the 3rd token completes (two tokens long; streamed and not), next to a request
             # that runs to its budget: the two are submitted together, so either may get the lower id
-            for stream in (False, True):
+            for rnd, stream in enumerate((False, True, False)):
+                if rnd == 2:
+                    rt.decode_steps = 4     # third round: the worker runs 4 decode steps per call, so tokens it produced
+                                            # after the stop sequence arrive in the same answer and must be dropped
                 e0, e1 = expected(rt._next_id), expected(rt._next_id + 1)
                 stops = [f"<{e[1]}> <{e[2]}>" for e in (e0, e1)] + ["never"]
                 (st, why_st), (other, why_other) = await asyncio.gather(gen({"stop": stops}, stream=stream), gen({}))
