@@ -443,7 +443,20 @@ class RouterApp:
 def controller_config_from_cluster(cluster: dict, tp: int, features: str, **overrides) -> "core.ControllerConfig":
     """Cluster JSON {init_states, replicas, machines} -> controller config (src/server/disaggregate.cc:31-50)."""
     cfg = core.ControllerConfig()
-    cfg.init_states = list(cluster["init_states"])
+    states = cluster.get("init_states") if isinstance(cluster, dict) else None
+    known = ("Prefill", "Decode", "Normal", "Inactive")
+    if not isinstance(states, list) or not states or not all(s in known for s in states):
+        raise ValueError(f"cluster config: `init_states` must be a non-empty list of {known} with one entry per rank")
+    if tp < 1 or len(states) % tp:
+        raise ValueError(f"cluster config: {len(states)} ranks cannot be split into replicas of {tp} tensor-parallel ranks")
+    for r0 in range(0, len(states), tp):
+        if len(set(states[r0:r0 + tp])) != 1:
+            raise ValueError(f"cluster config: ranks {r0}..{r0 + tp - 1} form one replica and must share a state, "
+                             f"got {states[r0:r0 + tp]}")
+    machines = cluster.get("machines")
+    if machines is not None and (not isinstance(machines, list) or len(machines) != len(states)):
+        raise ValueError("cluster config: `machines` must name one machine per rank")
+    cfg.init_states = list(states)
     cfg.num_ranks = len(cfg.init_states)
     cfg.tp = tp
     cfg.machines = list(cluster.get("machines") or [0] * cfg.num_ranks)
@@ -580,8 +593,24 @@ def main(argv=None) -> None:
     from ..utils.otlp import SpanExporter, init_logging
     log_listener = init_logging(a.log_level, a.json_output, a.log_path)
     from ..models.config import get_config
-    cluster = json.load(open(a.deployment_config_path))
-    urls = json.loads(a.client_config) if a.client_config.strip().startswith("[") else json.load(open(a.client_config))
+    try:
+        cluster = json.load(open(a.deployment_config_path))
+        urls = json.loads(a.client_config) if a.client_config.strip().startswith("[") else json.load(open(a.client_config))
+        if not isinstance(urls, list) or not all(isinstance(u, str) for u in urls):
+            raise ValueError("--client-config must be a JSON list of worker addresses (or a file that holds one)")
+        if isinstance(cluster, dict) and isinstance(cluster.get("init_states"), list) and len(cluster["init_states"]) != len(urls):
+            raise ValueError(f"{len(urls)} worker addresses for {len(cluster['init_states'])} ranks in the cluster config")
+    except (OSError, ValueError) as e:
+        raise SystemExit(f"router: {e}")
+    try:
+        core.FeatureSet.parse(a.features)
+    except Exception as e:  # noqa: BLE001 - unknown feature or a combination the feature rules forbid
+        raise SystemExit(f"router: --features {a.features}: {e}")
+    try:
+        controller_config_from_cluster(cluster, a.tensor_parallel_size, a.features)      # shape of the cluster description
+        get_config(a.model_name)
+    except (ValueError, KeyError) as e:
+        raise SystemExit(f"router: {e}")
     cfg = controller_config_from_cluster(
         cluster, a.tensor_parallel_size, a.features, model_name=a.model_name,
         max_prefill_tokens=a.max_batch_prefill_tokens, max_total_tokens=max(a.max_total_tokens, 16000),

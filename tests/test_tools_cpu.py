@@ -416,3 +416,32 @@ def test_package_command_dispatcher():
     assert r.returncode == 0 and "usage" in r.stdout.lower()
     r = run("report", "--help")
     assert r.returncode == 0 and "--router-log" in r.stdout
+
+
+def test_router_cli_reports_configuration_mistakes_in_one_line(tmp_path):
+    """A cluster description or flag the router cannot work with ends the start-up with one line that names the
+    mistake, not a traceback."""
+    import json
+    import subprocess
+    import sys
+    good = tmp_path / "good.json"
+    good.write_text(json.dumps({"init_states": ["Prefill", "Decode"], "machines": [0, 0]}))
+    mixed = tmp_path / "mixed.json"
+    mixed.write_text(json.dumps({"init_states": ["Prefill", "Decode"], "machines": [0, 0]}))
+    nostates = tmp_path / "nostates.json"
+    nostates.write_text(json.dumps({"machines": [0, 0]}))
+    two = '["127.0.0.1:1", "127.0.0.1:2"]'
+
+    def run(*args):
+        cmd = [sys.executable, "-m", "blitz_scale_b200.router.server", "--model-name", "tiny", "--model-path", "x",
+               "--parameter-size", "1", *args]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=60,
+                           cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        assert r.returncode != 0 and "Traceback" not in r.stderr, r.stderr
+        return r.stderr.strip().splitlines()[-1]
+    assert "init_states" in run("--client-config", two, "--deployment-config-path", str(nostates))
+    assert "must share a state" in run("--client-config", two, "--deployment-config-path", str(mixed), "--tensor-parallel-size", "2")
+    assert "3 worker addresses for 2 ranks" in run("--client-config", '["a:1", "b:2", "c:3"]', "--deployment-config-path", str(good))
+    assert "unknown feature: bogus" in run("--client-config", two, "--deployment-config-path", str(good), "--features", "impl_blitz,bogus")
+    assert "No such file" in run("--client-config", two, "--deployment-config-path", str(tmp_path / "none.json"))
+    assert "tunnel" in run("--client-config", two, "--deployment-config-path", str(good), "--ngrok")
