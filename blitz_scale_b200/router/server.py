@@ -443,19 +443,8 @@ class RouterApp:
 def controller_config_from_cluster(cluster: dict, tp: int, features: str, **overrides) -> "core.ControllerConfig":
     """Cluster JSON {init_states, replicas, machines} -> controller config (src/server/disaggregate.cc:31-50)."""
     cfg = core.ControllerConfig()
-    states = cluster.get("init_states") if isinstance(cluster, dict) else None
-    known = ("Prefill", "Decode", "Normal", "Inactive")
-    if not isinstance(states, list) or not states or not all(s in known for s in states):
-        raise ValueError(f"cluster config: `init_states` must be a non-empty list of {known} with one entry per rank")
-    if tp < 1 or len(states) % tp:
-        raise ValueError(f"cluster config: {len(states)} ranks cannot be split into replicas of {tp} tensor-parallel ranks")
-    for r0 in range(0, len(states), tp):
-        if len(set(states[r0:r0 + tp])) != 1:
-            raise ValueError(f"cluster config: ranks {r0}..{r0 + tp - 1} form one replica and must share a state, "
-                             f"got {states[r0:r0 + tp]}")
-    machines = cluster.get("machines")
-    if machines is not None and (not isinstance(machines, list) or len(machines) != len(states)):
-        raise ValueError("cluster config: `machines` must name one machine per rank")
+    from ..utils.cluster_config import check_cluster
+    states = check_cluster(cluster, tp)
     cfg.init_states = list(states)
     cfg.num_ranks = len(cfg.init_states)
     cfg.tp = tp

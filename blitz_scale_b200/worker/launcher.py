@@ -63,6 +63,16 @@ def main(argv=None) -> int:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    try:        # before anything touches a GPU: a description the job cannot run with ends it with one line
+        from ..models.config import get_config
+        from ..utils.cluster_config import check_cluster
+        cluster = json.load(open(a.config))
+        states = check_cluster(cluster, a.tensor_parallel)
+        get_config(a.model_name)
+        if len(states) != world:
+            raise ValueError(f"cluster config lists {len(states)} ranks, world size is {world}")
+    except (OSError, ValueError, KeyError) as e:
+        raise SystemExit(f"worker launcher: {e}")
     if a.log_dir:
         os.makedirs(a.log_dir, exist_ok=True)
         f = open(os.path.join(a.log_dir, f"rank-{rank}.log"), "a", buffering=1)
@@ -76,10 +86,6 @@ def main(argv=None) -> int:
         from ..utils.topology import bind_to_gpu_cpus
         cpus = bind_to_gpu_cpus(local)
         logging.getLogger("blitz.worker").info("rank %d bound to %d CPU cores next to GPU %d", rank, len(cpus), local)
-    cluster = json.load(open(a.config))
-    states = cluster["init_states"]
-    if len(states) != world:
-        raise SystemExit(f"cluster config lists {len(states)} ranks, world size is {world}")
     tp = a.tensor_parallel
     tp_group = None
     if world > 1:
