@@ -207,4 +207,7 @@ def main(argv: Optional[Iterable[str]] = None) -> int:
 
 
 if __name__ == "__main__":
-    raise SystemExit(main())
+    try:
+        raise SystemExit(main())
+    except (OSError, KeyError, ValueError, RuntimeError) as e:   # missing source, unknown model, tensor of another shape
+        raise SystemExit(f"convert: {e}")
