@@ -1027,6 +1027,61 @@ def test_malformed_request_bodies_are_validation_errors():
     assert ok == (200, "2")
 
 
+def test_stop_sequences_leaving_clients_and_progressive_migration_together():
+    """Soak of the ways a request can end before its budget, mixed at random on a 2 + 2 cluster with layer-progressive
+    migration and three decode steps per worker call: every request gets exactly the tokens up to its stop sequence
+    (or all of them), clients that leave are forgotten, and nothing is left behind anywhere."""
+    import random
+    from blitz_scale_b200.sim.stub_worker import stub_token
+
+    async def go():
+        rng = random.Random(3)
+        rt, backends, port, stop, tasks = await _cluster(4, ["Prefill", "Decode", "Prefill", "Decode"],
+                                                         "impl_blitz,impl_nvl,migrate_progressive", autoscale=False)
+        rt.decode_steps = 3
+        for b in backends:
+            b.decode_step_s, b.prefill_rate = 0.0005, 1e7
+
+        def detok(ids):
+            return " ".join(f"<{i}>" for i in ids)
+
+        async def one(i):
+            await asyncio.sleep(rng.random())
+            n_in, n_new = 5 + rng.randrange(60), 1 + rng.randrange(20)
+            exp = [stub_token(0, rt._next_id, n_in + n) for n in range(n_new)]
+            mode = rng.choice(["plain", "stop", "gone", "stop_at_last"])
+            stops, want = (), exp
+            if mode in ("stop", "stop_at_last") and n_new >= 3:
+                k = rng.randrange(1, n_new - 1) if mode == "stop" else n_new - 1
+                stops, want = (f"<{exp[k]}>",), exp[:k + 1]
+            lr = rt.submit(list(range(n_in)), n_new, stream=False, stop=stops, detok=detok)
+            if mode == "gone":
+                await asyncio.sleep(rng.random() * 0.05)
+                rt.client_gone(lr.id)
+                await asyncio.wait_for(lr.done, 30)
+                return None
+            assert (await asyncio.wait_for(lr.done, 30)) is None
+            if list(lr.tokens) != want:
+                return (mode, lr.tokens, want)
+            if len(want) < len(exp) and lr.finish_reason != "stop_sequence":
+                return (mode, lr.finish_reason)
+            return None
+        wrong = [r for r in await asyncio.gather(*[one(i) for i in range(150)]) if r]
+        for _ in range(200):
+            if rt.ctl.idle() and not rt.requests and not rt.cached and all(not b.batches for b in backends):
+                break
+            await asyncio.sleep(0.05)
+        state = (len(rt.requests), len(rt.cached), len(rt.first_tokens), len(rt.ctl.finished()), rt.ctl.inflight_ops(),
+                 rt.ctl.total_used_blocks(), [len(b.batches) for b in backends], [b.pool.used_pages for b in backends])
+        progressive = rt.ctl.counters().get("blitz_progressive_kv_cache_times", 0)
+        await _shutdown(stop, tasks)
+        return wrong, state, progressive
+    wrong, state, progressive = asyncio.run(go())
+    assert wrong == []
+    assert state == (0, 0, 0, 0, 0, 0, [0, 0, 0, 0], [0, 0, 0, 0])
+    assert progressive > 0
+
+
 def test_router_learns_the_workers_kv_capacity_at_start():
     async def go():
         ports = _free_ports(2)
