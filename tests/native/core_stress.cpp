@@ -106,11 +106,14 @@ static void controller_sim() {
       for (int k = 0; k < tp; ++k) c2.init_states.push_back(st);
     c2.max_incoming_migrations = 3;
     c2.quarantine_ms = 300;
-    for (int victim = 0; victim < 3; ++victim) {
-      ClusterSim sim(c2, cm);
-      const SimReport rep = sim.run(trace, 0.001, 120.0, victim, 4.0 + victim, /*gone_every=*/4);
-      CHECK(rep.submitted == trace.size() && rep.completed + rep.failed + rep.gone_in_queue == rep.submitted);
-      CHECK(rep.leftover_blocks == 0);
+    for (const char* feats : {"impl_blitz,impl_nvl,impl_live", "impl_blitz,impl_nvl,impl_live,migrate_progressive"}) {
+      c2.features = feats;   // the second set places a batch on its decode replica when its prefill is issued
+      for (int victim = 0; victim < 3; ++victim) {
+        ClusterSim sim(c2, cm);
+        const SimReport rep = sim.run(trace, 0.001, 120.0, victim, 4.0 + victim, /*gone_every=*/4);
+        CHECK(rep.submitted == trace.size() && rep.completed + rep.failed + rep.gone_in_queue == rep.submitted);
+        CHECK(rep.leftover_blocks == 0);
+      }
     }
   }
 }
