@@ -25,6 +25,7 @@
 #include "runtime/kv_pool.h"
 #include "sim/cluster_sim.h"
 #include "sim/trace.h"
+#include "util/pbwire.h"
 
 using namespace blitz;
 
@@ -67,6 +68,51 @@ static void pool_fuzz() {
     threw = true;
   }
   CHECK(threw);
+}
+
+// The wire reader takes whatever bytes a worker sends: valid responses round-trip, and truncated, bit-flipped or random
+// bytes either parse or raise, without a read outside the buffer (which the address sanitizer would report).
+static void wire_fuzz() {
+  std::mt19937 rng(11);
+  PagePool pool(64, 16);
+  Batch b(1, &pool);
+  std::vector<SeqSpec> specs;
+  for (int i = 0; i < 5; ++i) {
+    SeqSpec s;
+    s.id = 1000u + i;
+    s.prompt = {1, 2, 3};
+    s.max_new_tokens = 1 + i % 2;
+    s.eos_token = 7;
+    s.ignore_eos = false;
+    specs.push_back(s);
+  }
+  CHECK(b.add_prompts(specs));
+  b.mark_prefilled();
+  const std::vector<int32_t> toks = {5, 6, 7, 8, 9};
+  b.append_tokens(toks, false);
+  const std::string good = b.encode_generations(toks);
+  const pbwire::Generations g = pbwire::parse_generations(good);
+  CHECK(g.request_ids.size() == 5 && g.tokens == toks && g.request_ids[4] == 1004u);
+  CHECK(g.finished[0] && g.reasons[0] == 0 && !g.finished[1] && g.reasons[1] == -1 && g.finished[2] && g.reasons[2] == 1);
+  size_t parsed = 0, refused = 0;
+  for (int it = 0; it < 20000; ++it) {
+    std::string m = good;
+    switch (it % 4) {
+      case 0: m.resize(rng() % (good.size() + 1)); break;
+      case 1: for (int k = 0; k < 3; ++k) m[rng() % m.size()] = static_cast<char>(rng()); break;
+      case 2: m.assign(rng() % 64, '\0'); for (auto& c : m) c = static_cast<char>(rng()); break;
+      default: m.insert(rng() % m.size(), 1, static_cast<char>(rng())); break;
+    }
+    try {
+      const pbwire::Generations x = pbwire::parse_generations(m);
+      CHECK(x.request_ids.size() == x.tokens.size() && x.tokens.size() == x.finished.size() && x.finished.size() == x.reasons.size());
+      ++parsed;
+    } catch (const std::invalid_argument&) {
+      ++refused;
+    }
+  }
+  CHECK(parsed > 0 && refused > 0);
+  b.clear();
 }
 
 static void controller_sim() {
@@ -329,6 +375,7 @@ static void kv_push_protocol() {
 int main(int argc, char** argv) {
   const std::string what = argc > 1 ? argv[1] : "all";
   if (what == "all" || what == "pool") pool_fuzz();
+  if (what == "all" || what == "wire") wire_fuzz();
   if (what == "all" || what == "sim") controller_sim();
   if (what == "all" || what == "flags") flag_protocol();
   if (what == "all" || what == "tickets") ticket_protocol();
