@@ -1,7 +1,7 @@
 """Host code under AddressSanitizer + UndefinedBehaviorSanitizer and under ThreadSanitizer (CPU only).
 
-Builds tests/native/core_stress.cpp twice and runs it: the page pool and the controller-in-simulator under
-ASan/UBSan, the flag, ticket, all-reduce rendezvous and two-source KV-push protocols (CPU-thread emulation of what the kernels do) under TSan.
+Builds tests/native/core_stress.cpp twice and runs it: the page pool, the wire reader on mutated bytes and the
+controller-in-simulator under ASan/UBSan, the flag, ticket, all-reduce rendezvous and two-source KV-push protocols (CPU-thread emulation of what the kernels do) under TSan.
 """
 import os
 import shutil
@@ -27,7 +27,7 @@ def _build(tmp_path, name, flags):
 @pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
 def test_core_under_asan_ubsan(tmp_path):
     exe = _build(tmp_path, "cs_asan", ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"])
-    for part in ("pool", "sim"):
+    for part in ("pool", "wire", "sim"):
         r = subprocess.run([exe, part], capture_output=True, text=True, timeout=600,
                            env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0"))
         assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
