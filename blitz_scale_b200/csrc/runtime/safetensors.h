@@ -61,11 +61,20 @@ class SafeTensorsFile {
         for (const auto& d : kv.second.at("shape").arr) t.shape.push_back(d.as_int());
         const auto& off = kv.second.at("data_offsets").arr;
         if (off.size() != 2) throw std::runtime_error("safetensors: bad data_offsets for " + t.name);
+        // the offsets come from the file: compare them as the numbers they are before any conversion, so that a
+        // negative, fractional or huge value cannot wrap into the mapped range
+        const double avail = static_cast<double>(size_ - data_);
+        if (!(off[0].num >= 0) || !(off[1].num >= off[0].num) || !(off[1].num <= avail))
+          throw std::runtime_error("safetensors: tensor " + t.name + " does not fit its byte range");
         t.begin = static_cast<uint64_t>(off[0].num);
         t.end = static_cast<uint64_t>(off[1].num);
         uint64_t want = static_cast<uint64_t>(safetensors_dtype_size(t.dtype));
-        for (int64_t d : t.shape) want *= static_cast<uint64_t>(d);
-        if (t.end < t.begin || data_ + t.end > size_ || (want && want != t.end - t.begin))
+        for (int64_t d : t.shape) {
+          if (d < 0 || (d > 0 && want > (size_ / static_cast<uint64_t>(d))))   // also bounds the product: no overflow
+            throw std::runtime_error("safetensors: tensor " + t.name + " has a shape its file cannot hold");
+          want *= static_cast<uint64_t>(d);
+        }
+        if (t.end < t.begin || t.end > size_ - data_ || (safetensors_dtype_size(t.dtype) && want != t.end - t.begin))
           throw std::runtime_error("safetensors: tensor " + t.name + " does not fit its byte range");
         tensors_.push_back(std::move(t));
       }

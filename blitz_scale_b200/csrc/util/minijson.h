@@ -33,7 +33,13 @@ struct Value {
     return *v;
   }
   bool is_null() const { return type == Null; }
-  int64_t as_int() const { return static_cast<int64_t>(num); }
+  // saturating: a number outside the 64-bit range (or NaN) must not reach an undefined conversion
+  int64_t as_int() const {
+    if (!(num == num)) return 0;
+    if (num >= 9.2e18) return INT64_MAX;
+    if (num <= -9.2e18) return INT64_MIN;
+    return static_cast<int64_t>(num);
+  }
 };
 
 class Parser {

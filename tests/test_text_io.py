@@ -112,6 +112,20 @@ def test_safetensors_reader_and_hf_conversion(tmp_path):
     assert info.dtype == "BF16" and list(info.shape) == [cfg.vocab, cfg.hidden] and info.nbytes == cfg.vocab * cfg.hidden * 2
     with pytest.raises(KeyError):
         f.info("missing")
+    # a header whose numbers do not describe bytes of the file is refused, whatever they would wrap to
+    import json
+    import struct
+    for entry in ({"dtype": "WEIRD", "shape": [1], "data_offsets": [0, 1.8e19]}, {"dtype": "F32", "shape": [2], "data_offsets": [-8, 0]},
+                  {"dtype": "F32", "shape": [-2], "data_offsets": [0, 8]}, {"dtype": "F32", "shape": [2 ** 62, 4], "data_offsets": [0, 8]},
+                  {"dtype": "F32", "shape": [2], "data_offsets": [0, 1e300]}, {"dtype": "F32", "shape": [3], "data_offsets": [0, 8]}):
+        hb = json.dumps({"t": entry}).encode()
+        bad = tmp_path / "bad.bin"
+        bad.write_bytes(struct.pack("<Q", len(hb)) + hb + bytes(16))
+        with pytest.raises(RuntimeError):
+            core.SafeTensorsFile(str(bad))
+    bad.write_bytes(struct.pack("<Q", 2 ** 63) + b"{}")
+    with pytest.raises(RuntimeError):
+        core.SafeTensorsFile(str(bad))
     back = convert.hf_to_segment(convert.CheckpointReader(tmp_path), cfg)
     assert torch.equal(back.buffer, seg.buffer)             # byte-exact round trip through HF names and layout
     paths = convert.convert(tmp_path, "tiny", tmp_path / "out", tp=2)
