@@ -21,6 +21,7 @@
 #include <limits>
 #include <memory>
 #include <mutex>
+#include <queue>
 #include <sstream>
 #include <stdexcept>
 #include <string>
@@ -370,18 +371,54 @@ class Tokenizer {
     return space_end(s, i);
   }
 
+  // Apply the merges to the symbols of one piece: always the adjacent pair of lowest rank, the leftmost one among
+  // equals.  The symbols form a linked list and the candidate pairs a heap keyed by (rank, position), so a piece of
+  // n symbols costs O(n log n) whatever it contains (a long run of one letter, or a whole prompt for the
+  // SentencePiece-style models, which merge the text as one piece).  A heap entry remembers the byte lengths of its
+  // two symbols; symbols only ever grow, so an entry whose lengths no longer match is stale and skipped.
   void bpe(std::vector<std::string>& sym) const {
-    while (sym.size() > 1) {
-      int best = std::numeric_limits<int>::max();
-      size_t at = 0;
-      for (size_t k = 0; k + 1 < sym.size(); ++k) {
-        auto it = merges_.find(sym[k] + '\x01' + sym[k + 1]);
-        if (it != merges_.end() && it->second < best) { best = it->second; at = k; }
-      }
-      if (best == std::numeric_limits<int>::max()) break;
-      sym[at] += sym[at + 1];
-      sym.erase(sym.begin() + static_cast<long>(at) + 1);
+    const int n = static_cast<int>(sym.size());
+    if (n < 2) return;
+    struct Node { int prev, next; bool alive; };
+    std::vector<Node> nd(static_cast<size_t>(n));
+    for (int i = 0; i < n; ++i) nd[i] = {i - 1, i + 1 < n ? i + 1 : -1, true};
+    struct Ent { int rank, left; uint32_t len_l, len_r; };
+    auto later = [](const Ent& a, const Ent& b) { return a.rank != b.rank ? a.rank > b.rank : a.left > b.left; };
+    std::priority_queue<Ent, std::vector<Ent>, decltype(later)> heap(later);
+    std::string key;
+    auto consider = [&](int l) {
+      const int r = nd[l].next;
+      if (r < 0) return;
+      key.assign(sym[l]);
+      key.push_back('\x01');
+      key += sym[r];
+      auto it = merges_.find(key);
+      if (it != merges_.end())
+        heap.push({it->second, l, static_cast<uint32_t>(sym[l].size()), static_cast<uint32_t>(sym[r].size())});
+    };
+    for (int i = 0; i + 1 < n; ++i) consider(i);
+    while (!heap.empty()) {
+      const Ent e = heap.top();
+      heap.pop();
+      const int l = e.left;
+      if (!nd[l].alive) continue;
+      const int r = nd[l].next;
+      if (r < 0 || sym[l].size() != e.len_l || sym[r].size() != e.len_r) continue;
+      sym[l] += sym[r];
+      sym[r].clear();
+      nd[r].alive = false;
+      nd[l].next = nd[r].next;
+      if (nd[r].next >= 0) nd[nd[r].next].prev = l;
+      if (nd[l].prev >= 0) consider(nd[l].prev);
+      consider(l);
     }
+    size_t w = 0;
+    for (int i = 0; i < n; ++i) {
+      if (!nd[i].alive) continue;
+      if (w != static_cast<size_t>(i)) sym[w] = std::move(sym[i]);
+      ++w;
+    }
+    sym.resize(w);
   }
 
   void emit(const std::vector<std::string>& sym, std::vector<int32_t>& out) const {
@@ -424,7 +461,7 @@ class Tokenizer {
         emit(sym, ids);
         out.insert(out.end(), ids.begin(), ids.end());
         std::lock_guard<std::mutex> g(*cache_mu_);
-        if (cache_.size() < 200000) cache_.emplace(word, std::move(ids));
+        if (cache_.size() < 200000 && word.size() <= 256) cache_.emplace(word, std::move(ids));   // words, not blobs
       }
     } else {
       std::string norm = "\xE2\x96\x81";

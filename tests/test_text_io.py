@@ -93,6 +93,27 @@ def test_sentencepiece_style_bpe_with_byte_fallback():
     z = t.encode("hello Z")       # 'Z' is not in the vocabulary -> byte token
     assert z[-1] == vocab["<0x5A>"] and t.decode(z) == "hello Z"
     assert t.encode("<s>hello")[0] == 1
+    # this family merges a whole prompt as one piece: the merge loop must not be quadratic in its length
+    import time
+    long_text = "hello world " * 20000                       # 240 k characters
+    t0 = time.perf_counter()
+    ids = t.encode(long_text)
+    assert time.perf_counter() - t0 < 5.0
+    # the trailing space becomes a "▁" of its own, which this toy vocabulary holds
+    assert ids[:2] == [vocab["▁hello"], vocab["▁world"]] and len(ids) == 40001 and ids[-1] == vocab["▁"]
+
+
+def test_one_very_long_word_is_tokenized_in_near_linear_time(trained):
+    """A run of one letter is a single word for the pre-tokenizer; its cost must stay near linear (a quadratic merge
+    loop needs minutes for this input) and the ids are the reference library's."""
+    import time
+    ref, path = trained
+    t = core.Tokenizer.from_file(path)
+    for text in ("a" * 20000, "ab" * 10000, "the" * 7000):
+        assert t.encode(text) == ref.encode(text).ids
+    t0 = time.perf_counter()
+    n = len(t.encode("a" * 400000))
+    assert n > 0 and time.perf_counter() - t0 < 5.0
 
 
 def test_safetensors_reader_and_hf_conversion(tmp_path):
