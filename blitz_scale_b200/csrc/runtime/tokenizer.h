@@ -109,13 +109,20 @@ class Tokenizer {
   std::vector<int32_t> encode(std::string_view text) const {
     std::vector<int32_t> out;
     size_t pos = 0;
+    // next occurrence of every added token at or after `pos`, searched again only once `pos` has passed it: every
+    // added token scans the text once in total, however many of them the text contains
+    constexpr size_t kUnknown = std::string_view::npos - 1;
+    std::vector<size_t> next_at(added_.size(), kUnknown);
     while (pos < text.size()) {
       // earliest added token at or after pos (longest on ties)
       size_t best = std::string_view::npos, best_len = 0;
       int32_t best_id = -1;
-      for (const Added& a : added_) {
+      for (size_t ai = 0; ai < added_.size(); ++ai) {
+        const Added& a = added_[ai];
         if (a.content.empty()) continue;
-        const size_t f = text.find(a.content, pos);
+        if (next_at[ai] == kUnknown || (next_at[ai] != std::string_view::npos && next_at[ai] < pos))
+          next_at[ai] = text.find(a.content, pos);
+        const size_t f = next_at[ai];
         if (f != std::string_view::npos && (f < best || (f == best && a.content.size() > best_len))) {
           best = f;
           best_len = a.content.size();
