@@ -185,6 +185,12 @@ class Batch {
 
   // Keep only `keep` ids (finished or dropped requests release their pages).
   void filter(const std::vector<uint64_t>& keep) {
+    // the common call of a decode step keeps everybody, in order: nothing to do
+    if (keep.size() == seqs_.size()) {
+      bool same = true;
+      for (size_t i = 0; i < keep.size() && same; ++i) same = keep[i] == seqs_[i].spec.id;
+      if (same) return;
+    }
     std::vector<SeqState> kept;
     for (auto& s : seqs_) {
       if (std::find(keep.begin(), keep.end(), s.spec.id) != keep.end()) {
