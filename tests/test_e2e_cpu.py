@@ -14,7 +14,7 @@ import pytest
 
 from blitz_scale_b200.pb.schema import RPCS, pb, render_proto
 from blitz_scale_b200.router.runtime import RouterRuntime
-from blitz_scale_b200.router.server import RouterApp, controller_config_from_cluster, serve_router
+from blitz_scale_b200.router.server import controller_config_from_cluster, serve_router
 from blitz_scale_b200.router.stub import WorkerStub
 from blitz_scale_b200.sim import request_sim
 from blitz_scale_b200.sim.stub_worker import StubBackend

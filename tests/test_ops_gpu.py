@@ -1,5 +1,4 @@
 """GPU numerics of every hand-written kernel against a plain PyTorch fp32 reference of the same op."""
-import math
 
 import pytest
 import torch

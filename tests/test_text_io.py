@@ -1,7 +1,6 @@
 """Native tokenizer, safetensors reader and the Hugging Face -> weight-segment converter (CPU)."""
 import ctypes
 import json
-import os
 
 import pytest
 import torch
