@@ -54,6 +54,22 @@ def test_byte_level_bpe_matches_reference_library(trained):
     assert t.decode_bytes(t.encode("é")[:1], True) in ("é".encode(), "é".encode()[:1])
 
 
+def test_concurrent_encodes_share_the_word_cache_safely(trained):
+    """`encode` releases the interpreter lock and the router calls it from several threads: the shared word cache must
+    give every thread the ids a single thread gets."""
+    import random
+    from concurrent.futures import ThreadPoolExecutor
+    ref, path = trained
+    t = core.Tokenizer.from_file(path)
+    rng = random.Random(4)
+    words = ["hello", "world", "tokenizer", "naïve", "日本語", "123", "don't", "  ", "\n", "x" * 300]
+    texts = [" ".join(rng.choice(words) + str(rng.randrange(50)) for _ in range(200)) for _ in range(64)]
+    want = [ref.encode(x).ids for x in texts]
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        for _ in range(3):
+            assert list(ex.map(t.encode, texts)) == want
+
+
 def test_tokenizer_c_abi(trained):
     _, path = trained
     lib = ctypes.CDLL(core._m.__file__)     # the C ABI lives in the same shared object as the Python module
