@@ -337,7 +337,7 @@ class RouterRuntime:
             return
         lr.tokens.append(token)
         lr.times.append(now)
-        if not final and lr.stop and any(s in lr.detok(lr.tokens[-lr.stop_window:]) for s in lr.stop):
+        if not final and lr.stop and self._stop_hit(lr):
             # every token is at least one byte of text, so the last `stop_window` tokens hold any stop sequence that
             # this token completed; an earlier occurrence would have ended the request already
             final, lr.stopped = 3, True
@@ -359,6 +359,16 @@ class RouterRuntime:
                                    first_token_s=lr.times[0] - lr.t_submit, parent_span_id=self.root_trace.split("-")[2])
             if not lr.done.done():
                 lr.done.set_result(None)
+
+    @staticmethod
+    def _stop_hit(lr: LiveRequest) -> bool:
+        try:
+            text = lr.detok(lr.tokens[-lr.stop_window:])
+        except Exception as e:  # noqa: BLE001 - a detokenizer that fails must not look like a failed worker call
+            log.warning("request %d: detokenizer failed (%s); its stop sequences are ignored from here on", lr.id, e)
+            lr.stop = ()
+            return False
+        return any(s in text for s in lr.stop)
 
     def _deliver(self, now: float) -> None:
         """Hand the tokens the core has released since the last call to their requests."""
