@@ -70,6 +70,7 @@ void bind_runtime(py::module_& m) {
       .def("add_prompts", &Batch::add_prompts).def("mark_prefilled", &Batch::mark_prefilled)
       .def("append_tokens", &Batch::append_tokens, py::arg("tokens"), py::arg("count_cached") = true)
       .def("filter", &Batch::filter).def("unfinished_ids", &Batch::unfinished_ids)
+      .def("generated_tail", &Batch::generated_tail).def("finish_request", &Batch::finish_request)
       .def("extend", &Batch::extend).def("clear", &Batch::clear)
       .def("request_ids", &Batch::request_ids).def("prompt_lens", &Batch::prompt_lens).def("emit_info", &Batch::emit_info)
       .def("encode_generations", [](const Batch& b, const std::vector<int32_t>& toks) { return py::bytes(b.encode_generations(toks)); })

@@ -208,6 +208,26 @@ class Batch {
     return ids;
   }
   // Compact per-request views for the serving loop (the per-step paths must not copy prompts or token histories).
+  // The last `k` generated tokens of request `id` (fewer if it has not generated that many; empty if unknown).
+  std::vector<int32_t> generated_tail(uint64_t id, int k) const {
+    for (auto& s : seqs_) {
+      if (s.spec.id != id) continue;
+      const size_t n = s.generated.size(), take = std::min<size_t>(n, static_cast<size_t>(std::max(0, k)));
+      return std::vector<int32_t>(s.generated.end() - static_cast<long>(take), s.generated.end());
+    }
+    return {};
+  }
+  // End request `id` for a reason the caller found (a stop sequence in its text).  False if it is unknown or has
+  // finished already, in which case its recorded reason stays.
+  bool finish_request(uint64_t id, int reason) {
+    for (auto& s : seqs_) {
+      if (s.spec.id != id) continue;
+      if (s.finish != kFinishNone) return false;
+      s.finish = static_cast<FinishReason>(reason);
+      return true;
+    }
+    return false;
+  }
   std::vector<uint64_t> request_ids() const {
     std::vector<uint64_t> ids;
     ids.reserve(seqs_.size());

@@ -16,6 +16,7 @@ from typing import Dict, List, Optional
 from ..pb.schema import pb
 from ..runtime import core
 from ..worker.service import Backend, seq_spec_from_request
+from ..worker.stopping import StopSequences
 
 
 def stub_token(seed: int, request_id: int, position: int, vocab: int = 32000) -> int:
@@ -33,6 +34,7 @@ class StubBackend(Backend):
                  eos_token: int = -1):
         self.rank, self.world, self.seed, self.layers, self.vocab = rank, world, seed, layers, vocab
         self.eos_token = eos_token
+        self.stopper = StopSequences()        # no tokenizer here: stop sequences match the `<id>` text of the generations
         self.pool = core.PagePool(num_pages, page_size)
         self.status = core.ModelStatus(layers)
         if ready:
@@ -53,6 +55,7 @@ class StubBackend(Backend):
                 "ranks": {"rank": self.rank, "world": self.world}}
 
     def _specs(self, batch) -> List["core.SeqSpec"]:
+        self.stopper.add(batch)
         return [seq_spec_from_request(r, [1] * max(1, len(r.inputs.split())), self.eos_token) for r in batch.requests]
 
     def _cached(self, b) -> Optional[object]:
@@ -72,6 +75,7 @@ class StubBackend(Backend):
         if prefill:
             b.mark_prefilled()
         b.append_tokens(toks, not prefill)
+        self.stopper.check(b)
         return toks
 
     # ------------------------------------------------------------------ inference

@@ -35,6 +35,7 @@ from ..pb.schema import pb
 from ..runtime import core
 from ..runtime.engine import Engine
 from .service import Backend, seq_spec_from_request
+from .stopping import StopSequences
 
 CTL_SLOT_WORDS = 16384  # page ids one transfer slot can publish
 log = logging.getLogger("blitz.worker")
@@ -44,10 +45,12 @@ class GpuBackend(Backend):
     def __init__(self, rank: int, world: int, model: str, *, tp: int = 1, num_pages: int = 2048, page_size: int = 64,
                  max_batch: int = 256, max_batch_tokens: int = 8192, ready: bool = True, use_fabric: bool = True,
                  tp_group=None, model_path: str = "", seed: int = 0, use_multimem: bool = False, copy_ctas: int = 128,
-                 fused_tp: bool = True, precapture: bool = False, eos_token: Optional[int] = None):
+                 fused_tp: bool = True, precapture: bool = False, eos_token: Optional[int] = None,
+                 tokenizer_path: str = ""):
         self.rank, self.world, self.tp = rank, world, tp
         self.cfg = get_config(model)
         self.eos_token = self.cfg.eos_token if eos_token is None else int(eos_token)
+        self.stopper = StopSequences.from_tokenizer_file(tokenizer_path)
         self.model, self.model_path = model, model_path
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.lock = threading.RLock()
@@ -134,7 +137,9 @@ class GpuBackend(Backend):
         return {"ready": self.engine.status.fully_loaded(), "dtype": "bfloat16", "device_type": "cuda",
                 "ranks": {"rank": self.rank, "world": self.world, "tp": self.tp}}
 
-    def _specs(self, batch) -> List["core.SeqSpec"]:
+    def _specs(self, batch, track: bool = True) -> List["core.SeqSpec"]:
+        if track:
+            self.stopper.add(batch)     # the requests are about to live here: remember their stop sequences
         return [seq_spec_from_request(r, eos_token=self.eos_token) for r in batch.requests]
 
     def _cached(self, b):
@@ -147,6 +152,7 @@ class GpuBackend(Backend):
         return b.encode_generations(toks)
 
     def _finish_step(self, b, toks):
+        self.stopper.check(b)          # a request whose text now holds one of its stop sequences ends with this token
         gens = self._emit(b, toks)
         b.filter(b.unfinished_ids())
         if b.size:
@@ -547,7 +553,7 @@ class GpuBackend(Backend):
         return (((int(batch_id) + 1) & 0x0FFFFFFF) << 2) | (int(partial) & 3)
 
     def _rpc_page_list(self, b, batch) -> List[int]:
-        specs = self._specs(batch)
+        specs = self._specs(batch, track=False)
         ids = b.prompt_page_ids_for([sp.id for sp in specs], [len(sp.prompt) for sp in specs])
         if len(ids) + 1 > CTL_SLOT_WORDS:
             raise RuntimeError(f"batch {batch.id}: {len(ids)} KV pages exceed the {CTL_SLOT_WORDS - 1} a transfer slot holds")

@@ -102,7 +102,7 @@ def main(argv=None) -> int:
                          max_batch=a.max_batch_size, max_batch_tokens=a.max_batch_tokens,
                          ready=states[rank] != "Inactive", tp_group=tp_group, model_path=a.model_path,
                          seed=0, use_multimem=a.multimem, fused_tp=not a.no_fused_tp, precapture=a.precapture_graphs,
-                         eos_token=a.eos_token_id)
+                         eos_token=a.eos_token_id, tokenizer_path=a.tokenizer)
     urls = [f"{a.host}:{a.port + r}" for r in range(world)]
 
     async def run():

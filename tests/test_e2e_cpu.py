@@ -956,6 +956,8 @@ def test_end_of_sequence_token_and_stop_sequences_end_a_request():
             # a stop sequence that the 3rd token completes (two tokens long; streamed and not), next to a request
             # that runs to its budget: the two are submitted together, so either may get the lower id
             for rnd, stream in enumerate((False, True, False)):
+                for b in backends:
+                    b.stopper.enabled = rnd != 1         # second round: only the router checks the stop sequences
                 if rnd == 2:
                     rt.decode_steps = 4     # third round: the worker runs 4 decode steps per call, so tokens it produced
                                             # after the stop sequence arrive in the same answer and must be dropped
@@ -988,6 +990,47 @@ def test_end_of_sequence_token_and_stop_sequences_end_a_request():
     too_many, state = asyncio.run(go())
     assert too_many == 422
     assert state == (0, 0, 0, 0, [0, 0], [0, 0])
+
+
+def test_worker_applies_stop_sequences_of_the_contract_by_itself():
+    """A worker called directly (no router) ends a request when its generated text contains one of the request's
+    `stop_sequences`, reports FinishReason 2 and frees the pages; other requests of the batch go on."""
+    from blitz_scale_b200.runtime import core
+    from blitz_scale_b200.sim.stub_worker import stub_token
+    b = StubBackend(0, 1, ready=True)
+    b.prefill_rate, b.decode_step_s = 1e12, 0.0
+    exp = [stub_token(0, 7, 5 + n) for n in range(8)]
+    batch = pb.Batch(id=1, size=2, max_tokens=256)
+    for rid, stops in ((7, [f"<{exp[2]}> <{exp[3]}>", "never"]), (8, [])):
+        r = batch.requests.add()
+        r.id, r.inputs, r.prefill_logprobs, r.top_n_tokens = rid, "", False, 0
+        r.input_tokens.extend(range(5))
+        r.stopping_parameters.max_new_tokens, r.stopping_parameters.ignore_eos_token = 8, True
+        r.stopping_parameters.stop_sequences.extend(stops)
+    out, reasons = {7: [], 8: []}, {}
+
+    def take(raw):
+        for i, t, f, why in zip(*core.parse_generations_full(raw)):
+            out[i].append(t)
+            if f:
+                reasons[i] = why
+    gens, cb, _ = b.prefill(batch, 0, None, [])
+    take(gens)
+    while cb is not None:
+        gens, cb = b.decode([cb], [pb.Tokens()])
+        take(gens)
+    assert out[7] == exp[:4] and reasons == {7: 2, 8: 0} and len(out[8]) == 8
+    assert b.pool.used_pages == 0 and not b.batches and not b.stopper.stops
+    # the pieces: the tail of a request's tokens, and ending it for a reason found outside the batch
+    nb = core.Batch(3, b.pool)
+    assert nb.add_prompts([core.SeqSpec(1, [1, 2, 3], 9)])
+    nb.mark_prefilled()
+    for t in (4, 5, 6):
+        nb.append_tokens([t], True)
+    assert nb.generated_tail(1, 2) == [5, 6] and nb.generated_tail(1, 10) == [4, 5, 6] and nb.generated_tail(99, 2) == []
+    assert nb.finish_request(1, 2) and not nb.finish_request(1, 0) and not nb.finish_request(99, 2)
+    assert nb.unfinished_ids() == [] and core.parse_generations_full(nb.encode_generations([6]))[3] == [2]
+    nb.clear()
 
 
 def test_malformed_request_bodies_are_validation_errors():
@@ -1027,7 +1070,8 @@ def test_malformed_request_bodies_are_validation_errors():
     assert ok == (200, "2")
 
 
-def test_stop_sequences_leaving_clients_and_progressive_migration_together():
+@pytest.mark.parametrize("worker_stops", [True, False])
+def test_stop_sequences_leaving_clients_and_progressive_migration_together(worker_stops):
     """Soak of the ways a request can end before its budget, mixed at random on a 2 + 2 cluster with layer-progressive
     migration and three decode steps per worker call: every request gets exactly the tokens up to its stop sequence
     (or all of them), clients that leave are forgotten, and nothing is left behind anywhere."""
@@ -1041,6 +1085,9 @@ def test_stop_sequences_leaving_clients_and_progressive_migration_together():
         rt.decode_steps = 3
         for b in backends:
             b.decode_step_s, b.prefill_rate = 0.0005, 1e7
+            # workers apply stop sequences themselves; with that off the router's own check is what ends the requests
+            # (the case of a router and workers that do not share a tokenizer)
+            b.stopper.enabled = worker_stops
 
         def detok(ids):
             return " ".join(f"<{i}>" for i in ids)
