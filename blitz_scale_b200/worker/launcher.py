@@ -28,7 +28,8 @@ def parse_args(argv=None):
     ap = argparse.ArgumentParser("blitz-worker")
     ap.add_argument("--model-path", default="")
     ap.add_argument("--model-name", default="llama3_8b")
-    ap.add_argument("-T", "--tokenizer", default="")
+    ap.add_argument("-T", "--tokenizer", default="", help="tokenizer.json: text of generated tokens, which the worker "
+                    "needs to apply the stop sequences of a request (without it they match the <id> text of its generations)")
     ap.add_argument("-V", "--vocab-json", default="")
     ap.add_argument("-P", "--precision", default="bf16", choices=["bf16", "fp16"])
     ap.add_argument("--host", default="127.0.0.1")
