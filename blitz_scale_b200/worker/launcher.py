@@ -70,6 +70,8 @@ def main(argv=None) -> int:
         cluster = json.load(open(a.config))
         states = check_cluster(cluster, a.tensor_parallel)
         get_config(a.model_name)
+        if a.tokenizer and not os.path.isfile(a.tokenizer):
+            raise ValueError(f"tokenizer file {a.tokenizer} does not exist")
         if len(states) != world:
             raise ValueError(f"cluster config lists {len(states)} ranks, world size is {world}")
     except (OSError, ValueError, KeyError) as e:
