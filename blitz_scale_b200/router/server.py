@@ -589,6 +589,11 @@ def main(argv=None) -> None:
             raise ValueError("--client-config must be a JSON list of worker addresses (or a file that holds one)")
         if isinstance(cluster, dict) and isinstance(cluster.get("init_states"), list) and len(cluster["init_states"]) != len(urls):
             raise ValueError(f"{len(urls)} worker addresses for {len(cluster['init_states'])} ranks in the cluster config")
+        if a.tokenizer_path:
+            try:
+                core.Tokenizer.from_file(a.tokenizer_path)
+            except RuntimeError as e:
+                raise ValueError(f"--tokenizer-path: {e}")
     except (OSError, ValueError) as e:
         raise SystemExit(f"router: {e}")
     try:
