@@ -418,11 +418,80 @@ class RouterApp:
     async def prom(self, req):
         return web.Response(text=self.metrics.render(self.rt), content_type="text/plain")
 
+    def openapi(self) -> dict:
+        """The API as an OpenAPI 3 document (the reference generates one from its handler types,
+        router_v2/src/server.rs:704-780)."""
+        num, integer, boolean, string = {"type": "number"}, {"type": "integer"}, {"type": "boolean"}, {"type": "string"}
+        params = {"type": "object", "properties": {
+            "max_new_tokens": dict(integer, default=20, minimum=1), "do_sample": dict(boolean, default=False),
+            "temperature": dict(num, exclusiveMinimum=0), "top_k": dict(integer, minimum=1),
+            "top_p": dict(num, exclusiveMinimum=0, maximum=1), "typical_p": dict(num, exclusiveMinimum=0, maximum=1),
+            "repetition_penalty": dict(num, exclusiveMinimum=0), "seed": dict(integer, minimum=0),
+            "best_of": dict(integer, minimum=1, description="only 1 is served"),
+            "stop": {"type": "array", "items": string, "maxItems": self.limits.max_stop_sequences},
+            "ignore_eos_token": dict(boolean, default=False), "truncate": dict(integer, minimum=1),
+            "return_full_text": dict(boolean, default=False), "details": dict(boolean, default=False),
+            "top_n_tokens": dict(integer, minimum=0, maximum=self.limits.max_top_n_tokens), "watermark": boolean,
+            "decoder_input_details": boolean}}
+        token = {"type": "object", "properties": {"id": integer, "text": string, "logprob": num, "special": boolean}}
+        details = {"type": "object", "nullable": True, "properties": {
+            "finish_reason": {"type": "string", "enum": ["length", "eos_token", "stop_sequence"]}, "generated_tokens": integer,
+            "seed": dict(integer, nullable=True), "prefill": {"type": "array", "items": token},
+            "tokens": {"type": "array", "items": token}}}
+        schemas = {
+            "GenerateParameters": params,
+            "GenerateRequest": {"type": "object", "properties": {
+                "inputs": dict(string, description="prompt text (tokenized by the router)"),
+                "input_tokens": {"type": "array", "items": integer, "description": "prompt as token ids, instead of `inputs`"},
+                "stream": dict(boolean, description="only on `/` and `/invocations`: answer as an event stream"),
+                "parameters": {"$ref": "#/components/schemas/GenerateParameters"}}},
+            "Token": token, "Details": details,
+            "GenerateResponse": {"type": "object", "properties": {"generated_text": string, "details": {"$ref": "#/components/schemas/Details"}}},
+            "StreamResponse": {"type": "object", "properties": {"token": {"$ref": "#/components/schemas/Token"},
+                                                                 "generated_text": dict(string, nullable=True),
+                                                                 "details": {"$ref": "#/components/schemas/Details"}}},
+            "ErrorResponse": {"type": "object", "properties": {"error": string, "error_type": string}},
+            "ClusterStateChange": {"type": "object", "required": ["replica", "state"], "properties": {
+                "replica": integer, "state": {"type": "string", "enum": ["Prefill", "Decode", "Inactive"]}}},
+            "Info": {"type": "object", "properties": {k: {} for k in (
+                "model_id", "model_dtype", "model_device_type", "max_concurrent_requests", "max_best_of", "max_stop_sequences",
+                "max_input_length", "max_total_tokens", "max_batch_prefill_tokens", "max_batch_total_tokens",
+                "validation_workers", "version", "replicas")}}}
+
+        def ref(name):
+            return {"content": {"application/json": {"schema": {"$ref": f"#/components/schemas/{name}"}}}}
+        errors = {"422": dict(ref("ErrorResponse"), description="the request does not validate"),
+                  "429": dict(ref("ErrorResponse"), description="too many requests in flight"),
+                  "503": dict(ref("ErrorResponse"), description="the replica that served the request was lost")}
+        timing = {h: {"schema": integer, "description": "milliseconds"} for h in (
+            "x-total-time", "x-queue-time", "x-inference-time", "x-first-token-time", "x-first-decode-token-time",
+            "x-time-per-token", "x-max-time-between-tokens", "x-avg-time-between-tokens", "x-p99-time-between-tokens")}
+        gen = {"post": {"summary": "generate the whole answer", "requestBody": ref("GenerateRequest"), "responses": dict(
+            errors, **{"200": dict(ref("GenerateResponse"), description="the generation; timing in the headers", headers=timing)})}}
+        stream = {"post": {"summary": "generate token by token (server-sent events)", "requestBody": ref("GenerateRequest"),
+                           "responses": dict(errors, **{"200": {"description": "one `data:` event per token", "content": {
+                               "text/event-stream": {"schema": {"$ref": "#/components/schemas/StreamResponse"}}}}})}}
+        compat = {"post": dict(gen["post"], summary="as /generate inside a one-element list, or as /generate_stream when `stream` is set")}
+        plain = {"200": {"description": "ok"}}
+        return {"openapi": "3.0.3", "info": {"title": "blitz_scale_b200 router", "version": "0.1.0"},
+                "paths": {"/generate": gen, "/generate_stream": stream, "/": dict(compat, get={"summary": "health", "responses": plain}),
+                          "/invocations": compat,
+                          "/info": {"get": {"summary": "model and router parameters, replica states",
+                                            "responses": {"200": dict(ref("Info"), description="ok")}}},
+                          "/health": {"get": {"summary": "every replica in service answers", "responses": dict(
+                              plain, **{"503": dict(ref("ErrorResponse"), description="no replica in service, or one does not answer")})}},
+                          "/ping": {"get": {"summary": "as /health", "responses": plain}},
+                          "/metrics": {"get": {"summary": "Prometheus text format", "responses": plain}},
+                          "/modify_cluster_state": {"post": {
+                              "summary": "bring a replica into a role or take it out (feature manually_scale)",
+                              "requestBody": ref("ClusterStateChange"),
+                              "responses": {"200": {"description": "accepted"}, "403": {"description": "manually_scale is off"},
+                                            "409": {"description": "not possible in the replica's current state"},
+                                            "422": dict(ref("ErrorResponse"), description="malformed body")}}}},
+                "components": {"schemas": schemas}}
+
     async def docs(self, req):
-        paths = {p: {"post": {}} for p in ("/", "/generate", "/generate_stream", "/invocations", "/modify_cluster_state")}
-        paths.update({p: {"get": {}} for p in ("/info", "/health", "/ping", "/metrics")})
-        return web.json_response({"openapi": "3.0.3", "info": {"title": "blitz_scale_b200 router", "version": "0.1.0"},
-                                  "paths": paths})
+        return web.json_response(self.openapi())
 
     async def modify_cluster_state(self, req):
         if not self.rt.ctl.has_feature("manually_scale"):

@@ -1061,6 +1061,14 @@ def test_malformed_request_bodies_are_validation_errors():
                     out.append(("/modify_cluster_state", b, r.status))
             async with s.post(url + "/modify_cluster_state", json={"replica": 7, "state": "Decode"}) as r:
                 assert r.status == 409                       # well-formed, but there is no such replica
+            # the API description: every route, and every schema reference resolves
+            async with s.get(url + "/docs") as r:
+                api = await r.json()
+            import re
+            assert {"/generate", "/generate_stream", "/", "/invocations", "/info", "/health", "/metrics",
+                    "/modify_cluster_state"} <= set(api["paths"])
+            assert set(re.findall(r"#/components/schemas/(\w+)", json.dumps(api))) <= set(api["components"]["schemas"])
+            assert "stop" in api["components"]["schemas"]["GenerateParameters"]["properties"]
             async with s.post(url + "/generate", json={"inputs": "a b c d e", "parameters": {"truncate": 2, "max_new_tokens": 2}}) as r:
                 ok = (r.status, r.headers.get("x-input-length"))
         await _shutdown(stop, tasks)
