@@ -180,10 +180,14 @@ class RouterApp:
     async def _parse(self, body):
         """(token ids, parameters, error text).  Anything in the body that has the wrong type or shape is a validation
         error (HTTP 422), as a typed request structure makes it in the reference, never a server error."""
+        t0 = time.perf_counter()
         try:
-            return await self._parse_checked(body)
+            toks, g, err = await self._parse_checked(body)
         except (TypeError, ValueError, AttributeError, KeyError, OverflowError) as e:
             return None, None, f"invalid request body: {e}"
+        if g is not None:
+            g.validation_s = time.perf_counter() - t0      # tokenization + checks (the reference's validation stage)
+        return toks, g, err
 
     async def _parse_checked(self, body):
         if not isinstance(body, dict):
@@ -246,6 +250,7 @@ class RouterApp:
         times, out = lr.times, lr.tokens
         t_start = lr.t_submit
         total = (times[-1] if times else self.rt.now()) - t_start
+        validation = float(getattr(g, "validation_s", 0.0))
         t_first = times[0] if times else t_start
         t_first_dec = times[1] if len(times) > 1 else t_first
         # the interval between the prefill token and the first decode token contains the KV migration: it is reported
@@ -254,7 +259,8 @@ class RouterApp:
         e = lr.entry
         queue_s = (e.t_batched - e.t_arrival) if e is not None and e.t_batched >= 0 else 0.0
         stats = {
-            "x-compute-type": "gpu+optimized", "x-total-time": int(total * 1e3), "x-validation-time": 0,
+            "x-compute-type": "gpu+optimized", "x-total-time": int((total + validation) * 1e3),
+            "x-validation-time": int(validation * 1e3),
             "x-queue-time": int(queue_s * 1e3), "x-inference-time": int((total - queue_s) * 1e3),
             "x-first-token-time": int((t_first - t_start) * 1e3),
             "x-first-decode-token-time": int((t_first_dec - t_start) * 1e3),
@@ -266,7 +272,8 @@ class RouterApp:
             "x-input-length": len(toks), "x-output-length": len(out), "x-generated-tokens": len(out),
         }
         m = self.metrics
-        m.observe("blitz_request_duration", total)
+        m.observe("blitz_request_duration", total + validation)
+        m.observe("blitz_request_validation_duration", validation)
         m.observe("blitz_request_queue_duration", queue_s)
         m.observe("blitz_request_inference_duration", total - queue_s)
         m.observe("blitz_request_mean_time_per_token_duration", total / max(1, len(out)))
