@@ -51,7 +51,7 @@ class Tokenizer {
     const json::Value& model = root.at("model");
     if (const json::Value* ty = model.find("type"))
       if (ty->type == json::Value::String && ty->str != "BPE") throw std::runtime_error("tokenizer: only BPE models");
-    for (const auto& kv : model.at("vocab").obj) t.add_token(kv.first, static_cast<int32_t>(kv.second.as_int()));
+    for (const auto& kv : model.at("vocab").obj) t.add_token(kv.first, kv.second.as_int());
     int rank = 0;
     for (const json::Value& m : model.at("merges").arr) {
       std::string a, b;
@@ -85,8 +85,9 @@ class Tokenizer {
     if (const json::Value* add = root.find("added_tokens"))
       for (const json::Value& a : add->arr) {
         const std::string& content = a.at("content").str;
-        const int32_t id = static_cast<int32_t>(a.at("id").as_int());
-        t.add_token(content, id);
+        const int64_t id64 = a.at("id").as_int();
+        t.add_token(content, id64);
+        const int32_t id = static_cast<int32_t>(id64);
         bool special = false;
         if (const json::Value* sp = a.find("special")) special = sp->type == json::Value::Bool && sp->b;
         t.added_.push_back({content, id, special});
@@ -197,11 +198,13 @@ class Tokenizer {
   mutable std::unique_ptr<std::mutex> cache_mu_ = std::make_unique<std::mutex>();
   mutable std::unordered_map<std::string, std::vector<int32_t>> cache_;
 
-  void add_token(const std::string& s, int32_t id) {
+  void add_token(const std::string& s, int64_t id) {
     if (id < 0) return;
-    vocab_[s] = id;
-    if (static_cast<size_t>(id) >= id_to_token_.size()) id_to_token_.resize(id + 1);
-    id_to_token_[id] = s;
+    // the id table is dense: an id far beyond any real vocabulary (a damaged file) must not size it
+    if (id >= (int64_t{1} << 24)) throw std::runtime_error("tokenizer: token id " + std::to_string(id) + " is out of range");
+    vocab_[s] = static_cast<int32_t>(id);
+    if (static_cast<size_t>(id) >= id_to_token_.size()) id_to_token_.resize(static_cast<size_t>(id) + 1);
+    id_to_token_[static_cast<size_t>(id)] = s;
   }
   bool is_added(int32_t id) const {
     for (const Added& a : added_) if (a.id == id) return true;

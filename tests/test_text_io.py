@@ -108,6 +108,11 @@ def test_sentencepiece_style_bpe_with_byte_fallback():
     z = t.encode("hello Z")       # 'Z' is not in the vocabulary -> byte token
     assert z[-1] == vocab["<0x5A>"] and t.decode(z) == "hello Z"
     assert t.encode("<s>hello")[0] == 1
+    # a damaged file: an id far beyond any vocabulary is refused instead of sizing the id table
+    for broken in ({**js, "model": {**js["model"], "vocab": {**vocab, "zz": 99999999999}}},
+                   {**js, "added_tokens": [{"id": 2 ** 40, "content": "<x>", "special": True}]}):
+        with pytest.raises(RuntimeError):
+            core.Tokenizer.from_json(json.dumps(broken))
     # this family merges a whole prompt as one piece: the merge loop must not be quadratic in its length
     import time
     long_text = "hello world " * 20000                       # 240 k characters
