@@ -110,9 +110,14 @@ inline std::vector<TraceItem> load_trace_csv(const std::string& path, double sca
     std::string a, b, c;
     if (!std::getline(ss, a, ',') || !std::getline(ss, b, ',') || !std::getline(ss, c, ',')) continue;
     TraceItem it;
-    it.t = std::stod(a) * 1e-3 / scale_factor;
-    it.input_len = std::min<int64_t>(std::stoll(b), truncate);
-    it.output_len = std::max<int64_t>(1, std::stoll(c));
+    try {
+      it.t = std::stod(a) * 1e-3 / scale_factor;
+      it.input_len = std::min<int64_t>(std::stoll(b), truncate);
+      it.output_len = std::max<int64_t>(1, std::stoll(c));
+    } catch (const std::exception&) {
+      continue;   // a row whose fields are not numbers of a sane size is skipped like a header
+    }
+    if (!(it.t >= 0) || !std::isfinite(it.t) || it.input_len < 1) continue;
     it.seed = n++;
     out.push_back(it);
   }

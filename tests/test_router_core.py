@@ -206,6 +206,9 @@ def test_csv_trace(tmp_path):
     p.write_text("timestamp,prefill,decode\n1000,100,20\n500,9000,5\n")
     tr = core.load_trace_csv(str(p), 2.0, 4095)
     assert [(x.t, x.input_len, x.output_len) for x in tr] == [(0.25, 4095, 5), (0.5, 100, 20)]
+    # rows that are not three sane numbers are skipped, like the header
+    p.write_text("t,in,out\n1e300,99999999999999999999,5\n1e999,5,5\n5,0,4\nx,y,z\n1,2\n1000,64,8\n")
+    assert [(x.t, x.input_len, x.output_len) for x in core.load_trace_csv(str(p), 1.0, 4095)] == [(1.0, 64, 8)]
 
 
 # ------------------------------------------------------------------------------------------------ whole-cluster simulations
