@@ -447,23 +447,27 @@ def test_router_cli_reports_configuration_mistakes_in_one_line(tmp_path):
     assert "tunnel" in run("--client-config", two, "--deployment-config-path", str(good), "--ngrok")
 
 
-def test_worker_launcher_checks_the_cluster_description_before_touching_a_gpu(tmp_path):
+def test_worker_launcher_checks_the_cluster_description_before_touching_a_gpu(tmp_path, monkeypatch):
     import json
-    import subprocess
-    import sys
+
+    from blitz_scale_b200.worker import launcher
     good = tmp_path / "good.json"
     good.write_text(json.dumps({"init_states": ["Prefill", "Decode"]}))
     bad = tmp_path / "bad.json"
     bad.write_text(json.dumps({"init_states": ["Prefill", "Sleeping"]}))
 
     def run(world, *args):
-        env = dict(os.environ, WORLD_SIZE=str(world), RANK="0", LOCAL_RANK="0")
-        r = subprocess.run([sys.executable, "-m", "blitz_scale_b200.worker.launcher", *args], capture_output=True, text=True,
-                           timeout=120, env=env, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-        assert r.returncode != 0 and "Traceback" not in r.stderr, r.stderr
-        return r.stderr.strip().splitlines()[-1]
+        # the checks come first in `main`: it leaves with one line before any device, log file or process group is touched
+        monkeypatch.setenv("WORLD_SIZE", str(world))
+        monkeypatch.setenv("RANK", "0")
+        monkeypatch.setenv("LOCAL_RANK", "0")
+        with pytest.raises(SystemExit) as e:
+            launcher.main(list(args))
+        assert isinstance(e.value.code, str)
+        return e.value.code
     assert "lists 2 ranks, world size is 1" in run(1, "--config", str(good), "--model-name", "tiny")
     assert "init_states" in run(2, "--config", str(bad), "--model-name", "tiny")
     assert "must share a state" in run(2, "--config", str(good), "--model-name", "tiny", "-TP", "2")
     assert "unknown model" in run(2, "--config", str(good), "--model-name", "nope")
+    assert "tokenizer file" in run(2, "--config", str(good), "--model-name", "tiny", "-T", str(tmp_path / "none.json"))
     assert "pipeline parallelism" in run(2, "--config", str(good), "--model-name", "tiny", "-PP", "2")
