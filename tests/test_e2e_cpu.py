@@ -825,9 +825,12 @@ def test_client_disconnect_stops_generation_for_that_request():
     assert state[5] >= 1 and state[6] < 400                      # filtered; nowhere near the 2000 steps asked for
 
 
-def test_tensor_parallel_replicas_over_grpc_and_loss_of_one_shard():
+@pytest.mark.parametrize("progressive", [False, True])
+def test_tensor_parallel_replicas_over_grpc_and_loss_of_one_shard(progressive):
     """Replicas of two ranks each: every action goes to both ranks of a replica; when one shard's worker goes away the
-    whole replica is lost (the failing rank maps to its replica), and the survivor takes over both phases."""
+    whole replica is lost (the failing rank maps to its replica), and the survivor takes over both phases.  With
+    layer-progressive migration the prefill call spans both shards of both replicas; a decode shard that is gone is
+    then noticed before the prompt has produced anything, so the prompt is served again instead of failing."""
     async def go():
         n, tp = 4, 2
         ports = _free_ports(n)
@@ -839,7 +842,8 @@ def test_tensor_parallel_replicas_over_grpc_and_loss_of_one_shard():
             tasks.append(asyncio.create_task(serve(backends[r], "127.0.0.1", ports[r], stop_event=stop, ready_event=ready)))
             stops.append(stop)
             await ready.wait()
-        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n}, tp, "impl_blitz,impl_nvl",
+        cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * n}, tp,
+                                             "impl_blitz,impl_nvl" + (",migrate_progressive" if progressive else ""),
                                              max_blocks_per_replica=4000)
         rt = RouterRuntime(cfg, [f"127.0.0.1:{p}" for p in ports], model_layers=2)
         assert rt.ctl.num_replicas == 2
@@ -852,11 +856,16 @@ def test_tensor_parallel_replicas_over_grpc_and_loss_of_one_shard():
         assert err is None and len(toks) == 5
         counts = [dict(b.counters) for b in backends]
         assert counts[0]["prefill"] == counts[1]["prefill"] == 1 and counts[2]["decode"] == counts[3]["decode"] >= 4
-        assert counts[0]["migrate"] == counts[1]["migrate"] == 1 and counts[2]["immigrate"] == counts[3]["immigrate"] == 1
+        moved = "migrate_progressive" if progressive else "migrate"
+        assert counts[0][moved] == counts[1][moved] == 1 and counts[2]["immigrate"] == counts[3]["immigrate"] == 1
         stops[3].set()                                            # one shard of the decode replica goes away
         await asyncio.wait([tasks[3]], timeout=5)
-        err, _ = await one(5)
-        assert err == "replica lost" and rt.ctl.state_name(1) == "Inactive" and rt.ctl.state_name(0) == "Prefill"
+        err, toks_lost = await one(5)
+        if progressive:
+            assert err is None and len(toks_lost) == 5            # nothing had been delivered: served again by replica 0
+        else:
+            assert err == "replica lost"
+        assert rt.ctl.state_name(1) == "Inactive" and rt.ctl.state_name(0) == "Prefill"
         for _ in range(40):                                       # the surviving shard of the lost replica drops its state
             if not backends[2].batches:
                 break
