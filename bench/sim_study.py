@@ -28,6 +28,7 @@ MODELS = {
 POLICIES = {
     "multicast, stop-the-world load (impl_blitz,impl_nvl)": "impl_blitz,impl_nvl",
     "multicast + live execution (impl_blitz,impl_nvl,impl_live)": "impl_blitz,impl_nvl,impl_live",
+    "multicast + arrival-rate signal (impl_blitz,impl_nvl,planner_arrival_rate)": "impl_blitz,impl_nvl,planner_arrival_rate",
     "host-cache load (impl_sllm,cache_all_hit)": "impl_sllm,cache_all_hit",
     "disk load (impl_sllm,cache_all_miss)": "impl_sllm,cache_all_miss",
 }
@@ -68,13 +69,29 @@ def run(model: str, burst_factor: float, horizon_ms: float, seed: int = 0):
         p.tokens_prefilled_per_sec = max(1, int(m["prefill_tps"] * horizon_ms * 1e-3))
         p.tokens_transferred_per_sec = int(cm.kv_tokens_per_s)
         p.max_prefill, p.max_decode = R - 1, R - 1
+        # only read with the feature planner_arrival_rate: prompt tokens arrived in the last 50 ms against the rate of
+        # one replica, as a second lower bound on the prefill side
+        p.prefill_rate_per_sec, p.arrival_window_ms = float(m["prefill_tps"]), 50.0
         cfg.planner = p
         rep = core.ClusterSim(cfg, cm).run(trace)
         burst = [r for r in rep.requests if 5.0 <= r.t_arrival < 11.0]
         ttft = [r.ttft for r in burst]
         viol = sum(1 for r in burst if r.ttft > max(0.3, 0.000375 * r.input_len)) / max(1, len(burst))
+
+        def mean_count(samples, t_lo=5.0, t_hi=11.0):      # time-weighted replicas of a role during the burst
+            area, t_prev, n_prev = 0.0, t_lo, 0
+            for t, n in samples:                           # (time, count) whenever the count changed
+                if t <= t_lo:
+                    n_prev = n
+                    continue
+                if t >= t_hi:
+                    break
+                area += (t - t_prev) * n_prev
+                t_prev, n_prev = t, n
+            return (area + (t_hi - t_prev) * n_prev) / (t_hi - t_lo)
         rows.append({"policy": name, "requests": len(rep.requests), "failed": rep.failed,
                      "scale_outs": len(rep.scale_up_latency),
+                     "gpus_in_burst": round((mean_count(rep.prefill_replicas) + mean_count(rep.decode_replicas)) * tp, 2),
                      "scale_out_latency_ms": round(1e3 * (sum(rep.scale_up_latency.values()) / max(1, len(rep.scale_up_latency))), 1),
                      "ttft_ms_p50": round(1e3 * pct(ttft, 0.5), 1), "ttft_ms_p99": round(1e3 * pct(ttft, 0.99), 1),
                      "max_tbt_ms_p99": round(1e3 * pct([r.max_tbt for r in burst], 0.99), 1),
@@ -95,9 +112,9 @@ def main():
     for o in out:
         print(f"\n{o['model']} (tp {o['tp']}, {o['replicas']} replicas): {o['base_rps']} -> {o['burst_rps']} req/s, "
               f"{o['trace_requests']} requests, planner horizon {o['planner_horizon_ms']:.0f} ms  [{o['kind']}]")
-        print(f"{'policy':62s} {'ups':>3s} {'scale-out ms':>12s} {'TTFT p50':>9s} {'TTFT p99':>9s} {'maxTBT p99':>10s} {'SLO viol':>8s}")
+        print(f"{'policy':76s} {'ups':>3s} {'GPUs':>5s} {'scale-out ms':>12s} {'TTFT p50':>9s} {'TTFT p99':>9s} {'maxTBT p99':>10s} {'SLO viol':>8s}")
         for r in o["rows"]:
-            print(f"{r['policy']:62s} {r['scale_outs']:3d} {r['scale_out_latency_ms']:12.1f} {r['ttft_ms_p50']:9.1f} "
+            print(f"{r['policy']:76s} {r['scale_outs']:3d} {r['gpus_in_burst']:5.2f} {r['scale_out_latency_ms']:12.1f} {r['ttft_ms_p50']:9.1f} "
                   f"{r['ttft_ms_p99']:9.1f} {r['max_tbt_ms_p99']:10.1f} {r['ttft_violation_rate']:8.4f}")
     if a.json:
         json.dump(out, open(a.json, "w"), indent=1)

@@ -70,9 +70,12 @@ void bind_router(py::module_& m) {
       .def_readwrite("tokens_transferred_per_sec", &PlannerConfig::tokens_transferred_per_sec)
       .def_readwrite("max_blocks_per_replica", &PlannerConfig::max_blocks_per_replica)
       .def_readwrite("block_size", &PlannerConfig::block_size)
-      .def_readwrite("scale_down_threshold_ms", &PlannerConfig::scale_down_threshold_ms);
+      .def_readwrite("scale_down_threshold_ms", &PlannerConfig::scale_down_threshold_ms)
+      .def_readwrite("prefill_rate_per_sec", &PlannerConfig::prefill_rate_per_sec)
+      .def_readwrite("arrival_window_ms", &PlannerConfig::arrival_window_ms);
   py::class_<PlannerView>(m, "PlannerView").def(py::init<>())
       .def_readwrite("num_prefill", &PlannerView::num_prefill).def_readwrite("num_decode", &PlannerView::num_decode)
+      .def_readwrite("arrival_tokens_per_sec", &PlannerView::arrival_tokens_per_sec)
       .def_readwrite("decode_used_blocks", &PlannerView::decode_used_blocks)
       .def_readwrite("prefill_used_blocks", &PlannerView::prefill_used_blocks)
       .def_readwrite("waiting_prefill_tokens", &PlannerView::waiting_prefill_tokens);
@@ -80,7 +83,8 @@ void bind_router(py::module_& m) {
       .def_readonly("prefill_thpt_min", &ScaleBands::prefill_thpt_min).def_readonly("prefill_thpt_max", &ScaleBands::prefill_thpt_max)
       .def_readonly("prefill_kv_min", &ScaleBands::prefill_kv_min).def_readonly("prefill_kv_max", &ScaleBands::prefill_kv_max)
       .def_readonly("decode_mem_min", &ScaleBands::decode_mem_min).def_readonly("decode_mem_max", &ScaleBands::decode_mem_max)
-      .def_readonly("decode_kv_min", &ScaleBands::decode_kv_min).def_readonly("decode_kv_max", &ScaleBands::decode_kv_max);
+      .def_readonly("decode_kv_min", &ScaleBands::decode_kv_min).def_readonly("decode_kv_max", &ScaleBands::decode_kv_max)
+      .def_readonly("prefill_rate_min", &ScaleBands::prefill_rate_min).def_readonly("prefill_rate_max", &ScaleBands::prefill_rate_max);
   py::class_<ScaleTarget>(m, "ScaleTarget").def_readonly("d_prefill", &ScaleTarget::d_prefill)
       .def_readonly("d_decode", &ScaleTarget::d_decode).def_readonly("bands", &ScaleTarget::bands);
   m.def("plan_scale", &plan_scale);

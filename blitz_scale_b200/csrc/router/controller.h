@@ -106,6 +106,7 @@ class Controller {
       if (reps_[r].m.model_loaded) steer_.record_model_loaded(r);
       log_transition(r, RState::Inactive, *st, true);
     }
+    arrival_signal_ = features_.has("planner_arrival_rate") && cfg.planner.prefill_rate_per_sec > 0;
     cfg_.planner.block_size = cfg.block_size;
     cfg_.planner.max_blocks_per_replica = cfg.max_blocks_per_replica;
   }
@@ -115,6 +116,7 @@ class Controller {
     requests_[e.id] = e;
     queue_.append(e);
     counters_["blitz_request_count"] += 1;
+    if (arrival_signal_) arrivals_.push_back({e.t_arrival, e.input_len});
   }
   // The client of `id` went away.  A request that still waits in the queue is forgotten at once (returns true; the
   // queue drops its entry when it reaches it); one that is being served ends with its next token and, if the
@@ -1010,6 +1012,13 @@ class Controller {
       return;
     }
     v.waiting_prefill_tokens = queue_.waiting_prefill_tokens();
+    if (arrival_signal_) {
+      const double w = std::max(1.0, cfg_.planner.arrival_window_ms) * 1e-3;
+      while (!arrivals_.empty() && arrivals_.front().first < now - w) arrivals_.pop_front();
+      uint64_t tokens = 0;
+      for (auto& a : arrivals_) tokens += a.second;
+      v.arrival_tokens_per_sec = static_cast<double>(tokens) / w;
+    }
     ScaleTarget t = plan_scale(cfg_.planner, v);
     // The reference sizes the decode side by KV memory only.  A decode replica is also full when it holds as many
     // sequences as a worker step carries: when the decode side is nearly full in that sense (or prefilled batches
@@ -1485,6 +1494,8 @@ class Controller {
 
   ControllerConfig cfg_;
   FeatureSet features_;
+  bool arrival_signal_ = false;                            // feature planner_arrival_rate with a configured rate
+  std::deque<std::pair<double, uint32_t>> arrivals_;       // (arrival time, prompt tokens) inside the rate window
   BatchQueue queue_;
   Steersman steer_;
   std::vector<Rep> reps_;

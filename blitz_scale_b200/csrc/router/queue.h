@@ -198,7 +198,7 @@ class FeatureSet {
         {"fast", {}}, {"live", {}},
         {"cache_replace", {}}, {"cache_all_hit", {}}, {"cache_all_miss", {}},
         {"manually_scale", {}}, {"motiv", {}}, {"mock_transfer", {}}, {"optimize_op_loading", {}},
-        {"optimize_network_interference", {}}, {"decode_load_balance", {}}, {"decode_first_fit", {}}, {"prefill_share_idle", {}}, {"migrate_progressive", {}}, {"statistic", {}}, {"ngrok", {}},
+        {"optimize_network_interference", {}}, {"decode_load_balance", {}}, {"decode_first_fit", {}}, {"prefill_share_idle", {}}, {"migrate_progressive", {}}, {"planner_arrival_rate", {}}, {"statistic", {}}, {"ngrok", {}},
         {"eval_all", {"impl_blitz", "impl_fast_pro", "impl_live_pro"}},
         {"eval_net", {"impl_blitz", "impl_fast_pro", "impl_live_pro", "optimize_network_interference"}},
         {"eval_fast", {"impl_blitz", "impl_fast_pro"}},

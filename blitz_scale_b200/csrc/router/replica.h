@@ -88,6 +88,11 @@ struct PlannerConfig {
   uint32_t max_blocks_per_replica = 30000;
   uint32_t block_size = 64;
   double scale_down_threshold_ms = 333;
+  // Arrival-rate signal (feature `planner_arrival_rate`): prompt tokens that arrived during the last
+  // `arrival_window_ms`, as a rate, against what one prefill replica takes per second.  The queue-based rule above
+  // reacts once a backlog has built up; this one reacts to the rate that builds it.  0 = not configured.
+  double prefill_rate_per_sec = 0;
+  double arrival_window_ms = 50;
 };
 
 struct PlannerView {
@@ -95,11 +100,13 @@ struct PlannerView {
   uint64_t decode_used_blocks = 0;        // blocks held by decode-side replicas
   uint64_t prefill_used_blocks = 0;       // blocks held by prefill replicas (their KV awaits migration)
   uint64_t waiting_prefill_tokens = 0;
+  double arrival_tokens_per_sec = 0;      // 0 unless the arrival-rate signal is on
 };
 
 struct ScaleBands {
   uint32_t prefill_thpt_min = 0, prefill_thpt_max = 0, prefill_kv_min = 0, prefill_kv_max = 0;
   uint32_t decode_mem_min = 0, decode_mem_max = 0, decode_kv_min = 0, decode_kv_max = 0;
+  uint32_t prefill_rate_min = 0, prefill_rate_max = 0;
 };
 
 struct ScaleTarget {
@@ -138,8 +145,15 @@ inline ScaleTarget plan_scale(const PlannerConfig& c, const PlannerView& v) {
   };
   const uint32_t dmin = std::max(b.decode_mem_min, b.decode_kv_min);
   const uint32_t dmax = std::max({b.decode_mem_max, b.decode_kv_max, dmin});
-  const uint32_t pmin = std::max(b.prefill_thpt_min, b.prefill_kv_min);
-  const uint32_t pmax = std::max({b.prefill_thpt_max, b.prefill_kv_max, pmin});
+  uint32_t pmin = std::max(b.prefill_thpt_min, b.prefill_kv_min);
+  uint32_t pmax = std::max({b.prefill_thpt_max, b.prefill_kv_max, pmin});
+  if (c.prefill_rate_per_sec > 0 && v.arrival_tokens_per_sec > 0) {
+    // utilisation band on the arrival rate: enough replicas to take what arrives at no more than `prefill_upper`
+    b.prefill_rate_min = ceil_div_f(v.arrival_tokens_per_sec, c.prefill_upper, c.prefill_rate_per_sec);
+    b.prefill_rate_max = ceil_div_f(v.arrival_tokens_per_sec, c.prefill_lower, c.prefill_rate_per_sec);
+    pmin = std::max(pmin, b.prefill_rate_min);
+    pmax = std::max({pmax, b.prefill_rate_max, pmin});
+  }
   t.d_prefill = decide(pmin, pmax, v.num_prefill);
   t.d_decode = decide(dmin, dmax, v.num_decode);
   // clamp to the configured replica counts (planner.rs:110-126)

@@ -581,6 +581,9 @@ def build_parser() -> argparse.ArgumentParser:
                     help="how much queued prefill work per replica the planner tolerates before it adds one, as time: the "
                          "capacity it plans with is tokens-prefilled-per-sec x horizon.  1000 = the per-second rule of the "
                          "reference; with a ~25 ms scale-out 100 keeps p99 TTFT far lower under bursts")
+    ap.add_argument("--planner-arrival-window-ms", type=float, default=0.0, help="also size the prefill side by the rate "
+                    "at which prompt tokens arrived during the last W ms against --tokens-prefilled-per-sec (a utilisation "
+                    "band on the arrival rate: reacts before a backlog has built up, uses more replicas).  0 = off")
     ap.add_argument("--block-size", type=int, default=64, help="tokens per KV page; must equal the workers' --page-size")
     ap.add_argument("--tokens-prefilled-per-sec", type=int, default=15000)
     ap.add_argument("--tokens-transferred-per-sec", type=int, default=96000)
@@ -681,8 +684,13 @@ def main(argv=None) -> None:
         get_config(a.model_name)
     except (ValueError, KeyError) as e:
         raise SystemExit(f"router: {e}")
+    arrival = {}
+    if a.planner_arrival_window_ms > 0:
+        # the planner also sizes the prefill side by the rate at which prompt tokens arrive (feature planner_arrival_rate)
+        a.features = a.features + ",planner_arrival_rate"
+        arrival = dict(prefill_rate_per_sec=float(a.tokens_prefilled_per_sec), arrival_window_ms=float(a.planner_arrival_window_ms))
     cfg = controller_config_from_cluster(
-        cluster, a.tensor_parallel_size, a.features, model_name=a.model_name,
+        cluster, a.tensor_parallel_size, a.features, model_name=a.model_name, **arrival,
         max_prefill_tokens=a.max_batch_prefill_tokens, max_total_tokens=max(a.max_total_tokens, 16000),
         max_blocks_per_replica=a.max_blocks_per_replica, block_size=a.block_size, mock_load_ms=a.mock_load_millis,
         tokens_prefilled_per_sec=max(1, int(a.tokens_prefilled_per_sec * a.planner_horizon_ms * 1e-3)),

@@ -817,3 +817,40 @@ def test_deliveries_carry_the_finish_reason():
     ctl.on_prefill_done(pf.op_id, [core.TokenOut(1, 5, True, 1)], 0.01)
     d = [a for a in ctl.step(0.02) if a.type == A.Deliver]
     assert len(d) == 1 and d[0].final and d[0].finish_reason == 1
+
+
+def test_planner_arrival_rate_signal():
+    """With the feature planner_arrival_rate the prefill side is also sized by the rate at which prompt tokens arrive:
+    a utilisation band on that rate, which asks for replicas before a backlog exists."""
+    c = core.PlannerConfig()
+    c.prefill_lower, c.prefill_upper, c.max_prefill = 0.5, 0.7, 8
+    c.tokens_prefilled_per_sec, c.prefill_rate_per_sec = 1000, 10000.0
+    v = core.PlannerView()
+    v.num_prefill, v.num_decode = 1, 1
+    assert core.plan_scale(c, v).d_prefill == 0                      # nothing waits, nothing arrives
+    v.arrival_tokens_per_sec = 30000.0                               # 3 replicas' worth at full utilisation
+    t = core.plan_scale(c, v)
+    assert (t.bands.prefill_rate_min, t.bands.prefill_rate_max) == (5, 6) and t.d_prefill == 5   # to the middle of [5, 6]
+    c.prefill_rate_per_sec = 0.0
+    assert core.plan_scale(c, v).d_prefill == 0                      # not configured: the view's rate is not read
+    # in the controller: a burst of arrivals inside the window asks for replicas although the queue is still short
+    cfg = _cfg(["Prefill", "Decode", "Inactive", "Inactive"], "impl_blitz,impl_nvl,planner_arrival_rate")
+    p = cfg.planner
+    p.tokens_prefilled_per_sec, p.prefill_rate_per_sec, p.arrival_window_ms = 10 ** 6, 20000.0, 50.0   # the queue rule never fires
+    cfg.planner = p
+    ctl = core.Controller(cfg)
+    for i in range(6):
+        ctl.submit(E(i, 500, 4, 0.001 * i))                          # 3000 tokens in 6 ms = 60 k tokens/s over the window
+    acts = []
+    for k in range(30):
+        acts += ctl.step(0.006 + 0.001 * k)
+    assert any(a.type in (core.ActionType.NvlBroadcast, core.ActionType.TanzBroadcast) for a in acts)
+    same = _cfg(["Prefill", "Decode", "Inactive", "Inactive"], "impl_blitz,impl_nvl")
+    same.planner = p
+    ctl = core.Controller(same)
+    for i in range(6):
+        ctl.submit(E(i, 500, 4, 0.001 * i))
+    acts = []
+    for k in range(30):
+        acts += ctl.step(0.006 + 0.001 * k)
+    assert not any(a.type in (core.ActionType.NvlBroadcast, core.ActionType.TanzBroadcast) for a in acts)

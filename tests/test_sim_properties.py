@@ -13,7 +13,8 @@ FEATURES = ["impl_blitz,impl_nvl", "impl_blitz,impl_nvl,impl_live", "impl_blitz,
             "impl_blitz,impl_nvl,impl_tanz", "impl_blitz,impl_nvl,mutate", "impl_sllm,cache_replace",
             "impl_sllm,cache_all_miss", "impl_blitz,impl_nvl,unidirect", "impl_blitz,impl_nvl,prefill_share_idle",
             "impl_blitz,impl_nvl,impl_live,decode_first_fit", "impl_blitz,impl_nvl,migrate_progressive",
-            "impl_blitz,impl_fast_pro,impl_live_pro,migrate_progressive", "impl_blitz,impl_nvl,mutate,migrate_progressive"]
+            "impl_blitz,impl_fast_pro,impl_live_pro,migrate_progressive", "impl_blitz,impl_nvl,mutate,migrate_progressive",
+            "impl_blitz,impl_nvl,planner_arrival_rate", "impl_blitz,impl_fast_pro,impl_live_pro,planner_arrival_rate"]
 
 
 @settings(max_examples=int(os.environ.get("BLITZ_PROPERTY_EXAMPLES", "25")), deadline=None)
@@ -34,6 +35,7 @@ def test_requests_and_blocks_are_conserved(feat, seed, n_inactive, burst, cv, ki
     p = cfg.planner
     p.tokens_prefilled_per_sec, p.tokens_transferred_per_sec = int(prefill_rate * 0.2), 500000
     p.max_prefill, p.max_decode = len(states) - 1, len(states) - 1
+    p.prefill_rate_per_sec, p.arrival_window_ms = prefill_rate, 50.0      # read only with the feature planner_arrival_rate
     cfg.planner = p
     cm = core.CostModel()
     cm.prefill_tokens_per_s = prefill_rate
