@@ -69,9 +69,9 @@ def run(model: str, burst_factor: float, horizon_ms: float, seed: int = 0):
         p.tokens_prefilled_per_sec = max(1, int(m["prefill_tps"] * horizon_ms * 1e-3))
         p.tokens_transferred_per_sec = int(cm.kv_tokens_per_s)
         p.max_prefill, p.max_decode = R - 1, R - 1
-        # only read with the feature planner_arrival_rate: prompt tokens arrived in the last 50 ms against the rate of
+        # only read with the feature planner_arrival_rate: prompt tokens arrived in the last 200 ms against the rate of
         # one replica, as a second lower bound on the prefill side
-        p.prefill_rate_per_sec, p.arrival_window_ms = float(m["prefill_tps"]), 50.0
+        p.prefill_rate_per_sec, p.arrival_window_ms = float(m["prefill_tps"]), 200.0
         cfg.planner = p
         rep = core.ClusterSim(cfg, cm).run(trace)
         burst = [r for r in rep.requests if 5.0 <= r.t_arrival < 11.0]

@@ -583,7 +583,8 @@ def build_parser() -> argparse.ArgumentParser:
                          "reference; with a ~25 ms scale-out 100 keeps p99 TTFT far lower under bursts")
     ap.add_argument("--planner-arrival-window-ms", type=float, default=0.0, help="also size the prefill side by the rate "
                     "at which prompt tokens arrived during the last W ms against --tokens-prefilled-per-sec (a utilisation "
-                    "band on the arrival rate: reacts before a backlog has built up, uses more replicas).  0 = off")
+                    "band on the arrival rate: reacts before a backlog has built up, uses more replicas; a window that holds only a few "
+                    "arrivals makes replicas come and go, 200 is a sensible start).  0 = off")
     ap.add_argument("--block-size", type=int, default=64, help="tokens per KV page; must equal the workers' --page-size")
     ap.add_argument("--tokens-prefilled-per-sec", type=int, default=15000)
     ap.add_argument("--tokens-transferred-per-sec", type=int, default=96000)
