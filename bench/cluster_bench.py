@@ -60,6 +60,10 @@ def main():
     ap.add_argument("--scale-down-ms", type=float, default=0.0,
                     help="autoscale: how long demand must stay below capacity before a replica is released (0 = the default)")
     ap.add_argument("--max-decode", type=int, default=1, help="autoscale: decode replicas the planner may use")
+    ap.add_argument("--arrival-window-ms", type=float, default=0.0, help="autoscale: also size the prefill side by the "
+                    "arrival rate over this window (feature planner_arrival_rate); 0 = off")
+    ap.add_argument("--extra-features", default="", help="comma-separated router features added to the mode's set "
+                    "(e.g. migrate_progressive)")
     ap.add_argument("--trace", default="fixed", choices=["fixed", "gamma"],
                     help="fixed: evenly spaced requests of --prompt-len / --new-tokens; gamma: Gamma inter-arrivals (CV 4) whose "
                          "rate steps from --base-rate to --burst-rate at --base-s, lognormal prompt lengths (median "
@@ -160,10 +164,15 @@ def run_router(a, world, states, cfg_model, backend):
         extra = dict(tokens_prefilled_per_sec=max(1, int(a.prefill_rate * a.horizon_ms * 1e-3)),
                      tokens_transferred_per_sec=5000000, max_prefill=world - 1, max_decode=max(1, a.max_decode), min_prefill=1,
                      min_decode=1)
+        if a.arrival_window_ms > 0:
+            feats += ",planner_arrival_rate"
+            extra.update(prefill_rate_per_sec=float(a.prefill_rate), arrival_window_ms=float(a.arrival_window_ms))
         if a.scale_down_ms > 0:
             # a CV-4 arrival process has long gaps inside a burst: the patience has to cover them, or replicas are
             # released and reloaded between two clusters of arrivals
             extra["scale_down_threshold_ms"] = a.scale_down_ms
+    if a.extra_features:
+        feats += "," + a.extra_features.strip(",")
     cfg = controller_config_from_cluster({"init_states": states, "machines": [0] * world}, 1, feats,
                                          max_blocks_per_replica=a.pages - 64, block_size=64, max_prefill_tokens=8192,
                                          model_layers=cfg_model.layers, max_batch_seqs=256, **extra)
