@@ -368,17 +368,19 @@ class RouterApp:
             return web.json_response({"error": err, "error_type": "validation"}, status=422)
         resp = web.StreamResponse(headers={"Content-Type": "text/event-stream", "Cache-Control": "no-cache"})
         await resp.prepare(req)
-        n = 0
+        ids: List[int] = []
         agen = self._run(toks, g)
         try:
             async for tok, final, done in agen:
                 if done is not None:
                     continue
-                n += 1
+                ids.append(tok)
                 ev = {"token": {"id": tok, "text": self.tok.piece(tok), "logprob": 0.0, "special": False},
                       "generated_text": None, "details": None}
                 if final:
-                    ev["details"] = {"finish_reason": FINISH_REASONS.get(int(final), "length"), "generated_tokens": n}
+                    # the last event carries the whole text and why the request ended
+                    ev["generated_text"] = self.tok.decode(ids)
+                    ev["details"] = {"finish_reason": FINISH_REASONS.get(int(final), "length"), "generated_tokens": len(ids)}
                 await resp.write(f"data:{json.dumps(ev)}\n\n".encode())
             await resp.write_eof()
         except (ConnectionResetError, asyncio.CancelledError):

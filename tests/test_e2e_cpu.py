@@ -988,6 +988,8 @@ def test_end_of_sequence_token_and_stop_sequences_end_a_request():
                 assert r.status == 200 and r.headers["Content-Type"].startswith("text/event-stream")
                 events = [json.loads(l[5:]) async for l in r.content if l.startswith(b"data:")]
                 assert len(events) == 3 and events[-1]["details"]["finish_reason"] == "length"
+                assert events[0]["generated_text"] is None                       # the last event carries the whole text
+                assert events[-1]["generated_text"] == " ".join(f"<{e['token']['id']}>" for e in events)
         for _ in range(100):
             if rt.ctl.idle() and not rt.requests and not rt.cached and all(not b.batches for b in backends):
                 break
