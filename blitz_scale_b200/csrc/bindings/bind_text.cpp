@@ -65,6 +65,7 @@ void bind_text(py::module_& m) {
       .def("decode_bytes", [](const Tokenizer& t, const std::vector<int32_t>& ids, bool skip) { return py::bytes(t.decode(ids, skip)); },
            py::arg("ids"), py::arg("skip_special_tokens") = true)
       .def("num_ids", &Tokenizer::num_ids)
+      .def("is_special", &Tokenizer::is_special)
       .def("get_id", &Tokenizer::get_id)
       .def("token", &Tokenizer::token);
 

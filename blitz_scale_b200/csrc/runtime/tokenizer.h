@@ -91,12 +91,20 @@ class Tokenizer {
         bool special = false;
         if (const json::Value* sp = a.find("special")) special = sp->type == json::Value::Bool && sp->b;
         t.added_.push_back({content, id, special});
+        if (id >= 0) {
+          if (static_cast<size_t>(id) >= t.added_flag_.size()) t.added_flag_.resize(static_cast<size_t>(id) + 1, 0);
+          t.added_flag_[static_cast<size_t>(id)] = special ? 2 : 1;
+        }
       }
     t.init_byte_maps();
     return t;
   }
 
   int32_t num_ids() const { return static_cast<int32_t>(id_to_token_.size()); }
+  // An added token that the tokenizer file marks as special (end-of-text and the like).
+  bool is_special(int32_t id) const {
+    return id >= 0 && static_cast<size_t>(id) < added_flag_.size() && added_flag_[static_cast<size_t>(id)] == 2;
+  }
   // -1 when the token string is unknown.
   int32_t get_id(const std::string& token) const {
     auto it = vocab_.find(token);
@@ -206,13 +214,10 @@ class Tokenizer {
     if (static_cast<size_t>(id) >= id_to_token_.size()) id_to_token_.resize(static_cast<size_t>(id) + 1);
     id_to_token_[static_cast<size_t>(id)] = s;
   }
+  // per id: 0 ordinary, 1 added token, 2 added and special (looked up for every token of a decode)
+  std::vector<uint8_t> added_flag_;
   bool is_added(int32_t id) const {
-    for (const Added& a : added_) if (a.id == id) return true;
-    return false;
-  }
-  bool is_special(int32_t id) const {
-    for (const Added& a : added_) if (a.id == id) return a.special;
-    return false;
+    return id >= 0 && static_cast<size_t>(id) < added_flag_.size() && added_flag_[static_cast<size_t>(id)] != 0;
   }
   static bool mentions(const json::Value* v, const char* what) {
     if (!v) return false;

@@ -47,6 +47,9 @@ class WordHashTokenizer:
     def piece(self, tid: int) -> str:
         return f"<{tid}>"
 
+    def special(self, tid: int) -> bool:
+        return False
+
 
 class NativeTokenizer:
     """tokenizer.json through the native BPE tokenizer (the reference runs a pool of tokenizer workers,
@@ -64,6 +67,9 @@ class NativeTokenizer:
 
     def piece(self, tid: int) -> str:
         return self.t.decode([tid], False)
+
+    def special(self, tid: int) -> bool:
+        return bool(self.t.is_special(tid))
 
 
 def _pct(xs: List[float], q: float) -> float:
@@ -350,7 +356,7 @@ class RouterApp:
             chooser = getattr(g, "chooser", None)
             details = {"finish_reason": reason, "generated_tokens": len(out), "prefill": [],
                        "seed": int(chooser.seed) if chooser is not None else None,
-                       "tokens": [{"id": t, "text": self.tok.piece(t), "logprob": 0.0, "special": False} for t in out]}
+                       "tokens": [{"id": t, "text": self.tok.piece(t), "logprob": 0.0, "special": self.tok.special(t)} for t in out]}
         text = self.tok.decode(out)
         if (body.get("parameters") or {}).get("return_full_text") and isinstance(body.get("inputs"), str):
             text = body["inputs"] + text
@@ -375,7 +381,7 @@ class RouterApp:
                 if done is not None:
                     continue
                 ids.append(tok)
-                ev = {"token": {"id": tok, "text": self.tok.piece(tok), "logprob": 0.0, "special": False},
+                ev = {"token": {"id": tok, "text": self.tok.piece(tok), "logprob": 0.0, "special": self.tok.special(tok)},
                       "generated_text": None, "details": None}
                 if final:
                     # the last event carries the whole text and why the request ended

@@ -41,6 +41,7 @@ def test_byte_level_bpe_matches_reference_library(trained):
         assert t.decode(ids, False) == s
     assert t.decode(t.encode("<|begin|>hi<|end|>"), True) == "hi"
     assert t.get_id("<|end|>") == ref.token_to_id("<|end|>") and t.get_id("no such token") == -1
+    assert t.is_special(t.get_id("<|end|>")) and not t.is_special(t.get_id("a")) and not t.is_special(-1) and not t.is_special(10 ** 6)
     # ids that a model may emit in any order: bytes that form no character decode to U+FFFD, as in the library
     import random
     rng = random.Random(5)
