@@ -226,3 +226,8 @@ def render_proto() -> str:
             out.append("  }")
         out.append("}")
     return "\n".join(out) + "\n"
+
+
+if __name__ == "__main__":
+    # `python -m blitz_scale_b200.pb.schema > generate.proto`: the contract as text, for clients in other languages
+    print(render_proto(), end="")
