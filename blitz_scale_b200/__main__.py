@@ -11,6 +11,7 @@
     report        figures of a run (TTFT / TBT vs SLO, replica states, token rates) as HTML -> utils.plots
     chrome-trace  router log (+ client.jsonl) as a Chrome / Perfetto trace                  -> utils.tracing
     build         compile the kernel library and the native core                        -> build
+    proto         print the gRPC contract as a .proto file                              -> pb.schema
 """
 import importlib
 import sys
@@ -21,7 +22,7 @@ COMMANDS = {
     "convert": "blitz_scale_b200.models.convert", "repl": "blitz_scale_b200.utils.worker_client",
     "logs": "blitz_scale_b200.utils.logtools", "trace": "blitz_scale_b200.sim.trace_tools",
     "report": "blitz_scale_b200.utils.plots", "chrome-trace": "blitz_scale_b200.utils.tracing",
-    "build": "blitz_scale_b200.build",
+    "build": "blitz_scale_b200.build", "proto": "blitz_scale_b200.pb.schema",
 }
 
 
@@ -31,7 +32,7 @@ def main() -> int:
         return 0 if len(sys.argv) >= 2 and sys.argv[1] in ("-h", "--help") else 2
     mod = importlib.import_module(COMMANDS[sys.argv[1]])
     sys.argv = [f"blitz_scale_b200 {sys.argv[1]}"] + sys.argv[2:]
-    rc = mod.main()
+    rc = getattr(mod, "cli", mod.main)()      # `cli` where a module keeps a command-line wrapper around `main`
     return int(rc or 0)
 
 

@@ -206,8 +206,13 @@ def main(argv: Optional[Iterable[str]] = None) -> int:
     return 0
 
 
-if __name__ == "__main__":
+def cli(argv: Optional[Iterable[str]] = None) -> int:
+    """`main` for the command line: what is wrong with the arguments or the files is one line, not a traceback."""
     try:
-        raise SystemExit(main())
+        return main(argv)
     except (OSError, KeyError, ValueError, RuntimeError) as e:   # missing source, unknown model, tensor of another shape
         raise SystemExit(f"convert: {e}")
+
+
+if __name__ == "__main__":
+    raise SystemExit(cli())

@@ -228,6 +228,11 @@ def render_proto() -> str:
     return "\n".join(out) + "\n"
 
 
-if __name__ == "__main__":
-    # `python -m blitz_scale_b200.pb.schema > generate.proto`: the contract as text, for clients in other languages
+def main() -> int:
+    """`python -m blitz_scale_b200.pb.schema > generate.proto`: the contract as text, for clients in other languages."""
     print(render_proto(), end="")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
