@@ -32,7 +32,11 @@ def main() -> int:
         return 0 if len(sys.argv) >= 2 and sys.argv[1] in ("-h", "--help") else 2
     mod = importlib.import_module(COMMANDS[sys.argv[1]])
     sys.argv = [f"blitz_scale_b200 {sys.argv[1]}"] + sys.argv[2:]
-    rc = getattr(mod, "cli", mod.main)()      # `cli` where a module keeps a command-line wrapper around `main`
+    try:
+        rc = getattr(mod, "cli", mod.main)()      # `cli` where a module keeps a command-line wrapper around `main`
+    except (FileNotFoundError, IsADirectoryError, PermissionError) as e:
+        print(f"{sys.argv[0]}: {e}", file=sys.stderr)   # a path that cannot be read or written: one line is enough
+        return 1
     return int(rc or 0)
 
 
