@@ -68,6 +68,7 @@ async def _one(session, endpoint: str, idx: int, item, t0: float, out: list, voc
                            generated_tokens=int(g("x-generated-tokens")))
                 if record_tokens and data.get("details"):
                     rec["tokens"] = [t["id"] for t in data["details"]["tokens"]]
+                    rec["finish_reason"] = data["details"].get("finish_reason")
             else:
                 rec["error"] = data.get("error")
     except Exception as e:  # noqa: BLE001
